@@ -1,0 +1,1211 @@
+// Engine implementation: device memory, weight upload (BLOBFILE directories and raw/GGUF tensors),
+// kernel submission (direct or CUDA-graph replay, programmatic dependent launch between stages).
+#include "engine.h"
+
+#include <sys/stat.h>
+
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <mutex>
+#include <sstream>
+
+namespace esp {
+
+// ---------------------------------------------------------------------------------------------- errors
+
+static thread_local std::string g_last_error;
+static std::atomic<int> g_force_failure{0};
+
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+const char* last_error_cstr() { return g_last_error.c_str(); }
+bool force_failure_enabled() { return g_force_failure.load() != 0; }
+void set_force_failure(int on) { g_force_failure.store(on ? 1 : 0); }
+
+#define ESP_CUDA_TRY(expr)                                                                              \
+    do {                                                                                                \
+        cudaError_t _e = (expr);                                                                        \
+        if (_e != cudaSuccess) {                                                                        \
+            set_last_error(std::string(#expr) + ": " + cudaGetErrorString(_e));                         \
+            return _e == cudaErrorMemoryAllocation ? ESP_CUDA_ERR_OUT_OF_MEMORY : ESP_CUDA_ERR_CUDA;    \
+        }                                                                                               \
+    } while (0)
+
+static int32_t fail(int32_t code, const std::string& msg) {
+    set_last_error(msg);
+    return code;
+}
+
+// ---------------------------------------------------------------------------------------------- kernels
+
+template <int WT>
+__global__ void __launch_bounds__(kThreads) k_qkv(const QkvArgs p) {
+    extern __shared__ float smem[];
+    // Before the previous stage has finished: pull this CTA's weight rows towards L2.
+    {
+        const int n_items = (p.m.q_dim + 2 * p.m.kv_dim) / 2;
+        int begin, end;
+        cta_range(n_items, blockIdx.x, gridDim.x, begin, end);
+        const int half = p.m.head_dim / 2, q_items = p.m.q_dim / 2, k_items = p.m.kv_dim / 2;
+        for (int item = begin + threadIdx.x; item < end; item += kThreads) {
+            const Weight* W;
+            int local, row0, row1;
+            if (item < q_items) { W = &p.lw.wq; local = item; }
+            else if (item < q_items + k_items) { W = &p.lw.wk; local = item - q_items; }
+            else { W = &p.lw.wv; local = item - q_items - k_items; }
+            if (item < q_items + k_items) { int h = local / half; row0 = h * p.m.head_dim + (local - h * half); row1 = row0 + half; }
+            else { row0 = 2 * local; row1 = row0 + 1; }
+            unsigned rb = (unsigned)weight_row_bytes(W->type, W->cols);
+            l2_prefetch(weight_row(*W, row0), rb);
+            l2_prefetch(weight_row(*W, row1), rb);
+        }
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    stage_qkv<WT>(p, blockIdx.x, gridDim.x, smem + 8, smem);
+}
+
+__global__ void __launch_bounds__(kAttThreads) k_attention(const AttArgs p) {
+    __shared__ float sm[128 + kAttSplitTokens + 8 + (kAttThreads / 32) * 128];
+    pdl_launch_dependents();
+    pdl_wait();
+    stage_attention(p, blockIdx.y, blockIdx.x, blockIdx.z, sm);
+}
+
+template <int WT, int EPI>
+__global__ void __launch_bounds__(kThreads) k_gemv(const GemvArgs p) {
+    extern __shared__ float smem[];
+    {
+        const int n_items = EPI == EPI_SWIGLU ? p.w.rows : (p.w.rows + 1) / 2;
+        int begin, end;
+        cta_range(n_items, blockIdx.x, gridDim.x, begin, end);
+        if (end > begin && threadIdx.x == 0) {
+            // a CTA's rows are contiguous: bulk prefetches of at most 32 KiB each
+            const size_t rb = weight_row_bytes(p.w.type, p.w.cols);
+            const int r0 = EPI == EPI_SWIGLU ? begin : begin * 2;
+            const int r1 = min(EPI == EPI_SWIGLU ? end : end * 2, p.w.rows);
+            size_t bytes = (size_t)(r1 - r0) * rb;
+            const uint8_t* b0 = weight_row(p.w, r0);
+            const uint8_t* b1 = EPI == EPI_SWIGLU ? weight_row(p.w_up, r0) : nullptr;
+            for (size_t off = 0; off < bytes; off += (32u << 10)) {
+                unsigned n = (unsigned)min((size_t)(32u << 10), bytes - off);
+                l2_prefetch(b0 + off, n);
+                if (b1) l2_prefetch(b1 + off, n);
+            }
+        }
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    stage_gemv<WT, EPI>(p, blockIdx.x, gridDim.x, smem + 8, smem);
+}
+
+__global__ void k_bump(RowState rs, int rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    bump_positions(rs, rows);
+}
+
+// GGUF blocks (array of structs, file order) -> the split layout of esp::Weight.
+__global__ void k_repack_q8_0(const uint8_t* __restrict__ blocks, int64_t n_blocks, int8_t* q, __half* scales) {
+    int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    const uint8_t* s = blocks + b * 34;
+    scales[b] = __ushort_as_half((unsigned short)(s[0] | (s[1] << 8)));
+    for (int i = 0; i < 32; i++) q[b * 32 + i] = (int8_t)s[2 + i];
+}
+__global__ void k_repack_q4_0(const uint8_t* __restrict__ blocks, int64_t n_blocks, uint8_t* q, __half* scales) {
+    int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    const uint8_t* s = blocks + b * 18;
+    scales[b] = __ushort_as_half((unsigned short)(s[0] | (s[1] << 8)));
+    for (int i = 0; i < 16; i++) q[b * 16 + i] = s[2 + i];
+}
+
+// out[i] = fp32(d) * q  (bit-exact GGUF dequantisation; used by the parity entry point)
+__global__ void k_dequant(const uint8_t* __restrict__ blocks, int type, int64_t n_blocks, float* out) {
+    int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    if (type == WT_Q8_0) {
+        const uint8_t* s = blocks + b * 34;
+        float d = __half2float(__ushort_as_half((unsigned short)(s[0] | (s[1] << 8))));
+        for (int i = 0; i < 32; i++) out[b * 32 + i] = __fmul_rn(d, (float)(int8_t)s[2 + i]);
+    } else {
+        const uint8_t* s = blocks + b * 18;
+        float d = __half2float(__ushort_as_half((unsigned short)(s[0] | (s[1] << 8))));
+        for (int i = 0; i < 16; i++) {
+            out[b * 32 + i] = __fmul_rn(d, (float)((int)(s[2 + i] & 15) - 8));
+            out[b * 32 + 16 + i] = __fmul_rn(d, (float)((int)(s[2 + i] >> 4) - 8));
+        }
+    }
+}
+
+__global__ void k_to_f32(const void* src, int type, int64_t n, float* dst) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (type == ESP_CUDA_F32) dst[i] = static_cast<const float*>(src)[i];
+    else dst[i] = emb_to_float(static_cast<const uint16_t*>(src)[i], type == ESP_CUDA_BF16 ? WT_BF16 : WT_F16);
+}
+__global__ void k_f32_to_f16(const float* src, int64_t n, __half* dst) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = __float2half_rn(src[i]);
+}
+
+// ---------------------------------------------------------------------------------------------- launch helpers
+
+template <typename Kern, typename... Args>
+static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s, const Args&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+template <int EPI>
+static cudaError_t launch_gemv_typed(int type, dim3 grid, size_t smem, cudaStream_t s, const GemvArgs& a) {
+    switch (type) {
+        case WT_F16: return launch_pdl(k_gemv<WT_F16, EPI>, grid, dim3(kThreads), smem, s, a);
+        case WT_BF16: return launch_pdl(k_gemv<WT_BF16, EPI>, grid, dim3(kThreads), smem, s, a);
+        case WT_Q8_0: return launch_pdl(k_gemv<WT_Q8_0, EPI>, grid, dim3(kThreads), smem, s, a);
+        case WT_Q4_0: return launch_pdl(k_gemv<WT_Q4_0, EPI>, grid, dim3(kThreads), smem, s, a);
+    }
+    return cudaErrorInvalidValue;
+}
+static cudaError_t launch_gemv(int epi, int type, dim3 grid, size_t smem, cudaStream_t s, const GemvArgs& a) {
+    switch (epi) {
+        case EPI_RESIDUAL: return launch_gemv_typed<EPI_RESIDUAL>(type, grid, smem, s, a);
+        case EPI_SWIGLU: return launch_gemv_typed<EPI_SWIGLU>(type, grid, smem, s, a);
+        case EPI_GELU: return launch_gemv_typed<EPI_GELU>(type, grid, smem, s, a);
+        case EPI_HEAD: return launch_gemv_typed<EPI_HEAD>(type, grid, smem, s, a);
+    }
+    return cudaErrorInvalidValue;
+}
+static cudaError_t launch_qkv(int type, dim3 grid, size_t smem, cudaStream_t s, const QkvArgs& a) {
+    switch (type) {
+        case WT_F16: return launch_pdl(k_qkv<WT_F16>, grid, dim3(kThreads), smem, s, a);
+        case WT_BF16: return launch_pdl(k_qkv<WT_BF16>, grid, dim3(kThreads), smem, s, a);
+        case WT_Q8_0: return launch_pdl(k_qkv<WT_Q8_0>, grid, dim3(kThreads), smem, s, a);
+        case WT_Q4_0: return launch_pdl(k_qkv<WT_Q4_0>, grid, dim3(kThreads), smem, s, a);
+    }
+    return cudaErrorInvalidValue;
+}
+
+static int epl_of(int type) { return type == WT_Q8_0 ? 16 : type == WT_Q4_0 ? 32 : 8; }
+static int xs_floats_rt(int type, int K) { int e = 32 * epl_of(type); return ((K + e - 1) / e) * e; }
+
+static void raise_smem_limits_on_current_device() {
+    // allow the GEMV stages to stage long vectors (up to 200 KB of dynamic shared memory)
+    const int bytes = 200 * 1024;
+#define ESP_SET(k) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes)
+#define ESP_SET_ALL(WT)                                                                 \
+    ESP_SET((k_gemv<WT, EPI_RESIDUAL>)); ESP_SET((k_gemv<WT, EPI_SWIGLU>));             \
+    ESP_SET((k_gemv<WT, EPI_GELU>)); ESP_SET((k_gemv<WT, EPI_HEAD>)); ESP_SET((k_qkv<WT>));
+    ESP_SET_ALL(WT_F16) ESP_SET_ALL(WT_BF16) ESP_SET_ALL(WT_Q8_0) ESP_SET_ALL(WT_Q4_0)
+#undef ESP_SET_ALL
+#undef ESP_SET
+}
+// Function attributes belong to a device: set them once per device ordinal.
+static void raise_smem_limits(int device) {
+    static std::mutex mu;
+    static bool done[64] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    if (device < 0 || device >= 64 || done[device]) return;
+    raise_smem_limits_on_current_device();
+    done[device] = true;
+}
+
+// ---------------------------------------------------------------------------------------------- engine
+
+Engine::Engine(const esp_cuda_config& cfg) : cfg_(cfg) {}
+
+Engine::~Engine() {
+    if (cfg_.device >= 0) cudaSetDevice(cfg_.device);
+    if (stream_) cudaStreamSynchronize(stream_);
+    for (auto& g : graphs_) cudaGraphExecDestroy(g.second);
+    for (auto e : prof_events_) cudaEventDestroy(e);
+    if (ev_begin_) cudaEventDestroy(ev_begin_);
+    if (ev_end_) cudaEventDestroy(ev_end_);
+    for (void* p : owned_) cudaFree(p);
+    if (h_rows_block_) cudaFreeHost(h_rows_block_);
+    if (h_next_) cudaFreeHost(h_next_);
+    if (stream_) cudaStreamDestroy(stream_);
+}
+
+static int32_t validate_config(const esp_cuda_config& c) {
+    // validateConfig, RealModelInferenceEngine.swift:7615-7634
+    if (c.n_layer <= 0 || c.n_head <= 0 || c.n_kv_head <= 0 || c.d_model <= 0 || c.head_dim <= 0 || c.hidden_dim <= 0 ||
+        c.vocab <= 0 || c.max_seq <= 0)
+        return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "invalid config: every dimension must be > 0");
+    if (c.n_head % c.n_kv_head != 0) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "invalid config: nHead must be a multiple of nKVHead");
+    if (c.architecture != ESP_CUDA_ARCH_LLAMA && c.architecture != ESP_CUDA_ARCH_GPT2)
+        return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "invalid config: unknown architecture");
+    if (c.max_batch < 1) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "invalid config: max_batch must be >= 1");
+    if (c.head_dim < 8 || c.head_dim > 128 || (c.head_dim & (c.head_dim - 1)))
+        return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "invalid config: head_dim must be a power of two in [8, 128]");
+    if (c.d_model % 8 != 0 || c.hidden_dim % 8 != 0)
+        return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "invalid config: d_model and hidden_dim must be multiples of 8");
+    if (c.tp_size > 1) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "tensor parallel engines are created through esp_cuda_create_tp");
+    return ESP_CUDA_OK;
+}
+
+template <typename T>
+static int32_t dev_alloc(std::vector<void*>& owned, T** out, size_t count, bool zero = true) {
+    void* p = nullptr;
+    size_t bytes = std::max<size_t>(count * sizeof(T), 16);
+    ESP_CUDA_TRY(cudaMalloc(&p, bytes));
+    owned.push_back(p);
+    if (zero) ESP_CUDA_TRY(cudaMemset(p, 0, bytes));
+    *out = static_cast<T*>(p);
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::init() {
+    int32_t rc = validate_config(cfg_);
+    if (rc) return rc;
+    int n_dev = 0;
+    cudaError_t e = cudaGetDeviceCount(&n_dev);
+    if (e != cudaSuccess || n_dev == 0)
+        return fail(ESP_CUDA_ERR_CUDA, std::string("no CUDA device available: ") + cudaGetErrorString(e));
+    if (cfg_.device < 0 || cfg_.device >= n_dev) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "device ordinal out of range");
+    ESP_CUDA_TRY(cudaSetDevice(cfg_.device));
+    cudaDeviceProp prop;
+    ESP_CUDA_TRY(cudaGetDeviceProperties(&prop, cfg_.device));
+    if (prop.major < 10) return fail(ESP_CUDA_ERR_CUDA, "this library is built for sm_100a (B200) only");
+    sm_count_ = prop.multiProcessorCount;
+    raise_smem_limits(cfg_.device);
+    ESP_CUDA_TRY(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+
+    m_.arch = cfg_.architecture; m_.n_layer = cfg_.n_layer; m_.n_head = cfg_.n_head; m_.n_kv_head = cfg_.n_kv_head;
+    m_.d_model = cfg_.d_model; m_.head_dim = cfg_.head_dim; m_.hidden = cfg_.hidden_dim; m_.vocab = cfg_.vocab;
+    m_.max_seq = cfg_.max_seq; m_.q_dim = cfg_.n_head * cfg_.head_dim; m_.kv_dim = cfg_.n_kv_head * cfg_.head_dim;
+    m_.n_seq = cfg_.max_batch; m_.eps = cfg_.norm_eps; m_.eos_token = cfg_.eos_token;
+
+    max_rows_ = std::max(cfg_.max_batch, 8);
+    n_splits_ = (m_.max_seq + kAttSplitTokens - 1) / kAttSplitTokens;
+    out_stride_ = m_.max_seq;
+
+    if ((rc = dev_alloc(owned_, &act_.hidden, (size_t)max_rows_ * m_.d_model))) return rc;
+    if ((rc = dev_alloc(owned_, &act_.q, (size_t)max_rows_ * m_.q_dim))) return rc;
+    if ((rc = dev_alloc(owned_, &act_.ctx, (size_t)max_rows_ * m_.q_dim))) return rc;
+    if ((rc = dev_alloc(owned_, &act_.act, (size_t)max_rows_ * m_.hidden))) return rc;
+    if ((rc = dev_alloc(owned_, &act_.att_part, (size_t)max_rows_ * m_.n_head * n_splits_ * (m_.head_dim + 2)))) return rc;
+    if ((rc = dev_alloc(owned_, &act_.att_ticket, (size_t)max_rows_ * m_.n_head))) return rc;
+    act_.logits = nullptr;
+    act_.debug = nullptr;
+    act_.debug_layer = -1;
+    size_t kv_elems = (size_t)m_.n_layer * m_.n_seq * m_.n_kv_head * m_.max_seq * m_.head_dim;
+    if ((rc = dev_alloc(owned_, &kv_.k, kv_elems))) return rc;
+    if ((rc = dev_alloc(owned_, &kv_.v, kv_elems))) return rc;
+
+    if ((rc = dev_alloc(owned_, &d_rows_block_, (size_t)6 * max_rows_))) return rc;
+    rs_.seq = d_rows_block_;
+    rs_.pos = d_rows_block_ + max_rows_;
+    rs_.tok = reinterpret_cast<uint32_t*>(d_rows_block_ + 2 * max_rows_);
+    rs_.active = d_rows_block_ + 3 * max_rows_;
+    rs_.n_out = d_rows_block_ + 4 * max_rows_;
+    rs_.limit = d_rows_block_ + 5 * max_rows_;
+    if ((rc = dev_alloc(owned_, &rs_.next, (size_t)max_rows_))) return rc;
+    if ((rc = dev_alloc(owned_, &rs_.out, (size_t)max_rows_ * out_stride_))) return rc;
+    rs_.out_stride = out_stride_;
+    if ((rc = dev_alloc(owned_, &rs_.best, (size_t)max_rows_))) return rc;
+    if ((rc = dev_alloc(owned_, &rs_.ticket, 4))) return rc;
+    ESP_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&h_rows_block_), sizeof(int) * 6 * max_rows_));
+    ESP_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&h_next_), sizeof(uint32_t) * max_rows_));
+    h_visible_.assign(cfg_.max_batch, 0);
+
+    if (m_.arch == ARCH_LLAMA) {
+        // cos/sin of applyHalfSplitRoPEPerHead (Engine.swift:6745-6772), evaluated on the host in fp32
+        int half = m_.head_dim / 2;
+        std::vector<float2> tab((size_t)m_.max_seq * half);
+        for (int pos = 0; pos < m_.max_seq; pos++)
+            for (int i = 0; i < half; i++) {
+                float freq = 1.0f / powf(cfg_.rope_theta, (float)(2 * i) / (float)m_.head_dim);
+                float ang = (float)pos * freq;
+                tab[(size_t)pos * half + i] = make_float2(cosf(ang), sinf(ang));
+            }
+        if ((rc = dev_alloc(owned_, &d_rope_, tab.size(), false))) return rc;
+        ESP_CUDA_TRY(cudaMemcpy(d_rope_, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice));
+    }
+    ESP_CUDA_TRY(cudaDeviceSynchronize());  // the zero-fills above ran on the default stream
+    return ESP_CUDA_OK;
+}
+
+// Canonical tensor names; aliases follow the candidate lists of Engine.swift:2066-2154.
+static std::string canonical_name(const std::string& n, int arch) {
+    if (n == "embeddings/token_embeddings") return "embeddings/token";
+    if (n == "embeddings/position_embeddings") return "embeddings/position";
+    if (n == "classifier") return "lm_head";
+    if (arch == ARCH_LLAMA) {
+        if (n == "final_norm_gamma" || n == "final_norm") return "rms_final";
+    } else {
+        if (n == "ln_f_gamma" || n == "rms_final") return "final_norm_gamma";
+        if (n == "ln_f_beta" || n == "rms_final_beta") return "final_norm_beta";
+    }
+    return n;
+}
+
+DeviceTensor* Engine::slot(const std::string& raw, int* rows, int* cols, bool* is_matrix, bool* is_embedding) {
+    std::string name = canonical_name(raw, m_.arch);
+    const int d = m_.d_model, q = m_.q_dim, kv = m_.kv_dim, h = m_.hidden, V = m_.vocab;
+    *is_matrix = false;
+    *is_embedding = false;
+    auto set = [&](int r, int c) { *rows = r; *cols = c; return &tensors_[name]; };
+    if (name == "embeddings/token") { *is_embedding = true; return set(V, d); }
+    if (name == "embeddings/position" && m_.arch == ARCH_GPT2) { *is_embedding = true; return set(m_.max_seq, d); }
+    if (name == "lm_head") { *is_matrix = true; return set(V, d); }
+    if (name == "rms_final" && m_.arch == ARCH_LLAMA) return set(1, d);
+    if ((name == "final_norm_gamma" || name == "final_norm_beta") && m_.arch == ARCH_GPT2) return set(1, d);
+    int l = -1;
+    char leaf[64];
+    if (sscanf(name.c_str(), "layers/%d/%63s", &l, leaf) == 2 && l >= 0 && l < m_.n_layer) {
+        std::string lf(leaf);
+        struct E { const char* n; int r, c; bool mat; int arch; };
+        const E tab[] = {
+            {"wq", q, d, true, -1}, {"wk", kv, d, true, -1}, {"wv", kv, d, true, -1}, {"wo", d, q, true, -1},
+            {"w1", h, d, true, -1}, {"w2", d, h, true, -1}, {"w3", h, d, true, ARCH_LLAMA},
+            {"rms_att", 1, d, false, ARCH_LLAMA}, {"rms_ffn", 1, d, false, ARCH_LLAMA},
+            {"ln_1_gamma", 1, d, false, ARCH_GPT2}, {"ln_1_beta", 1, d, false, ARCH_GPT2},
+            {"ln_2_gamma", 1, d, false, ARCH_GPT2}, {"ln_2_beta", 1, d, false, ARCH_GPT2},
+            {"bq", 1, q, false, ARCH_GPT2}, {"bk", 1, kv, false, ARCH_GPT2}, {"bv", 1, kv, false, ARCH_GPT2},
+            {"bo", 1, d, false, ARCH_GPT2}, {"b1", 1, h, false, ARCH_GPT2}, {"b2", 1, d, false, ARCH_GPT2},
+        };
+        for (const E& e : tab)
+            if (lf == e.n && (e.arch < 0 || e.arch == m_.arch)) { *is_matrix = e.mat; return set(e.r, e.c); }
+    }
+    return nullptr;
+}
+
+int32_t Engine::load_tensor(const char* name_c, int32_t type, const void* data, uint64_t nbytes) {
+    if (!name_c || !data) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "load_tensor: null argument");
+    if (finalized_) return fail(ESP_CUDA_ERR_STATE, "load_tensor: engine already finalized");
+    ESP_CUDA_TRY(cudaSetDevice(cfg_.device));
+    int rows = 0, cols = 0;
+    bool is_matrix = false, is_embedding = false;
+    DeviceTensor* t = slot(name_c, &rows, &cols, &is_matrix, &is_embedding);
+    if (!t) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, std::string("load_tensor: unknown tensor name '") + name_c + "'");
+    const uint64_t n = (uint64_t)rows * cols;
+    uint64_t expect;
+    switch (type) {
+        case ESP_CUDA_F32: expect = n * 4; break;
+        case ESP_CUDA_F16: case ESP_CUDA_BF16: expect = n * 2; break;
+        case ESP_CUDA_Q8_0: expect = n / 32 * 34; break;
+        case ESP_CUDA_Q4_0: expect = n / 32 * 18; break;
+        default: return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "load_tensor: unsupported tensor type");
+    }
+    if (nbytes != expect) {  // invalidWeightCount(path, expected, actual), Engine.swift:85-115
+        std::ostringstream os;
+        os << "invalid weight count for " << name_c << ": expected " << expect << " bytes, got " << nbytes;
+        return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, os.str());
+    }
+    const bool quant = type == ESP_CUDA_Q8_0 || type == ESP_CUDA_Q4_0;
+    if (quant && (!is_matrix || cols % 32 != 0))
+        return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "load_tensor: Q8_0/Q4_0 are valid for matrices with cols % 32 == 0 only");
+    if (t->loaded) return fail(ESP_CUDA_ERR_STATE, std::string("load_tensor: tensor loaded twice: ") + name_c);
+    int32_t rc;
+    t->rows = rows; t->cols = cols;
+    void* staging = nullptr;
+    if (quant || type == ESP_CUDA_F32 || (!is_matrix && !is_embedding)) {
+        ESP_CUDA_TRY(cudaMalloc(&staging, std::max<uint64_t>(nbytes, 16)));
+        cudaError_t e = cudaMemcpyAsync(staging, data, nbytes, cudaMemcpyDefault, stream_);
+        if (e != cudaSuccess) { cudaFree(staging); ESP_CUDA_TRY(e); }
+    }
+    const int T = 256;
+    if (!is_matrix && !is_embedding) {  // norm gains / biases: keep an fp32 copy
+        if (quant) { cudaFree(staging); return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "vectors cannot be quantised"); }
+        if ((rc = dev_alloc(owned_, &t->f32, n, false))) { cudaFree(staging); return rc; }
+        k_to_f32<<<(unsigned)((n + T - 1) / T), T, 0, stream_>>>(staging, type, (int64_t)n, t->f32);
+        t->type = ESP_CUDA_F32;
+    } else if (quant) {
+        uint64_t nb = n / 32;
+        __half* sc = nullptr;
+        if ((rc = dev_alloc(owned_, &sc, nb, false))) { cudaFree(staging); return rc; }
+        t->scales = sc;
+        if (type == ESP_CUDA_Q8_0) {
+            int8_t* qd = nullptr;
+            if ((rc = dev_alloc(owned_, &qd, n, false))) { cudaFree(staging); return rc; }
+            k_repack_q8_0<<<(unsigned)((nb + T - 1) / T), T, 0, stream_>>>(static_cast<uint8_t*>(staging), (int64_t)nb, qd, sc);
+            t->data = qd;
+        } else {
+            uint8_t* qd = nullptr;
+            if ((rc = dev_alloc(owned_, &qd, n / 2, false))) { cudaFree(staging); return rc; }
+            k_repack_q4_0<<<(unsigned)((nb + T - 1) / T), T, 0, stream_>>>(static_cast<uint8_t*>(staging), (int64_t)nb, qd, sc);
+            t->data = qd;
+        }
+        t->type = type;
+    } else if (type == ESP_CUDA_F32) {  // matrices and embeddings are stored as fp16
+        __half* hd = nullptr;
+        if ((rc = dev_alloc(owned_, &hd, n, false))) { cudaFree(staging); return rc; }
+        k_f32_to_f16<<<(unsigned)((n + T - 1) / T), T, 0, stream_>>>(static_cast<float*>(staging), (int64_t)n, hd);
+        t->data = hd;
+        t->type = ESP_CUDA_F16;
+    } else {
+        uint16_t* hd = nullptr;
+        if ((rc = dev_alloc(owned_, &hd, n, false))) return rc;
+        ESP_CUDA_TRY(cudaMemcpyAsync(hd, data, nbytes, cudaMemcpyDefault, stream_));
+        t->data = hd;
+        t->type = type;
+    }
+    cudaError_t e = cudaStreamSynchronize(stream_);
+    if (staging) cudaFree(staging);
+    ESP_CUDA_TRY(e);
+    ESP_CUDA_TRY(cudaGetLastError());
+    t->loaded = true;
+    return ESP_CUDA_OK;
+}
+
+static bool path_exists(const std::string& p) { struct stat st; return stat(p.c_str(), &st) == 0; }
+static bool is_directory(const std::string& p) { struct stat st; return stat(p.c_str(), &st) == 0 && S_ISDIR(st.st_mode); }
+
+// BlobWeightLoader.load (Sources/ModelSupport/BlobWeightLoader.swift:25-92): header checks and payload read.
+static int32_t read_blob(const std::string& path, std::vector<uint16_t>& out) {
+    std::ifstream f(path, std::ios::binary);
+    if (!f) return fail(ESP_CUDA_ERR_IO, "missing weight file: " + path);
+    uint8_t header[128];
+    f.read(reinterpret_cast<char*>(header), 128);
+    if (f.gcount() < 128) return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "truncatedHeader: " + path);
+    uint32_t magic, size, off;
+    memcpy(&magic, header + 64, 4); memcpy(&size, header + 72, 4); memcpy(&off, header + 80, 4);
+    if (magic != 0xDEADBEEFu) return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "invalidMagic: " + path);
+    if (off != 128u) return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "invalidDataOffset: " + path);
+    if (size % 2u) return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "invalidPayloadSize: " + path);
+    out.resize(size / 2);
+    f.read(reinterpret_cast<char*>(out.data()), size);
+    if ((uint32_t)f.gcount() != size) return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "truncatedPayload: " + path);
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::load_directory(const char* dir_c) {
+    std::string dir(dir_c ? dir_c : "");
+    if (!is_directory(dir)) return fail(ESP_CUDA_ERR_IO, "weight directory not found: " + dir);
+    auto load_first = [&](std::initializer_list<const char*> cands, const char* label) -> int32_t {
+        for (const char* c : cands) {
+            std::string p = dir + "/" + c + ".bin";
+            if (!path_exists(p)) continue;
+            std::vector<uint16_t> buf;
+            int32_t rc = read_blob(p, buf);
+            if (rc) return rc;
+            return load_tensor(c, ESP_CUDA_F16, buf.data(), buf.size() * 2);
+        }
+        return fail(ESP_CUDA_ERR_IO, std::string("missing ") + label + " in " + dir);
+    };
+    int32_t rc;
+    if ((rc = load_first({"embeddings/token", "embeddings/token_embeddings"}, "token embedding"))) return rc;
+    if ((rc = load_first({"lm_head", "classifier"}, "lm head"))) return rc;
+    if (m_.arch == ARCH_GPT2) {
+        if ((rc = load_first({"embeddings/position", "embeddings/position_embeddings"}, "position embedding"))) return rc;
+        if ((rc = load_first({"final_norm_gamma", "ln_f_gamma", "rms_final"}, "final norm gamma"))) return rc;
+        if ((rc = load_first({"final_norm_beta", "ln_f_beta", "rms_final_beta"}, "final norm beta"))) return rc;
+    } else {
+        if ((rc = load_first({"rms_final", "final_norm_gamma", "final_norm"}, "final norm gamma"))) return rc;
+    }
+    const char* llama[] = {"rms_att", "wq", "wk", "wv", "wo", "rms_ffn", "w1", "w2", "w3"};
+    const char* gpt2[] = {"ln_1_gamma", "ln_1_beta", "wq", "wk", "wv", "wo", "bq", "bk", "bv", "bo",
+                          "ln_2_gamma", "ln_2_beta", "w1", "b1", "w2", "b2"};
+    for (int l = 0; l < m_.n_layer; l++) {
+        const char* const* names = m_.arch == ARCH_GPT2 ? gpt2 : llama;
+        int n = m_.arch == ARCH_GPT2 ? 16 : 9;
+        for (int i = 0; i < n; i++) {
+            std::string name = "layers/" + std::to_string(l) + "/" + names[i];
+            std::vector<uint16_t> buf;
+            if ((rc = read_blob(dir + "/" + name + ".bin", buf))) return rc;
+            if ((rc = load_tensor(name.c_str(), ESP_CUDA_F16, buf.data(), buf.size() * 2))) return rc;
+        }
+        if (m_.arch == ARCH_LLAMA && (path_exists(dir + "/layers/" + std::to_string(l) + "/q_norm.bin") ||
+                                      path_exists(dir + "/layers/" + std::to_string(l) + "/k_norm.bin")))
+            return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "per-head q_norm/k_norm weights are not supported by this build");
+    }
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::finalize() {
+    if (finalized_) return ESP_CUDA_OK;
+    auto need = [&](const std::string& n) { auto it = tensors_.find(n); return it != tensors_.end() && it->second.loaded; };
+    std::vector<std::string> req = {"embeddings/token", "lm_head"};
+    if (m_.arch == ARCH_GPT2) { req.push_back("embeddings/position"); req.push_back("final_norm_gamma"); req.push_back("final_norm_beta"); }
+    else req.push_back("rms_final");
+    for (int l = 0; l < m_.n_layer; l++) {
+        std::string p = "layers/" + std::to_string(l) + "/";
+        if (m_.arch == ARCH_GPT2)
+            for (const char* n : {"ln_1_gamma", "ln_1_beta", "wq", "wk", "wv", "wo", "bq", "bk", "bv", "bo", "ln_2_gamma", "ln_2_beta", "w1", "b1", "w2", "b2"}) req.push_back(p + n);
+        else
+            for (const char* n : {"rms_att", "wq", "wk", "wv", "wo", "rms_ffn", "w1", "w2", "w3"}) req.push_back(p + n);
+    }
+    for (auto& n : req)
+        if (!need(n)) return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "missing tensor: " + n);
+    for (int l = 0; l < m_.n_layer; l++) {
+        std::string p = "layers/" + std::to_string(l) + "/";
+        int tq = tensors_[p + "wq"].type;
+        if (tensors_[p + "wk"].type != tq || tensors_[p + "wv"].type != tq)
+            return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "wq/wk/wv of a layer must share one storage type");
+        if (m_.arch == ARCH_LLAMA && tensors_[p + "w1"].type != tensors_[p + "w3"].type)
+            return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "w1/w3 of a layer must share one storage type");
+    }
+    if (m_.arch == ARCH_GPT2 && tensors_["embeddings/position"].type != tensors_["embeddings/token"].type)
+        return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "token and position embeddings must share one storage type");
+    int32_t rc;
+    if ((rc = dev_alloc(owned_, &act_.logits, (size_t)max_rows_ * m_.vocab))) return rc;
+    size_t dbg = (size_t)m_.q_dim * 2 + 2 * m_.kv_dim + 2 * m_.d_model + m_.hidden;
+    if ((rc = dev_alloc(owned_, &d_debug_, dbg))) return rc;
+    ESP_CUDA_TRY(cudaDeviceSynchronize());
+    finalized_ = true;
+    return reset();
+}
+
+Weight Engine::weight_of(const DeviceTensor& t) const {
+    Weight w;
+    w.data = t.data; w.scales = t.scales; w.rows = t.rows; w.cols = t.cols; w.type = t.type; w.pad = 0;
+    return w;
+}
+
+LayerWeights Engine::layer_weights(int l) const {
+    std::string p = "layers/" + std::to_string(l) + "/";
+    auto T = [&](const char* n) -> const DeviceTensor& { return tensors_.at(p + n); };
+    auto F = [&](const char* n) -> const float* { auto it = tensors_.find(p + n); return it == tensors_.end() ? nullptr : it->second.f32; };
+    LayerWeights lw{};
+    lw.wq = weight_of(T("wq")); lw.wk = weight_of(T("wk")); lw.wv = weight_of(T("wv")); lw.wo = weight_of(T("wo"));
+    lw.w1 = weight_of(T("w1")); lw.w2 = weight_of(T("w2"));
+    if (m_.arch == ARCH_LLAMA) {
+        lw.w3 = weight_of(T("w3"));
+        lw.norm1_g = F("rms_att"); lw.norm2_g = F("rms_ffn");
+    } else {
+        lw.w3 = Weight{nullptr, nullptr, 0, 0, 0, 0};
+        lw.norm1_g = F("ln_1_gamma"); lw.norm1_b = F("ln_1_beta"); lw.norm2_g = F("ln_2_gamma"); lw.norm2_b = F("ln_2_beta");
+        lw.bq = F("bq"); lw.bk = F("bk"); lw.bv = F("bv"); lw.bo = F("bo"); lw.b1 = F("b1"); lw.b2 = F("b2");
+    }
+    return lw;
+}
+
+size_t Engine::gemv_smem(int type, int K, bool with_tmp) const {
+    return sizeof(float) * (size_t)(8 + xs_floats_rt(type, K) + (with_tmp ? m_.d_model : 0));
+}
+
+int32_t Engine::check_ready(const char* what) const {
+    if (!finalized_) return fail(ESP_CUDA_ERR_STATE, std::string(what) + ": engine is not finalized");
+    if (force_failure_enabled()) return fail(ESP_CUDA_ERR_FORCED_FAILURE, std::string(what) + ": forced failure is enabled");
+    cudaError_t e = cudaSetDevice(cfg_.device);
+    if (e != cudaSuccess) return fail(ESP_CUDA_ERR_CUDA, cudaGetErrorString(e));
+    return ESP_CUDA_OK;
+}
+
+// One pass over the model for `rows` rows.  mode: STEP_FORWARD runs the layers on (tok, pos) of every active
+// row; STEP_HEAD runs final norm + LM head + argmax; STEP_FEEDBACK makes the head emit and feed back its token.
+int32_t Engine::launch_step(int rows, int mode, cudaStream_t s, bool profile) {
+    const bool gpt2 = m_.arch == ARCH_GPT2;
+    const int cap = sm_count_ * 4;
+    int launches = 0;
+    Activations a = act_;
+    a.logits = nullptr;
+    a.debug = debug_layer_ >= 0 ? d_debug_ : nullptr;
+    a.debug_layer = debug_layer_;
+    size_t ev = 0;
+    auto mark = [&]() { if (profile && ev < prof_events_.size()) cudaEventRecord(prof_events_[ev++], s); };
+    mark();
+    if (mode & STEP_FORWARD) {
+        const DeviceTensor& te = tensors_.at("embeddings/token");
+        for (int l = 0; l < m_.n_layer; l++) {
+            LayerWeights lw = layer_weights(l);
+            QkvArgs qa{};
+            qa.m = m_; qa.lw = lw; qa.layer = l; qa.rows = rows; qa.rs = rs_; qa.a = a; qa.kv = kv_;
+            qa.tok_emb = static_cast<const uint16_t*>(te.data);
+            qa.pos_emb = gpt2 ? static_cast<const uint16_t*>(tensors_.at("embeddings/position").data) : nullptr;
+            qa.emb_type = te.type == ESP_CUDA_BF16 ? WT_BF16 : WT_F16;
+            qa.rope = d_rope_;
+            qa.from_embedding = l == 0;
+            int items = (m_.q_dim + 2 * m_.kv_dim) / 2;
+            int grid = std::max(1, std::min((items + kWarps - 1) / kWarps, cap));
+            ESP_CUDA_TRY(launch_qkv(lw.wq.type, dim3(grid), gemv_smem(lw.wq.type, m_.d_model, true), s, qa));
+            launches++;
+            mark();
+            AttArgs aa{};
+            aa.m = m_; aa.layer = l; aa.rows = rows; aa.n_splits = n_splits_; aa.rs = rs_; aa.a = a; aa.kv = kv_;
+            ESP_CUDA_TRY(launch_pdl(k_attention, dim3(m_.n_head, rows, n_splits_), dim3(kAttThreads), 0, s, aa));
+            launches++;
+            mark();
+            GemvArgs ga{};
+            ga.m = m_; ga.rows = rows; ga.rs = rs_; ga.a = a; ga.layer = l;
+            // output projection + residual
+            ga.w = lw.wo; ga.bias = lw.bo; ga.norm = NORM_NONE; ga.in = act_.ctx; ga.in_stride = m_.q_dim;
+            ga.out = act_.hidden; ga.out_stride = m_.d_model; ga.debug_slot = 2 * m_.q_dim + 2 * m_.kv_dim;
+            items = (m_.d_model + 1) / 2;
+            grid = std::max(1, std::min((items + kWarps - 1) / kWarps, cap));
+            ESP_CUDA_TRY(launch_gemv(EPI_RESIDUAL, lw.wo.type, dim3(grid), gemv_smem(lw.wo.type, m_.q_dim, false), s, ga));
+            launches++;
+            // FFN up (+gate) with the activation fused
+            ga.w = lw.w1; ga.w_up = lw.w3; ga.bias = lw.b1; ga.norm = gpt2 ? NORM_LAYER : NORM_RMS;
+            ga.norm_g = lw.norm2_g; ga.norm_b = lw.norm2_b; ga.in = act_.hidden; ga.in_stride = m_.d_model;
+            ga.out = act_.act; ga.out_stride = m_.hidden; ga.debug_slot = 2 * m_.q_dim + 2 * m_.kv_dim + m_.d_model;
+            items = gpt2 ? (m_.hidden + 1) / 2 : m_.hidden;
+            grid = std::max(1, std::min((items + kWarps - 1) / kWarps, cap));
+            ESP_CUDA_TRY(launch_gemv(gpt2 ? EPI_GELU : EPI_SWIGLU, lw.w1.type, dim3(grid), gemv_smem(lw.w1.type, m_.d_model, false), s, ga));
+            launches++;
+            // FFN down + residual
+            ga.w = lw.w2; ga.w_up = Weight{nullptr, nullptr, 0, 0, 0, 0}; ga.bias = lw.b2; ga.norm = NORM_NONE;
+            ga.norm_g = ga.norm_b = nullptr; ga.in = act_.act; ga.in_stride = m_.hidden; ga.out = act_.hidden;
+            ga.out_stride = m_.d_model; ga.debug_slot = 2 * m_.q_dim + 2 * m_.kv_dim + m_.d_model + m_.hidden;
+            items = (m_.d_model + 1) / 2;
+            grid = std::max(1, std::min((items + kWarps - 1) / kWarps, cap));
+            ESP_CUDA_TRY(launch_gemv(EPI_RESIDUAL, lw.w2.type, dim3(grid), gemv_smem(lw.w2.type, m_.hidden, false), s, ga));
+            launches++;
+            mark();
+        }
+    }
+    if (mode & STEP_HEAD) {
+        const DeviceTensor& lh = tensors_.at("lm_head");
+        GemvArgs ga{};
+        ga.m = m_; ga.rows = rows; ga.rs = rs_; ga.a = a; ga.layer = -1; ga.debug_slot = -1;
+        if (cfg_.flags & ESP_CUDA_FLAG_KEEP_LOGITS) ga.a.logits = act_.logits;
+        ga.w = weight_of(lh); ga.norm = gpt2 ? NORM_LAYER : NORM_RMS;
+        ga.norm_g = tensors_.at(gpt2 ? "final_norm_gamma" : "rms_final").f32;
+        ga.norm_b = gpt2 ? tensors_.at("final_norm_beta").f32 : nullptr;
+        ga.in = act_.hidden; ga.in_stride = m_.d_model; ga.out = nullptr; ga.out_stride = 0;
+        ga.finalize_mode = ((mode & STEP_FEEDBACK) ? 1 : 0) | ((mode & STEP_FORWARD) ? 2 : 0);
+        int items = (m_.vocab + 1) / 2;
+        int grid = std::max(1, std::min((items + kWarps - 1) / kWarps, cap));
+        ESP_CUDA_TRY(launch_gemv(EPI_HEAD, lh.type, dim3(grid), gemv_smem(lh.type, m_.d_model, false), s, ga));
+        launches++;
+    } else if (mode & STEP_FORWARD) {
+        ESP_CUDA_TRY(launch_pdl(k_bump, dim3(1), dim3(64), 0, s, rs_, rows));
+        launches++;
+    }
+    mark();
+    launches_last_step_ = launches;
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::submit(int rows, int mode) {
+    if (force_failure_enabled()) return fail(ESP_CUDA_ERR_FORCED_FAILURE, "forced failure is enabled");
+    const bool direct = (cfg_.flags & ESP_CUDA_FLAG_NO_GRAPH) || debug_layer_ >= 0;
+    if (direct) {
+        bool profile = (cfg_.flags & ESP_CUDA_FLAG_NO_GRAPH) && (mode & STEP_FORWARD) && (mode & STEP_HEAD);
+        if (profile && prof_events_.empty()) {
+            prof_events_.resize((size_t)3 * m_.n_layer + 2);
+            for (auto& e : prof_events_) ESP_CUDA_TRY(cudaEventCreate(&e));
+        }
+        int32_t rc = launch_step(rows, mode, stream_, profile);
+        if (rc) return rc;
+        if (profile) {
+            ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+            timings_ = esp_cuda_timings{};
+            for (int l = 0; l < m_.n_layer; l++) {
+                float t;
+                cudaEventElapsedTime(&t, prof_events_[3 * l], prof_events_[3 * l + 1]); timings_.qkv_ms += t;
+                cudaEventElapsedTime(&t, prof_events_[3 * l + 1], prof_events_[3 * l + 2]); timings_.attention_ms += t;
+                cudaEventElapsedTime(&t, prof_events_[3 * l + 2], prof_events_[3 * l + 3]); timings_.ffn_ms += t;
+            }
+            float t;
+            cudaEventElapsedTime(&t, prof_events_[3 * m_.n_layer], prof_events_[3 * m_.n_layer + 1]); timings_.head_ms = t;
+            cudaEventElapsedTime(&t, prof_events_[0], prof_events_[3 * m_.n_layer + 1]); timings_.total_ms = t;
+        }
+        timings_.kernel_launches = launches_last_step_;
+        return ESP_CUDA_OK;
+    }
+    const int key = rows * 8 + mode;
+    auto it = graphs_.find(key);
+    if (it == graphs_.end()) {
+        cudaGraph_t graph = nullptr;
+        ESP_CUDA_TRY(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+        int32_t rc = launch_step(rows, mode, stream_, false);
+        cudaError_t e = cudaStreamEndCapture(stream_, &graph);
+        if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+        ESP_CUDA_TRY(e);
+        cudaGraphExec_t exec = nullptr;
+        e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        ESP_CUDA_TRY(e);
+        it = graphs_.emplace(key, exec).first;
+        launches_by_key_[key] = launches_last_step_;
+    }
+    launches_last_step_ = launches_by_key_[key];
+    timings_.kernel_launches = launches_last_step_;
+    ESP_CUDA_TRY(cudaGraphLaunch(it->second, stream_));
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::upload_rows(int rows, const int* seq, const int* pos, const uint32_t* tok, const int* active,
+                            const int* limit, bool zero_out_counts) {
+    if (rows < 1 || rows > max_rows_) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "row count out of range");
+    // the pinned block may still be in flight from the previous call
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    int* h = h_rows_block_;
+    for (int r = 0; r < max_rows_; r++) {
+        bool in = r < rows;
+        h[r] = in ? seq[r] : 0;
+        h[max_rows_ + r] = in ? pos[r] : 0;
+        h[2 * max_rows_ + r] = in && tok ? (int)tok[r] : 0;
+        h[3 * max_rows_ + r] = in ? (active ? active[r] : 1) : 0;
+        h[4 * max_rows_ + r] = 0;
+        h[5 * max_rows_ + r] = in && limit ? limit[r] : 0;
+    }
+    (void)zero_out_counts;
+    ESP_CUDA_TRY(cudaMemcpyAsync(d_rows_block_, h, sizeof(int) * 6 * max_rows_, cudaMemcpyHostToDevice, stream_));
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::reset() {
+    int32_t rc = check_ready("reset");
+    if (rc) return rc;
+    // reset() zeroes the caches and the hidden state (Engine.swift:613-635)
+    size_t kv_bytes = (size_t)m_.n_layer * m_.n_seq * m_.n_kv_head * m_.max_seq * m_.head_dim * sizeof(__half);
+    ESP_CUDA_TRY(cudaMemsetAsync(kv_.k, 0, kv_bytes, stream_));
+    ESP_CUDA_TRY(cudaMemsetAsync(kv_.v, 0, kv_bytes, stream_));
+    ESP_CUDA_TRY(cudaMemsetAsync(act_.hidden, 0, sizeof(float) * (size_t)max_rows_ * m_.d_model, stream_));
+    ESP_CUDA_TRY(cudaMemsetAsync(rs_.best, 0, sizeof(unsigned long long) * max_rows_, stream_));
+    ESP_CUDA_TRY(cudaMemsetAsync(rs_.ticket, 0, 16, stream_));
+    ESP_CUDA_TRY(cudaMemsetAsync(act_.att_ticket, 0, sizeof(unsigned int) * (size_t)max_rows_ * m_.n_head, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    std::fill(h_visible_.begin(), h_visible_.end(), 0);
+    for (auto& c : checkpoints_) c.visible = -1;
+    pending_verify_ = 0;
+    return ESP_CUDA_OK;
+}
+
+// Feeds one token to each of `rows` rows (row r = sequence seq[r] at its current position) and optionally
+// selects the next greedy token of each row.
+int32_t Engine::feed_rows(int rows, const int* seq, const uint32_t* tok, bool with_head, uint32_t* next_out) {
+    std::vector<int> pos(rows);
+    std::vector<int> extra(m_.n_seq, 0);
+    for (int r = 0; r < rows; r++) {
+        int s = seq[r];
+        if (s < 0 || s >= m_.n_seq) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "sequence index out of range");
+        pos[r] = h_visible_[s] + extra[s]++;
+        if (pos[r] >= m_.max_seq) {  // advance guard, Engine.swift:673-677
+            std::ostringstream os;
+            os << "position " << pos[r] << " exceeds context " << m_.max_seq;
+            return fail(ESP_CUDA_ERR_OUT_OF_RANGE, os.str());
+        }
+        if (tok[r] >= (uint32_t)m_.vocab) {  // token guard, Engine.swift:687-689
+            std::ostringstream os;
+            os << "token " << tok[r] << " is outside vocab " << m_.vocab;
+            return fail(ESP_CUDA_ERR_OUT_OF_RANGE, os.str());
+        }
+    }
+    int32_t rc = upload_rows(rows, seq, pos.data(), tok, nullptr, nullptr, true);
+    if (rc) return rc;
+    if ((rc = submit(rows, STEP_FORWARD | (with_head ? STEP_HEAD : 0)))) return rc;
+    if (with_head) ESP_CUDA_TRY(cudaMemcpyAsync(h_next_, rs_.next, sizeof(uint32_t) * rows, cudaMemcpyDeviceToHost, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    for (int s = 0; s < m_.n_seq; s++) h_visible_[s] += extra[s];
+    if (with_head && next_out) memcpy(next_out, h_next_, sizeof(uint32_t) * rows);
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::feed(int rows, const int* seq, const uint32_t* tok, bool with_head, uint32_t* next_out) {
+    int32_t rc = check_ready("feed");
+    if (rc) return rc;
+    if (!seq || !tok || rows < 1 || rows > max_rows_) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "feed: bad arguments");
+    rc = feed_rows(rows, seq, tok, with_head, next_out);
+    if (rc == ESP_CUDA_OK && rows > 1 && seq[rows - 1] == 0 && seq[0] == 0) {
+        ESP_CUDA_TRY(cudaMemcpyAsync(act_.hidden, act_.hidden + (size_t)(rows - 1) * m_.d_model, sizeof(float) * m_.d_model,
+                                     cudaMemcpyDeviceToDevice, stream_));
+        ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    }
+    return rc;
+}
+
+int32_t Engine::advance(uint32_t token) {
+    int32_t rc = check_ready("advance");
+    if (rc) return rc;
+    int seq = 0;
+    return feed_rows(1, &seq, &token, false, nullptr);
+}
+
+int32_t Engine::decode_step(uint32_t token, uint32_t* next) {
+    int32_t rc = check_ready("decode_step");
+    if (rc) return rc;
+    if (!next) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "decode_step: null output");
+    int seq = 0;
+    return feed_rows(1, &seq, &token, true, next);
+}
+
+int32_t Engine::prefill(const uint32_t* tokens, int32_t n) {
+    int32_t rc = check_ready("prefill");
+    if (rc) return rc;
+    if (!tokens || n <= 0) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "Prompt tokens must not be empty");
+    if ((rc = reset())) return rc;
+    // the prompt is processed in chunks of rows that share sequence 0 at consecutive positions
+    const int chunk = std::min(max_rows_, 8);
+    std::vector<int> seq(chunk, 0);
+    for (int i = 0; i < n; i += chunk) {
+        int c = std::min(chunk, n - i);
+        if ((rc = feed_rows(c, seq.data(), tokens + i, false, nullptr))) return rc;
+        if (c > 1)  // the last row's hidden state is the sequence's lastHidden
+            ESP_CUDA_TRY(cudaMemcpyAsync(act_.hidden, act_.hidden + (size_t)(c - 1) * m_.d_model, sizeof(float) * m_.d_model,
+                                         cudaMemcpyDeviceToDevice, stream_));
+    }
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::select_greedy(uint32_t* token) {
+    int32_t rc = check_ready("select_greedy");
+    if (rc) return rc;
+    if (!token) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "select_greedy: null output");
+    int seq = 0, pos = h_visible_[0];
+    if ((rc = upload_rows(1, &seq, &pos, nullptr, nullptr, nullptr, true))) return rc;
+    if ((rc = submit(1, STEP_HEAD))) return rc;
+    ESP_CUDA_TRY(cudaMemcpyAsync(h_next_, rs_.next, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    *token = h_next_[0];
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::get_logits(int32_t seq, float* out, int32_t vocab) {
+    int32_t rc = check_ready("get_logits");
+    if (rc) return rc;
+    if (!out || vocab != m_.vocab) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "get_logits: output must hold exactly vocab floats");
+    if (seq < 0 || seq >= m_.n_seq) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "sequence index out of range");
+    int rows = seq + 1;
+    std::vector<int> s(rows), p(rows), a(rows, 0);
+    for (int r = 0; r < rows; r++) { s[r] = r; p[r] = h_visible_[r]; }
+    a[seq] = 1;
+    if ((rc = upload_rows(rows, s.data(), p.data(), nullptr, a.data(), nullptr, true))) return rc;
+    uint32_t saved = cfg_.flags;
+    int saved_dbg = debug_layer_;
+    cfg_.flags |= ESP_CUDA_FLAG_KEEP_LOGITS | ESP_CUDA_FLAG_NO_GRAPH;
+    rc = launch_step(rows, STEP_HEAD, stream_, false);
+    cfg_.flags = saved;
+    debug_layer_ = saved_dbg;
+    if (rc) return rc;
+    ESP_CUDA_TRY(cudaMemcpyAsync(out, act_.logits + (size_t)seq * m_.vocab, sizeof(float) * m_.vocab, cudaMemcpyDeviceToHost, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::checkpoint(int32_t* id) {
+    int32_t rc = check_ready("checkpoint");
+    if (rc) return rc;
+    if (!id) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "checkpoint: null output");
+    Checkpoint c;
+    c.visible = h_visible_[0];
+    if ((rc = dev_alloc(owned_, &c.hidden, (size_t)m_.d_model, false))) return rc;
+    ESP_CUDA_TRY(cudaMemcpyAsync(c.hidden, act_.hidden, sizeof(float) * m_.d_model, cudaMemcpyDeviceToDevice, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    checkpoints_.push_back(c);
+    *id = (int32_t)checkpoints_.size() - 1;
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::rollback(int32_t id) {
+    int32_t rc = check_ready("rollback");
+    if (rc) return rc;
+    if (id < 0 || id >= (int32_t)checkpoints_.size() || checkpoints_[id].visible < 0)
+        return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "rollback: unknown checkpoint");
+    const Checkpoint& c = checkpoints_[id];
+    if (c.visible > h_visible_[0]) return fail(ESP_CUDA_ERR_STATE, "rollback: checkpoint is ahead of the current state");
+    ESP_CUDA_TRY(cudaMemcpyAsync(act_.hidden, c.hidden, sizeof(float) * m_.d_model, cudaMemcpyDeviceToDevice, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    h_visible_[0] = c.visible;
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::verify2(uint32_t current, uint32_t proposed, uint32_t* exact_next, uint32_t* exact_future) {
+    int32_t rc = check_ready("verify2");
+    if (rc) return rc;
+    if (!exact_next || !exact_future) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "verify2: null output");
+    if (h_visible_[0] + 2 > m_.max_seq) return fail(ESP_CUDA_ERR_OUT_OF_RANGE, "verify2: two positions do not fit in the context");
+    int saved = h_visible_[0];
+    int seq[2] = {0, 0};
+    uint32_t tok[2] = {current, proposed};
+    uint32_t next[2];
+    if ((rc = feed_rows(2, seq, tok, true, next))) return rc;
+    h_visible_[0] = saved;  // nothing is visible until commit()
+    pending_verify_ = 2;
+    *exact_next = next[0];
+    *exact_future = next[1];
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::commit(int32_t steps) {
+    int32_t rc = check_ready("commit");
+    if (rc) return rc;
+    if (pending_verify_ != 2) return fail(ESP_CUDA_ERR_STATE, "commit: no verified pair is pending");
+    if (steps < 1 || steps > 2) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "commit: steps must be 1 or 2");
+    if (steps == 2)
+        ESP_CUDA_TRY(cudaMemcpyAsync(act_.hidden, act_.hidden + m_.d_model, sizeof(float) * m_.d_model, cudaMemcpyDeviceToDevice, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    h_visible_[0] += steps;
+    pending_verify_ = 0;
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::prefill_batch(const uint32_t* tokens, int32_t n_seq, int32_t len) {
+    int32_t rc = check_ready("prefill_batch");
+    if (rc) return rc;
+    if (!tokens || len <= 0) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "Prompt tokens must not be empty");
+    if (n_seq < 1 || n_seq > cfg_.max_batch) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "n_seq exceeds max_batch");
+    if ((rc = reset())) return rc;
+    std::vector<int> seq(n_seq);
+    std::vector<uint32_t> tok(n_seq);
+    for (int s = 0; s < n_seq; s++) seq[s] = s;
+    for (int t = 0; t < len; t++) {
+        for (int s = 0; s < n_seq; s++) tok[s] = tokens[(size_t)s * len + t];
+        if ((rc = feed_rows(n_seq, seq.data(), tok.data(), false, nullptr))) return rc;
+    }
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::decode_step_batch(const uint32_t* tokens, int32_t n_seq, uint32_t* next) {
+    int32_t rc = check_ready("decode_step_batch");
+    if (rc) return rc;
+    if (!tokens || !next) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "decode_step_batch: null argument");
+    if (n_seq < 1 || n_seq > cfg_.max_batch) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "n_seq exceeds max_batch");
+    std::vector<int> seq(n_seq);
+    for (int s = 0; s < n_seq; s++) seq[s] = s;
+    return feed_rows(n_seq, seq.data(), tokens, true, next);
+}
+
+// Greedy generation for n_seq prompts of equal length.  After the prefill the loop is driven entirely from
+// the device: each step's head feeds its token back as the next step's input, so the host only enqueues
+// graph launches (generateIncrementalExactCPULlama, Engine.swift:6349-6431, with the limits of :1419-1426).
+int32_t Engine::generate_batch(const uint32_t* prompts, int32_t n_seq, int32_t n_prompt, int32_t max_tokens,
+                               uint32_t* out_tokens, int32_t* n_out, esp_cuda_generation_result* result) {
+    int32_t rc = check_ready("generate");
+    if (rc) return rc;
+    if (!prompts || !out_tokens || !n_out) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "generate: null argument");
+    if (n_prompt <= 0) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "Prompt tokens must not be empty");
+    if (max_tokens < 0) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "maxTokens must be >= 0");
+    if (n_prompt >= m_.max_seq) {
+        std::ostringstream os;
+        os << "Prompt token count " << n_prompt << " exceeds model context " << m_.max_seq - 1;
+        return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, os.str());
+    }
+    if (n_seq < 1 || n_seq > cfg_.max_batch) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "n_seq exceeds max_batch");
+    for (int64_t i = 0; i < (int64_t)n_seq * n_prompt; i++)
+        if (prompts[i] >= (uint32_t)m_.vocab) return fail(ESP_CUDA_ERR_OUT_OF_RANGE, "prompt token outside vocab");
+    const int eff = std::min(max_tokens, m_.max_seq - n_prompt);
+    if (result) { *result = esp_cuda_generation_result{}; result->prompt_tokens = n_prompt; }
+    for (int s = 0; s < n_seq; s++) n_out[s] = 0;
+    if (eff == 0) return ESP_CUDA_OK;
+
+    auto t_start = std::chrono::steady_clock::now();
+    if (n_seq == 1) rc = prefill(prompts, n_prompt);
+    else rc = prefill_batch(prompts, n_seq, n_prompt);
+    if (rc) return rc;
+    auto t_prefill = std::chrono::steady_clock::now();
+    double first_ms = 0.0;
+    if ((rc = decode_loop(n_seq, eff, out_tokens, max_tokens, n_out, nullptr, &first_ms))) return rc;
+    auto t_end = std::chrono::steady_clock::now();
+    if (result) {
+        auto ms = [](auto a, auto b) { return std::chrono::duration<double, std::milli>(b - a).count(); };
+        int total = 0;
+        bool eos = false;
+        for (int s = 0; s < n_seq; s++) { total += n_out[s]; if (n_out[s] < eff) eos = true; }
+        result->generated_tokens = total;
+        result->prefill_ms = ms(t_start, t_prefill);
+        result->first_token_latency_ms = first_ms;
+        result->total_decode_ms = ms(t_prefill, t_end);
+        result->tokens_per_second = total > 0 ? total / std::max(result->total_decode_ms / 1000.0, 1e-9) : 0.0;
+        result->stopped_on_eos = eos ? 1 : 0;
+    }
+    return ESP_CUDA_OK;
+}
+
+// Device-driven greedy decode of up to `count` tokens for sequences 0..n_seq-1, continuing from the current
+// state (ESPRuntimeSession.decode(count:), Sources/ESPRuntime/ESPRuntimeContracts.swift:5-13).  The first token
+// comes from the head alone (the state already holds the last hidden vector); each later token is one forward
+// step whose head feeds its result back on the device, so the host only enqueues graph launches.
+int32_t Engine::decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, int32_t out_stride, int32_t* n_out,
+                            float* device_ms, double* first_token_ms) {
+    int32_t rc = check_ready("decode");
+    if (rc) return rc;
+    if (n_seq < 1 || n_seq > cfg_.max_batch) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "n_seq exceeds max_batch");
+    if (count < 0 || (out_tokens && out_stride < count)) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "decode: bad count");
+    std::vector<int> seq(n_seq), pos(n_seq), lim(n_seq);
+    int max_lim = 0;
+    for (int s = 0; s < n_seq; s++) {
+        if (h_visible_[s] <= 0) return fail(ESP_CUDA_ERR_STATE, "decode: sequence has no prefilled tokens");
+        seq[s] = s; pos[s] = h_visible_[s];
+        lim[s] = std::max(0, std::min(count, m_.max_seq - h_visible_[s]));
+        max_lim = std::max(max_lim, lim[s]);
+        if (n_out) n_out[s] = 0;
+    }
+    if (max_lim == 0) { if (device_ms) *device_ms = 0.f; return ESP_CUDA_OK; }
+    std::vector<int> active(n_seq);
+    for (int s = 0; s < n_seq; s++) active[s] = lim[s] > 0;
+    if ((rc = upload_rows(n_seq, seq.data(), pos.data(), nullptr, active.data(), lim.data(), true))) return rc;
+    if (!ev_begin_) { ESP_CUDA_TRY(cudaEventCreate(&ev_begin_)); ESP_CUDA_TRY(cudaEventCreate(&ev_end_)); }
+    auto t0 = std::chrono::steady_clock::now();
+    ESP_CUDA_TRY(cudaEventRecord(ev_begin_, stream_));
+    if ((rc = submit(n_seq, STEP_HEAD | STEP_FEEDBACK))) return rc;
+    if (first_token_ms) {
+        ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+        *first_token_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    }
+    const bool may_stop_early = m_.arch == ARCH_GPT2 || m_.eos_token >= 0;
+    for (int i = 1; i < max_lim; i++) {
+        if ((rc = submit(n_seq, STEP_FORWARD | STEP_HEAD | STEP_FEEDBACK))) return rc;
+        if (may_stop_early && (i % 32) == 0) {
+            ESP_CUDA_TRY(cudaMemcpyAsync(h_rows_block_ + 3 * max_rows_, rs_.active, sizeof(int) * n_seq, cudaMemcpyDeviceToHost, stream_));
+            ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+            bool any = false;
+            for (int s = 0; s < n_seq; s++) any |= h_rows_block_[3 * max_rows_ + s] != 0;
+            if (!any) break;
+        }
+    }
+    ESP_CUDA_TRY(cudaEventRecord(ev_end_, stream_));
+    ESP_CUDA_TRY(cudaMemcpyAsync(h_rows_block_, d_rows_block_, sizeof(int) * 6 * max_rows_, cudaMemcpyDeviceToHost, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    if (device_ms) ESP_CUDA_TRY(cudaEventElapsedTime(device_ms, ev_begin_, ev_end_));
+    for (int s = 0; s < n_seq; s++) {
+        int n = std::min(h_rows_block_[4 * max_rows_ + s], lim[s]);
+        if (n_out) n_out[s] = n;
+        h_visible_[s] = h_rows_block_[max_rows_ + s];
+        if (n > 0 && out_tokens)
+            ESP_CUDA_TRY(cudaMemcpy(out_tokens + (size_t)s * out_stride, rs_.out + (size_t)s * out_stride_, sizeof(uint32_t) * n, cudaMemcpyDeviceToHost));
+    }
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::set_debug_layer(int32_t layer) {
+    if (layer >= m_.n_layer) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "debug layer out of range");
+    debug_layer_ = layer < 0 ? -1 : layer;
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::debug_dump(int32_t stage, float* out, int32_t capacity) {
+    int32_t rc = check_ready("debug_dump");
+    if (rc) return rc;
+    const int q = m_.q_dim, kv = m_.kv_dim, d = m_.d_model, h = m_.hidden;
+    const int offs[7] = {0, q, q + kv, q + 2 * kv, 2 * q + 2 * kv, 2 * q + 2 * kv + d, 2 * q + 2 * kv + d + h};
+    const int sizes[7] = {q, kv, kv, q, d, h, d};
+    if (stage < 0 || stage > 6 || !out || capacity < sizes[stage]) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "debug_dump: bad stage or capacity");
+    ESP_CUDA_TRY(cudaMemcpy(out, d_debug_ + offs[stage], sizeof(float) * sizes[stage], cudaMemcpyDeviceToHost));
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::get_timings(esp_cuda_timings* out) {
+    if (!out) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "get_timings: null output");
+    *out = timings_;
+    return ESP_CUDA_OK;
+}
+
+}  // namespace esp
+
+// ---------------------------------------------------------------------------------------------- stand-alone GEMV
+
+namespace esp {
+
+// y = W.x with the same inner loop as the decode stages: one warp per pair of rows, 16-byte weight loads.
+template <int WT>
+__global__ void __launch_bounds__(kThreads) k_gemv_plain(Weight w, const float* __restrict__ x, float* __restrict__ y) {
+    extern __shared__ float smem[];
+    constexpr int EPL = WTraits<WT>::EPL;
+    float* xs = smem + 8;
+    stage_vector<EPL>(x, w.cols, NORM_NONE, nullptr, nullptr, 0.f, xs, smem);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_items = (w.rows + 1) / 2;
+    int begin, end;
+    cta_range(n_items, blockIdx.x, gridDim.x, begin, end);
+    for (int item = begin + warp; item < end; item += kWarps) {
+        int row0 = item * 2, row1 = min(row0 + 1, w.rows - 1);
+        const uint8_t* wr[2] = {weight_row(w, row0), weight_row(w, row1)};
+        const __half* sr[2] = {scale_row(w, row0), scale_row(w, row1)};
+        float acc[2] = {0.f, 0.f};
+        dot_rows<WT, 2>(wr, sr, w.cols, xs, lane, acc);
+        float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
+        if (lane == 0) { y[row0] = v0; if (row1 != row0) y[row1] = v1; }
+    }
+}
+
+int32_t gemv_bench(int32_t type, const void* weights, int32_t rows, int32_t cols, const float* x, float* y, int32_t warmup,
+                   int32_t iterations, int32_t copies, float* avg_ms, int32_t device) {
+    if (!weights || !x || !y || rows <= 0 || cols <= 0 || iterations < 1 || copies < 1)
+        return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "gemv_bench: bad arguments");
+    if (type != WT_F16 && type != WT_BF16 && type != WT_Q8_0 && type != WT_Q4_0)
+        return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "gemv_bench: unsupported type");
+    if (cols % epl_of(type)) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "gemv_bench: cols must be a multiple of the load width");
+    if (force_failure_enabled()) return fail(ESP_CUDA_ERR_FORCED_FAILURE, "forced failure is enabled");
+    ESP_CUDA_TRY(cudaSetDevice(device));
+    {
+        const int bytes = 200 * 1024;
+        cudaFuncSetAttribute(k_gemv_plain<WT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(k_gemv_plain<WT_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(k_gemv_plain<WT_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(k_gemv_plain<WT_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    }
+    std::vector<void*> owned;
+    auto cleanup = [&] { for (void* p : owned) cudaFree(p); };
+    const size_t n = (size_t)rows * cols;
+    const bool quant = type == WT_Q8_0 || type == WT_Q4_0;
+    const size_t in_bytes = type == WT_Q8_0 ? n / 32 * 34 : type == WT_Q4_0 ? n / 32 * 18 : n * 2;
+    const size_t data_bytes = weight_row_bytes(type, cols) * rows;
+    void* staging = nullptr;
+    int32_t rc = ESP_CUDA_OK;
+    std::vector<Weight> ws(copies);
+    float *dx = nullptr, *dy = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    auto body = [&]() -> int32_t {
+        if (quant) {
+            ESP_CUDA_TRY(cudaMalloc(&staging, in_bytes));
+            owned.push_back(staging);
+            ESP_CUDA_TRY(cudaMemcpy(staging, weights, in_bytes, cudaMemcpyDefault));
+        }
+        for (int c = 0; c < copies; c++) {
+            void* d = nullptr;
+            __half* sc = nullptr;
+            ESP_CUDA_TRY(cudaMalloc(&d, data_bytes));
+            owned.push_back(d);
+            if (quant) {
+                ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&sc), n / 32 * 2));
+                owned.push_back(sc);
+                int64_t nb = (int64_t)(n / 32);
+                if (type == WT_Q8_0) k_repack_q8_0<<<(unsigned)((nb + 255) / 256), 256>>>(static_cast<uint8_t*>(staging), nb, static_cast<int8_t*>(d), sc);
+                else k_repack_q4_0<<<(unsigned)((nb + 255) / 256), 256>>>(static_cast<uint8_t*>(staging), nb, static_cast<uint8_t*>(d), sc);
+            } else {
+                ESP_CUDA_TRY(cudaMemcpy(d, weights, data_bytes, cudaMemcpyDefault));
+            }
+            ws[c] = Weight{d, sc, rows, cols, type, 0};
+        }
+        ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&dx), sizeof(float) * cols));
+        owned.push_back(dx);
+        ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&dy), sizeof(float) * rows));
+        owned.push_back(dy);
+        ESP_CUDA_TRY(cudaMemcpy(dx, x, sizeof(float) * cols, cudaMemcpyDefault));
+        ESP_CUDA_TRY(cudaDeviceSynchronize());
+        int sm = 148;
+        cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, device);
+        int items = (rows + 1) / 2;
+        int grid = std::max(1, std::min((items + kWarps - 1) / kWarps, sm * 8));
+        size_t smem = sizeof(float) * (size_t)(8 + xs_floats_rt(type, cols));
+        auto launch = [&](int c) {
+            switch (type) {
+                case WT_F16: k_gemv_plain<WT_F16><<<grid, kThreads, smem>>>(ws[c], dx, dy); break;
+                case WT_BF16: k_gemv_plain<WT_BF16><<<grid, kThreads, smem>>>(ws[c], dx, dy); break;
+                case WT_Q8_0: k_gemv_plain<WT_Q8_0><<<grid, kThreads, smem>>>(ws[c], dx, dy); break;
+                default: k_gemv_plain<WT_Q4_0><<<grid, kThreads, smem>>>(ws[c], dx, dy); break;
+            }
+        };
+        for (int i = 0; i < warmup; i++) launch(i % copies);
+        ESP_CUDA_TRY(cudaEventCreate(&e0));
+        ESP_CUDA_TRY(cudaEventCreate(&e1));
+        ESP_CUDA_TRY(cudaDeviceSynchronize());
+        ESP_CUDA_TRY(cudaEventRecord(e0));
+        for (int i = 0; i < iterations; i++) launch((warmup + i) % copies);
+        ESP_CUDA_TRY(cudaEventRecord(e1));
+        ESP_CUDA_TRY(cudaEventSynchronize(e1));
+        ESP_CUDA_TRY(cudaGetLastError());
+        float total = 0.f;
+        ESP_CUDA_TRY(cudaEventElapsedTime(&total, e0, e1));
+        if (avg_ms) *avg_ms = total / iterations;
+        launch(0);
+        ESP_CUDA_TRY(cudaMemcpy(y, dy, sizeof(float) * rows, cudaMemcpyDefault));
+        return ESP_CUDA_OK;
+    };
+    rc = body();
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cleanup();
+    return rc;
+}
+
+}  // namespace esp

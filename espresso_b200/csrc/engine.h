@@ -1,0 +1,125 @@
+// Host-side engine: owns the device copy of one model replica, the KV cache and the per-row decode
+// state, and submits the decode kernels.  It is the CUDA counterpart of the reference's
+// CPUExactLlamaRuntime (Sources/RealModelInference/RealModelInferenceEngine.swift:548-850) generalised to
+// `max_batch` independent sequences and to GPT-2.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/espresso_cuda.h"
+#include "decode_kernels.cuh"
+
+namespace esp {
+
+void set_last_error(const std::string& msg);
+const char* last_error_cstr();
+bool force_failure_enabled();
+
+struct DeviceTensor {
+    void* data = nullptr;       // matrix payload (see esp::Weight) or raw 16-bit elements (embeddings)
+    __half* scales = nullptr;   // Q8_0 / Q4_0 scales
+    float* f32 = nullptr;       // fp32 copy (norm gains, biases)
+    int type = -1;
+    int rows = 0, cols = 0;
+    bool loaded = false;
+};
+
+struct Checkpoint {
+    int visible = 0;
+    float* hidden = nullptr;  // device copy of the last hidden state of sequence 0
+};
+
+class Engine {
+public:
+    explicit Engine(const esp_cuda_config& cfg);
+    ~Engine();
+
+
+    int32_t init();  // device buffers
+    int32_t load_tensor(const char* name, int32_t type, const void* data, uint64_t nbytes);
+    int32_t load_directory(const char* dir);
+    int32_t finalize();
+
+    int32_t reset();
+    int32_t prefill(const uint32_t* tokens, int32_t n);
+    int32_t advance(uint32_t token);
+    int32_t select_greedy(uint32_t* token);
+    int32_t decode_step(uint32_t token, uint32_t* next);
+    int32_t get_logits(int32_t seq, float* out, int32_t vocab);
+    int32_t checkpoint(int32_t* id);
+    int32_t rollback(int32_t id);
+    int32_t verify2(uint32_t current, uint32_t proposed, uint32_t* exact_next, uint32_t* exact_future);
+    int32_t commit(int32_t steps);
+    int32_t prefill_batch(const uint32_t* tokens, int32_t n_seq, int32_t len);
+    int32_t decode_step_batch(const uint32_t* tokens, int32_t n_seq, uint32_t* next);
+    // Feeds tok[r] to sequence seq[r] for every row (rows sharing a sequence take consecutive positions) and
+    // optionally returns each row's next greedy token.
+    int32_t feed(int rows, const int* seq, const uint32_t* tok, bool with_head, uint32_t* next_out);
+    int32_t generate_batch(const uint32_t* prompts, int32_t n_seq, int32_t n_prompt, int32_t max_tokens,
+                           uint32_t* out_tokens, int32_t* n_out, esp_cuda_generation_result* result);
+    int32_t decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, int32_t out_stride, int32_t* n_out,
+                        float* device_ms, double* first_token_ms);
+    int32_t set_debug_layer(int32_t layer);
+    int32_t debug_dump(int32_t stage, float* out, int32_t capacity);
+    int32_t get_timings(esp_cuda_timings* out);
+
+    const esp_cuda_config& config() const { return cfg_; }
+    int visible(int seq) const { return h_visible_[seq]; }
+    bool finalized() const { return finalized_; }
+
+private:
+    enum StepMode { STEP_FORWARD = 1, STEP_HEAD = 2, STEP_FEEDBACK = 4 };
+    struct RowsHost {  // pinned mirror of the device row-control block
+        int* base = nullptr;
+    };
+
+    int32_t check_ready(const char* what) const;
+    DeviceTensor* slot(const std::string& name, int* rows, int* cols, bool* is_matrix, bool* is_embedding);
+    int32_t upload_rows(int rows, const int* seq, const int* pos, const uint32_t* tok, const int* active,
+                        const int* limit, bool zero_out_counts);
+    int32_t submit(int rows, int mode);                  // graph replay or direct launch
+    int32_t launch_step(int rows, int mode, cudaStream_t s, bool profile);
+    int32_t feed_rows(int rows, const int* seq, const uint32_t* tok, bool with_head, uint32_t* next_out);
+    Weight weight_of(const DeviceTensor& t) const;
+    LayerWeights layer_weights(int l) const;
+    size_t gemv_smem(int type, int K, bool with_tmp) const;
+
+    esp_cuda_config cfg_;
+    ModelDims m_{};
+    cudaStream_t stream_ = nullptr;
+    bool finalized_ = false;
+    int max_rows_ = 0;
+    int n_splits_ = 1;
+    int sm_count_ = 148;
+
+    std::map<std::string, DeviceTensor> tensors_;
+    std::vector<void*> owned_;  // every cudaMalloc'd pointer
+
+    // device state
+    Activations act_{};
+    KvLayout kv_{};
+    RowState rs_{};
+    int* d_rows_block_ = nullptr;  // [6][max_rows] seq,pos,tok,active,n_out,limit
+    int* h_rows_block_ = nullptr;  // pinned
+    uint32_t* h_next_ = nullptr;   // pinned [max_rows]
+    float2* d_rope_ = nullptr;
+    float* d_debug_ = nullptr;
+    int debug_layer_ = -1;
+    int out_stride_ = 0;
+
+    std::vector<int> h_visible_;   // per sequence
+    std::vector<Checkpoint> checkpoints_;
+    int pending_verify_ = 0;
+
+    std::map<int, cudaGraphExec_t> graphs_;  // key = rows * 8 + mode
+    std::map<int, int> launches_by_key_;
+    std::vector<cudaEvent_t> prof_events_;
+    cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
+    esp_cuda_timings timings_{};
+    int launches_last_step_ = 0;
+};
+
+}  // namespace esp

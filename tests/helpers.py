@@ -1,0 +1,61 @@
+"""Shared helpers of the GPU parity tests."""
+import numpy as np
+
+from espresso_b200 import gguf_quant
+from espresso_b200.synthetic import synthetic_tensors
+from espresso_b200.weight_blob import is_matrix
+
+ABS_TOL = 2e-2   # max-abs logit tolerance (fp16 KV cache, different summation order)
+REL_TOL = 1e-2   # relative tolerance
+
+
+def assert_logits_close(got, ref, what=""):
+    got = np.asarray(got, np.float32)
+    ref = np.asarray(ref, np.float32)
+    err = np.abs(got - ref)
+    assert err.max() <= ABS_TOL, f"{what}: max-abs {err.max():.3e} > {ABS_TOL}"
+    rel = np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-12)
+    assert rel <= REL_TOL, f"{what}: relative error {rel:.3e} > {REL_TOL}"
+
+
+def compare_greedy_stream(oracle_runtime, prompt, gpu_tokens, tol=ABS_TOL):
+    """Teacher-forced comparison of a greedy stream with the oracle.
+
+    The oracle is fed the GPU's tokens.  At every step the GPU token must be the oracle's argmax unless the
+    oracle's top-2 logit gap is within ``tol`` (then the GPU token's oracle logit must be within ``tol`` of the
+    maximum).  Returns the list of positions where the two argmaxes differed inside the tolerance.
+    """
+    assert oracle_runtime.prefill(prompt) == 0
+    near_ties = []
+    for i, tok in enumerate(gpu_tokens):
+        logits = oracle_runtime.logits()
+        best = int(np.argmax(logits))
+        if int(tok) != best:
+            gap = float(logits[best] - logits[int(tok)])
+            assert gap <= tol, f"step {i}: GPU token {tok} vs oracle {best}, oracle logit gap {gap:.4f} > {tol}"
+            near_ties.append(i)
+        if i + 1 < len(gpu_tokens):
+            assert oracle_runtime.advance(int(tok)) == 0
+    return near_ties
+
+
+def quantised_pair(oracle_lib, cfg, kind, seed=1234, quantise_head=True):
+    """Returns (oracle model holding the dequantised fp32 values, list of (name, kind, array) uploads)."""
+    model = oracle_lib.Model(cfg.to_metadata())
+    uploads = []
+    for name, vals in synthetic_tensors(cfg, seed):
+        leaf = name.rsplit("/", 1)[-1]
+        if is_matrix(name) and (leaf != "lm_head" or quantise_head):
+            blocks = gguf_quant.quantize(kind, vals.astype(np.float32))
+            model.set_tensor(name, gguf_quant.dequantize(kind, blocks))
+            uploads.append((name, kind, blocks))
+        else:
+            model.set_tensor(name, vals.astype(np.float32))
+            uploads.append((name, "f16", vals))
+    return model, uploads
+
+
+def upload_all(engine, uploads):
+    for name, kind, arr in uploads:
+        engine.load_tensor(name, kind, arr)
+    engine.finalize()

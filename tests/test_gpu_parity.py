@@ -1,0 +1,377 @@
+"""GPU parity tests: every case drives the CUDA library through its C ABI (ctypes) and compares with the
+CPU oracle on the same seeded inputs.  Integer/byte results must be bit-exact; logits must agree within
+max-abs 2e-2 and relative 1e-2 (fp16 KV cache and a different summation order are the only differences);
+greedy streams must be identical wherever the oracle's top-2 logit gap exceeds that tolerance."""
+import dataclasses
+import os
+
+import numpy as np
+import pytest
+
+from helpers import ABS_TOL, assert_logits_close, compare_greedy_stream, quantised_pair, upload_all
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.fixture(scope="module")
+def rt():
+    from espresso_b200 import runtime
+
+    runtime.load_library()
+    return runtime
+
+
+def test_dequantize_bit_exact(rt, oracle_lib):
+    g = np.load(os.path.join(GOLD, "gguf_blocks.npz"))
+    for kind in ("q8_0", "q4_0"):
+        got = rt.dequantize(kind, g[kind + "_blocks"], g["x"].size)
+        assert np.array_equal(got.view(np.uint32), g[kind + "_dequant"].view(np.uint32))
+    rng = np.random.default_rng(9)
+    x = (rng.standard_normal(32 * 5000) * 0.02).astype(np.float32)
+    for kind in ("q8_0", "q4_0"):
+        blocks = oracle_lib.quantize(kind, x)
+        got = rt.dequantize(kind, blocks, x.size)
+        assert np.array_equal(got.view(np.uint32), oracle_lib.dequantize(kind, blocks, x.size).view(np.uint32))
+    assert rt.dequantize("q8_0", np.zeros(0, np.uint8), 0).size == 0  # empty input
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16", "q8_0", "q4_0"])
+@pytest.mark.parametrize("shape", [(96, 128), (1000, 768), (257, 2048), (64, 5632)])
+def test_gemv_kernel_matches_oracle(rt, oracle_lib, kind, shape):
+    rows, cols = shape
+    rng = np.random.default_rng(rows * 31 + cols)
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    x = rng.standard_normal(cols).astype(np.float32)
+    if kind == "f16":
+        stored = w.astype(np.float16)
+        ref_w = stored.astype(np.float32)
+    elif kind == "bf16":
+        bits = (w.view(np.uint32) >> 16).astype(np.uint16)
+        stored = bits
+        ref_w = (bits.astype(np.uint32) << 16).view(np.float32)
+    else:
+        stored = oracle_lib.quantize(kind, w)
+        ref_w = oracle_lib.dequantize(kind, stored, w.size).reshape(rows, cols)
+    y, ms = rt.gemv_bench(kind, stored, rows, cols, x, warmup=1, iterations=2)
+    ref = oracle_lib.gemv(ref_w, x)
+    np.testing.assert_allclose(y, ref, atol=2e-4, rtol=1e-4)
+    assert ms > 0
+
+
+def _stepwise_logit_parity(rt, oracle_lib, weight_dir, prompt, extra_steps=6):
+    eng = rt.DecodeEngine.build(weight_dir)
+    ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(weight_dir))
+    eng.reset()
+    ora.reset()
+    for i, t in enumerate(prompt):
+        eng.advance(int(t))
+        assert ora.advance(int(t)) == 0
+        assert_logits_close(eng.logits(), ora.logits(), f"prompt position {i}")
+    tok = eng.select_greedy_token()
+    for i in range(extra_steps):
+        assert_logits_close(eng.logits(), ora.logits(), f"decode step {i}")
+        nxt = eng.decode_step(tok)
+        assert ora.advance(tok) == 0
+        tok = nxt
+    assert eng.visible_token_count() == ora.visible == len(prompt) + extra_steps
+    eng.close()
+
+
+@pytest.mark.parametrize("gqa", [True, False])
+def test_llama_tiny_logits_match_oracle(rt, oracle_lib, tmp_models, gqa):
+    from espresso_b200.model_config import tiny_llama
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = tiny_llama(vocab=512, max_seq=64, n_layer=2, gqa=gqa)
+    _stepwise_logit_parity(rt, oracle_lib, tmp_models(cfg), synthetic_prompt(cfg.vocab, 9))
+
+
+def test_gpt2_tiny_logits_match_oracle(rt, oracle_lib, tmp_models):
+    from espresso_b200.model_config import tiny_gpt2
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = tiny_gpt2(vocab=512, max_seq=64, n_layer=2)
+    _stepwise_logit_parity(rt, oracle_lib, tmp_models(cfg, 777), synthetic_prompt(cfg.vocab, 9, seed=777))
+
+
+def test_logits_match_huggingface_golden(rt, tmp_models):
+    from espresso_b200.model_config import tiny_gpt2, tiny_llama
+
+    g = np.load(os.path.join(GOLD, "hf_llama_tiny.npz"))
+    for tag, gqa in (("gqa", True), ("mha", False)):
+        cfg = tiny_llama(vocab=512, max_seq=64, n_layer=2, gqa=gqa)
+        eng = rt.DecodeEngine.build(tmp_models(cfg, int(g[tag + "_seed"])))
+        eng.reset()
+        for i, t in enumerate(g[tag + "_prompt"]):
+            eng.advance(int(t))
+            assert_logits_close(eng.logits(), g[tag + "_logits"][i], f"hf llama {tag} pos {i}")
+        eng.close()
+    g = np.load(os.path.join(GOLD, "hf_gpt2_tiny.npz"))
+    cfg = tiny_gpt2(vocab=512, max_seq=64, n_layer=2)
+    eng = rt.DecodeEngine.build(tmp_models(cfg, int(g["seed"])))
+    eng.reset()
+    for i, t in enumerate(g["prompt"]):
+        eng.advance(int(t))
+        assert_logits_close(eng.logits(), g["logits"][i], f"hf gpt2 pos {i}")
+    eng.close()
+
+
+def test_stage_dumps_match_oracle(rt, oracle_lib, tmp_models):
+    # bisect-by-stage hooks, as the reference's test_debug* helpers do (Engine.swift:419-484)
+    from espresso_b200.model_config import tiny_llama
+
+    cfg = tiny_llama(vocab=512, max_seq=64, n_layer=2, gqa=True)
+    d = tmp_models(cfg)
+    eng = rt.DecodeEngine.build(d)
+    ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(d))
+    for layer in (0, 1):
+        eng.reset(); ora.reset()
+        eng.set_debug_layer(layer)
+        ora.set_capture_layer(layer)
+        for t in (3, 77, 301, 12):
+            eng.advance(t)
+            assert ora.advance(t) == 0
+        for stage, tol in ((0, 2e-4), (1, 2e-3), (2, 2e-3), (3, 2e-3), (4, 2e-3), (5, 2e-3), (6, 3e-3)):
+            np.testing.assert_allclose(eng.debug_dump(stage), ora.captured(stage), atol=tol, rtol=1e-2,
+                                       err_msg=f"layer {layer} stage {stage}")
+    eng.set_debug_layer(-1)
+    eng.close()
+
+
+def test_prefill_equals_token_by_token(rt, tmp_models):
+    from espresso_b200.model_config import tiny_llama
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = tiny_llama(vocab=512, max_seq=64, n_layer=2)
+    eng = rt.DecodeEngine.build(tmp_models(cfg))
+    prompt = synthetic_prompt(cfg.vocab, 21)
+    eng.prefill(prompt)
+    a = eng.logits()
+    eng.reset()
+    for t in prompt:
+        eng.advance(int(t))
+    b = eng.logits()
+    np.testing.assert_allclose(a, b, atol=1e-4)
+    assert eng.visible_token_count() == 21
+    eng.close()
+
+
+def test_generate_matches_oracle_greedy_6_layer_model(rt, oracle_lib, tmp_models):
+    """The reference's own benchmark shape: 6 layers, d768, 12 heads, vocab 32000, 16-token prompt, 128 steps."""
+    from espresso_b200.model_config import llama_6l
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = llama_6l()
+    d = tmp_models(cfg)
+    prompt = synthetic_prompt(cfg.vocab, 16)
+    eng = rt.DecodeEngine.build(d)
+    res = eng.generate(prompt, 128)
+    assert len(res.tokens) == 128 and res.tokensPerSecond > 0
+    ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(d))
+    near = compare_greedy_stream(ora, prompt, res.tokens)
+    assert len(near) <= 2, f"too many near-tie positions: {near}"
+    # the device-driven loop and the step-by-step API give the same stream
+    eng.prefill(prompt)
+    tok = eng.select_greedy_token()
+    stream = [tok]
+    for _ in range(31):
+        tok = eng.decode_step(tok)
+        stream.append(tok)
+    assert stream == list(res.tokens[:32])
+    assert_logits_close(eng.logits(), _oracle_logits_after(ora, prompt, stream[:-1]), "after 31 steps")
+    eng.close()
+
+
+def _oracle_logits_after(ora, prompt, fed):
+    assert ora.prefill(prompt) == 0
+    for t in fed:
+        assert ora.advance(int(t)) == 0
+    return ora.logits()
+
+
+def test_generation_limits_and_eos(rt, oracle_lib, tmp_models, tmp_path):
+    import shutil
+    from espresso_b200.model_config import MultiModelConfig, tiny_gpt2, tiny_llama
+
+    cfg = tiny_llama(vocab=64, max_seq=24, n_layer=1)
+    d = tmp_models(cfg)
+    eng = rt.DecodeEngine.build(d)
+    ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(d))
+    prompt = [3, 4, 5]
+    res = eng.generate(prompt, 100)
+    assert len(res.tokens) == 21  # clamped to maxSeq - prompt (Engine.swift:1425-1426)
+    compare_greedy_stream(ora, prompt, res.tokens)
+    assert len(eng.generate(prompt, 0).tokens) == 0
+    with pytest.raises(rt.RealModelInferenceError):
+        eng.generate(list(range(24)), 4)  # prompt must be shorter than the context
+    with pytest.raises(rt.RealModelInferenceError):
+        eng.generate([], 4)
+    eng.close()
+    # Llama EOS: the EOS token is emitted, then generation stops (Engine.swift:6385-6388)
+    first = int(res.tokens[0])
+    third = int(res.tokens[2])
+    for eos, expect in ((first, 1), (third, None)):
+        d2 = str(tmp_path / f"eos{eos}")
+        shutil.copytree(d, d2)
+        dataclasses.replace(cfg, eosToken=eos).save(d2)
+        e2 = rt.DecodeEngine.build(d2)
+        out = e2.generate(prompt, 100)
+        ref = oracle_lib.Runtime(oracle_lib.Model.from_dir(d2)).generate(prompt, 100)
+        assert list(out.tokens) == list(ref)
+        assert out.tokens[-1] == eos and out.stoppedOnEOS
+        if expect:
+            assert len(out.tokens) == expect
+        e2.close()
+
+
+def test_batched_decode_equals_independent_sequences(rt, oracle_lib, tmp_models):
+    from espresso_b200.model_config import tiny_gpt2, tiny_llama
+    from espresso_b200.synthetic import synthetic_prompt
+
+    for cfg, seed in ((tiny_llama(vocab=512, max_seq=64, n_layer=2), 1234), (tiny_gpt2(vocab=512, max_seq=64, n_layer=2), 777)):
+        d = tmp_models(cfg, seed)
+        n_seq = 5
+        prompts = np.stack([synthetic_prompt(cfg.vocab, 7, seed=seed, stream=s) for s in range(n_seq)])
+        eng = rt.DecodeEngine.build(d, max_batch=n_seq)
+        toks, res = eng.generate_batch(prompts, 12)
+        model = oracle_lib.Model.from_dir(d)
+        for s in range(n_seq):
+            assert len(toks[s]) == 12
+            compare_greedy_stream(oracle_lib.Runtime(model), prompts[s], toks[s])
+        # step API: logits of every sequence against the oracle
+        eng.prefill_batch(prompts)
+        nxt = eng.decode_step_batch(prompts[:, 0])
+        for s in range(n_seq):
+            ora = oracle_lib.Runtime(model)
+            ora.prefill(list(prompts[s]) + [int(prompts[s, 0])])
+            assert_logits_close(eng.logits(s), ora.logits(), f"{cfg.name} seq {s}")
+            assert int(nxt[s]) == int(np.argmax(eng.logits(s)))
+        eng.close()
+
+
+def test_verify2_checkpoint_and_two_token_generation(rt, oracle_lib, tmp_models):
+    from espresso_b200.model_config import tiny_llama
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = tiny_llama(vocab=96, max_seq=48, n_layer=2)
+    dcfg = tiny_llama(vocab=96, max_seq=48, n_layer=1)
+    d, dd = tmp_models(cfg), tmp_models(dcfg, 1235)
+    eng = rt.DecodeEngine.build(d)
+    prompt = synthetic_prompt(cfg.vocab, 6)
+    greedy = eng.generate(prompt, 24).tokens
+    # verify2 = two sequential exact steps when the proposal is right; one when it is wrong
+    eng.prefill(prompt)
+    cur = eng.select_greedy_token()
+    assert cur == greedy[0]
+    nxt, fut = eng.verify2(cur, int(greedy[1]))
+    assert (nxt, fut) == (greedy[1], greedy[2])
+    eng.commit(2)
+    assert eng.visible_token_count() == len(prompt) + 2 and eng.select_greedy_token() == greedy[2]
+    wrong = (int(greedy[3]) + 1) % cfg.vocab
+    nxt, _ = eng.verify2(int(greedy[2]), wrong)
+    assert nxt == greedy[3]
+    eng.commit(1)
+    assert eng.select_greedy_token() == greedy[3]
+    # checkpoint / rollback (Engine.swift:647-661)
+    cp = eng.capture_checkpoint()
+    before = eng.logits()
+    eng.advance(7); eng.advance(9)
+    eng.rollback(cp)
+    assert eng.visible_token_count() == len(prompt) + 3
+    np.testing.assert_array_equal(eng.logits(), before)
+    assert eng.decode_step(int(greedy[3])) == greedy[4]
+    # two-token generation emits the plain greedy stream, with any draft
+    for draft_dir, expect_all in ((dd, False), (d, True)):
+        draft = rt.DecodeEngine.build(draft_dir)
+        res = eng.generate_two_token(draft, prompt, 24)
+        assert list(res.tokens) == list(greedy)
+        assert res.speculativePasses > 0
+        if expect_all:
+            assert res.acceptedFutureTokensPerPass > 0.8  # an identical draft is (almost) always accepted
+        draft.close()
+    ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(d))
+    compare_greedy_stream(ora, prompt, greedy)
+    eng.close()
+
+
+@pytest.mark.parametrize("kind", ["q8_0", "q4_0"])
+def test_quantised_llama_matches_oracle_on_dequantised_weights(rt, oracle_lib, kind):
+    from espresso_b200.model_config import MultiModelConfig
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = MultiModelConfig("tiny-gqa-q", 2, 8, 2, 256, 32, 512, 640, 96, 1e-5, 10000.0, None, "llama")
+    model, uploads = quantised_pair(oracle_lib, cfg, kind)
+    eng = rt.DecodeEngine.empty(cfg)
+    upload_all(eng, uploads)
+    ora = oracle_lib.Runtime(model)
+    prompt = synthetic_prompt(cfg.vocab, 10)
+    eng.prefill(prompt)
+    assert ora.prefill(prompt) == 0
+    assert_logits_close(eng.logits(), ora.logits(), kind)
+    res = eng.generate(prompt, 40)
+    compare_greedy_stream(ora, prompt, res.tokens)
+    eng.close()
+
+
+def test_long_context_split_kv_attention(rt, oracle_lib, tmp_models):
+    """Positions beyond one attention split (256) exercise the split-KV merge."""
+    from espresso_b200.model_config import MultiModelConfig
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = MultiModelConfig("tiny-long", 1, 4, 2, 128, 32, 256, 256, 640, 1e-5, 10000.0, None, "llama")
+    d = tmp_models(cfg)
+    eng = rt.DecodeEngine.build(d)
+    ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(d))
+    prompt = synthetic_prompt(cfg.vocab, 600)
+    eng.prefill(prompt)
+    assert ora.prefill(prompt) == 0
+    assert_logits_close(eng.logits(), ora.logits(), "600-token context")
+    eng.close()
+
+
+def test_error_codes_and_test_hooks(rt, tmp_models):
+    from espresso_b200.model_config import tiny_llama
+
+    cfg = tiny_llama(vocab=64, max_seq=8, n_layer=1)
+    before = rt.live_engine_count()
+    eng = rt.DecodeEngine.build(tmp_models(cfg))
+    assert rt.live_engine_count() == before + 1
+    eng.prefill([1, 2])
+    with pytest.raises(rt.RealModelInferenceError) as ei:
+        eng.advance(64)  # token outside vocab (Engine.swift:687-689)
+    assert ei.value.status == rt.ERR_OUT_OF_RANGE
+    for t in range(6):
+        eng.advance(t)
+    with pytest.raises(rt.RealModelInferenceError) as ei:
+        eng.advance(0)  # context full (Engine.swift:673-677)
+    assert ei.value.status == rt.ERR_OUT_OF_RANGE
+    with pytest.raises(rt.RealModelInferenceError):
+        eng.prefill([])
+    # forced failure hook (ane_interop_set_force_eval_failure, ane_interop.h:37-41)
+    rt.set_force_failure(True)
+    try:
+        with pytest.raises(rt.RealModelInferenceError) as ei:
+            eng.prefill([1])
+        assert ei.value.status == rt.ERR_FORCED_FAILURE
+    finally:
+        rt.set_force_failure(False)
+    eng.prefill([1])
+    eng.close()
+    assert rt.live_engine_count() == before
+    # missing directory / missing tensor / wrong size
+    with pytest.raises(rt.RealModelInferenceError) as ei:
+        rt.DecodeEngine.build("/nonexistent/dir", config=cfg)
+    assert ei.value.status == rt.ERR_IO
+    e2 = rt.DecodeEngine.empty(cfg)
+    with pytest.raises(rt.RealModelInferenceError) as ei:
+        e2.load_tensor("rms_final", "f16", np.ones(3, np.float16))
+    assert ei.value.status == rt.ERR_INVALID_WEIGHTS
+    with pytest.raises(rt.RealModelInferenceError) as ei:
+        e2.finalize()
+    assert ei.value.status == rt.ERR_INVALID_WEIGHTS
+    with pytest.raises(rt.RealModelInferenceError) as ei:
+        e2.prefill([1])
+    assert ei.value.status == rt.ERR_STATE
+    e2.close()
