@@ -229,7 +229,7 @@ def main() -> None:
             toks, ms = eng.decode(n_decode, n_seq)
             assert all(len(t) == n_decode for t in toks)
             step_ms.append(ms)
-            launches += eng.timings()["kernel_launches"] * (n_decode - 1) + 1
+            launches += eng.timings()["kernel_launches"]
         barrier()
         clocks = sampler.stop()
         total_ms = sum(step_ms)
@@ -259,31 +259,36 @@ def main() -> None:
         value = tokens_all / (total_ms / 1e3)
         e2e_value = tokens_all / e2e_total
 
-        # ---- roofline of the dominant kernel, measured live with CUDA events (direct launches) ----
+        # ---- roofline of the dominant kernel, timed live with CUDA events ----
         peak, peak_kind = read_peaks()
-        prof = runtime.DecodeEngine.build(tmp, max_batch=n_seq, device=local_rank, flags=runtime.FLAG_NO_GRAPH)
-        prof.prefill(prompts[0]) if n_seq == 1 else prof.prefill_batch(prompts)
-        tok = prof.select_greedy_token() if n_seq == 1 else None
-        head_ms, tot_ms = [], []
-        if n_seq == 1:
-            for i in range(40):
-                tok = prof.decode_step(tok)
-                t = prof.timings()
-                if i >= 8:
-                    head_ms.append(t["head_ms"])
-                    tot_ms.append(t["total_ms"])
-        prof.close()
         head_bytes = cfg.vocab * cfg.dModel * 2 + cfg.dModel * 2
-        head_t = statistics.mean(head_ms) if head_ms else None
         bytes_tok = algorithmic_bytes_per_token(cfg, n_prompt, n_decode, n_seq, 2.0)
-        step_gbs = bytes_tok * (n_seq * (n_decode - 1) * args.steps) / (total_ms / 1e3) / 1e9 / world * world
-        roofline = {
-            "bound": "hbm", "kernel": "k_gemv<F16,EPI_HEAD> (final norm + LM head + argmax)",
-            "achieved": (head_bytes / (head_t / 1e3) / 1e9) if head_t else None, "peak": peak, "unit": "GB/s",
-            "frac": (head_bytes / (head_t / 1e3) / 1e9 / peak) if head_t else None, "traffic": None, "peak_kind": peak_kind,
-            "whole_step": {"bytes_per_token": bytes_tok, "achieved": value / world * bytes_tok / 1e9,
-                           "frac": value / world * bytes_tok / 1e9 / peak},
-        }
+        persistent = n_seq == 1 and launches == args.steps
+        if persistent:
+            # one launch of the persistent kernel = one whole step (n_decode heads, n_decode - 1 forward passes)
+            launch_bytes = head_bytes + (n_decode - 1) * bytes_tok
+            launch_s = statistics.mean(step_ms) / 1e3
+            roofline = {"bound": "hbm", "kernel": "k_decode_mega (whole greedy loop: all layers + LM head, one launch per step)",
+                        "achieved": launch_bytes / launch_s / 1e9, "peak": peak, "unit": "GB/s",
+                        "frac": launch_bytes / launch_s / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
+                        "bytes_per_launch": launch_bytes, "bytes_per_token": bytes_tok}
+        else:
+            prof = runtime.DecodeEngine.build(tmp, max_batch=n_seq, device=local_rank, flags=runtime.FLAG_NO_GRAPH)
+            head_ms = []
+            if n_seq == 1:
+                prof.prefill(prompts[0])
+                tok = prof.select_greedy_token()
+                for i in range(40):
+                    tok = prof.decode_step(tok)
+                    if i >= 8:
+                        head_ms.append(prof.timings()["head_ms"])
+            prof.close()
+            head_t = statistics.mean(head_ms) if head_ms else None
+            roofline = {"bound": "hbm", "kernel": "k_lm_head (final norm + LM head + argmax)",
+                        "achieved": (head_bytes / (head_t / 1e3) / 1e9) if head_t else None, "peak": peak, "unit": "GB/s",
+                        "frac": (head_bytes / (head_t / 1e3) / 1e9 / peak) if head_t else None, "traffic": None, "peak_kind": peak_kind,
+                        "whole_step": {"bytes_per_token": bytes_tok, "achieved": value / world * bytes_tok / 1e9,
+                                       "frac": value / world * bytes_tok / 1e9 / peak}}
 
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

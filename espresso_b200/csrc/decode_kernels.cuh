@@ -165,87 +165,90 @@ __device__ __forceinline__ int xs_index(int k) {
 template <int EPL>
 __host__ __device__ inline int xs_floats(int K) { return ((K + 32 * EPL - 1) / (32 * EPL)) * (32 * EPL); }
 
+// Accumulates the products of one 16-byte weight vector (EPL elements starting at element k of its row) with
+// the matching EPL activations.
+template <int WT>
+__device__ __forceinline__ void fma_vec16(const uint4& w, const __half* srow, int k, const float* x, float sx, float& acc) {
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    if constexpr (WT == WT_F16) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[i]));
+            acc = fmaf(f.x, x[2 * i], acc);
+            acc = fmaf(f.y, x[2 * i + 1], acc);
+        }
+    } else if constexpr (WT == WT_BF16) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            acc = fmaf(__uint_as_float(ww[i] << 16), x[2 * i], acc);
+            acc = fmaf(__uint_as_float(ww[i] & 0xffff0000u), x[2 * i + 1], acc);
+        }
+    } else if constexpr (WT == WT_Q8_0) {
+        const float d = __half2float(srow[k >> 5]);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                int qv = (int)(int8_t)((ww[i] >> (8 * b)) & 0xffu);
+                s = fmaf((float)qv, x[4 * i + b], s);
+            }
+        }
+        acc = fmaf(d, s, acc);
+    } else {  // Q4_0: byte j of the group holds element j (low nibble) and element j+16 (high nibble)
+        const float d = __half2float(srow[k >> 5]);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                uint32_t byte = (ww[i] >> (8 * b)) & 0xffu;
+                s = fmaf((float)(byte & 15u), x[4 * i + b], s);
+                s = fmaf((float)(byte >> 4), x[16 + 4 * i + b], s);
+            }
+        }
+        acc = fmaf(d, s - 8.0f * sx, acc);
+    }
+}
+
 // Dot products of NR weight rows with the staged vector.  Each lane accumulates its slices; the caller
-// reduces across the warp.  K must be a multiple of EPL.
+// reduces across the warp.  K must be a multiple of EPL.  The loads of U consecutive 16-byte slices of all NR
+// rows are issued before any arithmetic so that each lane keeps U*NR*16 bytes in flight.
 template <int WT, int NR>
 __device__ __forceinline__ void dot_rows(const uint8_t* const (&wrow)[NR], const __half* const (&srow)[NR], int K,
                                          const float* __restrict__ xs, int lane, float (&acc)[NR]) {
     constexpr int EPL = WTraits<WT>::EPL;
     constexpr int NJ = EPL / 4;
+    constexpr int U = (WT == WT_F16 || WT == WT_BF16) ? 4 : 2;
     const float4* xs4 = reinterpret_cast<const float4*>(xs);
     const int iters = (K + 32 * EPL - 1) / (32 * EPL);
-#pragma unroll 2
-    for (int it = 0; it < iters; it++) {
-        const int k = it * 32 * EPL + lane * EPL;
-        if (k >= K) break;
-        uint4 w[NR];
+    for (int it0 = 0; it0 < iters; it0 += U) {
+        uint4 w[U][NR];
 #pragma unroll
-        for (int r = 0; r < NR; r++) {
-            size_t byte_off = WT == WT_Q8_0 ? (size_t)k : WT == WT_Q4_0 ? (size_t)k / 2 : (size_t)k * 2;
-            w[r] = ld_weight16(wrow[r] + byte_off);
+        for (int u = 0; u < U; u++) {
+            const int k = (it0 + u) * 32 * EPL + lane * EPL;
+            const size_t byte_off = WT == WT_Q8_0 ? (size_t)k : WT == WT_Q4_0 ? (size_t)k / 2 : (size_t)k * 2;
+#pragma unroll
+            for (int r = 0; r < NR; r++) w[u][r] = k < K ? ld_weight16(wrow[r] + byte_off) : make_uint4(0, 0, 0, 0);
         }
-        float x[EPL];
 #pragma unroll
-        for (int j = 0; j < NJ; j++) {
-            float4 v = xs4[(it * NJ + j) * 32 + lane];
-            x[4 * j] = v.x; x[4 * j + 1] = v.y; x[4 * j + 2] = v.z; x[4 * j + 3] = v.w;
-        }
-        if constexpr (WT == WT_F16) {
+        for (int u = 0; u < U; u++) {
+            const int it = it0 + u;
+            const int k = it * 32 * EPL + lane * EPL;
+            if (k < K) {
+                float x[EPL];
 #pragma unroll
-            for (int r = 0; r < NR; r++) {
-                const uint32_t ww[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[i]));
-                    acc[r] = fmaf(f.x, x[2 * i], acc[r]);
-                    acc[r] = fmaf(f.y, x[2 * i + 1], acc[r]);
+                for (int j = 0; j < NJ; j++) {
+                    float4 v = xs4[(it * NJ + j) * 32 + lane];
+                    x[4 * j] = v.x; x[4 * j + 1] = v.y; x[4 * j + 2] = v.z; x[4 * j + 3] = v.w;
                 }
-            }
-        } else if constexpr (WT == WT_BF16) {
+                float sx = 0.f;
+                if constexpr (WT == WT_Q4_0) {
 #pragma unroll
-            for (int r = 0; r < NR; r++) {
-                const uint32_t ww[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    acc[r] = fmaf(__uint_as_float(ww[i] << 16), x[2 * i], acc[r]);
-                    acc[r] = fmaf(__uint_as_float(ww[i] & 0xffff0000u), x[2 * i + 1], acc[r]);
+                    for (int i = 0; i < EPL; i++) sx += x[i];
                 }
-            }
-        } else if constexpr (WT == WT_Q8_0) {
 #pragma unroll
-            for (int r = 0; r < NR; r++) {
-                const float d = __half2float(srow[r][k >> 5]);
-                const uint32_t ww[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
-                float s = 0.f;
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-#pragma unroll
-                    for (int b = 0; b < 4; b++) {
-                        int qv = (int)(int8_t)((ww[i] >> (8 * b)) & 0xffu);
-                        s = fmaf((float)qv, x[4 * i + b], s);
-                    }
-                }
-                acc[r] = fmaf(d, s, acc[r]);
-            }
-        } else {  // Q4_0: byte j of the group holds element j (low nibble) and element j+16 (high nibble)
-            float sx = 0.f;
-#pragma unroll
-            for (int i = 0; i < EPL; i++) sx += x[i];
-#pragma unroll
-            for (int r = 0; r < NR; r++) {
-                const float d = __half2float(srow[r][k >> 5]);
-                const uint32_t ww[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
-                float s = 0.f;
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-#pragma unroll
-                    for (int b = 0; b < 4; b++) {
-                        uint32_t byte = (ww[i] >> (8 * b)) & 0xffu;
-                        s = fmaf((float)(byte & 15u), x[4 * i + b], s);
-                        s = fmaf((float)(byte >> 4), x[16 + 4 * i + b], s);
-                    }
-                }
-                acc[r] = fmaf(d, s - 8.0f * sx, acc[r]);
+                for (int r = 0; r < NR; r++) fma_vec16<WT>(w[u][r], srow[r], k, x, sx, acc[r]);
             }
         }
     }
@@ -350,25 +353,40 @@ __device__ void stage_qkv(const QkvArgs& p, int cta, int n_cta, float* xs, float
             stage_vector<EPL>(hid, m.d_model, gpt2 ? NORM_LAYER : NORM_RMS, p.lw.norm1_g, p.lw.norm1_b, m.eps, xs, red);
         }
         const int seq = p.rs.seq[r];
-        for (int item = begin + warp; item < end; item += kWarps) {
-            const Weight* W;
-            const float* bias;
-            int row0, row1, kind, local;
-            if (item < q_items) { kind = 0; local = item; W = &p.lw.wq; bias = p.lw.bq; }
-            else if (item < q_items + k_items) { kind = 1; local = item - q_items; W = &p.lw.wk; bias = p.lw.bk; }
-            else { kind = 2; local = item - q_items - k_items; W = &p.lw.wv; bias = p.lw.bv; }
-            int head = 0, i = 0;
-            if (kind < 2) { head = local / half; i = local - head * half; row0 = head * m.head_dim + i; row1 = row0 + half; }
-            else { row0 = 2 * local; row1 = row0 + 1; }
-            const uint8_t* wr[2] = {weight_row(*W, row0), weight_row(*W, row1)};
-            const __half* sr[2] = {scale_row(*W, row0), scale_row(*W, row1)};
-            float acc[2] = {0.f, 0.f};
-            dot_rows<WT, 2>(wr, sr, m.d_model, xs, lane, acc);
-            float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
-            if (lane == 0) {
+        // each warp takes two adjacent work items (four weight rows) per iteration
+        for (int item0 = begin + 2 * warp; item0 < end; item0 += 2 * kWarps) {
+            const uint8_t* wr[4];
+            const __half* sr[4];
+            int rows4[4], kinds[2], idx[2];
+            const float* biases[2];
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int item = min(item0 + j, end - 1);
+                const Weight* W;
+                int local;
+                if (item < q_items) { kinds[j] = 0; local = item; W = &p.lw.wq; biases[j] = p.lw.bq; }
+                else if (item < q_items + k_items) { kinds[j] = 1; local = item - q_items; W = &p.lw.wk; biases[j] = p.lw.bk; }
+                else { kinds[j] = 2; local = item - q_items - k_items; W = &p.lw.wv; biases[j] = p.lw.bv; }
+                int row0, row1;
+                idx[j] = 0;
+                if (kinds[j] < 2) { int head = local / half; idx[j] = local - head * half; row0 = head * m.head_dim + idx[j]; row1 = row0 + half; }
+                else { row0 = 2 * local; row1 = row0 + 1; }
+                rows4[2 * j] = row0; rows4[2 * j + 1] = row1;
+                wr[2 * j] = weight_row(*W, row0); wr[2 * j + 1] = weight_row(*W, row1);
+                sr[2 * j] = scale_row(*W, row0); sr[2 * j + 1] = scale_row(*W, row1);
+            }
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            dot_rows<WT, 4>(wr, sr, m.d_model, xs, lane, acc);
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[j] = warp_sum(acc[j]);
+            if (lane < 2 && item0 + lane < end) {
+                const int j = lane;
+                const int kind = kinds[j], row0 = rows4[2 * j], row1 = rows4[2 * j + 1];
+                float v0 = j == 0 ? acc[0] : acc[2], v1 = j == 0 ? acc[1] : acc[3];
+                const float* bias = biases[j];
                 if (bias) { v0 += bias[row0]; v1 += bias[row1]; }
                 if (kind < 2 && !gpt2) {
-                    float2 cs = p.rope[(size_t)pos * half + i];
+                    float2 cs = p.rope[(size_t)pos * half + idx[j]];
                     float r0 = v0 * cs.x - v1 * cs.y, r1 = v0 * cs.y + v1 * cs.x;
                     v0 = r0; v1 = r1;
                 }
@@ -399,7 +417,7 @@ __device__ void stage_qkv(const QkvArgs& p, int cta, int n_cta, float* xs, float
 // K/V rows are read as 16-byte vectors; softmax statistics use warp shuffles.  When the visible range is
 // split across several CTAs each writes (m, l, unnormalised ctx) and the last to finish merges them.
 
-constexpr int kAttThreads = 128;
+constexpr int kAttThreads = 256;
 constexpr int kAttSplitTokens = 256;  // positions handled by one CTA
 
 struct AttArgs {
@@ -437,15 +455,20 @@ __device__ inline void stage_attention(const AttArgs& p, int r, int head, int sp
     float lmax = -INFINITY;
     for (int t = tid; t < nt; t += kAttThreads) {
         const uint4* kr = reinterpret_cast<const uint4*>(K + (size_t)t * hd);
-        float dot = 0.f;
-        for (int c = 0; c < hd / 8; c++) {
-            uint4 w = kr[c];
-            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        uint4 kreg[16];  // the whole K row (head_dim <= 128) is requested before any arithmetic
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[i]));
-                dot = fmaf(f.x, qs[c * 8 + 2 * i], dot);
-                dot = fmaf(f.y, qs[c * 8 + 2 * i + 1], dot);
+        for (int c = 0; c < 16; c++) kreg[c] = c < hd / 8 ? __ldcg(kr + c) : make_uint4(0, 0, 0, 0);
+        float dot = 0.f;
+#pragma unroll
+        for (int c = 0; c < 16; c++) {
+            if (c < hd / 8) {
+                const uint32_t ww[4] = {kreg[c].x, kreg[c].y, kreg[c].z, kreg[c].w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[i]));
+                    dot = fmaf(f.x, qs[c * 8 + 2 * i], dot);
+                    dot = fmaf(f.y, qs[c * 8 + 2 * i + 1], dot);
+                }
             }
         }
         dot *= scale;
@@ -473,20 +496,31 @@ __device__ inline void stage_attention(const AttArgs& p, int r, int head, int sp
     const int cpl = hd / 32;  // channels per lane (head_dim 64 -> 2, 128 -> 4); smaller heads use lanes < hd
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     if (cpl >= 1) {
-        for (int t = warp; t < nt; t += nwarp) {
-            const float pt = sc[t];
-            const __half* vr = V + (size_t)t * hd + lane * cpl;
-            if (cpl == 2) {
-                float2 f = __half22float2(*reinterpret_cast<const __half2*>(vr));
-                acc[0] = fmaf(pt, f.x, acc[0]); acc[1] = fmaf(pt, f.y, acc[1]);
-            } else if (cpl == 4) {
-                uint2 w = *reinterpret_cast<const uint2*>(vr);
-                float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-                float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-                acc[0] = fmaf(pt, f0.x, acc[0]); acc[1] = fmaf(pt, f0.y, acc[1]);
-                acc[2] = fmaf(pt, f1.x, acc[2]); acc[3] = fmaf(pt, f1.y, acc[3]);
-            } else {
-                for (int c = 0; c < cpl && c < 4; c++) acc[c] = fmaf(pt, __half2float(vr[c]), acc[c]);
+        constexpr int PU = 8;  // V rows requested together
+        for (int tb = warp; tb < nt; tb += nwarp * PU) {
+            uint2 vreg[PU];
+#pragma unroll
+            for (int u = 0; u < PU; u++) {
+                const int t = tb + u * nwarp;
+                vreg[u] = make_uint2(0, 0);
+                if (t < nt) {
+                    const __half* vr = V + (size_t)t * hd + lane * cpl;
+                    if (cpl == 4) vreg[u] = __ldcg(reinterpret_cast<const uint2*>(vr));
+                    else if (cpl == 2) vreg[u].x = __ldcg(reinterpret_cast<const unsigned int*>(vr));
+                    else vreg[u].x = (unsigned int)__ldcg(reinterpret_cast<const unsigned short*>(vr));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < PU; u++) {
+                const int t = tb + u * nwarp;
+                if (t < nt) {
+                    const float pt = sc[t];
+                    float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&vreg[u].x));
+                    float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&vreg[u].y));
+                    acc[0] = fmaf(pt, f0.x, acc[0]);
+                    if (cpl >= 2) acc[1] = fmaf(pt, f0.y, acc[1]);
+                    if (cpl == 4) { acc[2] = fmaf(pt, f1.x, acc[2]); acc[3] = fmaf(pt, f1.y, acc[3]); }
+                }
             }
         }
         for (int c = 0; c < cpl && c < 4; c++) part[warp * hd + lane * cpl + c] = acc[c];
@@ -628,56 +662,68 @@ __device__ void stage_gemv(const GemvArgs& p, int cta, int n_cta, float* xs, flo
         stage_vector<EPL>(p.in + (size_t)r * p.in_stride, K, p.norm, p.norm_g, p.norm_b, m.eps, xs, red);
         float best_v = -INFINITY;
         int best_i = 0x7fffffff;
-        for (int item = begin + warp; item < end; item += kWarps) {
-            int row0, row1;
-            const uint8_t* wr[NR];
-            const __half* sr[NR];
-            if (EPI == EPI_SWIGLU) {
-                row0 = row1 = item;
-                wr[0] = weight_row(p.w, item); wr[1] = weight_row(p.w_up, item);
-                sr[0] = scale_row(p.w, item); sr[1] = scale_row(p.w_up, item);
-            } else {
-                row0 = item * NR; row1 = min(row0 + 1, n_out - 1);
-                wr[0] = weight_row(p.w, row0); wr[1] = weight_row(p.w, row1);
-                sr[0] = scale_row(p.w, row0); sr[1] = scale_row(p.w, row1);
-            }
-            float acc[NR] = {0.f, 0.f};
-            dot_rows<WT, NR>(wr, sr, K, xs, lane, acc);
-            float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
-            if (EPI == EPI_HEAD) {
-                // every lane holds the sums; keep a per-warp running first-max
-                if (v0 > best_v) { best_v = v0; best_i = row0; }
-                if (row1 != row0 && v1 > best_v) { best_v = v1; best_i = row1; }
-                if (lane == 0 && p.a.logits) {
-                    float* lg = p.a.logits + (size_t)r * m.vocab;
-                    lg[row0] = v0;
-                    if (row1 != row0) lg[row1] = v1;
+        // each warp takes two adjacent work items (four weight rows) per iteration
+        for (int item0 = begin + 2 * warp; item0 < end; item0 += 2 * kWarps) {
+            const uint8_t* wr[4];
+            const __half* sr[4];
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int item = min(item0 + j, end - 1);
+                if (EPI == EPI_SWIGLU) {
+                    wr[2 * j] = weight_row(p.w, item); wr[2 * j + 1] = weight_row(p.w_up, item);
+                    sr[2 * j] = scale_row(p.w, item); sr[2 * j + 1] = scale_row(p.w_up, item);
+                } else {
+                    const int row0 = item * NR, row1 = min(row0 + 1, n_out - 1);
+                    wr[2 * j] = weight_row(p.w, row0); wr[2 * j + 1] = weight_row(p.w, row1);
+                    sr[2 * j] = scale_row(p.w, row0); sr[2 * j + 1] = scale_row(p.w, row1);
                 }
-            } else if (lane == 0) {
-                if (EPI == EPI_RESIDUAL) {
-                    float* o = p.out + (size_t)r * p.out_stride;
-                    if (p.bias) { v0 += p.bias[row0]; v1 += p.bias[row1]; }
-                    float o0 = o[row0] + v0;
-                    o[row0] = o0;
-                    float o1 = 0.f;
-                    if (row1 != row0) { o1 = o[row1] + v1; o[row1] = o1; }
-                    if (p.a.debug && p.debug_slot >= 0 && p.layer == p.a.debug_layer && r == 0) {
-                        p.a.debug[p.debug_slot + row0] = o0;
-                        if (row1 != row0) p.a.debug[p.debug_slot + row1] = o1;
+            }
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            dot_rows<WT, 4>(wr, sr, K, xs, lane, acc);
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[j] = warp_sum(acc[j]);
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int item = item0 + j;
+                if (item >= end) break;
+                float v0 = acc[2 * j], v1 = acc[2 * j + 1];
+                const int row0 = EPI == EPI_SWIGLU ? item : item * NR;
+                const int row1 = EPI == EPI_SWIGLU ? item : min(row0 + 1, n_out - 1);
+                if (EPI == EPI_HEAD) {
+                    // every lane holds the sums; keep a per-warp running first-max
+                    if (v0 > best_v) { best_v = v0; best_i = row0; }
+                    if (row1 != row0 && v1 > best_v) { best_v = v1; best_i = row1; }
+                    if (lane == 0 && p.a.logits) {
+                        float* lg = p.a.logits + (size_t)r * m.vocab;
+                        lg[row0] = v0;
+                        if (row1 != row0) lg[row1] = v1;
                     }
-                } else if (EPI == EPI_SWIGLU) {
-                    float av = silu_f(v0) * v1;
-                    p.out[(size_t)r * p.out_stride + item] = av;
-                    if (p.a.debug && p.debug_slot >= 0 && p.layer == p.a.debug_layer && r == 0) p.a.debug[p.debug_slot + item] = av;
-                } else {  // EPI_GELU
-                    float* o = p.out + (size_t)r * p.out_stride;
-                    if (p.bias) { v0 += p.bias[row0]; v1 += p.bias[row1]; }
-                    float a0 = gelu_f(v0), a1 = gelu_f(v1);
-                    o[row0] = a0;
-                    if (row1 != row0) o[row1] = a1;
-                    if (p.a.debug && p.debug_slot >= 0 && p.layer == p.a.debug_layer && r == 0) {
-                        p.a.debug[p.debug_slot + row0] = a0;
-                        if (row1 != row0) p.a.debug[p.debug_slot + row1] = a1;
+                } else if (lane == 0) {
+                    if (EPI == EPI_RESIDUAL) {
+                        float* o = p.out + (size_t)r * p.out_stride;
+                        if (p.bias) { v0 += p.bias[row0]; v1 += p.bias[row1]; }
+                        float o0 = o[row0] + v0;
+                        o[row0] = o0;
+                        float o1 = 0.f;
+                        if (row1 != row0) { o1 = o[row1] + v1; o[row1] = o1; }
+                        if (p.a.debug && p.debug_slot >= 0 && p.layer == p.a.debug_layer && r == 0) {
+                            p.a.debug[p.debug_slot + row0] = o0;
+                            if (row1 != row0) p.a.debug[p.debug_slot + row1] = o1;
+                        }
+                    } else if (EPI == EPI_SWIGLU) {
+                        float av = silu_f(v0) * v1;
+                        p.out[(size_t)r * p.out_stride + item] = av;
+                        if (p.a.debug && p.debug_slot >= 0 && p.layer == p.a.debug_layer && r == 0) p.a.debug[p.debug_slot + item] = av;
+                    } else {  // EPI_GELU
+                        float* o = p.out + (size_t)r * p.out_stride;
+                        if (p.bias) { v0 += p.bias[row0]; v1 += p.bias[row1]; }
+                        float a0 = gelu_f(v0), a1 = gelu_f(v1);
+                        o[row0] = a0;
+                        if (row1 != row0) o[row1] = a1;
+                        if (p.a.debug && p.debug_slot >= 0 && p.layer == p.a.debug_layer && r == 0) {
+                            p.a.debug[p.debug_slot + row0] = a0;
+                            if (row1 != row0) p.a.debug[p.debug_slot + row1] = a1;
+                        }
                     }
                 }
             }

@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(kThreads) k_qkv(const QkvArgs p) {
 }
 
 __global__ void __launch_bounds__(kAttThreads) k_attention(const AttArgs p) {
-    __shared__ float sm[128 + kAttSplitTokens + 8 + (kAttThreads / 32) * 128];
+    __shared__ float sm[128 + kAttSplitTokens + 8 + (kAttThreads / 32) * 128];  // q, scores, reduction scratch, per-warp ctx
     pdl_launch_dependents();
     pdl_wait();
     stage_attention(p, blockIdx.y, blockIdx.x, blockIdx.z, sm);
@@ -101,6 +101,27 @@ __global__ void __launch_bounds__(kThreads) k_gemv(const GemvArgs p) {
     pdl_launch_dependents();
     pdl_wait();
     stage_gemv<WT, EPI>(p, blockIdx.x, gridDim.x, smem + 8, smem);
+}
+
+// Final norm + LM head + greedy argmax (a k_gemv<WT, EPI_HEAD> under its own name, so that profiles list it apart).
+template <int WT>
+__global__ void __launch_bounds__(kThreads) k_lm_head(const GemvArgs p) {
+    extern __shared__ float smem[];
+    {
+        const int n_items = (p.w.rows + 1) / 2;
+        int begin, end;
+        cta_range(n_items, blockIdx.x, gridDim.x, begin, end);
+        if (end > begin && threadIdx.x == 0) {
+            const size_t rb = weight_row_bytes(p.w.type, p.w.cols);
+            const int r0 = begin * 2, r1 = min(end * 2, p.w.rows);
+            size_t bytes = (size_t)(r1 - r0) * rb;
+            const uint8_t* b0 = weight_row(p.w, r0);
+            for (size_t off = 0; off < bytes; off += (32u << 10)) l2_prefetch(b0 + off, (unsigned)min((size_t)(32u << 10), bytes - off));
+        }
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    stage_gemv<WT, EPI_HEAD>(p, blockIdx.x, gridDim.x, smem + 8, smem);
 }
 
 __global__ void k_bump(RowState rs, int rows) {
@@ -186,7 +207,14 @@ static cudaError_t launch_gemv(int epi, int type, dim3 grid, size_t smem, cudaSt
         case EPI_RESIDUAL: return launch_gemv_typed<EPI_RESIDUAL>(type, grid, smem, s, a);
         case EPI_SWIGLU: return launch_gemv_typed<EPI_SWIGLU>(type, grid, smem, s, a);
         case EPI_GELU: return launch_gemv_typed<EPI_GELU>(type, grid, smem, s, a);
-        case EPI_HEAD: return launch_gemv_typed<EPI_HEAD>(type, grid, smem, s, a);
+        case EPI_HEAD:
+            switch (type) {
+                case WT_F16: return launch_pdl(k_lm_head<WT_F16>, grid, dim3(kThreads), smem, s, a);
+                case WT_BF16: return launch_pdl(k_lm_head<WT_BF16>, grid, dim3(kThreads), smem, s, a);
+                case WT_Q8_0: return launch_pdl(k_lm_head<WT_Q8_0>, grid, dim3(kThreads), smem, s, a);
+                case WT_Q4_0: return launch_pdl(k_lm_head<WT_Q4_0>, grid, dim3(kThreads), smem, s, a);
+            }
+            return cudaErrorInvalidValue;
     }
     return cudaErrorInvalidValue;
 }
@@ -209,7 +237,7 @@ static void raise_smem_limits_on_current_device() {
 #define ESP_SET(k) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes)
 #define ESP_SET_ALL(WT)                                                                 \
     ESP_SET((k_gemv<WT, EPI_RESIDUAL>)); ESP_SET((k_gemv<WT, EPI_SWIGLU>));             \
-    ESP_SET((k_gemv<WT, EPI_GELU>)); ESP_SET((k_gemv<WT, EPI_HEAD>)); ESP_SET((k_qkv<WT>));
+    ESP_SET((k_gemv<WT, EPI_GELU>)); ESP_SET((k_lm_head<WT>)); ESP_SET((k_qkv<WT>));
     ESP_SET_ALL(WT_F16) ESP_SET_ALL(WT_BF16) ESP_SET_ALL(WT_Q8_0) ESP_SET_ALL(WT_Q4_0)
 #undef ESP_SET_ALL
 #undef ESP_SET
@@ -238,6 +266,7 @@ Engine::~Engine() {
     for (void* p : owned_) cudaFree(p);
     if (h_rows_block_) cudaFreeHost(h_rows_block_);
     if (h_next_) cudaFreeHost(h_next_);
+    if (h_mega_ctl_) cudaFreeHost(h_mega_ctl_);
     if (stream_) cudaStreamDestroy(stream_);
 }
 
@@ -557,6 +586,7 @@ int32_t Engine::finalize() {
     size_t dbg = (size_t)m_.q_dim * 2 + 2 * m_.kv_dim + 2 * m_.d_model + m_.hidden;
     if ((rc = dev_alloc(owned_, &d_debug_, dbg))) return rc;
     ESP_CUDA_TRY(cudaDeviceSynchronize());
+    if ((rc = build_mega())) return rc;
     finalized_ = true;
     return reset();
 }
@@ -1030,6 +1060,12 @@ int32_t Engine::decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, 
         if (n_out) n_out[s] = 0;
     }
     if (max_lim == 0) { if (device_ms) *device_ms = 0.f; return ESP_CUDA_OK; }
+    if (mega_ready_ && n_seq == 1 && debug_layer_ < 0 && !(cfg_.flags & (ESP_CUDA_FLAG_NO_MEGAKERNEL | ESP_CUDA_FLAG_NO_GRAPH))) {
+        if ((rc = run_mega(lim[0], device_ms, first_token_ms))) return rc;
+        if (n_out) n_out[0] = lim[0];
+        if (out_tokens) ESP_CUDA_TRY(cudaMemcpy(out_tokens, rs_.out, sizeof(uint32_t) * lim[0], cudaMemcpyDeviceToHost));
+        return ESP_CUDA_OK;
+    }
     std::vector<int> active(n_seq);
     for (int s = 0; s < n_seq; s++) active[s] = lim[s] > 0;
     if ((rc = upload_rows(n_seq, seq.data(), pos.data(), nullptr, active.data(), lim.data(), true))) return rc;
@@ -1053,6 +1089,8 @@ int32_t Engine::decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, 
         }
     }
     ESP_CUDA_TRY(cudaEventRecord(ev_end_, stream_));
+    timings_.kernel_launches = launches_by_key_.count(n_seq * 8 + (STEP_HEAD | STEP_FEEDBACK)) ? launches_by_key_[n_seq * 8 + (STEP_HEAD | STEP_FEEDBACK)] : 1;
+    if (max_lim > 1) timings_.kernel_launches += (max_lim - 1) * launches_last_step_;
     ESP_CUDA_TRY(cudaMemcpyAsync(h_rows_block_, d_rows_block_, sizeof(int) * 6 * max_rows_, cudaMemcpyDeviceToHost, stream_));
     ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
     if (device_ms) ESP_CUDA_TRY(cudaEventElapsedTime(device_ms, ev_begin_, ev_end_));
@@ -1063,6 +1101,133 @@ int32_t Engine::decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, 
         if (n > 0 && out_tokens)
             ESP_CUDA_TRY(cudaMemcpy(out_tokens + (size_t)s * out_stride, rs_.out + (size_t)s * out_stride_, sizeof(uint32_t) * n, cudaMemcpyDeviceToHost));
     }
+    return ESP_CUDA_OK;
+}
+
+static int pad128(long long v) { return (int)((v + 127) / 128 * 128); }
+
+int32_t Engine::build_mega() {
+    mega_ready_ = false;
+    if (cfg_.flags & ESP_CUDA_FLAG_NO_MEGAKERNEL) return ESP_CUDA_OK;
+    if (m_.arch != ARCH_LLAMA || m_.eos_token >= 0) return ESP_CUDA_OK;
+    if (m_.head_dim != 32 && m_.head_dim != 64 && m_.head_dim != 128) return ESP_CUDA_OK;
+    if (m_.d_model > 4096 || m_.d_model % 8 || m_.n_head > sm_count_) return ESP_CUDA_OK;
+    if (tensors_.at("embeddings/token").type != ESP_CUDA_F16 || tensors_.at("lm_head").type != ESP_CUDA_F16) return ESP_CUDA_OK;
+    for (int l = 0; l < m_.n_layer; l++)
+        for (const char* n : {"wq", "wk", "wv", "wo", "w1", "w2", "w3"})
+            if (tensors_.at("layers/" + std::to_string(l) + "/" + n).type != ESP_CUDA_F16) return ESP_CUDA_OK;
+    int coop = 0, smem_max = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, cfg_.device);
+    cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, cfg_.device);
+    if (!coop) return ESP_CUDA_OK;
+    MegaPlan p{};
+    const int P = sm_count_;
+    p.n_cta = P;
+    p.row_bytes = m_.d_model * 2;
+    p.ppc = ((m_.q_dim + 2 * m_.kv_dim) / 2 + P - 1) / P;
+    p.blocks = P / m_.n_head;
+    p.rpb = (m_.d_model + p.blocks - 1) / p.blocks;
+    p.hpc = (m_.hidden + P - 1) / P;
+    p.vpc = (m_.vocab + P - 1) / P;
+    p.s1_bytes = pad128((long long)2 * p.ppc * p.row_bytes);
+    p.s2_bytes = pad128((long long)p.rpb * m_.head_dim * 2);
+    p.s3a_bytes = pad128((long long)2 * p.hpc * p.row_bytes);
+    p.s3b_bytes = pad128((long long)p.hpc * p.row_bytes);
+    int layer_max = std::max(std::max(p.s1_bytes, p.s2_bytes), std::max(p.s3a_bytes, p.s3b_bytes));
+    int rh = std::max(2, (std::max(layer_max, 48 * 1024) / p.row_bytes) & ~1);
+    rh = std::min(rh, (p.vpc + 1) & ~1);
+    p.head_rows_per_chunk = rh;
+    p.head_chunks = (p.vpc + rh - 1) / rh;
+    p.head_chunk_bytes = pad128((long long)rh * p.row_bytes);
+    p.slot_bytes = std::max(layer_max, p.head_chunk_bytes);
+    p.layer_bytes = (long long)p.s1_bytes + p.s2_bytes + p.s3a_bytes + p.s3b_bytes;
+    p.cta_bytes = p.layer_bytes * m_.n_layer + (long long)p.head_chunks * p.head_chunk_bytes;
+    p.n_slots = 2;
+    MegaPlan probe = p;
+    for (int ns = 8; ns >= 2; ns--) {
+        probe.n_slots = ns;
+        if (mega_smem_bytes(m_, probe) <= smem_max) { p.n_slots = ns; break; }
+        if (ns == 2) return ESP_CUDA_OK;  // the per-layer slice does not fit: the per-stage kernels serve this model
+    }
+    p.smem_bytes = mega_smem_bytes(m_, p);
+    if (p.smem_bytes > smem_max) return ESP_CUDA_OK;
+    ESP_CUDA_TRY(cudaFuncSetAttribute(k_decode_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes));
+    int occ = 0;
+    ESP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_decode_mega, kMegaThreads, p.smem_bytes));
+    if (occ < 1) return ESP_CUDA_OK;
+
+    int32_t rc;
+    if ((rc = dev_alloc(owned_, &d_pack_, (size_t)P * p.cta_bytes, false))) return rc;
+    if ((rc = dev_alloc(owned_, &d_norms_, (size_t)(2 * m_.n_layer + 1) * m_.d_model, false))) return rc;
+    if ((rc = dev_alloc(owned_, &d_xbuf_, (size_t)3 * m_.d_model))) return rc;
+    if ((rc = dev_alloc(owned_, &d_mega_ctl_, 8))) return rc;
+    ESP_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&h_mega_ctl_), 8 * sizeof(unsigned long long)));
+    // per-layer source pointers
+    std::vector<const __half*> ptrs((size_t)7 * m_.n_layer);
+    const char* names[7] = {"wq", "wk", "wv", "wo", "w1", "w2", "w3"};
+    for (int k = 0; k < 7; k++)
+        for (int l = 0; l < m_.n_layer; l++)
+            ptrs[(size_t)k * m_.n_layer + l] = static_cast<const __half*>(tensors_.at("layers/" + std::to_string(l) + "/" + names[k]).data);
+    const __half** d_ptrs = nullptr;
+    ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_ptrs), ptrs.size() * sizeof(void*)));
+    cudaError_t e = cudaMemcpy(d_ptrs, ptrs.data(), ptrs.size() * sizeof(void*), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) {
+        PackSources src{};
+        src.wq = d_ptrs; src.wk = d_ptrs + m_.n_layer; src.wv = d_ptrs + 2 * m_.n_layer; src.wo = d_ptrs + 3 * m_.n_layer;
+        src.w1 = d_ptrs + 4 * m_.n_layer; src.w2 = d_ptrs + 5 * m_.n_layer; src.w3 = d_ptrs + 6 * m_.n_layer;
+        src.lm_head = static_cast<const __half*>(tensors_.at("lm_head").data);
+        k_build_pack<<<P, 256, 0, stream_>>>(src, p, m_, d_pack_);
+        e = cudaGetLastError();
+    }
+    for (int l = 0; l < m_.n_layer && e == cudaSuccess; l++) {
+        std::string pre = "layers/" + std::to_string(l) + "/";
+        e = cudaMemcpyAsync(d_norms_ + (size_t)(2 * l) * m_.d_model, tensors_.at(pre + "rms_att").f32, sizeof(float) * m_.d_model, cudaMemcpyDeviceToDevice, stream_);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(d_norms_ + (size_t)(2 * l + 1) * m_.d_model, tensors_.at(pre + "rms_ffn").f32, sizeof(float) * m_.d_model, cudaMemcpyDeviceToDevice, stream_);
+    }
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(d_norms_ + (size_t)(2 * m_.n_layer) * m_.d_model, tensors_.at("rms_final").f32, sizeof(float) * m_.d_model, cudaMemcpyDeviceToDevice, stream_);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream_);
+    cudaFree(d_ptrs);
+    ESP_CUDA_TRY(e);
+    mega_plan_ = p;
+    mega_ready_ = true;
+    return ESP_CUDA_OK;
+}
+
+// Runs the whole greedy loop (n_steps emitted tokens) of sequence 0 as one cooperative launch.
+int32_t Engine::run_mega(int n_steps, float* device_ms, double* first_token_ms) {
+    MegaArgs a{};
+    a.m = m_; a.plan = mega_plan_; a.pack = d_pack_; a.norms = d_norms_;
+    a.tok_emb = static_cast<const uint16_t*>(tensors_.at("embeddings/token").data);
+    a.rope = d_rope_; a.kv = kv_; a.q = act_.q; a.xbuf = d_xbuf_; a.hidden_io = act_.hidden;
+    a.best = d_mega_ctl_;
+    a.barrier = reinterpret_cast<unsigned int*>(d_mega_ctl_ + 2);
+    a.error = reinterpret_cast<int*>(d_mega_ctl_ + 2) + 1;
+    a.stamps = d_mega_ctl_ + 3;
+    a.rs = rs_;
+    a.n_steps = n_steps;
+    a.pos0 = h_visible_[0];
+    if (!ev_begin_) { ESP_CUDA_TRY(cudaEventCreate(&ev_begin_)); ESP_CUDA_TRY(cudaEventCreate(&ev_end_)); }
+    ESP_CUDA_TRY(cudaMemsetAsync(d_mega_ctl_, 0, 8 * sizeof(unsigned long long), stream_));
+    ESP_CUDA_TRY(cudaEventRecord(ev_begin_, stream_));
+    void* args[] = {&a};
+    ESP_CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(k_decode_mega), dim3(mega_plan_.n_cta), dim3(kMegaThreads), args,
+                                             (size_t)mega_plan_.smem_bytes, stream_));
+    ESP_CUDA_TRY(cudaEventRecord(ev_end_, stream_));
+    ESP_CUDA_TRY(cudaMemcpyAsync(h_mega_ctl_, d_mega_ctl_, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    launches_last_step_ = 1;
+    timings_.kernel_launches = 1;
+    const int err = reinterpret_cast<int*>(h_mega_ctl_ + 2)[1];
+    if (err != 0) {
+        std::ostringstream os;
+        os << "persistent decode kernel gave up waiting (code " << err << ": 2 = grid barrier, 3 = weight chunk, 4 = ring slot)";
+        return fail(ESP_CUDA_ERR_TIMEOUT, os.str());
+    }
+    if (device_ms) ESP_CUDA_TRY(cudaEventElapsedTime(device_ms, ev_begin_, ev_end_));
+    if (first_token_ms) *first_token_ms = (double)(h_mega_ctl_[4] - h_mega_ctl_[3]) / 1e6;
+    h_visible_[0] += n_steps - 1;
     return ESP_CUDA_OK;
 }
 

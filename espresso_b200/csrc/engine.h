@@ -11,6 +11,7 @@
 
 #include "../../include/espresso_cuda.h"
 #include "decode_kernels.cuh"
+#include "mega_kernel.cuh"
 
 namespace esp {
 
@@ -86,6 +87,8 @@ private:
     Weight weight_of(const DeviceTensor& t) const;
     LayerWeights layer_weights(int l) const;
     size_t gemv_smem(int type, int K, bool with_tmp) const;
+    int32_t build_mega();   // packs the weights for the persistent decode kernel when the model qualifies
+    int32_t run_mega(int n_steps, float* device_ms, double* first_token_ms);
 
     esp_cuda_config cfg_;
     ModelDims m_{};
@@ -118,6 +121,15 @@ private:
     std::map<int, int> launches_by_key_;
     std::vector<cudaEvent_t> prof_events_;
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
+
+    // persistent decode kernel (single sequence, Llama fp16 models whose per-layer slice fits in shared memory)
+    bool mega_ready_ = false;
+    MegaPlan mega_plan_{};
+    uint8_t* d_pack_ = nullptr;
+    float* d_norms_ = nullptr;
+    float* d_xbuf_ = nullptr;
+    unsigned long long* d_mega_ctl_ = nullptr;  // [0..1] best, [2] barrier (u32) + error (i32), [3..4] time stamps
+    unsigned long long* h_mega_ctl_ = nullptr;  // pinned mirror
     esp_cuda_timings timings_{};
     int launches_last_step_ = 0;
 };

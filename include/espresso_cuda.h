@@ -94,7 +94,7 @@ typedef struct esp_cuda_generation_result {
  * (Sources/Espresso/DecodeForwardPass.swift:322-339): projections, attention, FFN, head. */
 typedef struct esp_cuda_timings {
     float qkv_ms, attention_ms, ffn_ms, head_ms, total_ms;
-    int32_t kernel_launches; /* kernels of this library launched by the most recent step */
+    int32_t kernel_launches; /* kernels of this library launched by the most recent step or decode loop */
 } esp_cuda_timings;
 
 /* ---- lifetime (replaces ane_interop_compile / ane_interop_free, ane_interop.h:24-35) ------------ */
