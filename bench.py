@@ -30,9 +30,21 @@ from espresso_b200 import model_config as mc  # noqa: E402
 from espresso_b200.synthetic import synthetic_prompt, write_synthetic_model  # noqa: E402
 
 WORKLOADS = {
-    # name: (config factory, prompt tokens, decode tokens, sequences per GPU, weight storage)
-    "c1": dict(cfg=mc.llama_6l, prompt=16, decode=128, n_seq=1, kind="f16",
+    # cfg factory, prompt tokens, decode tokens, sequences per GPU (total for sharded jobs), weight storage
+    "c1": dict(cfg=mc.llama_6l, prompt=16, decode=128, n_seq=1, kind="f16", bpw=2.0,
                label="llama 6L d768 12h vocab32000 ctx256 fp16, batch 1, 16-token prompt, 128 greedy steps"),
+    "c2": dict(cfg=mc.llama_6l, draft=mc.llama_draft_1l, prompt=16, decode=128, n_seq=1, kind="f16", bpw=2.0,
+               label="llama 6L d768 target + 1-layer draft, exact two-token verify, batch 1, 16-token prompt, 128 tokens"),
+    "c3": dict(cfg=mc.gpt2_117m, prompt=64, decode=256, n_seq=256, sharded=True, kind="f16", bpw=2.0,
+               label="gpt2-117M shape 12L d768 vocab50257 ctx1024 fp16, 256 independent sequences sharded over the GPUs, 64-token prompts, 256 greedy steps"),
+    "c4q8": dict(cfg=mc.llama_1b, prompt=128, decode=256, n_seq=1, kind="q8_0", bpw=34.0 / 32, device_weights=True,
+                 label="llama 1.1B shape 22L d2048 GQA 32/4 ctx2048, GGUF Q8_0 matrices + LM head, batch 1, 128-token prompt, 256 steps"),
+    "c4q4": dict(cfg=mc.llama_1b, prompt=128, decode=256, n_seq=1, kind="q4_0", bpw=18.0 / 32, device_weights=True,
+                 label="llama 1.1B shape 22L d2048 GQA 32/4 ctx2048, GGUF Q4_0 matrices + LM head, batch 1, 128-token prompt, 256 steps"),
+    "c4q8b16": dict(cfg=mc.llama_1b, prompt=128, decode=256, n_seq=16, kind="q8_0", bpw=34.0 / 32, device_weights=True,
+                    label="llama 1.1B shape Q8_0, batch 16, 128-token prompts, 256 steps"),
+    "c4q4b16": dict(cfg=mc.llama_1b, prompt=128, decode=256, n_seq=16, kind="q4_0", bpw=18.0 / 32, device_weights=True,
+                    label="llama 1.1B shape Q4_0, batch 16, 128-token prompts, 256 steps"),
 }
 
 
@@ -113,19 +125,16 @@ def algorithmic_bytes_per_token(cfg, prompt: int, decode: int, n_seq: int, bytes
     return w / n_seq + kv * mean_vis + kv
 
 
-def run_cpu_oracle(workload: dict, weight_dir: str, steps: int, warmup: int, threads: int | None = None) -> dict:
-    """Times the CPU restatement of the reference's decode path on the host cores."""
+def truncated(cfg, n_layer):
+    import dataclasses
+    return dataclasses.replace(cfg, nLayer=n_layer, name=f"{cfg.name}-{n_layer}l")
+
+
+def time_oracle_decode(weight_dir: str, prompt, decode: int, steps: int, warmup: int) -> list[float]:
+    """Seconds per decode run (prefill untimed) of the CPU restatement of the reference's path."""
     import oracle
 
-    lib = oracle.lib()
-    if threads:
-        lib.esp_oracle_set_num_threads(threads)
-    cores = lib.esp_oracle_num_threads()
-    cfg = workload["cfg"]()
-    model = oracle.Model.from_dir(weight_dir)
-    rt = oracle.Runtime(model)
-    prompt = synthetic_prompt(cfg.vocab, workload["prompt"])
-    decode = workload["decode"]
+    rt = oracle.Runtime(oracle.Model.from_dir(weight_dir))
     times = []
     for i in range(warmup + steps):
         assert rt.prefill(prompt) == 0
@@ -137,9 +146,90 @@ def run_cpu_oracle(workload: dict, weight_dir: str, steps: int, warmup: int, thr
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
-    total = sum(times)
-    return {"value": decode * len(times) / total, "ms_per_step": 1e3 * total / len(times), "cores": cores,
-            "sample": f"full workload per step: {workload['prompt']}-token prompt (untimed prefill) + {decode} greedy decode steps, {len(times)} steps"}
+    return times
+
+
+def run_cpu_oracle(workload: dict, steps: int, warmup: int, threads: int | None = None) -> dict:
+    """Times the CPU restatement of the reference's decode path on the host cores.
+
+    Small models run the whole workload.  For the larger shapes one sequence is decoded for a few tokens on
+    1- and 2-layer truncations of the model and the per-token time is extrapolated linearly in the layer count
+    (per-layer cost = t(2 layers) - t(1 layer); the remainder is embedding + head); the sample says so.
+    """
+    import oracle
+
+    lib = oracle.lib()
+    if threads:
+        lib.esp_oracle_set_num_threads(threads)
+    cores = lib.esp_oracle_num_threads()
+    cfg = workload["cfg"]()
+    decode = workload["decode"]
+    prompt = synthetic_prompt(cfg.vocab, workload["prompt"])
+    small = cfg.nLayer * cfg.dModel * cfg.hiddenDim < 6 * 768 * 2048 * 1.5 and not workload.get("sharded")
+    tmp = tempfile.mkdtemp(prefix="esp_cpu_")
+    try:
+        if small and "draft" not in workload:
+            write_synthetic_model(cfg, tmp)
+            times = time_oracle_decode(tmp, prompt, decode, steps, warmup)
+            total = sum(times)
+            return {"value": decode * len(times) / total, "ms_per_step": 1e3 * total / len(times), "cores": cores,
+                    "sample": f"full workload per step: {workload['prompt']}-token prompt (untimed prefill) + {decode} greedy decode steps, {len(times)} steps"}
+        if "draft" in workload:
+            # the reference's two-token loop on the CPU: target and draft advance token by token (Engine.swift:6014-6190)
+            write_synthetic_model(cfg, tmp)
+            dtmp = tempfile.mkdtemp(prefix="esp_cpu_draft_")
+            write_synthetic_model(workload["draft"](), dtmp, seed=1235)
+            full = oracle.Runtime(oracle.Model.from_dir(tmp))
+            draft = oracle.Runtime(oracle.Model.from_dir(dtmp))
+            times = []
+            for i in range(warmup + steps):
+                t0 = time.perf_counter()
+                toks, st = oracle.generate_two_token(full, draft, prompt, decode)
+                if i >= warmup:
+                    times.append(time.perf_counter() - t0)
+            shutil.rmtree(dtmp, ignore_errors=True)
+            total = sum(times)
+            return {"value": decode * len(times) / total, "ms_per_step": 1e3 * total / len(times), "cores": cores,
+                    "sample": f"full two-token loop incl. token-by-token prefill of target and draft, {decode} tokens, {len(times)} steps"}
+        few = 8
+        per = {}
+        for nl in (1, 2):
+            d = os.path.join(tmp, f"l{nl}")
+            write_synthetic_model(truncated(cfg, nl), d)
+            per[nl] = min(time_oracle_decode(d, prompt[:16], few, 1, 1)) / few
+            shutil.rmtree(d, ignore_errors=True)
+        layer = max(per[2] - per[1], 1e-9)
+        tok_s = 1.0 / (per[1] - layer + cfg.nLayer * layer)
+        return {"value": tok_s, "ms_per_step": 1e3 * decode / tok_s, "cores": cores,
+                "sample": f"one sequence, {few} decode steps at context ~16 on 1- and 2-layer truncations of the fp32 model, "
+                          f"per-token time extrapolated linearly to {cfg.nLayer} layers; sequences are decoded one at a time on the CPU"}
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+
+def gemv_table(runtime, device: int, peak: float) -> dict:
+    """Kernel-level y = W.x bandwidth for every weight storage type (matrix copies rotate so that reads miss L2)."""
+    import numpy as np
+    from espresso_b200 import gguf_quant
+
+    out = {}
+    rng = np.random.default_rng(7)
+    rows, cols = 8192, 4096
+    w = (rng.standard_normal((rows, cols)).astype(np.float32) * np.float32(0.02))
+    x = rng.standard_normal(cols).astype(np.float32)
+    for kind, bpw in (("f16", 2.0), ("bf16", 2.0), ("q8_0", 34 / 32), ("q4_0", 18 / 32)):
+        if kind == "f16":
+            stored = w.astype(np.float16)
+        elif kind == "bf16":
+            stored = (w.view(np.uint32) >> 16).astype(np.uint16)
+        else:
+            stored = gguf_quant.quantize(kind, w)
+        nbytes = rows * cols * bpw
+        copies = max(2, int(600e6 // nbytes) + 1)
+        _, ms = runtime.gemv_bench(kind, stored, rows, cols, x, warmup=5, iterations=40, copies=copies, device=device)
+        gbs = (nbytes + cols * 4 + rows * 4) / (ms / 1e3) / 1e9
+        out[kind] = {"rows": rows, "cols": cols, "ms": ms, "GBps": gbs, "frac_of_hbm_peak": gbs / peak}
+    return out
 
 
 def main() -> None:
@@ -150,57 +240,80 @@ def main() -> None:
     ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--decode-tokens", type=int, default=0, help="override the workload's decode length (profiling of small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gemv-table", action="store_true")
+    ap.add_argument("--per-stage", action="store_true", help="use the per-stage kernels even where the persistent kernel applies")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "ours":
+        args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.decode_tokens > 0:
+        wl["decode"] = args.decode_tokens
     cfg = wl["cfg"]()
     metric, unit = "decode tokens/s (whole job)", "tokens/s"
 
+    if args.impl == "reference":
+        # The reference's own CPU implementation of the path, restated (the Swift/Accelerate original does not
+        # build on Linux); rank 0 alone runs it on all host cores.
+        if rank != 0:
+            return
+        r = run_cpu_oracle(wl, max(args.steps, 1), args.warmup)
+        line = {
+            "impl": "reference", "metric": metric, "value": r["value"], "unit": unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": wl["label"], "l2": "fp32 weights exceed the host caches"},
+            "cpu_baseline": {"value": r["value"], "unit": unit, "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+            "e2e": {"value": r["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from espresso_b200 import runtime
+    from espresso_b200.sharding import shard_range
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU implementation")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
     tmp = tempfile.mkdtemp(prefix=f"esp_bench_r{rank}_")
     try:
-        if args.impl == "reference":
-            # The reference's own CPU implementation of the path, restated (the Swift/Accelerate original does not
-            # build on Linux); rank 0 alone runs it.
-            if rank != 0:
-                return
+        n_prompt, n_decode = wl["prompt"], wl["decode"]
+        if wl.get("sharded"):
+            b, e = shard_range(wl["n_seq"], rank, world)
+            n_seq, first_stream, scaling = e - b, b, "strong"
+        else:
+            n_seq, first_stream, scaling = wl["n_seq"], rank * wl["n_seq"], "weak"
+        prompts = np.stack([synthetic_prompt(cfg.vocab, n_prompt, stream=first_stream + s) for s in range(n_seq)])
+        flags = runtime.FLAG_NO_MEGAKERNEL if args.per_stage else 0
+        if wl.get("device_weights"):
+            from espresso_b200.synthetic_device import upload_synthetic
+
+            eng = runtime.DecodeEngine.empty(cfg, max_batch=n_seq, device=local_rank, flags=flags)
+            upload_synthetic(eng, cfg, wl["kind"], device=local_rank)
+        else:
             write_synthetic_model(cfg, tmp)
-            r = run_cpu_oracle(wl, tmp, max(args.steps, 1), args.warmup)
-            line = {
-                "impl": "reference", "metric": metric, "value": r["value"], "unit": unit, "n_gpus": args.gpus,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": wl["label"], "l2": "weights (268 MB fp32) exceed the host caches"},
-                "cpu_baseline": {"value": r["value"], "unit": unit, "cores": r["cores"], "kind": "port", "sample": r["sample"]},
-                "e2e": {"value": r["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            }
-            print(json.dumps(line))
-            return
-
-        import torch
-        import torch.distributed as dist
-
-        from espresso_b200 import runtime
-
-        if not torch.cuda.is_available():
-            raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU implementation")
-        torch.cuda.set_device(local_rank)
-        if world > 1:
-            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-
-        def barrier():
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-
-        write_synthetic_model(cfg, tmp)
-        n_seq, n_prompt, n_decode = wl["n_seq"], wl["prompt"], wl["decode"]
-        prompts = np.stack([synthetic_prompt(cfg.vocab, n_prompt, stream=rank * n_seq + s) for s in range(n_seq)])
-        eng = runtime.DecodeEngine.build(tmp, max_batch=n_seq, device=local_rank)
+            eng = runtime.DecodeEngine.build(tmp, max_batch=n_seq, device=local_rank, flags=flags)
+        draft = None
+        if "draft" in wl:
+            dtmp = os.path.join(tmp, "draft")
+            write_synthetic_model(wl["draft"](), dtmp, seed=1235)
+            draft = runtime.DecodeEngine.build(dtmp, device=local_rank, flags=flags)
 
         def prefill():
             if n_seq == 1:
@@ -208,29 +321,47 @@ def main() -> None:
             else:
                 eng.prefill_batch(prompts)
 
-        # ---- device-resident throughput: K timed steps, each a device-driven decode of n_decode tokens ----
-        prefill()
-        cp = eng.capture_checkpoint() if n_seq == 1 else None
-        for _ in range(args.warmup):
-            if cp is not None:
-                eng.rollback(cp)
-            else:
-                prefill()
-            eng.decode(n_decode, n_seq)
         sampler = ClockSampler(physical_gpu_index(local_rank))
-        barrier()
-        sampler.start()
-        step_ms, launches = [], 0
-        for _ in range(args.steps):
-            if cp is not None:
-                eng.rollback(cp)  # positions return to the end of the prompt; KV slots are simply overwritten
-            else:
-                prefill()
-            toks, ms = eng.decode(n_decode, n_seq)
-            assert all(len(t) == n_decode for t in toks)
-            step_ms.append(ms)
-            launches += eng.timings()["kernel_launches"]
-        barrier()
+        step_ms, launches, extra = [], 0, {}
+        if draft is None:
+            # ---- device-resident throughput: K timed steps, each a device-driven decode of n_decode tokens ----
+            prefill()
+            cp = eng.capture_checkpoint() if n_seq == 1 else None
+            for _ in range(args.warmup):
+                if cp is not None:
+                    eng.rollback(cp)
+                else:
+                    prefill()
+                eng.decode(n_decode, n_seq)
+            barrier()
+            sampler.start()
+            for _ in range(args.steps):
+                if cp is not None:
+                    eng.rollback(cp)  # positions return to the end of the prompt; KV slots are simply overwritten
+                else:
+                    prefill()
+                toks, ms = eng.decode(n_decode, n_seq)
+                assert all(len(t) == n_decode for t in toks) or cfg.architecture == "gpt2"
+                step_ms.append(ms)
+                launches += eng.timings()["kernel_launches"]
+            barrier()
+        else:
+            # ---- two-token speculative loop: host-driven passes, timed on the host from the end of prefill ----
+            for _ in range(args.warmup):
+                eng.generate_two_token(draft, prompts[0], n_decode)
+            barrier()
+            sampler.start()
+            acc, com = [], []
+            for _ in range(args.steps):
+                res = eng.generate_two_token(draft, prompts[0], n_decode)
+                assert len(res.tokens) == n_decode
+                step_ms.append(res.totalDecodeMs)
+                acc.append(res.acceptedFutureTokensPerPass)
+                com.append(res.committedExactTokensPerPass)
+                launches += res.speculativePasses * (eng.timings()["kernel_launches"] + draft.timings()["kernel_launches"])
+            barrier()
+            extra["two_token"] = {"accepted_future_tokens_per_pass": statistics.mean(acc), "committed_exact_tokens_per_pass": statistics.mean(com),
+                                  "note": "draft and target are independent random models, so proposals are almost never accepted"}
         clocks = sampler.stop()
         total_ms = sum(step_ms)
 
@@ -238,32 +369,36 @@ def main() -> None:
         e2e_times = []
         for i in range(args.warmup + args.steps):
             t0 = time.perf_counter()
-            if n_seq == 1:
+            if draft is not None:
+                res = eng.generate_two_token(draft, prompts[0], n_decode)
+            elif n_seq == 1:
                 res = eng.generate(prompts[0], n_decode)
-                assert len(res.tokens) == n_decode
             else:
-                toks, res = eng.generate_batch(prompts, n_decode)
+                _, res = eng.generate_batch(prompts, n_decode)
             torch.cuda.synchronize()
             if i >= args.warmup:
                 e2e_times.append(time.perf_counter() - t0)
         e2e_total = sum(e2e_times)
 
+        tokens_local = n_seq * n_decode * args.steps
         if world > 1:
             t = torch.tensor([total_ms, e2e_total], dtype=torch.float64, device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             total_ms, e2e_total = float(t[0]), float(t[1])
-            lt = torch.tensor([launches], dtype=torch.int64, device="cuda")
+            lt = torch.tensor([launches, tokens_local], dtype=torch.int64, device="cuda")
             dist.all_reduce(lt)
-            launches = int(lt[0])
-        tokens_all = world * n_seq * n_decode * args.steps
+            launches, tokens_all = int(lt[0]), int(lt[1])
+        else:
+            tokens_all = tokens_local
         value = tokens_all / (total_ms / 1e3)
         e2e_value = tokens_all / e2e_total
 
         # ---- roofline of the dominant kernel, timed live with CUDA events ----
         peak, peak_kind = read_peaks()
-        head_bytes = cfg.vocab * cfg.dModel * 2 + cfg.dModel * 2
-        bytes_tok = algorithmic_bytes_per_token(cfg, n_prompt, n_decode, n_seq, 2.0)
-        persistent = n_seq == 1 and launches == args.steps
+        bpw = wl["bpw"]
+        head_bytes = cfg.vocab * cfg.dModel * bpw + cfg.dModel * 2
+        bytes_tok = algorithmic_bytes_per_token(cfg, n_prompt, n_decode, n_seq, bpw)
+        persistent = draft is None and n_seq == 1 and launches == args.steps * world
         if persistent:
             # one launch of the persistent kernel = one whole step (n_decode heads, n_decode - 1 forward passes)
             launch_bytes = head_bytes + (n_decode - 1) * bytes_tok
@@ -273,41 +408,51 @@ def main() -> None:
                         "frac": launch_bytes / launch_s / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
                         "bytes_per_launch": launch_bytes, "bytes_per_token": bytes_tok}
         else:
-            prof = runtime.DecodeEngine.build(tmp, max_batch=n_seq, device=local_rank, flags=runtime.FLAG_NO_GRAPH)
             head_ms = []
-            if n_seq == 1:
+            if n_seq == 1 and draft is None and not wl.get("device_weights"):
+                prof = runtime.DecodeEngine.build(tmp, max_batch=n_seq, device=local_rank, flags=runtime.FLAG_NO_GRAPH)
                 prof.prefill(prompts[0])
                 tok = prof.select_greedy_token()
                 for i in range(40):
                     tok = prof.decode_step(tok)
                     if i >= 8:
                         head_ms.append(prof.timings()["head_ms"])
-            prof.close()
+                prof.close()
             head_t = statistics.mean(head_ms) if head_ms else None
-            roofline = {"bound": "hbm", "kernel": "k_lm_head (final norm + LM head + argmax)",
-                        "achieved": (head_bytes / (head_t / 1e3) / 1e9) if head_t else None, "peak": peak, "unit": "GB/s",
-                        "frac": (head_bytes / (head_t / 1e3) / 1e9 / peak) if head_t else None, "traffic": None, "peak_kind": peak_kind,
-                        "whole_step": {"bytes_per_token": bytes_tok, "achieved": value / world * bytes_tok / 1e9,
-                                       "frac": value / world * bytes_tok / 1e9 / peak}}
+            per_gpu_tok_s = value / world
+            roofline = {"bound": "hbm", "kernel": "k_lm_head (final norm + LM head + argmax)" if head_t else "whole decode step (all per-stage kernels of one token)",
+                        "achieved": (head_bytes / (head_t / 1e3) / 1e9) if head_t else per_gpu_tok_s * bytes_tok / 1e9, "peak": peak, "unit": "GB/s",
+                        "frac": ((head_bytes / (head_t / 1e3) / 1e9) if head_t else per_gpu_tok_s * bytes_tok / 1e9) / peak, "traffic": None,
+                        "peak_kind": peak_kind,
+                        "whole_step": {"bytes_per_token": bytes_tok, "achieved": per_gpu_tok_s * bytes_tok / 1e9,
+                                       "frac": per_gpu_tok_s * bytes_tok / 1e9 / peak}}
 
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": total_ms / args.steps, "ms_per_token": total_ms / args.steps / n_decode, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16 weights and KV, f32 accumulate", "data": "synthetic",
-            "config": {"workload": wl["label"], "parallelism": "replicas only (one independent sequence per GPU)" if world > 1 else "single GPU",
-                       "l2": "no flush: every decode step streams 134 MB of weights + KV, more than the 126 MB L2"},
+            "scaling": scaling, "vs_baseline": None, "dtype": f"{wl['kind']} weights, f16 KV, f32 accumulate", "data": "synthetic",
+            "config": {"workload": wl["label"],
+                       "parallelism": ("sequences sharded across GPUs, no collective" if wl.get("sharded") else
+                                       "replicas only (one independent job per GPU)") if world > 1 else "single GPU",
+                       "l2": "no flush: every decode step streams more weight + KV bytes than the 126 MB L2 holds"},
             "e2e": {"value": e2e_value, "unit": unit,
                     "h2d_bytes_per_step": int(n_seq * n_prompt * 4), "d2h_bytes_per_step": int(n_seq * n_decode * 4),
                     "note": "generate(): prompt upload + prefill + decode + token download, wall clock"},
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
         }
+        line.update(extra)
+        if rank == 0 and not args.no_gemv_table:
+            line["gemv"] = gemv_table(runtime, local_rank, peak)
         if rank == 0 and not args.no_cpu_baseline:
-            r = run_cpu_oracle(wl, tmp, args.cpu_steps, 1)
+            r = run_cpu_oracle(wl, args.cpu_steps, 1)
             line["cpu_baseline"] = {"value": r["value"], "unit": unit, "cores": r["cores"], "kind": "port", "sample": r["sample"]}
         eng.close()
+        if draft is not None:
+            draft.close()
         if rank == 0:
             print(json.dumps(line))
         if world > 1:
+            dist.barrier()
             dist.destroy_process_group()
     finally:
         shutil.rmtree(tmp, ignore_errors=True)

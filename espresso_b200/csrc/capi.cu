@@ -269,6 +269,10 @@ int32_t esp_cuda_generate_two_token(esp_cuda_engine* engine, esp_cuda_engine* dr
 }
 
 int32_t esp_cuda_get_timings(esp_cuda_engine* engine, esp_cuda_timings* out) { ESP_GUARD(engine); return engine->impl.get_timings(out); }
+int32_t esp_cuda_stage_trace(esp_cuda_engine* engine, int32_t cta, int64_t* out, int32_t capacity, int32_t* n) {
+    ESP_GUARD(engine);
+    return engine->impl.stage_trace(cta, reinterpret_cast<long long*>(out), capacity, n);
+}
 int32_t esp_cuda_set_debug_layer(esp_cuda_engine* engine, int32_t layer) { ESP_GUARD(engine); return engine->impl.set_debug_layer(layer); }
 int32_t esp_cuda_debug_dump(esp_cuda_engine* engine, int32_t stage, float* out, int32_t capacity) { ESP_GUARD(engine); return engine->impl.debug_dump(stage, out, capacity); }
 const char* esp_cuda_last_error_string(void) { return esp::last_error_cstr(); }

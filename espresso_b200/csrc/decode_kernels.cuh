@@ -628,7 +628,7 @@ __device__ inline void head_finalize(const GemvArgs& p) {
         unsigned long long key = p.rs.best[r];
         p.rs.best[r] = 0ull;
         if (!p.rs.active[r]) continue;
-        uint32_t tokn = 0xffffffffu - (uint32_t)(key & 0xffffffffull);
+        uint32_t tokn = min(0xffffffffu - (uint32_t)(key & 0xffffffffull), (uint32_t)(m.vocab - 1));  // in range even if every logit was NaN
         p.rs.next[r] = tokn;
         int pos = p.rs.pos[r];
         if (p.finalize_mode & 2) { pos += 1; p.rs.pos[r] = pos; }

@@ -1161,6 +1161,8 @@ int32_t Engine::build_mega() {
     if ((rc = dev_alloc(owned_, &d_norms_, (size_t)(2 * m_.n_layer + 1) * m_.d_model, false))) return rc;
     if ((rc = dev_alloc(owned_, &d_xbuf_, (size_t)3 * m_.d_model))) return rc;
     if ((rc = dev_alloc(owned_, &d_mega_ctl_, 8))) return rc;
+    if ((rc = dev_alloc(owned_, &d_mega_flags_, (size_t)P))) return rc;
+    if ((rc = dev_alloc(owned_, &d_mega_trace_, (size_t)14 * m_.n_layer + 8))) return rc;
     ESP_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&h_mega_ctl_), 8 * sizeof(unsigned long long)));
     // per-layer source pointers
     std::vector<const __half*> ptrs((size_t)7 * m_.n_layer);
@@ -1202,14 +1204,17 @@ int32_t Engine::run_mega(int n_steps, float* device_ms, double* first_token_ms) 
     a.tok_emb = static_cast<const uint16_t*>(tensors_.at("embeddings/token").data);
     a.rope = d_rope_; a.kv = kv_; a.q = act_.q; a.xbuf = d_xbuf_; a.hidden_io = act_.hidden;
     a.best = d_mega_ctl_;
-    a.barrier = reinterpret_cast<unsigned int*>(d_mega_ctl_ + 2);
+    a.barrier = d_mega_flags_;
     a.error = reinterpret_cast<int*>(d_mega_ctl_ + 2) + 1;
     a.stamps = d_mega_ctl_ + 3;
     a.rs = rs_;
+    a.trace = d_mega_trace_;
+    a.trace_cta = mega_trace_cta_;
     a.n_steps = n_steps;
     a.pos0 = h_visible_[0];
     if (!ev_begin_) { ESP_CUDA_TRY(cudaEventCreate(&ev_begin_)); ESP_CUDA_TRY(cudaEventCreate(&ev_end_)); }
     ESP_CUDA_TRY(cudaMemsetAsync(d_mega_ctl_, 0, 8 * sizeof(unsigned long long), stream_));
+    ESP_CUDA_TRY(cudaMemsetAsync(d_mega_flags_, 0, sizeof(unsigned int) * mega_plan_.n_cta, stream_));
     ESP_CUDA_TRY(cudaEventRecord(ev_begin_, stream_));
     void* args[] = {&a};
     ESP_CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(k_decode_mega), dim3(mega_plan_.n_cta), dim3(kMegaThreads), args,
@@ -1228,6 +1233,19 @@ int32_t Engine::run_mega(int n_steps, float* device_ms, double* first_token_ms) 
     if (device_ms) ESP_CUDA_TRY(cudaEventElapsedTime(device_ms, ev_begin_, ev_end_));
     if (first_token_ms) *first_token_ms = (double)(h_mega_ctl_[4] - h_mega_ctl_[3]) / 1e6;
     h_visible_[0] += n_steps - 1;
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::stage_trace(int32_t cta, long long* out, int32_t capacity, int32_t* n) {
+    if (!out || !n) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "stage_trace: null argument");
+    *n = 0;
+    if (!mega_ready_) return ESP_CUDA_OK;
+    const int count = 14 * m_.n_layer + 4;
+    if (capacity < count) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "stage_trace: capacity too small");
+    ESP_CUDA_TRY(cudaSetDevice(cfg_.device));
+    ESP_CUDA_TRY(cudaMemcpy(out, d_mega_trace_, sizeof(long long) * count, cudaMemcpyDeviceToHost));
+    *n = count;
+    mega_trace_cta_ = std::max(0, std::min(cta, mega_plan_.n_cta - 1));  // takes effect with the next decode loop
     return ESP_CUDA_OK;
 }
 

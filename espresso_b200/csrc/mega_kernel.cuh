@@ -23,7 +23,7 @@ namespace esp {
 constexpr int kMegaConsumerWarps = 8;
 constexpr int kMegaConsumers = kMegaConsumerWarps * 32;
 constexpr int kMegaThreads = kMegaConsumers + 32;  // + one producer warp
-constexpr unsigned kMegaSpinLimit = 1u << 22;
+constexpr unsigned kMegaSpinLimit = 1u << 21;  // attempts per wait before the kernel gives up (a few seconds)
 
 struct MegaPlan {
     int n_cta;
@@ -54,6 +54,8 @@ struct MegaArgs {
     unsigned int* barrier;    // [1] monotonic arrival counter, zero at launch
     int* error;               // [1] 0 = ok
     unsigned long long* stamps; // [2] globaltimer at kernel start and when the first token is known
+    long long* trace;         // optional [14*L + 4] SM clock stamps of the last step taken by CTA `trace_cta`, or null
+    int trace_cta;
     RowState rs;              // row 0 carries pos / tok / n_out / out
     int n_steps;              // tokens to emit (>= 1)
     int pos0;                 // visible tokens at launch
@@ -75,10 +77,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
     unsigned ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)  // each attempt may sleep for at most about a microsecond
         : "memory");
     return ok != 0;
 }
@@ -166,6 +168,7 @@ __device__ __forceinline__ void mega_wait(const MegaArgs& a, const MegaShared& s
 }
 
 // Grid-wide barrier of the consumer threads of all CTAs: arrivals are counted on one global counter.
+// (A flag word per CTA polled by one thread each was measured slower on B200: 6 us against 2-3 us.)
 __device__ __forceinline__ void mega_grid_sync(const MegaArgs& a, const MegaShared& s, unsigned& epoch) {
     consumer_sync();
     epoch++;
@@ -295,6 +298,9 @@ __device__ __forceinline__ void mega_s1(const MegaArgs& a, const MegaShared& s, 
 }
 
 // S2: attention of one head over positions [0, pos], then this CTA's block of the output projection.
+// Each warp owns the positions t = warp + 8*i; lane i scores position i of the warp's set, the probabilities
+// are then broadcast lane by lane while every lane accumulates its own channels of V.  The K and V rows are
+// requested before the query is even staged, and the eight per-warp (max, sum, ctx) triples are merged once.
 __device__ __forceinline__ void mega_s2(const MegaArgs& a, const MegaShared& s, int layer, int pos, const uint8_t* chunk, const float* x_in,
                                         const uint16_t* emb_row, float* x_mid) {
     const ModelDims& m = a.m;
@@ -308,86 +314,86 @@ __device__ __forceinline__ void mega_s2(const MegaArgs& a, const MegaShared& s, 
     const int visible = pos + 1;
     const __half* K = a.kv.k + a.kv.offset(m, layer, 0, kvh, 0);
     const __half* V = a.kv.v + a.kv.offset(m, layer, 0, kvh, 0);
-    if (tid < hd) s.qs[tid] = __ldcg(a.q + (size_t)head * hd + tid);
-    // V rows of this warp's positions are requested up front, before the scores are known
-    constexpr int VU = 32;
     const int cpl = hd / 32;  // channels per lane (head_dim 32/64/128 -> 1/2/4)
-    uint2 vreg[VU];
-#pragma unroll
-    for (int u = 0; u < VU; u++) {
-        const int t = warp + u * kMegaConsumerWarps;
-        vreg[u] = make_uint2(0, 0);
-        if (t < visible) {
-            const __half* vr = V + (size_t)t * hd + lane * cpl;
-            if (cpl == 4) vreg[u] = __ldcg(reinterpret_cast<const uint2*>(vr));
-            else if (cpl == 2) vreg[u].x = __ldcg(reinterpret_cast<const unsigned int*>(vr));
-            else vreg[u].x = (unsigned int)__ldcg(reinterpret_cast<const unsigned short*>(vr));
-        }
-    }
-    consumer_sync();
     const float scale = 1.0f / sqrtf((float)hd);
-    float lmax = -INFINITY;
-    for (int t = tid; t < visible; t += kMegaConsumers) {
-        const uint4* kr = reinterpret_cast<const uint4*>(K + (size_t)t * hd);
+    if (tid < hd) s.qs[tid] = __ldcg(a.q + (size_t)head * hd + tid);
+    float m_w = -INFINITY, l_w = 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int base = 0; base < visible; base += kMegaConsumers) {
+        // requests: this lane's K row, and the V rows of the warp's 32 positions (this lane's channels)
+        const int t_mine = base + warp + kMegaConsumerWarps * lane;
         uint4 kreg[16];
+        {
+            const uint4* kr = reinterpret_cast<const uint4*>(K + (size_t)min(t_mine, visible - 1) * hd);
 #pragma unroll
-        for (int c = 0; c < 16; c++) kreg[c] = c < hd / 8 ? __ldcg(kr + c) : make_uint4(0, 0, 0, 0);
-        float dot = 0.f;
+            for (int c = 0; c < 16; c++) kreg[c] = c < hd / 8 ? __ldcg(kr + c) : make_uint4(0, 0, 0, 0);
+        }
+        uint2 vreg[32];
 #pragma unroll
-        for (int c = 0; c < 16; c++) {
-            if (c < hd / 8) {
-                const uint32_t ww[4] = {kreg[c].x, kreg[c].y, kreg[c].z, kreg[c].w};
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[i]));
-                    dot = fmaf(f.x, s.qs[c * 8 + 2 * i], dot);
-                    dot = fmaf(f.y, s.qs[c * 8 + 2 * i + 1], dot);
-                }
+        for (int j = 0; j < 32; j++) {
+            const int t = base + warp + kMegaConsumerWarps * j;
+            vreg[j] = make_uint2(0, 0);
+            if (t < visible) {
+                const __half* vr = V + (size_t)t * hd + lane * cpl;
+                if (cpl == 4) vreg[j] = __ldcg(reinterpret_cast<const uint2*>(vr));
+                else if (cpl == 2) vreg[j].x = __ldcg(reinterpret_cast<const unsigned int*>(vr));
+                else vreg[j].x = (unsigned int)__ldcg(reinterpret_cast<const unsigned short*>(vr));
             }
         }
-        dot *= scale;
-        s.sc[t] = dot;
-        lmax = fmaxf(lmax, dot);
-    }
-    lmax = warp_max(lmax);
-    if (lane == 0) s.red[warp] = lmax;
-    consumer_sync();
-    float mx = s.red[0];
+        if (base == 0) consumer_sync();  // q is staged
+        float sc = -INFINITY;
+        if (t_mine < visible) {
+            float dot = 0.f;
 #pragma unroll
-    for (int i = 1; i < kMegaConsumerWarps; i++) mx = fmaxf(mx, s.red[i]);
-    float lsum = 0.f;
-    for (int t = tid; t < visible; t += kMegaConsumers) {
-        const float e = expf(s.sc[t] - mx);
-        s.sc[t] = e;
-        lsum += e;
-    }
-    const float denom = mega_block_sum(lsum, s.red + 8);  // the barrier inside also publishes sc[]
-    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int c = 0; c < 16; c++) {
+                if (c < hd / 8) {
+                    const uint32_t ww[4] = {kreg[c].x, kreg[c].y, kreg[c].z, kreg[c].w};
 #pragma unroll
-    for (int u = 0; u < VU; u++) {
-        const int t = warp + u * kMegaConsumerWarps;
-        if (t < visible) {
-            const float pt = s.sc[t];
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&vreg[u].x));
-            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&vreg[u].y));
-            acc[0] = fmaf(pt, f0.x, acc[0]);
-            if (cpl >= 2) acc[1] = fmaf(pt, f0.y, acc[1]);
-            if (cpl == 4) { acc[2] = fmaf(pt, f1.x, acc[2]); acc[3] = fmaf(pt, f1.y, acc[3]); }
+                    for (int i = 0; i < 4; i++) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[i]));
+                        dot = fmaf(f.x, s.qs[c * 8 + 2 * i], dot);
+                        dot = fmaf(f.y, s.qs[c * 8 + 2 * i + 1], dot);
+                    }
+                }
+            }
+            sc = dot * scale;
         }
+        const float m_new = fmaxf(m_w, warp_max(sc));
+        const float pr = t_mine < visible ? expf(sc - m_new) : 0.f;
+        const float corr = m_w == -INFINITY ? 0.f : expf(m_w - m_new);
+        l_w = l_w * corr + warp_sum(pr);
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[c] *= corr;
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const float pj = __shfl_sync(0xffffffffu, pr, j);
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&vreg[j].x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&vreg[j].y));
+            acc[0] = fmaf(pj, f0.x, acc[0]);
+            acc[1] = fmaf(pj, f0.y, acc[1]);
+            acc[2] = fmaf(pj, f1.x, acc[2]);
+            acc[3] = fmaf(pj, f1.y, acc[3]);
+        }
+        m_w = m_new;
     }
-    for (int t = warp + VU * kMegaConsumerWarps; t < visible; t += kMegaConsumerWarps) {  // contexts beyond 256 positions
-        const float pt = s.sc[t];
-        const __half* vr = V + (size_t)t * hd + lane * cpl;
-        for (int c = 0; c < cpl; c++) acc[c] = fmaf(pt, __half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(vr + c)))), acc[c]);
-    }
-    for (int c = 0; c < cpl; c++) s.part[warp * hd + lane * cpl + c] = acc[c];
+    // merge the per-warp partial results (a warp that saw no position carries max = -inf, sum = 0)
+#pragma unroll
+    for (int c = 0; c < 4; c++)
+        if (c < cpl) s.part[warp * hd + lane * cpl + c] = acc[c];
+    if (lane == 0) { s.red[warp] = m_w; s.red[8 + warp] = l_w; }
     consumer_sync();
     if (tid < hd) {
-        float t = 0.f;
+        float gm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kMegaConsumerWarps; w++) t += s.part[w * hd + tid];
-        s.ctx[tid] = t * inv;
+        for (int w = 0; w < kMegaConsumerWarps; w++) gm = fmaxf(gm, s.red[w]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < kMegaConsumerWarps; w++) {
+            const float f = s.red[w] == -INFINITY ? 0.f : expf(s.red[w] - gm);
+            num = fmaf(s.part[w * hd + tid], f, num);
+            den = fmaf(s.red[8 + w], f, den);
+        }
+        s.ctx[tid] = den > 0.f ? num / den : 0.f;
     }
     consumer_sync();
     // partial output projection: rows [blk*rpb, ...) of Wo restricted to this head's columns
@@ -467,7 +473,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             unsigned c = 0;
             auto issue = [&](long long off, int bytes) {
                 const unsigned slot = c % (unsigned)p.n_slots;
+                if (*reinterpret_cast<volatile int*>(s.abort)) return;  // once aborting, nothing more is copied
                 if (c >= (unsigned)p.n_slots) mega_wait(a, s, s.empty + slot, ((c / (unsigned)p.n_slots) - 1u) & 1u, 4);
+                if (*reinterpret_cast<volatile int*>(s.abort)) return;
                 mbar_expect_tx(s.full + slot, (unsigned)bytes);
                 bulk_copy_g2s(s.slots + (size_t)slot * p.slot_bytes, blob + off, (unsigned)bytes, s.full + slot);
                 c++;
@@ -500,6 +508,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         a.stamps[0] = t;
     }
+    int n_stamp = 0;
+    auto stamp = [&](int step) {
+        if (a.trace && (int)blockIdx.x == a.trace_cta && tid == 0 && step == a.n_steps - 1) a.trace[n_stamp++] = clock64();
+    };
     unsigned c = 0;      // chunk counter, advances in lock step with the producer's
     unsigned epoch = 0;  // grid barrier epoch
     int pos = a.pos0;    // visible tokens
@@ -515,34 +527,50 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 float* x_out = a.xbuf + (size_t)((2 * l + 2) % 3) * m.d_model;
                 const uint16_t* er = l == 0 ? emb_row : nullptr;
                 // S1
+                stamp(step);
                 mega_stage_norm(a, s, x_in, er, a.norms + (size_t)(2 * l) * m.d_model);
+                stamp(step);
                 if ((int)blockIdx.x == p.n_cta - 1)  // both accumulation targets of this layer start from zero
                     for (int k = tid; k < m.d_model; k += kMegaConsumers) { x_mid[k] = 0.f; x_out[k] = 0.f; }
                 const uint8_t* ch = mega_acquire(a, s, c);
+                stamp(step);
                 mega_s1(a, s, l, pos, ch);
                 mega_release(a, s, c); c++;
+                stamp(step);
                 mega_grid_sync(a, s, epoch);
+                stamp(step);
                 // S2
                 ch = mega_acquire(a, s, c);
+                stamp(step);
                 mega_s2(a, s, l, pos, ch, x_in, er, x_mid);
                 mega_release(a, s, c); c++;
+                stamp(step);
                 mega_grid_sync(a, s, epoch);
+                stamp(step);
                 // S3
                 mega_stage_norm(a, s, x_mid, nullptr, a.norms + (size_t)(2 * l + 1) * m.d_model);
+                stamp(step);
                 ch = mega_acquire(a, s, c);
+                stamp(step);
                 mega_s3_up(a, s, ch);
                 mega_release(a, s, c); c++;
                 consumer_sync();
+                stamp(step);
                 ch = mega_acquire(a, s, c);
+                stamp(step);
                 mega_s3_down(a, s, ch, x_mid, x_out);
                 mega_release(a, s, c); c++;
+                stamp(step);
                 mega_grid_sync(a, s, epoch);
+                stamp(step);
                 x_final = x_out;
             }
             pos++;  // the token that was just processed is now visible
         }
         // LM head over this CTA's vocab rows, first-max argmax
+        stamp(step);
         mega_stage_norm(a, s, x_final, nullptr, fin_gain);
+        stamp(step);
         float best_v = -INFINITY;
         int best_i = 0x7fffffff;
         for (int hc = 0; hc < p.head_chunks; hc++) {
@@ -560,9 +588,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             mega_release(a, s, c); c++;
         }
         if (lane == 0 && best_i != 0x7fffffff) atomicMax(a.best + (step & 1), pack_best(best_v, best_i));
+        stamp(step);
         mega_grid_sync(a, s, epoch);
+        stamp(step);
         const unsigned long long key = __ldcg(a.best + (step & 1));
-        tok = 0xffffffffu - (uint32_t)(key & 0xffffffffull);
+        tok = min(0xffffffffu - (uint32_t)(key & 0xffffffffull), (uint32_t)(m.vocab - 1));  // in range even if every logit was NaN
         if (blockIdx.x == 0 && tid == 0) {
             if (step == 0) {
                 unsigned long long t;

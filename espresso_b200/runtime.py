@@ -93,6 +93,7 @@ SIGNATURES = {
     "esp_cuda_generate_batch": (C.c_int32, [_vp, _u32p, C.c_int32, C.c_int32, C.c_int32, _u32p, _i32p, C.POINTER(EspCudaGenerationResult)]),
     "esp_cuda_generate_two_token": (C.c_int32, [_vp, _vp, _u32p, C.c_int32, C.c_int32, _u32p, _i32p, C.POINTER(EspCudaGenerationResult)]),
     "esp_cuda_get_timings": (C.c_int32, [_vp, C.POINTER(EspCudaTimings)]),
+    "esp_cuda_stage_trace": (C.c_int32, [_vp, C.c_int32, C.POINTER(C.c_int64), C.c_int32, _i32p]),
     "esp_cuda_set_debug_layer": (C.c_int32, [_vp, C.c_int32]),
     "esp_cuda_debug_dump": (C.c_int32, [_vp, C.c_int32, _f32p, C.c_int32]),
     "esp_cuda_last_error_string": (C.c_char_p, []),
@@ -320,6 +321,13 @@ class DecodeEngine:
         t = EspCudaTimings()
         _check(self._lib.esp_cuda_get_timings(self._h, C.byref(t)))
         return {k: getattr(t, k) for k, _ in EspCudaTimings._fields_}
+
+    def stage_trace(self, next_cta: int = 0) -> np.ndarray:
+        """SM clock stamps of the persistent kernel's last token (see ``esp_cuda_stage_trace``)."""
+        out = np.zeros(14 * self.config.nLayer + 8, np.int64)
+        n = C.c_int32()
+        _check(self._lib.esp_cuda_stage_trace(self._h, next_cta, out.ctypes.data_as(C.POINTER(C.c_int64)), out.size, C.byref(n)))
+        return out[: n.value].copy()
 
     def set_debug_layer(self, layer: int) -> None:
         _check(self._lib.esp_cuda_set_debug_layer(self._h, layer))

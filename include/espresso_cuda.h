@@ -194,6 +194,13 @@ ESP_CUDA_API int32_t esp_cuda_get_timings(esp_cuda_engine* engine, esp_cuda_timi
  * stored), 2 v (as stored), 3 attention context, 4 hidden after attention, 5 FFN activation, 6 layer
  * output.  Stages 0..5 are captured for `layer` only when esp_cuda_set_debug_layer(engine, layer) was called
  * before the step. */
+/* SM clock stamps taken by one CTA of the persistent decode kernel during the last token of the most recent
+ * decode loop (the fine-grained counterpart of the per-layer DecodeKernelProfile, DecodeForwardPass.swift:212-320).
+ * Per layer 14 stamps: S1 begin, norm done, weights arrived, rows done, barrier passed; S2 weights arrived, done,
+ * barrier passed; S3 norm done, weights arrived, gate/up done, weights arrived, down done, barrier passed; then
+ * 4 for the head: begin, norm done, rows done, barrier passed.  *n = 0 when the model does not use that kernel.
+ * `cta` selects which CTA records the NEXT loop. */
+ESP_CUDA_API int32_t esp_cuda_stage_trace(esp_cuda_engine* engine, int32_t cta, int64_t* out, int32_t capacity, int32_t* n);
 ESP_CUDA_API int32_t esp_cuda_set_debug_layer(esp_cuda_engine* engine, int32_t layer);
 ESP_CUDA_API int32_t esp_cuda_debug_dump(esp_cuda_engine* engine, int32_t stage, float* out, int32_t capacity);
 ESP_CUDA_API const char* esp_cuda_last_error_string(void);
