@@ -165,10 +165,10 @@ __device__ __forceinline__ int xs_index(int k) {
 template <int EPL>
 __host__ __device__ inline int xs_floats(int K) { return ((K + 32 * EPL - 1) / (32 * EPL)) * (32 * EPL); }
 
-// Accumulates the products of one 16-byte weight vector (EPL elements starting at element k of its row) with
-// the matching EPL activations.
+// Accumulates the products of one 16-byte vector of fp16/bf16 weights (8 elements) with 8 fp32 activations.
 template <int WT>
 __device__ __forceinline__ void fma_vec16(const uint4& w, const __half* srow, int k, const float* x, float sx, float& acc) {
+    (void)srow; (void)k; (void)sx;
     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
     if constexpr (WT == WT_F16) {
 #pragma unroll
@@ -177,50 +177,81 @@ __device__ __forceinline__ void fma_vec16(const uint4& w, const __half* srow, in
             acc = fmaf(f.x, x[2 * i], acc);
             acc = fmaf(f.y, x[2 * i + 1], acc);
         }
-    } else if constexpr (WT == WT_BF16) {
+    } else {
+        static_assert(WT == WT_BF16, "fp32-activation path is for fp16/bf16 weights");
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             acc = fmaf(__uint_as_float(ww[i] << 16), x[2 * i], acc);
             acc = fmaf(__uint_as_float(ww[i] & 0xffff0000u), x[2 * i + 1], acc);
         }
-    } else if constexpr (WT == WT_Q8_0) {
-        const float d = __half2float(srow[k >> 5]);
-        float s = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-#pragma unroll
-            for (int b = 0; b < 4; b++) {
-                int qv = (int)(int8_t)((ww[i] >> (8 * b)) & 0xffu);
-                s = fmaf((float)qv, x[4 * i + b], s);
-            }
-        }
-        acc = fmaf(d, s, acc);
-    } else {  // Q4_0: byte j of the group holds element j (low nibble) and element j+16 (high nibble)
-        const float d = __half2float(srow[k >> 5]);
-        float s = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-#pragma unroll
-            for (int b = 0; b < 4; b++) {
-                uint32_t byte = (ww[i] >> (8 * b)) & 0xffu;
-                s = fmaf((float)(byte & 15u), x[4 * i + b], s);
-                s = fmaf((float)(byte >> 4), x[16 + 4 * i + b], s);
-            }
-        }
-        acc = fmaf(d, s - 8.0f * sx, acc);
     }
 }
 
+// --- GGUF block arithmetic on packed halves -------------------------------------------------------------
+// Quantised weights are widened to fp16 exactly (an int8 or a nibble is an integer of at most 8 bits) with
+// byte-permute / logic tricks instead of integer->float conversions, multiplied with activations that were
+// staged as fp16 (scaled by a power of two so that |x| < 1, see stage_vector) and summed per 32-element block in
+// packed fp16; each block sum is then widened and multiplied by the block scale in fp32.  The dequantised
+// weight values themselves stay exactly fp32(d) * q.
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));  // (a & b) | c
+    return d;
+}
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+
+// 16 bytes = 16 int8 of one Q8_0 block half; xh = the matching 16 staged activations (two 16-byte groups).
+__device__ __forceinline__ float q8_block_dot(const uint4& w, const uint4& xa, const uint4& xb) {
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    const uint32_t xx[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);  // 1024 + 128
+    __half2 acc0 = __floats2half2_rn(0.f, 0.f), acc1 = acc0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t u = ww[i] ^ 0x80808080u;                       // int8 -> offset-128 unsigned
+        const uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140);      // halves 0x64b0, 0x64b1 = 1024 + b
+        const uint32_t hi = __byte_perm(u, 0x64646464u, 0x4342);
+        acc0 = __hfma2(__hsub2(u32_as_h2(lo), bias), u32_as_h2(xx[2 * i]), acc0);
+        acc1 = __hfma2(__hsub2(u32_as_h2(hi), bias), u32_as_h2(xx[2 * i + 1]), acc1);
+    }
+    const float2 f = __half22float2(__hadd2(acc0, acc1));
+    return f.x + f.y;
+}
+
+// 16 bytes = one Q4_0 block (byte j: low nibble = element j, high nibble = element j+16); x0..x3 = the staged
+// activations of words 0..3 in the order {e, e+2}, {16+e, 16+e+2}, {e+1, e+3}, {16+e+1, 16+e+3} (e = 4*word).
+__device__ __forceinline__ float q4_block_dot(const uint4& w, const uint4& x0, const uint4& x1, const uint4& x2, const uint4& x3) {
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    const uint4 xs4[4] = {x0, x1, x2, x3};
+    const __half2 bias = __floats2half2_rn(1032.f, 1032.f);  // 1024 + 8
+    __half2 acc0 = __floats2half2_rn(0.f, 0.f), acc1 = acc0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t v = ww[i];
+        const uint32_t n0 = lop3_and_or(v, 0x000F000Fu, 0x64006400u);
+        const uint32_t n1 = lop3_and_or(v >> 4, 0x000F000Fu, 0x64006400u);
+        const uint32_t n2 = lop3_and_or(v >> 8, 0x000F000Fu, 0x64006400u);
+        const uint32_t n3 = lop3_and_or(v >> 12, 0x000F000Fu, 0x64006400u);
+        acc0 = __hfma2(__hsub2(u32_as_h2(n0), bias), u32_as_h2(xs4[i].x), acc0);
+        acc1 = __hfma2(__hsub2(u32_as_h2(n1), bias), u32_as_h2(xs4[i].y), acc1);
+        acc0 = __hfma2(__hsub2(u32_as_h2(n2), bias), u32_as_h2(xs4[i].z), acc0);
+        acc1 = __hfma2(__hsub2(u32_as_h2(n3), bias), u32_as_h2(xs4[i].w), acc1);
+    }
+    const float2 f = __half22float2(__hadd2(acc0, acc1));
+    return f.x + f.y;
+}
+
 // Dot products of NR weight rows with the staged vector.  Each lane accumulates its slices; the caller
-// reduces across the warp.  K must be a multiple of EPL.  The loads of U consecutive 16-byte slices of all NR
-// rows are issued before any arithmetic so that each lane keeps U*NR*16 bytes in flight.
+// reduces across the warp (and, for the quantised types, multiplies by the activation de-scale factor).
+// K must be a multiple of EPL.  The loads of U consecutive 16-byte slices of all NR rows are issued before
+// any arithmetic so that each lane keeps U*NR*16 bytes in flight.
 template <int WT, int NR>
 __device__ __forceinline__ void dot_rows(const uint8_t* const (&wrow)[NR], const __half* const (&srow)[NR], int K,
                                          const float* __restrict__ xs, int lane, float (&acc)[NR]) {
     constexpr int EPL = WTraits<WT>::EPL;
-    constexpr int NJ = EPL / 4;
-    constexpr int U = (WT == WT_F16 || WT == WT_BF16) ? 4 : 2;
+    constexpr int U = 4;
     const float4* xs4 = reinterpret_cast<const float4*>(xs);
+    const uint4* xh4 = reinterpret_cast<const uint4*>(xs);  // quantised types: fp16 activations, 8 per 16-byte group
     const int iters = (K + 32 * EPL - 1) / (32 * EPL);
     for (int it0 = 0; it0 < iters; it0 += U) {
         uint4 w[U][NR];
@@ -236,19 +267,21 @@ __device__ __forceinline__ void dot_rows(const uint8_t* const (&wrow)[NR], const
             const int it = it0 + u;
             const int k = it * 32 * EPL + lane * EPL;
             if (k < K) {
-                float x[EPL];
+                if constexpr (WT == WT_F16 || WT == WT_BF16) {
+                    const float4 va = xs4[(it * 2) * 32 + lane], vb = xs4[(it * 2 + 1) * 32 + lane];
+                    const float x[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
 #pragma unroll
-                for (int j = 0; j < NJ; j++) {
-                    float4 v = xs4[(it * NJ + j) * 32 + lane];
-                    x[4 * j] = v.x; x[4 * j + 1] = v.y; x[4 * j + 2] = v.z; x[4 * j + 3] = v.w;
+                    for (int r = 0; r < NR; r++) fma_vec16<WT>(w[u][r], nullptr, 0, x, 0.f, acc[r]);
+                } else if constexpr (WT == WT_Q8_0) {
+                    const uint4 xa = xh4[(it * 2) * 32 + lane], xb = xh4[(it * 2 + 1) * 32 + lane];
+#pragma unroll
+                    for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(srow[r][k >> 5]), q8_block_dot(w[u][r], xa, xb), acc[r]);
+                } else {
+                    const uint4 x0 = xh4[(it * 4) * 32 + lane], x1 = xh4[(it * 4 + 1) * 32 + lane];
+                    const uint4 x2 = xh4[(it * 4 + 2) * 32 + lane], x3 = xh4[(it * 4 + 3) * 32 + lane];
+#pragma unroll
+                    for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(srow[r][k >> 5]), q4_block_dot(w[u][r], x0, x1, x2, x3), acc[r]);
                 }
-                float sx = 0.f;
-                if constexpr (WT == WT_Q4_0) {
-#pragma unroll
-                    for (int i = 0; i < EPL; i++) sx += x[i];
-                }
-#pragma unroll
-                for (int r = 0; r < NR; r++) fma_vec16<WT>(w[u][r], srow[r], k, x, sx, acc[r]);
             }
         }
     }
@@ -263,11 +296,46 @@ __device__ __forceinline__ const __half* scale_row(const Weight& w, int row) {
 
 enum NormKind { NORM_NONE = 0, NORM_RMS = 1, NORM_LAYER = 2 };
 
-// Stages `src` (K floats) into shared memory in the lane-major order, optionally normalised:
+// Position (in halves) of element k of the fp16-staged vector used by the quantised types: the lane that owns
+// the 16-byte weight vector holding k reads its activations as consecutive 16-byte groups, and inside a Q4_0
+// group the order follows the nibble extraction of q4_block_dot.
+template <int WT>
+__device__ __forceinline__ int xh_index(int k) {
+    constexpr int EPL = WTraits<WT>::EPL;
+    const int it = k / (32 * EPL);
+    const int rem = k - it * (32 * EPL);
+    const int lane = rem / EPL;
+    const int e = rem - lane * EPL;
+    if constexpr (WT == WT_Q8_0) {
+        return ((it * 2 + (e >> 3)) * 32 + lane) * 8 + (e & 7);
+    } else {
+        const int byte = e & 15, word = byte >> 2, r = byte & 3;
+        const int slot = ((r & 1) ? 4 : 0) + ((r & 2) ? 1 : 0) + ((e & 16) ? 2 : 0);
+        return ((it * 4 + word) * 32 + lane) * 8 + slot;
+    }
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+    v = warp_max(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = red[0];
+#pragma unroll
+    for (int i = 1; i < kWarps; i++) t = fmaxf(t, red[i]);
+    return t;
+}
+
+// Stages `src` (K floats) into shared memory, optionally normalised:
 //   RMSNorm   y = x * rsqrt(mean(x^2) + eps) * g          LayerNorm  y = (x-mean) * rsqrt(var + eps) * g + b
-template <int EPL>
-__device__ __forceinline__ void stage_vector(const float* __restrict__ src, int K, int norm, const float* g,
-                                             const float* b, float eps, float* xs, float* red) {
+// fp16/bf16 weights: fp32 values in the lane-major order of xs_index; returns 1.
+// Q8_0/Q4_0 weights: fp16 values scaled by a power of two 2^-e (so that |y| < 1) in the order of xh_index;
+// returns 2^e, the factor that undoes the scaling after the dot product.
+template <int WT>
+__device__ __forceinline__ float stage_vector(const float* __restrict__ src, int K, int norm, const float* g,
+                                              const float* b, float eps, float* xs, float* red) {
+    constexpr int EPL = WTraits<WT>::EPL;
+    constexpr bool kHalf = WT == WT_Q8_0 || WT == WT_Q4_0;
     float inv = 1.f, mean = 0.f;
     if (norm == NORM_RMS) {
         float ss = 0.f;
@@ -283,13 +351,28 @@ __device__ __forceinline__ void stage_vector(const float* __restrict__ src, int 
         vs = block_sum(vs, red);
         inv = 1.0f / sqrtf(vs / (float)K + eps);
     }
-    for (int k = threadIdx.x; k < K; k += kThreads) {
+    auto value = [&](int k) {
         float v = src[k];
         if (norm == NORM_RMS) v = (v * inv) * g[k];
         else if (norm == NORM_LAYER) v = (v - mean) * inv * g[k] + b[k];
-        xs[xs_index<EPL>(k)] = v;
+        return v;
+    };
+    float descale = 1.f;
+    if constexpr (kHalf) {
+        float amax = 0.f;
+        for (int k = threadIdx.x; k < K; k += kThreads) amax = fmaxf(amax, fabsf(value(k)));
+        amax = block_max(amax, red);
+        int e = 0;
+        if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &e);  // amax = m * 2^e with m in [0.5, 1)
+        const float scale = ldexpf(1.0f, -e);
+        descale = ldexpf(1.0f, e);
+        __half* xh = reinterpret_cast<__half*>(xs);
+        for (int k = threadIdx.x; k < K; k += kThreads) xh[xh_index<WT>(k)] = __float2half_rn(value(k) * scale);
+    } else {
+        for (int k = threadIdx.x; k < K; k += kThreads) xs[xs_index<EPL>(k)] = value(k);
     }
     __syncthreads();
+    return descale;
 }
 
 // Range of work items [begin, end) owned by CTA `cta` of `n_cta` (contiguous chunks, so that a CTA's weight
@@ -336,6 +419,7 @@ __device__ void stage_qkv(const QkvArgs& p, int cta, int n_cta, float* xs, float
         if (!p.rs.active[r]) continue;
         const int pos = p.rs.pos[r];
         float* hid = p.a.hidden + (size_t)r * m.d_model;
+        float xdescale = 1.f;
         if (p.from_embedding) {
             // hidden = tokenEmbedding[token] (+ positionEmbedding[pos]); every CTA needs it, CTA 0 stores it.
             const uint16_t* te = p.tok_emb + (size_t)p.rs.tok[r] * m.d_model;
@@ -348,9 +432,9 @@ __device__ void stage_qkv(const QkvArgs& p, int cta, int n_cta, float* xs, float
                 if (cta == 0) hid[k] = v;
             }
             __syncthreads();
-            stage_vector<EPL>(tmp, m.d_model, gpt2 ? NORM_LAYER : NORM_RMS, p.lw.norm1_g, p.lw.norm1_b, m.eps, xs, red);
+            xdescale = stage_vector<WT>(tmp, m.d_model, gpt2 ? NORM_LAYER : NORM_RMS, p.lw.norm1_g, p.lw.norm1_b, m.eps, xs, red);
         } else {
-            stage_vector<EPL>(hid, m.d_model, gpt2 ? NORM_LAYER : NORM_RMS, p.lw.norm1_g, p.lw.norm1_b, m.eps, xs, red);
+            xdescale = stage_vector<WT>(hid, m.d_model, gpt2 ? NORM_LAYER : NORM_RMS, p.lw.norm1_g, p.lw.norm1_b, m.eps, xs, red);
         }
         const int seq = p.rs.seq[r];
         // each warp takes two adjacent work items (four weight rows) per iteration
@@ -378,7 +462,7 @@ __device__ void stage_qkv(const QkvArgs& p, int cta, int n_cta, float* xs, float
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             dot_rows<WT, 4>(wr, sr, m.d_model, xs, lane, acc);
 #pragma unroll
-            for (int j = 0; j < 4; j++) acc[j] = warp_sum(acc[j]);
+            for (int j = 0; j < 4; j++) acc[j] = warp_sum(acc[j]) * xdescale;
             if (lane < 2 && item0 + lane < end) {
                 const int j = lane;
                 const int kind = kinds[j], row0 = rows4[2 * j], row1 = rows4[2 * j + 1];
@@ -659,7 +743,7 @@ __device__ void stage_gemv(const GemvArgs& p, int cta, int n_cta, float* xs, flo
     cta_range(n_items, cta, n_cta, begin, end);
     for (int r = 0; r < p.rows; r++) {
         if (!p.rs.active[r]) continue;
-        stage_vector<EPL>(p.in + (size_t)r * p.in_stride, K, p.norm, p.norm_g, p.norm_b, m.eps, xs, red);
+        const float xdescale = stage_vector<WT>(p.in + (size_t)r * p.in_stride, K, p.norm, p.norm_g, p.norm_b, m.eps, xs, red);
         float best_v = -INFINITY;
         int best_i = 0x7fffffff;
         // each warp takes two adjacent work items (four weight rows) per iteration
@@ -681,7 +765,7 @@ __device__ void stage_gemv(const GemvArgs& p, int cta, int n_cta, float* xs, flo
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             dot_rows<WT, 4>(wr, sr, K, xs, lane, acc);
 #pragma unroll
-            for (int j = 0; j < 4; j++) acc[j] = warp_sum(acc[j]);
+            for (int j = 0; j < 4; j++) acc[j] = warp_sum(acc[j]) * xdescale;
 #pragma unroll
             for (int j = 0; j < 2; j++) {
                 const int item = item0 + j;

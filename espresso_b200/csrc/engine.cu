@@ -1284,7 +1284,7 @@ __global__ void __launch_bounds__(kThreads) k_gemv_plain(Weight w, const float* 
     extern __shared__ float smem[];
     constexpr int EPL = WTraits<WT>::EPL;
     float* xs = smem + 8;
-    stage_vector<EPL>(x, w.cols, NORM_NONE, nullptr, nullptr, 0.f, xs, smem);
+    const float xdescale = stage_vector<WT>(x, w.cols, NORM_NONE, nullptr, nullptr, 0.f, xs, smem);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int n_items = (w.rows + 1) / 2;
     int begin, end;
@@ -1295,7 +1295,7 @@ __global__ void __launch_bounds__(kThreads) k_gemv_plain(Weight w, const float* 
         const __half* sr[2] = {scale_row(w, row0), scale_row(w, row1)};
         float acc[2] = {0.f, 0.f};
         dot_rows<WT, 2>(wr, sr, w.cols, xs, lane, acc);
-        float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
+        float v0 = warp_sum(acc[0]) * xdescale, v1 = warp_sum(acc[1]) * xdescale;
         if (lane == 0) { y[row0] = v0; if (row1 != row0) y[row1] = v1; }
     }
 }

@@ -56,7 +56,13 @@ def test_gemv_kernel_matches_oracle(rt, oracle_lib, kind, shape):
         ref_w = oracle_lib.dequantize(kind, stored, w.size).reshape(rows, cols)
     y, ms = rt.gemv_bench(kind, stored, rows, cols, x, warmup=1, iterations=2)
     ref = oracle_lib.gemv(ref_w, x)
-    np.testing.assert_allclose(y, ref, atol=2e-4, rtol=1e-4)
+    if kind in ("f16", "bf16"):
+        np.testing.assert_allclose(y, ref, atol=2e-4, rtol=1e-4)  # fp32 activations and accumulation
+    else:
+        # quantised types multiply in packed fp16 (activations rounded to fp16, per-block fp16 partial sums);
+        # the weights themselves are exact, so the error is pure rounding noise relative to the result's scale
+        assert np.abs(y - ref).max() <= 4e-3 * np.abs(ref).max()
+        assert np.linalg.norm(y - ref) <= 2e-3 * np.linalg.norm(ref)
     assert ms > 0
 
 
