@@ -2,3 +2,4 @@
 // functions, so the engine and the C ABI are compiled together.
 #include "engine.cu"
 #include "capi.cu"
+#include "static_head.cu"

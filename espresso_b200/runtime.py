@@ -101,6 +101,7 @@ SIGNATURES = {
     "esp_cuda_live_engine_count": (C.c_int32, []),
     "esp_cuda_version": (C.c_char_p, []),
     "esp_cuda_dequantize": (C.c_int32, [C.c_int32, _vp, C.c_int64, _f32p, C.c_int32]),
+    "esp_cuda_lm_head_argmax_static": (C.c_int32, [_vp, C.c_int32, C.c_int32, _vp, C.c_int32, _vp, C.c_float, _vp, _vp, C.c_int32]),
     "esp_cuda_gemv_bench": (C.c_int32, [C.c_int32, _vp, C.c_int32, C.c_int32, _f32p, _f32p, C.c_int32, C.c_int32, C.c_int32, _f32p, C.c_int32]),
 }
 
@@ -354,6 +355,17 @@ def dequantize(kind: str, blocks: np.ndarray, n_elements: int, device: int = 0) 
     _check(load_library().esp_cuda_dequantize(TENSOR_TYPES[kind], C.c_void_p(blocks.ctypes.data), n_elements,
                                               out.ctypes.data_as(_f32p), device))
     return out
+
+
+STATIC_HEAD_MAX_ROWS = 64
+
+
+def lm_head_argmax_static(lm_head_ptr: int, vocab: int, d_model: int, hidden_ptr: int, rows: int, gain_ptr: Optional[int],
+                          eps: float, tokens_ptr: int, stream: int = 0, device: int = 0) -> None:
+    """Allocation-free final norm + LM head + argmax; every ``*_ptr`` is a device address owned by the caller."""
+    _check(load_library().esp_cuda_lm_head_argmax_static(
+        C.c_void_p(lm_head_ptr), vocab, d_model, C.c_void_p(hidden_ptr), rows, C.c_void_p(gain_ptr) if gain_ptr else None,
+        eps, C.c_void_p(tokens_ptr), C.c_void_p(stream) if stream else None, device))
 
 
 def gemv_bench(kind: str, weights: np.ndarray, rows: int, cols: int, x: np.ndarray, warmup: int = 3, iterations: int = 20,

@@ -220,6 +220,27 @@ ESP_CUDA_API int32_t esp_cuda_gemv_bench(int32_t type, const void* weights, int3
                                          float* y, int32_t warmup, int32_t iterations, int32_t copies, float* avg_ms,
                                          int32_t device);
 
+/* ---- an entry point that allocates nothing --------------------------------------------------------- */
+
+/* No counterpart in the reference.  Final RMSNorm (skipped when d_norm_gain is NULL) + fp16 LM head +
+ * first-max greedy argmax for `rows` hidden vectors, for hosts that may not call the CUDA allocator while they
+ * run: processes whose device-memory budget was fixed up front, plugins living in another framework's arena,
+ * and latency-critical loops in which a cudaMalloc/cudaFree would stall the whole device.  Every pointer is a
+ * DEVICE pointer owned by the caller: d_lm_head_f16 [vocab][d_model] fp16 row-major, d_hidden [rows][d_model]
+ * fp32, d_norm_gain [d_model] fp32 or NULL, d_tokens [rows] uint32 (output).  The kernel's own working memory
+ * (packed running maxima, completion counter, per-row control words) is a 4 KiB array compiled into the library,
+ * which every GPU that loads the library holds until exit.  Limits: rows <= ESP_CUDA_STATIC_HEAD_MAX_ROWS,
+ * d_model a multiple of 8 and <= 8192; anything larger is refused with ESP_CUDA_ERR_INVALID_ARGUMENT.  The work
+ * is enqueued on `cuda_stream` (a cudaStream_t, NULL = default stream) and is complete when that stream reaches
+ * this point.  All calls on a device share the array and it keeps the previous call's contents: the call resets
+ * what it needs, and calls whose kernels overlap on the GPU race - serialise them.  The first call on a device
+ * looks up the array's address and should be made before any stream capture begins.  The call itself performs
+ * no cudaMalloc, cudaFree or other allocating routine. */
+#define ESP_CUDA_STATIC_HEAD_MAX_ROWS 64
+ESP_CUDA_API int32_t esp_cuda_lm_head_argmax_static(const void* d_lm_head_f16, int32_t vocab, int32_t d_model,
+                                                    const float* d_hidden, int32_t rows, const float* d_norm_gain,
+                                                    float norm_eps, uint32_t* d_tokens, void* cuda_stream, int32_t device);
+
 #ifdef __cplusplus
 }
 #endif
