@@ -405,7 +405,10 @@ def main() -> None:
             launch_s = statistics.mean(step_ms) / 1e3
             roofline = {"bound": "hbm", "kernel": "k_decode_mega (whole greedy loop: all layers + LM head, one launch per step)",
                         "achieved": launch_bytes / launch_s / 1e9, "peak": peak, "unit": "GB/s",
-                        "frac": launch_bytes / launch_s / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
+                        "frac": launch_bytes / launch_s / 1e9 / peak,
+                        # DRAM bytes of one launch: ncu measured 1.018 x the algorithmic bytes on a 4-token launch
+                        # (profiles/k_decode_mega_c1.md); traffic grows in proportion to the tokens of a launch
+                        "traffic": 1.018 * launch_bytes, "peak_kind": peak_kind,
                         "bytes_per_launch": launch_bytes, "bytes_per_token": bytes_tok}
         else:
             head_ms = []

@@ -116,11 +116,19 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return t;
 }
 
+// Weights are streamed once per token and would otherwise push the KV cache, the activations and the small
+// per-layer vectors out of L2: they are read with an evict-first L2 policy and without L1 allocation.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
 __device__ __forceinline__ uint4 ld_weight16(const void* p) {
     uint4 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+    const uint64_t pol = l2_evict_first_policy();
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
                  : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(p));
+                 : "l"(p), "l"(pol));
     return r;
 }
 
@@ -132,7 +140,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // Ask L2 to fetch a contiguous byte range (16-byte aligned start, size multiple of 16).
 __device__ __forceinline__ void l2_prefetch(const void* p, unsigned bytes) {
     if (bytes)
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(p), "r"(bytes), "l"(l2_evict_first_policy()) : "memory");
 }
 
 __device__ __forceinline__ float emb_to_float(uint16_t bits, int type) {
@@ -220,26 +228,29 @@ __device__ __forceinline__ float q8_block_dot(const uint4& w, const uint4& xa, c
 
 // 16 bytes = one Q4_0 block (byte j: low nibble = element j, high nibble = element j+16); x0..x3 = the staged
 // activations of words 0..3 in the order {e, e+2}, {16+e, 16+e+2}, {e+1, e+3}, {16+e+1, 16+e+3} (e = 4*word).
+// A masked nibble is used directly as the bit pattern of an fp16 subnormal: bits 0-3 read as n * 2^-24 and bits
+// 4-7 as 16n * 2^-24, both exact, so no conversion instruction is needed at all.  The activations are staged with
+// an extra factor 2^14 (see stage_vector) so that the products stay in the normal fp16 range, the "- 8" of the
+// format is applied once per block through the block's activation sum, and the remaining powers of two are
+// folded into the final de-scale factor.  Returns sum(n * 2^-24 * x'') over the 32 elements.
 __device__ __forceinline__ float q4_block_dot(const uint4& w, const uint4& x0, const uint4& x1, const uint4& x2, const uint4& x3) {
     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
     const uint4 xs4[4] = {x0, x1, x2, x3};
-    const __half2 bias = __floats2half2_rn(1032.f, 1032.f);  // 1024 + 8
-    __half2 acc0 = __floats2half2_rn(0.f, 0.f), acc1 = acc0;
+    __half2 acc_a = __floats2half2_rn(0.f, 0.f), acc_b = acc_a;  // acc_b carries the nibbles read at bit 4 (x16)
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const uint32_t v = ww[i];
-        const uint32_t n0 = lop3_and_or(v, 0x000F000Fu, 0x64006400u);
-        const uint32_t n1 = lop3_and_or(v >> 4, 0x000F000Fu, 0x64006400u);
-        const uint32_t n2 = lop3_and_or(v >> 8, 0x000F000Fu, 0x64006400u);
-        const uint32_t n3 = lop3_and_or(v >> 12, 0x000F000Fu, 0x64006400u);
-        acc0 = __hfma2(__hsub2(u32_as_h2(n0), bias), u32_as_h2(xs4[i].x), acc0);
-        acc1 = __hfma2(__hsub2(u32_as_h2(n1), bias), u32_as_h2(xs4[i].y), acc1);
-        acc0 = __hfma2(__hsub2(u32_as_h2(n2), bias), u32_as_h2(xs4[i].z), acc0);
-        acc1 = __hfma2(__hsub2(u32_as_h2(n3), bias), u32_as_h2(xs4[i].w), acc1);
+        const uint32_t v = ww[i], t = v >> 8;
+        acc_a = __hfma2(u32_as_h2(v & 0x000F000Fu), u32_as_h2(xs4[i].x), acc_a);
+        acc_b = __hfma2(u32_as_h2(v & 0x00F000F0u), u32_as_h2(xs4[i].y), acc_b);
+        acc_a = __hfma2(u32_as_h2(t & 0x000F000Fu), u32_as_h2(xs4[i].z), acc_a);
+        acc_b = __hfma2(u32_as_h2(t & 0x00F000F0u), u32_as_h2(xs4[i].w), acc_b);
     }
-    const float2 f = __half22float2(__hadd2(acc0, acc1));
-    return f.x + f.y;
+    const float2 fa = __half22float2(acc_a), fb = __half22float2(acc_b);
+    return (fa.x + fa.y) + (fb.x + fb.y) * 0.0625f;
 }
+
+// Per-block activation sums of the Q4_0 staging (pre-multiplied by 2^-21) live behind the staged halves.
+__device__ __forceinline__ const float* q4_block_sums(const float* xs, int K) { return xs + xs_floats<32>(K) / 2; }
 
 // Dot products of NR weight rows with the staged vector.  Each lane accumulates its slices; the caller
 // reduces across the warp (and, for the quantised types, multiplies by the activation de-scale factor).
@@ -280,10 +291,83 @@ __device__ __forceinline__ void dot_rows(const uint8_t* const (&wrow)[NR], const
                     const uint4 x0 = xh4[(it * 4) * 32 + lane], x1 = xh4[(it * 4 + 1) * 32 + lane];
                     const uint4 x2 = xh4[(it * 4 + 2) * 32 + lane], x3 = xh4[(it * 4 + 3) * 32 + lane];
 #pragma unroll
-                    for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(srow[r][k >> 5]), q4_block_dot(w[u][r], x0, x1, x2, x3), acc[r]);
+                    const float bs = q4_block_sums(xs, K)[k >> 5];
+#pragma unroll
+                    for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(srow[r][k >> 5]), q4_block_dot(w[u][r], x0, x1, x2, x3) - bs, acc[r]);
                 }
             }
         }
+    }
+}
+
+// --- software-pipelined variant ----------------------------------------------------------------------------
+// A "batch" is two consecutive 16-byte slices of NR rows.  While one batch is being multiplied the next one (of
+// the same rows, or the first batch of the rows the warp handles next) is already in flight, so a warp never
+// waits with an empty memory queue between work items.  Weights are constants, which lets the very first batch
+// be requested before the activation vector is staged, and even before the previous kernel has finished.
+template <int WT, int NR>
+struct WBatch {
+    uint4 v[2][NR];
+};
+
+template <int WT, int NR>
+__device__ __forceinline__ void load_batch(WBatch<WT, NR>& b, const uint8_t* const (&wrow)[NR], int K, int it0, int lane) {
+    constexpr int EPL = WTraits<WT>::EPL;
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+        const int k = (it0 + u) * 32 * EPL + lane * EPL;
+        const size_t byte_off = WT == WT_Q8_0 ? (size_t)k : WT == WT_Q4_0 ? (size_t)k / 2 : (size_t)k * 2;
+#pragma unroll
+        for (int r = 0; r < NR; r++) b.v[u][r] = k < K ? ld_weight16(wrow[r] + byte_off) : make_uint4(0, 0, 0, 0);
+    }
+}
+
+template <int WT, int NR>
+__device__ __forceinline__ void compute_batch(const WBatch<WT, NR>& b, const __half* const (&srow)[NR], int K, int it0,
+                                              const float* __restrict__ xs, int lane, float (&acc)[NR]) {
+    constexpr int EPL = WTraits<WT>::EPL;
+    const float4* xs4 = reinterpret_cast<const float4*>(xs);
+    const uint4* xh4 = reinterpret_cast<const uint4*>(xs);
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+        const int it = it0 + u;
+        const int k = it * 32 * EPL + lane * EPL;
+        if (k < K) {
+            if constexpr (WT == WT_F16 || WT == WT_BF16) {
+                const float4 va = xs4[(it * 2) * 32 + lane], vb = xs4[(it * 2 + 1) * 32 + lane];
+                const float x[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+                for (int r = 0; r < NR; r++) fma_vec16<WT>(b.v[u][r], nullptr, 0, x, 0.f, acc[r]);
+            } else if constexpr (WT == WT_Q8_0) {
+                const uint4 xa = xh4[(it * 2) * 32 + lane], xb = xh4[(it * 2 + 1) * 32 + lane];
+#pragma unroll
+                for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(srow[r][k >> 5]), q8_block_dot(b.v[u][r], xa, xb), acc[r]);
+            } else {
+                const uint4 x0 = xh4[(it * 4) * 32 + lane], x1 = xh4[(it * 4 + 1) * 32 + lane];
+                const uint4 x2 = xh4[(it * 4 + 2) * 32 + lane], x3 = xh4[(it * 4 + 3) * 32 + lane];
+#pragma unroll
+                const float bs = q4_block_sums(xs, K)[k >> 5];
+#pragma unroll
+                for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(srow[r][k >> 5]), q4_block_dot(b.v[u][r], x0, x1, x2, x3) - bs, acc[r]);
+            }
+        }
+    }
+}
+
+// `cur` holds batch 0 of `wrow` on entry and batch 0 of `next` (when has_next) on return.
+template <int WT, int NR>
+__device__ __forceinline__ void dot_rows_pipelined(const uint8_t* const (&wrow)[NR], const __half* const (&srow)[NR], int K,
+                                                   const float* __restrict__ xs, int lane, float (&acc)[NR], WBatch<WT, NR>& cur,
+                                                   const uint8_t* const (&next)[NR], bool has_next) {
+    constexpr int EPL = WTraits<WT>::EPL;
+    const int iters = (K + 32 * EPL - 1) / (32 * EPL);
+    for (int it0 = 0; it0 < iters; it0 += 2) {
+        WBatch<WT, NR> nxt;
+        const bool more = it0 + 2 < iters;
+        if (more) load_batch<WT, NR>(nxt, wrow, K, it0 + 2, lane);
+        else if (has_next) load_batch<WT, NR>(nxt, next, K, 0, lane);
+        compute_batch<WT, NR>(cur, srow, K, it0, xs, lane, acc);
+        if (more || has_next) cur = nxt;
     }
 }
 
@@ -331,18 +415,29 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // fp16/bf16 weights: fp32 values in the lane-major order of xs_index; returns 1.
 // Q8_0/Q4_0 weights: fp16 values scaled by a power of two 2^-e (so that |y| < 1) in the order of xh_index;
 // returns 2^e, the factor that undoes the scaling after the dot product.
+constexpr int kRedFloats = 16;  // reduction scratch in front of the staged vector
+
+// Block-wide (sum, max) of one pair per thread in a single exchange; `red` has kRedFloats floats.
+__device__ __forceinline__ void block_sum_max(float& sum, float& mx, float* red) {
+    sum = warp_sum(sum);
+    mx = warp_max(mx);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = sum; red[8 + (threadIdx.x >> 5)] = mx; }
+    __syncthreads();
+    float s = 0.f, m = red[8];
+#pragma unroll
+    for (int i = 0; i < kWarps; i++) { s += red[i]; m = fmaxf(m, red[8 + i]); }
+    sum = s;
+    mx = m;
+}
+
 template <int WT>
 __device__ __forceinline__ float stage_vector(const float* __restrict__ src, int K, int norm, const float* g,
                                               const float* b, float eps, float* xs, float* red) {
     constexpr int EPL = WTraits<WT>::EPL;
     constexpr bool kHalf = WT == WT_Q8_0 || WT == WT_Q4_0;
-    float inv = 1.f, mean = 0.f;
-    if (norm == NORM_RMS) {
-        float ss = 0.f;
-        for (int k = threadIdx.x; k < K; k += kThreads) { float v = src[k]; ss = fmaf(v, v, ss); }
-        ss = block_sum(ss, red);
-        inv = 1.0f / sqrtf(ss / (float)K + eps);
-    } else if (norm == NORM_LAYER) {
+    float inv = 1.f, mean = 0.f, amax = 0.f;
+    if (norm == NORM_LAYER) {
         float s = 0.f;
         for (int k = threadIdx.x; k < K; k += kThreads) s += src[k];
         mean = block_sum(s, red) / (float)K;
@@ -350,6 +445,21 @@ __device__ __forceinline__ float stage_vector(const float* __restrict__ src, int
         for (int k = threadIdx.x; k < K; k += kThreads) { float c = src[k] - mean; vs = fmaf(c, c, vs); }
         vs = block_sum(vs, red);
         inv = 1.0f / sqrtf(vs / (float)K + eps);
+        if (kHalf) {
+            for (int k = threadIdx.x; k < K; k += kThreads) amax = fmaxf(amax, fabsf((src[k] - mean) * inv * g[k] + b[k]));
+            amax = block_max(amax, red);
+        }
+    } else if (norm == NORM_RMS || kHalf) {
+        // one pass: sum of squares and, for the fp16-staged types, the largest |x*g| (the norm scale is applied after)
+        float ss = 0.f, mx = 0.f;
+        for (int k = threadIdx.x; k < K; k += kThreads) {
+            const float v = src[k];
+            ss = fmaf(v, v, ss);
+            if (kHalf) mx = fmaxf(mx, fabsf(norm == NORM_RMS ? v * g[k] : v));
+        }
+        block_sum_max(ss, mx, red);
+        if (norm == NORM_RMS) inv = 1.0f / sqrtf(ss / (float)K + eps);
+        amax = mx * inv;
     }
     auto value = [&](int k) {
         float v = src[k];
@@ -359,15 +469,22 @@ __device__ __forceinline__ float stage_vector(const float* __restrict__ src, int
     };
     float descale = 1.f;
     if constexpr (kHalf) {
-        float amax = 0.f;
-        for (int k = threadIdx.x; k < K; k += kThreads) amax = fmaxf(amax, fabsf(value(k)));
-        amax = block_max(amax, red);
         int e = 0;
-        if (amax > 0.f && amax < 3.0e38f) frexpf(amax, &e);  // amax = m * 2^e with m in [0.5, 1)
-        const float scale = ldexpf(1.0f, -e);
-        descale = ldexpf(1.0f, e);
+        if (amax > 0.f && amax < 3.0e38f) frexpf(amax * 1.0001f, &e);  // amax = m * 2^e with m in [0.5, 1)
+        // Q4_0 stages x * 2^(14-e) (see q4_block_dot) and owes a factor 2^10 at the end; Q8_0 stages x * 2^-e
+        const float scale = ldexpf(1.0f, (WT == WT_Q4_0 ? 14 : 0) - e);
+        descale = ldexpf(1.0f, e + (WT == WT_Q4_0 ? 10 : 0));
         __half* xh = reinterpret_cast<__half*>(xs);
         for (int k = threadIdx.x; k < K; k += kThreads) xh[xh_index<WT>(k)] = __float2half_rn(value(k) * scale);
+        if constexpr (WT == WT_Q4_0) {
+            __syncthreads();
+            float* bsum = xs + xs_floats<32>(K) / 2;
+            for (int blk = threadIdx.x; blk < K / 32; blk += kThreads) {
+                float t = 0.f;
+                for (int i = 0; i < 32; i++) t += __half2float(xh[xh_index<WT>(blk * 32 + i)]);
+                bsum[blk] = t * 4.76837158203125e-07f;  // 2^-21: 8 * 2^-14 (staging) * 2^-10 (folded into the de-scale)
+            }
+        }
     } else {
         for (int k = threadIdx.x; k < K; k += kThreads) xs[xs_index<EPL>(k)] = value(k);
     }
@@ -415,6 +532,37 @@ __device__ void stage_qkv(const QkvArgs& p, int cta, int n_cta, float* xs, float
     int begin, end;
     cta_range(n_items, cta, n_cta, begin, end);
     const bool gpt2 = m.arch == ARCH_GPT2;
+    // the four weight rows of the two adjacent work items starting at item0
+    struct Group {
+        const uint8_t* wr[4];
+        const __half* sr[4];
+        int rows4[4], kinds[2], idx[2];
+        const float* biases[2];
+    };
+    auto describe = [&](int item0, Group& gq) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int item = min(item0 + j, end - 1);
+            const Weight* W;
+            int local;
+            if (item < q_items) { gq.kinds[j] = 0; local = item; W = &p.lw.wq; gq.biases[j] = p.lw.bq; }
+            else if (item < q_items + k_items) { gq.kinds[j] = 1; local = item - q_items; W = &p.lw.wk; gq.biases[j] = p.lw.bk; }
+            else { gq.kinds[j] = 2; local = item - q_items - k_items; W = &p.lw.wv; gq.biases[j] = p.lw.bv; }
+            int row0, row1;
+            gq.idx[j] = 0;
+            if (gq.kinds[j] < 2) { int head = local / half; gq.idx[j] = local - head * half; row0 = head * m.head_dim + gq.idx[j]; row1 = row0 + half; }
+            else { row0 = 2 * local; row1 = row0 + 1; }
+            gq.rows4[2 * j] = row0; gq.rows4[2 * j + 1] = row1;
+            gq.wr[2 * j] = weight_row(*W, row0); gq.wr[2 * j + 1] = weight_row(*W, row1);
+            gq.sr[2 * j] = scale_row(*W, row0); gq.sr[2 * j + 1] = scale_row(*W, row1);
+        }
+    };
+    const int first = begin + 2 * warp;
+    Group cur_g, next_g;
+    WBatch<WT, 4> batch;
+    if (first < end) { describe(first, cur_g); load_batch<WT, 4>(batch, cur_g.wr, m.d_model, 0, lane); }  // weights: no dependency
+    pdl_launch_dependents();
+    pdl_wait();  // from here on the previous stage's outputs are visible
     for (int r = 0; r < p.rows; r++) {
         if (!p.rs.active[r]) continue;
         const int pos = p.rs.pos[r];
@@ -437,59 +585,45 @@ __device__ void stage_qkv(const QkvArgs& p, int cta, int n_cta, float* xs, float
             xdescale = stage_vector<WT>(hid, m.d_model, gpt2 ? NORM_LAYER : NORM_RMS, p.lw.norm1_g, p.lw.norm1_b, m.eps, xs, red);
         }
         const int seq = p.rs.seq[r];
+        if (r > 0 && first < end) { describe(first, cur_g); load_batch<WT, 4>(batch, cur_g.wr, m.d_model, 0, lane); }
         // each warp takes two adjacent work items (four weight rows) per iteration
-        for (int item0 = begin + 2 * warp; item0 < end; item0 += 2 * kWarps) {
-            const uint8_t* wr[4];
-            const __half* sr[4];
-            int rows4[4], kinds[2], idx[2];
-            const float* biases[2];
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const int item = min(item0 + j, end - 1);
-                const Weight* W;
-                int local;
-                if (item < q_items) { kinds[j] = 0; local = item; W = &p.lw.wq; biases[j] = p.lw.bq; }
-                else if (item < q_items + k_items) { kinds[j] = 1; local = item - q_items; W = &p.lw.wk; biases[j] = p.lw.bk; }
-                else { kinds[j] = 2; local = item - q_items - k_items; W = &p.lw.wv; biases[j] = p.lw.bv; }
-                int row0, row1;
-                idx[j] = 0;
-                if (kinds[j] < 2) { int head = local / half; idx[j] = local - head * half; row0 = head * m.head_dim + idx[j]; row1 = row0 + half; }
-                else { row0 = 2 * local; row1 = row0 + 1; }
-                rows4[2 * j] = row0; rows4[2 * j + 1] = row1;
-                wr[2 * j] = weight_row(*W, row0); wr[2 * j + 1] = weight_row(*W, row1);
-                sr[2 * j] = scale_row(*W, row0); sr[2 * j + 1] = scale_row(*W, row1);
-            }
+        for (int item0 = first; item0 < end; item0 += 2 * kWarps) {
+            const bool has_next = item0 + 2 * kWarps < end;
+            if (has_next) describe(item0 + 2 * kWarps, next_g);
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            dot_rows<WT, 4>(wr, sr, m.d_model, xs, lane, acc);
+            dot_rows_pipelined<WT, 4>(cur_g.wr, cur_g.sr, m.d_model, xs, lane, acc, batch, next_g.wr, has_next);
 #pragma unroll
             for (int j = 0; j < 4; j++) acc[j] = warp_sum(acc[j]) * xdescale;
-            if (lane < 2 && item0 + lane < end) {
-                const int j = lane;
-                const int kind = kinds[j], row0 = rows4[2 * j], row1 = rows4[2 * j + 1];
-                float v0 = j == 0 ? acc[0] : acc[2], v1 = j == 0 ? acc[1] : acc[3];
-                const float* bias = biases[j];
-                if (bias) { v0 += bias[row0]; v1 += bias[row1]; }
-                if (kind < 2 && !gpt2) {
-                    float2 cs = p.rope[(size_t)pos * half + idx[j]];
-                    float r0 = v0 * cs.x - v1 * cs.y, r1 = v0 * cs.y + v1 * cs.x;
-                    v0 = r0; v1 = r1;
-                }
-                if (kind == 0) {
-                    float* q = p.a.q + (size_t)r * m.q_dim;
-                    q[row0] = v0; q[row1] = v1;
-                } else {
-                    __half* base = (kind == 1 ? p.kv.k : p.kv.v);
-                    int kvh = row0 / m.head_dim;
-                    size_t off = p.kv.offset(m, p.layer, seq, kvh, pos);
-                    base[off + (row0 - kvh * m.head_dim)] = __float2half_rn(v0);
-                    base[off + (row1 - kvh * m.head_dim)] = __float2half_rn(v1);
-                }
-                if (p.a.debug && p.layer == p.a.debug_layer && r == 0) {
-                    float* dbg = p.a.debug + (kind == 0 ? 0 : kind == 1 ? m.q_dim : m.q_dim + m.kv_dim);
-                    dbg[row0] = kind == 0 ? v0 : __half2float(__float2half_rn(v0));
-                    dbg[row1] = kind == 0 ? v1 : __half2float(__float2half_rn(v1));
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                if (lane == j && item0 + j < end) {
+                    const int kind = cur_g.kinds[j], row0 = cur_g.rows4[2 * j], row1 = cur_g.rows4[2 * j + 1];
+                    float v0 = acc[2 * j], v1 = acc[2 * j + 1];
+                    const float* bias = cur_g.biases[j];
+                    if (bias) { v0 += bias[row0]; v1 += bias[row1]; }
+                    if (kind < 2 && !gpt2) {
+                        float2 cs = p.rope[(size_t)pos * half + cur_g.idx[j]];
+                        float r0 = v0 * cs.x - v1 * cs.y, r1 = v0 * cs.y + v1 * cs.x;
+                        v0 = r0; v1 = r1;
+                    }
+                    if (kind == 0) {
+                        float* q = p.a.q + (size_t)r * m.q_dim;
+                        q[row0] = v0; q[row1] = v1;
+                    } else {
+                        __half* base = (kind == 1 ? p.kv.k : p.kv.v);
+                        int kvh = row0 / m.head_dim;
+                        size_t off = p.kv.offset(m, p.layer, seq, kvh, pos);
+                        base[off + (row0 - kvh * m.head_dim)] = __float2half_rn(v0);
+                        base[off + (row1 - kvh * m.head_dim)] = __float2half_rn(v1);
+                    }
+                    if (p.a.debug && p.layer == p.a.debug_layer && r == 0) {
+                        float* dbg = p.a.debug + (kind == 0 ? 0 : kind == 1 ? m.q_dim : m.q_dim + m.kv_dim);
+                        dbg[row0] = kind == 0 ? v0 : __half2float(__float2half_rn(v0));
+                        dbg[row1] = kind == 0 ? v1 : __half2float(__float2half_rn(v1));
+                    }
                 }
             }
+            if (has_next) cur_g = next_g;
         }
         __syncthreads();
     }
@@ -741,29 +875,42 @@ __device__ void stage_gemv(const GemvArgs& p, int cta, int n_cta, float* xs, flo
     const int n_items = EPI == EPI_SWIGLU ? n_out : (n_out + NR - 1) / NR;
     int begin, end;
     cta_range(n_items, cta, n_cta, begin, end);
+    struct Group {
+        const uint8_t* wr[4];
+        const __half* sr[4];
+    };
+    auto describe = [&](int item0, Group& gq) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int item = min(item0 + j, end - 1);
+            if (EPI == EPI_SWIGLU) {
+                gq.wr[2 * j] = weight_row(p.w, item); gq.wr[2 * j + 1] = weight_row(p.w_up, item);
+                gq.sr[2 * j] = scale_row(p.w, item); gq.sr[2 * j + 1] = scale_row(p.w_up, item);
+            } else {
+                const int row0 = item * NR, row1 = min(row0 + 1, n_out - 1);
+                gq.wr[2 * j] = weight_row(p.w, row0); gq.wr[2 * j + 1] = weight_row(p.w, row1);
+                gq.sr[2 * j] = scale_row(p.w, row0); gq.sr[2 * j + 1] = scale_row(p.w, row1);
+            }
+        }
+    };
+    const int first = begin + 2 * warp;
+    Group cur_g, next_g;
+    WBatch<WT, 4> batch;
+    if (first < end) { describe(first, cur_g); load_batch<WT, 4>(batch, cur_g.wr, K, 0, lane); }  // weights: no dependency
+    pdl_launch_dependents();
+    pdl_wait();  // from here on the previous stage's outputs are visible
     for (int r = 0; r < p.rows; r++) {
         if (!p.rs.active[r]) continue;
         const float xdescale = stage_vector<WT>(p.in + (size_t)r * p.in_stride, K, p.norm, p.norm_g, p.norm_b, m.eps, xs, red);
         float best_v = -INFINITY;
         int best_i = 0x7fffffff;
+        if (r > 0 && first < end) { describe(first, cur_g); load_batch<WT, 4>(batch, cur_g.wr, K, 0, lane); }
         // each warp takes two adjacent work items (four weight rows) per iteration
-        for (int item0 = begin + 2 * warp; item0 < end; item0 += 2 * kWarps) {
-            const uint8_t* wr[4];
-            const __half* sr[4];
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const int item = min(item0 + j, end - 1);
-                if (EPI == EPI_SWIGLU) {
-                    wr[2 * j] = weight_row(p.w, item); wr[2 * j + 1] = weight_row(p.w_up, item);
-                    sr[2 * j] = scale_row(p.w, item); sr[2 * j + 1] = scale_row(p.w_up, item);
-                } else {
-                    const int row0 = item * NR, row1 = min(row0 + 1, n_out - 1);
-                    wr[2 * j] = weight_row(p.w, row0); wr[2 * j + 1] = weight_row(p.w, row1);
-                    sr[2 * j] = scale_row(p.w, row0); sr[2 * j + 1] = scale_row(p.w, row1);
-                }
-            }
+        for (int item0 = first; item0 < end; item0 += 2 * kWarps) {
+            const bool has_next = item0 + 2 * kWarps < end;
+            if (has_next) describe(item0 + 2 * kWarps, next_g);
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            dot_rows<WT, 4>(wr, sr, K, xs, lane, acc);
+            dot_rows_pipelined<WT, 4>(cur_g.wr, cur_g.sr, K, xs, lane, acc, batch, next_g.wr, has_next);
 #pragma unroll
             for (int j = 0; j < 4; j++) acc[j] = warp_sum(acc[j]) * xdescale;
 #pragma unroll
@@ -811,6 +958,7 @@ __device__ void stage_gemv(const GemvArgs& p, int cta, int n_cta, float* xs, flo
                     }
                 }
             }
+            if (has_next) cur_g = next_g;
         }
         if (EPI == EPI_HEAD) {
             // rows grow with the item index, so within a warp the first maximum is kept by the strict '>' above;

@@ -64,9 +64,7 @@ __global__ void __launch_bounds__(kThreads) k_qkv(const QkvArgs p) {
             l2_prefetch(weight_row(*W, row1), rb);
         }
     }
-    pdl_launch_dependents();
-    pdl_wait();
-    stage_qkv<WT>(p, blockIdx.x, gridDim.x, smem + 8, smem);
+    stage_qkv<WT>(p, blockIdx.x, gridDim.x, smem + kRedFloats, smem);  // signals and waits for its neighbours inside
 }
 
 __global__ void __launch_bounds__(kAttThreads) k_attention(const AttArgs p) {
@@ -98,9 +96,7 @@ __global__ void __launch_bounds__(kThreads) k_gemv(const GemvArgs p) {
             }
         }
     }
-    pdl_launch_dependents();
-    pdl_wait();
-    stage_gemv<WT, EPI>(p, blockIdx.x, gridDim.x, smem + 8, smem);
+    stage_gemv<WT, EPI>(p, blockIdx.x, gridDim.x, smem + kRedFloats, smem);
 }
 
 // Final norm + LM head + greedy argmax (a k_gemv<WT, EPI_HEAD> under its own name, so that profiles list it apart).
@@ -119,9 +115,7 @@ __global__ void __launch_bounds__(kThreads) k_lm_head(const GemvArgs p) {
             for (size_t off = 0; off < bytes; off += (32u << 10)) l2_prefetch(b0 + off, (unsigned)min((size_t)(32u << 10), bytes - off));
         }
     }
-    pdl_launch_dependents();
-    pdl_wait();
-    stage_gemv<WT, EPI_HEAD>(p, blockIdx.x, gridDim.x, smem + 8, smem);
+    stage_gemv<WT, EPI_HEAD>(p, blockIdx.x, gridDim.x, smem + kRedFloats, smem);
 }
 
 __global__ void k_bump(RowState rs, int rows) {
@@ -616,7 +610,7 @@ LayerWeights Engine::layer_weights(int l) const {
 }
 
 size_t Engine::gemv_smem(int type, int K, bool with_tmp) const {
-    return sizeof(float) * (size_t)(8 + xs_floats_rt(type, K) + (with_tmp ? m_.d_model : 0));
+    return sizeof(float) * (size_t)(kRedFloats + xs_floats_rt(type, K) + (with_tmp ? m_.d_model : 0));
 }
 
 int32_t Engine::check_ready(const char* what) const {
@@ -631,7 +625,7 @@ int32_t Engine::check_ready(const char* what) const {
 // row; STEP_HEAD runs final norm + LM head + argmax; STEP_FEEDBACK makes the head emit and feed back its token.
 int32_t Engine::launch_step(int rows, int mode, cudaStream_t s, bool profile) {
     const bool gpt2 = m_.arch == ARCH_GPT2;
-    const int cap = sm_count_ * 4;
+    const int cap = sm_count_ * 2;  // one wave: the stage kernels hold ~120 registers, two CTAs per SM
     int launches = 0;
     Activations a = act_;
     a.logits = nullptr;
@@ -1134,8 +1128,8 @@ int32_t Engine::build_mega() {
     p.s3a_bytes = pad128((long long)2 * p.hpc * p.row_bytes);
     p.s3b_bytes = pad128((long long)p.hpc * p.row_bytes);
     int layer_max = std::max(std::max(p.s1_bytes, p.s2_bytes), std::max(p.s3a_bytes, p.s3b_bytes));
-    int rh = std::max(2, (std::max(layer_max, 48 * 1024) / p.row_bytes) & ~1);
-    rh = std::min(rh, (p.vpc + 1) & ~1);
+    int rh = std::max(4, (std::max(layer_max, 48 * 1024) / p.row_bytes) & ~3);
+    rh = std::min(rh, (p.vpc + 3) & ~3);
     p.head_rows_per_chunk = rh;
     p.head_chunks = (p.vpc + rh - 1) / rh;
     p.head_chunk_bytes = pad128((long long)rh * p.row_bytes);
@@ -1279,11 +1273,13 @@ int32_t Engine::get_timings(esp_cuda_timings* out) {
 namespace esp {
 
 // y = W.x with the same inner loop as the decode stages: one warp per pair of rows, 16-byte weight loads.
+// (Measured on B200: this plain loop - two rows per warp, four 16-byte slices per row requested together, three
+// CTAs per SM - streams an LM-head sized fp16 matrix at 0.93 of the copy peak; the software-pipelined four-row
+// loop of the decode stages is slower here (0.83) because its register footprint halves the resident warps.)
 template <int WT>
 __global__ void __launch_bounds__(kThreads) k_gemv_plain(Weight w, const float* __restrict__ x, float* __restrict__ y) {
     extern __shared__ float smem[];
-    constexpr int EPL = WTraits<WT>::EPL;
-    float* xs = smem + 8;
+    float* xs = smem + kRedFloats;
     const float xdescale = stage_vector<WT>(x, w.cols, NORM_NONE, nullptr, nullptr, 0.f, xs, smem);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int n_items = (w.rows + 1) / 2;
@@ -1358,8 +1354,16 @@ int32_t gemv_bench(int32_t type, const void* weights, int32_t rows, int32_t cols
         int sm = 148;
         cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, device);
         int items = (rows + 1) / 2;
-        int grid = std::max(1, std::min((items + kWarps - 1) / kWarps, sm * 8));
-        size_t smem = sizeof(float) * (size_t)(8 + xs_floats_rt(type, cols));
+        size_t smem = sizeof(float) * (size_t)(kRedFloats + xs_floats_rt(type, cols));
+        // one wave of CTAs: every CTA stages the activation vector once and then streams many rows
+        int occ = 1;
+        switch (type) {
+            case WT_F16: cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_gemv_plain<WT_F16>, kThreads, smem); break;
+            case WT_BF16: cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_gemv_plain<WT_BF16>, kThreads, smem); break;
+            case WT_Q8_0: cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_gemv_plain<WT_Q8_0>, kThreads, smem); break;
+            default: cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_gemv_plain<WT_Q4_0>, kThreads, smem); break;
+        }
+        int grid = std::max(1, std::min((items + kWarps - 1) / kWarps, sm * std::max(occ, 1)));
         auto launch = [&](int c) {
             switch (type) {
                 case WT_F16: k_gemv_plain<WT_F16><<<grid, kThreads, smem>>>(ws[c], dx, dy); break;

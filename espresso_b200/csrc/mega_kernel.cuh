@@ -84,9 +84,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+// Weight chunks carry an evict-first L2 policy: they are used once per token, and keeping them out of the way
+// leaves the KV cache, the residual stream and the small per-layer vectors resident in L2.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
                  : "memory");
 }
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
@@ -197,7 +199,10 @@ struct ChunkCursor {
 
 __device__ __forceinline__ const uint8_t* mega_acquire(const MegaArgs& a, const MegaShared& s, unsigned c) {
     const unsigned slot = c % (unsigned)a.plan.n_slots;
-    mega_wait(a, s, s.full + slot, (c / (unsigned)a.plan.n_slots) & 1u, 3);
+    // one lane per warp polls the barrier (256 threads polling one shared-memory word serialise); the warp barrier
+    // that follows orders the other lanes' reads of the chunk after the observed completion
+    if ((threadIdx.x & 31) == 0) mega_wait(a, s, s.full + slot, (c / (unsigned)a.plan.n_slots) & 1u, 3);
+    __syncwarp();
     return s.slots + (size_t)slot * a.plan.slot_bytes;
 }
 __device__ __forceinline__ void mega_release(const MegaArgs& a, const MegaShared& s, unsigned c) {
@@ -261,6 +266,32 @@ __device__ __forceinline__ void mega_dot2(const uint8_t* r0, const uint8_t* r1, 
     o1 = warp_sum(a1);
 }
 
+// Dot products of four fp16 rows held in shared memory with the staged vector (results in every lane).
+__device__ __forceinline__ void mega_dot4(const uint8_t* base, int row_bytes, int K, const float* xs, int lane, float (&o)[4]) {
+    const float4* xs4 = reinterpret_cast<const float4*>(xs);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int iters = (K + 255) / 256;
+    for (int it = 0; it < iters; it++) {
+        const int k = it * 256 + lane * 8;
+        if (k < K) {
+            uint4 w[4];
+#pragma unroll
+            for (int r = 0; r < 4; r++) w[r] = lds128(base + (size_t)r * row_bytes + (size_t)k * 2);
+            const float4 xa = xs4[(it * 2) * 32 + lane], xb = xs4[(it * 2 + 1) * 32 + lane];
+            const float x[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+            for (int r = 0; r < 4; r++) fma_vec16<WT_F16>(w[r], nullptr, 0, x, 0.f, acc[r]);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int r = 0; r < 4; r++) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], off);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; r++) o[r] = acc[r];
+}
+
 // S1: q/k/v rows of this CTA (pairs that RoPE rotates together), RoPE, q store and KV-cache append.
 __device__ __forceinline__ void mega_s1(const MegaArgs& a, const MegaShared& s, int layer, int pos, const uint8_t* chunk) {
     const ModelDims& m = a.m;
@@ -298,35 +329,49 @@ __device__ __forceinline__ void mega_s1(const MegaArgs& a, const MegaShared& s, 
 }
 
 // S2: attention of one head over positions [0, pos], then this CTA's block of the output projection.
-// Each warp owns the positions t = warp + 8*i; lane i scores position i of the warp's set, the probabilities
-// are then broadcast lane by lane while every lane accumulates its own channels of V.  The K and V rows are
-// requested before the query is even staged, and the eight per-warp (max, sum, ctx) triples are merged once.
-__device__ __forceinline__ void mega_s2(const MegaArgs& a, const MegaShared& s, int layer, int pos, const uint8_t* chunk, const float* x_in,
-                                        const uint16_t* emb_row, float* x_mid) {
+// Each warp owns the positions t = warp + 8*i (i < 32 per round).  Four neighbouring lanes share one position:
+// each loads a quarter of its K row with 16-byte vectors (a warp instruction touches 8 cache lines, not 32) and the
+// score is completed with two shuffles.  The probabilities are then broadcast position by position while every
+// lane accumulates its own channels of V.  K and V rows are requested before the query is even staged, and the
+// eight per-warp (max, sum, ctx) triples are merged once.
+template <int HD>
+__device__ __forceinline__ void mega_s2_t(const MegaArgs& a, const MegaShared& s, int layer, int pos, const uint8_t* chunk, const float* x_in,
+                                          const uint16_t* emb_row, float* x_mid) {
     const ModelDims& m = a.m;
     const MegaPlan& p = a.plan;
     const int units = m.n_head * p.blocks;
     if ((int)blockIdx.x >= units) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int hd = m.head_dim;
+    constexpr int hd = HD;
+    constexpr int cpl = HD / 32;  // V channels per lane (head_dim 32/64/128 -> 1/2/4)
+    constexpr int KV4 = HD / 32;  // 16-byte vectors of a K row quarter
     const int head = blockIdx.x / p.blocks, blk = blockIdx.x - head * p.blocks;
     const int kvh = head / (m.n_head / m.n_kv_head);
     const int visible = pos + 1;
     const __half* K = a.kv.k + a.kv.offset(m, layer, 0, kvh, 0);
     const __half* V = a.kv.v + a.kv.offset(m, layer, 0, kvh, 0);
-    const int cpl = hd / 32;  // channels per lane (head_dim 32/64/128 -> 1/2/4)
     const float scale = 1.0f / sqrtf((float)hd);
+    const int sub = lane & 3, tl = lane >> 2;
     if (tid < hd) s.qs[tid] = __ldcg(a.q + (size_t)head * hd + tid);
+    // residual value this thread will add in the projection (head 0 only), requested early
+    const int tpr = hd / 16;
+    float resid = 0.f;
+    {
+        const int orow = blk * p.rpb + tid / tpr;
+        if (head == 0 && (tid % tpr) == 0 && tid / tpr < p.rpb && orow < m.d_model)
+            resid = emb_row ? __half2float(__ushort_as_half(emb_row[orow])) : __ldcg(x_in + orow);
+    }
     float m_w = -INFINITY, l_w = 0.f;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int base = 0; base < visible; base += kMegaConsumers) {
-        // requests: this lane's K row, and the V rows of the warp's 32 positions (this lane's channels)
-        const int t_mine = base + warp + kMegaConsumerWarps * lane;
-        uint4 kreg[16];
-        {
-            const uint4* kr = reinterpret_cast<const uint4*>(K + (size_t)min(t_mine, visible - 1) * hd);
+        // requests: K row quarters of the 4 x 8 positions of this round, V rows of the same positions
+        uint4 kreg[4][KV4];
 #pragma unroll
-            for (int c = 0; c < 16; c++) kreg[c] = c < hd / 8 ? __ldcg(kr + c) : make_uint4(0, 0, 0, 0);
+        for (int st = 0; st < 4; st++) {
+            const int t = base + warp + kMegaConsumerWarps * (st * 8 + tl);
+            const uint4* kr = reinterpret_cast<const uint4*>(K + (size_t)min(t, visible - 1) * hd + sub * (hd / 4));
+#pragma unroll
+            for (int c = 0; c < KV4; c++) kreg[st][c] = __ldcg(kr + c);
         }
         uint2 vreg[32];
 #pragma unroll
@@ -341,38 +386,47 @@ __device__ __forceinline__ void mega_s2(const MegaArgs& a, const MegaShared& s, 
             }
         }
         if (base == 0) consumer_sync();  // q is staged
-        float sc = -INFINITY;
-        if (t_mine < visible) {
+        float sc[4];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int st = 0; st < 4; st++) {
+            const int t = base + warp + kMegaConsumerWarps * (st * 8 + tl);
             float dot = 0.f;
 #pragma unroll
-            for (int c = 0; c < 16; c++) {
-                if (c < hd / 8) {
-                    const uint32_t ww[4] = {kreg[c].x, kreg[c].y, kreg[c].z, kreg[c].w};
+            for (int c = 0; c < KV4; c++) {
+                const uint32_t ww[4] = {kreg[st][c].x, kreg[st][c].y, kreg[st][c].z, kreg[st][c].w};
+                const float* qv = s.qs + sub * (hd / 4) + c * 8;
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[i]));
-                        dot = fmaf(f.x, s.qs[c * 8 + 2 * i], dot);
-                        dot = fmaf(f.y, s.qs[c * 8 + 2 * i + 1], dot);
-                    }
+                for (int i = 0; i < 4; i++) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[i]));
+                    dot = fmaf(f.x, qv[2 * i], dot);
+                    dot = fmaf(f.y, qv[2 * i + 1], dot);
                 }
             }
-            sc = dot * scale;
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            sc[st] = t < visible ? dot * scale : -INFINITY;
+            mx = fmaxf(mx, sc[st]);
         }
-        const float m_new = fmaxf(m_w, warp_max(sc));
-        const float pr = t_mine < visible ? expf(sc - m_new) : 0.f;
+        const float m_new = fmaxf(m_w, warp_max(mx));
+        float pr[4], psum = 0.f;
+#pragma unroll
+        for (int st = 0; st < 4; st++) {
+            pr[st] = sc[st] == -INFINITY ? 0.f : expf(sc[st] - m_new);
+            psum += pr[st];
+        }
         const float corr = m_w == -INFINITY ? 0.f : expf(m_w - m_new);
-        l_w = l_w * corr + warp_sum(pr);
+        l_w = l_w * corr + 0.25f * warp_sum(psum);  // every probability sits in four lanes
 #pragma unroll
         for (int c = 0; c < 4; c++) acc[c] *= corr;
 #pragma unroll
         for (int j = 0; j < 32; j++) {
-            const float pj = __shfl_sync(0xffffffffu, pr, j);
+            const float pj = __shfl_sync(0xffffffffu, pr[j >> 3], (j & 7) * 4);
             const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&vreg[j].x));
             const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&vreg[j].y));
             acc[0] = fmaf(pj, f0.x, acc[0]);
-            acc[1] = fmaf(pj, f0.y, acc[1]);
-            acc[2] = fmaf(pj, f1.x, acc[2]);
-            acc[3] = fmaf(pj, f1.y, acc[3]);
+            if (cpl >= 2) acc[1] = fmaf(pj, f0.y, acc[1]);
+            if (cpl == 4) { acc[2] = fmaf(pj, f1.x, acc[2]); acc[3] = fmaf(pj, f1.y, acc[3]); }
         }
         m_w = m_new;
     }
@@ -397,8 +451,7 @@ __device__ __forceinline__ void mega_s2(const MegaArgs& a, const MegaShared& s, 
     }
     consumer_sync();
     // partial output projection: rows [blk*rpb, ...) of Wo restricted to this head's columns
-    const int tpr = hd / 16;  // threads per row, 16 inputs each
-    const int sub = tid % tpr;
+    const int psub = tid % tpr;  // tpr threads per row, 16 inputs each
     const int rows_per_pass = kMegaConsumers / tpr;
     for (int rb = 0; rb < p.rpb; rb += rows_per_pass) {  // uniform trip count: the shuffles below need every lane
         const int r = rb + tid / tpr;
@@ -406,14 +459,14 @@ __device__ __forceinline__ void mega_s2(const MegaArgs& a, const MegaShared& s, 
         const bool valid = r < p.rpb;
         float v = 0.f;
         if (valid) {
-            const uint8_t* wrow = chunk + (size_t)r * hd * 2 + sub * 32;
+            const uint8_t* wrow = chunk + (size_t)r * hd * 2 + psub * 32;
             const uint4 w0 = lds128(wrow), w1 = lds128(wrow + 16);
-            fma_vec16<WT_F16>(w0, nullptr, 0, s.ctx + sub * 16, 0.f, v);
-            fma_vec16<WT_F16>(w1, nullptr, 0, s.ctx + sub * 16 + 8, 0.f, v);
+            fma_vec16<WT_F16>(w0, nullptr, 0, s.ctx + psub * 16, 0.f, v);
+            fma_vec16<WT_F16>(w1, nullptr, 0, s.ctx + psub * 16 + 8, 0.f, v);
         }
         for (int o = tpr / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (valid && sub == 0 && orow < m.d_model) {
-            if (head == 0) v += emb_row ? __half2float(__ushort_as_half(emb_row[orow])) : __ldcg(x_in + orow);  // residual, added once
+        if (valid && psub == 0 && orow < m.d_model) {
+            if (head == 0) v += rb == 0 ? resid : (emb_row ? __half2float(__ushort_as_half(emb_row[orow])) : __ldcg(x_in + orow));  // residual, added once
             atomicAdd(x_mid + orow, v);
         }
     }
@@ -471,13 +524,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         // ---------------- producer: one thread streams this CTA's chunks in consumption order ----------------
         if (lane == 0) {
             unsigned c = 0;
+            const uint64_t policy = l2_evict_first_policy();
             auto issue = [&](long long off, int bytes) {
                 const unsigned slot = c % (unsigned)p.n_slots;
                 if (*reinterpret_cast<volatile int*>(s.abort)) return;  // once aborting, nothing more is copied
                 if (c >= (unsigned)p.n_slots) mega_wait(a, s, s.empty + slot, ((c / (unsigned)p.n_slots) - 1u) & 1u, 4);
                 if (*reinterpret_cast<volatile int*>(s.abort)) return;
                 mbar_expect_tx(s.full + slot, (unsigned)bytes);
-                bulk_copy_g2s(s.slots + (size_t)slot * p.slot_bytes, blob + off, (unsigned)bytes, s.full + slot);
+                bulk_copy_g2s(s.slots + (size_t)slot * p.slot_bytes, blob + off, (unsigned)bytes, s.full + slot, policy);
                 c++;
             };
             for (int step = 0; step < a.n_steps; step++) {
@@ -542,7 +596,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 // S2
                 ch = mega_acquire(a, s, c);
                 stamp(step);
-                mega_s2(a, s, l, pos, ch, x_in, er, x_mid);
+                if (m.head_dim == 64) mega_s2_t<64>(a, s, l, pos, ch, x_in, er, x_mid);
+                else if (m.head_dim == 128) mega_s2_t<128>(a, s, l, pos, ch, x_in, er, x_mid);
+                else mega_s2_t<32>(a, s, l, pos, ch, x_in, er, x_mid);
                 mega_release(a, s, c); c++;
                 stamp(step);
                 mega_grid_sync(a, s, epoch);
@@ -577,13 +633,15 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             const uint8_t* ch = mega_acquire(a, s, c);
             const int row_base = hc * p.head_rows_per_chunk;
             const int nrows = min(p.head_rows_per_chunk, p.vpc - row_base);
-            for (int pi = warp; 2 * pi < nrows; pi += kMegaConsumerWarps) {
-                const int r0 = 2 * pi, r1 = min(r0 + 1, nrows - 1);
-                float v0, v1;
-                mega_dot2(ch + (size_t)r0 * p.row_bytes, ch + (size_t)r1 * p.row_bytes, m.d_model, s.xs, lane, v0, v1);
-                const int g0 = blockIdx.x * p.vpc + row_base + r0, g1 = blockIdx.x * p.vpc + row_base + r1;
-                if (g0 < m.vocab && v0 > best_v) { best_v = v0; best_i = g0; }
-                if (r1 != r0 && g1 < m.vocab && v1 > best_v) { best_v = v1; best_i = g1; }
+            // four rows per warp per pass; rows past the chunk's end are zero-filled in the pack and masked by `g < vocab`
+            for (int r0 = 4 * warp; r0 < nrows; r0 += 4 * kMegaConsumerWarps) {
+                float v[4];
+                mega_dot4(ch + (size_t)r0 * p.row_bytes, p.row_bytes, m.d_model, s.xs, lane, v);
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+                    const int g = blockIdx.x * p.vpc + row_base + r0 + r;
+                    if (r0 + r < nrows && g < m.vocab && v[r] > best_v) { best_v = v[r]; best_i = g; }
+                }
             }
             mega_release(a, s, c); c++;
         }

@@ -119,7 +119,7 @@ int32_t lm_head_argmax_static(const void* d_lm_head_f16, int32_t vocab, int32_t 
     cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, device);
     const int items = (vocab + 1) / 2;
     const int grid = std::max(1, std::min((items + kWarps - 1) / kWarps, sm * 4));
-    const size_t smem = sizeof(float) * (size_t)(8 + xs_floats_rt(WT_F16, d_model));
+    const size_t smem = sizeof(float) * (size_t)(kRedFloats + xs_floats_rt(WT_F16, d_model));
     ESP_CUDA_TRY(launch_pdl(k_lm_head<WT_F16>, dim3(grid), dim3(kThreads), smem, stream, ga));
     ESP_CUDA_TRY(cudaMemcpyAsync(d_tokens, v.next, sizeof(uint32_t) * rows, cudaMemcpyDeviceToDevice, stream));
     return ESP_CUDA_OK;
