@@ -3,3 +3,4 @@
 #include "engine.cu"
 #include "capi.cu"
 #include "static_head.cu"
+#include "tc_host.cu"

@@ -102,6 +102,7 @@ SIGNATURES = {
     "esp_cuda_version": (C.c_char_p, []),
     "esp_cuda_dequantize": (C.c_int32, [C.c_int32, _vp, C.c_int64, _f32p, C.c_int32]),
     "esp_cuda_lm_head_argmax_static": (C.c_int32, [_vp, C.c_int32, C.c_int32, _vp, C.c_int32, _vp, C.c_float, _vp, _vp, C.c_int32]),
+    "esp_cuda_gemm_tc_bench": (C.c_int32, [C.c_int32, _vp, C.c_int32, C.c_int32, _f32p, C.c_int32, _f32p, C.c_int32, C.c_int32, _f32p, C.c_int32]),
     "esp_cuda_gemv_bench": (C.c_int32, [C.c_int32, _vp, C.c_int32, C.c_int32, _f32p, _f32p, C.c_int32, C.c_int32, C.c_int32, _f32p, C.c_int32]),
 }
 
@@ -366,6 +367,19 @@ def lm_head_argmax_static(lm_head_ptr: int, vocab: int, d_model: int, hidden_ptr
     _check(load_library().esp_cuda_lm_head_argmax_static(
         C.c_void_p(lm_head_ptr), vocab, d_model, C.c_void_p(hidden_ptr), rows, C.c_void_p(gain_ptr) if gain_ptr else None,
         eps, C.c_void_p(tokens_ptr), C.c_void_p(stream) if stream else None, device))
+
+
+def gemm_tc_bench(kind: str, weights: np.ndarray, rows: int, cols: int, x: np.ndarray, warmup: int = 3, iterations: int = 20,
+                  device: int = 0) -> tuple[np.ndarray, float]:
+    """Tensor-core ``Y = X . W^T`` for a batch ``x`` of shape ``[n, cols]``; returns ``(Y [n, rows], mean kernel ms)``."""
+    w = np.ascontiguousarray(weights)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n = x.shape[0]
+    y = np.empty((n, rows), np.float32)
+    ms = C.c_float()
+    _check(load_library().esp_cuda_gemm_tc_bench(TENSOR_TYPES[kind], C.c_void_p(w.ctypes.data), rows, cols, x.ctypes.data_as(_f32p), n,
+                                                 y.ctypes.data_as(_f32p), warmup, iterations, C.byref(ms), device))
+    return y, float(ms.value)
 
 
 def gemv_bench(kind: str, weights: np.ndarray, rows: int, cols: int, x: np.ndarray, warmup: int = 3, iterations: int = 20,

@@ -220,6 +220,15 @@ ESP_CUDA_API int32_t esp_cuda_gemv_bench(int32_t type, const void* weights, int3
                                          float* y, int32_t warmup, int32_t iterations, int32_t copies, float* avg_ms,
                                          int32_t device);
 
+/* Y[n][m] = sum_k W[m][k] * X[n][k] on the tensor cores (tcgen05 / TMEM): W [rows, cols] fp16 or bf16 row-major,
+ * X [n, cols] fp32 (rounded to W's type on the device), Y [n, rows] fp32; 1 <= n <= 256, cols a multiple of 64.
+ * This is the batched counterpart of esp_cuda_gemv_bench (the reference multiplies one vector at a time with
+ * vDSP_mmul, Engine.swift:6674-6718, and uses cblas_sgemm for sequence verify, GenerationHarness.swift:2745-2761).
+ * All pointers are host pointers; *avg_ms receives the mean kernel time. */
+ESP_CUDA_API int32_t esp_cuda_gemm_tc_bench(int32_t type, const void* weights, int32_t rows, int32_t cols, const float* x,
+                                            int32_t n, float* y, int32_t warmup, int32_t iterations, float* avg_ms,
+                                            int32_t device);
+
 /* ---- an entry point that allocates nothing --------------------------------------------------------- */
 
 /* No counterpart in the reference.  Final RMSNorm (skipped when d_norm_gain is NULL) + fp16 LM head +

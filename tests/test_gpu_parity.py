@@ -66,6 +66,31 @@ def test_gemv_kernel_matches_oracle(rt, oracle_lib, kind, shape):
     assert ms > 0
 
 
+@pytest.mark.parametrize("kind,shape", [("f16", (128, 64, 16)), ("f16", (300, 768, 5)), ("f16", (2304, 768, 256)), ("bf16", (1000, 128, 33)),
+                                        ("f16", (4096, 2048, 64)), ("bf16", (515, 4096, 130))])
+def test_tensor_core_gemm_matches_fp32_reference(rt, kind, shape):
+    """tcgen05/TMEM GEMM: exact 16-bit operands, fp32 accumulation; ragged M (TMA zero fill) and ragged batch."""
+    import torch
+
+    M, K, N = shape
+    rng = np.random.default_rng(M * 7 + K + N)
+    w = (rng.standard_normal((M, K)) * 0.05).astype(np.float32)
+    x = rng.standard_normal((N, K)).astype(np.float32)
+    if kind == "f16":
+        stored = w.astype(np.float16)
+        wr, xr = stored.astype(np.float32), x.astype(np.float16).astype(np.float32)
+    else:
+        tw = torch.from_numpy(w).to(torch.bfloat16)
+        stored = tw.view(torch.int16).numpy().view(np.uint16)
+        wr, xr = tw.float().numpy(), torch.from_numpy(x).to(torch.bfloat16).float().numpy()
+    y, ms = rt.gemm_tc_bench(kind, stored, M, K, x, warmup=1, iterations=2)
+    ref = xr.astype(np.float64) @ wr.astype(np.float64).T
+    np.testing.assert_allclose(y, ref, atol=2e-4, rtol=2e-4)
+    assert ms > 0
+    with pytest.raises(rt.RealModelInferenceError):
+        rt.gemm_tc_bench(kind, stored, M, K, np.zeros((257, K), np.float32))  # batch beyond one accumulator tile
+
+
 def _stepwise_logit_parity(rt, oracle_lib, weight_dir, prompt, extra_steps=6):
     eng = rt.DecodeEngine.build(weight_dir)
     ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(weight_dir))
