@@ -1,6 +1,8 @@
 // Engine implementation: device memory, weight upload (BLOBFILE directories and raw/GGUF tensors),
 // kernel submission (direct or CUDA-graph replay, programmatic dependent launch between stages).
 #include "engine.h"
+#include "batch_kernels.cuh"
+#include "tc_gemm.cuh"
 
 #include <sys/stat.h>
 
@@ -39,6 +41,11 @@ static int32_t fail(int32_t code, const std::string& msg) {
     set_last_error(msg);
     return code;
 }
+
+int32_t tc_make_map(CUtensorMap* map, const void* base, bool bf16, uint64_t rows, uint64_t cols, uint32_t box_rows);
+int tc_tile_for(int rows);
+cudaError_t tc_launch(int tile, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, cudaStream_t s);
+constexpr int kTcMinRows = 9;  // below this the row-batched GEMV stages are used
 
 // ---------------------------------------------------------------------------------------------- kernels
 
@@ -313,7 +320,7 @@ int32_t Engine::init() {
     m_.max_seq = cfg_.max_seq; m_.q_dim = cfg_.n_head * cfg_.head_dim; m_.kv_dim = cfg_.n_kv_head * cfg_.head_dim;
     m_.n_seq = cfg_.max_batch; m_.eps = cfg_.norm_eps; m_.eos_token = cfg_.eos_token;
 
-    max_rows_ = std::max(cfg_.max_batch, 8);
+    max_rows_ = std::max(cfg_.max_batch, 64);  // rows of one pass: sequences of a batch, or positions of a prefill chunk
     n_splits_ = (m_.max_seq + kAttSplitTokens - 1) / kAttSplitTokens;
     out_stride_ = m_.max_seq;
 
@@ -581,6 +588,7 @@ int32_t Engine::finalize() {
     if ((rc = dev_alloc(owned_, &d_debug_, dbg))) return rc;
     ESP_CUDA_TRY(cudaDeviceSynchronize());
     if ((rc = build_mega())) return rc;
+    if ((rc = build_tc())) return rc;
     finalized_ = true;
     return reset();
 }
@@ -624,6 +632,7 @@ int32_t Engine::check_ready(const char* what) const {
 // One pass over the model for `rows` rows.  mode: STEP_FORWARD runs the layers on (tok, pos) of every active
 // row; STEP_HEAD runs final norm + LM head + argmax; STEP_FEEDBACK makes the head emit and feed back its token.
 int32_t Engine::launch_step(int rows, int mode, cudaStream_t s, bool profile) {
+    if (tc_ready_ && rows >= kTcMinRows) return launch_step_tc(rows, mode, s);
     const bool gpt2 = m_.arch == ARCH_GPT2;
     const int cap = sm_count_ * 2;  // one wave: the stage kernels hold ~120 registers, two CTAs per SM
     int launches = 0;
@@ -818,6 +827,11 @@ int32_t Engine::feed_rows(int rows, const int* seq, const uint32_t* tok, bool wi
     if ((rc = submit(rows, STEP_FORWARD | (with_head ? STEP_HEAD : 0)))) return rc;
     if (with_head) ESP_CUDA_TRY(cudaMemcpyAsync(h_next_, rs_.next, sizeof(uint32_t) * rows, cudaMemcpyDeviceToHost, stream_));
     ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    if (tc_ready_ && rows >= kTcMinRows) {
+        int herr = 0;
+        ESP_CUDA_TRY(cudaMemcpy(&herr, d_tc_error_, sizeof(int), cudaMemcpyDeviceToHost));
+        if (herr) return fail(ESP_CUDA_ERR_TIMEOUT, "tensor-core GEMM gave up waiting on a barrier");
+    }
     for (int s = 0; s < m_.n_seq; s++) h_visible_[s] += extra[s];
     if (with_head && next_out) memcpy(next_out, h_next_, sizeof(uint32_t) * rows);
     return ESP_CUDA_OK;
@@ -857,7 +871,7 @@ int32_t Engine::prefill(const uint32_t* tokens, int32_t n) {
     if (!tokens || n <= 0) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "Prompt tokens must not be empty");
     if ((rc = reset())) return rc;
     // the prompt is processed in chunks of rows that share sequence 0 at consecutive positions
-    const int chunk = std::min(max_rows_, 8);
+    const int chunk = std::min(max_rows_, tc_ready_ ? 64 : 8);
     std::vector<int> seq(chunk, 0);
     for (int i = 0; i < n; i += chunk) {
         int c = std::min(chunk, n - i);
@@ -1095,6 +1109,145 @@ int32_t Engine::decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, 
         if (n > 0 && out_tokens)
             ESP_CUDA_TRY(cudaMemcpy(out_tokens + (size_t)s * out_stride, rs_.out + (size_t)s * out_stride_, sizeof(uint32_t) * n, cudaMemcpyDeviceToHost));
     }
+    return ESP_CUDA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- batched tensor-core path
+
+int32_t Engine::build_tc() {
+    tc_ready_ = false;
+    if (max_rows_ > 256) return ESP_CUDA_OK;
+    if (m_.d_model % 64 || m_.q_dim % 64 || m_.hidden % 64) return ESP_CUDA_OK;
+    const int t0 = tensors_.at("lm_head").type;
+    if (t0 != ESP_CUDA_F16 && t0 != ESP_CUDA_BF16) return ESP_CUDA_OK;
+    std::vector<std::string> mats = {"lm_head"};
+    for (int l = 0; l < m_.n_layer; l++)
+        for (const char* n : {"wq", "wk", "wv", "wo", "w1", "w2", "w3"}) {
+            if (m_.arch == ARCH_GPT2 && std::string(n) == "w3") continue;
+            mats.push_back("layers/" + std::to_string(l) + "/" + n);
+        }
+    for (auto& n : mats)
+        if (tensors_.at(n).type != t0) return ESP_CUDA_OK;
+    tc_bf16_ = t0 == ESP_CUDA_BF16;
+    for (auto& n : mats) {
+        DeviceTensor& t = tensors_.at(n);
+        int32_t rc = tc_make_map(&t.map, t.data, tc_bf16_, t.rows, t.cols, kTcBlockM);
+        if (rc) return rc;
+        t.has_map = true;
+    }
+    tc_rows_alloc_ = tc_tile_for(max_rows_);
+    int32_t rc;
+    if ((rc = dev_alloc(owned_, &xh_d_, (size_t)tc_rows_alloc_ * m_.d_model))) return rc;
+    if ((rc = dev_alloc(owned_, &xh_q_, (size_t)tc_rows_alloc_ * m_.q_dim))) return rc;
+    if ((rc = dev_alloc(owned_, &xh_h_, (size_t)tc_rows_alloc_ * m_.hidden))) return rc;
+    if ((rc = dev_alloc(owned_, &kraw_, (size_t)max_rows_ * m_.kv_dim))) return rc;
+    if ((rc = dev_alloc(owned_, &vraw_, (size_t)max_rows_ * m_.kv_dim))) return rc;
+    if ((rc = dev_alloc(owned_, &up_, (size_t)max_rows_ * m_.hidden))) return rc;
+    if ((rc = dev_alloc(owned_, &d_tc_error_, 4))) return rc;
+    ESP_CUDA_TRY(cudaDeviceSynchronize());
+    tc_ready_ = true;
+    return ESP_CUDA_OK;
+}
+
+const CUtensorMap* Engine::activation_map(const uint16_t* buf, int K, int tile) {
+    auto key = std::make_pair(static_cast<const void*>(buf), tile);
+    auto it = act_maps_.find(key);
+    if (it == act_maps_.end()) {
+        CUtensorMap m;
+        if (tc_make_map(&m, buf, tc_bf16_, tc_rows_alloc_, K, tile)) return nullptr;
+        it = act_maps_.emplace(key, m).first;
+    }
+    return &it->second;
+}
+
+// One pass over the model for `rows` rows with the matrix products on the tensor cores: every weight matrix is
+// streamed once per pass whatever the row count.
+int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
+    const bool gpt2 = m_.arch == ARCH_GPT2;
+    const int tile = tc_tile_for(rows);
+    if (!tile) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "too many rows for one tensor-core pass");
+    int launches = 0;
+    float* dbg = debug_layer_ >= 0 ? d_debug_ : nullptr;
+    const int q = m_.q_dim, kv = m_.kv_dim, d = m_.d_model, h = m_.hidden;
+    auto prep = [&](const float* src, int K, int norm, const float* g, const float* b, uint16_t* dst, bool from_emb) -> int32_t {
+        PrepArgs p{};
+        p.m = m_; p.rs = rs_; p.src = src; p.hidden_out = act_.hidden; p.K = K; p.norm = norm; p.g = g; p.b = b; p.dst = dst; p.bf16 = tc_bf16_;
+        p.from_embedding = from_emb ? 1 : 0;
+        if (from_emb) {
+            const DeviceTensor& te = tensors_.at("embeddings/token");
+            p.tok_emb = static_cast<const uint16_t*>(te.data);
+            p.pos_emb = gpt2 ? static_cast<const uint16_t*>(tensors_.at("embeddings/position").data) : nullptr;
+            p.emb_type = te.type == ESP_CUDA_BF16 ? WT_BF16 : WT_F16;
+        }
+        k_prep_rows<<<rows, kThreads, 0, s>>>(p);
+        launches++;
+        ESP_CUDA_TRY(cudaGetLastError());
+        return ESP_CUDA_OK;
+    };
+    auto gemm = [&](const DeviceTensor& W, const uint16_t* xbuf, int epi, float* out, int ldo, const float* bias) -> int32_t {
+        const CUtensorMap* mx = activation_map(xbuf, W.cols, tile);
+        if (!mx || !W.has_map) return fail(ESP_CUDA_ERR_CUDA, "tensor map missing for the batched path");
+        TcArgs a{};
+        a.M = W.rows; a.K = W.cols; a.n_valid = rows; a.epilogue = epi; a.out = out; a.ldo = ldo; a.bias = bias; a.active = rs_.active;
+        a.error = d_tc_error_; a.bf16 = tc_bf16_;
+        if (epi == TC_HEAD) { a.best = rs_.best; a.logits = (cfg_.flags & ESP_CUDA_FLAG_KEEP_LOGITS) ? act_.logits : nullptr; }
+        ESP_CUDA_TRY(tc_launch(tile, W.map, *mx, a, s));
+        launches++;
+        return ESP_CUDA_OK;
+    };
+    auto copy_dbg = [&](const float* src, int offset, int n) {
+        if (dbg) { k_copy_debug<<<(n + 255) / 256, 256, 0, s>>>(src, dbg + offset, n); launches++; }
+    };
+    int32_t rc;
+    if (mode & STEP_FORWARD) {
+        for (int l = 0; l < m_.n_layer; l++) {
+            const std::string pre = "layers/" + std::to_string(l) + "/";
+            const LayerWeights lw = layer_weights(l);
+            const bool cap = dbg && l == debug_layer_;
+            if ((rc = prep(l == 0 ? nullptr : act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, lw.norm1_g, lw.norm1_b, xh_d_, l == 0))) return rc;
+            if ((rc = gemm(tensors_.at(pre + "wq"), xh_d_, TC_STORE, act_.q, q, lw.bq))) return rc;
+            if ((rc = gemm(tensors_.at(pre + "wk"), xh_d_, TC_STORE, kraw_, kv, lw.bk))) return rc;
+            if ((rc = gemm(tensors_.at(pre + "wv"), xh_d_, TC_STORE, vraw_, kv, lw.bv))) return rc;
+            RopeArgs ra{};
+            ra.m = m_; ra.rs = rs_; ra.kv = kv_; ra.q = act_.q; ra.k_raw = kraw_; ra.v_raw = vraw_; ra.rope = gpt2 ? nullptr : d_rope_; ra.layer = l;
+            ra.debug = cap ? dbg : nullptr;
+            k_rope_append<<<rows, kThreads, 0, s>>>(ra);
+            launches++;
+            AttArgs aa{};
+            aa.m = m_; aa.layer = l; aa.rows = rows; aa.n_splits = n_splits_; aa.rs = rs_; aa.a = act_; aa.kv = kv_;
+            aa.a.logits = nullptr; aa.a.debug = cap ? dbg : nullptr; aa.a.debug_layer = debug_layer_;
+            ESP_CUDA_TRY(launch_pdl(k_attention, dim3(m_.n_head, rows, n_splits_), dim3(kAttThreads), 0, s, aa));
+            launches++;
+            if ((rc = prep(act_.ctx, q, NORM_NONE, nullptr, nullptr, xh_q_, false))) return rc;
+            if ((rc = gemm(tensors_.at(pre + "wo"), xh_q_, TC_RESIDUAL, act_.hidden, d, lw.bo))) return rc;
+            if (cap) copy_dbg(act_.hidden, 2 * q + 2 * kv, d);
+            if ((rc = prep(act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, lw.norm2_g, lw.norm2_b, xh_d_, false))) return rc;
+            if ((rc = gemm(tensors_.at(pre + "w1"), xh_d_, TC_STORE, act_.act, h, lw.b1))) return rc;
+            if (!gpt2 && (rc = gemm(tensors_.at(pre + "w3"), xh_d_, TC_STORE, up_, h, nullptr))) return rc;
+            ActArgs ac{};
+            ac.rs = rs_; ac.gate = act_.act; ac.up = gpt2 ? nullptr : up_; ac.dst = xh_h_; ac.h = h; ac.bf16 = tc_bf16_;
+            ac.debug = cap ? dbg + 2 * q + 2 * kv + d : nullptr;
+            k_act_rows<<<dim3((h + kThreads - 1) / kThreads, rows), kThreads, 0, s>>>(ac);
+            launches++;
+            if ((rc = gemm(tensors_.at(pre + "w2"), xh_h_, TC_RESIDUAL, act_.hidden, d, lw.b2))) return rc;
+            if (cap) copy_dbg(act_.hidden, 2 * q + 2 * kv + d + h, d);
+        }
+    }
+    GemvArgs fin{};
+    fin.m = m_; fin.rows = rows; fin.rs = rs_;
+    if (mode & STEP_HEAD) {
+        if ((rc = prep(act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, tensors_.at(gpt2 ? "final_norm_gamma" : "rms_final").f32,
+                       gpt2 ? tensors_.at("final_norm_beta").f32 : nullptr, xh_d_, false))) return rc;
+        if ((rc = gemm(tensors_.at("lm_head"), xh_d_, TC_HEAD, nullptr, 0, nullptr))) return rc;
+        fin.finalize_mode = ((mode & STEP_FEEDBACK) ? 1 : 0) | ((mode & STEP_FORWARD) ? 2 : 0);
+        k_head_done<<<1, 256, 0, s>>>(fin);
+        launches++;
+    } else if (mode & STEP_FORWARD) {
+        ESP_CUDA_TRY(launch_pdl(k_bump, dim3(1), dim3(64), 0, s, rs_, rows));
+        launches++;
+    }
+    ESP_CUDA_TRY(cudaGetLastError());
+    launches_last_step_ = launches;
     return ESP_CUDA_OK;
 }
 

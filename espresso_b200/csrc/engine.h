@@ -3,6 +3,7 @@
 // CPUExactLlamaRuntime (Sources/RealModelInference/RealModelInferenceEngine.swift:548-850) generalised to
 // `max_batch` independent sequences and to GPT-2.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <map>
@@ -26,6 +27,8 @@ struct DeviceTensor {
     int type = -1;
     int rows = 0, cols = 0;
     bool loaded = false;
+    CUtensorMap map{};          // TMA map of a 16-bit matrix for the tensor-core path (128-row boxes)
+    bool has_map = false;
 };
 
 struct Checkpoint {
@@ -84,6 +87,9 @@ private:
                         const int* limit, bool zero_out_counts);
     int32_t submit(int rows, int mode);                  // graph replay or direct launch
     int32_t launch_step(int rows, int mode, cudaStream_t s, bool profile);
+    int32_t launch_step_tc(int rows, int mode, cudaStream_t s);  // batched path: tensor-core GEMMs + element-wise stages
+    int32_t build_tc();
+    const CUtensorMap* activation_map(const uint16_t* buf, int K, int tile);
     int32_t feed_rows(int rows, const int* seq, const uint32_t* tok, bool with_head, uint32_t* next_out);
     Weight weight_of(const DeviceTensor& t) const;
     LayerWeights layer_weights(int l) const;
@@ -122,6 +128,15 @@ private:
     std::map<int, int> launches_by_key_;
     std::vector<cudaEvent_t> prof_events_;
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
+
+    // batched tensor-core path (rows >= kTcMinRows, 16-bit weights)
+    bool tc_ready_ = false;
+    int tc_bf16_ = 0;
+    int tc_rows_alloc_ = 0;
+    uint16_t *xh_d_ = nullptr, *xh_q_ = nullptr, *xh_h_ = nullptr;  // 16-bit operand rows [tc_rows_alloc_][K]
+    float *kraw_ = nullptr, *vraw_ = nullptr, *up_ = nullptr;
+    int* d_tc_error_ = nullptr;
+    std::map<std::pair<const void*, int>, CUtensorMap> act_maps_;
 
     // persistent decode kernel (single sequence, Llama fp16 models whose per-layer slice fits in shared memory)
     bool mega_ready_ = false;

@@ -184,7 +184,8 @@ def test_prefill_equals_token_by_token(rt, tmp_models):
     for t in prompt:
         eng.advance(int(t))
     b = eng.logits()
-    np.testing.assert_allclose(a, b, atol=1e-4)
+    # the chunked prefill runs on the tensor cores with 16-bit activation rows, the single steps on the GEMV path
+    assert_logits_close(a, b, "chunked prefill vs token by token")
     assert eng.visible_token_count() == 21
     eng.close()
 
@@ -291,25 +292,27 @@ def test_batched_decode_equals_independent_sequences(rt, oracle_lib, tmp_models)
     from espresso_b200.model_config import tiny_gpt2, tiny_llama
     from espresso_b200.synthetic import synthetic_prompt
 
-    for cfg, seed in ((tiny_llama(vocab=512, max_seq=64, n_layer=2), 1234), (tiny_gpt2(vocab=512, max_seq=64, n_layer=2), 777)):
+    cases = ((tiny_llama(vocab=512, max_seq=64, n_layer=2), 1234), (tiny_gpt2(vocab=512, max_seq=64, n_layer=2), 777))
+    for cfg, seed in cases:
         d = tmp_models(cfg, seed)
-        n_seq = 5
-        prompts = np.stack([synthetic_prompt(cfg.vocab, 7, seed=seed, stream=s) for s in range(n_seq)])
-        eng = rt.DecodeEngine.build(d, max_batch=n_seq)
-        toks, res = eng.generate_batch(prompts, 12)
         model = oracle_lib.Model.from_dir(d)
-        for s in range(n_seq):
-            assert len(toks[s]) == 12
-            compare_greedy_stream(oracle_lib.Runtime(model), prompts[s], toks[s])
-        # step API: logits of every sequence against the oracle
-        eng.prefill_batch(prompts)
-        nxt = eng.decode_step_batch(prompts[:, 0])
-        for s in range(n_seq):
-            ora = oracle_lib.Runtime(model)
-            ora.prefill(list(prompts[s]) + [int(prompts[s, 0])])
-            assert_logits_close(eng.logits(s), ora.logits(), f"{cfg.name} seq {s}")
-            assert int(nxt[s]) == int(np.argmax(eng.logits(s)))
-        eng.close()
+        for n_seq in (5, 12):  # 5 rows: row-batched GEMV stages; 12 rows: tensor-core GEMM path
+            prompts = np.stack([synthetic_prompt(cfg.vocab, 7, seed=seed, stream=s) for s in range(n_seq)])
+            eng = rt.DecodeEngine.build(d, max_batch=n_seq)
+            toks, res = eng.generate_batch(prompts, 12)
+            for s in range(n_seq):
+                assert len(toks[s]) == 12
+                compare_greedy_stream(oracle_lib.Runtime(model), prompts[s], toks[s])
+            # step API: logits of every sequence against the oracle
+            eng.prefill_batch(prompts)
+            nxt = eng.decode_step_batch(prompts[:, 0])
+            for s in range(n_seq):
+                ora = oracle_lib.Runtime(model)
+                ora.prefill(list(prompts[s]) + [int(prompts[s, 0])])
+                assert_logits_close(eng.logits(s), ora.logits(), f"{cfg.name} n_seq {n_seq} seq {s}")
+                lg = eng.logits(s)
+                assert lg[int(nxt[s])] >= lg.max() - 2e-3
+            eng.close()
 
 
 def test_verify2_checkpoint_and_two_token_generation(rt, oracle_lib, tmp_models):
