@@ -37,6 +37,8 @@ WORKLOADS = {
                label="llama 6L d768 target + 1-layer draft, exact two-token verify, batch 1, 16-token prompt, 128 tokens"),
     "c3": dict(cfg=mc.gpt2_117m, prompt=64, decode=256, n_seq=256, sharded=True, kind="f16", bpw=2.0,
                label="gpt2-117M shape 12L d768 vocab50257 ctx1024 fp16, 256 independent sequences sharded over the GPUs, 64-token prompts, 256 greedy steps"),
+    "c5": dict(cfg=mc.llama3_8b, prompt=512, decode=256, n_seq=64, kind="bf16", bpw=2.0, device_weights=True, tp=True,
+               label="llama-3-8B shape 32L d4096 GQA 32/8 hd128 vocab128256 ctx1024 bf16, 64 sequences, 512-token prompts, 256 greedy steps, tensor parallel over the GPUs (NCCL all-reduce after Wo and W2)"),
     "c4q8": dict(cfg=mc.llama_1b, prompt=128, decode=256, n_seq=1, kind="q8_0", bpw=34.0 / 32, device_weights=True,
                  label="llama 1.1B shape 22L d2048 GQA 32/4 ctx2048, GGUF Q8_0 matrices + LM head, batch 1, 128-token prompt, 256 steps"),
     "c4q4": dict(cfg=mc.llama_1b, prompt=128, decode=256, n_seq=1, kind="q4_0", bpw=18.0 / 32, device_weights=True,
@@ -294,7 +296,10 @@ def main() -> None:
     tmp = tempfile.mkdtemp(prefix=f"esp_bench_r{rank}_")
     try:
         n_prompt, n_decode = wl["prompt"], wl["decode"]
-        if wl.get("sharded"):
+        tp = bool(wl.get("tp")) and world > 1
+        if wl.get("tp"):
+            n_seq, first_stream, scaling = wl["n_seq"], 0, "strong"  # every rank drives the same sequences
+        elif wl.get("sharded"):
             b, e = shard_range(wl["n_seq"], rank, world)
             n_seq, first_stream, scaling = e - b, b, "strong"
         else:
@@ -304,8 +309,13 @@ def main() -> None:
         if wl.get("device_weights"):
             from espresso_b200.synthetic_device import upload_synthetic
 
-            eng = runtime.DecodeEngine.empty(cfg, max_batch=n_seq, device=local_rank, flags=flags)
-            upload_synthetic(eng, cfg, wl["kind"], device=local_rank)
+            eng = runtime.DecodeEngine.empty(cfg, max_batch=n_seq, device=local_rank, flags=flags, tp_rank=rank if tp else 0,
+                                             tp_size=world if tp else 1)
+            if tp:
+                ids = [runtime.tp_unique_id() if rank == 0 else None]
+                dist.broadcast_object_list(ids, src=0)
+                eng.tp_init(ids[0])
+            upload_synthetic(eng, cfg, wl["kind"], device=local_rank, tp_rank=rank if tp else 0, tp_size=world if tp else 1)
         else:
             write_synthetic_model(cfg, tmp)
             eng = runtime.DecodeEngine.build(tmp, max_batch=n_seq, device=local_rank, flags=flags)
@@ -381,6 +391,8 @@ def main() -> None:
         e2e_total = sum(e2e_times)
 
         tokens_local = n_seq * n_decode * args.steps
+        if wl.get("tp") and world > 1 and rank != 0:
+            tokens_local = 0  # the ranks of a tensor-parallel group decode the same sequences together
         if world > 1:
             t = torch.tensor([total_ms, e2e_total], dtype=torch.float64, device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -435,7 +447,8 @@ def main() -> None:
             "ms_per_step": total_ms / args.steps, "ms_per_token": total_ms / args.steps / n_decode, "higher_is_better": True,
             "scaling": scaling, "vs_baseline": None, "dtype": f"{wl['kind']} weights, f16 KV, f32 accumulate", "data": "synthetic",
             "config": {"workload": wl["label"],
-                       "parallelism": ("sequences sharded across GPUs, no collective" if wl.get("sharded") else
+                       "parallelism": (f"tensor parallel x{world}, NCCL all-reduce after Wo and W2" if wl.get("tp") else
+                                       "sequences sharded across GPUs, no collective" if wl.get("sharded") else
                                        "replicas only (one independent job per GPU)") if world > 1 else "single GPU",
                        "l2": "no flush: every decode step streams more weight + KV bytes than the 126 MB L2 holds"},
             "e2e": {"value": e2e_value, "unit": unit,

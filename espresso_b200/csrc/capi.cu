@@ -13,6 +13,7 @@
 
 namespace esp {
 void set_force_failure(int on);
+int32_t tp_unique_id(uint8_t* out, int32_t capacity);
 int32_t gemv_bench(int32_t type, const void* weights, int32_t rows, int32_t cols, const float* x, float* y, int32_t warmup,
                    int32_t iterations, int32_t copies, float* avg_ms, int32_t device);
 __global__ void k_dequant(const uint8_t* blocks, int type, int64_t n_blocks, float* out);
@@ -111,6 +112,11 @@ int32_t esp_cuda_create_from_directory(const char* weight_dir, int32_t max_batch
 int32_t esp_cuda_load_tensor(esp_cuda_engine* engine, const char* name, int32_t type, const void* data, uint64_t nbytes) {
     ESP_GUARD(engine);
     return engine->impl.load_tensor(name, type, data, nbytes);
+}
+int32_t esp_cuda_tp_unique_id(uint8_t* out, int32_t capacity) { return esp::tp_unique_id(out, capacity); }
+int32_t esp_cuda_tp_init(esp_cuda_engine* engine, const uint8_t* unique_id, int32_t nbytes) {
+    ESP_GUARD(engine);
+    return engine->impl.tp_init(unique_id, nbytes);
 }
 int32_t esp_cuda_finalize(esp_cuda_engine* engine) { ESP_GUARD(engine); return engine->impl.finalize(); }
 int32_t esp_cuda_destroy(esp_cuda_engine* engine) {

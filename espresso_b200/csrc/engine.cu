@@ -4,6 +4,8 @@
 #include "batch_kernels.cuh"
 #include "tc_gemm.cuh"
 
+#include <dlfcn.h>
+#include <nccl.h>
 #include <sys/stat.h>
 
 #include <algorithm>
@@ -255,11 +257,42 @@ static void raise_smem_limits(int device) {
 
 // ---------------------------------------------------------------------------------------------- engine
 
+// NCCL is looked up at run time (the library loads without it on single-GPU hosts).  When torch.distributed has
+// already brought up its bundled NCCL the soname resolves to that copy.
+struct NcclApi {
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    bool ok = false;
+};
+static NcclApi& nccl_api() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) return;
+        api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
+        api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+        api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(h, "ncclAllReduce"));
+        api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+        api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+        api.ok = api.GetUniqueId && api.CommInitRank && api.AllReduce && api.CommDestroy && api.GetErrorString;
+    });
+    return api;
+}
+static int32_t nccl_fail(ncclResult_t r, const char* what) {
+    NcclApi& api = nccl_api();
+    return fail(ESP_CUDA_ERR_NCCL, std::string(what) + ": " + (api.GetErrorString ? api.GetErrorString(r) : "NCCL error"));
+}
+
 Engine::Engine(const esp_cuda_config& cfg) : cfg_(cfg) {}
 
 Engine::~Engine() {
     if (cfg_.device >= 0) cudaSetDevice(cfg_.device);
     if (stream_) cudaStreamSynchronize(stream_);
+    if (nccl_comm_ && nccl_api().ok) nccl_api().CommDestroy(static_cast<ncclComm_t>(nccl_comm_));
     for (auto& g : graphs_) cudaGraphExecDestroy(g.second);
     for (auto e : prof_events_) cudaEventDestroy(e);
     if (ev_begin_) cudaEventDestroy(ev_begin_);
@@ -284,7 +317,12 @@ static int32_t validate_config(const esp_cuda_config& c) {
         return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "invalid config: head_dim must be a power of two in [8, 128]");
     if (c.d_model % 8 != 0 || c.hidden_dim % 8 != 0)
         return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "invalid config: d_model and hidden_dim must be multiples of 8");
-    if (c.tp_size > 1) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "tensor parallel engines are created through esp_cuda_create_tp");
+    if (c.tp_size > 1) {
+        if (c.tp_rank < 0 || c.tp_rank >= c.tp_size) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "invalid config: tp_rank out of range");
+        if (c.n_head % c.tp_size || c.n_kv_head % c.tp_size || c.hidden_dim % c.tp_size || c.vocab % c.tp_size)
+            return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "invalid config: heads, kv heads, hidden_dim and vocab must divide by tp_size");
+        if (c.architecture != ESP_CUDA_ARCH_LLAMA) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "tensor parallelism is implemented for llama models");
+    }
     return ESP_CUDA_OK;
 }
 
@@ -317,6 +355,12 @@ int32_t Engine::init() {
 
     m_.arch = cfg_.architecture; m_.n_layer = cfg_.n_layer; m_.n_head = cfg_.n_head; m_.n_kv_head = cfg_.n_kv_head;
     m_.d_model = cfg_.d_model; m_.head_dim = cfg_.head_dim; m_.hidden = cfg_.hidden_dim; m_.vocab = cfg_.vocab;
+    vocab_global_ = cfg_.vocab;
+    tp_size_ = std::max(cfg_.tp_size, 1);
+    tp_rank_ = tp_size_ > 1 ? cfg_.tp_rank : 0;
+    if (tp_size_ > 1) {  // this rank's shard: its heads, its slice of the FFN hidden units and of the vocabulary
+        m_.n_head /= tp_size_; m_.n_kv_head /= tp_size_; m_.hidden /= tp_size_; m_.vocab /= tp_size_;
+    }
     m_.max_seq = cfg_.max_seq; m_.q_dim = cfg_.n_head * cfg_.head_dim; m_.kv_dim = cfg_.n_kv_head * cfg_.head_dim;
     m_.n_seq = cfg_.max_batch; m_.eps = cfg_.norm_eps; m_.eos_token = cfg_.eos_token;
 
@@ -390,7 +434,7 @@ DeviceTensor* Engine::slot(const std::string& raw, int* rows, int* cols, bool* i
     *is_matrix = false;
     *is_embedding = false;
     auto set = [&](int r, int c) { *rows = r; *cols = c; return &tensors_[name]; };
-    if (name == "embeddings/token") { *is_embedding = true; return set(V, d); }
+    if (name == "embeddings/token") { *is_embedding = true; return set(vocab_global_, d); }
     if (name == "embeddings/position" && m_.arch == ARCH_GPT2) { *is_embedding = true; return set(m_.max_seq, d); }
     if (name == "lm_head") { *is_matrix = true; return set(V, d); }
     if (name == "rms_final" && m_.arch == ARCH_LLAMA) return set(1, d);
@@ -559,6 +603,7 @@ int32_t Engine::load_directory(const char* dir_c) {
 
 int32_t Engine::finalize() {
     if (finalized_) return ESP_CUDA_OK;
+    if (tp_size_ > 1 && !nccl_comm_) return fail(ESP_CUDA_ERR_STATE, "finalize: call esp_cuda_tp_init on every rank first");
     auto need = [&](const std::string& n) { auto it = tensors_.find(n); return it != tensors_.end() && it->second.loaded; };
     std::vector<std::string> req = {"embeddings/token", "lm_head"};
     if (m_.arch == ARCH_GPT2) { req.push_back("embeddings/position"); req.push_back("final_norm_gamma"); req.push_back("final_norm_beta"); }
@@ -632,7 +677,8 @@ int32_t Engine::check_ready(const char* what) const {
 // One pass over the model for `rows` rows.  mode: STEP_FORWARD runs the layers on (tok, pos) of every active
 // row; STEP_HEAD runs final norm + LM head + argmax; STEP_FEEDBACK makes the head emit and feed back its token.
 int32_t Engine::launch_step(int rows, int mode, cudaStream_t s, bool profile) {
-    if (tc_ready_ && rows >= kTcMinRows) return launch_step_tc(rows, mode, s);
+    if (tp_size_ > 1 && !tc_ready_) return fail(ESP_CUDA_ERR_STATE, "tensor parallelism needs 16-bit weights with 64-aligned shard sizes");
+    if (tc_ready_ && (rows >= kTcMinRows || tp_size_ > 1)) return launch_step_tc(rows, mode, s);
     const bool gpt2 = m_.arch == ARCH_GPT2;
     const int cap = sm_count_ * 2;  // one wave: the stage kernels hold ~120 registers, two CTAs per SM
     int launches = 0;
@@ -816,9 +862,9 @@ int32_t Engine::feed_rows(int rows, const int* seq, const uint32_t* tok, bool wi
             os << "position " << pos[r] << " exceeds context " << m_.max_seq;
             return fail(ESP_CUDA_ERR_OUT_OF_RANGE, os.str());
         }
-        if (tok[r] >= (uint32_t)m_.vocab) {  // token guard, Engine.swift:687-689
+        if (tok[r] >= (uint32_t)vocab_global_) {  // token guard, Engine.swift:687-689
             std::ostringstream os;
-            os << "token " << tok[r] << " is outside vocab " << m_.vocab;
+            os << "token " << tok[r] << " is outside vocab " << vocab_global_;
             return fail(ESP_CUDA_ERR_OUT_OF_RANGE, os.str());
         }
     }
@@ -900,6 +946,7 @@ int32_t Engine::select_greedy(uint32_t* token) {
 int32_t Engine::get_logits(int32_t seq, float* out, int32_t vocab) {
     int32_t rc = check_ready("get_logits");
     if (rc) return rc;
+    if (tp_size_ > 1) return fail(ESP_CUDA_ERR_STATE, "get_logits: a tensor-parallel rank holds only its vocabulary shard");
     if (!out || vocab != m_.vocab) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "get_logits: output must hold exactly vocab floats");
     if (seq < 0 || seq >= m_.n_seq) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "sequence index out of range");
     int rows = seq + 1;
@@ -1019,7 +1066,7 @@ int32_t Engine::generate_batch(const uint32_t* prompts, int32_t n_seq, int32_t n
     }
     if (n_seq < 1 || n_seq > cfg_.max_batch) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "n_seq exceeds max_batch");
     for (int64_t i = 0; i < (int64_t)n_seq * n_prompt; i++)
-        if (prompts[i] >= (uint32_t)m_.vocab) return fail(ESP_CUDA_ERR_OUT_OF_RANGE, "prompt token outside vocab");
+        if (prompts[i] >= (uint32_t)vocab_global_) return fail(ESP_CUDA_ERR_OUT_OF_RANGE, "prompt token outside vocab");
     const int eff = std::min(max_tokens, m_.max_seq - n_prompt);
     if (result) { *result = esp_cuda_generation_result{}; result->prompt_tokens = n_prompt; }
     for (int s = 0; s < n_seq; s++) n_out[s] = 0;
@@ -1112,6 +1159,44 @@ int32_t Engine::decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, 
     return ESP_CUDA_OK;
 }
 
+// ---------------------------------------------------------------------------------------------- tensor parallelism
+
+int32_t tp_unique_id(uint8_t* out, int32_t capacity) {
+    NcclApi& api = nccl_api();
+    if (!api.ok) return fail(ESP_CUDA_ERR_NCCL, "libnccl.so.2 could not be loaded");
+    if (!out || capacity < (int32_t)sizeof(ncclUniqueId)) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "tp_unique_id: need 128 bytes");
+    ncclUniqueId id;
+    ncclResult_t r = api.GetUniqueId(&id);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclGetUniqueId");
+    memcpy(out, &id, sizeof id);
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::tp_init(const uint8_t* unique_id, int32_t nbytes) {
+    if (tp_size_ <= 1) return fail(ESP_CUDA_ERR_STATE, "tp_init: the engine was created with tp_size <= 1");
+    if (nccl_comm_) return fail(ESP_CUDA_ERR_STATE, "tp_init: already initialised");
+    NcclApi& api = nccl_api();
+    if (!api.ok) return fail(ESP_CUDA_ERR_NCCL, "libnccl.so.2 could not be loaded");
+    if (!unique_id || nbytes != (int32_t)sizeof(ncclUniqueId)) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "tp_init: the unique id is 128 bytes");
+    ESP_CUDA_TRY(cudaSetDevice(cfg_.device));
+    ncclUniqueId id;
+    memcpy(&id, unique_id, sizeof id);
+    ncclComm_t comm = nullptr;
+    ncclResult_t r = api.CommInitRank(&comm, tp_size_, id, tp_rank_);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclCommInitRank");
+    nccl_comm_ = comm;
+    return ESP_CUDA_OK;
+}
+
+// sum of fp32 vectors, or maximum of packed 64-bit argmax keys
+int32_t Engine::all_reduce(const void* send, void* recv, size_t count, bool sum_f32, cudaStream_t s) {
+    NcclApi& api = nccl_api();
+    ncclResult_t r = api.AllReduce(send, recv, count, sum_f32 ? ncclFloat32 : ncclUint64, sum_f32 ? ncclSum : ncclMax,
+                                   static_cast<ncclComm_t>(nccl_comm_), s);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclAllReduce");
+    return ESP_CUDA_OK;
+}
+
 // ---------------------------------------------------------------------------------------------- batched tensor-core path
 
 int32_t Engine::build_tc() {
@@ -1144,6 +1229,7 @@ int32_t Engine::build_tc() {
     if ((rc = dev_alloc(owned_, &vraw_, (size_t)max_rows_ * m_.kv_dim))) return rc;
     if ((rc = dev_alloc(owned_, &up_, (size_t)max_rows_ * m_.hidden))) return rc;
     if ((rc = dev_alloc(owned_, &d_tc_error_, 4))) return rc;
+    if (tp_size_ > 1 && (rc = dev_alloc(owned_, &tp_partial_, (size_t)max_rows_ * m_.d_model))) return rc;
     ESP_CUDA_TRY(cudaDeviceSynchronize());
     tc_ready_ = true;
     return ESP_CUDA_OK;
@@ -1190,10 +1276,23 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
         TcArgs a{};
         a.M = W.rows; a.K = W.cols; a.n_valid = rows; a.epilogue = epi; a.out = out; a.ldo = ldo; a.bias = bias; a.active = rs_.active;
         a.error = d_tc_error_; a.bf16 = tc_bf16_;
+        a.row_offset = epi == TC_HEAD ? tp_rank_ * m_.vocab : 0;
         if (epi == TC_HEAD) { a.best = rs_.best; a.logits = (cfg_.flags & ESP_CUDA_FLAG_KEEP_LOGITS) ? act_.logits : nullptr; }
         ESP_CUDA_TRY(tc_launch(tile, W.map, *mx, a, s));
         launches++;
         return ESP_CUDA_OK;
+    };
+    // hidden += W . x (+ bias).  Tensor parallel: W holds this rank's slice of the input dimension, so the product
+    // is a partial sum; rank 0's partial also carries the residual and the bias, and one all-reduce leaves the
+    // new residual stream on every rank.
+    auto project = [&](const DeviceTensor& W, const uint16_t* xbuf, const float* bias) -> int32_t {
+        if (tp_size_ <= 1) return gemm(W, xbuf, TC_RESIDUAL, act_.hidden, d, bias);
+        int32_t prc;
+        if (tp_rank_ == 0) {
+            ESP_CUDA_TRY(cudaMemcpyAsync(tp_partial_, act_.hidden, sizeof(float) * (size_t)rows * d, cudaMemcpyDeviceToDevice, s));
+            if ((prc = gemm(W, xbuf, TC_RESIDUAL, tp_partial_, d, bias))) return prc;
+        } else if ((prc = gemm(W, xbuf, TC_STORE, tp_partial_, d, nullptr))) return prc;
+        return all_reduce(tp_partial_, act_.hidden, (size_t)rows * d, true, s);
     };
     auto copy_dbg = [&](const float* src, int offset, int n) {
         if (dbg) { k_copy_debug<<<(n + 255) / 256, 256, 0, s>>>(src, dbg + offset, n); launches++; }
@@ -1219,7 +1318,7 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
             ESP_CUDA_TRY(launch_pdl(k_attention, dim3(m_.n_head, rows, n_splits_), dim3(kAttThreads), 0, s, aa));
             launches++;
             if ((rc = prep(act_.ctx, q, NORM_NONE, nullptr, nullptr, xh_q_, false))) return rc;
-            if ((rc = gemm(tensors_.at(pre + "wo"), xh_q_, TC_RESIDUAL, act_.hidden, d, lw.bo))) return rc;
+            if ((rc = project(tensors_.at(pre + "wo"), xh_q_, lw.bo))) return rc;
             if (cap) copy_dbg(act_.hidden, 2 * q + 2 * kv, d);
             if ((rc = prep(act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, lw.norm2_g, lw.norm2_b, xh_d_, false))) return rc;
             if ((rc = gemm(tensors_.at(pre + "w1"), xh_d_, TC_STORE, act_.act, h, lw.b1))) return rc;
@@ -1229,7 +1328,7 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
             ac.debug = cap ? dbg + 2 * q + 2 * kv + d : nullptr;
             k_act_rows<<<dim3((h + kThreads - 1) / kThreads, rows), kThreads, 0, s>>>(ac);
             launches++;
-            if ((rc = gemm(tensors_.at(pre + "w2"), xh_h_, TC_RESIDUAL, act_.hidden, d, lw.b2))) return rc;
+            if ((rc = project(tensors_.at(pre + "w2"), xh_h_, lw.b2))) return rc;
             if (cap) copy_dbg(act_.hidden, 2 * q + 2 * kv + d + h, d);
         }
     }
@@ -1239,6 +1338,8 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
         if ((rc = prep(act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, tensors_.at(gpt2 ? "final_norm_gamma" : "rms_final").f32,
                        gpt2 ? tensors_.at("final_norm_beta").f32 : nullptr, xh_d_, false))) return rc;
         if ((rc = gemm(tensors_.at("lm_head"), xh_d_, TC_HEAD, nullptr, 0, nullptr))) return rc;
+        if (tp_size_ > 1 && (rc = all_reduce(rs_.best, rs_.best, (size_t)rows, false, s))) return rc;  // max of (value, ~index) keys
+        fin.m.vocab = vocab_global_;
         fin.finalize_mode = ((mode & STEP_FEEDBACK) ? 1 : 0) | ((mode & STEP_FORWARD) ? 2 : 0);
         k_head_done<<<1, 256, 0, s>>>(fin);
         launches++;
@@ -1255,7 +1356,7 @@ static int pad128(long long v) { return (int)((v + 127) / 128 * 128); }
 
 int32_t Engine::build_mega() {
     mega_ready_ = false;
-    if (cfg_.flags & ESP_CUDA_FLAG_NO_MEGAKERNEL) return ESP_CUDA_OK;
+    if ((cfg_.flags & ESP_CUDA_FLAG_NO_MEGAKERNEL) || tp_size_ > 1) return ESP_CUDA_OK;
     if (m_.arch != ARCH_LLAMA || m_.eos_token >= 0) return ESP_CUDA_OK;
     if (m_.head_dim != 32 && m_.head_dim != 64 && m_.head_dim != 128) return ESP_CUDA_OK;
     if (m_.d_model > 4096 || m_.d_model % 8 || m_.n_head > sm_count_) return ESP_CUDA_OK;

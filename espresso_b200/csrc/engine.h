@@ -46,6 +46,7 @@ public:
     int32_t load_tensor(const char* name, int32_t type, const void* data, uint64_t nbytes);
     int32_t load_directory(const char* dir);
     int32_t finalize();
+    int32_t tp_init(const uint8_t* unique_id, int32_t nbytes);  // tensor parallel: joins the NCCL communicator (collective call)
 
     int32_t reset();
     int32_t prefill(const uint32_t* tokens, int32_t n);
@@ -89,6 +90,7 @@ private:
     int32_t launch_step(int rows, int mode, cudaStream_t s, bool profile);
     int32_t launch_step_tc(int rows, int mode, cudaStream_t s);  // batched path: tensor-core GEMMs + element-wise stages
     int32_t build_tc();
+    int32_t all_reduce(const void* send, void* recv, size_t count, bool sum_f32, cudaStream_t s);
     const CUtensorMap* activation_map(const uint16_t* buf, int K, int tile);
     int32_t feed_rows(int rows, const int* seq, const uint32_t* tok, bool with_head, uint32_t* next_out);
     Weight weight_of(const DeviceTensor& t) const;
@@ -128,6 +130,12 @@ private:
     std::map<int, int> launches_by_key_;
     std::vector<cudaEvent_t> prof_events_;
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
+
+    // tensor parallelism (Megatron column/row split, NCCL all-reduce after Wo and W2, max-reduce of the packed argmax)
+    int tp_rank_ = 0, tp_size_ = 1;
+    int vocab_global_ = 0;
+    void* nccl_comm_ = nullptr;
+    float* tp_partial_ = nullptr;  // [max_rows][d_model] partial projection before the all-reduce
 
     // batched tensor-core path (rows >= kTcMinRows, 16-bit weights)
     bool tc_ready_ = false;

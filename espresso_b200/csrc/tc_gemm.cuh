@@ -39,6 +39,7 @@ struct TcArgs {
     float* logits;              // TC_HEAD: optional [n][M] logits store, or null
     int* error;                 // set to non-zero when a wait gave up
     int bf16;                   // operand type: 0 = fp16, 1 = bf16
+    int row_offset;             // TC_HEAD: added to the row index (vocab shard of a tensor-parallel rank)
 };
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -183,7 +184,7 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
                 if (a.epilogue == TC_HEAD) {
                     // first-max over the 32 rows of this warp, then one packed atomicMax per batch row
                     float bv = row_ok ? v : -INFINITY;
-                    int bi = row_ok ? m : 0x7fffffff;
+                    int bi = row_ok ? m + a.row_offset : 0x7fffffff;
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) {
                         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);

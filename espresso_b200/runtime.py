@@ -72,6 +72,8 @@ SIGNATURES = {
     "esp_cuda_create": (C.c_int32, [C.POINTER(EspCudaConfig), C.c_char_p, C.POINTER(_vp)]),
     "esp_cuda_create_from_directory": (C.c_int32, [C.c_char_p, C.c_int32, C.c_int32, C.c_uint32, C.POINTER(_vp)]),
     "esp_cuda_load_tensor": (C.c_int32, [_vp, C.c_char_p, C.c_int32, _vp, C.c_uint64]),
+    "esp_cuda_tp_unique_id": (C.c_int32, [C.POINTER(C.c_uint8), C.c_int32]),
+    "esp_cuda_tp_init": (C.c_int32, [_vp, C.POINTER(C.c_uint8), C.c_int32]),
     "esp_cuda_finalize": (C.c_int32, [_vp]),
     "esp_cuda_destroy": (C.c_int32, [_vp]),
     "esp_cuda_get_config": (C.c_int32, [_vp, C.POINTER(EspCudaConfig)]),
@@ -151,11 +153,12 @@ class GenerationResult:
     stoppedOnEOS: bool = False
 
 
-def make_c_config(cfg: MultiModelConfig, max_batch: int = 1, device: int = 0, flags: int = 0) -> EspCudaConfig:
+def make_c_config(cfg: MultiModelConfig, max_batch: int = 1, device: int = 0, flags: int = 0, tp_rank: int = 0,
+                  tp_size: int = 1) -> EspCudaConfig:
     return EspCudaConfig(
         1 if cfg.architecture == "gpt2" else 0, cfg.nLayer, cfg.nHead, cfg.nKVHead, cfg.dModel, cfg.headDim,
         cfg.hiddenDim, cfg.vocab, cfg.maxSeq, cfg.normEps, cfg.ropeTheta, -1 if cfg.eosToken is None else cfg.eosToken,
-        max_batch, device, 0, 1, flags)
+        max_batch, device, tp_rank, tp_size, flags)
 
 
 class DecodeEngine:
@@ -180,12 +183,16 @@ class DecodeEngine:
         return cls(out.value, config, max_batch)
 
     @classmethod
-    def empty(cls, config: MultiModelConfig, max_batch: int = 1, device: int = 0, flags: int = 0) -> "DecodeEngine":
-        """An engine whose tensors are uploaded with :meth:`load_tensor` and sealed with :meth:`finalize`."""
+    def empty(cls, config: MultiModelConfig, max_batch: int = 1, device: int = 0, flags: int = 0, tp_rank: int = 0,
+              tp_size: int = 1) -> "DecodeEngine":
+        """An engine whose tensors are uploaded with :meth:`load_tensor` and sealed with :meth:`finalize`.
+
+        With ``tp_size > 1`` this is one rank of a tensor-parallel group: upload the rank's Megatron shard
+        (see :func:`espresso_b200.sharding.tp_shard`) and call :meth:`tp_init` before :meth:`finalize`."""
         lib = load_library()
         config.validate()
         out = C.c_void_p()
-        cc = make_c_config(config, max_batch, device, flags)
+        cc = make_c_config(config, max_batch, device, flags, tp_rank, tp_size)
         _check(lib.esp_cuda_create(C.byref(cc), None, C.byref(out)))
         return cls(out.value, config, max_batch)
 
@@ -198,6 +205,11 @@ class DecodeEngine:
             self._keep = arr
             ptr, nbytes = arr.ctypes.data, arr.nbytes
         _check(self._lib.esp_cuda_load_tensor(self._h, name.encode(), TENSOR_TYPES[kind], C.c_void_p(ptr), nbytes))
+
+    def tp_init(self, unique_id: bytes) -> None:
+        """Join the NCCL communicator of the tensor-parallel group (collective: every rank calls it)."""
+        buf = (C.c_uint8 * len(unique_id)).from_buffer_copy(unique_id)
+        _check(self._lib.esp_cuda_tp_init(self._h, buf, len(unique_id)))
 
     def finalize(self) -> None:
         _check(self._lib.esp_cuda_finalize(self._h))
@@ -340,6 +352,13 @@ class DecodeEngine:
         out = np.empty(sizes[stage], np.float32)
         _check(self._lib.esp_cuda_debug_dump(self._h, stage, out.ctypes.data_as(_f32p), out.size))
         return out
+
+
+def tp_unique_id() -> bytes:
+    """A fresh NCCL unique id (rank 0 creates it and shares the bytes with the other ranks)."""
+    buf = (C.c_uint8 * 128)()
+    _check(load_library().esp_cuda_tp_unique_id(buf, 128))
+    return bytes(buf)
 
 
 def set_force_failure(enabled: bool) -> None:

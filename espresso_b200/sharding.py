@@ -52,3 +52,31 @@ def gather_token_streams(local: Sequence[np.ndarray], n_total: int, rank: int, w
             n = int(g[i, 0])
             out.append(g[i, 1:1 + n].astype(np.uint32))
     return out
+
+
+# ---- tensor parallelism: which slice of each tensor a rank holds -------------------------------------------------
+
+_ROW_SPLIT = ("wq", "wk", "wv", "w1", "w3", "lm_head", "bq", "bk", "bv", "b1")   # split along the output dimension
+_COL_SPLIT = ("wo", "w2")                                                          # split along the input dimension
+
+
+def tp_shard(name: str, tensor, rank: int, world: int):
+    """Megatron shard of one tensor for ``rank`` of ``world`` (works on numpy arrays and torch tensors).
+
+    Matrices whose rows are per-head or per-hidden-unit outputs (wq, wk, wv, w1, w3, lm_head and their biases) are
+    split by rows; wo and w2 consume those outputs and are split by columns; embeddings, norm gains and the
+    output-side biases (bo, b2: added once, by rank 0) stay whole."""
+    if world <= 1:
+        return tensor
+    leaf = name.rsplit("/", 1)[-1]
+    if leaf in _ROW_SPLIT:
+        b, e = shard_range(tensor.shape[0], rank, world)
+        if tensor.shape[0] % world:
+            raise ValueError(f"{name}: {tensor.shape[0]} rows do not divide by {world}")
+        return tensor[b:e]
+    if leaf in _COL_SPLIT:
+        if tensor.shape[1] % world:
+            raise ValueError(f"{name}: {tensor.shape[1]} columns do not divide by {world}")
+        b, e = shard_range(tensor.shape[1], rank, world)
+        return tensor[:, b:e]
+    return tensor

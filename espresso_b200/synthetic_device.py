@@ -47,8 +47,12 @@ def quantize_q4_0_torch(x: torch.Tensor) -> torch.Tensor:
 
 
 def upload_synthetic(engine, cfg: MultiModelConfig, kind: str = "f16", seed: int = 1234, quantise_head: bool = True,
-                     device: int = 0) -> None:
-    """Generate every tensor on ``cuda:device`` and upload it; ``kind``: f16 | bf16 | q8_0 | q4_0 for the matrices."""
+                     device: int = 0, tp_rank: int = 0, tp_size: int = 1) -> None:
+    """Generate every tensor on ``cuda:device`` and upload it; ``kind``: f16 | bf16 | q8_0 | q4_0 for the matrices.
+
+    With ``tp_size > 1`` every rank draws the full tensor from the same seed and uploads only its Megatron shard,
+    so the group holds exactly the model a single GPU would hold."""
+    from .sharding import tp_shard
     dev = torch.device("cuda", device)
     dense = torch.bfloat16 if kind == "bf16" else torch.float16
     dense_kind = "bf16" if kind == "bf16" else "f16"
@@ -63,6 +67,7 @@ def upload_synthetic(engine, cfg: MultiModelConfig, kind: str = "f16", seed: int
             g = torch.Generator(device=dev)
             g.manual_seed(_seed(seed, src))
             t = torch.randn(shape, dtype=torch.float32, device=dev, generator=g) * 0.02
+        t = tp_shard(name, t, tp_rank, tp_size).contiguous()
         if is_matrix(name) and kind in ("q8_0", "q4_0") and (leaf != "lm_head" or quantise_head):
             master = t.to(torch.float16).float().reshape(-1)
             blocks = quantize_q8_0_torch(master) if kind == "q8_0" else quantize_q4_0_torch(master)
