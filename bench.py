@@ -462,6 +462,8 @@ def main() -> None:
         if rank == 0 and not args.no_cpu_baseline:
             r = run_cpu_oracle(wl, args.cpu_steps, 1)
             line["cpu_baseline"] = {"value": r["value"], "unit": unit, "cores": r["cores"], "kind": "port", "sample": r["sample"]}
+        if world > 1:
+            dist.barrier()  # members of a tensor-parallel group tear their communicator down together
         eng.close()
         if draft is not None:
             draft.close()

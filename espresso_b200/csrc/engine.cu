@@ -292,8 +292,11 @@ Engine::Engine(const esp_cuda_config& cfg) : cfg_(cfg) {}
 Engine::~Engine() {
     if (cfg_.device >= 0) cudaSetDevice(cfg_.device);
     if (stream_) cudaStreamSynchronize(stream_);
-    if (nccl_comm_ && nccl_api().ok) nccl_api().CommDestroy(static_cast<ncclComm_t>(nccl_comm_));
-    for (auto& g : graphs_) cudaGraphExecDestroy(g.second);
+    for (auto& g : graphs_) cudaGraphExecDestroy(g.second);  // graphs hold captured collectives: they go first
+    if (nccl_comm_ && nccl_api().ok) {
+        cudaDeviceSynchronize();
+        nccl_api().CommDestroy(static_cast<ncclComm_t>(nccl_comm_));
+    }
     for (auto e : prof_events_) cudaEventDestroy(e);
     if (ev_begin_) cudaEventDestroy(ev_begin_);
     if (ev_end_) cudaEventDestroy(ev_end_);
@@ -360,8 +363,10 @@ int32_t Engine::init() {
     tp_rank_ = tp_size_ > 1 ? cfg_.tp_rank : 0;
     if (tp_size_ > 1) {  // this rank's shard: its heads, its slice of the FFN hidden units and of the vocabulary
         m_.n_head /= tp_size_; m_.n_kv_head /= tp_size_; m_.hidden /= tp_size_; m_.vocab /= tp_size_;
+        m_.q_dim = m_.n_head * m_.head_dim;
+        m_.kv_dim = m_.n_kv_head * m_.head_dim;
     }
-    m_.max_seq = cfg_.max_seq; m_.q_dim = cfg_.n_head * cfg_.head_dim; m_.kv_dim = cfg_.n_kv_head * cfg_.head_dim;
+    m_.max_seq = cfg_.max_seq; m_.q_dim = m_.n_head * m_.head_dim; m_.kv_dim = m_.n_kv_head * m_.head_dim;
     m_.n_seq = cfg_.max_batch; m_.eps = cfg_.norm_eps; m_.eos_token = cfg_.eos_token;
 
     max_rows_ = std::max(cfg_.max_batch, 64);  // rows of one pass: sequences of a batch, or positions of a prefill chunk

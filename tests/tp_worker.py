@@ -44,6 +44,7 @@ def main() -> None:
             compare_greedy_stream(oracle.Runtime(model), prompts[s], toks[s])
         compare_greedy_stream(oracle.Runtime(model), prompts[0], single)
         print(f"tensor parallel x{world} ok: {n_seq} streams match the oracle")
+    dist.barrier()  # the ranks leave together: a communicator is torn down by all of its members
     eng.close()
     dist.barrier()
     dist.destroy_process_group()
