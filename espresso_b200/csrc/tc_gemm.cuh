@@ -98,6 +98,16 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
     uint64_t* acc_ready = empty + STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
 
+    // which batch rows are written (live and active), fetched once: one 16-bit mask per group of 16 columns
+    __shared__ uint32_t s_live16[16];
+    if (threadIdx.x < 16) {
+        uint32_t mask = 0;
+        for (int j = 0; j < 16; j++) {
+            const int n = threadIdx.x * 16 + j;
+            if (n < N_TILE && n < a.n_valid && (!a.active || a.active[n])) mask |= 1u << j;
+        }
+        s_live16[threadIdx.x] = mask;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * kTcBlockM;
     const int num_kb = a.K / kTcBlockK;
@@ -165,38 +175,55 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
         const int m = m0 + lane_base + lane;
         const bool row_ok = ok && m < a.M;
         const float bias = (row_ok && a.bias) ? a.bias[m] : 0.f;
+        // kernel parameters used per column live in registers for the whole loop
+        const int epilogue = a.epilogue, ldo = a.ldo, M = a.M, row_offset = a.row_offset;
+        float* const out = a.out;
+        float* const logits = a.logits;
+        unsigned long long* const best = a.best;
 #pragma unroll 1
         for (int c0 = 0; c0 < N_TILE; c0 += 16) {
+            const uint32_t live = s_live16[c0 >> 4];  // bit j: batch row c0 + j is written (warp-uniform)
+            if (!live) continue;
             uint32_t r[16];
             const uint32_t taddr = tmem_acc + ((uint32_t)lane_base << 16) + (uint32_t)c0;
             asm volatile(
                 "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                : "r"(taddr));
+                : "r"(taddr)
+                : "memory");
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (epilogue == TC_HEAD) {
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const int n = c0 + j;
-                if (n >= a.n_valid) continue;               // warp-uniform
-                if (a.active && !a.active[n]) continue;      // warp-uniform
-                const float v = __uint_as_float(r[j]) + bias;
-                if (a.epilogue == TC_HEAD) {
+                for (int j = 0; j < 16; j++) {
+                    if (!((live >> j) & 1u)) continue;
+                    const int n = c0 + j;
+                    const float v = __uint_as_float(r[j]) + bias;
                     // first-max over the 32 rows of this warp, then one packed atomicMax per batch row
                     float bv = row_ok ? v : -INFINITY;
-                    int bi = row_ok ? m + a.row_offset : 0x7fffffff;
+                    int bi = row_ok ? m + row_offset : 0x7fffffff;
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) {
                         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
                         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
                         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
                     }
-                    if (lane == 0 && bi != 0x7fffffff) atomicMax(a.best + n, pack_best(bv, bi));
-                    if (a.logits && row_ok) a.logits[(size_t)n * a.M + m] = v;
-                } else if (row_ok) {
-                    float* o = a.out + (size_t)n * a.ldo + m;
-                    *o = a.epilogue == TC_RESIDUAL ? *o + v : v;
+                    if (lane == 0 && bi != 0x7fffffff) atomicMax(best + n, pack_best(bv, bi));
+                    if (logits && row_ok) logits[(size_t)n * M + m] = v;
                 }
+            } else if (row_ok) {
+                float* o = out + (size_t)c0 * ldo + m;
+                float prev[16];
+                if (epilogue == TC_RESIDUAL) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) prev[j] = ((live >> j) & 1u) ? o[(size_t)j * ldo] : 0.f;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) prev[j] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j++)
+                    if ((live >> j) & 1u) o[(size_t)j * ldo] = prev[j] + (__uint_as_float(r[j]) + bias);
             }
         }
     }
