@@ -3,7 +3,10 @@
 //   k_prep_rows    (embedding) -> RMSNorm / LayerNorm / none -> fp16 or bf16 operand rows
 //   k_rope_append  half-split RoPE on q (in place) and k, KV-cache append of k and v
 //   k_act_rows     SiLU(gate) * up  or  GELU(up)  -> 16-bit operand rows of the down projection
+//   k_attention_rows  attention for many rows at once: one warp per (row, head), 16-bit context rows out
 //   k_head_done    turns the packed per-row maxima of the LM-head GEMM into tokens (head_finalize)
+// Every kernel here is launched with programmatic stream serialization: it lets its successor start early and
+// waits for its predecessor before it touches global memory.
 // Reference arithmetic: see decode_kernels.cuh.
 #pragma once
 #include "decode_kernels.cuh"
@@ -29,13 +32,22 @@ struct PrepArgs {
     const float* b;
     uint16_t* dst;            // [rows][K] fp16/bf16
     int bf16;
+    float* zero[3];           // optional fp32 rows to clear ([rows][zero_n[i]]): outputs that K-sliced products add into
+    int zero_n[3];
 };
 
 // One CTA per row.
 __global__ void __launch_bounds__(kThreads) k_prep_rows(const PrepArgs p) {
     __shared__ float red[kRedFloats];
     const int r = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (!p.rs.active[r]) return;
+    for (int z = 0; z < 3; z++)
+        if (p.zero[z]) {
+            float* zr = p.zero[z] + (size_t)r * p.zero_n[z];
+            for (int k = threadIdx.x; k < p.zero_n[z]; k += kThreads) zr[k] = 0.f;
+        }
     const int K = p.K;
     const float* src = p.src ? p.src + (size_t)r * K : nullptr;
     const uint16_t* te = nullptr;
@@ -91,6 +103,8 @@ struct RopeArgs {
 // One CTA per row; threads stride over the rotation pairs of q and k and over the elements of v.
 __global__ void __launch_bounds__(kThreads) k_rope_append(const RopeArgs p) {
     const int r = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (!p.rs.active[r]) return;
     const ModelDims& m = p.m;
     const int pos = p.rs.pos[r], seq = p.rs.seq[r];
@@ -143,6 +157,8 @@ struct ActArgs {
 
 __global__ void __launch_bounds__(kThreads) k_act_rows(const ActArgs p) {
     const int r = blockIdx.y;
+    pdl_launch_dependents();
+    pdl_wait();
     if (!p.rs.active[r]) return;
     const int i = blockIdx.x * kThreads + threadIdx.x;
     if (i >= p.h) return;
@@ -152,7 +168,151 @@ __global__ void __launch_bounds__(kThreads) k_act_rows(const ActArgs p) {
     if (p.debug && r == 0) p.debug[i] = v;
 }
 
-__global__ void k_head_done(const GemvArgs p) { head_finalize(p); }
+__global__ void k_head_done(const GemvArgs p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    head_finalize(p);
+}
+
+struct AttRowsArgs {
+    ModelDims m;
+    RowState rs;
+    KvLayout kv;
+    const float* q;    // [rows][q_dim] fp32, RoPE applied
+    uint16_t* ctx16;   // [rows][q_dim] fp16/bf16: operand rows of the output projection
+    int bf16;
+    int layer;
+    int rows;
+    float* debug;      // optional fp32 capture of row 0's context (already offset), or null
+};
+
+constexpr int kAttRowsWarps = 4;
+
+__device__ __forceinline__ void halves16_to_float(const uint4& a, const uint4& b, float (&f)[16]) {
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+// Attention of one new token per row against its sequence's cache, for many rows: one warp per (row, head).
+// HD / 16 lanes share a cache position (16 channels each), so a warp covers 32 / (HD / 16) positions per pass and
+// every load instruction reads whole 128-byte (or longer) cache rows.  Each lane group keeps its own running
+// (max, sum, context) over the positions it visits; the groups are merged once at the end.  Softmax in fp32 as in
+// decodeContext (Sources/RealModelInference/RealModelInferenceEngine.swift:6560-6640), evaluated online.
+template <int HD>
+__global__ void __launch_bounds__(kAttRowsWarps * 32) k_attention_rows(const AttRowsArgs p) {
+    constexpr int LPP = HD / 16;   // lanes per position
+    constexpr int G = 32 / LPP;    // positions per pass of one warp
+    pdl_launch_dependents();
+    pdl_wait();
+    const ModelDims& m = p.m;
+    const int lane = threadIdx.x & 31;
+    const int w = blockIdx.x * kAttRowsWarps + (threadIdx.x >> 5);
+    if (w >= p.rows * m.n_head) return;
+    const int r = w / m.n_head, head = w - r * m.n_head;
+    if (!p.rs.active[r]) return;
+    const int sub = lane % LPP, slot = lane / LPP;
+    const int visible = p.rs.pos[r] + 1;
+    const int kvh = head / (m.n_head / m.n_kv_head);
+    const size_t base = p.kv.offset(m, p.layer, p.rs.seq[r], kvh, 0) + (size_t)sub * 16;
+    const __half* K = p.kv.k + base;
+    const __half* V = p.kv.v + base;
+    float q[16];
+    {
+        const float4* qp = reinterpret_cast<const float4*>(p.q + (size_t)r * m.q_dim + (size_t)head * HD + sub * 16);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float4 t = qp[i];
+            q[4 * i] = t.x; q[4 * i + 1] = t.y; q[4 * i + 2] = t.z; q[4 * i + 3] = t.w;
+        }
+    }
+    const float scale = 1.0f / sqrtf((float)HD);
+    float mx = -INFINITY, sum = 0.f, acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) acc[i] = 0.f;
+
+    auto load = [&](int t0, uint4 (&k)[2][2], uint4 (&v)[2][2]) {
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int t = t0 + u * G + slot;
+            if (t < visible) {
+                const uint4* kp = reinterpret_cast<const uint4*>(K + (size_t)t * HD);
+                const uint4* vp = reinterpret_cast<const uint4*>(V + (size_t)t * HD);
+                k[u][0] = __ldcg(kp); k[u][1] = __ldcg(kp + 1);
+                v[u][0] = __ldcg(vp); v[u][1] = __ldcg(vp + 1);
+            } else {
+                k[u][0] = k[u][1] = v[u][0] = v[u][1] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    auto compute = [&](int t0, const uint4 (&k)[2][2], const uint4 (&v)[2][2]) {
+        float s[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            float kf[16];
+            halves16_to_float(k[u][0], k[u][1], kf);
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; i++) d = fmaf(kf[i], q[i], d);
+#pragma unroll
+            for (int o = 1; o < LPP; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+            s[u] = (t0 + u * G + slot < visible) ? d * scale : -INFINITY;
+        }
+        const float mn = fmaxf(mx, fmaxf(s[0], s[1]));
+        if (mn == -INFINITY) return;  // nothing visible in this lane group yet
+        const float corr = expf(mx - mn);  // exp(-inf) = 0 on the first visit
+        const float p0 = expf(s[0] - mn), p1 = expf(s[1] - mn);
+        mx = mn;
+        sum = sum * corr + p0 + p1;
+        float v0[16], v1[16];
+        halves16_to_float(v[0][0], v[0][1], v0);
+        halves16_to_float(v[1][0], v[1][1], v1);
+#pragma unroll
+        for (int i = 0; i < 16; i++) acc[i] = fmaf(p1, v1[i], fmaf(p0, v0[i], acc[i] * corr));
+    };
+
+    uint4 ka[2][2], va[2][2], kb[2][2], vb[2][2];
+    load(0, ka, va);
+    for (int t0 = 0; t0 < visible; t0 += 4 * G) {
+        load(t0 + 2 * G, kb, vb);
+        compute(t0, ka, va);
+        load(t0 + 4 * G, ka, va);
+        compute(t0 + 2 * G, kb, vb);
+    }
+    // merge the lane groups
+#pragma unroll
+    for (int o = LPP; o < 32; o <<= 1) {
+        const float mo = __shfl_xor_sync(0xffffffffu, mx, o);
+        const float so = __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mn = fmaxf(mx, mo);
+        const float c1 = mx == -INFINITY ? 0.f : expf(mx - mn);
+        const float c2 = mo == -INFINITY ? 0.f : expf(mo - mn);
+        sum = sum * c1 + so * c2;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const float ao = __shfl_xor_sync(0xffffffffu, acc[i], o);
+            acc[i] = acc[i] * c1 + ao * c2;
+        }
+        mx = mn;
+    }
+    if (slot == 0) {
+        const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+        uint32_t packed[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float a0 = acc[2 * i] * inv, a1 = acc[2 * i + 1] * inv;
+            packed[i] = (uint32_t)to_16bit(a0, p.bf16) | ((uint32_t)to_16bit(a1, p.bf16) << 16);
+            if (p.debug && r == 0) { p.debug[head * HD + sub * 16 + 2 * i] = a0; p.debug[head * HD + sub * 16 + 2 * i + 1] = a1; }
+        }
+        uint4* dst = reinterpret_cast<uint4*>(p.ctx16 + (size_t)r * m.q_dim + (size_t)head * HD + sub * 16);
+        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    }
+}
 
 __global__ void k_copy_debug(const float* src, float* dst, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;

@@ -46,7 +46,8 @@ static int32_t fail(int32_t code, const std::string& msg) {
 
 int32_t tc_make_map(CUtensorMap* map, const void* base, bool bf16, uint64_t rows, uint64_t cols, uint32_t box_rows);
 int tc_tile_for(int rows);
-cudaError_t tc_launch(int tile, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, cudaStream_t s);
+TcPlan tc_plan(int m_tiles, int rows, int kb, bool may_split_k, int sms);
+cudaError_t tc_launch(const TcPlan& plan, bool dual, const CUtensorMap* const* mw, const CUtensorMap& mx, TcArgs a, cudaStream_t s);
 constexpr int kTcMinRows = 9;  // below this the row-batched GEMV stages are used
 
 // ---------------------------------------------------------------------------------------------- kernels
@@ -1255,12 +1256,12 @@ const CUtensorMap* Engine::activation_map(const uint16_t* buf, int K, int tile) 
 // streamed once per pass whatever the row count.
 int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
     const bool gpt2 = m_.arch == ARCH_GPT2;
-    const int tile = tc_tile_for(rows);
-    if (!tile) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "too many rows for one tensor-core pass");
+    if (!tc_tile_for(rows)) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "too many rows for one tensor-core pass");
     int launches = 0;
     float* dbg = debug_layer_ >= 0 ? d_debug_ : nullptr;
     const int q = m_.q_dim, kv = m_.kv_dim, d = m_.d_model, h = m_.hidden;
-    auto prep = [&](const float* src, int K, int norm, const float* g, const float* b, uint16_t* dst, bool from_emb) -> int32_t {
+    auto tiles_of = [](int M) { return (M + kTcBlockM - 1) / kTcBlockM; };
+    auto prep = [&](const float* src, int K, int norm, const float* g, const float* b, uint16_t* dst, bool from_emb, bool zero_qkv) -> int32_t {
         PrepArgs p{};
         p.m = m_; p.rs = rs_; p.src = src; p.hidden_out = act_.hidden; p.K = K; p.norm = norm; p.g = g; p.b = b; p.dst = dst; p.bf16 = tc_bf16_;
         p.from_embedding = from_emb ? 1 : 0;
@@ -1270,20 +1271,37 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
             p.pos_emb = gpt2 ? static_cast<const uint16_t*>(tensors_.at("embeddings/position").data) : nullptr;
             p.emb_type = te.type == ESP_CUDA_BF16 ? WT_BF16 : WT_F16;
         }
-        k_prep_rows<<<rows, kThreads, 0, s>>>(p);
+        if (zero_qkv) {
+            p.zero[0] = act_.q; p.zero_n[0] = q;
+            p.zero[1] = kraw_; p.zero_n[1] = kv;
+            p.zero[2] = vraw_; p.zero_n[2] = kv;
+        }
+        ESP_CUDA_TRY(launch_pdl(k_prep_rows, dim3(rows), dim3(kThreads), 0, s, p));
         launches++;
-        ESP_CUDA_TRY(cudaGetLastError());
         return ESP_CUDA_OK;
     };
-    auto gemm = [&](const DeviceTensor& W, const uint16_t* xbuf, int epi, float* out, int ldo, const float* bias) -> int32_t {
-        const CUtensorMap* mx = activation_map(xbuf, W.cols, tile);
-        if (!mx || !W.has_map) return fail(ESP_CUDA_ERR_CUDA, "tensor map missing for the batched path");
+    struct Part { const DeviceTensor* W; float* out; int ldo; const float* bias; };
+    // one launch over up to three weight matrices that read the same operand rows
+    auto gemm = [&](const TcPlan& plan, bool dual, std::initializer_list<Part> parts, const uint16_t* xbuf, int epi, uint16_t* out16, int ld16,
+                    float* capture) -> int32_t {
+        const int K = parts.begin()->W->cols;
+        const CUtensorMap* mx = activation_map(xbuf, K, plan.tile);
+        if (!mx) return fail(ESP_CUDA_ERR_CUDA, "tensor map missing for the batched path");
         TcArgs a{};
-        a.M = W.rows; a.K = W.cols; a.n_valid = rows; a.epilogue = epi; a.out = out; a.ldo = ldo; a.bias = bias; a.active = rs_.active;
-        a.error = d_tc_error_; a.bf16 = tc_bf16_;
+        const CUtensorMap* maps[3] = {&parts.begin()->W->map, &parts.begin()->W->map, &parts.begin()->W->map};
+        int g = 0;
+        for (const Part& pt : parts) {
+            if (!pt.W->has_map || pt.W->cols != K) return fail(ESP_CUDA_ERR_CUDA, "tensor map missing for the batched path");
+            maps[g] = &pt.W->map;
+            a.g[g].M = pt.W->rows; a.g[g].out = pt.out; a.g[g].ldo = pt.ldo; a.g[g].bias = pt.bias;
+            g++;
+        }
+        a.n_groups = dual ? 1 : g;
+        a.K = K; a.n_valid = rows; a.epilogue = epi; a.active = rs_.active; a.error = d_tc_error_; a.bf16 = tc_bf16_;
+        a.out16 = out16; a.ld16 = ld16; a.debug = capture;
         a.row_offset = epi == TC_HEAD ? tp_rank_ * m_.vocab : 0;
         if (epi == TC_HEAD) { a.best = rs_.best; a.logits = (cfg_.flags & ESP_CUDA_FLAG_KEEP_LOGITS) ? act_.logits : nullptr; }
-        ESP_CUDA_TRY(tc_launch(tile, W.map, *mx, a, s));
+        ESP_CUDA_TRY(tc_launch(plan, dual, maps, *mx, a, s));
         launches++;
         return ESP_CUDA_OK;
     };
@@ -1291,48 +1309,69 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
     // is a partial sum; rank 0's partial also carries the residual and the bias, and one all-reduce leaves the
     // new residual stream on every rank.
     auto project = [&](const DeviceTensor& W, const uint16_t* xbuf, const float* bias) -> int32_t {
-        if (tp_size_ <= 1) return gemm(W, xbuf, TC_RESIDUAL, act_.hidden, d, bias);
+        const TcPlan plan = tc_plan(tiles_of(W.rows), rows, W.cols / kTcBlockK, true, sm_count_);
+        if (tp_size_ <= 1) return gemm(plan, false, {{&W, act_.hidden, d, bias}}, xbuf, TC_RESIDUAL, nullptr, 0, nullptr);
         int32_t prc;
         if (tp_rank_ == 0) {
             ESP_CUDA_TRY(cudaMemcpyAsync(tp_partial_, act_.hidden, sizeof(float) * (size_t)rows * d, cudaMemcpyDeviceToDevice, s));
-            if ((prc = gemm(W, xbuf, TC_RESIDUAL, tp_partial_, d, bias))) return prc;
-        } else if ((prc = gemm(W, xbuf, TC_STORE, tp_partial_, d, nullptr))) return prc;
+            if ((prc = gemm(plan, false, {{&W, tp_partial_, d, bias}}, xbuf, TC_RESIDUAL, nullptr, 0, nullptr))) return prc;
+        } else {
+            if (plan.splits > 1) ESP_CUDA_TRY(cudaMemsetAsync(tp_partial_, 0, sizeof(float) * (size_t)rows * d, s));
+            if ((prc = gemm(plan, false, {{&W, tp_partial_, d, nullptr}}, xbuf, TC_STORE, nullptr, 0, nullptr))) return prc;
+        }
         return all_reduce(tp_partial_, act_.hidden, (size_t)rows * d, true, s);
     };
     auto copy_dbg = [&](const float* src, int offset, int n) {
         if (dbg) { k_copy_debug<<<(n + 255) / 256, 256, 0, s>>>(src, dbg + offset, n); launches++; }
     };
+    // many (row, head) pairs: one warp each; few rows with long contexts: the split-KV kernel of the GEMV path
+    const bool att_rows = (m_.head_dim == 32 || m_.head_dim == 64 || m_.head_dim == 128) && (long long)rows * m_.n_head >= 4LL * sm_count_;
     int32_t rc;
     if (mode & STEP_FORWARD) {
+        const TcPlan plan_qkv = tc_plan(tiles_of(q) + 2 * tiles_of(kv), rows, d / kTcBlockK, true, sm_count_);
+        const TcPlan plan_up = tc_plan(tiles_of(h), rows, d / kTcBlockK, false, sm_count_);
         for (int l = 0; l < m_.n_layer; l++) {
             const std::string pre = "layers/" + std::to_string(l) + "/";
             const LayerWeights lw = layer_weights(l);
             const bool cap = dbg && l == debug_layer_;
-            if ((rc = prep(l == 0 ? nullptr : act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, lw.norm1_g, lw.norm1_b, xh_d_, l == 0))) return rc;
-            if ((rc = gemm(tensors_.at(pre + "wq"), xh_d_, TC_STORE, act_.q, q, lw.bq))) return rc;
-            if ((rc = gemm(tensors_.at(pre + "wk"), xh_d_, TC_STORE, kraw_, kv, lw.bk))) return rc;
-            if ((rc = gemm(tensors_.at(pre + "wv"), xh_d_, TC_STORE, vraw_, kv, lw.bv))) return rc;
+            if ((rc = prep(l == 0 ? nullptr : act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, lw.norm1_g, lw.norm1_b, xh_d_, l == 0, plan_qkv.splits > 1)))
+                return rc;
+            if ((rc = gemm(plan_qkv, false,
+                           {{&tensors_.at(pre + "wq"), act_.q, q, lw.bq}, {&tensors_.at(pre + "wk"), kraw_, kv, lw.bk}, {&tensors_.at(pre + "wv"), vraw_, kv, lw.bv}},
+                           xh_d_, TC_STORE, nullptr, 0, nullptr)))
+                return rc;
             RopeArgs ra{};
             ra.m = m_; ra.rs = rs_; ra.kv = kv_; ra.q = act_.q; ra.k_raw = kraw_; ra.v_raw = vraw_; ra.rope = gpt2 ? nullptr : d_rope_; ra.layer = l;
             ra.debug = cap ? dbg : nullptr;
-            k_rope_append<<<rows, kThreads, 0, s>>>(ra);
+            ESP_CUDA_TRY(launch_pdl(k_rope_append, dim3(rows), dim3(kThreads), 0, s, ra));
             launches++;
-            AttArgs aa{};
-            aa.m = m_; aa.layer = l; aa.rows = rows; aa.n_splits = n_splits_; aa.rs = rs_; aa.a = act_; aa.kv = kv_;
-            aa.a.logits = nullptr; aa.a.debug = cap ? dbg : nullptr; aa.a.debug_layer = debug_layer_;
-            ESP_CUDA_TRY(launch_pdl(k_attention, dim3(m_.n_head, rows, n_splits_), dim3(kAttThreads), 0, s, aa));
-            launches++;
-            if ((rc = prep(act_.ctx, q, NORM_NONE, nullptr, nullptr, xh_q_, false))) return rc;
+            if (att_rows) {
+                AttRowsArgs ar{};
+                ar.m = m_; ar.rs = rs_; ar.kv = kv_; ar.q = act_.q; ar.ctx16 = xh_q_; ar.bf16 = tc_bf16_; ar.layer = l; ar.rows = rows;
+                ar.debug = cap ? dbg + q + 2 * kv : nullptr;
+                const dim3 grid((rows * m_.n_head + kAttRowsWarps - 1) / kAttRowsWarps);
+                if (m_.head_dim == 32) ESP_CUDA_TRY(launch_pdl(k_attention_rows<32>, grid, dim3(kAttRowsWarps * 32), 0, s, ar));
+                else if (m_.head_dim == 64) ESP_CUDA_TRY(launch_pdl(k_attention_rows<64>, grid, dim3(kAttRowsWarps * 32), 0, s, ar));
+                else ESP_CUDA_TRY(launch_pdl(k_attention_rows<128>, grid, dim3(kAttRowsWarps * 32), 0, s, ar));
+                launches++;
+            } else {
+                AttArgs aa{};
+                aa.m = m_; aa.layer = l; aa.rows = rows; aa.n_splits = n_splits_; aa.rs = rs_; aa.a = act_; aa.kv = kv_;
+                aa.a.logits = nullptr; aa.a.debug = cap ? dbg : nullptr; aa.a.debug_layer = debug_layer_;
+                ESP_CUDA_TRY(launch_pdl(k_attention, dim3(m_.n_head, rows, n_splits_), dim3(kAttThreads), 0, s, aa));
+                launches++;
+                if ((rc = prep(act_.ctx, q, NORM_NONE, nullptr, nullptr, xh_q_, false, false))) return rc;
+            }
             if ((rc = project(tensors_.at(pre + "wo"), xh_q_, lw.bo))) return rc;
             if (cap) copy_dbg(act_.hidden, 2 * q + 2 * kv, d);
-            if ((rc = prep(act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, lw.norm2_g, lw.norm2_b, xh_d_, false))) return rc;
-            if ((rc = gemm(tensors_.at(pre + "w1"), xh_d_, TC_STORE, act_.act, h, lw.b1))) return rc;
-            if (!gpt2 && (rc = gemm(tensors_.at(pre + "w3"), xh_d_, TC_STORE, up_, h, nullptr))) return rc;
-            ActArgs ac{};
-            ac.rs = rs_; ac.gate = act_.act; ac.up = gpt2 ? nullptr : up_; ac.dst = xh_h_; ac.h = h; ac.bf16 = tc_bf16_;
-            ac.debug = cap ? dbg + 2 * q + 2 * kv + d : nullptr;
-            k_act_rows<<<dim3((h + kThreads - 1) / kThreads, rows), kThreads, 0, s>>>(ac);
-            launches++;
+            if ((rc = prep(act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, lw.norm2_g, lw.norm2_b, xh_d_, false, false))) return rc;
+            // up projection with the activation in the epilogue: GELU(w1 x + b1), or SiLU(w1 x) * (w3 x) from two accumulators
+            float* capture = cap ? dbg + 2 * q + 2 * kv + d : nullptr;
+            if (gpt2) {
+                if ((rc = gemm(plan_up, false, {{&tensors_.at(pre + "w1"), nullptr, 0, lw.b1}}, xh_d_, TC_GELU16, xh_h_, h, capture))) return rc;
+            } else if ((rc = gemm(plan_up, true, {{&tensors_.at(pre + "w1"), nullptr, 0, nullptr}, {&tensors_.at(pre + "w3"), nullptr, 0, nullptr}}, xh_d_,
+                                  TC_SWIGLU16, xh_h_, h, capture)))
+                return rc;
             if ((rc = project(tensors_.at(pre + "w2"), xh_h_, lw.b2))) return rc;
             if (cap) copy_dbg(act_.hidden, 2 * q + 2 * kv + d + h, d);
         }
@@ -1341,12 +1380,14 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
     fin.m = m_; fin.rows = rows; fin.rs = rs_;
     if (mode & STEP_HEAD) {
         if ((rc = prep(act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, tensors_.at(gpt2 ? "final_norm_gamma" : "rms_final").f32,
-                       gpt2 ? tensors_.at("final_norm_beta").f32 : nullptr, xh_d_, false))) return rc;
-        if ((rc = gemm(tensors_.at("lm_head"), xh_d_, TC_HEAD, nullptr, 0, nullptr))) return rc;
+                       gpt2 ? tensors_.at("final_norm_beta").f32 : nullptr, xh_d_, false, false))) return rc;
+        const DeviceTensor& lh = tensors_.at("lm_head");
+        const TcPlan plan_head = tc_plan(tiles_of(lh.rows), rows, d / kTcBlockK, false, sm_count_);
+        if ((rc = gemm(plan_head, false, {{&lh, nullptr, 0, nullptr}}, xh_d_, TC_HEAD, nullptr, 0, nullptr))) return rc;
         if (tp_size_ > 1 && (rc = all_reduce(rs_.best, rs_.best, (size_t)rows, false, s))) return rc;  // max of (value, ~index) keys
         fin.m.vocab = vocab_global_;
         fin.finalize_mode = ((mode & STEP_FEEDBACK) ? 1 : 0) | ((mode & STEP_FORWARD) ? 2 : 0);
-        k_head_done<<<1, 256, 0, s>>>(fin);
+        ESP_CUDA_TRY(launch_pdl(k_head_done, dim3(1), dim3(256), 0, s, fin));
         launches++;
     } else if (mode & STEP_FORWARD) {
         ESP_CUDA_TRY(launch_pdl(k_bump, dim3(1), dim3(64), 0, s, rs_, rows));

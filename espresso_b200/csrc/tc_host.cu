@@ -48,30 +48,80 @@ int tc_tile_for(int rows) {
     return 0;
 }
 
-template <int N_TILE, int STAGES>
-static cudaError_t tc_launch_one(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, cudaStream_t s) {
+// Batch tile, batch tiles and K slices for a product with `m_tiles` 128-row weight tiles, `rows` batch rows and
+// `kb` 64-wide K blocks on `sms` SMs.  A large matrix keeps one wide batch tile (W is streamed once); a small one
+// is cut along the batch and then along K until the grid covers the SMs (a slice keeps at least 3 K blocks).
+TcPlan tc_plan(int m_tiles, int rows, int kb, bool may_split_k, int sms) {
+    TcPlan p;
+    p.tile = tc_tile_for(rows);
+    p.n_tiles = 1;
+    while (p.tile > 64 && m_tiles * p.n_tiles * 2 <= sms) {
+        p.tile /= 2;
+        p.n_tiles = (rows + p.tile - 1) / p.tile;
+    }
+    p.splits = 1;
+    if (may_split_k) {
+        const int ctas = m_tiles * p.n_tiles;
+        int want = std::max(1, std::min(sms / std::max(1, ctas), kb / 3));
+        p.kb_per_split = (kb + want - 1) / want;
+        p.splits = (kb + p.kb_per_split - 1) / p.kb_per_split;
+    } else {
+        p.kb_per_split = kb;
+    }
+    return p;
+}
+
+template <int N_TILE, bool DUAL>
+static cudaError_t tc_launch_one(const TcPlan& plan, const CUtensorMap* const* mw, const CUtensorMap& mx, const TcArgs& a, int m_tiles, cudaStream_t s) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    constexpr size_t smem = tc_smem_bytes<N_TILE, STAGES>();
+    constexpr size_t smem = TcShape<N_TILE, DUAL>::SMEM;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<N_TILE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<N_TILE, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    const int grid = (a.M + kTcBlockM - 1) / kTcBlockM;
-    k_gemm_tc<N_TILE, STAGES><<<grid, kTcThreads, smem, s>>>(mw, mx, a);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(m_tiles, plan.n_tiles, plan.splits);
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, k_gemm_tc<N_TILE, DUAL>, *mw[0], *mw[1], *mw[2], mx, a);
 }
 
-// map_x must have been built with box_rows == tile.
-cudaError_t tc_launch(int tile, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, cudaStream_t s) {
-    switch (tile) {
-        case 16: return tc_launch_one<16, 6>(mw, mx, a, s);
-        case 32: return tc_launch_one<32, 6>(mw, mx, a, s);
-        case 64: return tc_launch_one<64, 6>(mw, mx, a, s);
-        case 128: return tc_launch_one<128, 5>(mw, mx, a, s);
-        case 256: return tc_launch_one<256, 4>(mw, mx, a, s);
+// mw: the weight maps of the group (unused slots repeat slot 0); map_x must have been built with box_rows == plan.tile.
+// The argument block's tile0, kb_per_split and atomic_out are filled in here.
+cudaError_t tc_launch(const TcPlan& plan, bool dual, const CUtensorMap* const* mw, const CUtensorMap& mx, TcArgs a, cudaStream_t s) {
+    int m_tiles = 0;
+    const int groups = dual ? 1 : a.n_groups;
+    for (int g = 0; g < groups; g++) {
+        a.g[g].tile0 = m_tiles;
+        m_tiles += (a.g[g].M + kTcBlockM - 1) / kTcBlockM;
+    }
+    a.kb_per_split = plan.kb_per_split;
+    a.atomic_out = plan.splits > 1 ? 1 : 0;
+    if (dual) {
+        switch (plan.tile) {
+            case 16: return tc_launch_one<16, true>(plan, mw, mx, a, m_tiles, s);
+            case 32: return tc_launch_one<32, true>(plan, mw, mx, a, m_tiles, s);
+            case 64: return tc_launch_one<64, true>(plan, mw, mx, a, m_tiles, s);
+            case 128: return tc_launch_one<128, true>(plan, mw, mx, a, m_tiles, s);
+            case 256: return tc_launch_one<256, true>(plan, mw, mx, a, m_tiles, s);
+        }
+        return cudaErrorInvalidValue;
+    }
+    switch (plan.tile) {
+        case 16: return tc_launch_one<16, false>(plan, mw, mx, a, m_tiles, s);
+        case 32: return tc_launch_one<32, false>(plan, mw, mx, a, m_tiles, s);
+        case 64: return tc_launch_one<64, false>(plan, mw, mx, a, m_tiles, s);
+        case 128: return tc_launch_one<128, false>(plan, mw, mx, a, m_tiles, s);
+        case 256: return tc_launch_one<256, false>(plan, mw, mx, a, m_tiles, s);
     }
     return cudaErrorInvalidValue;
 }
@@ -113,16 +163,30 @@ int32_t gemm_tc_bench(int32_t type, const void* w, int32_t M, int32_t K, const f
         CUtensorMap mw, mx;
         int32_t rc;
         if ((rc = tc_make_map(&mw, dw, type == WT_BF16, M, K, kTcBlockM))) return rc;
-        if ((rc = tc_make_map(&mx, dx16, type == WT_BF16, tile, K, tile))) return rc;
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        // the plan the decode engine would use for a product of this shape (K slices add into a zeroed output)
+        const TcPlan plan = tc_plan((M + kTcBlockM - 1) / kTcBlockM, N, K / kTcBlockK, true, sms);
+        if ((rc = tc_make_map(&mx, dx16, type == WT_BF16, tile, K, plan.tile))) return rc;
+        const CUtensorMap* maps[3] = {&mw, &mw, &mw};
         TcArgs a{};
-        a.M = M; a.K = K; a.n_valid = N; a.epilogue = TC_STORE; a.out = dy; a.ldo = M; a.error = derr; a.bf16 = type == WT_BF16;
-        for (int i = 0; i < warmup; i++) ESP_CUDA_TRY(tc_launch(tile, mw, mx, a, nullptr));
+        a.n_groups = 1;
+        a.g[0].M = M; a.g[0].out = dy; a.g[0].ldo = M;
+        a.K = K; a.n_valid = N; a.epilogue = TC_STORE; a.error = derr; a.bf16 = type == WT_BF16;
+        auto launch = [&]() -> cudaError_t {
+            if (plan.splits > 1) {
+                cudaError_t e = cudaMemsetAsync(dy, 0, sizeof(float) * (size_t)N * M, nullptr);
+                if (e != cudaSuccess) return e;
+            }
+            return tc_launch(plan, false, maps, mx, a, nullptr);
+        };
+        for (int i = 0; i < warmup; i++) ESP_CUDA_TRY(launch());
         cudaEvent_t e0, e1;
         ESP_CUDA_TRY(cudaEventCreate(&e0));
         ESP_CUDA_TRY(cudaEventCreate(&e1));
         ESP_CUDA_TRY(cudaDeviceSynchronize());
         ESP_CUDA_TRY(cudaEventRecord(e0));
-        for (int i = 0; i < iterations; i++) ESP_CUDA_TRY(tc_launch(tile, mw, mx, a, nullptr));
+        for (int i = 0; i < iterations; i++) ESP_CUDA_TRY(launch());
         ESP_CUDA_TRY(cudaEventRecord(e1));
         cudaError_t e = cudaEventSynchronize(e1);
         float total = 0.f;
