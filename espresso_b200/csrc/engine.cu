@@ -179,6 +179,27 @@ __global__ void k_f32_to_f16(const float* src, int64_t n, __half* dst) {
     if (i < n) dst[i] = __float2half_rn(src[i]);
 }
 
+// Split-layout Q8_0 / Q4_0 matrix -> fp16(d * q): the operand of the tensor-core path for batches.
+__global__ void k_expand_quant(const void* __restrict__ q, const __half* __restrict__ scales, int type, int64_t n_blocks, __half* out) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 elements
+    const int64_t b = t >> 2;
+    const int part = (int)(t & 3);
+    if (b >= n_blocks) return;
+    const float d = __half2float(scales[b]);
+    __half o[8];
+    if (type == WT_Q8_0) {
+        const int8_t* s = static_cast<const int8_t*>(q) + b * 32 + part * 8;
+#pragma unroll
+        for (int i = 0; i < 8; i++) o[i] = __float2half_rn(d * (float)s[i]);
+    } else {
+        // elements 0..15 are the low nibbles of the block's 16 bytes, 16..31 the high nibbles
+        const uint8_t* s = static_cast<const uint8_t*>(q) + b * 16 + (part & 1) * 8;
+#pragma unroll
+        for (int i = 0; i < 8; i++) o[i] = __float2half_rn(d * (float)((int)((part & 2) ? (s[i] >> 4) : (s[i] & 15)) - 8));
+    }
+    *reinterpret_cast<uint4*>(out + b * 32 + part * 8) = *reinterpret_cast<const uint4*>(o);
+}
+
 // ---------------------------------------------------------------------------------------------- launch helpers
 
 template <typename Kern, typename... Args>
@@ -1210,19 +1231,33 @@ int32_t Engine::build_tc() {
     if (max_rows_ > 256) return ESP_CUDA_OK;
     if (m_.d_model % 64 || m_.q_dim % 64 || m_.hidden % 64) return ESP_CUDA_OK;
     const int t0 = tensors_.at("lm_head").type;
-    if (t0 != ESP_CUDA_F16 && t0 != ESP_CUDA_BF16) return ESP_CUDA_OK;
+    if (t0 != ESP_CUDA_F16 && t0 != ESP_CUDA_BF16 && t0 != ESP_CUDA_Q8_0 && t0 != ESP_CUDA_Q4_0) return ESP_CUDA_OK;
     std::vector<std::string> mats = {"lm_head"};
     for (int l = 0; l < m_.n_layer; l++)
         for (const char* n : {"wq", "wk", "wv", "wo", "w1", "w2", "w3"}) {
             if (m_.arch == ARCH_GPT2 && std::string(n) == "w3") continue;
             mats.push_back("layers/" + std::to_string(l) + "/" + n);
         }
-    for (auto& n : mats)
-        if (tensors_.at(n).type != t0) return ESP_CUDA_OK;
+    const bool quantised = t0 == ESP_CUDA_Q8_0 || t0 == ESP_CUDA_Q4_0;
+    for (auto& n : mats) {
+        const int t = tensors_.at(n).type;
+        if (quantised ? (t != ESP_CUDA_Q8_0 && t != ESP_CUDA_Q4_0) : t != t0) return ESP_CUDA_OK;
+    }
+    if (quantised && (cfg_.flags & ESP_CUDA_FLAG_NO_TC_SHADOW)) return ESP_CUDA_OK;
     tc_bf16_ = t0 == ESP_CUDA_BF16;
     for (auto& n : mats) {
         DeviceTensor& t = tensors_.at(n);
-        int32_t rc = tc_make_map(&t.map, t.data, tc_bf16_, t.rows, t.cols, kTcBlockM);
+        const void* base = t.data;
+        if (quantised) {
+            // batches multiply by an fp16 expansion of the quantised matrix; single rows keep reading the blocks
+            const int64_t nb = (int64_t)t.rows * t.cols / 32;
+            int32_t rc = dev_alloc(owned_, &t.shadow16, (size_t)t.rows * t.cols, false);
+            if (rc) return rc;
+            k_expand_quant<<<(unsigned)((nb * 4 + 255) / 256), 256, 0, stream_>>>(t.data, t.scales, t.type == ESP_CUDA_Q8_0 ? WT_Q8_0 : WT_Q4_0, nb, t.shadow16);
+            ESP_CUDA_TRY(cudaGetLastError());
+            base = t.shadow16;
+        }
+        int32_t rc = tc_make_map(&t.map, base, tc_bf16_, t.rows, t.cols, kTcBlockM);
         if (rc) return rc;
         t.has_map = true;
     }

@@ -29,6 +29,7 @@ struct DeviceTensor {
     bool loaded = false;
     CUtensorMap map{};          // TMA map of a 16-bit matrix for the tensor-core path (128-row boxes)
     bool has_map = false;
+    __half* shadow16 = nullptr; // fp16 expansion of a quantised matrix: what the tensor-core path multiplies by
 };
 
 struct Checkpoint {

@@ -31,6 +31,7 @@ TENSOR_TYPES = {"f32": F32, "f16": F16, "q4_0": Q4_0, "q8_0": Q8_0, "bf16": BF16
 FLAG_KEEP_LOGITS = 1
 FLAG_NO_GRAPH = 2
 FLAG_NO_MEGAKERNEL = 4
+FLAG_NO_TC_SHADOW = 8
 
 
 class RealModelInferenceError(RuntimeError):

@@ -75,6 +75,7 @@ typedef struct esp_cuda_config {
 #define ESP_CUDA_FLAG_KEEP_LOGITS 1u /* every step also stores the full fp32 logits (parity runs) */
 #define ESP_CUDA_FLAG_NO_GRAPH 2u    /* launch kernels directly instead of replaying a CUDA graph */
 #define ESP_CUDA_FLAG_NO_MEGAKERNEL 4u /* always use the per-stage kernels */
+#define ESP_CUDA_FLAG_NO_TC_SHADOW 8u  /* quantised models: keep no fp16 expansion, batches use the row-wise kernels */
 
 /* Result of a generate call: the numeric fields of GenerationResult (Engine.swift:17-55). */
 typedef struct esp_cuda_generation_result {

@@ -379,6 +379,30 @@ def test_quantised_llama_matches_oracle_on_dequantised_weights(rt, oracle_lib, k
     eng.close()
 
 
+@pytest.mark.parametrize("kind", ["q8_0", "q4_0"])
+def test_quantised_batch_uses_fp16_expansion_and_matches_oracle(rt, oracle_lib, kind):
+    """12 sequences of a quantised model decode on the tensor cores against the fp16 expansion of the blocks."""
+    from espresso_b200.model_config import MultiModelConfig
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = MultiModelConfig("tiny-gqa-qb", 2, 8, 2, 256, 32, 512, 640, 96, 1e-5, 10000.0, None, "llama")
+    model, uploads = quantised_pair(oracle_lib, cfg, kind)
+    n_seq = 12
+    prompts = np.stack([synthetic_prompt(cfg.vocab, 9, seed=5, stream=s) for s in range(n_seq)])
+    eng = rt.DecodeEngine.empty(cfg, max_batch=n_seq)
+    upload_all(eng, uploads)
+    toks, _ = eng.generate_batch(prompts, 16)
+    for s in range(n_seq):
+        compare_greedy_stream(oracle_lib.Runtime(model), prompts[s], toks[s])
+    eng.prefill_batch(prompts)
+    eng.decode_step_batch(prompts[:, 0])
+    for s in (0, 7, 11):
+        ora = oracle_lib.Runtime(model)
+        ora.prefill(list(prompts[s]) + [int(prompts[s, 0])])
+        assert_logits_close(eng.logits(s), ora.logits(), f"{kind} seq {s}")
+    eng.close()
+
+
 def test_long_context_split_kv_attention(rt, oracle_lib, tmp_models):
     """Positions beyond one attention split (256) exercise the split-KV merge."""
     from espresso_b200.model_config import MultiModelConfig
