@@ -36,7 +36,8 @@ struct PrepArgs {
     int zero_n[3];
 };
 
-// One CTA per row.
+// One CTA per row.  Rows of up to 8192 elements are held in registers (one global read, 16-byte accesses); longer
+// rows are re-read for every pass.
 __global__ void __launch_bounds__(kThreads) k_prep_rows(const PrepArgs p) {
     __shared__ float red[kRedFloats];
     const int r = blockIdx.x;
@@ -45,8 +46,8 @@ __global__ void __launch_bounds__(kThreads) k_prep_rows(const PrepArgs p) {
     if (!p.rs.active[r]) return;
     for (int z = 0; z < 3; z++)
         if (p.zero[z]) {
-            float* zr = p.zero[z] + (size_t)r * p.zero_n[z];
-            for (int k = threadIdx.x; k < p.zero_n[z]; k += kThreads) zr[k] = 0.f;
+            float4* zr = reinterpret_cast<float4*>(p.zero[z] + (size_t)r * p.zero_n[z]);  // row lengths are multiples of 16
+            for (int k = threadIdx.x; k < p.zero_n[z] / 4; k += kThreads) zr[k] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
     const int K = p.K;
     const float* src = p.src ? p.src + (size_t)r * K : nullptr;
@@ -55,6 +56,76 @@ __global__ void __launch_bounds__(kThreads) k_prep_rows(const PrepArgs p) {
     if (p.from_embedding) {
         te = p.tok_emb + (size_t)p.rs.tok[r] * K;
         if (p.pos_emb) pe = p.pos_emb + (size_t)p.rs.pos[r] * K;
+    }
+    uint16_t* dst = p.dst + (size_t)r * K;
+    constexpr int kVec = 8;  // float4 per thread held in registers
+    if (K % 4 == 0 && K / 4 <= kVec * kThreads) {
+        const int nvec = K / 4;
+        float4 v[kVec];
+#pragma unroll
+        for (int i = 0; i < kVec; i++) {
+            const int idx = threadIdx.x + i * kThreads;
+            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (idx < nvec) {
+                if (!p.from_embedding) {
+                    v[i] = reinterpret_cast<const float4*>(src)[idx];
+                } else {
+                    const uint2 t = reinterpret_cast<const uint2*>(te)[idx];
+                    v[i] = make_float4(emb_to_float((uint16_t)(t.x & 0xffffu), p.emb_type), emb_to_float((uint16_t)(t.x >> 16), p.emb_type),
+                                       emb_to_float((uint16_t)(t.y & 0xffffu), p.emb_type), emb_to_float((uint16_t)(t.y >> 16), p.emb_type));
+                    if (pe) {
+                        const uint2 u = reinterpret_cast<const uint2*>(pe)[idx];
+                        v[i].x += emb_to_float((uint16_t)(u.x & 0xffffu), p.emb_type);
+                        v[i].y += emb_to_float((uint16_t)(u.x >> 16), p.emb_type);
+                        v[i].z += emb_to_float((uint16_t)(u.y & 0xffffu), p.emb_type);
+                        v[i].w += emb_to_float((uint16_t)(u.y >> 16), p.emb_type);
+                    }
+                    reinterpret_cast<float4*>(p.hidden_out + (size_t)r * K)[idx] = v[i];
+                }
+            }
+        }
+        float inv = 1.f, mean = 0.f;
+        if (p.norm == NORM_RMS) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < kVec; i++) ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, ss))));
+            ss = block_sum(ss, red);
+            inv = 1.0f / sqrtf(ss / (float)K + p.m.eps);
+        } else if (p.norm == NORM_LAYER) {
+            float sm = 0.f;
+#pragma unroll
+            for (int i = 0; i < kVec; i++) sm += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+            mean = block_sum(sm, red) / (float)K;
+            float vs = 0.f;
+#pragma unroll
+            for (int i = 0; i < kVec; i++) {
+                if (threadIdx.x + i * kThreads < nvec) {
+                    const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+                    vs = fmaf(a, a, fmaf(b, b, fmaf(c, c, fmaf(d, d, vs))));
+                }
+            }
+            vs = block_sum(vs, red);
+            inv = 1.0f / sqrtf(vs / (float)K + p.m.eps);
+        }
+#pragma unroll
+        for (int i = 0; i < kVec; i++) {
+            const int idx = threadIdx.x + i * kThreads;
+            if (idx >= nvec) continue;
+            float4 o = v[i];
+            if (p.norm == NORM_RMS) {
+                const float4 g = reinterpret_cast<const float4*>(p.g)[idx];
+                o = make_float4((o.x * inv) * g.x, (o.y * inv) * g.y, (o.z * inv) * g.z, (o.w * inv) * g.w);
+            } else if (p.norm == NORM_LAYER) {
+                const float4 g = reinterpret_cast<const float4*>(p.g)[idx];
+                const float4 b = reinterpret_cast<const float4*>(p.b)[idx];
+                o = make_float4((o.x - mean) * inv * g.x + b.x, (o.y - mean) * inv * g.y + b.y, (o.z - mean) * inv * g.z + b.z,
+                                (o.w - mean) * inv * g.w + b.w);
+            }
+            reinterpret_cast<uint2*>(dst)[idx] =
+                make_uint2((uint32_t)to_16bit(o.x, p.bf16) | ((uint32_t)to_16bit(o.y, p.bf16) << 16),
+                           (uint32_t)to_16bit(o.z, p.bf16) | ((uint32_t)to_16bit(o.w, p.bf16) << 16));
+        }
+        return;
     }
     auto raw = [&](int k) {
         if (!p.from_embedding) return src[k];
@@ -77,7 +148,6 @@ __global__ void __launch_bounds__(kThreads) k_prep_rows(const PrepArgs p) {
         vs = block_sum(vs, red);
         inv = 1.0f / sqrtf(vs / (float)K + p.m.eps);
     }
-    uint16_t* dst = p.dst + (size_t)r * K;
     for (int k = threadIdx.x; k < K; k += kThreads) {
         const float x = raw(k);
         if (p.from_embedding) p.hidden_out[(size_t)r * K + k] = x;
@@ -100,24 +170,25 @@ struct RopeArgs {
     float* debug;        // optional capture of row 0 (q, k, v as stored)
 };
 
-// One CTA per row; threads stride over the rotation pairs of q and k and over the elements of v.
+// grid = (rows, chunks): one thread per rotation pair of q, per rotation pair of k, or per pair of v elements.
 __global__ void __launch_bounds__(kThreads) k_rope_append(const RopeArgs p) {
     const int r = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
     if (!p.rs.active[r]) return;
     const ModelDims& m = p.m;
-    const int pos = p.rs.pos[r], seq = p.rs.seq[r];
     const int half = m.head_dim / 2;
-    float* q = p.q + (size_t)r * m.q_dim;
-    const float* kr = p.k_raw + (size_t)r * m.kv_dim;
-    const float* vr = p.v_raw + (size_t)r * m.kv_dim;
     const int q_pairs = m.q_dim / 2, k_pairs = m.kv_dim / 2;
-    for (int i = threadIdx.x; i < q_pairs + k_pairs; i += kThreads) {
+    const int i = blockIdx.y * kThreads + threadIdx.x;
+    if (i >= q_pairs + 2 * k_pairs) return;
+    const int pos = p.rs.pos[r], seq = p.rs.seq[r];
+    if (i < q_pairs + k_pairs) {
         const bool is_q = i < q_pairs;
         const int local = is_q ? i : i - q_pairs;
         const int head = local / half, idx = local - head * half;
         const int i0 = head * m.head_dim + idx, i1 = i0 + half;
+        float* q = p.q + (size_t)r * m.q_dim;
+        const float* kr = p.k_raw + (size_t)r * m.kv_dim;
         float v0 = is_q ? q[i0] : kr[i0], v1 = is_q ? q[i1] : kr[i1];
         if (p.rope) {
             const float2 cs = p.rope[(size_t)pos * half + idx];
@@ -136,12 +207,16 @@ __global__ void __launch_bounds__(kThreads) k_rope_append(const RopeArgs p) {
                 p.debug[m.q_dim + i1] = __half2float(__float2half_rn(v1));
             }
         }
-    }
-    for (int i = threadIdx.x; i < m.kv_dim; i += kThreads) {
-        const int head = i / m.head_dim, idx = i - head * m.head_dim;
-        const __half hv = __float2half_rn(vr[i]);
-        p.kv.v[p.kv.offset(m, p.layer, seq, head, pos) + idx] = hv;
-        if (p.debug && r == 0) p.debug[m.q_dim + m.kv_dim + i] = __half2float(hv);
+    } else {
+        const int e = 2 * (i - q_pairs - k_pairs);  // head_dim is even: both elements belong to one head
+        const int head = e / m.head_dim, idx = e - head * m.head_dim;
+        const float2 vv = *reinterpret_cast<const float2*>(p.v_raw + (size_t)r * m.kv_dim + e);
+        const __half2 hv = __floats2half2_rn(vv.x, vv.y);
+        *reinterpret_cast<__half2*>(p.kv.v + p.kv.offset(m, p.layer, seq, head, pos) + idx) = hv;
+        if (p.debug && r == 0) {
+            p.debug[m.q_dim + m.kv_dim + e] = __low2float(hv);
+            p.debug[m.q_dim + m.kv_dim + e + 1] = __high2float(hv);
+        }
     }
 }
 

@@ -46,7 +46,7 @@ static int32_t fail(int32_t code, const std::string& msg) {
 
 int32_t tc_make_map(CUtensorMap* map, const void* base, bool bf16, uint64_t rows, uint64_t cols, uint32_t box_rows);
 int tc_tile_for(int rows);
-TcPlan tc_plan(int m_tiles, int rows, int kb, bool may_split_k, int sms);
+TcPlan tc_plan(int w_tiles, int rows, int kb, bool may_split_k, bool dual, int sms);
 cudaError_t tc_launch(const TcPlan& plan, bool dual, const CUtensorMap* const* mw, const CUtensorMap& mx, TcArgs a, cudaStream_t s);
 constexpr int kTcMinRows = 9;  // below this the row-batched GEMV stages are used
 
@@ -1229,7 +1229,7 @@ int32_t Engine::all_reduce(const void* send, void* recv, size_t count, bool sum_
 int32_t Engine::build_tc() {
     tc_ready_ = false;
     if (max_rows_ > 256) return ESP_CUDA_OK;
-    if (m_.d_model % 64 || m_.q_dim % 64 || m_.hidden % 64) return ESP_CUDA_OK;
+    if (m_.d_model % 64 || m_.q_dim % 64 || m_.hidden % 64 || m_.kv_dim % 16) return ESP_CUDA_OK;
     const int t0 = tensors_.at("lm_head").type;
     if (t0 != ESP_CUDA_F16 && t0 != ESP_CUDA_BF16 && t0 != ESP_CUDA_Q8_0 && t0 != ESP_CUDA_Q4_0) return ESP_CUDA_OK;
     std::vector<std::string> mats = {"lm_head"};
@@ -1257,11 +1257,11 @@ int32_t Engine::build_tc() {
             ESP_CUDA_TRY(cudaGetLastError());
             base = t.shadow16;
         }
-        int32_t rc = tc_make_map(&t.map, base, tc_bf16_, t.rows, t.cols, kTcBlockM);
+        int32_t rc = tc_make_map(&t.map, base, tc_bf16_, t.rows, t.cols, kTcHalf);
         if (rc) return rc;
         t.has_map = true;
     }
-    tc_rows_alloc_ = tc_tile_for(max_rows_);
+    tc_rows_alloc_ = (max_rows_ + 15) / 16 * 16;
     int32_t rc;
     if ((rc = dev_alloc(owned_, &xh_d_, (size_t)tc_rows_alloc_ * m_.d_model))) return rc;
     if ((rc = dev_alloc(owned_, &xh_q_, (size_t)tc_rows_alloc_ * m_.q_dim))) return rc;
@@ -1295,7 +1295,7 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
     int launches = 0;
     float* dbg = debug_layer_ >= 0 ? d_debug_ : nullptr;
     const int q = m_.q_dim, kv = m_.kv_dim, d = m_.d_model, h = m_.hidden;
-    auto tiles_of = [](int M) { return (M + kTcBlockM - 1) / kTcBlockM; };
+    auto tiles_of = [](int M) { return (M + kTcHalf - 1) / kTcHalf; };
     auto prep = [&](const float* src, int K, int norm, const float* g, const float* b, uint16_t* dst, bool from_emb, bool zero_qkv) -> int32_t {
         PrepArgs p{};
         p.m = m_; p.rs = rs_; p.src = src; p.hidden_out = act_.hidden; p.K = K; p.norm = norm; p.g = g; p.b = b; p.dst = dst; p.bf16 = tc_bf16_;
@@ -1320,7 +1320,7 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
     auto gemm = [&](const TcPlan& plan, bool dual, std::initializer_list<Part> parts, const uint16_t* xbuf, int epi, uint16_t* out16, int ld16,
                     float* capture) -> int32_t {
         const int K = parts.begin()->W->cols;
-        const CUtensorMap* mx = activation_map(xbuf, K, plan.tile);
+        const CUtensorMap* mx = activation_map(xbuf, K, plan.x_rows);
         if (!mx) return fail(ESP_CUDA_ERR_CUDA, "tensor map missing for the batched path");
         TcArgs a{};
         const CUtensorMap* maps[3] = {&parts.begin()->W->map, &parts.begin()->W->map, &parts.begin()->W->map};
@@ -1344,7 +1344,7 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
     // is a partial sum; rank 0's partial also carries the residual and the bias, and one all-reduce leaves the
     // new residual stream on every rank.
     auto project = [&](const DeviceTensor& W, const uint16_t* xbuf, const float* bias) -> int32_t {
-        const TcPlan plan = tc_plan(tiles_of(W.rows), rows, W.cols / kTcBlockK, true, sm_count_);
+        const TcPlan plan = tc_plan(tiles_of(W.rows), rows, W.cols / kTcBlockK, true, false, sm_count_);
         if (tp_size_ <= 1) return gemm(plan, false, {{&W, act_.hidden, d, bias}}, xbuf, TC_RESIDUAL, nullptr, 0, nullptr);
         int32_t prc;
         if (tp_rank_ == 0) {
@@ -1363,8 +1363,8 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
     const bool att_rows = (m_.head_dim == 32 || m_.head_dim == 64 || m_.head_dim == 128) && (long long)rows * m_.n_head >= 4LL * sm_count_;
     int32_t rc;
     if (mode & STEP_FORWARD) {
-        const TcPlan plan_qkv = tc_plan(tiles_of(q) + 2 * tiles_of(kv), rows, d / kTcBlockK, true, sm_count_);
-        const TcPlan plan_up = tc_plan(tiles_of(h), rows, d / kTcBlockK, false, sm_count_);
+        const TcPlan plan_qkv = tc_plan(tiles_of(q) + 2 * tiles_of(kv), rows, d / kTcBlockK, true, false, sm_count_);
+        const TcPlan plan_up = tc_plan(tiles_of(h), rows, d / kTcBlockK, false, !gpt2, sm_count_);
         for (int l = 0; l < m_.n_layer; l++) {
             const std::string pre = "layers/" + std::to_string(l) + "/";
             const LayerWeights lw = layer_weights(l);
@@ -1378,7 +1378,7 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
             RopeArgs ra{};
             ra.m = m_; ra.rs = rs_; ra.kv = kv_; ra.q = act_.q; ra.k_raw = kraw_; ra.v_raw = vraw_; ra.rope = gpt2 ? nullptr : d_rope_; ra.layer = l;
             ra.debug = cap ? dbg : nullptr;
-            ESP_CUDA_TRY(launch_pdl(k_rope_append, dim3(rows), dim3(kThreads), 0, s, ra));
+            ESP_CUDA_TRY(launch_pdl(k_rope_append, dim3(rows, (q / 2 + kv + kThreads - 1) / kThreads), dim3(kThreads), 0, s, ra));
             launches++;
             if (att_rows) {
                 AttRowsArgs ar{};
@@ -1417,7 +1417,7 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
         if ((rc = prep(act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, tensors_.at(gpt2 ? "final_norm_gamma" : "rms_final").f32,
                        gpt2 ? tensors_.at("final_norm_beta").f32 : nullptr, xh_d_, false, false))) return rc;
         const DeviceTensor& lh = tensors_.at("lm_head");
-        const TcPlan plan_head = tc_plan(tiles_of(lh.rows), rows, d / kTcBlockK, false, sm_count_);
+        const TcPlan plan_head = tc_plan(tiles_of(lh.rows), rows, d / kTcBlockK, false, false, sm_count_);
         if ((rc = gemm(plan_head, false, {{&lh, nullptr, 0, nullptr}}, xh_d_, TC_HEAD, nullptr, 0, nullptr))) return rc;
         if (tp_size_ > 1 && (rc = all_reduce(rs_.best, rs_.best, (size_t)rows, false, s))) return rc;  // max of (value, ~index) keys
         fin.m.vocab = vocab_global_;

@@ -2,21 +2,25 @@
 // path: Y[n][m] = sum_k W[m][k] * X[n][k] for weight matrices W [M, K] (row-major, fp16 or bf16) and a batch of
 // activation rows X [N, K] (the same 16-bit type), N = 1..256 rows.
 //
-// Mapping: the weight rows are the MMA's M dimension (128 per CTA), the batch is its N dimension, so with one
-// batch tile a CTA streams its 128 x K slice of W exactly once whatever the batch size.  Operands are staged in
-// shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast), the fp32 accumulator lives in
-// tensor memory (128 lanes x N columns) and is read back with tcgen05.ld for the epilogue.
+// Mapping: the batch rows are the MMA's M dimension (one tile of up to 128 rows, TMEM lanes), the weight rows
+// are its N dimension: a CTA owns 256 weight rows (two 128-row halves) and streams their K extent once.  One
+// tcgen05.mma was measured at ~148 cycles whatever its shape, so the widest instruction (128 x 256 x 16) moves
+// the most weight bytes per issue: 8 KB, about 55 bytes per cycle per SM, well above the SM's share of HBM.
+// Operands are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast); the fp32
+// accumulator (128 lanes x 256 columns) lives in tensor memory and is read back with tcgen05.ld.
 //
-// Grid: x = 128-row tiles of up to three weight matrices that share X (a "group": q, k and v projections run as one
-// launch), y = batch tiles, z = slices of K.  One MMA of 128 x N x 16 occupies the tensor pipe for about 128
-// cycles whatever N is (measured), so a small matrix only goes faster with more CTAs: the host splits the batch
-// and K until the grid covers the SMs.  K slices add their partial sums with fp32 atomics.
+// Grid: x = pairs of 128-row weight tiles, taken from up to three matrices that share X (a "group": the q, k and
+// v projections run as one launch), y = batch tiles of 128 rows, z = slices of K.  The two halves of a CTA are
+// independent (matrix, first row) pairs, so a pair may straddle two matrices.  A small matrix only goes faster
+// with more CTAs: the host cuts K (and uses single-half CTAs) until the grid covers the SMs; K slices add their
+// partial sums with fp32 vector atomics.
 //
-// DUAL: the CTA keeps two accumulators, gate (W of group 0) and up (W of group 1) for the same 128 rows, and its
+// DUAL (SwiGLU): half 0 holds 128 rows of the gate matrix, half 1 the same 128 rows of the up matrix, and the
 // epilogue writes silu(gate) * up as 16-bit rows: the operand of the down projection, without an fp32 round trip.
 //
 // Warp roles (192 threads): warp 0 allocates tensor memory and issues the TMA loads, warp 1 issues the MMAs
-// (one elected thread), warps 2..5 run the epilogue (a warp may only touch the TMEM lanes 32*(warp%4)..+31).
+// (one elected thread), warps 2..5 run the epilogue (a warp may only touch the TMEM lanes 32*(warp%4)..+31, i.e.
+// 32 batch rows; a thread owns one batch row and walks the weight rows, so its stores are 64-byte runs).
 // Every mbarrier wait is bounded; on a timeout the kernel records an error and unwinds normally.
 // Programmatic dependent launch: the weight tiles of the first pipeline stages are requested before the wait on
 // the previous kernel (weights never change); everything that depends on that kernel comes after the wait.
@@ -32,16 +36,22 @@
 namespace esp {
 
 constexpr int kTcThreads = 192;
-constexpr int kTcBlockM = 128;
-constexpr int kTcBlockK = 64;  // 64 x 16-bit = one 128-byte swizzle row
+constexpr int kTcHalf = 128;    // weight rows of one half tile (one TMA box)
+constexpr int kTcBatch = 128;   // batch rows of one batch tile (the MMA's M)
+constexpr int kTcBlockK = 64;   // 64 x 16-bit = one 128-byte swizzle row
+constexpr int kTcStages = 4;
 constexpr unsigned kTcSpinLimit = 1u << 22;
+constexpr int kTcXBytes = kTcBatch * kTcBlockK * 2;       // 16 KB slot of the activation tile
+constexpr int kTcHalfBytes = kTcHalf * kTcBlockK * 2;     // 16 KB per weight half
+constexpr int kTcStageBytes = kTcXBytes + 2 * kTcHalfBytes;
+constexpr size_t kTcSmemBytes = (size_t)kTcStages * kTcStageBytes + (2 * kTcStages + 1) * 8 + 16 + 1024;
 
 enum TcEpilogue { TC_STORE = 0, TC_RESIDUAL = 1, TC_HEAD = 2, TC_GELU16 = 3, TC_SWIGLU16 = 4 };
 constexpr int kTcMaxGroups = 3;
 
 struct TcGroup {
     int M;              // weight rows of this matrix
-    int tile0;          // first blockIdx.x of this matrix
+    int tile0;          // index of its first 128-row tile in the launch's tile list
     float* out;         // [n][ldo] fp32 (TC_STORE: overwritten, TC_RESIDUAL: accumulated into)
     int ldo;
     const float* bias;  // [M] or null
@@ -50,7 +60,11 @@ struct TcGroup {
 struct TcArgs {
     int n_groups;
     TcGroup g[kTcMaxGroups];
+    int n_tiles;                // 128-row weight tiles in the launch (all groups)
+    int halves;                 // weight tiles per CTA: 1 or 2 (DUAL: 2 = gate and up)
+    int dual;                   // SwiGLU pairing: half 0 from matrix 0, half 1 the same rows of matrix 1
     int K, n_valid;             // reduction length (multiple of 64), live batch rows
+    int x_rows;                 // rows of the activation TMA box (16, 32, 64 or 128)
     int epilogue;               // TcEpilogue
     int kb_per_split;           // 64-wide K blocks per grid.z slice
     int atomic_out;             // K is sliced: TC_STORE / TC_RESIDUAL add into out (TC_STORE: out is zero beforehand)
@@ -63,6 +77,15 @@ struct TcArgs {
     int* error;                 // set to non-zero when a wait gave up
     int bf16;                   // operand type: 0 = fp16, 1 = bf16
     int row_offset;             // TC_HEAD: added to the row index (vocab shard of a tensor-parallel rank)
+};
+
+// Launch shape chosen by the host.
+struct TcPlan {
+    int x_rows = 16;       // activation box rows
+    int n_tiles = 1;       // batch tiles (grid.y)
+    int halves = 2;        // weight tiles per CTA
+    int splits = 1;        // K slices (grid.z)
+    int kb_per_split = 1;
 };
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -84,14 +107,15 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(const void* smem_tile) 
     return d;
 }
 
-// Instruction descriptor of tcgen05.mma.kind::f16: fp32 accumulator, fp16 or bf16 operands, both K-major.
+// Instruction descriptor of tcgen05.mma.kind::f16: fp32 accumulator, fp16 or bf16 operands, both K-major,
+// M = 128 (batch rows), N = n (weight rows).
 __device__ __forceinline__ uint32_t umma_idesc_f16(int n, int bf16) {
     uint32_t d = 0;
     d |= 1u << 4;                        // accumulator format: f32
     d |= (uint32_t)(bf16 ? 1 : 0) << 7;  // A format
     d |= (uint32_t)(bf16 ? 1 : 0) << 10; // B format
     d |= (uint32_t)(n >> 3) << 17;       // N / 8
-    d |= (uint32_t)(kTcBlockM >> 4) << 24;  // M / 16
+    d |= (uint32_t)(kTcBatch >> 4) << 24;  // M / 16
     return d;
 }
 
@@ -106,22 +130,6 @@ __device__ __forceinline__ bool tc_wait(uint64_t* bar, unsigned parity, int* err
     return true;
 }
 
-// Launch shape chosen by the host: batch tile width, batch tiles (grid.y), K slices (grid.z).
-struct TcPlan {
-    int tile = 16, n_tiles = 1, splits = 1, kb_per_split = 1;
-};
-
-template <int N_TILE, bool DUAL>
-struct TcShape {
-    static constexpr int A_BYTES = kTcBlockM * kTcBlockK * 2 * (DUAL ? 2 : 1);
-    static constexpr int B_BYTES = N_TILE * kTcBlockK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + ((B_BYTES + 1023) / 1024) * 1024;
-    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 6 ? 6 : (200 * 1024 / STAGE_BYTES);
-    static constexpr int ACC_COLS = N_TILE * (DUAL ? 2 : 1);
-    static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;  // power of two >= 32 (N_TILE is 16/32/64/128/256)
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 1) * 8 + 16 + 1024;
-};
-
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -130,116 +138,124 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t 
         : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&f)[16]) {
+    uint32_t r[16];
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
           "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 16; j++) f[j] = __uint_as_float(r[j]);
 }
 
-// N_TILE: accumulator columns (batch rows of one batch tile): 16, 32, 64, 128 or 256.  DUAL doubles the columns
-// (two accumulators), up to the 512 columns of tensor memory.
-template <int N_TILE, bool DUAL>
+__device__ __forceinline__ uint32_t pack16x2(float a, float b, int bf16) {
+    const uint32_t lo = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(a)) : __half_as_ushort(__float2half_rn(a));
+    const uint32_t hi = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(b)) : __half_as_ushort(__float2half_rn(b));
+    return lo | (hi << 16);
+}
+
 __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
                                                         const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_x,
                                                         const TcArgs a) {
-    using S = TcShape<N_TILE, DUAL>;
-    constexpr int STAGES = S::STAGES;
-    constexpr int W_BYTES = kTcBlockM * kTcBlockK * 2;
     extern __shared__ __align__(1024) uint8_t tc_smem[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>(((uintptr_t)tc_smem + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * S::STAGE_BYTES);
-    uint64_t* empty = full + STAGES;
-    uint64_t* acc_ready = empty + STAGES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)kTcStages * kTcStageBytes);
+    uint64_t* empty = full + kTcStages;
+    uint64_t* acc_ready = empty + kTcStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
-    __shared__ uint32_t s_live16[16];  // bit j of word c: batch row n0 + 16 c + j is written (live and active)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // which matrix of the group this CTA works on
-    int gi = 0;
-    if (!DUAL) {
-        if (a.n_groups > 1 && (int)blockIdx.x >= a.g[1].tile0) gi = 1;
-        if (a.n_groups > 2 && (int)blockIdx.x >= a.g[2].tile0) gi = 2;
+    // The (matrix, first row) of this CTA's weight halves.  Group fields are selected with constant indices: a
+    // dynamically indexed parameter struct would be copied to local memory.
+#define ESP_TC_G(gi, field) ((gi) == 0 ? a.g[0].field : (gi) == 1 ? a.g[1].field : a.g[2].field)
+    int g_h0 = 0, g_h1 = 0, m0_h0 = 0, m0_h1 = 0;
+    int n_halves = 0;
+    if (a.dual) {
+        g_h1 = 1;
+        m0_h0 = m0_h1 = (int)blockIdx.x * kTcHalf;
+        n_halves = 2;
+    } else {
+        const int t0 = (int)blockIdx.x * a.halves;
+        if (t0 < a.n_tiles) {
+            if (a.n_groups > 1 && t0 >= a.g[1].tile0) g_h0 = 1;
+            if (a.n_groups > 2 && t0 >= a.g[2].tile0) g_h0 = 2;
+            m0_h0 = (t0 - ESP_TC_G(g_h0, tile0)) * kTcHalf;
+            n_halves = 1;
+        }
+        const int t1 = t0 + 1;
+        if (a.halves == 2 && t1 < a.n_tiles) {
+            if (a.n_groups > 1 && t1 >= a.g[1].tile0) g_h1 = 1;
+            if (a.n_groups > 2 && t1 >= a.g[2].tile0) g_h1 = 2;
+            m0_h1 = (t1 - ESP_TC_G(g_h1, tile0)) * kTcHalf;
+            n_halves = 2;
+        }
     }
-    const CUtensorMap* map_w = gi == 0 ? &map_w0 : gi == 1 ? &map_w1 : &map_w2;
-    // (selected with constant indices: a dynamically indexed parameter struct would be copied to local memory)
-#define ESP_TC_G(field) (gi == 0 ? a.g[0].field : gi == 1 ? a.g[1].field : a.g[2].field)
-    const int m0 = ((int)blockIdx.x - ESP_TC_G(tile0)) * kTcBlockM;
-    const int n0 = (int)blockIdx.y * N_TILE;
+    const CUtensorMap* const map_h0 = g_h0 == 0 ? &map_w0 : g_h0 == 1 ? &map_w1 : &map_w2;
+    const CUtensorMap* const map_h1 = g_h1 == 0 ? &map_w0 : g_h1 == 1 ? &map_w1 : &map_w2;
+    const int n0 = (int)blockIdx.y * kTcBatch;
     const int kb_total = a.K / kTcBlockK;
     const int kb0 = (int)blockIdx.z * a.kb_per_split;
-    const int num_kb = min(a.kb_per_split, kb_total - kb0);
+    const int num_kb = n_halves > 0 ? min(a.kb_per_split, kb_total - kb0) : 0;
+    const uint32_t stage_tx = (uint32_t)(a.x_rows * kTcBlockK * 2 + n_halves * kTcHalfBytes);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        for (int s = 0; s < kTcStages; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
         mbar_init(acc_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // weight tiles of the first stages do not depend on the previous kernel
-        const int pre = min(num_kb, STAGES);
+        const int pre = min(num_kb, kTcStages);
         for (int kb = 0; kb < pre; kb++) {
-            uint8_t* sa = tiles + (size_t)kb * S::STAGE_BYTES;
-            mbar_expect_tx(full + kb, S::A_BYTES + S::B_BYTES);
-            tma_load_2d(sa, map_w, (kb0 + kb) * kTcBlockK, m0, full + kb);
-            if (DUAL) tma_load_2d(sa + W_BYTES, &map_w1, (kb0 + kb) * kTcBlockK, m0, full + kb);
+            uint8_t* sw = tiles + (size_t)kb * kTcStageBytes + kTcXBytes;
+            mbar_expect_tx(full + kb, stage_tx);
+            tma_load_2d(sw, map_h0, (kb0 + kb) * kTcBlockK, m0_h0, full + kb);
+            if (n_halves == 2) tma_load_2d(sw + kTcHalfBytes, map_h1, (kb0 + kb) * kTcBlockK, m0_h1, full + kb);
         }
     }
     if (warp == 0) {  // the whole warp allocates the accumulator columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)S::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // The next kernel of the stream may be scheduled only after every CTA of this one holds its tensor memory:
     // a CTA of this kernel must never queue for columns behind a successor that is itself waiting for this kernel.
-    __syncthreads();
-    pdl_launch_dependents();
-    pdl_wait();
-    if (threadIdx.x >= 32 && threadIdx.x < 48) {
-        const int c = threadIdx.x - 32;
-        uint32_t mask = 0;
-        for (int j = 0; j < 16; j++) {
-            const int n = n0 + c * 16 + j;
-            if (c * 16 + j < N_TILE && n < a.n_valid && (!a.active || a.active[n])) mask |= 1u << j;
-        }
-        s_live16[c] = mask;
-    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t tmem_acc = *tmem_slot;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             for (int kb = 0; kb < num_kb; kb++) {
-                const int s = kb % STAGES;
-                uint8_t* sa = tiles + (size_t)s * S::STAGE_BYTES;
-                if (kb >= STAGES) {
-                    if (!tc_wait(empty + s, ((kb / STAGES) - 1) & 1, a.error)) break;
-                    mbar_expect_tx(full + s, S::A_BYTES + S::B_BYTES);
-                    tma_load_2d(sa, map_w, (kb0 + kb) * kTcBlockK, m0, full + s);
-                    if (DUAL) tma_load_2d(sa + W_BYTES, &map_w1, (kb0 + kb) * kTcBlockK, m0, full + s);
+                const int s = kb % kTcStages;
+                uint8_t* sx = tiles + (size_t)s * kTcStageBytes;
+                if (kb >= kTcStages) {
+                    if (!tc_wait(empty + s, ((kb / kTcStages) - 1) & 1, a.error)) break;
+                    mbar_expect_tx(full + s, stage_tx);
+                    tma_load_2d(sx + kTcXBytes, map_h0, (kb0 + kb) * kTcBlockK, m0_h0, full + s);
+                    if (n_halves == 2) tma_load_2d(sx + kTcXBytes + kTcHalfBytes, map_h1, (kb0 + kb) * kTcBlockK, m0_h1, full + s);
                 }
-                tma_load_2d(sa + S::A_BYTES, &map_x, (kb0 + kb) * kTcBlockK, n0, full + s);
+                tma_load_2d(sx, &map_x, (kb0 + kb) * kTcBlockK, n0, full + s);
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_f16(N_TILE, a.bf16);
+            const uint32_t idesc = umma_idesc_f16(n_halves * kTcHalf, a.bf16);
             for (int kb = 0; kb < num_kb; kb++) {
-                const int s = kb % STAGES;
-                if (!tc_wait(full + s, (kb / STAGES) & 1, a.error)) break;
+                const int s = kb % kTcStages;
+                if (!tc_wait(full + s, (kb / kTcStages) & 1, a.error)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint8_t* sa = tiles + (size_t)s * S::STAGE_BYTES;
-                const uint64_t da = umma_smem_desc_sw128(sa), db = umma_smem_desc_sw128(sa + S::A_BYTES);
-                const uint64_t da2 = DUAL ? umma_smem_desc_sw128(sa + W_BYTES) : 0;
+                const uint8_t* sx = tiles + (size_t)s * kTcStageBytes;
+                const uint64_t da = umma_smem_desc_sw128(sx), db = umma_smem_desc_sw128(sx + kTcXBytes);
 #pragma unroll
                 for (int k = 0; k < kTcBlockK / 16; k++) {
                     // advancing 16 elements along K inside the swizzled row = 32 bytes = 2 descriptor units
-                    const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-                    umma_f16(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, accumulate);
-                    if (DUAL) umma_f16(tmem_acc + (uint32_t)N_TILE, da2 + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, accumulate);
+                    umma_f16(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
                 }
                 // the stage may be refilled once these MMAs have read it
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(empty + s)) : "memory");
@@ -249,92 +265,121 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
         }
     } else {
         // ---------------- epilogue: TMEM -> registers -> global ----------------
+        const int lane_base = 32 * (warp & 3);
+        const int n = n0 + lane_base + lane;  // this thread's batch row
+        const bool warp_has_rows = n0 + lane_base < a.n_valid;
+        const bool live = n < a.n_valid && (!a.active || a.active[n]);
         const bool ok = tc_wait(acc_ready, 0, a.error) && __ldcg(a.error) == 0 && num_kb > 0;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int lane_base = 32 * (warp & 3);
-        const int m = m0 + lane_base + lane;
-        // kernel parameters used per column live in registers for the whole loop
-        const int epilogue = a.epilogue, M = ESP_TC_G(M), ldo = ESP_TC_G(ldo), row_offset = a.row_offset, ld16 = a.ld16, bf16 = a.bf16;
-        const bool atomic_out = a.atomic_out != 0;
-        const bool row_ok = ok && m < M;
-        const float* const bias_p = ESP_TC_G(bias);
-        const float bias = (row_ok && bias_p && blockIdx.z == 0) ? bias_p[m] : 0.f;
-        float* const out = ESP_TC_G(out);
-#undef ESP_TC_G
+        // kernel parameters used per column chunk live in registers for the whole loop
+        const int epilogue = a.epilogue, bf16 = a.bf16, ld16 = a.ld16, row_offset = a.row_offset;
+        const bool atomic_out = a.atomic_out != 0, first_split = blockIdx.z == 0;
         float* const logits = a.logits;
         float* const debug = a.debug;
         uint16_t* const out16 = a.out16;
-        unsigned long long* const best = a.best;
+        const uint32_t trow = tmem_acc + ((uint32_t)lane_base << 16);
+        if (ok && warp_has_rows) {
+            if (epilogue == TC_SWIGLU16) {
+                const int M = a.g[0].M;
 #pragma unroll 1
-        for (int c0 = 0; c0 < N_TILE; c0 += 16) {
-            const uint32_t live = s_live16[c0 >> 4];  // warp-uniform
-            if (!live) continue;
-            uint32_t r[16];
-            const uint32_t taddr = tmem_acc + ((uint32_t)lane_base << 16) + (uint32_t)c0;
-            tmem_ld16(taddr, r);
-            uint32_t r2[16];
-            if (DUAL) tmem_ld16(taddr + (uint32_t)N_TILE, r2);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            const int nb = n0 + c0;
-            if (epilogue == TC_HEAD) {
+                for (int c0 = 0; c0 < kTcHalf; c0 += 16) {
+                    if (m0_h0 + c0 >= M) break;
+                    float gt[16], up[16];
+                    tmem_ld16(trow + (uint32_t)c0, gt);
+                    tmem_ld16(trow + (uint32_t)(kTcHalf + c0), up);
+                    if (!live) continue;
+                    float v[16];
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    if (!((live >> j) & 1u)) continue;
-                    const int n = nb + j;
-                    const float v = __uint_as_float(r[j]) + bias;
-                    // first-max over the 32 rows of this warp, then one packed atomicMax per batch row
-                    float bv = row_ok ? v : -INFINITY;
-                    int bi = row_ok ? m + row_offset : 0x7fffffff;
+                    for (int j = 0; j < 16; j++) v[j] = silu_f(gt[j]) * up[j];
+                    uint4* o = reinterpret_cast<uint4*>(out16 + (size_t)n * ld16 + m0_h0 + c0);
+                    o[0] = make_uint4(pack16x2(v[0], v[1], bf16), pack16x2(v[2], v[3], bf16), pack16x2(v[4], v[5], bf16), pack16x2(v[6], v[7], bf16));
+                    o[1] = make_uint4(pack16x2(v[8], v[9], bf16), pack16x2(v[10], v[11], bf16), pack16x2(v[12], v[13], bf16), pack16x2(v[14], v[15], bf16));
+                    if (debug && n == 0) {
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-                    }
-                    if (lane == 0 && bi != 0x7fffffff) atomicMax(best + n, pack_best(bv, bi));
-                    if (logits && row_ok) logits[(size_t)n * M + m] = v;
-                }
-            } else if (epilogue == TC_GELU16 || epilogue == TC_SWIGLU16) {
-                if (row_ok) {
-                    uint16_t* o = out16 + (size_t)nb * ld16 + m;
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        if (!((live >> j) & 1u)) continue;
-                        float v;
-                        if (DUAL) v = silu_f(__uint_as_float(r[j])) * __uint_as_float(r2[j]);
-                        else v = gelu_f(__uint_as_float(r[j]) + bias);
-                        o[(size_t)j * ld16] = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
-                        if (debug && nb + j == 0) debug[m] = v;
+                        for (int j = 0; j < 16; j++) debug[m0_h0 + c0 + j] = v[j];
                     }
                 }
-            } else if (row_ok) {
-                float* o = out + (size_t)nb * ldo + m;
-                if (atomic_out) {
+            } else {
+                float bv = -INFINITY;
+                int bi = 0x7fffffff;
+#pragma unroll 1
+                for (int hh = 0; hh < n_halves; hh++) {
+                    const int gi = hh ? g_h1 : g_h0, m0 = hh ? m0_h1 : m0_h0;
+                    const int M = ESP_TC_G(gi, M), ldo = ESP_TC_G(gi, ldo);
+                    const float* const bias = first_split ? ESP_TC_G(gi, bias) : nullptr;
+                    float* const out = ESP_TC_G(gi, out);
+#pragma unroll 1
+                    for (int c0 = 0; c0 < kTcHalf; c0 += 16) {
+                        const int m = m0 + c0;
+                        if (m >= M) break;
+                        float v[16];
+                        tmem_ld16(trow + (uint32_t)(hh * kTcHalf + c0), v);
+                        if (!live) continue;
+                        const bool whole = m + 16 <= M;  // false only at a ragged vocabulary end
+                        if (bias) {
 #pragma unroll
-                    for (int j = 0; j < 16; j++)
-                        if ((live >> j) & 1u) atomicAdd(o + (size_t)j * ldo, __uint_as_float(r[j]) + bias);
-                } else {
-                    float prev[16];
-                    if (epilogue == TC_RESIDUAL) {
+                            for (int j = 0; j < 16; j++) v[j] += (whole || m + j < M) ? bias[m + j] : 0.f;
+                        }
+                        if (epilogue == TC_HEAD) {
+                            // first maximum over this thread's weight rows, ascending: a later equal value does not replace it
 #pragma unroll
-                        for (int j = 0; j < 16; j++) prev[j] = ((live >> j) & 1u) ? o[(size_t)j * ldo] : 0.f;
-                    } else {
+                            for (int j = 0; j < 16; j++)
+                                if ((whole || m + j < M) && v[j] > bv) { bv = v[j]; bi = m + j + row_offset; }
+                            if (logits) {
 #pragma unroll
-                        for (int j = 0; j < 16; j++) prev[j] = 0.f;
+                                for (int j = 0; j < 16; j++)
+                                    if (whole || m + j < M) logits[(size_t)n * M + m + j] = v[j];
+                            }
+                        } else if (epilogue == TC_GELU16) {
+                            float gl[16];
+#pragma unroll
+                            for (int j = 0; j < 16; j++) gl[j] = gelu_f(v[j]);
+                            uint4* o = reinterpret_cast<uint4*>(out16 + (size_t)n * ld16 + m);
+                            o[0] = make_uint4(pack16x2(gl[0], gl[1], bf16), pack16x2(gl[2], gl[3], bf16), pack16x2(gl[4], gl[5], bf16), pack16x2(gl[6], gl[7], bf16));
+                            o[1] = make_uint4(pack16x2(gl[8], gl[9], bf16), pack16x2(gl[10], gl[11], bf16), pack16x2(gl[12], gl[13], bf16), pack16x2(gl[14], gl[15], bf16));
+                            if (debug && n == 0) {
+#pragma unroll
+                                for (int j = 0; j < 16; j++) debug[m + j] = gl[j];
+                            }
+                        } else if (!whole || (ldo & 3)) {  // ragged end or unaligned rows: element by element
+                            float* o = out + (size_t)n * ldo + m;
+#pragma unroll
+                            for (int j = 0; j < 16; j++) {
+                                if (m + j >= M) continue;
+                                if (atomic_out) atomicAdd(o + j, v[j]);
+                                else o[j] = epilogue == TC_RESIDUAL ? o[j] + v[j] : v[j];
+                            }
+                        } else {
+                            float* o = out + (size_t)n * ldo + m;
+                            if (atomic_out) {
+#pragma unroll
+                                for (int j = 0; j < 16; j += 4) red_add_v4(o + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            } else if (epilogue == TC_RESIDUAL) {
+                                float4 prev[4];
+#pragma unroll
+                                for (int j = 0; j < 4; j++) prev[j] = reinterpret_cast<const float4*>(o)[j];
+#pragma unroll
+                                for (int j = 0; j < 4; j++)
+                                    reinterpret_cast<float4*>(o)[j] =
+                                        make_float4(prev[j].x + v[4 * j], prev[j].y + v[4 * j + 1], prev[j].z + v[4 * j + 2], prev[j].w + v[4 * j + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 4; j++) reinterpret_cast<float4*>(o)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                            }
+                        }
                     }
-#pragma unroll
-                    for (int j = 0; j < 16; j++)
-                        if ((live >> j) & 1u) o[(size_t)j * ldo] = prev[j] + (__uint_as_float(r[j]) + bias);
                 }
+                if (epilogue == TC_HEAD && live && bi != 0x7fffffff) atomicMax(a.best + n, pack_best(bv, bi));
             }
         }
     }
+#undef ESP_TC_G
     // tensor memory is released by the warp that allocated it, after everybody is done with it
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)S::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(256u) : "memory");
     }
 }
 

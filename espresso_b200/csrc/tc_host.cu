@@ -42,88 +42,73 @@ int32_t tc_make_map(CUtensorMap* map, const void* base, bool bf16, uint64_t rows
     return ESP_CUDA_OK;
 }
 
+// Rows of the activation TMA box for `rows` batch rows (one batch tile holds at most 128).
 int tc_tile_for(int rows) {
-    for (int t : {16, 32, 64, 128, 256})
+    if (rows > 2 * kTcBatch) return 0;
+    for (int t : {16, 32, 64, 128})
         if (rows <= t) return t;
-    return 0;
+    return 128;
 }
 
-// Batch tile, batch tiles and K slices for a product with `m_tiles` 128-row weight tiles, `rows` batch rows and
-// `kb` 64-wide K blocks on `sms` SMs.  A large matrix keeps one wide batch tile (W is streamed once); a small one
-// is cut along the batch and then along K until the grid covers the SMs (a slice keeps at least 3 K blocks).
-TcPlan tc_plan(int m_tiles, int rows, int kb, bool may_split_k, int sms) {
+// Launch shape for a product with `w_tiles` 128-row weight tiles, `rows` batch rows and `kb` 64-wide K blocks on
+// `sms` SMs.  A large matrix runs two weight tiles per CTA (256 weight rows per MMA) over all of K; a small one is
+// cut along K (a slice keeps at least 3 K blocks), and goes to one tile per CTA, until the grid covers the SMs.
+TcPlan tc_plan(int w_tiles, int rows, int kb, bool may_split_k, bool dual, int sms) {
     TcPlan p;
-    p.tile = tc_tile_for(rows);
-    p.n_tiles = 1;
-    while (p.tile > 64 && m_tiles * p.n_tiles * 2 <= sms) {
-        p.tile /= 2;
-        p.n_tiles = (rows + p.tile - 1) / p.tile;
-    }
-    p.splits = 1;
-    if (may_split_k) {
-        const int ctas = m_tiles * p.n_tiles;
-        int want = std::max(1, std::min(sms / std::max(1, ctas), kb / 3));
+    p.x_rows = tc_tile_for(std::min(rows, kTcBatch));
+    p.n_tiles = (rows + kTcBatch - 1) / kTcBatch;
+    auto shape = [&](int halves) {
+        p.halves = halves;
+        const int ctas = (dual ? w_tiles : (w_tiles + halves - 1) / halves) * p.n_tiles;
+        const int want = may_split_k ? std::max(1, std::min(sms / std::max(1, ctas), kb / 3)) : 1;
         p.kb_per_split = (kb + want - 1) / want;
         p.splits = (kb + p.kb_per_split - 1) / p.kb_per_split;
-    } else {
-        p.kb_per_split = kb;
-    }
+        return ctas * p.splits;
+    };
+    if (shape(2) * 2 <= sms && !dual) shape(1);
     return p;
 }
 
-template <int N_TILE, bool DUAL>
-static cudaError_t tc_launch_one(const TcPlan& plan, const CUtensorMap* const* mw, const CUtensorMap& mx, const TcArgs& a, int m_tiles, cudaStream_t s) {
+static cudaError_t tc_configure() {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    constexpr size_t smem = TcShape<N_TILE, DUAL>::SMEM;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<N_TILE, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
+    return cudaSuccess;
+}
+
+// mw: the weight maps of the group (unused slots repeat slot 0); map_x must have been built with box_rows ==
+// plan.x_rows.  The argument block's tile list, K slicing and box size are filled in here.
+cudaError_t tc_launch(const TcPlan& plan, bool dual, const CUtensorMap* const* mw, const CUtensorMap& mx, TcArgs a, cudaStream_t s) {
+    cudaError_t e = tc_configure();
+    if (e != cudaSuccess) return e;
+    int tiles = 0;
+    const int groups = dual ? 1 : a.n_groups;
+    for (int g = 0; g < groups; g++) {
+        a.g[g].tile0 = tiles;
+        tiles += (a.g[g].M + kTcHalf - 1) / kTcHalf;
+    }
+    a.n_tiles = tiles;
+    a.dual = dual ? 1 : 0;
+    a.halves = dual ? 2 : plan.halves;
+    a.x_rows = plan.x_rows;
+    a.kb_per_split = plan.kb_per_split;
+    a.atomic_out = plan.splits > 1 ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(m_tiles, plan.n_tiles, plan.splits);
+    cfg.gridDim = dim3(dual ? tiles : (tiles + a.halves - 1) / a.halves, plan.n_tiles, plan.splits);
     cfg.blockDim = dim3(kTcThreads);
-    cfg.dynamicSmemBytes = smem;
+    cfg.dynamicSmemBytes = kTcSmemBytes;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, k_gemm_tc<N_TILE, DUAL>, *mw[0], *mw[1], *mw[2], mx, a);
-}
-
-// mw: the weight maps of the group (unused slots repeat slot 0); map_x must have been built with box_rows == plan.tile.
-// The argument block's tile0, kb_per_split and atomic_out are filled in here.
-cudaError_t tc_launch(const TcPlan& plan, bool dual, const CUtensorMap* const* mw, const CUtensorMap& mx, TcArgs a, cudaStream_t s) {
-    int m_tiles = 0;
-    const int groups = dual ? 1 : a.n_groups;
-    for (int g = 0; g < groups; g++) {
-        a.g[g].tile0 = m_tiles;
-        m_tiles += (a.g[g].M + kTcBlockM - 1) / kTcBlockM;
-    }
-    a.kb_per_split = plan.kb_per_split;
-    a.atomic_out = plan.splits > 1 ? 1 : 0;
-    if (dual) {
-        switch (plan.tile) {
-            case 16: return tc_launch_one<16, true>(plan, mw, mx, a, m_tiles, s);
-            case 32: return tc_launch_one<32, true>(plan, mw, mx, a, m_tiles, s);
-            case 64: return tc_launch_one<64, true>(plan, mw, mx, a, m_tiles, s);
-            case 128: return tc_launch_one<128, true>(plan, mw, mx, a, m_tiles, s);
-            case 256: return tc_launch_one<256, true>(plan, mw, mx, a, m_tiles, s);
-        }
-        return cudaErrorInvalidValue;
-    }
-    switch (plan.tile) {
-        case 16: return tc_launch_one<16, false>(plan, mw, mx, a, m_tiles, s);
-        case 32: return tc_launch_one<32, false>(plan, mw, mx, a, m_tiles, s);
-        case 64: return tc_launch_one<64, false>(plan, mw, mx, a, m_tiles, s);
-        case 128: return tc_launch_one<128, false>(plan, mw, mx, a, m_tiles, s);
-        case 256: return tc_launch_one<256, false>(plan, mw, mx, a, m_tiles, s);
-    }
-    return cudaErrorInvalidValue;
+    return cudaLaunchKernelEx(&cfg, k_gemm_tc, *mw[0], *mw[1], *mw[2], mx, a);
 }
 
 __global__ void k_f32_to_16(const float* src, int64_t n, uint16_t* dst, int bf16) {
@@ -141,7 +126,7 @@ int32_t gemm_tc_bench(int32_t type, const void* w, int32_t M, int32_t K, const f
     if (type != WT_F16 && type != WT_BF16) return esp::fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "gemm_tc_bench: fp16 or bf16 weights only");
     if (force_failure_enabled()) return esp::fail(ESP_CUDA_ERR_FORCED_FAILURE, "forced failure is enabled");
     ESP_CUDA_TRY(cudaSetDevice(device));
-    const int tile = tc_tile_for(N);
+    const int alloc_rows = (N + 15) / 16 * 16;
     std::vector<void*> owned;
     auto cleanup = [&] { for (void* p : owned) cudaFree(p); };
     auto body = [&]() -> int32_t {
@@ -150,24 +135,24 @@ int32_t gemm_tc_bench(int32_t type, const void* w, int32_t M, int32_t K, const f
         int* derr = nullptr;
         ESP_CUDA_TRY(cudaMalloc(&dw, (size_t)M * K * 2)); owned.push_back(dw);
         ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&dx), sizeof(float) * (size_t)N * K)); owned.push_back(dx);
-        ESP_CUDA_TRY(cudaMalloc(&dx16, (size_t)tile * K * 2)); owned.push_back(dx16);
+        ESP_CUDA_TRY(cudaMalloc(&dx16, (size_t)alloc_rows * K * 2)); owned.push_back(dx16);
         ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&dy), sizeof(float) * (size_t)N * M)); owned.push_back(dy);
         ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&derr), sizeof(int))); owned.push_back(derr);
         ESP_CUDA_TRY(cudaMemcpy(dw, w, (size_t)M * K * 2, cudaMemcpyDefault));
         ESP_CUDA_TRY(cudaMemcpy(dx, x, sizeof(float) * (size_t)N * K, cudaMemcpyDefault));
-        ESP_CUDA_TRY(cudaMemset(dx16, 0, (size_t)tile * K * 2));
+        ESP_CUDA_TRY(cudaMemset(dx16, 0, (size_t)alloc_rows * K * 2));
         ESP_CUDA_TRY(cudaMemset(derr, 0, sizeof(int)));
         const int64_t nx = (int64_t)N * K;
         k_f32_to_16<<<(unsigned)((nx + 255) / 256), 256>>>(dx, nx, static_cast<uint16_t*>(dx16), type == WT_BF16);
         ESP_CUDA_TRY(cudaGetLastError());
         CUtensorMap mw, mx;
         int32_t rc;
-        if ((rc = tc_make_map(&mw, dw, type == WT_BF16, M, K, kTcBlockM))) return rc;
+        if ((rc = tc_make_map(&mw, dw, type == WT_BF16, M, K, kTcHalf))) return rc;
         int sms = 148;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         // the plan the decode engine would use for a product of this shape (K slices add into a zeroed output)
-        const TcPlan plan = tc_plan((M + kTcBlockM - 1) / kTcBlockM, N, K / kTcBlockK, true, sms);
-        if ((rc = tc_make_map(&mx, dx16, type == WT_BF16, tile, K, plan.tile))) return rc;
+        const TcPlan plan = tc_plan((M + kTcHalf - 1) / kTcHalf, N, K / kTcBlockK, true, false, sms);
+        if ((rc = tc_make_map(&mx, dx16, type == WT_BF16, alloc_rows, K, plan.x_rows))) return rc;
         const CUtensorMap* maps[3] = {&mw, &mw, &mw};
         TcArgs a{};
         a.n_groups = 1;
