@@ -52,7 +52,8 @@ int tc_tile_for(int rows) {
 
 // Launch shape for a product with `w_tiles` 128-row weight tiles, `rows` batch rows and `kb` 64-wide K blocks on
 // `sms` SMs.  A large matrix runs two weight tiles per CTA (256 weight rows per MMA) over all of K; a small one is
-// cut along K (a slice keeps at least 3 K blocks), and goes to one tile per CTA, until the grid covers the SMs.
+// cut along K (a slice keeps at least 3 K blocks; wide batches take fewer slices, measured), and goes to one tile
+// per CTA, until the grid covers the SMs.
 TcPlan tc_plan(int w_tiles, int rows, int kb, bool may_split_k, bool dual, int sms) {
     TcPlan p;
     p.x_rows = tc_tile_for(std::min(rows, kTcBatch));
@@ -60,7 +61,8 @@ TcPlan tc_plan(int w_tiles, int rows, int kb, bool may_split_k, bool dual, int s
     auto shape = [&](int halves) {
         p.halves = halves;
         const int ctas = (dual ? w_tiles : (w_tiles + halves - 1) / halves) * p.n_tiles;
-        const int want = may_split_k ? std::max(1, std::min(sms / std::max(1, ctas), kb / 3)) : 1;
+        int want = may_split_k ? std::max(1, std::min(sms / std::max(1, ctas), kb / 3)) : 1;
+        want = std::min(want, std::max(4, 1024 / std::max(1, rows)));  // every slice adds rows x M floats with atomics
         p.kb_per_split = (kb + want - 1) / want;
         p.splits = (kb + p.kb_per_split - 1) / p.kb_per_split;
         return ctas * p.splits;
