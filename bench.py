@@ -234,6 +234,23 @@ def gemv_table(runtime, device: int, peak: float) -> dict:
     return out
 
 
+def gemm_table(runtime, device: int, peak: float) -> dict:
+    """Kernel-level Y = X.W^T on the tensor cores (the batched path's product) on an LM-head sized fp16 matrix."""
+    import numpy as np
+
+    out = {}
+    rng = np.random.default_rng(11)
+    rows, cols = 32768, 4096  # 268 MB of weights: every launch streams them from HBM
+    w = (rng.standard_normal((rows, cols)).astype(np.float32) * np.float32(0.02)).astype(np.float16)
+    for n in (16, 64, 256):
+        x = rng.standard_normal((n, cols)).astype(np.float32)
+        _, ms = runtime.gemm_tc_bench("f16", w, rows, cols, x, warmup=5, iterations=40, device=device)
+        nbytes = rows * cols * 2 + n * cols * 2 + n * rows * 4  # weights + 16-bit operand rows + fp32 result
+        out[f"n{n}"] = {"rows": rows, "cols": cols, "batch": n, "ms": ms, "GBps": nbytes / (ms / 1e3) / 1e9,
+                        "frac_of_hbm_peak": nbytes / (ms / 1e3) / 1e9 / peak, "TFLOPs": 2.0 * rows * cols * n / (ms / 1e3) / 1e12}
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -459,6 +476,7 @@ def main() -> None:
         line.update(extra)
         if rank == 0 and not args.no_gemv_table:
             line["gemv"] = gemv_table(runtime, local_rank, peak)
+            line["gemm_tc"] = gemm_table(runtime, local_rank, peak)
         if rank == 0 and not args.no_cpu_baseline:
             r = run_cpu_oracle(wl, args.cpu_steps, 1)
             line["cpu_baseline"] = {"value": r["value"], "unit": unit, "cores": r["cores"], "kind": "port", "sample": r["sample"]}

@@ -9,8 +9,9 @@
 // Operands are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast); the fp32
 // accumulator (128 lanes x 256 columns) lives in tensor memory and is read back with tcgen05.ld.
 //
-// Grid: x = pairs of 128-row weight tiles, taken from up to three matrices that share X (a "group": the q, k and
-// v projections run as one launch), y = batch tiles of 128 rows, z = slices of K.  The two halves of a CTA are
+// Grid: x = batch tiles of 128 rows (fastest, so that the CTAs that share a weight tile run together and the second
+// one finds it in L2), y = pairs of 128-row weight tiles, taken from up to three matrices that share X (a "group":
+// the q, k and v projections run as one launch), z = slices of K.  The two halves of a CTA are
 // independent (matrix, first row) pairs, so a pair may straddle two matrices.  A small matrix only goes faster
 // with more CTAs: the host cuts K (and uses single-half CTAs) until the grid covers the SMs; K slices add their
 // partial sums with fp32 vector atomics.
@@ -18,9 +19,12 @@
 // DUAL (SwiGLU): half 0 holds 128 rows of the gate matrix, half 1 the same 128 rows of the up matrix, and the
 // epilogue writes silu(gate) * up as 16-bit rows: the operand of the down projection, without an fp32 round trip.
 //
-// Warp roles (192 threads): warp 0 allocates tensor memory and issues the TMA loads, warp 1 issues the MMAs
-// (one elected thread), warps 2..5 run the epilogue (a warp may only touch the TMEM lanes 32*(warp%4)..+31, i.e.
-// 32 batch rows; a thread owns one batch row and walks the weight rows, so its stores are 64-byte runs).
+// Warp roles (320 threads): warp 0 allocates tensor memory and issues the TMA loads, warp 1 issues the MMAs
+// (one elected thread), warps 2..9 run the epilogue.  A warp may only touch the TMEM lanes 32*(warp%4)..+31, i.e.
+// 32 batch rows, so two warps share a lane quadrant and split the columns.  tcgen05.ld hands a thread one batch
+// row; written straight to global memory that is 32 different lines per store instruction (measured: 620 cycles
+// per 16 columns), so the tile goes through shared memory (the idle pipeline stages) and leaves with the lanes
+// along the weight rows: every global access is a contiguous 256-byte run per batch row.
 // Every mbarrier wait is bounded; on a timeout the kernel records an error and unwinds normally.
 // Programmatic dependent launch: the weight tiles of the first pipeline stages are requested before the wait on
 // the previous kernel (weights never change); everything that depends on that kernel comes after the wait.
@@ -35,7 +39,7 @@
 
 namespace esp {
 
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kTcHalf = 128;    // weight rows of one half tile (one TMA box)
 constexpr int kTcBatch = 128;   // batch rows of one batch tile (the MMA's M)
 constexpr int kTcBlockK = 64;   // 64 x 16-bit = one 128-byte swizzle row
@@ -151,6 +155,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&f)[16]) {
     for (int j = 0; j < 16; j++) f[j] = __uint_as_float(r[j]);
 }
 
+// Activations of the batched epilogue.  The results are rounded to 16 bits right away, so the exponential may be
+// the hardware approximation (relative error ~2^-21) instead of the exact tanhf of the single-row kernels.
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float gelu_fast(float x) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    const float t = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));  // tanh(u)
+    return 0.5f * x * (1.0f + t);
+}
+
 __device__ __forceinline__ uint32_t pack16x2(float a, float b, int bf16) {
     const uint32_t lo = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(a)) : __half_as_ushort(__float2half_rn(a));
     const uint32_t hi = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(b)) : __half_as_ushort(__float2half_rn(b));
@@ -175,10 +188,10 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
     int n_halves = 0;
     if (a.dual) {
         g_h1 = 1;
-        m0_h0 = m0_h1 = (int)blockIdx.x * kTcHalf;
+        m0_h0 = m0_h1 = (int)blockIdx.y * kTcHalf;
         n_halves = 2;
     } else {
-        const int t0 = (int)blockIdx.x * a.halves;
+        const int t0 = (int)blockIdx.y * a.halves;
         if (t0 < a.n_tiles) {
             if (a.n_groups > 1 && t0 >= a.g[1].tile0) g_h0 = 1;
             if (a.n_groups > 2 && t0 >= a.g[2].tile0) g_h0 = 2;
@@ -195,7 +208,7 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
     }
     const CUtensorMap* const map_h0 = g_h0 == 0 ? &map_w0 : g_h0 == 1 ? &map_w1 : &map_w2;
     const CUtensorMap* const map_h1 = g_h1 == 0 ? &map_w0 : g_h1 == 1 ? &map_w1 : &map_w2;
-    const int n0 = (int)blockIdx.y * kTcBatch;
+    const int n0 = (int)blockIdx.x * kTcBatch;
     const int kb_total = a.K / kTcBlockK;
     const int kb0 = (int)blockIdx.z * a.kb_per_split;
     const int num_kb = n_halves > 0 ? min(a.kb_per_split, kb_total - kb0) : 0;
@@ -264,112 +277,147 @@ __global__ void __launch_bounds__(kTcThreads) k_gemm_tc(const __grid_constant__ 
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(acc_ready)) : "memory");
         }
     } else {
-        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        // ---------------- epilogue: TMEM -> registers -> shared -> global ----------------
+        const int ew = warp - 2;            // 0..7
         const int lane_base = 32 * (warp & 3);
-        const int n = n0 + lane_base + lane;  // this thread's batch row
+        const int sub = ew >> 2;            // which 64-column half of every 128-row weight tile this warp owns
+        const int n = n0 + lane_base + lane;  // phase 1: this thread's batch row
         const bool warp_has_rows = n0 + lane_base < a.n_valid;
         const bool live = n < a.n_valid && (!a.active || a.active[n]);
         const bool ok = tc_wait(acc_ready, 0, a.error) && __ldcg(a.error) == 0 && num_kb > 0;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // kernel parameters used per column chunk live in registers for the whole loop
+        // kernel parameters used per chunk live in registers for the whole loop
         const int epilogue = a.epilogue, bf16 = a.bf16, ld16 = a.ld16, row_offset = a.row_offset;
         const bool atomic_out = a.atomic_out != 0, first_split = blockIdx.z == 0;
         float* const logits = a.logits;
         float* const debug = a.debug;
         uint16_t* const out16 = a.out16;
         const uint32_t trow = tmem_acc + ((uint32_t)lane_base << 16);
-        if (ok && warp_has_rows) {
-            if (epilogue == TC_SWIGLU16) {
-                const int M = a.g[0].M;
+        if (ok && warp_has_rows && epilogue == TC_HEAD) {
+            // a thread scans the weight rows of its batch row: first maximum, ascending, so a later equal value does not
+            // replace an earlier one; the packed atomicMax (value, ~index) merges threads and CTAs with the same rule
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            const int M = a.g[0].M;
 #pragma unroll 1
-                for (int c0 = 0; c0 < kTcHalf; c0 += 16) {
-                    if (m0_h0 + c0 >= M) break;
-                    float gt[16], up[16];
-                    tmem_ld16(trow + (uint32_t)c0, gt);
-                    tmem_ld16(trow + (uint32_t)(kTcHalf + c0), up);
-                    if (!live) continue;
+            for (int hh = 0; hh < n_halves; hh++) {
+                const int mbase = (hh ? m0_h1 : m0_h0) + sub * 64;
+#pragma unroll 1
+                for (int c0 = 0; c0 < 64; c0 += 16) {
+                    const int m = mbase + c0;
+                    if (m >= M) break;
                     float v[16];
+                    tmem_ld16(trow + (uint32_t)(hh * kTcHalf + sub * 64 + c0), v);
+                    if (!live) continue;
+                    const bool whole = m + 16 <= M;  // false only at a ragged vocabulary end
 #pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] = silu_f(gt[j]) * up[j];
-                    uint4* o = reinterpret_cast<uint4*>(out16 + (size_t)n * ld16 + m0_h0 + c0);
-                    o[0] = make_uint4(pack16x2(v[0], v[1], bf16), pack16x2(v[2], v[3], bf16), pack16x2(v[4], v[5], bf16), pack16x2(v[6], v[7], bf16));
-                    o[1] = make_uint4(pack16x2(v[8], v[9], bf16), pack16x2(v[10], v[11], bf16), pack16x2(v[12], v[13], bf16), pack16x2(v[14], v[15], bf16));
-                    if (debug && n == 0) {
+                    for (int j = 0; j < 16; j++)
+                        if ((whole || m + j < M) && v[j] > bv) { bv = v[j]; bi = m + j + row_offset; }
+                    if (logits) {
 #pragma unroll
-                        for (int j = 0; j < 16; j++) debug[m0_h0 + c0 + j] = v[j];
+                        for (int j = 0; j < 16; j++)
+                            if (whole || m + j < M) logits[(size_t)n * M + m + j] = v[j];
+                    }
+                }
+            }
+            if (live && bi != 0x7fffffff) atomicMax(a.best + n, pack_best(bv, bi));
+        } else if (ok && warp_has_rows) {
+            // Phase 1: this warp's 32 batch rows x (64 columns of each weight half) go to its private staging rows.
+            // Every MMA has completed, so the pipeline stages are idle and nothing else touches this memory.
+            constexpr int kStride = 2 * 64 + 4;  // floats per staged row; the pad keeps the 16-byte row stores conflict-free
+            float* const stg = reinterpret_cast<float*>(tiles) + (size_t)ew * 32 * kStride;
+            {
+                float* const mine = stg + (size_t)lane * kStride;
+#pragma unroll 1
+                for (int hh = 0; hh < n_halves; hh++) {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        float v[16];
+                        tmem_ld16(trow + (uint32_t)(hh * kTcHalf + sub * 64 + c * 16), v);
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            reinterpret_cast<float4*>(mine + hh * 64 + c * 16)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    }
+                }
+            }
+            __syncwarp();
+            // Phase 2: a half-warp per batch row, 16 lanes x 4 consecutive weight rows = one 256-byte run.
+            const unsigned live_mask = __ballot_sync(0xffffffffu, live);
+            const int nrow0 = n0 + lane_base;
+            const int hl = lane >> 4, cl = (lane & 15) * 4;
+            if (epilogue == TC_SWIGLU16) {
+                const int m = m0_h0 + sub * 64 + cl;
+                if (m < a.g[0].M) {
+#pragma unroll 4
+                    for (int r0 = 0; r0 < 32; r0 += 2) {
+                        const int r = r0 + hl;
+                        if (!((live_mask >> r) & 1u)) continue;
+                        const float4 gt = *reinterpret_cast<const float4*>(stg + (size_t)r * kStride + cl);
+                        const float4 up = *reinterpret_cast<const float4*>(stg + (size_t)r * kStride + 64 + cl);
+                        const float v0 = silu_fast(gt.x) * up.x, v1 = silu_fast(gt.y) * up.y, v2 = silu_fast(gt.z) * up.z, v3 = silu_fast(gt.w) * up.w;
+                        *reinterpret_cast<uint2*>(out16 + (size_t)(nrow0 + r) * ld16 + m) = make_uint2(pack16x2(v0, v1, bf16), pack16x2(v2, v3, bf16));
+                        if (debug && nrow0 + r == 0) *reinterpret_cast<float4*>(debug + m) = make_float4(v0, v1, v2, v3);
                     }
                 }
             } else {
-                float bv = -INFINITY;
-                int bi = 0x7fffffff;
 #pragma unroll 1
                 for (int hh = 0; hh < n_halves; hh++) {
-                    const int gi = hh ? g_h1 : g_h0, m0 = hh ? m0_h1 : m0_h0;
+                    const int gi = hh ? g_h1 : g_h0;
                     const int M = ESP_TC_G(gi, M), ldo = ESP_TC_G(gi, ldo);
                     const float* const bias = first_split ? ESP_TC_G(gi, bias) : nullptr;
                     float* const out = ESP_TC_G(gi, out);
-#pragma unroll 1
-                    for (int c0 = 0; c0 < kTcHalf; c0 += 16) {
-                        const int m = m0 + c0;
-                        if (m >= M) break;
-                        float v[16];
-                        tmem_ld16(trow + (uint32_t)(hh * kTcHalf + c0), v);
-                        if (!live) continue;
-                        const bool whole = m + 16 <= M;  // false only at a ragged vocabulary end
-                        if (bias) {
-#pragma unroll
-                            for (int j = 0; j < 16; j++) v[j] += (whole || m + j < M) ? bias[m + j] : 0.f;
-                        }
-                        if (epilogue == TC_HEAD) {
-                            // first maximum over this thread's weight rows, ascending: a later equal value does not replace it
-#pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if ((whole || m + j < M) && v[j] > bv) { bv = v[j]; bi = m + j + row_offset; }
-                            if (logits) {
-#pragma unroll
-                                for (int j = 0; j < 16; j++)
-                                    if (whole || m + j < M) logits[(size_t)n * M + m + j] = v[j];
+                    const int m = (hh ? m0_h1 : m0_h0) + sub * 64 + cl;
+                    if (m >= M) continue;
+                    const bool vec = m + 4 <= M && ((ldo | ld16) & 3) == 0;
+                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (bias) {
+                        b4.x = bias[m];
+                        if (m + 1 < M) b4.y = bias[m + 1];
+                        if (m + 2 < M) b4.z = bias[m + 2];
+                        if (m + 3 < M) b4.w = bias[m + 3];
+                    }
+#pragma unroll 4
+                    for (int r0 = 0; r0 < 32; r0 += 2) {
+                        const int r = r0 + hl;
+                        if (!((live_mask >> r) & 1u)) continue;
+                        float4 v = *reinterpret_cast<const float4*>(stg + (size_t)r * kStride + hh * 64 + cl);
+                        v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
+                        const size_t nr = (size_t)(nrow0 + r);
+                        if (epilogue == TC_GELU16) {
+                            const float g0 = gelu_fast(v.x), g1 = gelu_fast(v.y), g2 = gelu_fast(v.z), g3 = gelu_fast(v.w);
+                            uint16_t* o = out16 + nr * ld16 + m;
+                            if (vec) {
+                                *reinterpret_cast<uint2*>(o) = make_uint2(pack16x2(g0, g1, bf16), pack16x2(g2, g3, bf16));
+                            } else {
+                                const float gl[4] = {g0, g1, g2, g3};
+                                for (int j = 0; j < 4 && m + j < M; j++) o[j] = (uint16_t)(pack16x2(gl[j], 0.f, bf16) & 0xffffu);
                             }
-                        } else if (epilogue == TC_GELU16) {
-                            float gl[16];
-#pragma unroll
-                            for (int j = 0; j < 16; j++) gl[j] = gelu_f(v[j]);
-                            uint4* o = reinterpret_cast<uint4*>(out16 + (size_t)n * ld16 + m);
-                            o[0] = make_uint4(pack16x2(gl[0], gl[1], bf16), pack16x2(gl[2], gl[3], bf16), pack16x2(gl[4], gl[5], bf16), pack16x2(gl[6], gl[7], bf16));
-                            o[1] = make_uint4(pack16x2(gl[8], gl[9], bf16), pack16x2(gl[10], gl[11], bf16), pack16x2(gl[12], gl[13], bf16), pack16x2(gl[14], gl[15], bf16));
-                            if (debug && n == 0) {
-#pragma unroll
-                                for (int j = 0; j < 16; j++) debug[m + j] = gl[j];
-                            }
-                        } else if (!whole || (ldo & 3)) {  // ragged end or unaligned rows: element by element
-                            float* o = out + (size_t)n * ldo + m;
-#pragma unroll
-                            for (int j = 0; j < 16; j++) {
-                                if (m + j >= M) continue;
-                                if (atomic_out) atomicAdd(o + j, v[j]);
-                                else o[j] = epilogue == TC_RESIDUAL ? o[j] + v[j] : v[j];
+                            if (debug && nr == 0) {
+                                const float gl[4] = {g0, g1, g2, g3};
+                                for (int j = 0; j < 4 && m + j < M; j++) debug[m + j] = gl[j];
                             }
                         } else {
-                            float* o = out + (size_t)n * ldo + m;
-                            if (atomic_out) {
-#pragma unroll
-                                for (int j = 0; j < 16; j += 4) red_add_v4(o + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            } else if (epilogue == TC_RESIDUAL) {
-                                float4 prev[4];
-#pragma unroll
-                                for (int j = 0; j < 4; j++) prev[j] = reinterpret_cast<const float4*>(o)[j];
-#pragma unroll
-                                for (int j = 0; j < 4; j++)
-                                    reinterpret_cast<float4*>(o)[j] =
-                                        make_float4(prev[j].x + v[4 * j], prev[j].y + v[4 * j + 1], prev[j].z + v[4 * j + 2], prev[j].w + v[4 * j + 3]);
+                            float* o = out + nr * ldo + m;
+                            if (vec) {
+                                if (atomic_out) {
+                                    red_add_v4(o, v.x, v.y, v.z, v.w);
+                                } else {
+                                    if (epilogue == TC_RESIDUAL) {
+                                        const float4 pv = *reinterpret_cast<const float4*>(o);
+                                        v.x += pv.x; v.y += pv.y; v.z += pv.z; v.w += pv.w;
+                                    }
+                                    *reinterpret_cast<float4*>(o) = v;
+                                }
                             } else {
-#pragma unroll
-                                for (int j = 0; j < 4; j++) reinterpret_cast<float4*>(o)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                                const float vv[4] = {v.x, v.y, v.z, v.w};
+                                for (int j = 0; j < 4 && m + j < M; j++) {
+                                    if (atomic_out) atomicAdd(o + j, vv[j]);
+                                    else o[j] = epilogue == TC_RESIDUAL ? o[j] + vv[j] : vv[j];
+                                }
                             }
                         }
                     }
                 }
-                if (epilogue == TC_HEAD && live && bi != 0x7fffffff) atomicMax(a.best + n, pack_best(bv, bi));
             }
         }
     }

@@ -101,7 +101,7 @@ cudaError_t tc_launch(const TcPlan& plan, bool dual, const CUtensorMap* const* m
     a.kb_per_split = plan.kb_per_split;
     a.atomic_out = plan.splits > 1 ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(dual ? tiles : (tiles + a.halves - 1) / a.halves, plan.n_tiles, plan.splits);
+    cfg.gridDim = dim3(plan.n_tiles, dual ? tiles : (tiles + a.halves - 1) / a.halves, plan.splits);
     cfg.blockDim = dim3(kTcThreads);
     cfg.dynamicSmemBytes = kTcSmemBytes;
     cfg.stream = s;
