@@ -2,5 +2,6 @@
 // functions, so the engine and the C ABI are compiled together.
 #include "engine.cu"
 #include "capi.cu"
+#include "gguf_reader.cu"
 #include "static_head.cu"
 #include "tc_host.cu"

@@ -72,6 +72,10 @@ _vp, _u32p, _i32p, _f32p = C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_int3
 SIGNATURES = {
     "esp_cuda_create": (C.c_int32, [C.POINTER(EspCudaConfig), C.c_char_p, C.POINTER(_vp)]),
     "esp_cuda_create_from_directory": (C.c_int32, [C.c_char_p, C.c_int32, C.c_int32, C.c_uint32, C.POINTER(_vp)]),
+    "esp_cuda_gguf_inspect": (C.c_int32, [C.c_char_p, C.POINTER(EspCudaConfig), C.c_char_p, C.c_int32, _i32p, _i32p]),
+    "esp_cuda_gguf_tensor_info": (C.c_int32, [C.c_char_p, C.c_int32, C.c_char_p, C.c_int32, C.c_char_p, C.c_int32, _i32p,
+                                              C.POINTER(C.c_int64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "esp_cuda_create_from_gguf": (C.c_int32, [C.c_char_p, C.c_int32, C.c_int32, C.c_uint32, C.POINTER(_vp)]),
     "esp_cuda_load_tensor": (C.c_int32, [_vp, C.c_char_p, C.c_int32, _vp, C.c_uint64]),
     "esp_cuda_tp_unique_id": (C.c_int32, [C.POINTER(C.c_uint8), C.c_int32]),
     "esp_cuda_tp_init": (C.c_int32, [_vp, C.POINTER(C.c_uint8), C.c_int32]),
@@ -181,6 +185,14 @@ class DecodeEngine:
             config = MultiModelConfig.load(weight_dir)
         cc = make_c_config(config, max_batch, device, flags)
         _check(lib.esp_cuda_create(C.byref(cc), os.fsencode(weight_dir), C.byref(out)))
+        return cls(out.value, config, max_batch)
+
+    @classmethod
+    def from_gguf(cls, path: str, max_batch: int = 1, device: int = 0, flags: int = 0) -> "DecodeEngine":
+        """An engine built straight from a ``.gguf`` file (GGUFModelLoader.prepare + engine construction)."""
+        config, _, _, _ = gguf_inspect(path)
+        out = C.c_void_p()
+        _check(load_library().esp_cuda_create_from_gguf(os.fsencode(path), max_batch, device, flags, C.byref(out)))
         return cls(out.value, config, max_batch)
 
     @classmethod
@@ -387,6 +399,31 @@ def lm_head_argmax_static(lm_head_ptr: int, vocab: int, d_model: int, hidden_ptr
     _check(load_library().esp_cuda_lm_head_argmax_static(
         C.c_void_p(lm_head_ptr), vocab, d_model, C.c_void_p(hidden_ptr), rows, C.c_void_p(gain_ptr) if gain_ptr else None,
         eps, C.c_void_p(tokens_ptr), C.c_void_p(stream) if stream else None, device))
+
+
+def gguf_inspect(path: str) -> tuple[MultiModelConfig, str, int, bool]:
+    """``(model shape, GGUF architecture name, tensor count, LM head tied to the embedding)`` of a ``.gguf`` file."""
+    cc = EspCudaConfig()
+    name = C.create_string_buffer(64)
+    n, tied = C.c_int32(), C.c_int32()
+    _check(load_library().esp_cuda_gguf_inspect(os.fsencode(path), C.byref(cc), name, 64, C.byref(n), C.byref(tied)))
+    arch = "gpt2" if cc.architecture == 1 else "llama"
+    cfg = MultiModelConfig(name.value.decode(), cc.n_layer, cc.n_head, cc.n_kv_head, cc.d_model, cc.head_dim, cc.hidden_dim, cc.vocab,
+                           cc.max_seq, cc.norm_eps, cc.rope_theta, None if cc.eos_token < 0 else cc.eos_token, arch)
+    return cfg, name.value.decode(), int(n.value), bool(tied.value)
+
+
+def gguf_tensors(path: str) -> list[dict]:
+    """The tensor directory of a ``.gguf`` file: name, mapped weight-directory path, GGML type, dims, offset, bytes."""
+    _, _, n, _ = gguf_inspect(path)
+    out = []
+    for i in range(n):
+        name, slot = C.create_string_buffer(256), C.create_string_buffer(256)
+        t, dims, off, nb = C.c_int32(), (C.c_int64 * 4)(), C.c_uint64(), C.c_uint64()
+        _check(load_library().esp_cuda_gguf_tensor_info(os.fsencode(path), i, name, 256, slot, 256, C.byref(t), dims, C.byref(off), C.byref(nb)))
+        out.append({"name": name.value.decode(), "slot": slot.value.decode(), "type": int(t.value), "dims": [int(d) for d in dims],
+                    "offset": int(off.value), "nbytes": int(nb.value)})
+    return out
 
 
 def gemm_tc_bench(kind: str, weights: np.ndarray, rows: int, cols: int, x: np.ndarray, warmup: int = 3, iterations: int = 20,

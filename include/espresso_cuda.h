@@ -112,6 +112,31 @@ ESP_CUDA_API int32_t esp_cuda_create(const esp_cuda_config* config, const char* 
 ESP_CUDA_API int32_t esp_cuda_create_from_directory(const char* weight_dir, int32_t max_batch, int32_t device,
                                                    uint32_t flags, esp_cuda_engine** out);
 
+/* ---- GGUF front end (replaces GGUFModelLoader.prepare, Sources/EspressoGGUF/GGUFModelLoader.swift:273-405; the
+ * parser itself lives in the reference's un-vendored Edgerunner package) -------------------------------------- */
+
+/* Parses a .gguf file (versions 2 and 3) on the host: fills the model shape the reference derives from the metadata
+ * (GGUFModelLoader.swift:297-326: <arch>.block_count, attention.head_count[_kv], embedding_length,
+ * feed_forward_length, context_length, attention.layer_norm[_rms]_epsilon, rope.freq_base (default 10000), vocab =
+ * length of tokenizer.ggml.tokens, eos = tokenizer.ggml.eos_token_id), the architecture name, the tensor count and
+ * whether the LM head is tied to the embedding (no "output.weight", :224-263).  Needs no GPU. */
+ESP_CUDA_API int32_t esp_cuda_gguf_inspect(const char* path, esp_cuda_config* config, char* architecture_name, int32_t name_capacity,
+                                           int32_t* n_tensors, int32_t* tied_lm_head);
+
+/* One entry of the tensor directory: GGUF name, the weight-directory path it maps to ("" = not read by the decode
+ * path; "layers/N/wqkv" = GPT-2's fused projection, split at upload), GGML type, dims (dims[0] = row length), offset
+ * inside the data section and byte size (0 for GGML types that cannot be uploaded).  Needs no GPU. */
+ESP_CUDA_API int32_t esp_cuda_gguf_tensor_info(const char* path, int32_t index, char* name, int32_t name_capacity, char* slot,
+                                               int32_t slot_capacity, int32_t* ggml_type, int64_t* dims4, uint64_t* data_offset,
+                                               uint64_t* nbytes);
+
+/* Builds and finalises an engine from a .gguf file: F32/F16/BF16 tensors as they are, Q8_0/Q4_0 matrices as
+ * quantised blocks (no fp16 materialisation, unlike GGUFModelLoader.swift:341-369), quantised embedding tables
+ * expanded to fp16, Wq/Wk rows of llama/mistral files put back from llama.cpp's per-head interleave into the
+ * half-split rotation order, a missing output.weight replaced by the embedding matrix. */
+ESP_CUDA_API int32_t esp_cuda_create_from_gguf(const char* path, int32_t max_batch, int32_t device, uint32_t flags,
+                                               esp_cuda_engine** out);
+
 /* Uploads one tensor.  name is the weight-directory relative path without ".bin"
  * ("embeddings/token", "rms_final", "lm_head", "layers/3/wq", ...).  data may be a host or a device
  * pointer.  Matrices are row-major [out, in].  F16/BF16/F32 take raw elements; Q8_0/Q4_0 take GGUF
