@@ -322,6 +322,16 @@ class DecodeEngine:
         _check(self._lib.esp_cuda_generate(self._h, p, arr.size, max_tokens, out.ctypes.data_as(_u32p), C.byref(n), C.byref(res)))
         return self._result(res, out[: n.value].copy(), arr)
 
+    def generate_text(self, tokenizer, prompt: str, max_tokens: int = 128) -> tuple[str, GenerationResult]:
+        """``generate(prompt:maxTokens:)`` on text (RealModelInferenceEngine.swift:1405-1460): the prompt is encoded
+        with ``tokenizer`` (see :mod:`espresso_b200.tokenizers`), an empty encoding is ``invalidPrompt`` as in the
+        reference (:5405-5408), and the generated ids are decoded back."""
+        ids = tokenizer.encode(prompt)
+        if not ids:
+            raise RealModelInferenceError(ERR_INVALID_ARGUMENT, "Prompt produced no tokens")
+        res = self.generate(ids, max_tokens)
+        return tokenizer.decode([int(t) for t in res.tokens]), res
+
     def generate_batch(self, prompts, max_tokens: int = 128) -> tuple[list[np.ndarray], GenerationResult]:
         arr, p = _u32(prompts)
         assert arr.ndim == 2
