@@ -659,8 +659,8 @@ int32_t Engine::finalize() {
     size_t dbg = (size_t)m_.q_dim * 2 + 2 * m_.kv_dim + 2 * m_.d_model + m_.hidden;
     if ((rc = dev_alloc(owned_, &d_debug_, dbg))) return rc;
     ESP_CUDA_TRY(cudaDeviceSynchronize());
+    if ((rc = build_tc())) return rc;  // first: it makes the fp16 expansions the persistent kernel may pack
     if ((rc = build_mega())) return rc;
-    if ((rc = build_tc())) return rc;
     finalized_ = true;
     return reset();
 }
@@ -1441,10 +1441,18 @@ int32_t Engine::build_mega() {
     if (m_.arch != ARCH_LLAMA || m_.eos_token >= 0) return ESP_CUDA_OK;
     if (m_.head_dim != 32 && m_.head_dim != 64 && m_.head_dim != 128) return ESP_CUDA_OK;
     if (m_.d_model > 4096 || m_.d_model % 8 || m_.n_head > sm_count_) return ESP_CUDA_OK;
-    if (tensors_.at("embeddings/token").type != ESP_CUDA_F16 || tensors_.at("lm_head").type != ESP_CUDA_F16) return ESP_CUDA_OK;
+    // fp16 source of a matrix: its own storage, or the fp16 expansion of a quantised matrix (the persistent kernel
+    // then streams 2 bytes per weight instead of the blocks; it still beats the per-stage kernels by removing their
+    // ~110 dependent launches per token)
+    auto f16_source = [&](const std::string& name) -> const __half* {
+        const DeviceTensor& t = tensors_.at(name);
+        if (t.type == ESP_CUDA_F16) return static_cast<const __half*>(t.data);
+        return t.shadow16;  // null unless build_tc made one
+    };
+    if (tensors_.at("embeddings/token").type != ESP_CUDA_F16 || !f16_source("lm_head")) return ESP_CUDA_OK;
     for (int l = 0; l < m_.n_layer; l++)
         for (const char* n : {"wq", "wk", "wv", "wo", "w1", "w2", "w3"})
-            if (tensors_.at("layers/" + std::to_string(l) + "/" + n).type != ESP_CUDA_F16) return ESP_CUDA_OK;
+            if (!f16_source("layers/" + std::to_string(l) + "/" + n)) return ESP_CUDA_OK;
     int coop = 0, smem_max = 0;
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, cfg_.device);
     cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, cfg_.device);
@@ -1462,7 +1470,22 @@ int32_t Engine::build_mega() {
     p.s2_bytes = pad128((long long)p.rpb * m_.head_dim * 2);
     p.s3a_bytes = pad128((long long)2 * p.hpc * p.row_bytes);
     p.s3b_bytes = pad128((long long)p.hpc * p.row_bytes);
-    int layer_max = std::max(std::max(p.s1_bytes, p.s2_bytes), std::max(p.s3a_bytes, p.s3b_bytes));
+    // A stage slice of up to 64 KB travels as one chunk; larger ones as chunks of about 48 KB of whole items.
+    const int kWhole = 64 * 1024, kTarget = 48 * 1024;
+    auto per_chunk = [&](int items, int item_bytes, int multiple) {
+        if ((long long)items * item_bytes <= kWhole) return std::max(items, 1);
+        int n = std::max(1, kTarget / item_bytes);
+        if (multiple > 1) n = std::max(multiple, n / multiple * multiple);
+        return n;
+    };
+    const int s2_rows_per_pass = kMegaConsumers / (m_.head_dim / 16);
+    p.s1_ipc = per_chunk(p.ppc, 2 * p.row_bytes, 1);
+    p.s2_rpc = per_chunk(p.rpb, m_.head_dim * 2, s2_rows_per_pass);
+    p.s3a_ipc = per_chunk(p.hpc, 2 * p.row_bytes, 1);
+    p.s3b_rpc = per_chunk(p.hpc, p.row_bytes, 1);
+    auto chunk_bytes = [](int items, int per, int item_bytes) { return pad128((long long)std::min(items, per) * item_bytes); };
+    int layer_max = std::max(std::max(chunk_bytes(p.ppc, p.s1_ipc, 2 * p.row_bytes), chunk_bytes(p.rpb, p.s2_rpc, m_.head_dim * 2)),
+                             std::max(chunk_bytes(p.hpc, p.s3a_ipc, 2 * p.row_bytes), chunk_bytes(p.hpc, p.s3b_rpc, p.row_bytes)));
     int rh = std::max(4, (std::max(layer_max, 48 * 1024) / p.row_bytes) & ~3);
     rh = std::min(rh, (p.vpc + 3) & ~3);
     p.head_rows_per_chunk = rh;
@@ -1498,7 +1521,7 @@ int32_t Engine::build_mega() {
     const char* names[7] = {"wq", "wk", "wv", "wo", "w1", "w2", "w3"};
     for (int k = 0; k < 7; k++)
         for (int l = 0; l < m_.n_layer; l++)
-            ptrs[(size_t)k * m_.n_layer + l] = static_cast<const __half*>(tensors_.at("layers/" + std::to_string(l) + "/" + names[k]).data);
+            ptrs[(size_t)k * m_.n_layer + l] = f16_source("layers/" + std::to_string(l) + "/" + names[k]);
     const __half** d_ptrs = nullptr;
     ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_ptrs), ptrs.size() * sizeof(void*)));
     cudaError_t e = cudaMemcpy(d_ptrs, ptrs.data(), ptrs.size() * sizeof(void*), cudaMemcpyHostToDevice);
@@ -1506,7 +1529,7 @@ int32_t Engine::build_mega() {
         PackSources src{};
         src.wq = d_ptrs; src.wk = d_ptrs + m_.n_layer; src.wv = d_ptrs + 2 * m_.n_layer; src.wo = d_ptrs + 3 * m_.n_layer;
         src.w1 = d_ptrs + 4 * m_.n_layer; src.w2 = d_ptrs + 5 * m_.n_layer; src.w3 = d_ptrs + 6 * m_.n_layer;
-        src.lm_head = static_cast<const __half*>(tensors_.at("lm_head").data);
+        src.lm_head = f16_source("lm_head");
         k_build_pack<<<P, 256, 0, stream_>>>(src, p, m_, d_pack_);
         e = cudaGetLastError();
     }

@@ -33,7 +33,12 @@ struct MegaPlan {
     int vpc;          // head: vocab rows per CTA
     int head_rows_per_chunk, head_chunks;
     int row_bytes;    // d_model * 2
-    int s1_bytes, s2_bytes, s3a_bytes, s3b_bytes, head_chunk_bytes;  // ring chunk sizes (multiples of 128)
+    int s1_bytes, s2_bytes, s3a_bytes, s3b_bytes, head_chunk_bytes;  // packed bytes of a stage per layer / of a head chunk (multiples of 128)
+    // A stage whose slice is larger than a ring slot arrives in several chunks of whole items:
+    int s1_ipc;       // S1 row pairs per chunk
+    int s2_rpc;       // S2 projection rows per chunk (a multiple of the rows one pass of the CTA covers)
+    int s3a_ipc;      // S3 (gate, up) pairs per chunk
+    int s3b_rpc;      // S3 down-projection rows per chunk
     int slot_bytes, n_slots;
     long long layer_bytes, cta_bytes;  // packed bytes per CTA: one layer, everything
     int smem_bytes;
@@ -293,13 +298,13 @@ __device__ __forceinline__ void mega_dot4(const uint8_t* base, int row_bytes, in
 }
 
 // S1: q/k/v rows of this CTA (pairs that RoPE rotates together), RoPE, q store and KV-cache append.
-__device__ __forceinline__ void mega_s1(const MegaArgs& a, const MegaShared& s, int layer, int pos, const uint8_t* chunk) {
+__device__ __forceinline__ void mega_s1(const MegaArgs& a, const MegaShared& s, int layer, int pos, const uint8_t* chunk, int i0, int n_items) {
     const ModelDims& m = a.m;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int half = m.head_dim / 2;
     const int q_items = m.q_dim / 2, k_items = m.kv_dim / 2, total = q_items + 2 * k_items;
-    for (int i = warp; i < a.plan.ppc; i += kMegaConsumerWarps) {
-        const int item = blockIdx.x * a.plan.ppc + i;
+    for (int i = warp; i < n_items; i += kMegaConsumerWarps) {  // i: item inside the chunk, i0 + i: item of this CTA
+        const int item = blockIdx.x * a.plan.ppc + i0 + i;
         if (item >= total) break;
         float v0, v1;
         mega_dot2(chunk + (size_t)(2 * i) * a.plan.row_bytes, chunk + (size_t)(2 * i + 1) * a.plan.row_bytes, m.d_model, s.xs, lane, v0, v1);
@@ -335,7 +340,7 @@ __device__ __forceinline__ void mega_s1(const MegaArgs& a, const MegaShared& s, 
 // lane accumulates its own channels of V.  K and V rows are requested before the query is even staged, and the
 // eight per-warp (max, sum, ctx) triples are merged once.
 template <int HD>
-__device__ __forceinline__ void mega_s2_t(const MegaArgs& a, const MegaShared& s, int layer, int pos, const uint8_t* chunk, const float* x_in,
+__device__ __forceinline__ void mega_s2_t(const MegaArgs& a, const MegaShared& s, int layer, int pos, unsigned& c, const float* x_in,
                                           const uint16_t* emb_row, float* x_mid) {
     const ModelDims& m = a.m;
     const MegaPlan& p = a.plan;
@@ -453,51 +458,80 @@ __device__ __forceinline__ void mega_s2_t(const MegaArgs& a, const MegaShared& s
     // partial output projection: rows [blk*rpb, ...) of Wo restricted to this head's columns
     const int psub = tid % tpr;  // tpr threads per row, 16 inputs each
     const int rows_per_pass = kMegaConsumers / tpr;
-    for (int rb = 0; rb < p.rpb; rb += rows_per_pass) {  // uniform trip count: the shuffles below need every lane
-        const int r = rb + tid / tpr;
-        const int orow = blk * p.rpb + r;
-        const bool valid = r < p.rpb;
-        float v = 0.f;
-        if (valid) {
-            const uint8_t* wrow = chunk + (size_t)r * hd * 2 + psub * 32;
-            const uint4 w0 = lds128(wrow), w1 = lds128(wrow + 16);
-            fma_vec16<WT_F16>(w0, nullptr, 0, s.ctx + psub * 16, 0.f, v);
-            fma_vec16<WT_F16>(w1, nullptr, 0, s.ctx + psub * 16 + 8, 0.f, v);
+    for (int r0 = 0; r0 < p.rpb; r0 += p.s2_rpc) {  // the block's rows arrive in chunks of s2_rpc
+        const uint8_t* chunk = mega_acquire(a, s, c);
+        const int nr = min(p.s2_rpc, p.rpb - r0);
+        for (int rb = 0; rb < nr; rb += rows_per_pass) {  // uniform trip count: the shuffles below need every lane
+            const int r = rb + tid / tpr;
+            const int orow = blk * p.rpb + r0 + r;
+            const bool valid = r < nr;
+            float v = 0.f;
+            if (valid) {
+                const uint8_t* wrow = chunk + (size_t)r * hd * 2 + psub * 32;
+                const uint4 w0 = lds128(wrow), w1 = lds128(wrow + 16);
+                fma_vec16<WT_F16>(w0, nullptr, 0, s.ctx + psub * 16, 0.f, v);
+                fma_vec16<WT_F16>(w1, nullptr, 0, s.ctx + psub * 16 + 8, 0.f, v);
+            }
+            for (int o = tpr / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (valid && psub == 0 && orow < m.d_model) {
+                if (head == 0)  // residual, added once
+                    v += (r0 == 0 && rb == 0) ? resid : (emb_row ? __half2float(__ushort_as_half(emb_row[orow])) : __ldcg(x_in + orow));
+                atomicAdd(x_mid + orow, v);
+            }
         }
-        for (int o = tpr / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (valid && psub == 0 && orow < m.d_model) {
-            if (head == 0) v += rb == 0 ? resid : (emb_row ? __half2float(__ushort_as_half(emb_row[orow])) : __ldcg(x_in + orow));  // residual, added once
-            atomicAdd(x_mid + orow, v);
-        }
+        mega_release(a, s, c);
+        c++;
     }
 }
 
 // S3: gate/up rows of this CTA's hidden units, SiLU*up, then the partial down projection (W2 transposed).
-__device__ __forceinline__ void mega_s3_up(const MegaArgs& a, const MegaShared& s, const uint8_t* chunk) {
+__device__ __forceinline__ void mega_s3_up(const MegaArgs& a, const MegaShared& s, const uint8_t* chunk, int j0, int n_items) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int j = warp; j < a.plan.hpc; j += kMegaConsumerWarps) {
+    for (int j = warp; j < n_items; j += kMegaConsumerWarps) {
         float g, u;
         mega_dot2(chunk + (size_t)(2 * j) * a.plan.row_bytes, chunk + (size_t)(2 * j + 1) * a.plan.row_bytes, a.m.d_model, s.xs, lane, g, u);
-        if (lane == 0) s.act[j] = silu_f(g) * u;
+        if (lane == 0) s.act[j0 + j] = silu_f(g) * u;
     }
 }
-__device__ __forceinline__ void mega_s3_down(const MegaArgs& a, const MegaShared& s, const uint8_t* chunk, const float* x_mid, float* x_out) {
+// Partial down projection: a thread owns up to four groups of 4 output columns (d_model <= 4096) and accumulates
+// over the CTA's hidden units, whose rows of W2-transposed arrive in chunks of s3b_rpc.
+constexpr int kMegaDownGroups = 4;
+__device__ __forceinline__ void mega_s3_down(const MegaArgs& a, const MegaShared& s, unsigned& c, const float* x_mid, float* x_out) {
     const int d = a.m.d_model;
-    for (int c = threadIdx.x * 4; c < d; c += kMegaConsumers * 4) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < a.plan.hpc; j++) {
-            const uint2 w = lds64(chunk + (size_t)j * a.plan.row_bytes + (size_t)c * 2);
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-            const float av = s.act[j];
-            acc[0] = fmaf(av, f0.x, acc[0]); acc[1] = fmaf(av, f0.y, acc[1]);
-            acc[2] = fmaf(av, f1.x, acc[2]); acc[3] = fmaf(av, f1.y, acc[3]);
+    const MegaPlan& p = a.plan;
+    float acc[kMegaDownGroups][4];
+#pragma unroll
+    for (int g = 0; g < kMegaDownGroups; g++) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+    for (int j0 = 0; j0 < p.hpc; j0 += p.s3b_rpc) {
+        const uint8_t* chunk = mega_acquire(a, s, c);
+        const int nj = min(p.s3b_rpc, p.hpc - j0);
+#pragma unroll
+        for (int g = 0; g < kMegaDownGroups; g++) {
+            const int col = threadIdx.x * 4 + g * kMegaConsumers * 4;
+            if (col < d) {
+                for (int j = 0; j < nj; j++) {
+                    const uint2 w = lds64(chunk + (size_t)j * p.row_bytes + (size_t)col * 2);
+                    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+                    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+                    const float av = s.act[j0 + j];
+                    acc[g][0] = fmaf(av, f0.x, acc[g][0]); acc[g][1] = fmaf(av, f0.y, acc[g][1]);
+                    acc[g][2] = fmaf(av, f1.x, acc[g][2]); acc[g][3] = fmaf(av, f1.y, acc[g][3]);
+                }
+            }
         }
-        if (blockIdx.x == 0) {  // residual, added once
-            const float4 r = __ldcg(reinterpret_cast<const float4*>(x_mid + c));
-            acc[0] += r.x; acc[1] += r.y; acc[2] += r.z; acc[3] += r.w;
+        mega_release(a, s, c);
+        c++;
+    }
+#pragma unroll
+    for (int g = 0; g < kMegaDownGroups; g++) {
+        const int col = threadIdx.x * 4 + g * kMegaConsumers * 4;
+        if (col < d) {
+            if (blockIdx.x == 0) {  // residual, added once
+                const float4 r = __ldcg(reinterpret_cast<const float4*>(x_mid + col));
+                acc[g][0] += r.x; acc[g][1] += r.y; acc[g][2] += r.z; acc[g][3] += r.w;
+            }
+            red_add_v4(x_out + col, acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
         }
-        red_add_v4(x_out + c, acc[0], acc[1], acc[2], acc[3]);
     }
 }
 
@@ -518,7 +552,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
     __syncthreads();
     const uint8_t* blob = a.pack + (size_t)blockIdx.x * p.cta_bytes;
     const long long head_off = (long long)L * p.layer_bytes;
-    const unsigned chunks_per_forward = 4u * (unsigned)L;
 
     if (warp == kMegaConsumerWarps) {
         // ---------------- producer: one thread streams this CTA's chunks in consumption order ----------------
@@ -534,14 +567,19 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 bulk_copy_g2s(s.slots + (size_t)slot * p.slot_bytes, blob + off, (unsigned)bytes, s.full + slot, policy);
                 c++;
             };
+            // a stage's slice: whole items, `per_chunk` at a time (the pack pads a CTA's last items with zero rows)
+            auto issue_stage = [&](long long off, int items, int per_chunk, int item_bytes) {
+                for (int i0 = 0; i0 < items; i0 += per_chunk) issue(off + (long long)i0 * item_bytes, min(per_chunk, items - i0) * item_bytes);
+            };
             for (int step = 0; step < a.n_steps; step++) {
                 if (step > 0) {
                     for (int l = 0; l < L; l++) {
                         long long off = (long long)l * p.layer_bytes;
-                        issue(off, p.s1_bytes); off += p.s1_bytes;
-                        issue(off, p.s2_bytes); off += p.s2_bytes;
-                        issue(off, p.s3a_bytes); off += p.s3a_bytes;
-                        issue(off, p.s3b_bytes);
+                        issue_stage(off, p.ppc, p.s1_ipc, 2 * p.row_bytes); off += p.s1_bytes;
+                        if ((int)blockIdx.x < m.n_head * p.blocks) issue_stage(off, p.rpb, p.s2_rpc, m.head_dim * 2);  // S2 runs on n_head * blocks CTAs
+                        off += p.s2_bytes;
+                        issue_stage(off, p.hpc, p.s3a_ipc, 2 * p.row_bytes); off += p.s3a_bytes;
+                        issue_stage(off, p.hpc, p.s3b_rpc, p.row_bytes);
                     }
                 }
                 for (int hc = 0; hc < p.head_chunks; hc++) issue(head_off + (long long)hc * p.head_chunk_bytes, p.head_chunk_bytes);
@@ -586,36 +624,36 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 stamp(step);
                 if ((int)blockIdx.x == p.n_cta - 1)  // both accumulation targets of this layer start from zero
                     for (int k = tid; k < m.d_model; k += kMegaConsumers) { x_mid[k] = 0.f; x_out[k] = 0.f; }
-                const uint8_t* ch = mega_acquire(a, s, c);
-                stamp(step);
-                mega_s1(a, s, l, pos, ch);
-                mega_release(a, s, c); c++;
+                for (int i0 = 0; i0 < p.ppc; i0 += p.s1_ipc) {
+                    const uint8_t* ch = mega_acquire(a, s, c);
+                    if (i0 == 0) stamp(step);
+                    mega_s1(a, s, l, pos, ch, i0, min(p.s1_ipc, p.ppc - i0));
+                    mega_release(a, s, c); c++;
+                }
                 stamp(step);
                 mega_grid_sync(a, s, epoch);
                 stamp(step);
-                // S2
-                ch = mega_acquire(a, s, c);
+                // S2 (acquires its projection chunks itself, after the attention)
                 stamp(step);
-                if (m.head_dim == 64) mega_s2_t<64>(a, s, l, pos, ch, x_in, er, x_mid);
-                else if (m.head_dim == 128) mega_s2_t<128>(a, s, l, pos, ch, x_in, er, x_mid);
-                else mega_s2_t<32>(a, s, l, pos, ch, x_in, er, x_mid);
-                mega_release(a, s, c); c++;
+                if (m.head_dim == 64) mega_s2_t<64>(a, s, l, pos, c, x_in, er, x_mid);
+                else if (m.head_dim == 128) mega_s2_t<128>(a, s, l, pos, c, x_in, er, x_mid);
+                else mega_s2_t<32>(a, s, l, pos, c, x_in, er, x_mid);
                 stamp(step);
                 mega_grid_sync(a, s, epoch);
                 stamp(step);
                 // S3
                 mega_stage_norm(a, s, x_mid, nullptr, a.norms + (size_t)(2 * l + 1) * m.d_model);
                 stamp(step);
-                ch = mega_acquire(a, s, c);
-                stamp(step);
-                mega_s3_up(a, s, ch);
-                mega_release(a, s, c); c++;
+                for (int j0 = 0; j0 < p.hpc; j0 += p.s3a_ipc) {
+                    const uint8_t* ch = mega_acquire(a, s, c);
+                    if (j0 == 0) stamp(step);
+                    mega_s3_up(a, s, ch, j0, min(p.s3a_ipc, p.hpc - j0));
+                    mega_release(a, s, c); c++;
+                }
                 consumer_sync();
                 stamp(step);
-                ch = mega_acquire(a, s, c);
                 stamp(step);
-                mega_s3_down(a, s, ch, x_mid, x_out);
-                mega_release(a, s, c); c++;
+                mega_s3_down(a, s, c, x_mid, x_out);
                 stamp(step);
                 mega_grid_sync(a, s, epoch);
                 stamp(step);
