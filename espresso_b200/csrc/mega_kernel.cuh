@@ -252,49 +252,70 @@ __device__ __forceinline__ void mega_stage_norm(const MegaArgs& a, const MegaSha
     consumer_sync();
 }
 
-// Dot products of two fp16 rows held in shared memory with the staged vector.
-__device__ __forceinline__ void mega_dot2(const uint8_t* r0, const uint8_t* r1, int K, const float* xs, int lane, float& o0, float& o1) {
-    const float4* xs4 = reinterpret_cast<const float4*>(xs);
-    float a0 = 0.f, a1 = 0.f;
-    const int iters = (K + 255) / 256;
-    for (int it = 0; it < iters; it++) {
-        const int k = it * 256 + lane * 8;
-        if (k < K) {
-            const uint4 w0 = lds128(r0 + (size_t)k * 2), w1 = lds128(r1 + (size_t)k * 2);
-            const float4 xa = xs4[(it * 2) * 32 + lane], xb = xs4[(it * 2 + 1) * 32 + lane];
-            const float x[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-            fma_vec16<WT_F16>(w0, nullptr, 0, x, 0.f, a0);
-            fma_vec16<WT_F16>(w1, nullptr, 0, x, 0.f, a1);
-        }
-    }
-    o0 = warp_sum(a0);
-    o1 = warp_sum(a1);
+// Products of one 16-byte vector of fp16 weights with 8 activations, split over two accumulators so that the
+// dependent FMA chain is 4 long instead of 8.
+__device__ __forceinline__ void mega_fma8(const uint4& w, const float4& xa, const float4& xb, float& even, float& odd) {
+    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+    const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w.z));
+    const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&w.w));
+    even = fmaf(f0.x, xa.x, even); odd = fmaf(f0.y, xa.y, odd);
+    even = fmaf(f1.x, xa.z, even); odd = fmaf(f1.y, xa.w, odd);
+    even = fmaf(f2.x, xb.x, even); odd = fmaf(f2.y, xb.y, odd);
+    even = fmaf(f3.x, xb.z, even); odd = fmaf(f3.y, xb.w, odd);
 }
 
-// Dot products of four fp16 rows held in shared memory with the staged vector (results in every lane).
-__device__ __forceinline__ void mega_dot4(const uint8_t* base, int row_bytes, int K, const float* xs, int lane, float (&o)[4]) {
+// Dot products of NR fp16 rows held in shared memory (row r at base + r * row_bytes) with the staged vector; the
+// results are in every lane.  Two 256-element slices are in flight per pass: all of their shared-memory loads are
+// issued before the first multiply, and every row has four independent accumulators (the consumer warps are too
+// few to hide the load and FMA latencies of a one-slice-at-a-time loop: that form measured ~400 cycles per slice).
+template <int NR>
+__device__ __forceinline__ void mega_dot_rows(const uint8_t* base, int row_bytes, int K, const float* xs, int lane, float (&o)[NR]) {
     const float4* xs4 = reinterpret_cast<const float4*>(xs);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[NR][4];
+#pragma unroll
+    for (int r = 0; r < NR; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
     const int iters = (K + 255) / 256;
-    for (int it = 0; it < iters; it++) {
-        const int k = it * 256 + lane * 8;
-        if (k < K) {
-            uint4 w[4];
+    for (int it = 0; it < iters; it += 2) {
+        const int k0 = it * 256 + lane * 8, k1 = k0 + 256;
+        const bool in0 = k0 < K, in1 = k1 < K;
+        uint4 w0[NR], w1[NR];
 #pragma unroll
-            for (int r = 0; r < 4; r++) w[r] = lds128(base + (size_t)r * row_bytes + (size_t)k * 2);
-            const float4 xa = xs4[(it * 2) * 32 + lane], xb = xs4[(it * 2 + 1) * 32 + lane];
-            const float x[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        for (int r = 0; r < NR; r++) {
+            w0[r] = in0 ? lds128(base + (size_t)r * row_bytes + (size_t)k0 * 2) : make_uint4(0, 0, 0, 0);
+            w1[r] = in1 ? lds128(base + (size_t)r * row_bytes + (size_t)k1 * 2) : make_uint4(0, 0, 0, 0);
+        }
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 xa0 = in0 ? xs4[(it * 2) * 32 + lane] : z, xb0 = in0 ? xs4[(it * 2 + 1) * 32 + lane] : z;
+        const float4 xa1 = in1 ? xs4[(it * 2 + 2) * 32 + lane] : z, xb1 = in1 ? xs4[(it * 2 + 3) * 32 + lane] : z;
 #pragma unroll
-            for (int r = 0; r < 4; r++) fma_vec16<WT_F16>(w[r], nullptr, 0, x, 0.f, acc[r]);
+        for (int r = 0; r < NR; r++) {
+            mega_fma8(w0[r], xa0, xb0, acc[r][0], acc[r][1]);
+            mega_fma8(w1[r], xa1, xb1, acc[r][2], acc[r][3]);
         }
     }
+    float t[NR];
+#pragma unroll
+    for (int r = 0; r < NR; r++) t[r] = (acc[r][0] + acc[r][1]) + (acc[r][2] + acc[r][3]);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
 #pragma unroll
-        for (int r = 0; r < 4; r++) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], off);
+        for (int r = 0; r < NR; r++) t[r] += __shfl_xor_sync(0xffffffffu, t[r], off);
     }
 #pragma unroll
-    for (int r = 0; r < 4; r++) o[r] = acc[r];
+    for (int r = 0; r < NR; r++) o[r] = t[r];
+}
+
+// Two rows at arbitrary addresses (r1 - r0 is the row pitch).
+__device__ __forceinline__ void mega_dot2(const uint8_t* r0, const uint8_t* r1, int K, const float* xs, int lane, float& o0, float& o1) {
+    float o[2];
+    mega_dot_rows<2>(r0, (int)(r1 - r0), K, xs, lane, o);
+    o0 = o[0];
+    o1 = o[1];
+}
+
+__device__ __forceinline__ void mega_dot4(const uint8_t* base, int row_bytes, int K, const float* xs, int lane, float (&o)[4]) {
+    mega_dot_rows<4>(base, row_bytes, K, xs, lane, o);
 }
 
 // S1: q/k/v rows of this CTA (pairs that RoPE rotates together), RoPE, q store and KV-cache append.
@@ -509,6 +530,7 @@ __device__ __forceinline__ void mega_s3_down(const MegaArgs& a, const MegaShared
         for (int g = 0; g < kMegaDownGroups; g++) {
             const int col = threadIdx.x * 4 + g * kMegaConsumers * 4;
             if (col < d) {
+#pragma unroll 4
                 for (int j = 0; j < nj; j++) {
                     const uint2 w = lds64(chunk + (size_t)j * p.row_bytes + (size_t)col * 2);
                     const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
