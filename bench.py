@@ -161,8 +161,8 @@ def run_cpu_oracle(workload: dict, steps: int, warmup: int, threads: int | None 
     import oracle
 
     lib = oracle.lib()
-    if threads:
-        lib.esp_oracle_set_num_threads(threads)
+    # all host cores, also under torchrun (which exports OMP_NUM_THREADS=1 to its workers)
+    lib.esp_oracle_set_num_threads(threads or len(os.sched_getaffinity(0)))
     cores = lib.esp_oracle_num_threads()
     cfg = workload["cfg"]()
     decode = workload["decode"]
