@@ -285,6 +285,7 @@ struct NcclApi {
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
     bool ok = false;
@@ -298,6 +299,7 @@ static NcclApi& nccl_api() {
         api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
         api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
         api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(h, "ncclAllReduce"));
+        api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(h, "ncclAllGather"));
         api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
         api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
         api.ok = api.GetUniqueId && api.CommInitRank && api.AllReduce && api.CommDestroy && api.GetErrorString;
@@ -315,6 +317,9 @@ Engine::~Engine() {
     if (cfg_.device >= 0) cudaSetDevice(cfg_.device);
     if (stream_) cudaStreamSynchronize(stream_);
     for (auto& g : graphs_) cudaGraphExecDestroy(g.second);  // graphs hold captured collectives: they go first
+    for (int p = 0; p < 8; p++)
+        if (tp_peer_block_[p] && p != tp_rank_) cudaIpcCloseMemHandle(tp_peer_block_[p]);
+    if (tp_block_) cudaFree(tp_block_);
     if (nccl_comm_ && nccl_api().ok) {
         cudaDeviceSynchronize();
         nccl_api().CommDestroy(static_cast<ncclComm_t>(nccl_comm_));
@@ -660,6 +665,7 @@ int32_t Engine::finalize() {
     if ((rc = dev_alloc(owned_, &d_debug_, dbg))) return rc;
     ESP_CUDA_TRY(cudaDeviceSynchronize());
     if ((rc = build_tc())) return rc;  // first: it makes the fp16 expansions the persistent kernel may pack
+    if (tp_size_ > 1 && tc_ready_ && (rc = tp_peer_setup())) return rc;
     if ((rc = build_mega())) return rc;
     finalized_ = true;
     return reset();
@@ -900,10 +906,10 @@ int32_t Engine::feed_rows(int rows, const int* seq, const uint32_t* tok, bool wi
     if ((rc = submit(rows, STEP_FORWARD | (with_head ? STEP_HEAD : 0)))) return rc;
     if (with_head) ESP_CUDA_TRY(cudaMemcpyAsync(h_next_, rs_.next, sizeof(uint32_t) * rows, cudaMemcpyDeviceToHost, stream_));
     ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
-    if (tc_ready_ && rows >= kTcMinRows) {
+    if (tc_ready_ && (rows >= kTcMinRows || tp_size_ > 1)) {
         int herr = 0;
         ESP_CUDA_TRY(cudaMemcpy(&herr, d_tc_error_, sizeof(int), cudaMemcpyDeviceToHost));
-        if (herr) return fail(ESP_CUDA_ERR_TIMEOUT, "tensor-core GEMM gave up waiting on a barrier");
+        if (herr) return fail(ESP_CUDA_ERR_TIMEOUT, herr == 8 ? "peer all-reduce gave up waiting for another rank" : "tensor-core GEMM gave up waiting on a barrier");
     }
     for (int s = 0; s < m_.n_seq; s++) h_visible_[s] += extra[s];
     if (with_head && next_out) memcpy(next_out, h_next_, sizeof(uint32_t) * rows);
@@ -1175,6 +1181,11 @@ int32_t Engine::decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, 
     if (max_lim > 1) timings_.kernel_launches += (max_lim - 1) * launches_last_step_;
     ESP_CUDA_TRY(cudaMemcpyAsync(h_rows_block_, d_rows_block_, sizeof(int) * 6 * max_rows_, cudaMemcpyDeviceToHost, stream_));
     ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    if (tc_ready_ && (n_seq >= kTcMinRows || tp_size_ > 1)) {  // bounded device waits report here
+        int herr = 0;
+        ESP_CUDA_TRY(cudaMemcpy(&herr, d_tc_error_, sizeof(int), cudaMemcpyDeviceToHost));
+        if (herr) return fail(ESP_CUDA_ERR_TIMEOUT, herr == 8 ? "peer all-reduce gave up waiting for another rank" : "tensor-core GEMM gave up waiting on a barrier");
+    }
     if (device_ms) ESP_CUDA_TRY(cudaEventElapsedTime(device_ms, ev_begin_, ev_end_));
     for (int s = 0; s < n_seq; s++) {
         int n = std::min(h_rows_block_[4 * max_rows_ + s], lim[s]);
@@ -1212,6 +1223,152 @@ int32_t Engine::tp_init(const uint8_t* unique_id, int32_t nbytes) {
     ncclResult_t r = api.CommInitRank(&comm, tp_size_, id, tp_rank_);
     if (r != ncclSuccess) return nccl_fail(r, "ncclCommInitRank");
     nccl_comm_ = comm;
+    return ESP_CUDA_OK;
+}
+
+// ---- all-reduce over peer memory (NVLink loads and stores; no multicast, no library kernel touches a peer) ----
+// Exchange block of a rank: [partial buffer 0][partial buffer 1][arrival flags: one uint32 per rank].
+// One all-reduce = one launch per rank: announce "my partial n is complete" in every peer's flag array, wait (bounded)
+// until every peer has announced n, then read the peers' partials and add them in rank order (the same order on every
+// rank, so all ranks hold bit-identical sums and keep choosing the same tokens).  Buffers alternate: a rank may
+// overwrite buffer n%2 for all-reduce n+2 only after it passed the wait of n+1, which every peer reaches after it has
+// finished reading n.  An even number of all-reduces per decode step keeps the parity of a captured graph fixed.
+constexpr unsigned kTpSpinLimit = 1u << 22;  // a couple of seconds of polling
+
+struct TpSumArgs {
+    const float* partial[8];     // every rank's current partial buffer (own one included), index = rank
+    unsigned int* peer_flags[8]; // every rank's arrival flags
+    unsigned int* my_flags;
+    unsigned int* epoch;         // [0] completed all-reduces, [1] CTA ticket (local)
+    float* out;
+    int world, rank, count4;
+    int* error;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_peer_v4(const float* p) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(256) k_tp_sum_peers(const TpSumArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();  // this rank's partial (written by the previous kernels of the stream) is complete and visible
+    __shared__ unsigned int s_epoch;
+    if (threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(a.epoch) + 1u;
+    __syncthreads();
+    const unsigned int epoch = s_epoch;
+    const int p = threadIdx.x;
+    if (p < a.world && p != a.rank) {
+        if (blockIdx.x == 0) {
+            __threadfence_system();
+            st_release_sys(a.peer_flags[p] + a.rank, epoch);
+        }
+        unsigned spins = __ldcg(a.error) != 0 ? kTpSpinLimit : 0u;  // after a timeout nothing waits any more
+        while ((int)(ld_acquire_sys(a.my_flags + p) - epoch) < 0) {  // peers may already be one all-reduce ahead
+            if (++spins > kTpSpinLimit || ((spins & 0xfffu) == 0 && __ldcg(a.error) != 0)) {
+                atomicCAS(a.error, 0, 8);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < a.count4; i += gridDim.x * blockDim.x) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+        for (int r = 0; r < a.world; r++) {
+            const float4 v = r == a.rank ? __ldcg(reinterpret_cast<const float4*>(a.partial[r]) + i) : ld_peer_v4(a.partial[r] + (size_t)i * 4);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        reinterpret_cast<float4*>(a.out)[i] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int t = atomicAdd(a.epoch + 1, 1u);
+        if (t == gridDim.x - 1) {  // last CTA: this all-reduce is complete on this rank
+            a.epoch[1] = 0u;
+            *reinterpret_cast<volatile unsigned int*>(a.epoch) = epoch;
+            __threadfence();
+        }
+    }
+}
+
+float* Engine::tp_current_partial() const {
+    if (!tp_peer_ready_) return tp_partial_;
+    return reinterpret_cast<float*>(tp_block_) + (size_t)tp_parity_ * tp_buf_floats_;
+}
+
+// Collective: every rank calls it once (from finalize).  On any failure the engine keeps the NCCL all-reduce.
+int32_t Engine::tp_peer_setup() {
+    tp_peer_ready_ = false;
+    if (tp_size_ <= 1 || tp_size_ > 8 || !nccl_comm_ || getenv("ESP_CUDA_TP_NCCL_ONLY")) return ESP_CUDA_OK;
+    NcclApi& api = nccl_api();
+    if (!api.AllGather) return ESP_CUDA_OK;
+    tp_buf_floats_ = ((size_t)max_rows_ * m_.d_model + 63) / 64 * 64;
+    const size_t block_bytes = 2 * tp_buf_floats_ * sizeof(float) + 256;
+    ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&tp_block_), block_bytes));
+    ESP_CUDA_TRY(cudaMemset(tp_block_, 0, block_bytes));
+    int32_t rc;
+    if ((rc = dev_alloc(owned_, &tp_epoch_, 2))) return rc;
+    cudaIpcMemHandle_t mine;
+    ESP_CUDA_TRY(cudaIpcGetMemHandle(&mine, tp_block_));
+    uint8_t* d_handles = nullptr;
+    ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_handles), sizeof(mine) * (size_t)(tp_size_ + 1)));
+    std::vector<cudaIpcMemHandle_t> all((size_t)tp_size_);
+    cudaError_t e = cudaMemcpy(d_handles + sizeof(mine) * tp_size_, &mine, sizeof(mine), cudaMemcpyHostToDevice);
+    ncclResult_t r = ncclSuccess;
+    if (e == cudaSuccess) r = api.AllGather(d_handles + sizeof(mine) * tp_size_, d_handles, sizeof(mine), ncclInt8, static_cast<ncclComm_t>(nccl_comm_), stream_);
+    if (e == cudaSuccess && r == ncclSuccess) e = cudaStreamSynchronize(stream_);
+    if (e == cudaSuccess && r == ncclSuccess) e = cudaMemcpy(all.data(), d_handles, sizeof(mine) * tp_size_, cudaMemcpyDeviceToHost);
+    cudaFree(d_handles);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclAllGather");
+    ESP_CUDA_TRY(e);
+    bool ok = true;
+    for (int p = 0; p < tp_size_; p++) {
+        if (p == tp_rank_) { tp_peer_block_[p] = tp_block_; continue; }
+        void* ptr = nullptr;
+        if (cudaIpcOpenMemHandle(&ptr, all[(size_t)p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); ok = false; break; }
+        tp_peer_block_[p] = static_cast<uint8_t*>(ptr);
+    }
+    // all ranks must agree: one that could not map a peer makes everybody fall back
+    unsigned long long* d_ok = nullptr;
+    ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_ok), 16));
+    unsigned long long h_ok = ok ? 0ull : 1ull;  // max over ranks of "failed"
+    e = cudaMemcpy(d_ok, &h_ok, 8, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) r = api.AllReduce(d_ok, d_ok + 1, 1, ncclUint64, ncclMax, static_cast<ncclComm_t>(nccl_comm_), stream_);
+    if (e == cudaSuccess && r == ncclSuccess) e = cudaStreamSynchronize(stream_);
+    if (e == cudaSuccess && r == ncclSuccess) e = cudaMemcpy(&h_ok, d_ok + 1, 8, cudaMemcpyDeviceToHost);
+    cudaFree(d_ok);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclAllReduce");
+    ESP_CUDA_TRY(e);
+    tp_peer_ready_ = h_ok == 0ull;
+    tp_parity_ = 0;
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::tp_sum_peers(float* out, int rows, cudaStream_t s) {
+    TpSumArgs a{};
+    for (int p = 0; p < tp_size_; p++) {
+        a.partial[p] = reinterpret_cast<const float*>(tp_peer_block_[p]) + (size_t)tp_parity_ * tp_buf_floats_;
+        a.peer_flags[p] = reinterpret_cast<unsigned int*>(tp_peer_block_[p] + 2 * tp_buf_floats_ * sizeof(float));
+    }
+    a.my_flags = a.peer_flags[tp_rank_];
+    a.epoch = tp_epoch_;
+    a.out = out;
+    a.world = tp_size_; a.rank = tp_rank_;
+    a.count4 = rows * m_.d_model / 4;
+    a.error = d_tc_error_;
+    const int grid = std::max(1, std::min(sm_count_, (a.count4 + 1023) / 1024));
+    ESP_CUDA_TRY(launch_pdl(k_tp_sum_peers, dim3(grid), dim3(256), 0, s, a));
+    tp_parity_ ^= 1;
     return ESP_CUDA_OK;
 }
 
@@ -1292,6 +1449,7 @@ const CUtensorMap* Engine::activation_map(const uint16_t* buf, int K, int tile) 
 int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
     const bool gpt2 = m_.arch == ARCH_GPT2;
     if (!tc_tile_for(rows)) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "too many rows for one tensor-core pass");
+    tp_parity_ = 0;  // a step holds an even number of all-reduces: every step starts on partial buffer 0
     int launches = 0;
     float* dbg = debug_layer_ >= 0 ? d_debug_ : nullptr;
     const int q = m_.q_dim, kv = m_.kv_dim, d = m_.d_model, h = m_.hidden;
@@ -1347,14 +1505,16 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
         const TcPlan plan = tc_plan(tiles_of(W.rows), rows, W.cols / kTcBlockK, true, false, sm_count_);
         if (tp_size_ <= 1) return gemm(plan, false, {{&W, act_.hidden, d, bias}}, xbuf, TC_RESIDUAL, nullptr, 0, nullptr);
         int32_t prc;
+        float* partial = tp_current_partial();
         if (tp_rank_ == 0) {
-            ESP_CUDA_TRY(cudaMemcpyAsync(tp_partial_, act_.hidden, sizeof(float) * (size_t)rows * d, cudaMemcpyDeviceToDevice, s));
-            if ((prc = gemm(plan, false, {{&W, tp_partial_, d, bias}}, xbuf, TC_RESIDUAL, nullptr, 0, nullptr))) return prc;
+            ESP_CUDA_TRY(cudaMemcpyAsync(partial, act_.hidden, sizeof(float) * (size_t)rows * d, cudaMemcpyDeviceToDevice, s));
+            if ((prc = gemm(plan, false, {{&W, partial, d, bias}}, xbuf, TC_RESIDUAL, nullptr, 0, nullptr))) return prc;
         } else {
-            if (plan.splits > 1) ESP_CUDA_TRY(cudaMemsetAsync(tp_partial_, 0, sizeof(float) * (size_t)rows * d, s));
-            if ((prc = gemm(plan, false, {{&W, tp_partial_, d, nullptr}}, xbuf, TC_STORE, nullptr, 0, nullptr))) return prc;
+            if (plan.splits > 1) ESP_CUDA_TRY(cudaMemsetAsync(partial, 0, sizeof(float) * (size_t)rows * d, s));
+            if ((prc = gemm(plan, false, {{&W, partial, d, nullptr}}, xbuf, TC_STORE, nullptr, 0, nullptr))) return prc;
         }
-        return all_reduce(tp_partial_, act_.hidden, (size_t)rows * d, true, s);
+        if (tp_peer_ready_) { launches++; return tp_sum_peers(act_.hidden, rows, s); }
+        return all_reduce(partial, act_.hidden, (size_t)rows * d, true, s);
     };
     auto copy_dbg = [&](const float* src, int offset, int n) {
         if (dbg) { k_copy_debug<<<(n + 255) / 256, 256, 0, s>>>(src, dbg + offset, n); launches++; }

@@ -136,7 +136,17 @@ private:
     int tp_rank_ = 0, tp_size_ = 1;
     int vocab_global_ = 0;
     void* nccl_comm_ = nullptr;
-    float* tp_partial_ = nullptr;  // [max_rows][d_model] partial projection before the all-reduce
+    float* tp_partial_ = nullptr;  // [max_rows][d_model] partial projection before the all-reduce (NCCL path)
+    // Peer-memory all-reduce: every rank maps every other rank's exchange block (two partial buffers + arrival flags)
+    int32_t tp_peer_setup();
+    int32_t tp_sum_peers(float* out, int rows, cudaStream_t s);  // out = sum over ranks of the current partial buffer
+    float* tp_current_partial() const;  // where this rank's partial of the next all-reduce goes
+    bool tp_peer_ready_ = false;
+    uint8_t* tp_block_ = nullptr;               // this rank's exchange block (cudaMalloc, exported with cudaIpc)
+    uint8_t* tp_peer_block_[8] = {};            // mapped exchange blocks, index = rank (own block at own index)
+    size_t tp_buf_floats_ = 0;                  // floats per partial buffer
+    unsigned int* tp_epoch_ = nullptr;          // [2] local: completed all-reduces, CTA ticket
+    int tp_parity_ = 0;                         // partial buffer of the next all-reduce (host side, fixed at graph capture)
 
     // batched tensor-core path (rows >= kTcMinRows, 16-bit weights)
     bool tc_ready_ = false;
