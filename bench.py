@@ -234,6 +234,32 @@ def gemv_table(runtime, device: int, peak: float) -> dict:
     return out
 
 
+def stage_trace_us(eng, cfg, prompt, n_decode: int, sm_mhz: float) -> dict:
+    """Per-layer averages (microseconds) of the persistent kernel's stage stamps for the last decoded token; empty when
+    the engine decodes with the per-stage kernels."""
+    import numpy as np
+
+    names = ["s1_norm", "s1_wait_weights", "s1_rows", "s1_barrier", "s2_wait_weights", "s2_attention_projection", "s2_barrier", "s3_norm",
+             "s3_wait_weights", "s3_gate_up", "s3_wait_weights2", "s3_down", "s3_barrier"]
+    eng.prefill(prompt)
+    eng.decode(n_decode)
+    eng.stage_trace(100)  # selects the CTA whose stamps the next loop records
+    eng.prefill(prompt)
+    eng.decode(n_decode)
+    t = eng.stage_trace(100).astype(np.float64) / sm_mhz
+    L = cfg.nLayer
+    if t.size < 14 * L + 4 or not t.any():
+        return {}
+    per = np.zeros(13)
+    for layer in range(L):
+        per += np.diff(t[14 * layer:14 * layer + 14])
+    head = np.diff(t[14 * L:14 * L + 4])
+    out = {n: round(float(v) / L, 2) for n, v in zip(names, per)}
+    out.update({"head_norm": round(float(head[0]), 2), "head_rows": round(float(head[1]), 2), "head_barrier": round(float(head[2]), 2),
+                "cta": 100, "note": "per-layer means over the last token, SM clock stamps of one CTA"})
+    return out
+
+
 def gemm_table(runtime, device: int, peak: float) -> dict:
     """Kernel-level Y = X.W^T on the tensor cores (the batched path's product) on an LM-head sized fp16 matrix."""
     import numpy as np
@@ -474,6 +500,10 @@ def main() -> None:
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
         }
         line.update(extra)
+        if rank == 0 and draft is None and n_seq == 1:
+            st = stage_trace_us(eng, cfg, prompts[0], n_decode, clocks.get("sm_mhz") or 1965.0)
+            if st:
+                line["stage_trace_us"] = st
         if rank == 0 and not args.no_gemv_table:
             line["gemv"] = gemv_table(runtime, local_rank, peak)
             line["gemm_tc"] = gemm_table(runtime, local_rank, peak)

@@ -1630,8 +1630,8 @@ int32_t Engine::build_mega() {
     p.s2_bytes = pad128((long long)p.rpb * m_.head_dim * 2);
     p.s3a_bytes = pad128((long long)2 * p.hpc * p.row_bytes);
     p.s3b_bytes = pad128((long long)p.hpc * p.row_bytes);
-    // A stage slice of up to 64 KB travels as one chunk; larger ones as chunks of about 48 KB of whole items.
-    const int kWhole = 64 * 1024, kTarget = 48 * 1024;
+    // A stage slice of up to 64 KB travels as one chunk; larger ones as chunks of up to 64 KB of whole items.
+    const int kWhole = 64 * 1024, kTarget = 64 * 1024;  // 64 KB = eight 2048-wide row pairs: one per consumer warp
     auto per_chunk = [&](int items, int item_bytes, int multiple) {
         if ((long long)items * item_bytes <= kWhole) return std::max(items, 1);
         int n = std::max(1, kTarget / item_bytes);

@@ -150,8 +150,9 @@ ESP_CUDA_API int32_t esp_cuda_load_tensor(esp_cuda_engine* engine, const char* n
  * created with the GLOBAL model shape and tp_rank / tp_size in the config.  Rank r then expects its Megatron
  * shard from esp_cuda_load_tensor: rows [r*n/G, (r+1)*n/G) of wq, wk, wv, w1, w3, lm_head (n = that matrix's row
  * count), the matching COLUMNS of wo and w2 (stored row-major [d_model, n/G]), and full copies of the embedding
- * and the norm gains.  An NCCL all-reduce follows the Wo and W2 products, and the vocabulary-sharded argmax is
- * merged with a max-reduce.  esp_cuda_tp_unique_id (rank 0; share the 128 bytes with the other ranks) and
+ * and the norm gains.  An all-reduce follows the Wo and W2 products (over IPC-mapped peer memory with this library's
+ * own kernel; NCCL when a peer cannot be mapped or ESP_CUDA_TP_NCCL_ONLY is set), and the vocabulary-sharded argmax
+ * is merged with an NCCL max-reduce.  esp_cuda_tp_unique_id (rank 0; share the 128 bytes with the other ranks) and
  * esp_cuda_tp_init (every rank; collective) must run before esp_cuda_finalize.  Every rank must then make the same
  * sequence of decode calls. */
 ESP_CUDA_API int32_t esp_cuda_tp_unique_id(uint8_t* out, int32_t capacity);
