@@ -403,6 +403,39 @@ def test_quantised_batch_uses_fp16_expansion_and_matches_oracle(rt, oracle_lib, 
     eng.close()
 
 
+@pytest.mark.parametrize("kind", ["f16", "q8_0"])
+def test_persistent_kernel_streams_wide_stages_in_chunks(rt, oracle_lib, tmp_models, kind):
+    """d_model 2048 / hidden 5632: every stage slice of the persistent kernel exceeds a ring slot and arrives in chunks
+    (q/k/v pairs, Wo rows, gate/up pairs, down rows); the quantised variant packs the fp16 expansion of the blocks."""
+    from espresso_b200.model_config import MultiModelConfig
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = MultiModelConfig("wide-gqa", 2, 32, 4, 2048, 64, 5632, 768, 64, 1e-5, 10000.0, None, "llama")
+    prompt = synthetic_prompt(cfg.vocab, 12)
+    if kind == "f16":
+        d = tmp_models(cfg)
+        eng = rt.DecodeEngine.build(d)
+        ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(d))
+    else:
+        model, uploads = quantised_pair(oracle_lib, cfg, kind)
+        eng = rt.DecodeEngine.empty(cfg)
+        upload_all(eng, uploads)
+        ora = oracle_lib.Runtime(model)
+    res = eng.generate(prompt, 24)
+    assert eng.timings()["kernel_launches"] == 1  # the whole greedy loop was one persistent launch
+    compare_greedy_stream(ora, prompt, res.tokens)
+    # same tokens from the per-stage kernels
+    flags = rt.FLAG_NO_MEGAKERNEL
+    if kind == "f16":
+        ref = rt.DecodeEngine.build(tmp_models(cfg), flags=flags)
+    else:
+        ref = rt.DecodeEngine.empty(cfg, flags=flags)
+        upload_all(ref, uploads)
+    compare_greedy_stream(ora, prompt, ref.generate(prompt, 24).tokens)
+    ref.close()
+    eng.close()
+
+
 def test_long_context_split_kv_attention(rt, oracle_lib, tmp_models):
     """Positions beyond one attention split (256) exercise the split-KV merge."""
     from espresso_b200.model_config import MultiModelConfig
