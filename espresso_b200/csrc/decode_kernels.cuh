@@ -266,12 +266,16 @@ __device__ __forceinline__ void dot_rows(const uint8_t* const (&wrow)[NR], const
     const int iters = (K + 32 * EPL - 1) / (32 * EPL);
     for (int it0 = 0; it0 < iters; it0 += U) {
         uint4 w[U][NR];
+        __half sc[U][NR];  // block scales of the quantised types, requested together with the weights
 #pragma unroll
         for (int u = 0; u < U; u++) {
             const int k = (it0 + u) * 32 * EPL + lane * EPL;
             const size_t byte_off = WT == WT_Q8_0 ? (size_t)k : WT == WT_Q4_0 ? (size_t)k / 2 : (size_t)k * 2;
 #pragma unroll
-            for (int r = 0; r < NR; r++) w[u][r] = k < K ? ld_weight16(wrow[r] + byte_off) : make_uint4(0, 0, 0, 0);
+            for (int r = 0; r < NR; r++) {
+                w[u][r] = k < K ? ld_weight16(wrow[r] + byte_off) : make_uint4(0, 0, 0, 0);
+                if constexpr (WT == WT_Q8_0 || WT == WT_Q4_0) sc[u][r] = k < K ? srow[r][k >> 5] : __float2half(0.f);
+            }
         }
 #pragma unroll
         for (int u = 0; u < U; u++) {
@@ -286,14 +290,13 @@ __device__ __forceinline__ void dot_rows(const uint8_t* const (&wrow)[NR], const
                 } else if constexpr (WT == WT_Q8_0) {
                     const uint4 xa = xh4[(it * 2) * 32 + lane], xb = xh4[(it * 2 + 1) * 32 + lane];
 #pragma unroll
-                    for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(srow[r][k >> 5]), q8_block_dot(w[u][r], xa, xb), acc[r]);
+                    for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(sc[u][r]), q8_block_dot(w[u][r], xa, xb), acc[r]);
                 } else {
                     const uint4 x0 = xh4[(it * 4) * 32 + lane], x1 = xh4[(it * 4 + 1) * 32 + lane];
                     const uint4 x2 = xh4[(it * 4 + 2) * 32 + lane], x3 = xh4[(it * 4 + 3) * 32 + lane];
-#pragma unroll
                     const float bs = q4_block_sums(xs, K)[k >> 5];
 #pragma unroll
-                    for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(srow[r][k >> 5]), q4_block_dot(w[u][r], x0, x1, x2, x3) - bs, acc[r]);
+                    for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(sc[u][r]), q4_block_dot(w[u][r], x0, x1, x2, x3) - bs, acc[r]);
                 }
             }
         }

@@ -1800,17 +1800,29 @@ __global__ void __launch_bounds__(kThreads) k_gemv_plain(Weight w, const float* 
     float* xs = smem + kRedFloats;
     const float xdescale = stage_vector<WT>(x, w.cols, NORM_NONE, nullptr, nullptr, 0.f, xs, smem);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n_items = (w.rows + 1) / 2;
+    // rows per warp pass: the quantised types read 2-4x more staged activation bytes per weight byte than fp16, so
+    // they share one activation read between four rows
+    constexpr int NR = (WT == WT_Q8_0 || WT == WT_Q4_0) ? 4 : 2;
+    const int n_items = (w.rows + NR - 1) / NR;
     int begin, end;
     cta_range(n_items, blockIdx.x, gridDim.x, begin, end);
     for (int item = begin + warp; item < end; item += kWarps) {
-        int row0 = item * 2, row1 = min(row0 + 1, w.rows - 1);
-        const uint8_t* wr[2] = {weight_row(w, row0), weight_row(w, row1)};
-        const __half* sr[2] = {scale_row(w, row0), scale_row(w, row1)};
-        float acc[2] = {0.f, 0.f};
-        dot_rows<WT, 2>(wr, sr, w.cols, xs, lane, acc);
-        float v0 = warp_sum(acc[0]) * xdescale, v1 = warp_sum(acc[1]) * xdescale;
-        if (lane == 0) { y[row0] = v0; if (row1 != row0) y[row1] = v1; }
+        const uint8_t* wr[NR];
+        const __half* sr[NR];
+        float acc[NR];
+#pragma unroll
+        for (int r = 0; r < NR; r++) {
+            const int row = min(item * NR + r, w.rows - 1);
+            wr[r] = weight_row(w, row);
+            sr[r] = scale_row(w, row);
+            acc[r] = 0.f;
+        }
+        dot_rows<WT, NR>(wr, sr, w.cols, xs, lane, acc);
+#pragma unroll
+        for (int r = 0; r < NR; r++) {
+            const float v = warp_sum(acc[r]) * xdescale;
+            if (lane == 0 && item * NR + r < w.rows) y[item * NR + r] = v;
+        }
     }
 }
 
