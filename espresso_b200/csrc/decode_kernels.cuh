@@ -256,50 +256,69 @@ __device__ __forceinline__ const float* q4_block_sums(const float* xs, int K) { 
 // reduces across the warp (and, for the quantised types, multiplies by the activation de-scale factor).
 // K must be a multiple of EPL.  The loads of U consecutive 16-byte slices of all NR rows are issued before
 // any arithmetic so that each lane keeps U*NR*16 bytes in flight.
+// One "group" = U consecutive 16-byte slices of NR rows, with the block scales of the quantised types.
+constexpr int kDotU = 4;
+template <int WT, int NR>
+struct DotGroup {
+    uint4 w[kDotU][NR];
+    __half sc[kDotU][NR];
+};
+
+template <int WT, int NR>
+__device__ __forceinline__ void dot_load(DotGroup<WT, NR>& g, const uint8_t* const (&wrow)[NR], const __half* const (&srow)[NR], int K, int it0,
+                                         int lane) {
+    constexpr int EPL = WTraits<WT>::EPL;
+#pragma unroll
+    for (int u = 0; u < kDotU; u++) {
+        const int k = (it0 + u) * 32 * EPL + lane * EPL;
+        const size_t byte_off = WT == WT_Q8_0 ? (size_t)k : WT == WT_Q4_0 ? (size_t)k / 2 : (size_t)k * 2;
+#pragma unroll
+        for (int r = 0; r < NR; r++) {
+            g.w[u][r] = k < K ? ld_weight16(wrow[r] + byte_off) : make_uint4(0, 0, 0, 0);
+            if constexpr (WT == WT_Q8_0 || WT == WT_Q4_0) g.sc[u][r] = k < K ? srow[r][k >> 5] : __float2half(0.f);
+        }
+    }
+}
+
+template <int WT, int NR>
+__device__ __forceinline__ void dot_compute(const DotGroup<WT, NR>& g, int K, int it0, const float* __restrict__ xs, int lane, float (&acc)[NR]) {
+    constexpr int EPL = WTraits<WT>::EPL;
+    const float4* xs4 = reinterpret_cast<const float4*>(xs);
+    const uint4* xh4 = reinterpret_cast<const uint4*>(xs);  // quantised types: fp16 activations, 8 per 16-byte group
+#pragma unroll
+    for (int u = 0; u < kDotU; u++) {
+        const int it = it0 + u;
+        const int k = it * 32 * EPL + lane * EPL;
+        if (k < K) {
+            if constexpr (WT == WT_F16 || WT == WT_BF16) {
+                const float4 va = xs4[(it * 2) * 32 + lane], vb = xs4[(it * 2 + 1) * 32 + lane];
+                const float x[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+                for (int r = 0; r < NR; r++) fma_vec16<WT>(g.w[u][r], nullptr, 0, x, 0.f, acc[r]);
+            } else if constexpr (WT == WT_Q8_0) {
+                const uint4 xa = xh4[(it * 2) * 32 + lane], xb = xh4[(it * 2 + 1) * 32 + lane];
+#pragma unroll
+                for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(g.sc[u][r]), q8_block_dot(g.w[u][r], xa, xb), acc[r]);
+            } else {
+                const uint4 x0 = xh4[(it * 4) * 32 + lane], x1 = xh4[(it * 4 + 1) * 32 + lane];
+                const uint4 x2 = xh4[(it * 4 + 2) * 32 + lane], x3 = xh4[(it * 4 + 3) * 32 + lane];
+                const float bs = q4_block_sums(xs, K)[k >> 5];
+#pragma unroll
+                for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(g.sc[u][r]), q4_block_dot(g.w[u][r], x0, x1, x2, x3) - bs, acc[r]);
+            }
+        }
+    }
+}
+
 template <int WT, int NR>
 __device__ __forceinline__ void dot_rows(const uint8_t* const (&wrow)[NR], const __half* const (&srow)[NR], int K,
                                          const float* __restrict__ xs, int lane, float (&acc)[NR]) {
     constexpr int EPL = WTraits<WT>::EPL;
-    constexpr int U = 4;
-    const float4* xs4 = reinterpret_cast<const float4*>(xs);
-    const uint4* xh4 = reinterpret_cast<const uint4*>(xs);  // quantised types: fp16 activations, 8 per 16-byte group
     const int iters = (K + 32 * EPL - 1) / (32 * EPL);
-    for (int it0 = 0; it0 < iters; it0 += U) {
-        uint4 w[U][NR];
-        __half sc[U][NR];  // block scales of the quantised types, requested together with the weights
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int k = (it0 + u) * 32 * EPL + lane * EPL;
-            const size_t byte_off = WT == WT_Q8_0 ? (size_t)k : WT == WT_Q4_0 ? (size_t)k / 2 : (size_t)k * 2;
-#pragma unroll
-            for (int r = 0; r < NR; r++) {
-                w[u][r] = k < K ? ld_weight16(wrow[r] + byte_off) : make_uint4(0, 0, 0, 0);
-                if constexpr (WT == WT_Q8_0 || WT == WT_Q4_0) sc[u][r] = k < K ? srow[r][k >> 5] : __float2half(0.f);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int it = it0 + u;
-            const int k = it * 32 * EPL + lane * EPL;
-            if (k < K) {
-                if constexpr (WT == WT_F16 || WT == WT_BF16) {
-                    const float4 va = xs4[(it * 2) * 32 + lane], vb = xs4[(it * 2 + 1) * 32 + lane];
-                    const float x[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-#pragma unroll
-                    for (int r = 0; r < NR; r++) fma_vec16<WT>(w[u][r], nullptr, 0, x, 0.f, acc[r]);
-                } else if constexpr (WT == WT_Q8_0) {
-                    const uint4 xa = xh4[(it * 2) * 32 + lane], xb = xh4[(it * 2 + 1) * 32 + lane];
-#pragma unroll
-                    for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(sc[u][r]), q8_block_dot(w[u][r], xa, xb), acc[r]);
-                } else {
-                    const uint4 x0 = xh4[(it * 4) * 32 + lane], x1 = xh4[(it * 4 + 1) * 32 + lane];
-                    const uint4 x2 = xh4[(it * 4 + 2) * 32 + lane], x3 = xh4[(it * 4 + 3) * 32 + lane];
-                    const float bs = q4_block_sums(xs, K)[k >> 5];
-#pragma unroll
-                    for (int r = 0; r < NR; r++) acc[r] = fmaf(__half2float(sc[u][r]), q4_block_dot(w[u][r], x0, x1, x2, x3) - bs, acc[r]);
-                }
-            }
-        }
+    for (int it0 = 0; it0 < iters; it0 += kDotU) {
+        DotGroup<WT, NR> g;
+        dot_load<WT, NR>(g, wrow, srow, K, it0, lane);
+        dot_compute<WT, NR>(g, K, it0, xs, lane, acc);
     }
 }
 

@@ -1806,23 +1806,30 @@ __global__ void __launch_bounds__(kThreads) k_gemv_plain(Weight w, const float* 
     const int n_items = (w.rows + NR - 1) / NR;
     int begin, end;
     cta_range(n_items, blockIdx.x, gridDim.x, begin, end);
-    for (int item = begin + warp; item < end; item += kWarps) {
-        const uint8_t* wr[NR];
-        const __half* sr[NR];
-        float acc[NR];
+    auto rows_of = [&](int item, const uint8_t* (&wr)[NR], const __half* (&sr)[NR]) {
 #pragma unroll
         for (int r = 0; r < NR; r++) {
             const int row = min(item * NR + r, w.rows - 1);
             wr[r] = weight_row(w, row);
             sr[r] = scale_row(w, row);
-            acc[r] = 0.f;
         }
-        dot_rows<WT, NR>(wr, sr, w.cols, xs, lane, acc);
+    };
+    auto finish = [&](int item, float (&acc)[NR]) {
 #pragma unroll
         for (int r = 0; r < NR; r++) {
             const float v = warp_sum(acc[r]) * xdescale;
             if (lane == 0 && item * NR + r < w.rows) y[item * NR + r] = v;
         }
+    };
+    for (int item = begin + warp; item < end; item += kWarps) {
+        const uint8_t* wr[NR];
+        const __half* sr[NR];
+        float acc[NR];
+        rows_of(item, wr, sr);
+#pragma unroll
+        for (int r = 0; r < NR; r++) acc[r] = 0.f;
+        dot_rows<WT, NR>(wr, sr, w.cols, xs, lane, acc);
+        finish(item, acc);
     }
 }
 
