@@ -6,7 +6,7 @@ writes them back out as a weight directory, and that directory must be byte-iden
 written by ``espresso_b200.synthetic`` (this pins the directory layout and the Conv1D transposes).
 The HF logits are the golden values; the tests regenerate the weights from the seed.
 
-    python tests/golden/make_hf_gpt2_golden.py /root/reference
+    python tests/golden/make_hf_gpt2_golden.py <path to the reference checkout>
 """
 import filecmp
 import os
@@ -81,4 +81,6 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: " + sys.argv[0] + " <path to the reference checkout>")
+    main(sys.argv[1])

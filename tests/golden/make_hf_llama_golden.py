@@ -6,7 +6,7 @@ fixture pins the oracle (and the weight-directory layout) against an implementat
 independent of this repository.  The fixture stores only the model seed/shape, the prompt and the
 logits; the tests regenerate the identical weights from the seed.
 
-    python tests/golden/make_hf_llama_golden.py /root/reference
+    python tests/golden/make_hf_llama_golden.py <path to the reference checkout>
 """
 import os
 import shutil
@@ -49,4 +49,6 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: " + sys.argv[0] + " <path to the reference checkout>")
+    main(sys.argv[1])
