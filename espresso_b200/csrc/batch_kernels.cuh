@@ -175,13 +175,13 @@ __global__ void __launch_bounds__(kThreads) k_rope_append(const RopeArgs p) {
     const int r = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
-    if (!p.rs.active[r]) return;
+    const int row_active = p.rs.active[r], pos = p.rs.pos[r], seq = p.rs.seq[r];  // one round trip for the three
+    if (!row_active) return;
     const ModelDims& m = p.m;
     const int half = m.head_dim / 2;
     const int q_pairs = m.q_dim / 2, k_pairs = m.kv_dim / 2;
     const int i = blockIdx.y * kThreads + threadIdx.x;
     if (i >= q_pairs + 2 * k_pairs) return;
-    const int pos = p.rs.pos[r], seq = p.rs.seq[r];
     if (i < q_pairs + k_pairs) {
         const bool is_q = i < q_pairs;
         const int local = is_q ? i : i - q_pairs;
@@ -289,14 +289,10 @@ __global__ void __launch_bounds__(kAttRowsWarps * 32) k_attention_rows(const Att
     const int w = blockIdx.x * kAttRowsWarps + (threadIdx.x >> 5);
     if (w >= p.rows * m.n_head) return;
     const int r = w / m.n_head, head = w - r * m.n_head;
-    if (!p.rs.active[r]) return;
+    // the three row-state words are requested together (one memory round trip, not three)
+    const int row_active = p.rs.active[r], row_pos = p.rs.pos[r], row_seq = p.rs.seq[r];
     const int sub = lane % LPP, slot = lane / LPP;
-    const int visible = p.rs.pos[r] + 1;
-    const int kvh = head / (m.n_head / m.n_kv_head);
-    const size_t base = p.kv.offset(m, p.layer, p.rs.seq[r], kvh, 0) + (size_t)sub * 16;
-    const __half* K = p.kv.k + base;
-    const __half* V = p.kv.v + base;
-    float q[16];
+    float q[16];  // this lane's 16 channels of the query, requested with the row state
     {
         const float4* qp = reinterpret_cast<const float4*>(p.q + (size_t)r * m.q_dim + (size_t)head * HD + sub * 16);
 #pragma unroll
@@ -305,6 +301,12 @@ __global__ void __launch_bounds__(kAttRowsWarps * 32) k_attention_rows(const Att
             q[4 * i] = t.x; q[4 * i + 1] = t.y; q[4 * i + 2] = t.z; q[4 * i + 3] = t.w;
         }
     }
+    if (!row_active) return;
+    const int visible = row_pos + 1;
+    const int kvh = head / (m.n_head / m.n_kv_head);
+    const size_t base = p.kv.offset(m, p.layer, row_seq, kvh, 0) + (size_t)sub * 16;
+    const __half* K = p.kv.k + base;
+    const __half* V = p.kv.v + base;
     const float scale = 1.0f / sqrtf((float)HD);
     float mx = -INFINITY, sum = 0.f, acc[16];
 #pragma unroll
