@@ -260,6 +260,17 @@ def stage_trace_us(eng, cfg, prompt, n_decode: int, sm_mhz: float) -> dict:
     return out
 
 
+def cpu_model() -> str:
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("model name"):
+                    return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
 def gemm_table(runtime, device: int, peak: float) -> dict:
     """Kernel-level Y = X.W^T on the tensor cores (the batched path's product) on an LM-head sized fp16 matrix."""
     import numpy as np
@@ -313,7 +324,7 @@ def main() -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl["label"], "l2": "fp32 weights exceed the host caches"},
-            "cpu_baseline": {"value": r["value"], "unit": unit, "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+            "cpu_baseline": {"value": r["value"], "unit": unit, "cores": r["cores"], "cpu_model": cpu_model(), "kind": "port", "sample": r["sample"]},
             "e2e": {"value": r["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }
         print(json.dumps(line))
@@ -485,6 +496,7 @@ def main() -> None:
                         "whole_step": {"bytes_per_token": bytes_tok, "achieved": per_gpu_tok_s * bytes_tok / 1e9,
                                        "frac": per_gpu_tok_s * bytes_tok / 1e9 / peak}}
 
+        roofline["frac_of_nominal_8000_GBps"] = roofline["achieved"] / 8000.0  # beside the fraction of the measured copy peak
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": total_ms / args.steps, "ms_per_token": total_ms / args.steps / n_decode, "higher_is_better": True,
@@ -504,12 +516,17 @@ def main() -> None:
             st = stage_trace_us(eng, cfg, prompts[0], n_decode, clocks.get("sm_mhz") or 1965.0)
             if st:
                 line["stage_trace_us"] = st
+            tt = eng.token_times_ns()  # of the loop stage_trace_us just ran
+            if tt.size > 2:
+                gaps = np.diff(tt.astype(np.int64)) / 1e6
+                line["ms_per_token_gaps"] = {"median": float(np.median(gaps)), "p95": float(np.percentile(gaps, 95)), "tokens": int(tt.size),
+                                             "note": "GPU-timer gaps between consecutive tokens inside one decode loop"}
         if rank == 0 and not args.no_gemv_table:
             line["gemv"] = gemv_table(runtime, local_rank, peak)
             line["gemm_tc"] = gemm_table(runtime, local_rank, peak)
         if rank == 0 and not args.no_cpu_baseline:
             r = run_cpu_oracle(wl, args.cpu_steps, 1)
-            line["cpu_baseline"] = {"value": r["value"], "unit": unit, "cores": r["cores"], "kind": "port", "sample": r["sample"]}
+            line["cpu_baseline"] = {"value": r["value"], "unit": unit, "cores": r["cores"], "cpu_model": cpu_model(), "kind": "port", "sample": r["sample"]}
         if world > 1:
             dist.barrier()  # members of a tensor-parallel group tear their communicator down together
         eng.close()

@@ -279,6 +279,10 @@ int32_t esp_cuda_stage_trace(esp_cuda_engine* engine, int32_t cta, int64_t* out,
     ESP_GUARD(engine);
     return engine->impl.stage_trace(cta, reinterpret_cast<long long*>(out), capacity, n);
 }
+int32_t esp_cuda_token_times(esp_cuda_engine* engine, uint64_t* out_ns, int32_t capacity, int32_t* n) {
+    ESP_GUARD(engine);
+    return engine->impl.token_times(reinterpret_cast<unsigned long long*>(out_ns), capacity, n);
+}
 int32_t esp_cuda_set_debug_layer(esp_cuda_engine* engine, int32_t layer) { ESP_GUARD(engine); return engine->impl.set_debug_layer(layer); }
 int32_t esp_cuda_debug_dump(esp_cuda_engine* engine, int32_t stage, float* out, int32_t capacity) { ESP_GUARD(engine); return engine->impl.debug_dump(stage, out, capacity); }
 const char* esp_cuda_last_error_string(void) { return esp::last_error_cstr(); }

@@ -1675,6 +1675,7 @@ int32_t Engine::build_mega() {
     if ((rc = dev_alloc(owned_, &d_mega_ctl_, 8))) return rc;
     if ((rc = dev_alloc(owned_, &d_mega_flags_, (size_t)P))) return rc;
     if ((rc = dev_alloc(owned_, &d_mega_trace_, (size_t)14 * m_.n_layer + 8))) return rc;
+    if ((rc = dev_alloc(owned_, &d_token_times_, (size_t)m_.max_seq + 1))) return rc;
     ESP_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&h_mega_ctl_), 8 * sizeof(unsigned long long)));
     // per-layer source pointers
     std::vector<const __half*> ptrs((size_t)7 * m_.n_layer);
@@ -1721,6 +1722,8 @@ int32_t Engine::run_mega(int n_steps, float* device_ms, double* first_token_ms) 
     a.stamps = d_mega_ctl_ + 3;
     a.rs = rs_;
     a.trace = d_mega_trace_;
+    a.token_times = n_steps <= m_.max_seq + 1 ? d_token_times_ : nullptr;
+    token_times_n_ = a.token_times ? n_steps : 0;
     a.trace_cta = mega_trace_cta_;
     a.n_steps = n_steps;
     a.pos0 = h_visible_[0];
@@ -1758,6 +1761,19 @@ int32_t Engine::stage_trace(int32_t cta, long long* out, int32_t capacity, int32
     ESP_CUDA_TRY(cudaMemcpy(out, d_mega_trace_, sizeof(long long) * count, cudaMemcpyDeviceToHost));
     *n = count;
     mega_trace_cta_ = std::max(0, std::min(cta, mega_plan_.n_cta - 1));  // takes effect with the next decode loop
+    return ESP_CUDA_OK;
+}
+
+// Emission time (GPU global timer, ns) of every token of the most recent persistent decode loop: the per-token gaps
+// the reference's CLI reports as median / p95 latency (Sources/EspressoGenerate/CLI.swift:1153-1165).
+int32_t Engine::token_times(unsigned long long* out_ns, int32_t capacity, int32_t* n) {
+    if (!out_ns || !n) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "token_times: null argument");
+    *n = 0;
+    if (!mega_ready_ || token_times_n_ <= 0) return ESP_CUDA_OK;
+    if (capacity < token_times_n_) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "token_times: capacity too small");
+    ESP_CUDA_TRY(cudaSetDevice(cfg_.device));
+    ESP_CUDA_TRY(cudaMemcpy(out_ns, d_token_times_, sizeof(unsigned long long) * token_times_n_, cudaMemcpyDeviceToHost));
+    *n = token_times_n_;
     return ESP_CUDA_OK;
 }
 

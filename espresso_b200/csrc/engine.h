@@ -69,6 +69,7 @@ public:
     int32_t decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, int32_t out_stride, int32_t* n_out,
                         float* device_ms, double* first_token_ms);
     int32_t stage_trace(int32_t cta, long long* out, int32_t capacity, int32_t* n);
+    int32_t token_times(unsigned long long* out_ns, int32_t capacity, int32_t* n);
     int32_t set_debug_layer(int32_t layer);
     int32_t debug_dump(int32_t stage, float* out, int32_t capacity);
     int32_t get_timings(esp_cuda_timings* out);
@@ -166,6 +167,8 @@ private:
     unsigned long long* d_mega_ctl_ = nullptr;  // [0..1] best, [2] barrier (u32) + error (i32), [3..4] time stamps
     unsigned long long* h_mega_ctl_ = nullptr;  // pinned mirror
     long long* d_mega_trace_ = nullptr;
+    unsigned long long* d_token_times_ = nullptr;  // [max_seq] emission time of every token of the last persistent loop
+    int token_times_n_ = 0;
     unsigned int* d_mega_flags_ = nullptr;     // grid barrier: one epoch word per CTA
     int mega_trace_cta_ = 0;
     esp_cuda_timings timings_{};

@@ -59,6 +59,7 @@ struct MegaArgs {
     unsigned int* barrier;    // [1] monotonic arrival counter, zero at launch
     int* error;               // [1] 0 = ok
     unsigned long long* stamps; // [2] globaltimer at kernel start and when the first token is known
+    unsigned long long* token_times; // optional [n_steps] globaltimer (ns) at which each token became known, or null
     long long* trace;         // optional [14*L + 4] SM clock stamps of the last step taken by CTA `trace_cta`, or null
     int trace_cta;
     RowState rs;              // row 0 carries pos / tok / n_out / out
@@ -718,6 +719,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 a.stamps[1] = t;
             }
             a.rs.out[step] = tok;
+            if (a.token_times) {
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                a.token_times[step] = t;
+            }
             a.best[(step + 1) & 1] = 0ull;  // nobody reads that slot before the next head's barrier
         }
         if (step > 0 && step == a.n_steps - 1 && blockIdx.x == 0)  // keep the sequence's last hidden state

@@ -101,6 +101,7 @@ SIGNATURES = {
     "esp_cuda_generate_two_token": (C.c_int32, [_vp, _vp, _u32p, C.c_int32, C.c_int32, _u32p, _i32p, C.POINTER(EspCudaGenerationResult)]),
     "esp_cuda_get_timings": (C.c_int32, [_vp, C.POINTER(EspCudaTimings)]),
     "esp_cuda_stage_trace": (C.c_int32, [_vp, C.c_int32, C.POINTER(C.c_int64), C.c_int32, _i32p]),
+    "esp_cuda_token_times": (C.c_int32, [_vp, C.POINTER(C.c_uint64), C.c_int32, _i32p]),
     "esp_cuda_set_debug_layer": (C.c_int32, [_vp, C.c_int32]),
     "esp_cuda_debug_dump": (C.c_int32, [_vp, C.c_int32, _f32p, C.c_int32]),
     "esp_cuda_last_error_string": (C.c_char_p, []),
@@ -364,6 +365,13 @@ class DecodeEngine:
         out = np.zeros(14 * self.config.nLayer + 8, np.int64)
         n = C.c_int32()
         _check(self._lib.esp_cuda_stage_trace(self._h, next_cta, out.ctypes.data_as(C.POINTER(C.c_int64)), out.size, C.byref(n)))
+        return out[: n.value].copy()
+
+    def token_times_ns(self) -> np.ndarray:
+        """GPU timer value (ns) at which each token of the last persistent decode loop became known (empty otherwise)."""
+        out = np.zeros(self.config.maxSeq + 1, np.uint64)
+        n = C.c_int32()
+        _check(self._lib.esp_cuda_token_times(self._h, out.ctypes.data_as(C.POINTER(C.c_uint64)), out.size, C.byref(n)))
         return out[: n.value].copy()
 
     def set_debug_layer(self, layer: int) -> None:

@@ -239,6 +239,10 @@ ESP_CUDA_API int32_t esp_cuda_get_timings(esp_cuda_engine* engine, esp_cuda_timi
  * 4 for the head: begin, norm done, rows done, barrier passed.  *n = 0 when the model does not use that kernel.
  * `cta` selects which CTA records the NEXT loop. */
 ESP_CUDA_API int32_t esp_cuda_stage_trace(esp_cuda_engine* engine, int32_t cta, int64_t* out, int32_t capacity, int32_t* n);
+/* Emission time (GPU global timer, nanoseconds) of every token of the most recent decode loop that ran as the
+ * persistent kernel; consecutive differences are the per-token latencies the reference's CLI summarises as median
+ * and p95 (Sources/EspressoGenerate/CLI.swift:1153-1165, 1283-1284).  *n = 0 when that loop used other kernels. */
+ESP_CUDA_API int32_t esp_cuda_token_times(esp_cuda_engine* engine, uint64_t* out_ns, int32_t capacity, int32_t* n);
 ESP_CUDA_API int32_t esp_cuda_set_debug_layer(esp_cuda_engine* engine, int32_t layer);
 ESP_CUDA_API int32_t esp_cuda_debug_dump(esp_cuda_engine* engine, int32_t stage, float* out, int32_t capacity);
 ESP_CUDA_API const char* esp_cuda_last_error_string(void);

@@ -403,6 +403,25 @@ def test_quantised_batch_uses_fp16_expansion_and_matches_oracle(rt, oracle_lib, 
     eng.close()
 
 
+def test_token_emission_times_of_the_persistent_loop(rt, tmp_models):
+    from espresso_b200.model_config import tiny_llama
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = tiny_llama(vocab=128, max_seq=64, n_layer=2)
+    eng = rt.DecodeEngine.build(tmp_models(cfg))
+    eng.prefill(synthetic_prompt(cfg.vocab, 5))
+    toks, _ = eng.decode(20)
+    t = eng.token_times_ns().astype(np.int64)
+    assert t.size == 20 and np.all(np.diff(t) > 0)  # one stamp per token, strictly increasing
+    assert np.diff(t).max() < 5_000_000  # a token of this model takes microseconds, not milliseconds
+    ref = rt.DecodeEngine.build(tmp_models(cfg), flags=rt.FLAG_NO_MEGAKERNEL)
+    ref.prefill(synthetic_prompt(cfg.vocab, 5))
+    ref.decode(4)
+    assert ref.token_times_ns().size == 0  # the per-stage kernels record no such stamps
+    ref.close()
+    eng.close()
+
+
 @pytest.mark.parametrize("kind", ["f16", "q8_0"])
 def test_persistent_kernel_streams_wide_stages_in_chunks(rt, oracle_lib, tmp_models, kind):
     """d_model 2048 / hidden 5632: every stage slice of the persistent kernel exceeds a ring slot and arrives in chunks
