@@ -331,8 +331,10 @@ __global__ void __launch_bounds__(kAttRowsWarps * 32) k_attention_rows(const Att
             if (t < visible) {
                 const uint4* kp = reinterpret_cast<const uint4*>(K + (size_t)t * HD);
                 const uint4* vp = reinterpret_cast<const uint4*>(V + (size_t)t * HD);
-                k[u][0] = __ldcg(kp); k[u][1] = __ldcg(kp + 1);
-                v[u][0] = __ldcg(vp); v[u][1] = __ldcg(vp + 1);
+                // through L1: with grouped-query attention the warps of a CTA are the query heads of one KV head and
+                // walk the same rows almost in step, so three of four reads are L1 hits (the cache is only read here)
+                k[u][0] = __ldg(kp); k[u][1] = __ldg(kp + 1);
+                v[u][0] = __ldg(vp); v[u][1] = __ldg(vp + 1);
             } else {
                 k[u][0] = k[u][1] = v[u][0] = v[u][1] = make_uint4(0, 0, 0, 0);
             }
