@@ -403,6 +403,28 @@ def test_quantised_batch_uses_fp16_expansion_and_matches_oracle(rt, oracle_lib, 
     eng.close()
 
 
+@pytest.mark.parametrize("n_head,n_kv,head_dim", [(16, 4, 64), (16, 16, 64), (12, 4, 128), (20, 20, 32)])
+def test_many_row_attention_kernels_in_a_prefill_chunk(rt, oracle_lib, tmp_models, n_head, n_kv, head_dim):
+    """A 64-row prefill chunk with rows x heads >= 4 x SMs runs the one-warp-per-(row, head) attention (multi-head and
+    grouped-query shapes, head_dim 32 / 64 / 128)."""
+    from espresso_b200.model_config import MultiModelConfig
+    from espresso_b200.synthetic import synthetic_prompt
+
+    d = n_head * head_dim
+    cfg = MultiModelConfig(f"att-{n_head}-{n_kv}-{head_dim}", 1, n_head, n_kv, d, head_dim, 2 * d if d <= 640 else d, 320, 160, 1e-5, 10000.0, None, "llama")
+    if 64 * n_head < 4 * 148:
+        pytest.skip("too few (row, head) pairs for the many-row kernels")
+    wd = tmp_models(cfg)
+    eng = rt.DecodeEngine.build(wd)
+    ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(wd))
+    prompt = synthetic_prompt(cfg.vocab, 100)  # chunks of 64 and 36 rows: the second one sees 64..99 cached positions
+    eng.prefill(prompt)
+    assert ora.prefill(prompt) == 0
+    assert_logits_close(eng.logits(), ora.logits(), cfg.name)
+    compare_greedy_stream(ora, prompt, eng.generate(prompt, 8).tokens)
+    eng.close()
+
+
 def test_token_emission_times_of_the_persistent_loop(rt, tmp_models):
     from espresso_b200.model_config import tiny_llama
     from espresso_b200.synthetic import synthetic_prompt
