@@ -290,15 +290,21 @@ __device__ __forceinline__ void halves16_to_float(const uint4& a, const uint4& b
 // every load instruction reads whole 128-byte (or longer) cache rows.  Each lane group keeps its own running
 // (max, sum, context) over the positions it visits; the groups are merged once at the end.  Softmax in fp32 as in
 // decodeContext (Sources/RealModelInference/RealModelInferenceEngine.swift:6560-6640), evaluated online.
-template <int HD>
-__global__ void __launch_bounds__(kAttRowsWarps * 32) k_attention_rows(const AttRowsArgs p) {
+// SPLIT = 2: two warps share one (row, head) and take alternate blocks of positions (twice the cache bytes in
+// flight when there are few (row, head) pairs and long contexts); the second warp hands its (max, sum, context) to the
+// first through shared memory.  Needs n_head % 4 == 0 so that a CTA (4 heads x SPLIT warps) never straddles two rows.
+template <int HD, int SPLIT>
+__global__ void __launch_bounds__(kAttRowsWarps * 32 * SPLIT) k_attention_rows(const AttRowsArgs p) {
     constexpr int LPP = HD / 16;   // lanes per position
     constexpr int G = 32 / LPP;    // positions per pass of one warp
+    __shared__ float s_merge[SPLIT > 1 ? kAttRowsWarps * LPP * 18 : 1];
     pdl_launch_dependents();
     pdl_wait();
     const ModelDims& m = p.m;
     const int lane = threadIdx.x & 31;
-    const int w = blockIdx.x * kAttRowsWarps + (threadIdx.x >> 5);
+    const int warp_in_cta = threadIdx.x >> 5;
+    const int split = SPLIT > 1 ? warp_in_cta / kAttRowsWarps : 0;
+    const int w = blockIdx.x * kAttRowsWarps + (SPLIT > 1 ? warp_in_cta % kAttRowsWarps : warp_in_cta);
     if (w >= p.rows * m.n_head) return;
     const int r = w / m.n_head, head = w - r * m.n_head;
     // the three row-state words are requested together (one memory round trip, not three)
@@ -367,11 +373,12 @@ __global__ void __launch_bounds__(kAttRowsWarps * 32) k_attention_rows(const Att
     };
 
     uint4 ka[2][2], va[2][2], kb[2][2], vb[2][2];
-    load(0, ka, va);
-    for (int t0 = 0; t0 < visible; t0 += 4 * G) {
+    const int first = split * 4 * G;  // warps of one (row, head) take alternate blocks of 4 G positions
+    load(first, ka, va);
+    for (int t0 = first; t0 < visible; t0 += 4 * G * SPLIT) {
         load(t0 + 2 * G, kb, vb);
         compute(t0, ka, va);
-        load(t0 + 4 * G, ka, va);
+        load(t0 + 4 * G * SPLIT, ka, va);
         compute(t0 + 2 * G, kb, vb);
     }
     // merge the lane groups
@@ -390,7 +397,25 @@ __global__ void __launch_bounds__(kAttRowsWarps * 32) k_attention_rows(const Att
         }
         mx = mn;
     }
-    if (slot == 0) {
+    if (SPLIT > 1) {  // (the whole CTA works on one row, so every warp reaches this barrier)
+        float* mine = s_merge + ((warp_in_cta % kAttRowsWarps) * LPP + sub) * 18;
+        if (split == 1 && slot == 0) {
+            mine[0] = mx; mine[1] = sum;
+#pragma unroll
+            for (int i = 0; i < 16; i++) mine[2 + i] = acc[i];
+        }
+        __syncthreads();
+        if (split == 0 && slot == 0) {
+            const float mo = mine[0], so = mine[1];
+            const float mn = fmaxf(mx, mo);
+            const float c1 = mx == -INFINITY ? 0.f : expf(mx - mn);
+            const float c2 = mo == -INFINITY ? 0.f : expf(mo - mn);
+            sum = sum * c1 + so * c2;
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[i] = acc[i] * c1 + mine[2 + i] * c2;
+        }
+    }
+    if (slot == 0 && split == 0) {
         const float inv = sum > 0.f ? 1.0f / sum : 0.f;
         uint32_t packed[8];
 #pragma unroll

@@ -1545,9 +1545,18 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
                 ar.m = m_; ar.rs = rs_; ar.kv = kv_; ar.q = act_.q; ar.ctx16 = xh_q_; ar.bf16 = tc_bf16_; ar.layer = l; ar.rows = rows;
                 ar.debug = cap ? dbg + q + 2 * kv : nullptr;
                 const dim3 grid((rows * m_.n_head + kAttRowsWarps - 1) / kAttRowsWarps);
-                if (m_.head_dim == 32) ESP_CUDA_TRY(launch_pdl(k_attention_rows<32>, grid, dim3(kAttRowsWarps * 32), 0, s, ar));
-                else if (m_.head_dim == 64) ESP_CUDA_TRY(launch_pdl(k_attention_rows<64>, grid, dim3(kAttRowsWarps * 32), 0, s, ar));
-                else ESP_CUDA_TRY(launch_pdl(k_attention_rows<128>, grid, dim3(kAttRowsWarps * 32), 0, s, ar));
+                // few (row, head) pairs (less than ~28 warps per SM): two warps per pair, on alternate position blocks
+                const bool split2 = m_.n_head % kAttRowsWarps == 0 && (long long)rows * m_.n_head < 28LL * sm_count_;
+                const dim3 block(kAttRowsWarps * 32 * (split2 ? 2 : 1));
+#define ESP_ATT(HDV)                                                                                             \
+    do {                                                                                                         \
+        if (split2) ESP_CUDA_TRY(launch_pdl(k_attention_rows<HDV, 2>, grid, block, 0, s, ar));                   \
+        else ESP_CUDA_TRY(launch_pdl(k_attention_rows<HDV, 1>, grid, block, 0, s, ar));                          \
+    } while (0)
+                if (m_.head_dim == 32) ESP_ATT(32);
+                else if (m_.head_dim == 64) ESP_ATT(64);
+                else ESP_ATT(128);
+#undef ESP_ATT
                 launches++;
             } else {
                 AttArgs aa{};

@@ -403,10 +403,10 @@ def test_quantised_batch_uses_fp16_expansion_and_matches_oracle(rt, oracle_lib, 
     eng.close()
 
 
-@pytest.mark.parametrize("n_head,n_kv,head_dim", [(16, 4, 64), (16, 16, 64), (12, 4, 128), (20, 20, 32)])
+@pytest.mark.parametrize("n_head,n_kv,head_dim", [(16, 4, 64), (16, 16, 64), (12, 4, 128), (20, 20, 32), (10, 5, 64)])
 def test_many_row_attention_kernels_in_a_prefill_chunk(rt, oracle_lib, tmp_models, n_head, n_kv, head_dim):
-    """A 64-row prefill chunk with rows x heads >= 4 x SMs runs the one-warp-per-(row, head) attention (multi-head and
-    grouped-query shapes, head_dim 32 / 64 / 128)."""
+    """A 64-row prefill chunk with rows x heads >= 4 x SMs runs the many-row attention (multi-head and grouped-query
+    shapes, head_dim 32 / 64 / 128): two warps per (row, head) when n_head is a multiple of 4, one warp otherwise."""
     from espresso_b200.model_config import MultiModelConfig
     from espresso_b200.synthetic import synthetic_prompt
 
