@@ -1050,7 +1050,8 @@ int32_t Engine::commit(int32_t steps) {
     if (steps < 1 || steps > 2) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "commit: steps must be 1 or 2");
     if (steps == 2)
         ESP_CUDA_TRY(cudaMemcpyAsync(act_.hidden, act_.hidden + m_.d_model, sizeof(float) * m_.d_model, cudaMemcpyDeviceToDevice, stream_));
-    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    // No host wait: the copy is ordered before the next pass on the engine's stream, and verify2 has already
+    // waited for the pair's tokens.
     h_visible_[0] += steps;
     pending_verify_ = 0;
     return ESP_CUDA_OK;
@@ -1818,9 +1819,11 @@ namespace esp {
 // y = W.x with the same inner loop as the decode stages: one warp per pair of rows, 16-byte weight loads.
 // (Measured on B200: this plain loop - two rows per warp, four 16-byte slices per row requested together, three
 // CTAs per SM - streams an LM-head sized fp16 matrix at 0.93 of the copy peak; the software-pipelined four-row
-// loop of the decode stages is slower here (0.83) because its register footprint halves the resident warps.)
+// loop of the decode stages is slower here (0.83) because its register footprint halves the resident warps.
+// The Q4_0 instance sits right at 128 registers; small source changes pushed it to ~157 and one CTA per SM
+// (Q4_0 20.6 -> 24.4 us on 32768 x 4096), hence the two-CTA launch bound.)
 template <int WT>
-__global__ void __launch_bounds__(kThreads) k_gemv_plain(Weight w, const float* __restrict__ x, float* __restrict__ y) {
+__global__ void __launch_bounds__(kThreads, 2) k_gemv_plain(Weight w, const float* __restrict__ x, float* __restrict__ y) {
     extern __shared__ float smem[];
     float* xs = smem + kRedFloats;
     const float xdescale = stage_vector<WT>(x, w.cols, NORM_NONE, nullptr, nullptr, 0.f, xs, smem);
