@@ -38,7 +38,7 @@ WORKLOADS = {
     "c3": dict(cfg=mc.gpt2_117m, prompt=64, decode=256, n_seq=256, sharded=True, kind="f16", bpw=2.0,
                label="gpt2-117M shape 12L d768 vocab50257 ctx1024 fp16, 256 independent sequences sharded over the GPUs, 64-token prompts, 256 greedy steps"),
     "c5": dict(cfg=mc.llama3_8b, prompt=512, decode=256, n_seq=64, kind="bf16", bpw=2.0, device_weights=True, tp=True,
-               label="llama-3-8B shape 32L d4096 GQA 32/8 hd128 vocab128256 ctx1024 bf16, 64 sequences, 512-token prompts, 256 greedy steps, tensor parallel over the GPUs (NCCL all-reduce after Wo and W2)"),
+               label="llama-3-8B shape 32L d4096 GQA 32/8 hd128 vocab128256 ctx1024 bf16, 64 sequences, 512-token prompts, 256 greedy steps, tensor parallel over the GPUs (sum after Wo and W2 over peer memory)"),
     "c4q8": dict(cfg=mc.llama_1b, prompt=128, decode=256, n_seq=1, kind="q8_0", bpw=34.0 / 32, device_weights=True,
                  label="llama 1.1B shape 22L d2048 GQA 32/4 ctx2048, GGUF Q8_0 matrices + LM head, batch 1, 128-token prompt, 256 steps"),
     "c4q4": dict(cfg=mc.llama_1b, prompt=128, decode=256, n_seq=1, kind="q4_0", bpw=18.0 / 32, device_weights=True,
@@ -502,7 +502,7 @@ def main() -> None:
             "ms_per_step": total_ms / args.steps, "ms_per_token": total_ms / args.steps / n_decode, "higher_is_better": True,
             "scaling": scaling, "vs_baseline": None, "dtype": f"{wl['kind']} weights, f16 KV, f32 accumulate", "data": "synthetic",
             "config": {"workload": wl["label"],
-                       "parallelism": (f"tensor parallel x{world}, NCCL all-reduce after Wo and W2" if wl.get("tp") else
+                       "parallelism": (f"tensor parallel x{world}, partial sums after Wo and W2 added over NVLink peer memory (NCCL when ESP_CUDA_TP_NCCL_ONLY is set), arg-max over NCCL" if wl.get("tp") else
                                        "sequences sharded across GPUs, no collective" if wl.get("sharded") else
                                        "replicas only (one independent job per GPU)") if world > 1 else "single GPU",
                        "l2": "no flush: every decode step streams more weight + KV bytes than the 126 MB L2 holds"},
