@@ -239,8 +239,7 @@ def stage_trace_us(eng, cfg, prompt, n_decode: int, sm_mhz: float) -> dict:
     the engine decodes with the per-stage kernels."""
     import numpy as np
 
-    names = ["s1_norm", "s1_wait_weights", "s1_rows", "s1_barrier", "s2_wait_weights", "s2_attention_projection", "s2_barrier", "s3_norm",
-             "s3_wait_weights", "s3_gate_up", "s3_wait_weights2", "s3_down", "s3_barrier"]
+    names = ["x_wait_norm", "qkv_rows", "qkv_wait", "attention", "wo_partial", "xmid_wait_norm", "gate_up", "act_wait", "down"]
     eng.prefill(prompt)
     eng.decode(n_decode)
     eng.stage_trace(100)  # selects the CTA whose stamps the next loop records
@@ -248,15 +247,16 @@ def stage_trace_us(eng, cfg, prompt, n_decode: int, sm_mhz: float) -> dict:
     eng.decode(n_decode)
     t = eng.stage_trace(100).astype(np.float64) / sm_mhz
     L = cfg.nLayer
-    if t.size < 14 * L + 4 or not t.any():
+    if t.size < 10 * L + 4 or not t.any():
         return {}
-    per = np.zeros(13)
+    per = np.zeros(9)
     for layer in range(L):
-        per += np.diff(t[14 * layer:14 * layer + 14])
-    head = np.diff(t[14 * L:14 * L + 4])
+        per += np.diff(t[10 * layer:10 * layer + 10])
+    head = np.diff(t[10 * L:10 * L + 4])
     out = {n: round(float(v) / L, 2) for n, v in zip(names, per)}
-    out.update({"head_norm": round(float(head[0]), 2), "head_rows": round(float(head[1]), 2), "head_barrier": round(float(head[2]), 2),
-                "cta": 100, "note": "per-layer means over the last token, SM clock stamps of one CTA"})
+    out.update({"layer_total": round(float(t[10 * L] - t[0]) / L, 2), "head_x_wait": round(float(head[0]), 2), "head_rows": round(float(head[1]), 2),
+                "head_token_wait": round(float(head[2]), 2),
+                "cta": 100, "note": "per-layer means over the last token, SM clock stamps of one CTA; *_wait = polling for another CTA's words"})
     return out
 
 

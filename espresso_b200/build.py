@@ -34,7 +34,7 @@ def needs_build() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
-    cmd = [find_nvcc(), *NVCC_FLAGS, "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
+    cmd = [find_nvcc(), *NVCC_FLAGS, *os.environ.get("ESP_CUDA_EXTRA_NVCC_FLAGS", "").split(), "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     env = dict(os.environ)

@@ -287,6 +287,7 @@ int32_t esp_cuda_set_debug_layer(esp_cuda_engine* engine, int32_t layer) { ESP_G
 int32_t esp_cuda_debug_dump(esp_cuda_engine* engine, int32_t stage, float* out, int32_t capacity) { ESP_GUARD(engine); return engine->impl.debug_dump(stage, out, capacity); }
 const char* esp_cuda_last_error_string(void) { return esp::last_error_cstr(); }
 void esp_cuda_set_force_failure(int32_t enabled) { esp::set_force_failure(enabled); }
+int32_t esp_cuda_set_wait_limit(esp_cuda_engine* engine, uint32_t spins) { ESP_GUARD(engine); return engine->impl.set_wait_limit(spins); }
 int32_t esp_cuda_live_engine_count(void) { return g_live_engines.load(); }
 const char* esp_cuda_version(void) { return "espresso-cuda 0.1 (sm_100a)"; }
 

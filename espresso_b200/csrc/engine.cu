@@ -1150,9 +1150,10 @@ int32_t Engine::decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, 
     }
     if (max_lim == 0) { if (device_ms) *device_ms = 0.f; return ESP_CUDA_OK; }
     if (mega_ready_ && n_seq == 1 && debug_layer_ < 0 && !(cfg_.flags & (ESP_CUDA_FLAG_NO_MEGAKERNEL | ESP_CUDA_FLAG_NO_GRAPH))) {
-        if ((rc = run_mega(lim[0], device_ms, first_token_ms))) return rc;
-        if (n_out) n_out[0] = lim[0];
-        if (out_tokens) ESP_CUDA_TRY(cudaMemcpy(out_tokens, rs_.out, sizeof(uint32_t) * lim[0], cudaMemcpyDeviceToHost));
+        int emitted = 0;
+        if ((rc = run_mega(lim[0], &emitted, device_ms, first_token_ms))) return rc;
+        if (n_out) n_out[0] = emitted;
+        if (out_tokens) ESP_CUDA_TRY(cudaMemcpy(out_tokens, rs_.out, sizeof(uint32_t) * emitted, cudaMemcpyDeviceToHost));
         return ESP_CUDA_OK;
     }
     std::vector<int> active(n_seq);
@@ -1605,15 +1606,21 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
 
 static int pad128(long long v) { return (int)((v + 127) / 128 * 128); }
 
+static const void* mega_kernel_for(int head_dim) {
+    if (head_dim == 64) return reinterpret_cast<const void*>(&k_decode_mega<64>);
+    if (head_dim == 128) return reinterpret_cast<const void*>(&k_decode_mega<128>);
+    return reinterpret_cast<const void*>(&k_decode_mega<32>);
+}
+
+// Plans and packs the persistent decode kernel.  Every CTA owns a contiguous share of the rows of every matrix;
+// the model qualifies when one item of every stage fits a ring slot and the ring fits shared memory.
 int32_t Engine::build_mega() {
     mega_ready_ = false;
     if ((cfg_.flags & ESP_CUDA_FLAG_NO_MEGAKERNEL) || tp_size_ > 1) return ESP_CUDA_OK;
-    if (m_.arch != ARCH_LLAMA || m_.eos_token >= 0) return ESP_CUDA_OK;
+    if (m_.arch != ARCH_LLAMA) return ESP_CUDA_OK;
     if (m_.head_dim != 32 && m_.head_dim != 64 && m_.head_dim != 128) return ESP_CUDA_OK;
-    if (m_.d_model > 4096 || m_.d_model % 8 || m_.n_head > sm_count_) return ESP_CUDA_OK;
-    // fp16 source of a matrix: its own storage, or the fp16 expansion of a quantised matrix (the persistent kernel
-    // then streams 2 bytes per weight instead of the blocks; it still beats the per-stage kernels by removing their
-    // ~110 dependent launches per token)
+    if (m_.d_model % 8 || m_.hidden % 8 || m_.n_head > sm_count_ || m_.n_head > 255) return ESP_CUDA_OK;
+    // fp16 source of a matrix: its own storage, or the fp16 expansion of a quantised matrix
     auto f16_source = [&](const std::string& name) -> const __half* {
         const DeviceTensor& t = tensors_.at(name);
         if (t.type == ESP_CUDA_F16) return static_cast<const __half*>(t.data);
@@ -1628,63 +1635,61 @@ int32_t Engine::build_mega() {
     cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, cfg_.device);
     if (!coop) return ESP_CUDA_OK;
     MegaPlan p{};
-    const int P = sm_count_;
+    // every CTA must own at least one FFN unit and one row of W2 (it then takes part in every all-to-all exchange)
+    const int P = std::min(sm_count_, std::min(m_.d_model, m_.hidden));
+    if (P < m_.n_head) return ESP_CUDA_OK;
     p.n_cta = P;
+    p.qpk = m_.n_head / m_.n_kv_head;
+    p.group_items = (p.qpk + 2) * m_.head_dim / 2;
+    p.cph = std::max(1, std::min(std::min(P / m_.n_head, m_.d_model), p.group_items / p.qpk));
+    p.gsize = p.cph * p.qpk;
+    p.n_group_cta = p.cph * m_.n_head;
+    p.s1_max = (p.group_items + p.gsize - 1) / p.gsize;
+    p.rpb = (m_.d_model + p.cph - 1) / p.cph;
+    p.hpc_max = (m_.hidden + P - 1) / P;
+    p.dpc_max = (m_.d_model + P - 1) / P;
+    p.vpc_max = (m_.vocab + P - 1) / P;
     p.row_bytes = m_.d_model * 2;
-    p.ppc = ((m_.q_dim + 2 * m_.kv_dim) / 2 + P - 1) / P;
-    p.blocks = P / m_.n_head;
-    p.rpb = (m_.d_model + p.blocks - 1) / p.blocks;
-    p.hpc = (m_.hidden + P - 1) / P;
-    p.vpc = (m_.vocab + P - 1) / P;
-    p.s1_bytes = pad128((long long)2 * p.ppc * p.row_bytes);
+    p.down_row_bytes = m_.hidden * 2;
+    p.s1_bytes = pad128((long long)2 * p.s1_max * p.row_bytes);
     p.s2_bytes = pad128((long long)p.rpb * m_.head_dim * 2);
-    p.s3a_bytes = pad128((long long)2 * p.hpc * p.row_bytes);
-    p.s3b_bytes = pad128((long long)p.hpc * p.row_bytes);
-    // A stage slice of up to 64 KB travels as one chunk; larger ones as chunks of up to 64 KB of whole items.
-    const int kWhole = 64 * 1024, kTarget = 64 * 1024;  // 64 KB = eight 2048-wide row pairs: one per consumer warp
-    auto per_chunk = [&](int items, int item_bytes, int multiple) {
-        if ((long long)items * item_bytes <= kWhole) return std::max(items, 1);
-        int n = std::max(1, kTarget / item_bytes);
-        if (multiple > 1) n = std::max(multiple, n / multiple * multiple);
-        return n;
-    };
-    const int s2_rows_per_pass = kMegaConsumers / (m_.head_dim / 16);
-    p.s1_ipc = per_chunk(p.ppc, 2 * p.row_bytes, 1);
-    p.s2_rpc = per_chunk(p.rpb, m_.head_dim * 2, s2_rows_per_pass);
-    p.s3a_ipc = per_chunk(p.hpc, 2 * p.row_bytes, 1);
-    p.s3b_rpc = per_chunk(p.hpc, p.row_bytes, 1);
-    auto chunk_bytes = [](int items, int per, int item_bytes) { return pad128((long long)std::min(items, per) * item_bytes); };
-    int layer_max = std::max(std::max(chunk_bytes(p.ppc, p.s1_ipc, 2 * p.row_bytes), chunk_bytes(p.rpb, p.s2_rpc, m_.head_dim * 2)),
-                             std::max(chunk_bytes(p.hpc, p.s3a_ipc, 2 * p.row_bytes), chunk_bytes(p.hpc, p.s3b_rpc, p.row_bytes)));
-    int rh = std::max(4, (std::max(layer_max, 48 * 1024) / p.row_bytes) & ~3);
-    rh = std::min(rh, (p.vpc + 3) & ~3);
-    p.head_rows_per_chunk = rh;
-    p.head_chunks = (p.vpc + rh - 1) / rh;
-    p.head_chunk_bytes = pad128((long long)rh * p.row_bytes);
-    p.slot_bytes = std::max(layer_max, p.head_chunk_bytes);
+    p.s3a_bytes = pad128((long long)2 * p.hpc_max * p.row_bytes);
+    p.s3b_bytes = pad128((long long)p.dpc_max * p.down_row_bytes);
     p.layer_bytes = (long long)p.s1_bytes + p.s2_bytes + p.s3a_bytes + p.s3b_bytes;
-    p.cta_bytes = p.layer_bytes * m_.n_layer + (long long)p.head_chunks * p.head_chunk_bytes;
-    p.n_slots = 2;
-    MegaPlan probe = p;
+    p.head_bytes = pad128((long long)p.vpc_max * p.row_bytes);
+    p.cta_bytes = p.layer_bytes * m_.n_layer + p.head_bytes;
+    // ring slots of 48 KB (more when one item of a stage is larger); a stage slice travels as chunks of whole items
+    const int s2_rows_per_pass = kMegaConsumers / (m_.head_dim <= 64 ? m_.head_dim / 8 : m_.head_dim / 16);
+    const int item_max = std::max(std::max(2 * p.row_bytes, p.down_row_bytes), m_.head_dim * 2 * std::min(p.rpb, s2_rows_per_pass));
+    p.slot_bytes = pad128(std::max(48 * 1024, item_max));
+    p.s1_ipc = std::max(1, std::min(p.s1_max, p.slot_bytes / (2 * p.row_bytes)));
+    p.s3a_ipc = std::max(1, std::min(p.hpc_max, p.slot_bytes / (2 * p.row_bytes)));
+    p.s3b_rpc = std::max(1, std::min(p.dpc_max, p.slot_bytes / p.down_row_bytes));
+    p.head_rpc = std::max(1, std::min(p.vpc_max, p.slot_bytes / p.row_bytes));
+    if ((long long)p.rpb * m_.head_dim * 2 <= p.slot_bytes) p.s2_rpc = p.rpb;
+    else p.s2_rpc = std::max(s2_rows_per_pass, p.slot_bytes / (m_.head_dim * 2) / s2_rows_per_pass * s2_rows_per_pass);
+    p.n_slots = 0;
     for (int ns = 8; ns >= 2; ns--) {
+        MegaPlan probe = p;
         probe.n_slots = ns;
-        if (mega_smem_bytes(m_, probe) <= smem_max) { p.n_slots = ns; break; }
-        if (ns == 2) return ESP_CUDA_OK;  // the per-layer slice does not fit: the per-stage kernels serve this model
+        mega_layout(m_, probe);
+        if (probe.smem_bytes <= smem_max) { p = probe; break; }
     }
-    p.smem_bytes = mega_smem_bytes(m_, p);
-    if (p.smem_bytes > smem_max) return ESP_CUDA_OK;
-    ESP_CUDA_TRY(cudaFuncSetAttribute(k_decode_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes));
+    if (p.n_slots == 0) return ESP_CUDA_OK;  // does not fit: the per-stage kernels serve this model
+    const void* kern = mega_kernel_for(m_.head_dim);
+    ESP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes));
     int occ = 0;
-    ESP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_decode_mega, kMegaThreads, p.smem_bytes));
+    ESP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kMegaThreads, p.smem_bytes));
     if (occ < 1) return ESP_CUDA_OK;
 
     int32_t rc;
     if ((rc = dev_alloc(owned_, &d_pack_, (size_t)P * p.cta_bytes, false))) return rc;
     if ((rc = dev_alloc(owned_, &d_norms_, (size_t)(2 * m_.n_layer + 1) * m_.d_model, false))) return rc;
-    if ((rc = dev_alloc(owned_, &d_xbuf_, (size_t)3 * m_.d_model))) return rc;
+    // exchange arena: x words, activation words, q/k/v words per KV head, counted sums, arg-max candidates
+    mega_arena_words_ = (size_t)2 * m_.d_model + m_.hidden + (size_t)m_.n_kv_head * 2 * p.group_items + (size_t)4 * P + 8;
+    if ((rc = dev_alloc(owned_, &d_mega_arena_, mega_arena_words_))) return rc;
     if ((rc = dev_alloc(owned_, &d_mega_ctl_, 8))) return rc;
-    if ((rc = dev_alloc(owned_, &d_mega_flags_, (size_t)P))) return rc;
-    if ((rc = dev_alloc(owned_, &d_mega_trace_, (size_t)14 * m_.n_layer + 8))) return rc;
+    if ((rc = dev_alloc(owned_, &d_mega_trace_, (size_t)kMegaTraceLayer * m_.n_layer + kMegaTraceHead + 4 + 512))) return rc;
     if ((rc = dev_alloc(owned_, &d_token_times_, (size_t)m_.max_seq + 1))) return rc;
     ESP_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&h_mega_ctl_), 8 * sizeof(unsigned long long)));
     // per-layer source pointers
@@ -1720,30 +1725,35 @@ int32_t Engine::build_mega() {
     return ESP_CUDA_OK;
 }
 
-// Runs the whole greedy loop (n_steps emitted tokens) of sequence 0 as one cooperative launch.
-int32_t Engine::run_mega(int n_steps, float* device_ms, double* first_token_ms) {
+// Runs the greedy loop (at most n_steps emitted tokens; fewer when the end-of-sequence token comes up) of sequence 0
+// as one cooperative launch.  *emitted receives the number of tokens written to rs_.out.
+int32_t Engine::run_mega(int n_steps, int* emitted, float* device_ms, double* first_token_ms) {
     MegaArgs a{};
-    a.m = m_; a.plan = mega_plan_; a.pack = d_pack_; a.norms = d_norms_;
+    const MegaPlan& p = mega_plan_;
+    a.m = m_; a.plan = p; a.pack = d_pack_; a.norms = d_norms_;
     a.tok_emb = static_cast<const uint16_t*>(tensors_.at("embeddings/token").data);
-    a.rope = d_rope_; a.kv = kv_; a.q = act_.q; a.xbuf = d_xbuf_; a.hidden_io = act_.hidden;
-    a.best = d_mega_ctl_;
-    a.barrier = d_mega_flags_;
+    a.rope = d_rope_; a.kv = kv_; a.hidden_io = act_.hidden;
+    a.x_words = d_mega_arena_;
+    a.mid_sums = a.x_words + m_.d_model;
+    a.act_words = a.mid_sums + m_.d_model;
+    a.qkv_words = a.act_words + m_.hidden;
+    a.cand_words = a.qkv_words + (size_t)m_.n_kv_head * 2 * p.group_items;
     a.error = reinterpret_cast<int*>(d_mega_ctl_ + 2) + 1;
     a.stamps = d_mega_ctl_ + 3;
     a.rs = rs_;
     a.trace = d_mega_trace_;
     a.token_times = n_steps <= m_.max_seq + 1 ? d_token_times_ : nullptr;
-    token_times_n_ = a.token_times ? n_steps : 0;
-    a.trace_cta = mega_trace_cta_;
+    token_times_n_ = 0;
+    a.trace_cta = std::min(mega_trace_cta_, p.n_cta - 1);
     a.n_steps = n_steps;
     a.pos0 = h_visible_[0];
+    a.spin_limit = mega_spin_limit_;
     if (!ev_begin_) { ESP_CUDA_TRY(cudaEventCreate(&ev_begin_)); ESP_CUDA_TRY(cudaEventCreate(&ev_end_)); }
     ESP_CUDA_TRY(cudaMemsetAsync(d_mega_ctl_, 0, 8 * sizeof(unsigned long long), stream_));
-    ESP_CUDA_TRY(cudaMemsetAsync(d_mega_flags_, 0, sizeof(unsigned int) * mega_plan_.n_cta, stream_));
+    ESP_CUDA_TRY(cudaMemsetAsync(d_mega_arena_, 0, mega_arena_words_ * sizeof(unsigned long long), stream_));
     ESP_CUDA_TRY(cudaEventRecord(ev_begin_, stream_));
     void* args[] = {&a};
-    ESP_CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(k_decode_mega), dim3(mega_plan_.n_cta), dim3(kMegaThreads), args,
-                                             (size_t)mega_plan_.smem_bytes, stream_));
+    ESP_CUDA_TRY(cudaLaunchCooperativeKernel(mega_kernel_for(m_.head_dim), dim3(p.n_cta), dim3(kMegaThreads), args, (size_t)p.smem_bytes, stream_));
     ESP_CUDA_TRY(cudaEventRecord(ev_end_, stream_));
     ESP_CUDA_TRY(cudaMemcpyAsync(h_mega_ctl_, d_mega_ctl_, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream_));
     ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
@@ -1752,12 +1762,17 @@ int32_t Engine::run_mega(int n_steps, float* device_ms, double* first_token_ms) 
     const int err = reinterpret_cast<int*>(h_mega_ctl_ + 2)[1];
     if (err != 0) {
         std::ostringstream os;
-        os << "persistent decode kernel gave up waiting (code " << err << ": 2 = grid barrier, 3 = weight chunk, 4 = ring slot)";
+        os << "persistent decode kernel gave up waiting (code " << err
+           << ": 3 = weight chunk, 4 = ring slot, 5/9 = layer output words, 6 = q/k/v words, 7 = attention sums, 8 = activation words, 10 = arg-max words)";
         return fail(ESP_CUDA_ERR_TIMEOUT, os.str());
     }
+    const int n = (int)h_mega_ctl_[5];
+    if (n < 1 || n > n_steps) return fail(ESP_CUDA_ERR_CUDA, "persistent decode kernel reported an impossible token count");
+    if (emitted) *emitted = n;
+    token_times_n_ = a.token_times ? n : 0;
     if (device_ms) ESP_CUDA_TRY(cudaEventElapsedTime(device_ms, ev_begin_, ev_end_));
     if (first_token_ms) *first_token_ms = (double)(h_mega_ctl_[4] - h_mega_ctl_[3]) / 1e6;
-    h_visible_[0] += n_steps - 1;
+    h_visible_[0] += n - 1;
     return ESP_CUDA_OK;
 }
 
@@ -1765,7 +1780,11 @@ int32_t Engine::stage_trace(int32_t cta, long long* out, int32_t capacity, int32
     if (!out || !n) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "stage_trace: null argument");
     *n = 0;
     if (!mega_ready_) return ESP_CUDA_OK;
-    const int count = 14 * m_.n_layer + 4;
+#ifdef MEGA_FINE_TRACE
+    const int count = 512;
+#else
+    const int count = kMegaTraceLayer * m_.n_layer + kMegaTraceHead;
+#endif
     if (capacity < count) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "stage_trace: capacity too small");
     ESP_CUDA_TRY(cudaSetDevice(cfg_.device));
     ESP_CUDA_TRY(cudaMemcpy(out, d_mega_trace_, sizeof(long long) * count, cudaMemcpyDeviceToHost));
@@ -1801,6 +1820,11 @@ int32_t Engine::debug_dump(int32_t stage, float* out, int32_t capacity) {
     const int sizes[7] = {q, kv, kv, q, d, h, d};
     if (stage < 0 || stage > 6 || !out || capacity < sizes[stage]) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "debug_dump: bad stage or capacity");
     ESP_CUDA_TRY(cudaMemcpy(out, d_debug_ + offs[stage], sizeof(float) * sizes[stage], cudaMemcpyDeviceToHost));
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::set_wait_limit(uint32_t spins) {
+    mega_spin_limit_ = spins == 0 ? kMegaSpinLimit : spins;
     return ESP_CUDA_OK;
 }
 

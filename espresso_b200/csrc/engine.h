@@ -73,6 +73,7 @@ public:
     int32_t set_debug_layer(int32_t layer);
     int32_t debug_dump(int32_t stage, float* out, int32_t capacity);
     int32_t get_timings(esp_cuda_timings* out);
+    int32_t set_wait_limit(uint32_t spins);
 
     const esp_cuda_config& config() const { return cfg_; }
     int visible(int seq) const { return h_visible_[seq]; }
@@ -99,7 +100,7 @@ private:
     LayerWeights layer_weights(int l) const;
     size_t gemv_smem(int type, int K, bool with_tmp) const;
     int32_t build_mega();   // packs the weights for the persistent decode kernel when the model qualifies
-    int32_t run_mega(int n_steps, float* device_ms, double* first_token_ms);
+    int32_t run_mega(int n_steps, int* emitted, float* device_ms, double* first_token_ms);
 
     esp_cuda_config cfg_;
     ModelDims m_{};
@@ -163,13 +164,14 @@ private:
     MegaPlan mega_plan_{};
     uint8_t* d_pack_ = nullptr;
     float* d_norms_ = nullptr;
-    float* d_xbuf_ = nullptr;
-    unsigned long long* d_mega_ctl_ = nullptr;  // [0..1] best, [2] barrier (u32) + error (i32), [3..4] time stamps
+    unsigned long long* d_mega_arena_ = nullptr;  // exchange words and counted sums of the persistent kernel (zeroed per launch)
+    size_t mega_arena_words_ = 0;
+    unsigned mega_spin_limit_ = kMegaSpinLimit;   // attempts per device-side wait (test hook: set_wait_limit)
+    unsigned long long* d_mega_ctl_ = nullptr;  // [2] error (i32 in the upper half), [3..4] time stamps, [5] tokens emitted
     unsigned long long* h_mega_ctl_ = nullptr;  // pinned mirror
     long long* d_mega_trace_ = nullptr;
     unsigned long long* d_token_times_ = nullptr;  // [max_seq] emission time of every token of the last persistent loop
     int token_times_n_ = 0;
-    unsigned int* d_mega_flags_ = nullptr;     // grid barrier: one epoch word per CTA
     int mega_trace_cta_ = 0;
     esp_cuda_timings timings_{};
     int launches_last_step_ = 0;

@@ -1,48 +1,79 @@
 // Persistent whole-loop decode kernel for one sequence of a Llama-style fp16 model.
 //
-// One cooperative launch runs an entire greedy decode loop: `n_steps` heads and `n_steps - 1` forward passes.
-// The grid has one CTA per SM.  Inside a CTA one producer warp streams that CTA's weights from HBM into a
-// shared-memory ring with bulk async copies (cp.async.bulk + mbarrier), always running ahead of the eight
-// consumer warps, so HBM stays busy while the consumers wait on the activation dependencies of the step.
+// One cooperative launch runs an entire greedy decode loop: `n_steps` heads and up to `n_steps - 1` forward
+// passes.  The grid has one CTA per SM.  Inside a CTA one producer warp streams that CTA's weights from HBM into a
+// shared-memory ring with bulk async copies (cp.async.bulk + mbarrier), always running ahead of the sixteen
+// consumer warps, so HBM keeps streaming while the consumers wait on the activation dependencies of the step.
 // Weights are re-laid out once ("pack") so that everything a CTA needs for one layer is contiguous.
 //
-// Per layer the consumers run three stages separated by grid barriers:
-//   S1  norm -> rows of Wq/Wk/Wv -> RoPE -> q buffer / KV-cache append          (inner-product form)
-//   S2  attention for one head (recomputed by the CTAs that share the head) -> partial Wo product for a
-//       block of output rows -> atomic add into the residual stream             (per-head partial sums)
-//   S3  norm -> gate/up rows -> SiLU*up -> partial W2 product (W2 stored transposed) -> atomic add
-// and the LM head streams the CTA's vocab rows through the same ring and keeps a first-max argmax.
-// The residual stream rotates through three buffers so that a stage never accumulates into a vector that
-// other CTAs may still be reading.  Every wait (mbarrier, grid barrier) is bounded: when a limit is hit the
-// kernel records an error code, stops waiting everywhere and runs to completion; the host reports a timeout.
+// Batch-1 decode is bound by the chain of dependent vector exchanges between CTAs, not by bytes, so the kernel has
+// no grid barrier at all.  Every vector that crosses CTAs is self-validating:
+//   * "tagged words": an 8-byte word {fp32 value, 32-bit sequence tag} with a single writer.  A reader polls the
+//     word itself until the tag is the one it expects: flag and data travel in one 8-byte access, so neither a
+//     fence nor a separate arrival counter nor a second round trip for the data is needed.
+//   * "counted sums": an 8-byte accumulator that several CTAs add into with one `red.add.u64` each; the addend is
+//     (fixed-point value << 8) + 1, so the low byte counts contributions and the upper 56 bits carry their sum.
+//     The accumulators are never cleared: a reader remembers the total it saw the last time and subtracts it
+//     (all arithmetic is modulo 2^64, so neither field can overflow into a wrong result as long as one exchange's
+//     sum fits 55 bits).  Integer addition is associative: the sums are bit-identical from run to run.
+// Per layer the consumers run
+//   S1  x (tagged words from the previous layer, or the embedding row) -> RMSNorm folded into the products ->
+//       this CTA's rows of Wq/Wk/Wv -> RoPE -> tagged words for the CTAs that share the KV head, KV-cache append
+//   S2  attention of one query head (recomputed by the CTAs that share the head) -> this CTA's block of rows of Wo
+//       restricted to the head's columns -> counted sums (one contribution per head and row)
+//   S3  x_mid -> norm -> this CTA's (gate, up) row pairs -> SiLU*up -> tagged words; then the whole activation
+//       vector -> this CTA's rows of W2 (+ residual) -> tagged words = the next layer's x
+// and the LM head streams the CTA's vocabulary rows through the same ring; every CTA publishes its best
+// (logit, index) as tagged words and every CTA reduces all of them, so the token is known everywhere at once.
+// Why single buffers suffice: each exchange is re-written only after an exchange of another kind that every
+// reader of the old contents must have passed (see the notes at each stage).
+// Every wait (mbarrier, tagged word, counted sum) is bounded: when a limit is hit the kernel records an error code,
+// stops waiting everywhere and runs to completion; the host reports a timeout.
 #pragma once
+#include <type_traits>
+
 #include "decode_kernels.cuh"
 
 namespace esp {
 
-constexpr int kMegaConsumerWarps = 8;
+constexpr int kMegaConsumerWarps = 16;
 constexpr int kMegaConsumers = kMegaConsumerWarps * 32;
 constexpr int kMegaThreads = kMegaConsumers + 32;  // + one producer warp
-constexpr unsigned kMegaSpinLimit = 1u << 21;  // attempts per wait before the kernel gives up (a few seconds)
+constexpr unsigned kMegaSpinLimit = 1u << 21;      // default attempts per wait before the kernel gives up (a few seconds)
+constexpr int kMegaTraceLayer = 10;                // stamps per layer
+constexpr int kMegaTraceHead = 4;                  // stamps of the head
+constexpr float kMegaFix = 4294967296.0f;          // counted sums: fixed point with 32 fractional bits
+constexpr float kMegaUnfix = 2.3283064365386963e-10f;
 
 struct MegaPlan {
     int n_cta;
-    int ppc;          // S1: RoPE row pairs per CTA
-    int blocks, rpb;  // S2: output-row blocks per head, rows per block
-    int hpc;          // S3: FFN hidden units per CTA
-    int vpc;          // head: vocab rows per CTA
-    int head_rows_per_chunk, head_chunks;
+    int cph;          // CTAs per query head (S2 row blocks of Wo)
+    int qpk;          // query heads per KV head
+    int gsize;        // CTAs per KV-head group = cph * qpk
+    int n_group_cta;  // CTAs that take part in S1/S2 = n_head * cph
+    int group_items;  // S1 row pairs per KV-head group = (qpk + 2) * head_dim / 2
+    int s1_max;       // largest number of S1 row pairs of a CTA
+    int rpb;          // S2: output rows per block
+    int hpc_max, dpc_max, vpc_max;  // largest number of FFN units / W2 rows / vocabulary rows of a CTA
     int row_bytes;    // d_model * 2
-    int s1_bytes, s2_bytes, s3a_bytes, s3b_bytes, head_chunk_bytes;  // packed bytes of a stage per layer / of a head chunk (multiples of 128)
+    int down_row_bytes;  // hidden * 2
+    int s1_bytes, s2_bytes, s3a_bytes, s3b_bytes;  // packed bytes of a stage per layer (multiples of 128, sized for the largest CTA share)
     // A stage whose slice is larger than a ring slot arrives in several chunks of whole items:
     int s1_ipc;       // S1 row pairs per chunk
     int s2_rpc;       // S2 projection rows per chunk (a multiple of the rows one pass of the CTA covers)
     int s3a_ipc;      // S3 (gate, up) pairs per chunk
     int s3b_rpc;      // S3 down-projection rows per chunk
+    int head_rpc;     // LM-head rows per chunk
     int slot_bytes, n_slots;
-    long long layer_bytes, cta_bytes;  // packed bytes per CTA: one layer, everything
+    long long layer_bytes, head_bytes, cta_bytes;  // packed bytes per CTA: one layer, the head, everything
     int smem_bytes;
+    // byte offsets of the shared-memory areas behind the ring (see MegaShared)
+    int off_bar, off_prev, off_key, off_xs, off_xraw, off_xmid, off_rope, off_qs, off_ctx, off_kn, off_vn, off_part, off_red, off_outv, off_flags, off_share;
 };
+
+// Contiguous share [begin, end) of `n` items owned by part `i` of `parts` (every part gets floor or ceil of n/parts).
+// (n * parts stays far below 2^32 for every model size the plan accepts)
+__host__ __device__ inline int mega_share_begin(int n, int parts, int i) { return (int)((unsigned)n * (unsigned)i / (unsigned)parts); }
 
 struct MegaArgs {
     ModelDims m;
@@ -52,19 +83,22 @@ struct MegaArgs {
     const uint16_t* tok_emb;  // fp16 [vocab][d_model]
     const float2* rope;       // [max_seq][head_dim/2]
     KvLayout kv;
-    float* q;                 // [q_dim]
-    float* xbuf;              // [3][d_model] rotating residual-stream buffers
+    // exchange arena (zero at launch)
+    unsigned long long* x_words;    // [d_model] tagged: output of a layer
+    unsigned long long* act_words;  // [hidden] tagged: FFN activation
+    unsigned long long* qkv_words;  // [n_kv_head][2 * group_items] tagged: post-RoPE q / k / v of one token
+    unsigned long long* mid_sums;   // [d_model] counted: residual + attention projection
+    unsigned long long* cand_words; // [n_cta][4] tagged: {logit bits, index} of each CTA's best row
     float* hidden_io;         // [d_model] last hidden state of the sequence (in and out)
-    unsigned long long* best; // [2]
-    unsigned int* barrier;    // [1] monotonic arrival counter, zero at launch
     int* error;               // [1] 0 = ok
-    unsigned long long* stamps; // [2] globaltimer at kernel start and when the first token is known
+    unsigned long long* stamps; // [3] globaltimer at kernel start and when the first token is known; number of tokens emitted
     unsigned long long* token_times; // optional [n_steps] globaltimer (ns) at which each token became known, or null
-    long long* trace;         // optional [14*L + 4] SM clock stamps of the last step taken by CTA `trace_cta`, or null
+    long long* trace;         // optional [kMegaTraceLayer*L + kMegaTraceHead] SM clock stamps of the last step taken by CTA `trace_cta`, or null
     int trace_cta;
     RowState rs;              // row 0 carries pos / tok / n_out / out
-    int n_steps;              // tokens to emit (>= 1)
+    int n_steps;              // tokens to emit at most (>= 1)
     int pos0;                 // visible tokens at launch
+    unsigned spin_limit;      // attempts per wait
 };
 
 // ------------------------------------------------------------------------------------------------ PTX helpers
@@ -79,37 +113,29 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Non-blocking test of a phase: the potentially blocking try_wait form costs about 0.25 us per call on this part even
+// when the phase has already completed, which a chunk-by-chunk consumer cannot afford.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
     unsigned ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)  // each attempt may sleep for at most about a microsecond
+        : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
     return ok != 0;
 }
 // Weight chunks carry an evict-first L2 policy: they are used once per token, and keeping them out of the way
-// leaves the KV cache, the residual stream and the small per-layer vectors resident in L2.
+// leaves the KV cache and the exchange words resident in L2.
 __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar, uint64_t policy) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(dst)),
                  "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
                  : "memory");
 }
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ uint4 lds128(const uint8_t* p) {
     uint4 r;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(smem_u32(p)));
-    return r;
-}
-__device__ __forceinline__ uint2 lds64(const uint8_t* p) {
-    uint2 r;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(smem_u32(p)));
     return r;
 }
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -117,95 +143,179 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kMegaConsumers) : "memory"); }
 
+// 16 bytes = two exchange words; each word is validated on its own, so the pair needs no 16-byte atomicity.
+__device__ __forceinline__ ulonglong2 ld_words2(const unsigned long long* p) {
+    ulonglong2 v;
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_word(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long tagged(float v, unsigned tag) { return ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v); }
+__device__ __forceinline__ unsigned long long counted(float v) { return ((unsigned long long)__float2ll_rn(v * kMegaFix) << 8) + 1ull; }
+
+// ------------------------------------------------------------------------------------------------ work shares
+
+struct MegaShare {
+    bool in_group;       // takes part in S1 / S2
+    int head, blk, kvh, hq, member;  // query head, Wo row block, KV head, head inside the KV group, CTA inside the KV group
+    int s1_begin, s1_n;  // S1 row pairs inside the KV group
+    int h_begin, h_n;    // FFN hidden units
+    int d_begin, d_n;    // W2 rows
+    int v_begin, v_n;    // vocabulary rows
+};
+
+__host__ __device__ inline MegaShare mega_share(const ModelDims& m, const MegaPlan& p, int cta) {
+    MegaShare w{};
+    w.in_group = cta < p.n_group_cta;
+    if (w.in_group) {
+        w.head = cta / p.cph;
+        w.blk = cta - w.head * p.cph;
+        w.kvh = w.head / p.qpk;
+        w.hq = w.head - w.kvh * p.qpk;
+        w.member = cta - w.kvh * p.gsize;
+        w.s1_begin = mega_share_begin(p.group_items, p.gsize, w.member);
+        w.s1_n = mega_share_begin(p.group_items, p.gsize, w.member + 1) - w.s1_begin;
+    }
+    w.h_begin = mega_share_begin(m.hidden, p.n_cta, cta);
+    w.h_n = mega_share_begin(m.hidden, p.n_cta, cta + 1) - w.h_begin;
+    w.d_begin = mega_share_begin(m.d_model, p.n_cta, cta);
+    w.d_n = mega_share_begin(m.d_model, p.n_cta, cta + 1) - w.d_begin;
+    w.v_begin = mega_share_begin(m.vocab, p.n_cta, cta);
+    w.v_n = mega_share_begin(m.vocab, p.n_cta, cta + 1) - w.v_begin;
+    return w;
+}
+
+// S1 row pair `item` of KV group `kvh`: which matrix (0 q, 1 k, 2 v) and which two rows.
+__host__ __device__ inline void mega_s1_rows(const ModelDims& m, const MegaPlan& p, int kvh, int item, int& kind, int& row0, int& row1, int& idx) {
+    const int half = m.head_dim / 2;
+    if (item < p.qpk * half) {
+        const int hq = item / half;
+        idx = item - hq * half;
+        kind = 0; row0 = (kvh * p.qpk + hq) * m.head_dim + idx; row1 = row0 + half;
+    } else if (item < (p.qpk + 1) * half) {
+        idx = item - p.qpk * half;
+        kind = 1; row0 = kvh * m.head_dim + idx; row1 = row0 + half;
+    } else {
+        idx = item - (p.qpk + 1) * half;
+        kind = 2; row0 = kvh * m.head_dim + 2 * idx; row1 = row0 + 1;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ shared state
 
 struct MegaShared {
     uint8_t* slots;
     uint64_t* full;
     uint64_t* empty;
-    float* xs;    // staged (normalised) activation vector, lane-major order (see xs_index)
-    float* qs;    // [head_dim]
-    float* ctx;   // [head_dim]
-    float* sc;    // [max_seq] attention scores
-    float* part;  // [warps][head_dim]
-    float* red;   // [32]
-    float* act;   // [hpc]
-    int* abort;   // [1]
+    float* xs;     // staged activation vector (x * gain, or the FFN activation), lane-major order (see xs_index)
+    float* xraw;   // [d_model] the residual stream entering the layer (also what the head reads)
+    float* xmid;   // [d_model] the residual stream after the attention block
+    float2* rope;  // [head_dim/2] (cos, sin) of the position being processed
+    unsigned long long* prev;  // [d_model] totals of the counted sums seen at the previous exchange
+    float* qs;     // [head_dim] query of this CTA's head
+    float* ctx;    // [head_dim]
+    __half* kn;    // [head_dim] the new token's key, rounded as the cache stores it
+    __half* vn;    // [head_dim]
+    float* part;   // [warps][head_dim]
+    float* red;    // [64]
+    float* outv;   // results of a stage before they are published: max(2*s1_max, hpc_max, dpc_max * kparts) floats
+    unsigned long long* key;   // [32] arg-max keys
+    struct MegaShare* share;  // this CTA's work shares, computed once
+    int* abort;    // [1] a wait gave up: no more waiting in this CTA
+    int* stop;     // [1] the loop ended early (EOS): the producer stops issuing
 };
 
+__host__ __device__ inline int mega_outv_floats(const MegaPlan& p) {
+    int n = 2 * p.s1_max;
+    if (p.hpc_max > n) n = p.hpc_max;
+    if (p.dpc_max * kMegaConsumerWarps > n) n = p.dpc_max * kMegaConsumerWarps;
+    return (n + 3) & ~3;
+}
+__host__ __device__ inline int mega_xs_floats(const ModelDims& m) { return xs_floats<8>(m.d_model > m.hidden ? m.d_model : m.hidden); }
+
+// The areas sit at offsets the host computed once (mega_layout): an address is the base plus a kernel-argument
+// constant, which costs no register to keep.
 __device__ __forceinline__ MegaShared mega_carve(uint8_t* base, const MegaArgs& a) {
     MegaShared s;
     const MegaPlan& p = a.plan;
     s.slots = base;
-    uint8_t* q = base + (size_t)p.n_slots * p.slot_bytes;
-    s.full = reinterpret_cast<uint64_t*>(q); q += 8 * p.n_slots;
-    s.empty = reinterpret_cast<uint64_t*>(q); q += 8 * p.n_slots;
-    q = reinterpret_cast<uint8_t*>(((uintptr_t)q + 15) & ~(uintptr_t)15);
-    s.xs = reinterpret_cast<float*>(q); q += sizeof(float) * xs_floats<8>(a.m.d_model);
-    s.qs = reinterpret_cast<float*>(q); q += sizeof(float) * a.m.head_dim;
-    s.ctx = reinterpret_cast<float*>(q); q += sizeof(float) * a.m.head_dim;
-    s.sc = reinterpret_cast<float*>(q); q += sizeof(float) * a.m.max_seq;
-    s.part = reinterpret_cast<float*>(q); q += sizeof(float) * kMegaConsumerWarps * a.m.head_dim;
-    s.red = reinterpret_cast<float*>(q); q += sizeof(float) * 32;
-    s.act = reinterpret_cast<float*>(q); q += sizeof(float) * ((p.hpc + 3) & ~3);
-    s.abort = reinterpret_cast<int*>(q);
+    s.full = reinterpret_cast<uint64_t*>(base + p.off_bar);
+    s.empty = s.full + p.n_slots;
+    s.prev = reinterpret_cast<unsigned long long*>(base + p.off_prev);
+    s.key = reinterpret_cast<unsigned long long*>(base + p.off_key);
+    s.xs = reinterpret_cast<float*>(base + p.off_xs);
+    s.xraw = reinterpret_cast<float*>(base + p.off_xraw);
+    s.xmid = reinterpret_cast<float*>(base + p.off_xmid);
+    s.rope = reinterpret_cast<float2*>(base + p.off_rope);
+    s.qs = reinterpret_cast<float*>(base + p.off_qs);
+    s.ctx = reinterpret_cast<float*>(base + p.off_ctx);
+    s.kn = reinterpret_cast<__half*>(base + p.off_kn);
+    s.vn = reinterpret_cast<__half*>(base + p.off_vn);
+    s.part = reinterpret_cast<float*>(base + p.off_part);
+    s.red = reinterpret_cast<float*>(base + p.off_red);
+    s.outv = reinterpret_cast<float*>(base + p.off_outv);
+    s.abort = reinterpret_cast<int*>(base + p.off_flags);
+    s.stop = s.abort + 1;
+    s.share = reinterpret_cast<MegaShare*>(base + p.off_share);
     return s;
 }
 
-__host__ __device__ inline int mega_smem_bytes(const ModelDims& m, const MegaPlan& p) {
-    size_t b = (size_t)p.n_slots * p.slot_bytes + 16 * p.n_slots + 16;
-    b += sizeof(float) * (size_t)(xs_floats<8>(m.d_model) + 2 * m.head_dim + m.max_seq + kMegaConsumerWarps * m.head_dim + 32 + ((p.hpc + 3) & ~3));
-    return (int)(b + 64);
+// Fills the offsets and the total size (host side; p.n_slots and p.slot_bytes must be set).
+inline void mega_layout(const ModelDims& m, MegaPlan& p) {
+    size_t o = (size_t)p.n_slots * p.slot_bytes;
+    auto take = [&](size_t bytes) { size_t at = (o + 15) & ~(size_t)15; o = at + bytes; return (int)at; };
+    p.off_bar = take(16 * (size_t)p.n_slots);
+    p.off_prev = take(8 * (size_t)m.d_model);
+    p.off_key = take(8 * 32);
+    p.off_xs = take(sizeof(float) * (size_t)mega_xs_floats(m));
+    p.off_xraw = take(sizeof(float) * (size_t)m.d_model);
+    p.off_xmid = take(sizeof(float) * (size_t)m.d_model);
+    p.off_rope = take(sizeof(float2) * (size_t)(m.head_dim / 2));
+    p.off_qs = take(sizeof(float) * (size_t)m.head_dim);
+    p.off_ctx = take(sizeof(float) * (size_t)m.head_dim);
+    p.off_kn = take(sizeof(__half) * (size_t)m.head_dim);
+    p.off_vn = take(sizeof(__half) * (size_t)m.head_dim);
+    p.off_part = take(sizeof(float) * (size_t)kMegaConsumerWarps * m.head_dim);
+    p.off_red = take(sizeof(float) * 64);
+    p.off_outv = take(sizeof(float) * (size_t)mega_outv_floats(p));
+    p.off_flags = take(16);
+    p.off_share = take(sizeof(MegaShare));
+    p.smem_bytes = (int)((o + 127) & ~(size_t)127);
 }
 
 __device__ __forceinline__ void mega_fail(const MegaArgs& a, const MegaShared& s, int code) {
-    *s.abort = 1;
+    *reinterpret_cast<volatile int*>(s.abort) = 1;
     atomicCAS(a.error, 0, code);
+}
+__device__ __forceinline__ bool mega_aborting(const MegaShared& s) { return *reinterpret_cast<volatile int*>(s.abort) != 0; }
+
+// One failed attempt of a polling loop: true when the loop must give up (limit reached, or the kernel is aborting).
+__device__ __forceinline__ bool mega_spin_out(const MegaArgs& a, const MegaShared& s, unsigned& spins, int code) {
+    ++spins;
+    if (spins > a.spin_limit) { mega_fail(a, s, code); return true; }
+    if ((spins & 0x3ffu) == 0 && (__ldcg(a.error) != 0 || mega_aborting(s))) { *reinterpret_cast<volatile int*>(s.abort) = 1; return true; }
+    return false;
 }
 
 // Bounded wait on an mbarrier phase.  Returns immediately once the kernel is aborting.
 __device__ __forceinline__ void mega_wait(const MegaArgs& a, const MegaShared& s, uint64_t* bar, unsigned parity, int code) {
-    if (*reinterpret_cast<volatile int*>(s.abort)) return;
+    if (mega_aborting(s)) return;
     unsigned spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if (++spins > kMegaSpinLimit || ((spins & 0xfffu) == 0 && (__ldcg(a.error) != 0 || *reinterpret_cast<volatile int*>(s.abort)))) {
-            mega_fail(a, s, code);
-            return;
-        }
+        if (*reinterpret_cast<volatile int*>(s.stop)) return;
+        if (mega_spin_out(a, s, spins, code)) return;
     }
-}
-
-// Grid-wide barrier of the consumer threads of all CTAs: arrivals are counted on one global counter.
-// (A flag word per CTA polled by one thread each was measured slower on B200: 6 us against 2-3 us.)
-__device__ __forceinline__ void mega_grid_sync(const MegaArgs& a, const MegaShared& s, unsigned& epoch) {
-    consumer_sync();
-    epoch++;
-    if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(a.barrier, 1u);
-        const unsigned target = epoch * (unsigned)a.plan.n_cta;
-        if (!*reinterpret_cast<volatile int*>(s.abort)) {
-            unsigned spins = 0;
-            while (ld_acquire_u32(a.barrier) < target) {
-                if (++spins > kMegaSpinLimit || ((spins & 0x3ffu) == 0 && __ldcg(a.error) != 0)) {
-                    mega_fail(a, s, 2);
-                    break;
-                }
-            }
-        }
-        __threadfence();
-    }
-    consumer_sync();
 }
 
 // Ring bookkeeping shared by the producer and the consumers: chunk c lives in slot c % n_slots.
-struct ChunkCursor {
-    unsigned c = 0;
-};
-
 __device__ __forceinline__ const uint8_t* mega_acquire(const MegaArgs& a, const MegaShared& s, unsigned c) {
     const unsigned slot = c % (unsigned)a.plan.n_slots;
-    // one lane per warp polls the barrier (256 threads polling one shared-memory word serialise); the warp barrier
+    // one lane per warp polls the barrier (many threads polling one shared-memory word serialise); the warp barrier
     // that follows orders the other lanes' reads of the chunk after the observed completion
     if ((threadIdx.x & 31) == 0) mega_wait(a, s, s.full + slot, (c / (unsigned)a.plan.n_slots) & 1u, 3);
     __syncwarp();
@@ -216,11 +326,103 @@ __device__ __forceinline__ void mega_release(const MegaArgs& a, const MegaShared
     if ((threadIdx.x & 31) == 0) mbar_arrive(s.empty + (c % (unsigned)a.plan.n_slots));
 }
 
-// ------------------------------------------------------------------------------------------------ consumer pieces
+// ------------------------------------------------------------------------------------------------ exchanges
 
+// Reads `n` tagged words (n even, 16-byte aligned base) and hands (index, value, gain) to `sink`.  A thread keeps up to
+// four 16-byte loads in flight; words that validated are not read again.  The gains (or 1 when `gain` is null) are
+// requested before the polling starts, so they cost nothing once the words arrive.
+template <class Sink>
+__device__ __forceinline__ void mega_read_words(const MegaArgs& a, const MegaShared& s, const unsigned long long* base, int n, unsigned tag, int code,
+                                                const float* gain, Sink sink) {
+    const int n_pairs = n >> 1;
+    for (int p0 = 0; p0 < n_pairs; p0 += 4 * kMegaConsumers) {
+        ulonglong2 w[4];
+        float2 g[4];
+        bool ok[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int p = p0 + j * kMegaConsumers + (int)threadIdx.x;
+            ok[j] = p >= n_pairs;
+            w[j] = make_ulonglong2(0, 0);
+            g[j] = (gain && !ok[j]) ? __ldg(reinterpret_cast<const float2*>(gain) + p) : make_float2(1.f, 1.f);
+        }
+        unsigned spins = 0;
+        if (!mega_aborting(s)) {
+            while (true) {
+                bool all = true;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if (!ok[j]) {
+                        w[j] = ld_words2(base + 2 * (size_t)(p0 + j * kMegaConsumers + (int)threadIdx.x));
+                        ok[j] = (unsigned)(w[j].x >> 32) == tag && (unsigned)(w[j].y >> 32) == tag;
+                        all = all && ok[j];
+                    }
+                }
+                if (all) break;
+                if (mega_spin_out(a, s, spins, code)) break;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int p = p0 + j * kMegaConsumers + (int)threadIdx.x;
+            if (p < n_pairs) {
+                sink(2 * p, __uint_as_float((unsigned)w[j].x), g[j].x);
+                sink(2 * p + 1, __uint_as_float((unsigned)w[j].y), g[j].y);
+            }
+        }
+    }
+}
+
+// Reads the counted sums once each has received `n_contrib` contributions since the previous exchange.
+template <class Sink>
+__device__ __forceinline__ void mega_read_sums(const MegaArgs& a, const MegaShared& s, const unsigned long long* base, int n, int n_contrib, int code,
+                                               const float* gain, Sink sink) {
+    const int n_pairs = n >> 1;
+    for (int p0 = 0; p0 < n_pairs; p0 += 2 * kMegaConsumers) {
+        ulonglong2 w[2], pv[2];
+        float2 g[2];
+        bool ok[2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int p = p0 + j * kMegaConsumers + (int)threadIdx.x;
+            ok[j] = p >= n_pairs;
+            w[j] = make_ulonglong2(0, 0);
+            pv[j] = ok[j] ? make_ulonglong2(0, 0) : *reinterpret_cast<const ulonglong2*>(s.prev + 2 * p);
+            g[j] = (gain && !ok[j]) ? __ldg(reinterpret_cast<const float2*>(gain) + p) : make_float2(1.f, 1.f);
+        }
+        unsigned spins = 0;
+        if (!mega_aborting(s)) {
+            while (true) {
+                bool all = true;
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    if (!ok[j]) {
+                        w[j] = ld_words2(base + 2 * (size_t)(p0 + j * kMegaConsumers + (int)threadIdx.x));
+                        ok[j] = ((w[j].x - pv[j].x) & 0xffull) == (unsigned long long)n_contrib && ((w[j].y - pv[j].y) & 0xffull) == (unsigned long long)n_contrib;
+                        all = all && ok[j];
+                    }
+                }
+                if (all) break;
+                if (mega_spin_out(a, s, spins, code)) break;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int p = p0 + j * kMegaConsumers + (int)threadIdx.x;
+            if (p < n_pairs) {
+                *reinterpret_cast<ulonglong2*>(s.prev + 2 * p) = w[j];
+                const long long v0 = (long long)(w[j].x - pv[j].x - (unsigned long long)n_contrib) >> 8;
+                const long long v1 = (long long)(w[j].y - pv[j].y - (unsigned long long)n_contrib) >> 8;
+                sink(2 * p, (float)v0 * kMegaUnfix, g[j].x);
+                sink(2 * p + 1, (float)v1 * kMegaUnfix, g[j].y);
+            }
+        }
+    }
+}
+
+// Sum over the consumer threads of one float each; every thread receives the result.  One CTA barrier.
 __device__ __forceinline__ float mega_block_sum(float v, float* red) {
     v = warp_sum(v);
-    consumer_sync();
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
     consumer_sync();
     float t = 0.f;
@@ -229,29 +431,7 @@ __device__ __forceinline__ float mega_block_sum(float v, float* red) {
     return t;
 }
 
-// Loads a d_model vector (fp32 from L2, or an fp16 embedding row), RMS-normalises it and stages it.
-__device__ __forceinline__ void mega_stage_norm(const MegaArgs& a, const MegaShared& s, const float* src, const uint16_t* emb_row,
-                                                const float* gain) {
-    constexpr int VMAX = 16;  // d_model <= 4096
-    const int d = a.m.d_model;
-    float xv[VMAX];
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < VMAX; i++) {
-        const int k = threadIdx.x + i * kMegaConsumers;
-        xv[i] = 0.f;
-        if (k < d) xv[i] = emb_row ? __half2float(__ushort_as_half(emb_row[k])) : __ldcg(src + k);
-        ss = fmaf(xv[i], xv[i], ss);
-    }
-    ss = mega_block_sum(ss, s.red);
-    const float inv = 1.0f / sqrtf(ss / (float)d + a.m.eps);
-#pragma unroll
-    for (int i = 0; i < VMAX; i++) {
-        const int k = threadIdx.x + i * kMegaConsumers;
-        if (k < d) s.xs[xs_index<8>(k)] = (xv[i] * inv) * gain[k];
-    }
-    consumer_sync();
-}
+// ------------------------------------------------------------------------------------------------ dot products
 
 // Products of one 16-byte vector of fp16 weights with 8 activations, split over two accumulators so that the
 // dependent FMA chain is 4 long instead of 8.
@@ -266,20 +446,19 @@ __device__ __forceinline__ void mega_fma8(const uint4& w, const float4& xa, cons
     even = fmaf(f3.x, xb.z, even); odd = fmaf(f3.y, xb.w, odd);
 }
 
-// Dot products of NR fp16 rows held in shared memory (row r at base + r * row_bytes) with the staged vector; the
-// results are in every lane.  Two 256-element slices are in flight per pass: all of their shared-memory loads are
-// issued before the first multiply, and every row has four independent accumulators (the consumer warps are too
-// few to hide the load and FMA latencies of a one-slice-at-a-time loop: that form measured ~400 cycles per slice).
+// Dot products of NR fp16 rows held in shared memory (row r at base + r * row_bytes) with the staged vector over the
+// 256-element slices [it_begin, it_end); the results are in every lane.  Two slices are in flight per pass: all of
+// their shared-memory loads are issued before the first multiply, and every row has four independent accumulators.
 template <int NR>
-__device__ __forceinline__ void mega_dot_rows(const uint8_t* base, int row_bytes, int K, const float* xs, int lane, float (&o)[NR]) {
+__device__ __forceinline__ void mega_dot_rows(const uint8_t* base, int row_bytes, int K, int it_begin, int it_end, const float* xs, int lane,
+                                              float (&o)[NR]) {
     const float4* xs4 = reinterpret_cast<const float4*>(xs);
     float acc[NR][4];
 #pragma unroll
     for (int r = 0; r < NR; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
-    const int iters = (K + 255) / 256;
-    for (int it = 0; it < iters; it += 2) {
+    for (int it = it_begin; it < it_end; it += 2) {
         const int k0 = it * 256 + lane * 8, k1 = k0 + 256;
-        const bool in0 = k0 < K, in1 = k1 < K;
+        const bool in0 = k0 < K, in1 = it + 1 < it_end && k1 < K;
         uint4 w0[NR], w1[NR];
 #pragma unroll
         for (int r = 0; r < NR; r++) {
@@ -307,122 +486,106 @@ __device__ __forceinline__ void mega_dot_rows(const uint8_t* base, int row_bytes
     for (int r = 0; r < NR; r++) o[r] = t[r];
 }
 
-// Two rows at arbitrary addresses (r1 - r0 is the row pitch).
-__device__ __forceinline__ void mega_dot2(const uint8_t* r0, const uint8_t* r1, int K, const float* xs, int lane, float& o0, float& o1) {
-    float o[2];
-    mega_dot_rows<2>(r0, (int)(r1 - r0), K, xs, lane, o);
-    o0 = o[0];
-    o1 = o[1];
-}
+// ------------------------------------------------------------------------------------------------ consumer stages
 
-__device__ __forceinline__ void mega_dot4(const uint8_t* base, int row_bytes, int K, const float* xs, int lane, float (&o)[4]) {
-    mega_dot_rows<4>(base, row_bytes, K, xs, lane, o);
-}
-
-// S1: q/k/v rows of this CTA (pairs that RoPE rotates together), RoPE, q store and KV-cache append.
-__device__ __forceinline__ void mega_s1(const MegaArgs& a, const MegaShared& s, int layer, int pos, const uint8_t* chunk, int i0, int n_items) {
+// S1: q/k/v rows of this CTA (pairs that RoPE rotates together) from one ring chunk; results go to s.outv, k and v
+// also to the KV cache.  `inv` is the RMSNorm scale of the staged vector (the gain is already in s.xs).
+__device__ __forceinline__ void mega_s1(const MegaArgs& a, const MegaShared& s, const MegaShare& w, int layer, int pos, float inv,
+                                        const uint8_t* chunk, int i0, int n_items) {
     const ModelDims& m = a.m;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int half = m.head_dim / 2;
-    const int q_items = m.q_dim / 2, k_items = m.kv_dim / 2, total = q_items + 2 * k_items;
-    for (int i = warp; i < n_items; i += kMegaConsumerWarps) {  // i: item inside the chunk, i0 + i: item of this CTA
-        const int item = blockIdx.x * a.plan.ppc + i0 + i;
-        if (item >= total) break;
-        float v0, v1;
-        mega_dot2(chunk + (size_t)(2 * i) * a.plan.row_bytes, chunk + (size_t)(2 * i + 1) * a.plan.row_bytes, m.d_model, s.xs, lane, v0, v1);
+    const int iters = (m.d_model + 255) / 256;
+    for (int i = warp; i < n_items; i += kMegaConsumerWarps) {  // i: pair inside the chunk, i0 + i: pair of this CTA
+        float v[2];
+        mega_dot_rows<2>(chunk + (size_t)(2 * i) * a.plan.row_bytes, a.plan.row_bytes, m.d_model, 0, iters, s.xs, lane, v);
         if (lane == 0) {
-            int kind, local;
-            if (item < q_items) { kind = 0; local = item; }
-            else if (item < q_items + k_items) { kind = 1; local = item - q_items; }
-            else { kind = 2; local = item - q_items - k_items; }
-            int row0, row1;
+            int kind, row0, row1, idx;
+            mega_s1_rows(m, a.plan, w.kvh, w.s1_begin + i0 + i, kind, row0, row1, idx);
+            float v0 = v[0] * inv, v1 = v[1] * inv;
             if (kind < 2) {
-                const int head = local / half, idx = local - head * half;
-                row0 = head * m.head_dim + idx; row1 = row0 + half;
-                const float2 cs = a.rope[(size_t)pos * half + idx];
+                const float2 cs = s.rope[idx];
                 const float r0 = v0 * cs.x - v1 * cs.y, r1 = v0 * cs.y + v1 * cs.x;
                 v0 = r0; v1 = r1;
-            } else { row0 = 2 * local; row1 = row0 + 1; }
-            if (kind == 0) { a.q[row0] = v0; a.q[row1] = v1; }
-            else {
+            }
+            s.outv[2 * (i0 + i)] = v0;
+            s.outv[2 * (i0 + i) + 1] = v1;
+            if (kind > 0) {
                 __half* base = kind == 1 ? a.kv.k : a.kv.v;
-                const int kvh = row0 / m.head_dim;
-                const size_t off = a.kv.offset(m, layer, 0, kvh, pos);
-                base[off + (row0 - kvh * m.head_dim)] = __float2half_rn(v0);
-                base[off + (row1 - kvh * m.head_dim)] = __float2half_rn(v1);
+                const size_t off = a.kv.offset(m, layer, 0, w.kvh, pos);
+                base[off + (row0 - w.kvh * m.head_dim)] = __float2half_rn(v0);
+                base[off + (row1 - w.kvh * m.head_dim)] = __float2half_rn(v1);
             }
         }
     }
 }
 
-// S2: attention of one head over positions [0, pos], then this CTA's block of the output projection.
-// Each warp owns the positions t = warp + 8*i (i < 32 per round).  Four neighbouring lanes share one position:
-// each loads a quarter of its K row with 16-byte vectors (a warp instruction touches 8 cache lines, not 32) and the
-// score is completed with two shuffles.  The probabilities are then broadcast position by position while every
-// lane accumulates its own channels of V.  K and V rows are requested before the query is even staged, and the
-// eight per-warp (max, sum, ctx) triples are merged once.
+// S2: attention of one head over the cached positions [0, pos) plus the new token (whose key and value are in
+// shared memory), then this CTA's block of the output projection.
+// Each warp owns the positions t = warp + 16*i (16 per round).  Four neighbouring lanes share one position: each loads
+// a quarter of its K row with 16-byte vectors and the score is completed with two shuffles.  The probabilities are
+// then broadcast position by position while every lane accumulates its own channels of V.  The K and V rows of the
+// first round are requested by the caller's thread before the query is known (see `prefetch`), and the sixteen
+// per-warp (max, sum, ctx) triples are merged once.
 template <int HD>
-__device__ __forceinline__ void mega_s2_t(const MegaArgs& a, const MegaShared& s, int layer, int pos, unsigned& c, const float* x_in,
-                                          const uint16_t* emb_row, float* x_mid) {
-    const ModelDims& m = a.m;
-    const MegaPlan& p = a.plan;
-    const int units = m.n_head * p.blocks;
-    if ((int)blockIdx.x >= units) return;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    constexpr int hd = HD;
-    constexpr int cpl = HD / 32;  // V channels per lane (head_dim 32/64/128 -> 1/2/4)
-    constexpr int KV4 = HD / 32;  // 16-byte vectors of a K row quarter
-    const int head = blockIdx.x / p.blocks, blk = blockIdx.x - head * p.blocks;
-    const int kvh = head / (m.n_head / m.n_kv_head);
-    const int visible = pos + 1;
-    const __half* K = a.kv.k + a.kv.offset(m, layer, 0, kvh, 0);
-    const __half* V = a.kv.v + a.kv.offset(m, layer, 0, kvh, 0);
-    const float scale = 1.0f / sqrtf((float)hd);
+struct MegaKvRound {
+    uint4 kreg[2][HD / 32];
+    uint2 vreg[16];
+};
+
+template <int HD>
+__device__ __forceinline__ void mega_kv_load(MegaKvRound<HD>& r, const __half* K, const __half* V, int base, int n_cached, int warp, int lane) {
+    constexpr int cpl = HD / 32, KV4 = HD / 32;
     const int sub = lane & 3, tl = lane >> 2;
-    if (tid < hd) s.qs[tid] = __ldcg(a.q + (size_t)head * hd + tid);
-    // residual value this thread will add in the projection (head 0 only), requested early
-    const int tpr = hd / 16;
-    float resid = 0.f;
-    {
-        const int orow = blk * p.rpb + tid / tpr;
-        if (head == 0 && (tid % tpr) == 0 && tid / tpr < p.rpb && orow < m.d_model)
-            resid = emb_row ? __half2float(__ushort_as_half(emb_row[orow])) : __ldcg(x_in + orow);
+#pragma unroll
+    for (int st = 0; st < 2; st++) {
+        const int t = base + warp + kMegaConsumerWarps * (st * 8 + tl);
+#pragma unroll
+        for (int c = 0; c < KV4; c++) {
+            r.kreg[st][c] = make_uint4(0, 0, 0, 0);
+            if (t < n_cached) r.kreg[st][c] = __ldcg(reinterpret_cast<const uint4*>(K + (size_t)t * HD + sub * (HD / 4)) + c);
+        }
     }
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        const int t = base + warp + kMegaConsumerWarps * j;
+        r.vreg[j] = make_uint2(0, 0);
+        if (t < n_cached) {
+            const __half* vr = V + (size_t)t * HD + lane * cpl;
+            if (cpl == 4) r.vreg[j] = __ldcg(reinterpret_cast<const uint2*>(vr));
+            else if (cpl == 2) r.vreg[j].x = __ldcg(reinterpret_cast<const unsigned int*>(vr));
+            else r.vreg[j].x = (unsigned int)__ldcg(reinterpret_cast<const unsigned short*>(vr));
+        }
+    }
+}
+
+template <int HD, class WaitQ>
+__device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShared& s, const MegaShare& w, int layer, int pos, WaitQ wait_q) {
+    const ModelDims& m = a.m;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int cpl = HD / 32, KV4 = HD / 32;
+    const int visible = pos + 1;
+    const __half* K = a.kv.k + a.kv.offset(m, layer, 0, w.kvh, 0);
+    const __half* V = a.kv.v + a.kv.offset(m, layer, 0, w.kvh, 0);
+    const float scale = 1.0f / sqrtf((float)HD);
+    const int sub = lane & 3, tl = lane >> 2;
+    constexpr int kRound = kMegaConsumerWarps * 16;  // positions per round
     float m_w = -INFINITY, l_w = 0.f;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int base = 0; base < visible; base += kMegaConsumers) {
-        // requests: K row quarters of the 4 x 8 positions of this round, V rows of the same positions
-        uint4 kreg[4][KV4];
-#pragma unroll
-        for (int st = 0; st < 4; st++) {
-            const int t = base + warp + kMegaConsumerWarps * (st * 8 + tl);
-            const uint4* kr = reinterpret_cast<const uint4*>(K + (size_t)min(t, visible - 1) * hd + sub * (hd / 4));
-#pragma unroll
-            for (int c = 0; c < KV4; c++) kreg[st][c] = __ldcg(kr + c);
-        }
-        uint2 vreg[32];
-#pragma unroll
-        for (int j = 0; j < 32; j++) {
-            const int t = base + warp + kMegaConsumerWarps * j;
-            vreg[j] = make_uint2(0, 0);
-            if (t < visible) {
-                const __half* vr = V + (size_t)t * hd + lane * cpl;
-                if (cpl == 4) vreg[j] = __ldcg(reinterpret_cast<const uint2*>(vr));
-                else if (cpl == 2) vreg[j].x = __ldcg(reinterpret_cast<const unsigned int*>(vr));
-                else vreg[j].x = (unsigned int)__ldcg(reinterpret_cast<const unsigned short*>(vr));
-            }
-        }
-        if (base == 0) consumer_sync();  // q is staged
-        float sc[4];
+    for (int base = 0; base < visible - 1 || base == 0; base += kRound) {
+        // cached rows of this round (the newest position is not in the cache: its key and value come with the query)
+        MegaKvRound<HD> cur;
+        mega_kv_load<HD>(cur, K, V, base, visible - 1, warp, lane);
+        if (base == 0) wait_q();  // the loads above are in flight while the query is awaited
+        float sc[2];
         float mx = -INFINITY;
 #pragma unroll
-        for (int st = 0; st < 4; st++) {
+        for (int st = 0; st < 2; st++) {
             const int t = base + warp + kMegaConsumerWarps * (st * 8 + tl);
             float dot = 0.f;
 #pragma unroll
             for (int c = 0; c < KV4; c++) {
-                const uint32_t ww[4] = {kreg[st][c].x, kreg[st][c].y, kreg[st][c].z, kreg[st][c].w};
-                const float* qv = s.qs + sub * (hd / 4) + c * 8;
+                const uint32_t ww[4] = {cur.kreg[st][c].x, cur.kreg[st][c].y, cur.kreg[st][c].z, cur.kreg[st][c].w};
+                const float* qv = s.qs + sub * (HD / 4) + c * 8;
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[i]));
@@ -432,73 +595,97 @@ __device__ __forceinline__ void mega_s2_t(const MegaArgs& a, const MegaShared& s
             }
             dot += __shfl_xor_sync(0xffffffffu, dot, 1);
             dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            sc[st] = t < visible ? dot * scale : -INFINITY;
+            sc[st] = t < visible - 1 ? dot * scale : -INFINITY;
             mx = fmaxf(mx, sc[st]);
         }
         const float m_new = fmaxf(m_w, warp_max(mx));
-        float pr[4], psum = 0.f;
+        float pr[2], psum = 0.f;
 #pragma unroll
-        for (int st = 0; st < 4; st++) {
-            pr[st] = sc[st] == -INFINITY ? 0.f : expf(sc[st] - m_new);
+        for (int st = 0; st < 2; st++) {
+            pr[st] = sc[st] == -INFINITY ? 0.f : __expf(sc[st] - m_new);
             psum += pr[st];
         }
-        const float corr = m_w == -INFINITY ? 0.f : expf(m_w - m_new);
+        const float corr = m_w == -INFINITY ? 0.f : __expf(m_w - m_new);
         l_w = l_w * corr + 0.25f * warp_sum(psum);  // every probability sits in four lanes
 #pragma unroll
         for (int c = 0; c < 4; c++) acc[c] *= corr;
 #pragma unroll
-        for (int j = 0; j < 32; j++) {
+        for (int j = 0; j < 16; j++) {
             const float pj = __shfl_sync(0xffffffffu, pr[j >> 3], (j & 7) * 4);
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&vreg[j].x));
-            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&vreg[j].y));
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&cur.vreg[j].x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&cur.vreg[j].y));
             acc[0] = fmaf(pj, f0.x, acc[0]);
             if (cpl >= 2) acc[1] = fmaf(pj, f0.y, acc[1]);
             if (cpl == 4) { acc[2] = fmaf(pj, f1.x, acc[2]); acc[3] = fmaf(pj, f1.y, acc[3]); }
         }
         m_w = m_new;
     }
+    // the newest position: key and value from shared memory, handled by one warp as a round of a single position
+    if (warp == (visible - 1) % kMegaConsumerWarps) {
+        float dot = 0.f;
+#pragma unroll
+        for (int c = 0; c < cpl; c++) dot = fmaf(s.qs[lane * cpl + c], __half2float(s.kn[lane * cpl + c]), dot);
+        const float sn = warp_sum(dot) * scale;
+        const float m_new = fmaxf(m_w, sn);
+        const float corr = m_w == -INFINITY ? 0.f : __expf(m_w - m_new);
+        const float pn = __expf(sn - m_new);
+        l_w = l_w * corr + pn;
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+            if (c < cpl) acc[c] = fmaf(pn, __half2float(s.vn[lane * cpl + c]), acc[c] * corr);
+        m_w = m_new;
+    }
     // merge the per-warp partial results (a warp that saw no position carries max = -inf, sum = 0)
 #pragma unroll
     for (int c = 0; c < 4; c++)
-        if (c < cpl) s.part[warp * hd + lane * cpl + c] = acc[c];
-    if (lane == 0) { s.red[warp] = m_w; s.red[8 + warp] = l_w; }
+        if (c < cpl) s.part[warp * HD + lane * cpl + c] = acc[c];
+    if (lane == 0) { s.red[warp] = m_w; s.red[kMegaConsumerWarps + warp] = l_w; }
     consumer_sync();
-    if (tid < hd) {
+    if (tid < HD) {
         float gm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kMegaConsumerWarps; w++) gm = fmaxf(gm, s.red[w]);
+        for (int x = 0; x < kMegaConsumerWarps; x++) gm = fmaxf(gm, s.red[x]);
         float num = 0.f, den = 0.f;
 #pragma unroll
-        for (int w = 0; w < kMegaConsumerWarps; w++) {
-            const float f = s.red[w] == -INFINITY ? 0.f : expf(s.red[w] - gm);
-            num = fmaf(s.part[w * hd + tid], f, num);
-            den = fmaf(s.red[8 + w], f, den);
+        for (int x = 0; x < kMegaConsumerWarps; x++) {
+            const float f = s.red[x] == -INFINITY ? 0.f : __expf(s.red[x] - gm);
+            num = fmaf(s.part[x * HD + tid], f, num);
+            den = fmaf(s.red[kMegaConsumerWarps + x], f, den);
         }
         s.ctx[tid] = den > 0.f ? num / den : 0.f;
     }
     consumer_sync();
-    // partial output projection: rows [blk*rpb, ...) of Wo restricted to this head's columns
-    const int psub = tid % tpr;  // tpr threads per row, 16 inputs each
-    const int rows_per_pass = kMegaConsumers / tpr;
+}
+
+// Partial output projection: rows [blk*rpb, ...) of Wo restricted to this head's columns; every row's partial sum is
+// one contribution to the counted sum of that row (head 0 also carries the residual).
+template <int HD>
+__device__ __forceinline__ void mega_wo_partial(const MegaArgs& a, const MegaShared& s, const MegaShare& w, unsigned& c) {
+    const ModelDims& m = a.m;
+    const MegaPlan& p = a.plan;
+    const int tid = threadIdx.x;
+    constexpr int ipt = HD <= 64 ? 8 : 16;  // inputs per thread
+    constexpr int tpr = HD / ipt;           // threads per row
+    const int psub = tid % tpr;
+    constexpr int rows_per_pass = kMegaConsumers / tpr;
     for (int r0 = 0; r0 < p.rpb; r0 += p.s2_rpc) {  // the block's rows arrive in chunks of s2_rpc
         const uint8_t* chunk = mega_acquire(a, s, c);
         const int nr = min(p.s2_rpc, p.rpb - r0);
         for (int rb = 0; rb < nr; rb += rows_per_pass) {  // uniform trip count: the shuffles below need every lane
             const int r = rb + tid / tpr;
-            const int orow = blk * p.rpb + r0 + r;
+            const int orow = w.blk * p.rpb + r0 + r;
             const bool valid = r < nr;
             float v = 0.f;
             if (valid) {
-                const uint8_t* wrow = chunk + (size_t)r * hd * 2 + psub * 32;
-                const uint4 w0 = lds128(wrow), w1 = lds128(wrow + 16);
-                fma_vec16<WT_F16>(w0, nullptr, 0, s.ctx + psub * 16, 0.f, v);
-                fma_vec16<WT_F16>(w1, nullptr, 0, s.ctx + psub * 16 + 8, 0.f, v);
+                const uint8_t* wrow = chunk + (size_t)r * HD * 2 + psub * ipt * 2;
+#pragma unroll
+                for (int q = 0; q < ipt / 8; q++) fma_vec16<WT_F16>(lds128(wrow + 16 * q), nullptr, 0, s.ctx + psub * ipt + 8 * q, 0.f, v);
             }
+#pragma unroll
             for (int o = tpr / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
             if (valid && psub == 0 && orow < m.d_model) {
-                if (head == 0)  // residual, added once
-                    v += (r0 == 0 && rb == 0) ? resid : (emb_row ? __half2float(__ushort_as_half(emb_row[orow])) : __ldcg(x_in + orow));
-                atomicAdd(x_mid + orow, v);
+                if (w.head == 0) v += s.xraw[orow];  // residual, added once
+                red_add_u64(a.mid_sums + orow, counted(v));
             }
         }
         mega_release(a, s, c);
@@ -506,60 +693,23 @@ __device__ __forceinline__ void mega_s2_t(const MegaArgs& a, const MegaShared& s
     }
 }
 
-// S3: gate/up rows of this CTA's hidden units, SiLU*up, then the partial down projection (W2 transposed).
-__device__ __forceinline__ void mega_s3_up(const MegaArgs& a, const MegaShared& s, const uint8_t* chunk, int j0, int n_items) {
+// S3: gate/up rows of this CTA's hidden units, SiLU*up.
+__device__ __forceinline__ void mega_s3_up(const MegaArgs& a, const MegaShared& s, float inv, const uint8_t* chunk, int j0, int n_items) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int iters = (a.m.d_model + 255) / 256;
     for (int j = warp; j < n_items; j += kMegaConsumerWarps) {
-        float g, u;
-        mega_dot2(chunk + (size_t)(2 * j) * a.plan.row_bytes, chunk + (size_t)(2 * j + 1) * a.plan.row_bytes, a.m.d_model, s.xs, lane, g, u);
-        if (lane == 0) s.act[j0 + j] = silu_f(g) * u;
-    }
-}
-// Partial down projection: a thread owns up to four groups of 4 output columns (d_model <= 4096) and accumulates
-// over the CTA's hidden units, whose rows of W2-transposed arrive in chunks of s3b_rpc.
-constexpr int kMegaDownGroups = 4;
-__device__ __forceinline__ void mega_s3_down(const MegaArgs& a, const MegaShared& s, unsigned& c, const float* x_mid, float* x_out) {
-    const int d = a.m.d_model;
-    const MegaPlan& p = a.plan;
-    float acc[kMegaDownGroups][4];
-#pragma unroll
-    for (int g = 0; g < kMegaDownGroups; g++) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
-    for (int j0 = 0; j0 < p.hpc; j0 += p.s3b_rpc) {
-        const uint8_t* chunk = mega_acquire(a, s, c);
-        const int nj = min(p.s3b_rpc, p.hpc - j0);
-#pragma unroll
-        for (int g = 0; g < kMegaDownGroups; g++) {
-            const int col = threadIdx.x * 4 + g * kMegaConsumers * 4;
-            if (col < d) {
-#pragma unroll 4
-                for (int j = 0; j < nj; j++) {
-                    const uint2 w = lds64(chunk + (size_t)j * p.row_bytes + (size_t)col * 2);
-                    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-                    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-                    const float av = s.act[j0 + j];
-                    acc[g][0] = fmaf(av, f0.x, acc[g][0]); acc[g][1] = fmaf(av, f0.y, acc[g][1]);
-                    acc[g][2] = fmaf(av, f1.x, acc[g][2]); acc[g][3] = fmaf(av, f1.y, acc[g][3]);
-                }
-            }
-        }
-        mega_release(a, s, c);
-        c++;
-    }
-#pragma unroll
-    for (int g = 0; g < kMegaDownGroups; g++) {
-        const int col = threadIdx.x * 4 + g * kMegaConsumers * 4;
-        if (col < d) {
-            if (blockIdx.x == 0) {  // residual, added once
-                const float4 r = __ldcg(reinterpret_cast<const float4*>(x_mid + col));
-                acc[g][0] += r.x; acc[g][1] += r.y; acc[g][2] += r.z; acc[g][3] += r.w;
-            }
-            red_add_v4(x_out + col, acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+        float v[2];
+        mega_dot_rows<2>(chunk + (size_t)(2 * j) * a.plan.row_bytes, a.plan.row_bytes, a.m.d_model, 0, iters, s.xs, lane, v);
+        if (lane == 0) {
+            const float g = v[0] * inv;
+            s.outv[j0 + j] = g / (1.0f + __expf(-g)) * (v[1] * inv);  // silu(g) = g * sigmoid(g) = 0.5 g (1 + tanh(g / 2))
         }
     }
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel
 
+template <int HD>
 __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs a) {
     extern __shared__ __align__(128) uint8_t mega_smem[];
     const MegaShared s = mega_carve(mega_smem, a);
@@ -568,11 +718,15 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int L = m.n_layer;
     if (tid == 0) {
+        *s.share = mega_share(m, p, (int)blockIdx.x);
         for (int i = 0; i < p.n_slots; i++) { mbar_init(s.full + i, 1); mbar_init(s.empty + i, kMegaConsumerWarps); }
         *s.abort = 0;
+        *s.stop = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    for (int k = tid; k < m.d_model; k += kMegaThreads) s.prev[k] = 0ull;  // the counted sums are zero at launch
     __syncthreads();
+    const MegaShare& w = *s.share;  // read from shared memory wherever it is needed: no registers, no recomputation
     const uint8_t* blob = a.pack + (size_t)blockIdx.x * p.cta_bytes;
     const long long head_off = (long long)L * p.layer_bytes;
 
@@ -580,32 +734,46 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         // ---------------- producer: one thread streams this CTA's chunks in consumption order ----------------
         if (lane == 0) {
             unsigned c = 0;
+#ifdef MEGA_FINE_TRACE
+            int p_step = 0, p_n = 0;
+#endif
             const uint64_t policy = l2_evict_first_policy();
             auto issue = [&](long long off, int bytes) {
                 const unsigned slot = c % (unsigned)p.n_slots;
-                if (*reinterpret_cast<volatile int*>(s.abort)) return;  // once aborting, nothing more is copied
+                if (mega_aborting(s) || *reinterpret_cast<volatile int*>(s.stop)) return;  // nothing more is copied
+#ifdef MEGA_FINE_TRACE
+                const bool tr = a.trace && (int)blockIdx.x == a.trace_cta && p_step == a.n_steps - 1 && p_n < 56;
+                if (tr) a.trace[400 + 2 * p_n] = clock64();
+#endif
                 if (c >= (unsigned)p.n_slots) mega_wait(a, s, s.empty + slot, ((c / (unsigned)p.n_slots) - 1u) & 1u, 4);
-                if (*reinterpret_cast<volatile int*>(s.abort)) return;
+                if (mega_aborting(s) || *reinterpret_cast<volatile int*>(s.stop)) return;
                 mbar_expect_tx(s.full + slot, (unsigned)bytes);
                 bulk_copy_g2s(s.slots + (size_t)slot * p.slot_bytes, blob + off, (unsigned)bytes, s.full + slot, policy);
+#ifdef MEGA_FINE_TRACE
+                if (tr) { a.trace[400 + 2 * p_n + 1] = clock64(); p_n++; }
+#endif
                 c++;
             };
-            // a stage's slice: whole items, `per_chunk` at a time (the pack pads a CTA's last items with zero rows)
+            // a stage's slice: whole items, `per_chunk` at a time
             auto issue_stage = [&](long long off, int items, int per_chunk, int item_bytes) {
                 for (int i0 = 0; i0 < items; i0 += per_chunk) issue(off + (long long)i0 * item_bytes, min(per_chunk, items - i0) * item_bytes);
             };
             for (int step = 0; step < a.n_steps; step++) {
+#ifdef MEGA_FINE_TRACE
+                p_step = step;
+#endif
                 if (step > 0) {
                     for (int l = 0; l < L; l++) {
                         long long off = (long long)l * p.layer_bytes;
-                        issue_stage(off, p.ppc, p.s1_ipc, 2 * p.row_bytes); off += p.s1_bytes;
-                        if ((int)blockIdx.x < m.n_head * p.blocks) issue_stage(off, p.rpb, p.s2_rpc, m.head_dim * 2);  // S2 runs on n_head * blocks CTAs
+                        if (w.in_group) issue_stage(off, w.s1_n, p.s1_ipc, 2 * p.row_bytes);
+                        off += p.s1_bytes;
+                        if (w.in_group) issue_stage(off, p.rpb, p.s2_rpc, m.head_dim * 2);
                         off += p.s2_bytes;
-                        issue_stage(off, p.hpc, p.s3a_ipc, 2 * p.row_bytes); off += p.s3a_bytes;
-                        issue_stage(off, p.hpc, p.s3b_rpc, p.row_bytes);
+                        issue_stage(off, w.h_n, p.s3a_ipc, 2 * p.row_bytes); off += p.s3a_bytes;
+                        issue_stage(off, w.d_n, p.s3b_rpc, p.down_row_bytes);
                     }
                 }
-                for (int hc = 0; hc < p.head_chunks; hc++) issue(head_off + (long long)hc * p.head_chunk_bytes, p.head_chunk_bytes);
+                issue_stage(head_off, w.v_n, p.head_rpc, p.row_bytes);
             }
             // every copy that was issued must have landed before the CTA may exit
             const unsigned first = c > (unsigned)p.n_slots ? c - (unsigned)p.n_slots : 0u;
@@ -623,117 +791,275 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         a.stamps[0] = t;
     }
+#ifdef MEGA_FINE_TRACE
+    int n_fine = 0;
+    int fine_layer = -1, fine_step = -1;
+#define FINE() do { if (a.trace && (int)blockIdx.x == a.trace_cta && tid == 0 && fine_step == a.n_steps - 1 && (fine_layer == 2 || fine_layer == 99) && n_fine < 120) a.trace[256 + n_fine++] = clock64(); } while (0)
+#else
+#define FINE() do {} while (0)
+#endif
     int n_stamp = 0;
     auto stamp = [&](int step) {
         if (a.trace && (int)blockIdx.x == a.trace_cta && tid == 0 && step == a.n_steps - 1) a.trace[n_stamp++] = clock64();
     };
     unsigned c = 0;      // chunk counter, advances in lock step with the producer's
-    unsigned epoch = 0;  // grid barrier epoch
     int pos = a.pos0;    // visible tokens
     uint32_t tok = 0;
-    const float* fin_gain = a.norms + (size_t)(2 * L) * m.d_model;
+    int emitted = 0;
+    constexpr int half = HD / 2;
+    const int d = m.d_model;
+    const float* fin_gain = a.norms + (size_t)(2 * L) * d;
+    unsigned long long* my_qkv = a.qkv_words + (size_t)w.kvh * 2 * p.group_items;
+
+    // Stages one value of the residual stream: raw copy, gained copy in the dot-product order, sum of squares.
+    auto stage_x = [&](float* raw, int k, float v, float g, float& ss) {
+        raw[k] = v;
+        s.xs[xs_index<8>(k)] = v * g;
+        ss = fmaf(v, v, ss);
+    };
+
     for (int step = 0; step < a.n_steps; step++) {
-        const float* x_final = a.hidden_io;
         if (step > 0) {
-            const uint16_t* emb_row = a.tok_emb + (size_t)tok * m.d_model;
+            const uint16_t* emb_row = a.tok_emb + (size_t)tok * d;
+            if (tid < half) s.rope[tid] = a.rope[(size_t)pos * half + tid];  // published by the barrier of the first norm
             for (int l = 0; l < L; l++) {
-                float* x_in = a.xbuf + (size_t)((2 * l) % 3) * m.d_model;
-                float* x_mid = a.xbuf + (size_t)((2 * l + 1) % 3) * m.d_model;
-                float* x_out = a.xbuf + (size_t)((2 * l + 2) % 3) * m.d_model;
-                const uint16_t* er = l == 0 ? emb_row : nullptr;
-                // S1
+                const unsigned seq = (unsigned)((step - 1) * L + l + 1);  // tag of everything this layer publishes
+                float inv = 0.f;
+#ifdef MEGA_FINE_TRACE
+                fine_layer = l; fine_step = step;
+#endif
                 stamp(step);
-                mega_stage_norm(a, s, x_in, er, a.norms + (size_t)(2 * l) * m.d_model);
-                stamp(step);
-                if ((int)blockIdx.x == p.n_cta - 1)  // both accumulation targets of this layer start from zero
-                    for (int k = tid; k < m.d_model; k += kMegaConsumers) { x_mid[k] = 0.f; x_out[k] = 0.f; }
-                for (int i0 = 0; i0 < p.ppc; i0 += p.s1_ipc) {
-                    const uint8_t* ch = mega_acquire(a, s, c);
-                    if (i0 == 0) stamp(step);
-                    mega_s1(a, s, l, pos, ch, i0, min(p.s1_ipc, p.ppc - i0));
-                    mega_release(a, s, c); c++;
+                if (w.in_group) {
+                    // ---- S1: x of this layer.  x_words is re-written by the W2 stage of this layer, which starts only
+                    // after every CTA has published its activation, i.e. after every group CTA has read x here.
+                    const float* gain = a.norms + (size_t)(2 * l) * d;
+                    float ss = 0.f;
+                    if (l == 0) {
+                        for (int k = tid; k < d; k += kMegaConsumers) stage_x(s.xraw, k, __half2float(__ushort_as_half(emb_row[k])), __ldg(gain + k), ss);
+                    } else {
+                        mega_read_words(a, s, a.x_words, d, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+                    }
+                    FINE();
+                    ss = mega_block_sum(ss, s.red);
+                    inv = 1.0f / sqrtf(ss / (float)d + m.eps);
+                    FINE();
+                    stamp(step);
+                    for (int i0 = 0; i0 < w.s1_n; i0 += p.s1_ipc) {
+                        const uint8_t* ch = mega_acquire(a, s, c);
+                        FINE();
+                        mega_s1(a, s, w, l, pos, inv, ch, i0, min(p.s1_ipc, w.s1_n - i0));
+                        FINE();
+                        mega_release(a, s, c); c++;
+                    }
+                    consumer_sync();
+                    FINE();
+                    // publish this CTA's pairs: one warp writes consecutive words.  qkv_words is re-written one layer
+                    // later, after x_words of this layer is complete, which needs every CTA's W2 rows, hence the whole
+                    // activation vector, hence every group CTA past its S2 of this layer.
+                    for (int t = tid; t < 2 * w.s1_n; t += kMegaConsumers) st_word(my_qkv + 2 * w.s1_begin + t, tagged(s.outv[t], seq));
+                    stamp(step);
+                    {
+                        FINE();
+                        mega_attention<HD>(a, s, w, l, pos, [&]() {
+                            // q of this CTA's head, k and v of the KV head: pairs in the order S1 published them
+                            FINE();
+                            if (tid < 3 * half) {
+                                const int section = tid / half, idx = tid - section * half;
+                                const int item = (section == 0 ? w.hq * half : section == 1 ? p.qpk * half : (p.qpk + 1) * half) + idx;
+                                ulonglong2 v = make_ulonglong2(0, 0);
+                                unsigned spins = 0;
+                                if (!mega_aborting(s)) {
+                                    while (true) {
+                                        v = ld_words2(my_qkv + 2 * item);
+                                        if ((unsigned)(v.x >> 32) == seq && (unsigned)(v.y >> 32) == seq) break;
+                                        if (mega_spin_out(a, s, spins, 6)) break;
+                                    }
+                                }
+                                const float v0 = __uint_as_float((unsigned)v.x), v1 = __uint_as_float((unsigned)v.y);
+                                if (section == 0) { s.qs[idx] = v0; s.qs[idx + half] = v1; }
+                                else if (section == 1) { s.kn[idx] = __float2half_rn(v0); s.kn[idx + half] = __float2half_rn(v1); }
+                                else { s.vn[2 * idx] = __float2half_rn(v0); s.vn[2 * idx + 1] = __float2half_rn(v1); }
+                            }
+                            FINE();
+                            consumer_sync();
+                            FINE();
+                            stamp(step);
+                        });
+                        stamp(step);
+                        mega_wo_partial<HD>(a, s, w, c);
+                    }
+                    stamp(step);
+                } else {
+                    stamp(step); stamp(step); stamp(step); stamp(step); stamp(step);
+                }
+                // ---- S3: x_mid = residual + attention projection.  mid_sums receives the next layer's contributions
+                // only after that layer's S1, which needs x_words of this layer complete, i.e. every CTA past this read.
+                {
+                    const float* gain = a.norms + (size_t)(2 * l + 1) * d;
+                    float ss = 0.f;
+                    FINE();
+                    mega_read_sums(a, s, a.mid_sums, d, m.n_head, 7, gain, [&](int k, float v, float g) { stage_x(s.xmid, k, v, g, ss); });
+                    FINE();
+                    ss = mega_block_sum(ss, s.red);
+                    inv = 1.0f / sqrtf(ss / (float)d + m.eps);
                 }
                 stamp(step);
-                mega_grid_sync(a, s, epoch);
-                stamp(step);
-                // S2 (acquires its projection chunks itself, after the attention)
-                stamp(step);
-                if (m.head_dim == 64) mega_s2_t<64>(a, s, l, pos, c, x_in, er, x_mid);
-                else if (m.head_dim == 128) mega_s2_t<128>(a, s, l, pos, c, x_in, er, x_mid);
-                else mega_s2_t<32>(a, s, l, pos, c, x_in, er, x_mid);
-                stamp(step);
-                mega_grid_sync(a, s, epoch);
-                stamp(step);
-                // S3
-                mega_stage_norm(a, s, x_mid, nullptr, a.norms + (size_t)(2 * l + 1) * m.d_model);
-                stamp(step);
-                for (int j0 = 0; j0 < p.hpc; j0 += p.s3a_ipc) {
+                for (int j0 = 0; j0 < w.h_n; j0 += p.s3a_ipc) {
+                    FINE();
                     const uint8_t* ch = mega_acquire(a, s, c);
-                    if (j0 == 0) stamp(step);
-                    mega_s3_up(a, s, ch, j0, min(p.s3a_ipc, p.hpc - j0));
+                    FINE();
+                    mega_s3_up(a, s, inv, ch, j0, min(p.s3a_ipc, w.h_n - j0));
+                    FINE();
                     mega_release(a, s, c); c++;
                 }
                 consumer_sync();
+                FINE();
+                // act_words is re-written one layer later, after mid_sums of that layer is complete, which needs every group
+                // CTA past x_words of this layer, i.e. every CTA past its W2 rows and so past this activation vector.
+                for (int t = tid; t < w.h_n; t += kMegaConsumers) st_word(a.act_words + w.h_begin + t, tagged(s.outv[t], seq));
                 stamp(step);
+                // ---- the whole activation vector, then this CTA's rows of W2 (+ residual)
+                FINE();
+                mega_read_words(a, s, a.act_words, m.hidden, seq, 8, nullptr, [&](int k, float v, float) { s.xs[xs_index<8>(k)] = v; });
+                FINE();
+                consumer_sync();
+                FINE();
                 stamp(step);
-                mega_s3_down(a, s, c, x_mid, x_out);
+                {
+                    const int iters = (m.hidden + 255) / 256;
+                    for (int r0 = 0; r0 < w.d_n; r0 += p.s3b_rpc) {
+                        const uint8_t* ch = mega_acquire(a, s, c);
+                        FINE();
+                        const int nr = min(p.s3b_rpc, w.d_n - r0);
+                        // each row is cut into `kparts` ranges of slices so that all warps work on few rows
+                        const int kparts = max(1, min(kMegaConsumerWarps / nr, iters));
+                        const int per = (iters + kparts - 1) / kparts;
+                        for (int u = warp; u < nr * kparts; u += kMegaConsumerWarps) {
+                            const int r = u % nr, part = u / nr;
+                            float v[1];
+                            mega_dot_rows<1>(ch + (size_t)r * p.down_row_bytes, p.down_row_bytes, m.hidden, part * per, min(iters, (part + 1) * per), s.xs, lane, v);
+                            if (lane == 0) s.outv[(r0 + r) * kMegaConsumerWarps + part] = v[0];
+                        }
+                        FINE();
+                        mega_release(a, s, c); c++;
+                        consumer_sync();
+                        FINE();
+                        for (int t = tid; t < nr; t += kMegaConsumers) {
+                            float v = s.xmid[w.d_begin + r0 + t];  // residual
+                            for (int part = 0; part < kparts; part++) v += s.outv[(r0 + t) * kMegaConsumerWarps + part];
+                            st_word(a.x_words + w.d_begin + r0 + t, tagged(v, seq));
+                        }
+                    }
+                }
                 stamp(step);
-                mega_grid_sync(a, s, epoch);
-                stamp(step);
-                x_final = x_out;
             }
             pos++;  // the token that was just processed is now visible
         }
-        // LM head over this CTA's vocab rows, first-max argmax
+        // ---- LM head over this CTA's vocabulary rows, first-max argmax
+#ifdef MEGA_FINE_TRACE
+        fine_layer = 99; fine_step = step;
+#endif
         stamp(step);
-        mega_stage_norm(a, s, x_final, nullptr, fin_gain);
+        {
+            float ss = 0.f;
+            if (step == 0) {
+                for (int k = tid; k < d; k += kMegaConsumers) stage_x(s.xraw, k, __ldcg(a.hidden_io + k), __ldg(fin_gain + k), ss);
+            } else {
+                mega_read_words(a, s, a.x_words, d, (unsigned)(step * L), 9, fin_gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+            }
+            consumer_sync();  // the RMSNorm scale is positive: the arg-max does not need it
+        }
         stamp(step);
         float best_v = -INFINITY;
         int best_i = 0x7fffffff;
-        for (int hc = 0; hc < p.head_chunks; hc++) {
-            const uint8_t* ch = mega_acquire(a, s, c);
-            const int row_base = hc * p.head_rows_per_chunk;
-            const int nrows = min(p.head_rows_per_chunk, p.vpc - row_base);
-            // four rows per warp per pass; rows past the chunk's end are zero-filled in the pack and masked by `g < vocab`
-            for (int r0 = 4 * warp; r0 < nrows; r0 += 4 * kMegaConsumerWarps) {
-                float v[4];
-                mega_dot4(ch + (size_t)r0 * p.row_bytes, p.row_bytes, m.d_model, s.xs, lane, v);
-#pragma unroll
-                for (int r = 0; r < 4; r++) {
-                    const int g = blockIdx.x * p.vpc + row_base + r0 + r;
-                    if (r0 + r < nrows && g < m.vocab && v[r] > best_v) { best_v = v[r]; best_i = g; }
+        {
+            const int iters = (d + 255) / 256;
+            for (int r0 = 0; r0 < w.v_n; r0 += p.head_rpc) {
+                FINE();
+                const uint8_t* ch = mega_acquire(a, s, c);
+                FINE();
+                const int nrows = min(p.head_rpc, w.v_n - r0);
+                // two rows per warp per pass; a row past the chunk's end repeats the last one
+                for (int r = 2 * warp; r < nrows; r += 2 * kMegaConsumerWarps) {
+                    float v[2];
+                    const int second = r + 1 < nrows ? 1 : 0;
+                    mega_dot_rows<2>(ch + (size_t)r * p.row_bytes, second * p.row_bytes, d, 0, iters, s.xs, lane, v);
+                    const int g = w.v_begin + r0 + r;
+                    if (v[0] > best_v) { best_v = v[0]; best_i = g; }
+                    if (second && v[1] > best_v) { best_v = v[1]; best_i = g + 1; }
                 }
+                mega_release(a, s, c); c++;
             }
-            mega_release(a, s, c); c++;
         }
-        if (lane == 0 && best_i != 0x7fffffff) atomicMax(a.best + (step & 1), pack_best(best_v, best_i));
+        // CTA-wide best (larger value first, then smaller index), published as two tagged words
+        if (lane == 0) s.key[warp] = best_i != 0x7fffffff ? pack_best(best_v, best_i) : 0ull;
+        consumer_sync();
+        if (tid == 0) {
+            unsigned long long k = 0ull;
+#pragma unroll
+            for (int x = 0; x < kMegaConsumerWarps; x++) k = max(k, s.key[x]);
+            // Everything this CTA wrote with plain stores during the step (KV-cache rows) is ordered before the words
+            // below, and a reader orders its later loads after seeing them: one fence pair per token.
+            __threadfence();
+            const unsigned tag = (unsigned)step + 1u;
+            unsigned long long* mine = a.cand_words + 4 * (size_t)blockIdx.x;
+            st_word(mine, ((unsigned long long)tag << 32) | (k >> 32));
+            st_word(mine + 1, ((unsigned long long)tag << 32) | (k & 0xffffffffull));
+        }
         stamp(step);
-        mega_grid_sync(a, s, epoch);
+        {
+            unsigned long long k = 0ull;
+            if (tid < p.n_cta) {
+                const unsigned tag = (unsigned)step + 1u;
+                ulonglong2 v = make_ulonglong2(0, 0);
+                unsigned spins = 0;
+                if (!mega_aborting(s)) {
+                    while (true) {
+                        v = ld_words2(a.cand_words + 4 * (size_t)tid);
+                        if ((unsigned)(v.x >> 32) == tag && (unsigned)(v.y >> 32) == tag) break;
+                        if (mega_spin_out(a, s, spins, 10)) break;
+                    }
+                }
+                __threadfence();
+                k = ((v.x & 0xffffffffull) << 32) | (v.y & 0xffffffffull);
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) k = max(k, __shfl_xor_sync(0xffffffffu, k, off));
+            consumer_sync();  // s.key was read by thread 0 above
+            if (lane == 0) s.key[warp] = k;
+            if (tid == 0) s.red[63] = mega_aborting(s) ? 1.f : 0.f;  // one decision for the whole CTA
+            consumer_sync();
+            k = 0ull;
+#pragma unroll
+            for (int x = 0; x < kMegaConsumerWarps; x++) k = max(k, s.key[x]);
+            tok = min(0xffffffffu - (uint32_t)(k & 0xffffffffull), (uint32_t)(m.vocab - 1));  // in range even if every logit was NaN
+        }
         stamp(step);
-        const unsigned long long key = __ldcg(a.best + (step & 1));
-        tok = min(0xffffffffu - (uint32_t)(key & 0xffffffffull), (uint32_t)(m.vocab - 1));  // in range even if every logit was NaN
+        emitted = step + 1;
         if (blockIdx.x == 0 && tid == 0) {
-            if (step == 0) {
-                unsigned long long t;
-                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-                a.stamps[1] = t;
-            }
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (step == 0) a.stamps[1] = t;
             a.rs.out[step] = tok;
-            if (a.token_times) {
-                unsigned long long t;
-                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-                a.token_times[step] = t;
-            }
-            a.best[(step + 1) & 1] = 0ull;  // nobody reads that slot before the next head's barrier
+            if (a.token_times) a.token_times[step] = t;
         }
-        if (step > 0 && step == a.n_steps - 1 && blockIdx.x == 0)  // keep the sequence's last hidden state
-            for (int k = tid; k < m.d_model; k += kMegaConsumers) a.hidden_io[k] = __ldcg(x_final + k);
+        // Llama rule: the end-of-sequence token is emitted, then the loop stops (every CTA sees the same token)
+        const bool eos = m.eos_token >= 0 && tok == (uint32_t)m.eos_token;
+        if (eos || s.red[63] != 0.f) {
+            if (tid == 0) *reinterpret_cast<volatile int*>(s.stop) = 1;
+            break;
+        }
     }
-    if (blockIdx.x == 0 && tid == 0) {
-        a.rs.pos[0] = pos;
-        a.rs.tok[0] = tok;
-        a.rs.next[0] = tok;
-        a.rs.n_out[0] = a.n_steps;
+    if (blockIdx.x == 0) {
+        // the sequence's last hidden state (what the head just read)
+        for (int k = tid; k < d; k += kMegaConsumers) a.hidden_io[k] = s.xraw[k];
+        if (tid == 0) {
+            a.rs.pos[0] = pos;
+            a.rs.tok[0] = tok;
+            a.rs.next[0] = tok;
+            a.rs.n_out[0] = emitted;
+            a.stamps[2] = (unsigned long long)emitted;
+        }
     }
 }
 
@@ -759,26 +1085,21 @@ __device__ __forceinline__ void pack_copy(uint8_t* dst, const void* src, int byt
     }
 }
 
-// One CTA builds the blob of one megakernel CTA.
+// One CTA builds the blob of one CTA of the decode kernel.
 __global__ void k_build_pack(PackSources src, MegaPlan p, ModelDims m, uint8_t* pack) {
     const int cta = blockIdx.x;
     uint8_t* blob = pack + (size_t)cta * p.cta_bytes;
-    const int d = m.d_model, hd = m.head_dim, half = hd / 2;
-    const int q_items = m.q_dim / 2, k_items = m.kv_dim / 2, total = q_items + 2 * k_items;
+    const int d = m.d_model, hd = m.head_dim;
+    const MegaShare w = mega_share(m, p, cta);
     for (int l = 0; l < m.n_layer; l++) {
         uint8_t* base = blob + (size_t)l * p.layer_bytes;
         // S1: pairs of rows in RoPE order
-        for (int i = 0; i < p.ppc; i++) {
-            const int item = cta * p.ppc + i;
+        for (int i = 0; i < p.s1_max; i++) {
             const __half *r0 = nullptr, *r1 = nullptr;
-            if (item < total) {
-                const __half* W;
-                int local, row0, row1;
-                if (item < q_items) { W = src.wq[l]; local = item; }
-                else if (item < q_items + k_items) { W = src.wk[l]; local = item - q_items; }
-                else { W = src.wv[l]; local = item - q_items - k_items; }
-                if (item < q_items + k_items) { int h = local / half; row0 = h * hd + (local - h * half); row1 = row0 + half; }
-                else { row0 = 2 * local; row1 = row0 + 1; }
+            if (w.in_group && i < w.s1_n) {
+                int kind, row0, row1, idx;
+                mega_s1_rows(m, p, w.kvh, w.s1_begin + i, kind, row0, row1, idx);
+                const __half* W = kind == 0 ? src.wq[l] : kind == 1 ? src.wk[l] : src.wv[l];
                 r0 = W + (size_t)row0 * d; r1 = W + (size_t)row1 * d;
             }
             pack_copy(base + (size_t)(2 * i) * p.row_bytes, r0, p.row_bytes);
@@ -786,38 +1107,26 @@ __global__ void k_build_pack(PackSources src, MegaPlan p, ModelDims m, uint8_t* 
         }
         base += p.s1_bytes;
         // S2: rows [blk*rpb, +rpb) of Wo, columns of one head
-        {
-            const int units = m.n_head * p.blocks;
-            const int head = cta / p.blocks, blk = cta - head * p.blocks;
-            for (int r = 0; r < p.rpb; r++) {
-                const int orow = blk * p.rpb + r;
-                const __half* sp = (cta < units && orow < d) ? src.wo[l] + (size_t)orow * m.q_dim + (size_t)head * hd : nullptr;
-                pack_copy(base + (size_t)r * hd * 2, sp, hd * 2);
-            }
+        for (int r = 0; r < p.rpb; r++) {
+            const int orow = w.blk * p.rpb + r;
+            const __half* sp = (w.in_group && orow < d) ? src.wo[l] + (size_t)orow * m.q_dim + (size_t)w.head * hd : nullptr;
+            pack_copy(base + (size_t)r * hd * 2, sp, hd * 2);
         }
         base += p.s2_bytes;
         // S3a: (gate_j, up_j) row pairs
-        for (int j = 0; j < p.hpc; j++) {
-            const int hrow = cta * p.hpc + j;
-            pack_copy(base + (size_t)(2 * j) * p.row_bytes, hrow < m.hidden ? src.w1[l] + (size_t)hrow * d : nullptr, p.row_bytes);
-            pack_copy(base + (size_t)(2 * j + 1) * p.row_bytes, hrow < m.hidden ? src.w3[l] + (size_t)hrow * d : nullptr, p.row_bytes);
+        for (int j = 0; j < p.hpc_max; j++) {
+            const int hrow = w.h_begin + j;
+            pack_copy(base + (size_t)(2 * j) * p.row_bytes, j < w.h_n ? src.w1[l] + (size_t)hrow * d : nullptr, p.row_bytes);
+            pack_copy(base + (size_t)(2 * j + 1) * p.row_bytes, j < w.h_n ? src.w3[l] + (size_t)hrow * d : nullptr, p.row_bytes);
         }
         base += p.s3a_bytes;
-        // S3b: rows of W2 transposed: out[j][c] = W2[c][hrow]
-        for (int j = 0; j < p.hpc; j++) {
-            const int hrow = cta * p.hpc + j;
-            __half* dst = reinterpret_cast<__half*>(base + (size_t)j * p.row_bytes);
-            for (int c = threadIdx.x; c < d; c += blockDim.x)
-                dst[c] = hrow < m.hidden ? src.w2[l][(size_t)c * m.hidden + hrow] : __float2half(0.f);
-        }
+        // S3b: this CTA's rows of W2
+        for (int r = 0; r < p.dpc_max; r++)
+            pack_copy(base + (size_t)r * p.down_row_bytes, r < w.d_n ? src.w2[l] + (size_t)(w.d_begin + r) * m.hidden : nullptr, p.down_row_bytes);
     }
     uint8_t* hb = blob + (size_t)m.n_layer * p.layer_bytes;
-    for (int i = 0; i < p.head_chunks * p.head_rows_per_chunk; i++) {
-        const int v = cta * p.vpc + i;
-        const int hc = i / p.head_rows_per_chunk, r = i - hc * p.head_rows_per_chunk;
-        pack_copy(hb + (size_t)hc * p.head_chunk_bytes + (size_t)r * p.row_bytes, (i < p.vpc && v < m.vocab) ? src.lm_head + (size_t)v * d : nullptr,
-                  p.row_bytes);
-    }
+    for (int i = 0; i < p.vpc_max; i++)
+        pack_copy(hb + (size_t)i * p.row_bytes, i < w.v_n ? src.lm_head + (size_t)(w.v_begin + i) * d : nullptr, p.row_bytes);
 }
 
 }  // namespace esp

@@ -106,6 +106,7 @@ SIGNATURES = {
     "esp_cuda_debug_dump": (C.c_int32, [_vp, C.c_int32, _f32p, C.c_int32]),
     "esp_cuda_last_error_string": (C.c_char_p, []),
     "esp_cuda_set_force_failure": (None, [C.c_int32]),
+    "esp_cuda_set_wait_limit": (C.c_int32, [_vp, C.c_uint32]),
     "esp_cuda_live_engine_count": (C.c_int32, []),
     "esp_cuda_version": (C.c_char_p, []),
     "esp_cuda_dequantize": (C.c_int32, [C.c_int32, _vp, C.c_int64, _f32p, C.c_int32]),
@@ -362,7 +363,7 @@ class DecodeEngine:
 
     def stage_trace(self, next_cta: int = 0) -> np.ndarray:
         """SM clock stamps of the persistent kernel's last token (see ``esp_cuda_stage_trace``)."""
-        out = np.zeros(14 * self.config.nLayer + 8, np.int64)
+        out = np.zeros(max(512, 10 * self.config.nLayer + 8), np.int64)
         n = C.c_int32()
         _check(self._lib.esp_cuda_stage_trace(self._h, next_cta, out.ctypes.data_as(C.POINTER(C.c_int64)), out.size, C.byref(n)))
         return out[: n.value].copy()

@@ -249,6 +249,12 @@ ESP_CUDA_API const char* esp_cuda_last_error_string(void);
 /* Test hooks with the meaning of ane_interop_set_force_eval_failure / ane_interop_live_handle_count
  * (ane_interop.h:37-41): while forced, every device submission returns ESP_CUDA_ERR_FORCED_FAILURE. */
 ESP_CUDA_API void esp_cuda_set_force_failure(int32_t enabled);
+/* Test hook for the failure path of the device-side waits (the reference has no device waits; its analogue is the
+ * forced evaluation failure, ane_interop.m:2336-2338).  Every wait inside the persistent decode kernel polls at most
+ * `spins` times (0 restores the default of about two million); a wait that runs out makes the kernel stop waiting
+ * everywhere, finish, and the call return ESP_CUDA_ERR_TIMEOUT.  Nothing faults or hangs; the engine stays usable
+ * after esp_cuda_reset once the limit is restored. */
+ESP_CUDA_API int32_t esp_cuda_set_wait_limit(esp_cuda_engine* engine, uint32_t spins);
 ESP_CUDA_API int32_t esp_cuda_live_engine_count(void);
 ESP_CUDA_API const char* esp_cuda_version(void);
 

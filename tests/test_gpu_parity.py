@@ -227,23 +227,29 @@ def test_persistent_kernel_matches_per_stage_kernels(rt, oracle_lib, tmp_models)
         d = tmp_models(cfg)
         prompt = synthetic_prompt(cfg.vocab, 11)
         ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(d))
-        streams = []
+        streams, near = [], []
         for flags in (0, rt.FLAG_NO_MEGAKERNEL):
             eng = rt.DecodeEngine.build(d, flags=flags)
             eng.prefill(prompt)
             toks, ms = eng.decode(n)
             assert len(toks[0]) == n and ms > 0
-            assert eng.timings()["kernel_launches"] == (1 if flags == 0 else eng.timings()["kernel_launches"])
-            compare_greedy_stream(ora, prompt, toks[0])
+            if flags == 0:
+                assert eng.timings()["kernel_launches"] == 1  # the whole loop was one persistent launch
+            else:
+                assert eng.timings()["kernel_launches"] > n
+            near.append(compare_greedy_stream(ora, prompt, toks[0]))
             # the state left behind continues correctly through the step API
             assert eng.visible_token_count() == len(prompt) + n - 1
             assert_logits_close(eng.logits(), _oracle_logits_after(ora, prompt, toks[0][:-1]), f"{cfg.name} flags {flags}")
             nxt = eng.decode_step(int(toks[0][-1]))
-            assert nxt == int(np.argmax(eng.logits())) or True
+            lg = eng.logits()
+            assert lg[nxt] >= lg.max() - 1e-3  # the step's token is the arg-max of the logits the engine reports
             streams.append(toks[0])
             eng.close()
-        agree = int((streams[0] == streams[1]).sum())
-        assert agree >= n - 8, f"{cfg.name}: persistent and per-stage streams agree on {agree}/{n} tokens"
+        # Both routes follow the oracle's arg-max except at its near ties, so they are identical up to the first position
+        # where either met one (after that the two sequences are different inputs).
+        first = min(near[0] + near[1] + [n])
+        assert np.array_equal(streams[0][:first], streams[1][:first]), f"{cfg.name}: streams differ before the first near tie at {first}"
 
 
 def _oracle_logits_after(ora, prompt, fed):
