@@ -1619,7 +1619,7 @@ int32_t Engine::build_mega() {
     if ((cfg_.flags & ESP_CUDA_FLAG_NO_MEGAKERNEL) || tp_size_ > 1) return ESP_CUDA_OK;
     if (m_.arch != ARCH_LLAMA) return ESP_CUDA_OK;
     if (m_.head_dim != 32 && m_.head_dim != 64 && m_.head_dim != 128) return ESP_CUDA_OK;
-    if (m_.d_model % 8 || m_.hidden % 8 || m_.n_head > sm_count_ || m_.n_head > 255) return ESP_CUDA_OK;
+    if (m_.d_model % 32 || m_.hidden % 32 || m_.n_head > sm_count_ || m_.n_head > 255) return ESP_CUDA_OK;
     // fp16 source of a matrix: its own storage, or the fp16 expansion of a quantised matrix
     auto f16_source = [&](const std::string& name) -> const __half* {
         const DeviceTensor& t = tensors_.at(name);
@@ -1658,16 +1658,15 @@ int32_t Engine::build_mega() {
     p.layer_bytes = (long long)p.s1_bytes + p.s2_bytes + p.s3a_bytes + p.s3b_bytes;
     p.head_bytes = pad128((long long)p.vpc_max * p.row_bytes);
     p.cta_bytes = p.layer_bytes * m_.n_layer + p.head_bytes;
-    // ring slots of 48 KB (more when one item of a stage is larger); a stage slice travels as chunks of whole items
-    const int s2_rows_per_pass = kMegaConsumers / (m_.head_dim <= 64 ? m_.head_dim / 8 : m_.head_dim / 16);
-    const int item_max = std::max(std::max(2 * p.row_bytes, p.down_row_bytes), m_.head_dim * 2 * std::min(p.rpb, s2_rows_per_pass));
+    // ring slots of 48 KB (more when one item of a stage is larger); a stage slice travels as chunks of whole items,
+    // at most kMegaChunkRows rows each (the products of a chunk are spread over the warps as 8-row tiles)
+    const int item_max = std::max(2 * p.row_bytes, p.down_row_bytes);
     p.slot_bytes = pad128(std::max(48 * 1024, item_max));
-    p.s1_ipc = std::max(1, std::min(p.s1_max, p.slot_bytes / (2 * p.row_bytes)));
-    p.s3a_ipc = std::max(1, std::min(p.hpc_max, p.slot_bytes / (2 * p.row_bytes)));
-    p.s3b_rpc = std::max(1, std::min(p.dpc_max, p.slot_bytes / p.down_row_bytes));
-    p.head_rpc = std::max(1, std::min(p.vpc_max, p.slot_bytes / p.row_bytes));
-    if ((long long)p.rpb * m_.head_dim * 2 <= p.slot_bytes) p.s2_rpc = p.rpb;
-    else p.s2_rpc = std::max(s2_rows_per_pass, p.slot_bytes / (m_.head_dim * 2) / s2_rows_per_pass * s2_rows_per_pass);
+    p.s1_ipc = std::max(1, std::min(std::min(p.s1_max, kMegaChunkRows / 2), p.slot_bytes / (2 * p.row_bytes)));
+    p.s3a_ipc = std::max(1, std::min(std::min(p.hpc_max, kMegaChunkRows / 2), p.slot_bytes / (2 * p.row_bytes)));
+    p.s3b_rpc = std::max(1, std::min(std::min(p.dpc_max, kMegaChunkRows), p.slot_bytes / p.down_row_bytes));
+    p.head_rpc = std::max(1, std::min(std::min(p.vpc_max, kMegaChunkRows), p.slot_bytes / p.row_bytes));
+    p.s2_rpc = std::max(1, std::min(std::min(p.rpb, kMegaChunkRows), p.slot_bytes / (m_.head_dim * 2)));
     p.n_slots = 0;
     for (int ns = 8; ns >= 2; ns--) {
         MegaPlan probe = p;

@@ -25,6 +25,11 @@
 //       vector -> this CTA's rows of W2 (+ residual) -> tagged words = the next layer's x
 // and the LM head streams the CTA's vocabulary rows through the same ring; every CTA publishes its best
 // (logit, index) as tagged words and every CTA reduces all of them, so the token is known everywhere at once.
+// Products.  The fp16->fp32 conversion rate of the CUDA cores (measured: 20-26 weights per clock per SM from shared
+// memory) would make the row products the longest link of the chain, so they are issued as m16n8k16 tensor-core
+// instructions: sixteen weight rows are the A operand, and the fp32 activation vector, split exactly into two fp16
+// vectors (x = hi + lo, |error| <= 2^-22 |x|), occupies columns 0 and 1 of the B operand; the accumulators are fp32.  The
+// pack stores every chunk in the order the A fragments are read: for each block of 32 columns, for each row, 64 bytes.
 // Why single buffers suffice: each exchange is re-written only after an exchange of another kind that every
 // reader of the old contents must have passed (see the notes at each stage).
 // Every wait (mbarrier, tagged word, counted sum) is bounded: when a limit is hit the kernel records an error code,
@@ -42,6 +47,7 @@ constexpr int kMegaThreads = kMegaConsumers + 32;  // + one producer warp
 constexpr unsigned kMegaSpinLimit = 1u << 21;      // default attempts per wait before the kernel gives up (a few seconds)
 constexpr int kMegaTraceLayer = 10;                // stamps per layer
 constexpr int kMegaTraceHead = 4;                  // stamps of the head
+constexpr int kMegaChunkRows = 256;                // most rows of one chunk (16 tiles of 16 rows)
 constexpr float kMegaFix = 4294967296.0f;          // counted sums: fixed point with 32 fractional bits
 constexpr float kMegaUnfix = 2.3283064365386963e-10f;
 
@@ -192,9 +198,9 @@ __host__ __device__ inline MegaShare mega_share(const ModelDims& m, const MegaPl
 
 // S1 row pair `item` of KV group `kvh`: which matrix (0 q, 1 k, 2 v) and which two rows.
 __host__ __device__ inline void mega_s1_rows(const ModelDims& m, const MegaPlan& p, int kvh, int item, int& kind, int& row0, int& row1, int& idx) {
-    const int half = m.head_dim / 2;
+    const int half = m.head_dim / 2, lg_half = m.head_dim == 32 ? 4 : m.head_dim == 64 ? 5 : 6;  // head_dim is 32, 64 or 128
     if (item < p.qpk * half) {
-        const int hq = item / half;
+        const int hq = item >> lg_half;
         idx = item - hq * half;
         kind = 0; row0 = (kvh * p.qpk + hq) * m.head_dim + idx; row1 = row0 + half;
     } else if (item < (p.qpk + 1) * half) {
@@ -206,37 +212,32 @@ __host__ __device__ inline void mega_s1_rows(const ModelDims& m, const MegaPlan&
     }
 }
 
+// Bytes of a staged vector of K values (hi and lo fp16 parts; see xa_index).
+__host__ __device__ inline int xa_bytes(int K) { return (K / 32) * 128; }
+
 // ------------------------------------------------------------------------------------------------ shared state
 
 struct MegaShared {
     uint8_t* slots;
     uint64_t* full;
     uint64_t* empty;
-    float* xs;     // staged activation vector (x * gain, or the FFN activation), lane-major order (see xs_index)
+    uint8_t* xa;   // staged activation vector (x * gain, or the FFN activation) as the A operand: hi/lo fp16 (see xa_index)
     float* xraw;   // [d_model] the residual stream entering the layer (also what the head reads)
     float* xmid;   // [d_model] the residual stream after the attention block
     float2* rope;  // [head_dim/2] (cos, sin) of the position being processed
     unsigned long long* prev;  // [d_model] totals of the counted sums seen at the previous exchange
     float* qs;     // [head_dim] query of this CTA's head
-    float* ctx;    // [head_dim]
+    float* ctx;    // [head_dim] attention output of this CTA's head, staged like xa
     __half* kn;    // [head_dim] the new token's key, rounded as the cache stores it
     __half* vn;    // [head_dim]
     float* part;   // [warps][head_dim]
     float* red;    // [64]
-    float* outv;   // results of a stage before they are published: max(2*s1_max, hpc_max, dpc_max * kparts) floats
+    float* partial;  // [2][kMegaChunkRows] partial row sums of a chunk (alternating halves)
     unsigned long long* key;   // [32] arg-max keys
     struct MegaShare* share;  // this CTA's work shares, computed once
     int* abort;    // [1] a wait gave up: no more waiting in this CTA
     int* stop;     // [1] the loop ended early (EOS): the producer stops issuing
 };
-
-__host__ __device__ inline int mega_outv_floats(const MegaPlan& p) {
-    int n = 2 * p.s1_max;
-    if (p.hpc_max > n) n = p.hpc_max;
-    if (p.dpc_max * kMegaConsumerWarps > n) n = p.dpc_max * kMegaConsumerWarps;
-    return (n + 3) & ~3;
-}
-__host__ __device__ inline int mega_xs_floats(const ModelDims& m) { return xs_floats<8>(m.d_model > m.hidden ? m.d_model : m.hidden); }
 
 // The areas sit at offsets the host computed once (mega_layout): an address is the base plus a kernel-argument
 // constant, which costs no register to keep.
@@ -248,7 +249,7 @@ __device__ __forceinline__ MegaShared mega_carve(uint8_t* base, const MegaArgs& 
     s.empty = s.full + p.n_slots;
     s.prev = reinterpret_cast<unsigned long long*>(base + p.off_prev);
     s.key = reinterpret_cast<unsigned long long*>(base + p.off_key);
-    s.xs = reinterpret_cast<float*>(base + p.off_xs);
+    s.xa = base + p.off_xs;
     s.xraw = reinterpret_cast<float*>(base + p.off_xraw);
     s.xmid = reinterpret_cast<float*>(base + p.off_xmid);
     s.rope = reinterpret_cast<float2*>(base + p.off_rope);
@@ -258,7 +259,7 @@ __device__ __forceinline__ MegaShared mega_carve(uint8_t* base, const MegaArgs& 
     s.vn = reinterpret_cast<__half*>(base + p.off_vn);
     s.part = reinterpret_cast<float*>(base + p.off_part);
     s.red = reinterpret_cast<float*>(base + p.off_red);
-    s.outv = reinterpret_cast<float*>(base + p.off_outv);
+    s.partial = reinterpret_cast<float*>(base + p.off_outv);
     s.abort = reinterpret_cast<int*>(base + p.off_flags);
     s.stop = s.abort + 1;
     s.share = reinterpret_cast<MegaShare*>(base + p.off_share);
@@ -272,7 +273,7 @@ inline void mega_layout(const ModelDims& m, MegaPlan& p) {
     p.off_bar = take(16 * (size_t)p.n_slots);
     p.off_prev = take(8 * (size_t)m.d_model);
     p.off_key = take(8 * 32);
-    p.off_xs = take(sizeof(float) * (size_t)mega_xs_floats(m));
+    p.off_xs = take((size_t)xa_bytes(m.d_model > m.hidden ? m.d_model : m.hidden));
     p.off_xraw = take(sizeof(float) * (size_t)m.d_model);
     p.off_xmid = take(sizeof(float) * (size_t)m.d_model);
     p.off_rope = take(sizeof(float2) * (size_t)(m.head_dim / 2));
@@ -282,7 +283,7 @@ inline void mega_layout(const ModelDims& m, MegaPlan& p) {
     p.off_vn = take(sizeof(__half) * (size_t)m.head_dim);
     p.off_part = take(sizeof(float) * (size_t)kMegaConsumerWarps * m.head_dim);
     p.off_red = take(sizeof(float) * 64);
-    p.off_outv = take(sizeof(float) * (size_t)mega_outv_floats(p));
+    p.off_outv = take(sizeof(float) * 2 * kMegaChunkRows);
     p.off_flags = take(16);
     p.off_share = take(sizeof(MegaShare));
     p.smem_bytes = (int)((o + 127) & ~(size_t)127);
@@ -312,18 +313,27 @@ __device__ __forceinline__ void mega_wait(const MegaArgs& a, const MegaShared& s
     }
 }
 
-// Ring bookkeeping shared by the producer and the consumers: chunk c lives in slot c % n_slots.
-__device__ __forceinline__ const uint8_t* mega_acquire(const MegaArgs& a, const MegaShared& s, unsigned c) {
-    const unsigned slot = c % (unsigned)a.plan.n_slots;
+// Ring bookkeeping shared by the producer and the consumers: chunk c lives in slot c % n_slots and completes phase
+// (c / n_slots) & 1 of that slot's barriers.  Kept incrementally: a division by a run-time value on the critical path
+// of every chunk costs a lone thread a quarter of a microsecond.
+struct MegaCursor {
+    unsigned slot = 0, phase = 0;
+    __device__ __forceinline__ void next(unsigned n_slots) {
+        if (++slot == n_slots) { slot = 0; phase ^= 1u; }
+    }
+};
+
+__device__ __forceinline__ const uint8_t* mega_acquire(const MegaArgs& a, const MegaShared& s, const MegaCursor& c) {
     // one lane per warp polls the barrier (many threads polling one shared-memory word serialise); the warp barrier
     // that follows orders the other lanes' reads of the chunk after the observed completion
-    if ((threadIdx.x & 31) == 0) mega_wait(a, s, s.full + slot, (c / (unsigned)a.plan.n_slots) & 1u, 3);
+    if ((threadIdx.x & 31) == 0) mega_wait(a, s, s.full + c.slot, c.phase, 3);
     __syncwarp();
-    return s.slots + (size_t)slot * a.plan.slot_bytes;
+    return s.slots + (size_t)c.slot * a.plan.slot_bytes;
 }
-__device__ __forceinline__ void mega_release(const MegaArgs& a, const MegaShared& s, unsigned c) {
+__device__ __forceinline__ void mega_release(const MegaArgs& a, const MegaShared& s, MegaCursor& c) {
     __syncwarp();
-    if ((threadIdx.x & 31) == 0) mbar_arrive(s.empty + (c % (unsigned)a.plan.n_slots));
+    if ((threadIdx.x & 31) == 0) mbar_arrive(s.empty + c.slot);
+    c.next((unsigned)a.plan.n_slots);
 }
 
 // ------------------------------------------------------------------------------------------------ exchanges
@@ -431,93 +441,96 @@ __device__ __forceinline__ float mega_block_sum(float v, float* red) {
     return t;
 }
 
-// ------------------------------------------------------------------------------------------------ dot products
+// ------------------------------------------------------------------------------------------------ products
 
-// Products of one 16-byte vector of fp16 weights with 8 activations, split over two accumulators so that the
-// dependent FMA chain is 4 long instead of 8.
-__device__ __forceinline__ void mega_fma8(const uint4& w, const float4& xa, const float4& xb, float& even, float& odd) {
-    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-    const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w.z));
-    const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&w.w));
-    even = fmaf(f0.x, xa.x, even); odd = fmaf(f0.y, xa.y, odd);
-    even = fmaf(f1.x, xa.z, even); odd = fmaf(f1.y, xa.w, odd);
-    even = fmaf(f2.x, xb.x, even); odd = fmaf(f2.y, xb.y, odd);
-    even = fmaf(f3.x, xb.z, even); odd = fmaf(f3.y, xb.w, odd);
+// Where element k of a staged vector lives (in halves): block of 32 columns kb, column g of the B operand (0 = hi part,
+// 1 = lo part), piece t; the 16 bytes of a piece are the B registers of the two m16n8k16 steps of the block.
+__device__ __forceinline__ int xa_index(int k, int g) {
+    const int kb = k >> 5, kk = k & 31;
+    return (((kb * 2 + g) * 4 + ((kk & 7) >> 1)) << 3) + ((kk >> 3) << 1) + (kk & 1);
 }
 
-// Dot products of NR fp16 rows held in shared memory (row r at base + r * row_bytes) with the staged vector over the
-// 256-element slices [it_begin, it_end); the results are in every lane.  Two slices are in flight per pass: all of
-// their shared-memory loads are issued before the first multiply, and every row has four independent accumulators.
-template <int NR>
-__device__ __forceinline__ void mega_dot_rows(const uint8_t* base, int row_bytes, int K, int it_begin, int it_end, const float* xs, int lane,
-                                              float (&o)[NR]) {
-    const float4* xs4 = reinterpret_cast<const float4*>(xs);
-    float acc[NR][4];
-#pragma unroll
-    for (int r = 0; r < NR; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
-    for (int it = it_begin; it < it_end; it += 2) {
-        const int k0 = it * 256 + lane * 8, k1 = k0 + 256;
-        const bool in0 = k0 < K, in1 = it + 1 < it_end && k1 < K;
-        uint4 w0[NR], w1[NR];
-#pragma unroll
-        for (int r = 0; r < NR; r++) {
-            w0[r] = in0 ? lds128(base + (size_t)r * row_bytes + (size_t)k0 * 2) : make_uint4(0, 0, 0, 0);
-            w1[r] = in1 ? lds128(base + (size_t)r * row_bytes + (size_t)k1 * 2) : make_uint4(0, 0, 0, 0);
-        }
-        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float4 xa0 = in0 ? xs4[(it * 2) * 32 + lane] : z, xb0 = in0 ? xs4[(it * 2 + 1) * 32 + lane] : z;
-        const float4 xa1 = in1 ? xs4[(it * 2 + 2) * 32 + lane] : z, xb1 = in1 ? xs4[(it * 2 + 3) * 32 + lane] : z;
-#pragma unroll
-        for (int r = 0; r < NR; r++) {
-            mega_fma8(w0[r], xa0, xb0, acc[r][0], acc[r][1]);
-            mega_fma8(w1[r], xa1, xb1, acc[r][2], acc[r][3]);
+// Stores v as hi + lo (both fp16, hi saturating) at position k of a staged vector.
+__device__ __forceinline__ void xa_store(__half* xa, int k, float v) {
+    __half hi;
+    asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(*reinterpret_cast<unsigned short*>(&hi)) : "f"(v));
+    xa[xa_index(k, 0)] = hi;
+    xa[xa_index(k, 1)] = __float2half_rn(v - __half2float(hi));
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Partial products of the 16-row tile `tile` of a chunk of R rows with the staged vector over the column blocks
+// [kb0, kb1).  The weights are the A operand (rows g and g + 8 of the tile: one 16-byte shared-memory load each per two
+// m16n8k16 steps), the staged vector the B operand (column 0 = hi part, column 1 = lo part, held by lanes 0..7).  The
+// lanes with lane % 4 == 0 return the sums of rows tile*16 + lane/4 (.x) and + 8 (.y); rows past R are meaningless.
+__device__ __forceinline__ float2 mega_tile_dot(const uint8_t* chunk, int R, int tile, int kb0, int kb1, const uint8_t* xa, int lane) {
+    // four independent accumulator sets: a dependent m16n8k16 costs ~40-60 cycles, and a warp has only a few blocks
+    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f}, c3[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint8_t* wp = chunk + ((size_t)(tile * 16 + (lane >> 2)) * 64 + (lane & 3) * 16);
+    const size_t kstride = (size_t)R * 64;
+    const uint8_t* xp = xa + lane * 16;
+    // plain loads: the compiler may move them ahead of the previous block's products, never across a barrier
+    auto block = [&](int kb, float (&ce)[4], float (&co)[4]) {
+        const uint4 w0 = *reinterpret_cast<const uint4*>(wp + kb * kstride);
+        const uint4 w8 = *reinterpret_cast<const uint4*>(wp + kb * kstride + 8 * 64);
+        uint4 xv = make_uint4(0, 0, 0, 0);
+        if (lane < 8) xv = *reinterpret_cast<const uint4*>(xp + kb * 128);
+        mma_16816(ce, w0.x, w8.x, w0.y, w8.y, xv.x, xv.y);
+        mma_16816(co, w0.z, w8.z, w0.w, w8.w, xv.z, xv.w);
+    };
+    int kb = kb0;
+#pragma unroll 2
+    for (; kb + 1 < kb1; kb += 2) {
+        block(kb, c0, c1);
+        block(kb + 1, c2, c3);
+    }
+    if (kb < kb1) block(kb, c0, c1);
+    // column 0 of the product is w . x_hi, column 1 is w . x_lo
+    return make_float2(((c0[0] + c1[0]) + (c2[0] + c3[0])) + ((c0[1] + c1[1]) + (c2[1] + c3[1])),
+                       ((c0[2] + c1[2]) + (c2[2] + c3[2])) + ((c0[3] + c1[3]) + (c2[3] + c3[3])));
+}
+
+// All products of one chunk (R <= kMegaChunkRows rows over n_kb column blocks), spread over the consumer warps as
+// (16-row tile, column range) units; the number of column ranges is a power of two so that a warp finds its unit with
+// shifts (per chunk every scalar instruction of this set-up is on the critical path of the token).  Unit u = tile <<
+// lg | range stores its sixteen partial sums at partial[u * 16 ...]; returns lg.  The caller synchronises before reading.
+__device__ __forceinline__ int mega_chunk_dots(const uint8_t* chunk, int R, int n_kb, const uint8_t* xa, float* partial, int warp, int lane) {
+    const int n_tiles = (R + 15) >> 4;
+    // lg = log2(column ranges): the largest value with tiles << lg <= warps and 1 << lg <= n_kb
+    const int lg_t = n_tiles > 1 ? 32 - __clz(n_tiles - 1) : 0;  // ceil(log2(tiles))
+    const int lg = max(0, min(4 - lg_t, 31 - __clz(n_kb)));
+    const int per = (n_kb + (1 << lg) - 1) >> lg;
+    for (int u = warp; u < (n_tiles << lg); u += kMegaConsumerWarps) {
+        const int tile = u >> lg, part = u & ((1 << lg) - 1);
+        const float2 y = mega_tile_dot(chunk, R, tile, part * per, min(n_kb, (part + 1) * per), xa, lane);
+        if ((lane & 3) == 0) {
+            float* dst = partial + u * 16 + (lane >> 2);
+            dst[0] = y.x;
+            dst[8] = y.y;
         }
     }
-    float t[NR];
+    return lg;
+}
+// Row r's sum over the column ranges: all loads are issued before the first addition.
+__device__ __forceinline__ float mega_take_sum(const float* partial, int lg, int r) {
+    const float* src = partial + ((r >> 4) << lg) * 16 + (r & 15);
+    float v[16];
 #pragma unroll
-    for (int r = 0; r < NR; r++) t[r] = (acc[r][0] + acc[r][1]) + (acc[r][2] + acc[r][3]);
+    for (int part = 0; part < 16; part++) v[part] = part < (1 << lg) ? src[part * 16] : 0.f;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
+    for (int o = 8; o > 0; o >>= 1) {
 #pragma unroll
-        for (int r = 0; r < NR; r++) t[r] += __shfl_xor_sync(0xffffffffu, t[r], off);
+        for (int part = 0; part < o; part++) v[part] += v[part + o];
     }
-#pragma unroll
-    for (int r = 0; r < NR; r++) o[r] = t[r];
+    return v[0];
 }
 
 // ------------------------------------------------------------------------------------------------ consumer stages
-
-// S1: q/k/v rows of this CTA (pairs that RoPE rotates together) from one ring chunk; results go to s.outv, k and v
-// also to the KV cache.  `inv` is the RMSNorm scale of the staged vector (the gain is already in s.xs).
-__device__ __forceinline__ void mega_s1(const MegaArgs& a, const MegaShared& s, const MegaShare& w, int layer, int pos, float inv,
-                                        const uint8_t* chunk, int i0, int n_items) {
-    const ModelDims& m = a.m;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int iters = (m.d_model + 255) / 256;
-    for (int i = warp; i < n_items; i += kMegaConsumerWarps) {  // i: pair inside the chunk, i0 + i: pair of this CTA
-        float v[2];
-        mega_dot_rows<2>(chunk + (size_t)(2 * i) * a.plan.row_bytes, a.plan.row_bytes, m.d_model, 0, iters, s.xs, lane, v);
-        if (lane == 0) {
-            int kind, row0, row1, idx;
-            mega_s1_rows(m, a.plan, w.kvh, w.s1_begin + i0 + i, kind, row0, row1, idx);
-            float v0 = v[0] * inv, v1 = v[1] * inv;
-            if (kind < 2) {
-                const float2 cs = s.rope[idx];
-                const float r0 = v0 * cs.x - v1 * cs.y, r1 = v0 * cs.y + v1 * cs.x;
-                v0 = r0; v1 = r1;
-            }
-            s.outv[2 * (i0 + i)] = v0;
-            s.outv[2 * (i0 + i) + 1] = v1;
-            if (kind > 0) {
-                __half* base = kind == 1 ? a.kv.k : a.kv.v;
-                const size_t off = a.kv.offset(m, layer, 0, w.kvh, pos);
-                base[off + (row0 - w.kvh * m.head_dim)] = __float2half_rn(v0);
-                base[off + (row1 - w.kvh * m.head_dim)] = __float2half_rn(v1);
-            }
-        }
-    }
-}
 
 // S2: attention of one head over the cached positions [0, pos) plus the new token (whose key and value are in
 // shared memory), then this CTA's block of the output projection.
@@ -652,59 +665,9 @@ __device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShar
             num = fmaf(s.part[x * HD + tid], f, num);
             den = fmaf(s.red[kMegaConsumerWarps + x], f, den);
         }
-        s.ctx[tid] = den > 0.f ? num / den : 0.f;
+        xa_store(reinterpret_cast<__half*>(s.ctx), tid, den > 0.f ? num / den : 0.f);  // the A operand of the Wo products
     }
     consumer_sync();
-}
-
-// Partial output projection: rows [blk*rpb, ...) of Wo restricted to this head's columns; every row's partial sum is
-// one contribution to the counted sum of that row (head 0 also carries the residual).
-template <int HD>
-__device__ __forceinline__ void mega_wo_partial(const MegaArgs& a, const MegaShared& s, const MegaShare& w, unsigned& c) {
-    const ModelDims& m = a.m;
-    const MegaPlan& p = a.plan;
-    const int tid = threadIdx.x;
-    constexpr int ipt = HD <= 64 ? 8 : 16;  // inputs per thread
-    constexpr int tpr = HD / ipt;           // threads per row
-    const int psub = tid % tpr;
-    constexpr int rows_per_pass = kMegaConsumers / tpr;
-    for (int r0 = 0; r0 < p.rpb; r0 += p.s2_rpc) {  // the block's rows arrive in chunks of s2_rpc
-        const uint8_t* chunk = mega_acquire(a, s, c);
-        const int nr = min(p.s2_rpc, p.rpb - r0);
-        for (int rb = 0; rb < nr; rb += rows_per_pass) {  // uniform trip count: the shuffles below need every lane
-            const int r = rb + tid / tpr;
-            const int orow = w.blk * p.rpb + r0 + r;
-            const bool valid = r < nr;
-            float v = 0.f;
-            if (valid) {
-                const uint8_t* wrow = chunk + (size_t)r * HD * 2 + psub * ipt * 2;
-#pragma unroll
-                for (int q = 0; q < ipt / 8; q++) fma_vec16<WT_F16>(lds128(wrow + 16 * q), nullptr, 0, s.ctx + psub * ipt + 8 * q, 0.f, v);
-            }
-#pragma unroll
-            for (int o = tpr / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (valid && psub == 0 && orow < m.d_model) {
-                if (w.head == 0) v += s.xraw[orow];  // residual, added once
-                red_add_u64(a.mid_sums + orow, counted(v));
-            }
-        }
-        mega_release(a, s, c);
-        c++;
-    }
-}
-
-// S3: gate/up rows of this CTA's hidden units, SiLU*up.
-__device__ __forceinline__ void mega_s3_up(const MegaArgs& a, const MegaShared& s, float inv, const uint8_t* chunk, int j0, int n_items) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int iters = (a.m.d_model + 255) / 256;
-    for (int j = warp; j < n_items; j += kMegaConsumerWarps) {
-        float v[2];
-        mega_dot_rows<2>(chunk + (size_t)(2 * j) * a.plan.row_bytes, a.plan.row_bytes, a.m.d_model, 0, iters, s.xs, lane, v);
-        if (lane == 0) {
-            const float g = v[0] * inv;
-            s.outv[j0 + j] = g / (1.0f + __expf(-g)) * (v[1] * inv);  // silu(g) = g * sigmoid(g) = 0.5 g (1 + tanh(g / 2))
-        }
-    }
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel
@@ -733,26 +696,27 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
     if (warp == kMegaConsumerWarps) {
         // ---------------- producer: one thread streams this CTA's chunks in consumption order ----------------
         if (lane == 0) {
-            unsigned c = 0;
+            MegaCursor c;
+            unsigned issued = 0;
 #ifdef MEGA_FINE_TRACE
             int p_step = 0, p_n = 0;
 #endif
             const uint64_t policy = l2_evict_first_policy();
             auto issue = [&](long long off, int bytes) {
-                const unsigned slot = c % (unsigned)p.n_slots;
                 if (mega_aborting(s) || *reinterpret_cast<volatile int*>(s.stop)) return;  // nothing more is copied
 #ifdef MEGA_FINE_TRACE
                 const bool tr = a.trace && (int)blockIdx.x == a.trace_cta && p_step == a.n_steps - 1 && p_n < 56;
                 if (tr) a.trace[400 + 2 * p_n] = clock64();
 #endif
-                if (c >= (unsigned)p.n_slots) mega_wait(a, s, s.empty + slot, ((c / (unsigned)p.n_slots) - 1u) & 1u, 4);
+                if (issued >= (unsigned)p.n_slots) mega_wait(a, s, s.empty + c.slot, c.phase ^ 1u, 4);  // the previous use of the slot was released
                 if (mega_aborting(s) || *reinterpret_cast<volatile int*>(s.stop)) return;
-                mbar_expect_tx(s.full + slot, (unsigned)bytes);
-                bulk_copy_g2s(s.slots + (size_t)slot * p.slot_bytes, blob + off, (unsigned)bytes, s.full + slot, policy);
+                mbar_expect_tx(s.full + c.slot, (unsigned)bytes);
+                bulk_copy_g2s(s.slots + (size_t)c.slot * p.slot_bytes, blob + off, (unsigned)bytes, s.full + c.slot, policy);
 #ifdef MEGA_FINE_TRACE
                 if (tr) { a.trace[400 + 2 * p_n + 1] = clock64(); p_n++; }
 #endif
-                c++;
+                c.next((unsigned)p.n_slots);
+                issued++;
             };
             // a stage's slice: whole items, `per_chunk` at a time
             auto issue_stage = [&](long long off, int items, int per_chunk, int item_bytes) {
@@ -767,7 +731,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                         long long off = (long long)l * p.layer_bytes;
                         if (w.in_group) issue_stage(off, w.s1_n, p.s1_ipc, 2 * p.row_bytes);
                         off += p.s1_bytes;
-                        if (w.in_group) issue_stage(off, p.rpb, p.s2_rpc, m.head_dim * 2);
+                        if (w.in_group) issue_stage(off, p.rpb, p.s2_rpc, HD * 2);
                         off += p.s2_bytes;
                         issue_stage(off, w.h_n, p.s3a_ipc, 2 * p.row_bytes); off += p.s3a_bytes;
                         issue_stage(off, w.d_n, p.s3b_rpc, p.down_row_bytes);
@@ -775,11 +739,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 }
                 issue_stage(head_off, w.v_n, p.head_rpc, p.row_bytes);
             }
-            // every copy that was issued must have landed before the CTA may exit
-            const unsigned first = c > (unsigned)p.n_slots ? c - (unsigned)p.n_slots : 0u;
-            for (unsigned k = first; k < c; k++) {
+            // every copy that was issued must have landed before the CTA may exit: walk the last n_slots chunks backwards
+            MegaCursor k = c;
+            const unsigned back = issued < (unsigned)p.n_slots ? issued : (unsigned)p.n_slots;
+            for (unsigned i = 0; i < back; i++) {
+                if (k.slot == 0) { k.slot = (unsigned)p.n_slots - 1; k.phase ^= 1u; } else k.slot--;
                 unsigned spins = 0;
-                while (!mbar_try_wait(s.full + (k % (unsigned)p.n_slots), (k / (unsigned)p.n_slots) & 1u) && ++spins < kMegaSpinLimit) {}
+                while (!mbar_try_wait(s.full + k.slot, k.phase) && ++spins < kMegaSpinLimit) {}
             }
         }
         return;
@@ -802,20 +768,35 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
     auto stamp = [&](int step) {
         if (a.trace && (int)blockIdx.x == a.trace_cta && tid == 0 && step == a.n_steps - 1) a.trace[n_stamp++] = clock64();
     };
-    unsigned c = 0;      // chunk counter, advances in lock step with the producer's
+    MegaCursor c;        // ring position, advances in lock step with the producer's
     int pos = a.pos0;    // visible tokens
     uint32_t tok = 0;
     int emitted = 0;
+    int par = 0;         // which half of s.partial the next chunk's sums go to
     constexpr int half = HD / 2;
     const int d = m.d_model;
     const float* fin_gain = a.norms + (size_t)(2 * L) * d;
     unsigned long long* my_qkv = a.qkv_words + (size_t)w.kvh * 2 * p.group_items;
+    __half* xa_h = reinterpret_cast<__half*>(s.xa);
 
-    // Stages one value of the residual stream: raw copy, gained copy in the dot-product order, sum of squares.
+    // Stages one value of the residual stream: raw copy, gained copy as the products' A operand, sum of squares.
     auto stage_x = [&](float* raw, int k, float v, float g, float& ss) {
         raw[k] = v;
-        s.xs[xs_index<8>(k)] = v * g;
+        xa_store(xa_h, k, v * g);
         ss = fmaf(v, v, ss);
+    };
+    // One chunk of a stage: acquire, all products, release, CTA barrier; returns where the sums are.
+    int lg_parts = 0;    // log2 of the column ranges of the chunk whose sums are being read
+    auto chunk_products = [&](int rows, int n_kb, const uint8_t* xa) {
+        const uint8_t* ch = mega_acquire(a, s, c);
+        FINE();
+        float* partial = s.partial + par * kMegaChunkRows;
+        par ^= 1;
+        lg_parts = mega_chunk_dots(ch, rows, n_kb, xa, partial, warp, lane);
+        mega_release(a, s, c);
+        consumer_sync();
+        FINE();
+        return partial;
     };
 
     for (int step = 0; step < a.n_steps; step++) {
@@ -844,49 +825,75 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     inv = 1.0f / sqrtf(ss / (float)d + m.eps);
                     FINE();
                     stamp(step);
+                    // q/k/v row pairs of this CTA, RoPE, words for the CTAs that share the KV head, KV-cache append.
+                    // qkv_words is re-written one layer later, after x_words of this layer is complete, which needs every
+                    // CTA's W2 rows, hence the whole activation vector, hence every group CTA past its S2 of this layer.
                     for (int i0 = 0; i0 < w.s1_n; i0 += p.s1_ipc) {
-                        const uint8_t* ch = mega_acquire(a, s, c);
-                        FINE();
-                        mega_s1(a, s, w, l, pos, inv, ch, i0, min(p.s1_ipc, w.s1_n - i0));
-                        FINE();
-                        mega_release(a, s, c); c++;
-                    }
-                    consumer_sync();
-                    FINE();
-                    // publish this CTA's pairs: one warp writes consecutive words.  qkv_words is re-written one layer
-                    // later, after x_words of this layer is complete, which needs every CTA's W2 rows, hence the whole
-                    // activation vector, hence every group CTA past its S2 of this layer.
-                    for (int t = tid; t < 2 * w.s1_n; t += kMegaConsumers) st_word(my_qkv + 2 * w.s1_begin + t, tagged(s.outv[t], seq));
-                    stamp(step);
-                    {
-                        FINE();
-                        mega_attention<HD>(a, s, w, l, pos, [&]() {
-                            // q of this CTA's head, k and v of the KV head: pairs in the order S1 published them
-                            FINE();
-                            if (tid < 3 * half) {
-                                const int section = tid / half, idx = tid - section * half;
-                                const int item = (section == 0 ? w.hq * half : section == 1 ? p.qpk * half : (p.qpk + 1) * half) + idx;
-                                ulonglong2 v = make_ulonglong2(0, 0);
-                                unsigned spins = 0;
-                                if (!mega_aborting(s)) {
-                                    while (true) {
-                                        v = ld_words2(my_qkv + 2 * item);
-                                        if ((unsigned)(v.x >> 32) == seq && (unsigned)(v.y >> 32) == seq) break;
-                                        if (mega_spin_out(a, s, spins, 6)) break;
-                                    }
-                                }
-                                const float v0 = __uint_as_float((unsigned)v.x), v1 = __uint_as_float((unsigned)v.y);
-                                if (section == 0) { s.qs[idx] = v0; s.qs[idx + half] = v1; }
-                                else if (section == 1) { s.kn[idx] = __float2half_rn(v0); s.kn[idx + half] = __float2half_rn(v1); }
-                                else { s.vn[2 * idx] = __float2half_rn(v0); s.vn[2 * idx + 1] = __float2half_rn(v1); }
+                        const int n_items = min(p.s1_ipc, w.s1_n - i0);
+                        float* sums = chunk_products(2 * n_items, d >> 5, s.xa);
+                        for (int i = tid; i < n_items; i += kMegaConsumers) {
+                            int kind, row0, row1, idx;
+                            mega_s1_rows(m, p, w.kvh, w.s1_begin + i0 + i, kind, row0, row1, idx);
+                            float v0 = mega_take_sum(sums, lg_parts, 2 * i) * inv;
+                            float v1 = mega_take_sum(sums, lg_parts, 2 * i + 1) * inv;
+                            if (kind < 2) {
+                                const float2 cs = s.rope[idx];
+                                const float r0 = v0 * cs.x - v1 * cs.y, r1 = v0 * cs.y + v1 * cs.x;
+                                v0 = r0; v1 = r1;
                             }
-                            FINE();
-                            consumer_sync();
-                            FINE();
-                            stamp(step);
-                        });
+                            unsigned long long* dst = my_qkv + 2 * (w.s1_begin + i0 + i);
+                            st_word(dst, tagged(v0, seq));
+                            st_word(dst + 1, tagged(v1, seq));
+                            if (kind > 0) {
+                                __half* base = kind == 1 ? a.kv.k : a.kv.v;
+                                const size_t off = a.kv.offset(m, l, 0, w.kvh, pos);
+                                base[off + (row0 - w.kvh * HD)] = __float2half_rn(v0);
+                                base[off + (row1 - w.kvh * HD)] = __float2half_rn(v1);
+                            }
+                        }
+                    }
+                    stamp(step);
+                    // ---- S2: attention of this CTA's head (the cached K/V rows are requested before the query is awaited)
+                    FINE();
+                    mega_attention<HD>(a, s, w, l, pos, [&]() {
+                        // q of this CTA's head, k and v of the KV head: pairs in the order S1 published them
+                        FINE();
+                        if (tid < 3 * half) {
+                            const int section = tid / half, idx = tid - section * half;
+                            const int item = (section == 0 ? w.hq * half : section == 1 ? p.qpk * half : (p.qpk + 1) * half) + idx;
+                            ulonglong2 v = make_ulonglong2(0, 0);
+                            unsigned spins = 0;
+                            if (!mega_aborting(s)) {
+                                while (true) {
+                                    v = ld_words2(my_qkv + 2 * item);
+                                    if ((unsigned)(v.x >> 32) == seq && (unsigned)(v.y >> 32) == seq) break;
+                                    if (mega_spin_out(a, s, spins, 6)) break;
+                                }
+                            }
+                            const float v0 = __uint_as_float((unsigned)v.x), v1 = __uint_as_float((unsigned)v.y);
+                            if (section == 0) { s.qs[idx] = v0; s.qs[idx + half] = v1; }
+                            else if (section == 1) { s.kn[idx] = __float2half_rn(v0); s.kn[idx + half] = __float2half_rn(v1); }
+                            else { s.vn[2 * idx] = __float2half_rn(v0); s.vn[2 * idx + 1] = __float2half_rn(v1); }
+                        }
+                        FINE();
+                        consumer_sync();
+                        FINE();
                         stamp(step);
-                        mega_wo_partial<HD>(a, s, w, c);
+                    });
+                    stamp(step);
+                    // ---- rows [blk*rpb, ...) of Wo restricted to this head's columns: every row's partial sum is one
+                    // contribution to the counted sum of that row (head 0 also carries the residual)
+                    for (int r0 = 0; r0 < p.rpb; r0 += p.s2_rpc) {
+                        const int nr = min(p.s2_rpc, p.rpb - r0);
+                        float* sums = chunk_products(nr, HD >> 5, reinterpret_cast<const uint8_t*>(s.ctx));
+                        for (int r = tid; r < nr; r += kMegaConsumers) {
+                            const int orow = w.blk * p.rpb + r0 + r;
+                            float v = mega_take_sum(sums, lg_parts, r);
+                            if (orow < d) {
+                                if (w.head == 0) v += s.xraw[orow];
+                                red_add_u64(a.mid_sums + orow, counted(v));
+                            }
+                        }
                     }
                     stamp(step);
                 } else {
@@ -904,52 +911,32 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     inv = 1.0f / sqrtf(ss / (float)d + m.eps);
                 }
                 stamp(step);
+                // (gate, up) row pairs of this CTA's hidden units, SiLU(gate) * up.  act_words is re-written one layer later,
+                // after mid_sums of that layer is complete, which needs every group CTA past x_words of this layer, i.e.
+                // every CTA past its W2 rows and so past this activation vector.
                 for (int j0 = 0; j0 < w.h_n; j0 += p.s3a_ipc) {
-                    FINE();
-                    const uint8_t* ch = mega_acquire(a, s, c);
-                    FINE();
-                    mega_s3_up(a, s, inv, ch, j0, min(p.s3a_ipc, w.h_n - j0));
-                    FINE();
-                    mega_release(a, s, c); c++;
-                }
-                consumer_sync();
-                FINE();
-                // act_words is re-written one layer later, after mid_sums of that layer is complete, which needs every group
-                // CTA past x_words of this layer, i.e. every CTA past its W2 rows and so past this activation vector.
-                for (int t = tid; t < w.h_n; t += kMegaConsumers) st_word(a.act_words + w.h_begin + t, tagged(s.outv[t], seq));
-                stamp(step);
-                // ---- the whole activation vector, then this CTA's rows of W2 (+ residual)
-                FINE();
-                mega_read_words(a, s, a.act_words, m.hidden, seq, 8, nullptr, [&](int k, float v, float) { s.xs[xs_index<8>(k)] = v; });
-                FINE();
-                consumer_sync();
-                FINE();
-                stamp(step);
-                {
-                    const int iters = (m.hidden + 255) / 256;
-                    for (int r0 = 0; r0 < w.d_n; r0 += p.s3b_rpc) {
-                        const uint8_t* ch = mega_acquire(a, s, c);
-                        FINE();
-                        const int nr = min(p.s3b_rpc, w.d_n - r0);
-                        // each row is cut into `kparts` ranges of slices so that all warps work on few rows
-                        const int kparts = max(1, min(kMegaConsumerWarps / nr, iters));
-                        const int per = (iters + kparts - 1) / kparts;
-                        for (int u = warp; u < nr * kparts; u += kMegaConsumerWarps) {
-                            const int r = u % nr, part = u / nr;
-                            float v[1];
-                            mega_dot_rows<1>(ch + (size_t)r * p.down_row_bytes, p.down_row_bytes, m.hidden, part * per, min(iters, (part + 1) * per), s.xs, lane, v);
-                            if (lane == 0) s.outv[(r0 + r) * kMegaConsumerWarps + part] = v[0];
-                        }
-                        FINE();
-                        mega_release(a, s, c); c++;
-                        consumer_sync();
-                        FINE();
-                        for (int t = tid; t < nr; t += kMegaConsumers) {
-                            float v = s.xmid[w.d_begin + r0 + t];  // residual
-                            for (int part = 0; part < kparts; part++) v += s.outv[(r0 + t) * kMegaConsumerWarps + part];
-                            st_word(a.x_words + w.d_begin + r0 + t, tagged(v, seq));
-                        }
+                    const int n_items = min(p.s3a_ipc, w.h_n - j0);
+                    float* sums = chunk_products(2 * n_items, d >> 5, s.xa);
+                    for (int j = tid; j < n_items; j += kMegaConsumers) {
+                        const float g = mega_take_sum(sums, lg_parts, 2 * j) * inv;
+                        const float u = mega_take_sum(sums, lg_parts, 2 * j + 1) * inv;
+                        // silu(g) = g * sigmoid(g) = 0.5 g (1 + tanh(g / 2))
+                        st_word(a.act_words + w.h_begin + j0 + j, tagged(g / (1.0f + __expf(-g)) * u, seq));
                     }
+                }
+                stamp(step);
+                // ---- the whole activation vector, then this CTA's rows of W2 (+ residual) = the next layer's x
+                FINE();
+                mega_read_words(a, s, a.act_words, m.hidden, seq, 8, nullptr, [&](int k, float v, float) { xa_store(xa_h, k, v); });
+                FINE();
+                consumer_sync();
+                FINE();
+                stamp(step);
+                for (int r0 = 0; r0 < w.d_n; r0 += p.s3b_rpc) {
+                    const int nr = min(p.s3b_rpc, w.d_n - r0);
+                    float* sums = chunk_products(nr, m.hidden >> 5, s.xa);
+                    for (int r = tid; r < nr; r += kMegaConsumers)
+                        st_word(a.x_words + w.d_begin + r0 + r, tagged(mega_take_sum(sums, lg_parts, r) + s.xmid[w.d_begin + r0 + r], seq));
                 }
                 stamp(step);
             }
@@ -972,27 +959,23 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         stamp(step);
         float best_v = -INFINITY;
         int best_i = 0x7fffffff;
-        {
-            const int iters = (d + 255) / 256;
-            for (int r0 = 0; r0 < w.v_n; r0 += p.head_rpc) {
-                FINE();
-                const uint8_t* ch = mega_acquire(a, s, c);
-                FINE();
-                const int nrows = min(p.head_rpc, w.v_n - r0);
-                // two rows per warp per pass; a row past the chunk's end repeats the last one
-                for (int r = 2 * warp; r < nrows; r += 2 * kMegaConsumerWarps) {
-                    float v[2];
-                    const int second = r + 1 < nrows ? 1 : 0;
-                    mega_dot_rows<2>(ch + (size_t)r * p.row_bytes, second * p.row_bytes, d, 0, iters, s.xs, lane, v);
-                    const int g = w.v_begin + r0 + r;
-                    if (v[0] > best_v) { best_v = v[0]; best_i = g; }
-                    if (second && v[1] > best_v) { best_v = v[1]; best_i = g + 1; }
-                }
-                mega_release(a, s, c); c++;
+        for (int r0 = 0; r0 < w.v_n; r0 += p.head_rpc) {
+            const int nrows = min(p.head_rpc, w.v_n - r0);
+            FINE();
+            float* sums = chunk_products(nrows, d >> 5, s.xa);
+            // thread r keeps the best of rows r0 + r over the chunks (ascending rows: '>' keeps the first maximum)
+            if (tid < nrows) {
+                const float v = mega_take_sum(sums, lg_parts, tid);
+                if (v > best_v) { best_v = v; best_i = w.v_begin + r0 + tid; }
             }
         }
         // CTA-wide best (larger value first, then smaller index), published as two tagged words
-        if (lane == 0) s.key[warp] = best_i != 0x7fffffff ? pack_best(best_v, best_i) : 0ull;
+        {
+            unsigned long long k = best_i != 0x7fffffff ? pack_best(best_v, best_i) : 0ull;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) k = max(k, __shfl_xor_sync(0xffffffffu, k, off));
+            if (lane == 0) s.key[warp] = k;
+        }
         consumer_sync();
         if (tid == 0) {
             unsigned long long k = 0ull;
@@ -1076,16 +1059,28 @@ struct PackSources {
     const __half* lm_head;
 };
 
-__device__ __forceinline__ void pack_copy(uint8_t* dst, const void* src, int bytes) {
-    // bytes is a multiple of 16; src == nullptr writes zeros
-    for (int o = threadIdx.x * 16; o < bytes; o += blockDim.x * 16) {
+// Writes `nr` rows of K halves each in the order the products read them: for every block of 32 columns, for every row,
+// 64 bytes = four 16-byte pieces; piece t holds columns {2t, 2t+1, 2t+8, 2t+9, 16+2t, 17+2t, 24+2t, 25+2t} of the block
+// (A registers of two m16n8k16 steps for the lanes with that t).  row_of(r) returns the row's first element or
+// null for a row of zeros.
+template <class RowOf>
+__device__ __forceinline__ void pack_tiled(uint8_t* dst, int nr, int K, RowOf row_of) {
+    const int n_kb = K >> 5;
+    for (int i = threadIdx.x; i < n_kb * nr * 4; i += blockDim.x) {
+        const int t = i & 3, q = i >> 2;
+        const int kb = q / nr, r = q - kb * nr;
+        const __half* src = row_of(r);
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (src) v = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(src) + o);
-        *reinterpret_cast<uint4*>(dst + o) = v;
+        if (src) {
+            const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src + (size_t)kb * 32);
+            v = make_uint4(s32[t], s32[t + 4], s32[t + 8], s32[t + 12]);
+        }
+        *reinterpret_cast<uint4*>(dst + ((size_t)q * 64 + t * 16)) = v;
     }
 }
 
-// One CTA builds the blob of one CTA of the decode kernel.
+// One CTA builds the blob of one CTA of the decode kernel: per layer [S1 | S2 | S3 gate/up | S3 W2], then the head;
+// every stage is a sequence of chunks (the units the ring carries), each in the tiled order above.
 __global__ void k_build_pack(PackSources src, MegaPlan p, ModelDims m, uint8_t* pack) {
     const int cta = blockIdx.x;
     uint8_t* blob = pack + (size_t)cta * p.cta_bytes;
@@ -1094,39 +1089,46 @@ __global__ void k_build_pack(PackSources src, MegaPlan p, ModelDims m, uint8_t* 
     for (int l = 0; l < m.n_layer; l++) {
         uint8_t* base = blob + (size_t)l * p.layer_bytes;
         // S1: pairs of rows in RoPE order
-        for (int i = 0; i < p.s1_max; i++) {
-            const __half *r0 = nullptr, *r1 = nullptr;
-            if (w.in_group && i < w.s1_n) {
-                int kind, row0, row1, idx;
-                mega_s1_rows(m, p, w.kvh, w.s1_begin + i, kind, row0, row1, idx);
-                const __half* W = kind == 0 ? src.wq[l] : kind == 1 ? src.wk[l] : src.wv[l];
-                r0 = W + (size_t)row0 * d; r1 = W + (size_t)row1 * d;
+        if (w.in_group)
+            for (int i0 = 0; i0 < w.s1_n; i0 += p.s1_ipc) {
+                const int n = min(p.s1_ipc, w.s1_n - i0);
+                pack_tiled(base + (size_t)i0 * 2 * p.row_bytes, 2 * n, d, [&](int r) {
+                    int kind, row0, row1, idx;
+                    mega_s1_rows(m, p, w.kvh, w.s1_begin + i0 + (r >> 1), kind, row0, row1, idx);
+                    const __half* W = kind == 0 ? src.wq[l] : kind == 1 ? src.wk[l] : src.wv[l];
+                    return W + (size_t)((r & 1) ? row1 : row0) * d;
+                });
             }
-            pack_copy(base + (size_t)(2 * i) * p.row_bytes, r0, p.row_bytes);
-            pack_copy(base + (size_t)(2 * i + 1) * p.row_bytes, r1, p.row_bytes);
-        }
         base += p.s1_bytes;
         // S2: rows [blk*rpb, +rpb) of Wo, columns of one head
-        for (int r = 0; r < p.rpb; r++) {
-            const int orow = w.blk * p.rpb + r;
-            const __half* sp = (w.in_group && orow < d) ? src.wo[l] + (size_t)orow * m.q_dim + (size_t)w.head * hd : nullptr;
-            pack_copy(base + (size_t)r * hd * 2, sp, hd * 2);
-        }
+        if (w.in_group)
+            for (int r0 = 0; r0 < p.rpb; r0 += p.s2_rpc) {
+                const int n = min(p.s2_rpc, p.rpb - r0);
+                pack_tiled(base + (size_t)r0 * hd * 2, n, hd, [&](int r) {
+                    const int orow = w.blk * p.rpb + r0 + r;
+                    return orow < d ? src.wo[l] + (size_t)orow * m.q_dim + (size_t)w.head * hd : (const __half*)nullptr;
+                });
+            }
         base += p.s2_bytes;
-        // S3a: (gate_j, up_j) row pairs
-        for (int j = 0; j < p.hpc_max; j++) {
-            const int hrow = w.h_begin + j;
-            pack_copy(base + (size_t)(2 * j) * p.row_bytes, j < w.h_n ? src.w1[l] + (size_t)hrow * d : nullptr, p.row_bytes);
-            pack_copy(base + (size_t)(2 * j + 1) * p.row_bytes, j < w.h_n ? src.w3[l] + (size_t)hrow * d : nullptr, p.row_bytes);
+        // S3: (gate_j, up_j) row pairs
+        for (int j0 = 0; j0 < w.h_n; j0 += p.s3a_ipc) {
+            const int n = min(p.s3a_ipc, w.h_n - j0);
+            pack_tiled(base + (size_t)j0 * 2 * p.row_bytes, 2 * n, d, [&](int r) {
+                return ((r & 1) ? src.w3[l] : src.w1[l]) + (size_t)(w.h_begin + j0 + (r >> 1)) * d;
+            });
         }
         base += p.s3a_bytes;
-        // S3b: this CTA's rows of W2
-        for (int r = 0; r < p.dpc_max; r++)
-            pack_copy(base + (size_t)r * p.down_row_bytes, r < w.d_n ? src.w2[l] + (size_t)(w.d_begin + r) * m.hidden : nullptr, p.down_row_bytes);
+        // S3: this CTA's rows of W2
+        for (int r0 = 0; r0 < w.d_n; r0 += p.s3b_rpc) {
+            const int n = min(p.s3b_rpc, w.d_n - r0);
+            pack_tiled(base + (size_t)r0 * p.down_row_bytes, n, m.hidden, [&](int r) { return src.w2[l] + (size_t)(w.d_begin + r0 + r) * m.hidden; });
+        }
     }
     uint8_t* hb = blob + (size_t)m.n_layer * p.layer_bytes;
-    for (int i = 0; i < p.vpc_max; i++)
-        pack_copy(hb + (size_t)i * p.row_bytes, i < w.v_n ? src.lm_head + (size_t)(w.v_begin + i) * d : nullptr, p.row_bytes);
+    for (int r0 = 0; r0 < w.v_n; r0 += p.head_rpc) {
+        const int n = min(p.head_rpc, w.v_n - r0);
+        pack_tiled(hb + (size_t)r0 * p.row_bytes, n, d, [&](int r) { return src.lm_head + (size_t)(w.v_begin + r0 + r) * d; });
+    }
 }
 
 }  // namespace esp
