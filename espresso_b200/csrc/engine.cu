@@ -1688,7 +1688,7 @@ int32_t Engine::build_mega() {
     mega_arena_words_ = (size_t)2 * m_.d_model + m_.hidden + (size_t)m_.n_kv_head * 2 * p.group_items + (size_t)4 * P + 8;
     if ((rc = dev_alloc(owned_, &d_mega_arena_, mega_arena_words_))) return rc;
     if ((rc = dev_alloc(owned_, &d_mega_ctl_, 8))) return rc;
-    if ((rc = dev_alloc(owned_, &d_mega_trace_, (size_t)kMegaTraceLayer * m_.n_layer + kMegaTraceHead + 4 + 512))) return rc;
+    if ((rc = dev_alloc(owned_, &d_mega_trace_, (size_t)kMegaTraceLayer * m_.n_layer + kMegaTraceHead + 4 + 1024))) return rc;
     if ((rc = dev_alloc(owned_, &d_token_times_, (size_t)m_.max_seq + 1))) return rc;
     ESP_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&h_mega_ctl_), 8 * sizeof(unsigned long long)));
     // per-layer source pointers
@@ -1780,7 +1780,7 @@ int32_t Engine::stage_trace(int32_t cta, long long* out, int32_t capacity, int32
     *n = 0;
     if (!mega_ready_) return ESP_CUDA_OK;
 #ifdef MEGA_FINE_TRACE
-    const int count = 512;
+    const int count = 1000;
 #else
     const int count = kMegaTraceLayer * m_.n_layer + kMegaTraceHead;
 #endif

@@ -335,6 +335,14 @@ __device__ __forceinline__ void mega_release(const MegaArgs& a, const MegaShared
     if ((threadIdx.x & 31) == 0) mbar_arrive(s.empty + c.slot);
     c.next((unsigned)a.plan.n_slots);
 }
+// Hands back `n` consecutive slots starting at `from` whose release was put off (see the kernel's chunk_products).
+__device__ __forceinline__ void mega_release_deferred(const MegaArgs& a, const MegaShared& s, MegaCursor from, int n) {
+    __syncwarp();
+    for (int i = 0; i < n; i++) {
+        if ((threadIdx.x & 31) == 0) mbar_arrive(s.empty + from.slot);
+        from.next((unsigned)a.plan.n_slots);
+    }
+}
 
 // ------------------------------------------------------------------------------------------------ exchanges
 
@@ -702,6 +710,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             int p_step = 0, p_n = 0;
 #endif
             const uint64_t policy = l2_evict_first_policy();
+            uint64_t keep_policy;
+            asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep_policy));
+            // head rows behind the first (n_slots - 1) chunks: what still has to come from memory when the head begins
+            const long long tail_off = (long long)min(w.v_n, (p.n_slots - 1) * p.head_rpc) * p.row_bytes;
+            const long long tail_bytes = (long long)w.v_n * p.row_bytes - tail_off;
             auto issue = [&](long long off, int bytes) {
                 if (mega_aborting(s) || *reinterpret_cast<volatile int*>(s.stop)) return;  // nothing more is copied
 #ifdef MEGA_FINE_TRACE
@@ -728,6 +741,15 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
 #endif
                 if (step > 0) {
                     for (int l = 0; l < L; l++) {
+                        // HBM idles during the layers (their weights are a full layer ahead in the ring): the part of the head
+                        // that the ring cannot hold before the head begins is brought into L2 now, a slice per layer
+                        if (tail_bytes > 0 && !mega_aborting(s)) {
+                            const long long b0 = tail_bytes * l / L / 16 * 16, b1 = l + 1 == L ? tail_bytes : tail_bytes * (l + 1) / L / 16 * 16;
+                            if (b1 > b0)
+                                asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(blob + head_off + tail_off + b0), "r"((unsigned)(b1 - b0)),
+                                             "l"(keep_policy)
+                                             : "memory");
+                        }
                         long long off = (long long)l * p.layer_bytes;
                         if (w.in_group) issue_stage(off, w.s1_n, p.s1_ipc, 2 * p.row_bytes);
                         off += p.s1_bytes;
@@ -787,13 +809,29 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
     };
     // One chunk of a stage: acquire, all products, release, CTA barrier; returns where the sums are.
     int lg_parts = 0;    // log2 of the column ranges of the chunk whose sums are being read
-    auto chunk_products = [&](int rows, int n_kb, const uint8_t* xa) {
+    // A freed slot makes the producer request the chunk that is n_slots ahead at once: megabytes of reads over all
+    // CTAs, which would travel through L2 together with the words of the exchange that follows the stage and delay
+    // them by microseconds.  The last chunk of a stage is therefore handed back only after that exchange (the chunk it
+    // makes room for is needed a whole layer later).
+    MegaCursor pend_from;
+    int n_pend = 0;
+    auto release_pending = [&]() {
+        if (n_pend) mega_release_deferred(a, s, pend_from, n_pend);
+        n_pend = 0;
+    };
+    auto chunk_products = [&](int rows, int n_kb, const uint8_t* xa, bool defer) {
         const uint8_t* ch = mega_acquire(a, s, c);
         FINE();
         float* partial = s.partial + par * kMegaChunkRows;
         par ^= 1;
         lg_parts = mega_chunk_dots(ch, rows, n_kb, xa, partial, warp, lane);
-        mega_release(a, s, c);
+        if (defer) {
+            if (n_pend == 0) pend_from = c;
+            n_pend++;
+            c.next((unsigned)p.n_slots);
+        } else {
+            mega_release(a, s, c);
+        }
         consumer_sync();
         FINE();
         return partial;
@@ -821,6 +859,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                         mega_read_words(a, s, a.x_words, d, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
                     }
                     FINE();
+                    release_pending();  // the W2 chunk of the previous layer
                     ss = mega_block_sum(ss, s.red);
                     inv = 1.0f / sqrtf(ss / (float)d + m.eps);
                     FINE();
@@ -830,7 +869,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     // CTA's W2 rows, hence the whole activation vector, hence every group CTA past its S2 of this layer.
                     for (int i0 = 0; i0 < w.s1_n; i0 += p.s1_ipc) {
                         const int n_items = min(p.s1_ipc, w.s1_n - i0);
-                        float* sums = chunk_products(2 * n_items, d >> 5, s.xa);
+                        float* sums = chunk_products(2 * n_items, d >> 5, s.xa, i0 + p.s1_ipc >= w.s1_n);
                         for (int i = tid; i < n_items; i += kMegaConsumers) {
                             int kind, row0, row1, idx;
                             mega_s1_rows(m, p, w.kvh, w.s1_begin + i0 + i, kind, row0, row1, idx);
@@ -875,6 +914,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                             else if (section == 1) { s.kn[idx] = __float2half_rn(v0); s.kn[idx + half] = __float2half_rn(v1); }
                             else { s.vn[2 * idx] = __float2half_rn(v0); s.vn[2 * idx + 1] = __float2half_rn(v1); }
                         }
+                        release_pending();  // the q/k/v chunk
                         FINE();
                         consumer_sync();
                         FINE();
@@ -885,7 +925,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     // contribution to the counted sum of that row (head 0 also carries the residual)
                     for (int r0 = 0; r0 < p.rpb; r0 += p.s2_rpc) {
                         const int nr = min(p.s2_rpc, p.rpb - r0);
-                        float* sums = chunk_products(nr, HD >> 5, reinterpret_cast<const uint8_t*>(s.ctx));
+                        float* sums = chunk_products(nr, HD >> 5, reinterpret_cast<const uint8_t*>(s.ctx), r0 + p.s2_rpc >= p.rpb);
                         for (int r = tid; r < nr; r += kMegaConsumers) {
                             const int orow = w.blk * p.rpb + r0 + r;
                             float v = mega_take_sum(sums, lg_parts, r);
@@ -902,11 +942,16 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 // ---- S3: x_mid = residual + attention projection.  mid_sums receives the next layer's contributions
                 // only after that layer's S1, which needs x_words of this layer complete, i.e. every CTA past this read.
                 {
+                    // The arg-max candidate words are used once per token; between two uses a whole model's worth of
+                    // weights streams through L2.  Reading them once per layer keeps their lines resident, so that the
+                    // token exchange does not start with a round trip to memory.
+                    if (tid < p.n_cta) (void)ld_words2(a.cand_words + 4 * (size_t)tid);
                     const float* gain = a.norms + (size_t)(2 * l + 1) * d;
                     float ss = 0.f;
                     FINE();
                     mega_read_sums(a, s, a.mid_sums, d, m.n_head, 7, gain, [&](int k, float v, float g) { stage_x(s.xmid, k, v, g, ss); });
                     FINE();
+                    release_pending();  // the Wo chunk (CTAs outside the head groups: the W2 chunk of the previous layer)
                     ss = mega_block_sum(ss, s.red);
                     inv = 1.0f / sqrtf(ss / (float)d + m.eps);
                 }
@@ -916,7 +961,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 // every CTA past its W2 rows and so past this activation vector.
                 for (int j0 = 0; j0 < w.h_n; j0 += p.s3a_ipc) {
                     const int n_items = min(p.s3a_ipc, w.h_n - j0);
-                    float* sums = chunk_products(2 * n_items, d >> 5, s.xa);
+                    float* sums = chunk_products(2 * n_items, d >> 5, s.xa, j0 + p.s3a_ipc >= w.h_n);
                     for (int j = tid; j < n_items; j += kMegaConsumers) {
                         const float g = mega_take_sum(sums, lg_parts, 2 * j) * inv;
                         const float u = mega_take_sum(sums, lg_parts, 2 * j + 1) * inv;
@@ -929,12 +974,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 FINE();
                 mega_read_words(a, s, a.act_words, m.hidden, seq, 8, nullptr, [&](int k, float v, float) { xa_store(xa_h, k, v); });
                 FINE();
+                release_pending();  // the gate/up chunk
                 consumer_sync();
                 FINE();
                 stamp(step);
                 for (int r0 = 0; r0 < w.d_n; r0 += p.s3b_rpc) {
                     const int nr = min(p.s3b_rpc, w.d_n - r0);
-                    float* sums = chunk_products(nr, m.hidden >> 5, s.xa);
+                    float* sums = chunk_products(nr, m.hidden >> 5, s.xa, r0 + p.s3b_rpc >= w.d_n);
                     for (int r = tid; r < nr; r += kMegaConsumers)
                         st_word(a.x_words + w.d_begin + r0 + r, tagged(mega_take_sum(sums, lg_parts, r) + s.xmid[w.d_begin + r0 + r], seq));
                 }
@@ -947,6 +993,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         fine_layer = 99; fine_step = step;
 #endif
         stamp(step);
+#ifndef MEGA_NO_FENCE
+        // Everything this CTA wrote with plain stores during the step (KV-cache rows; the CTA barriers since then order
+        // them before this thread) is made visible before the candidate words that thread 0 publishes at the end of the
+        // head.  Issued here, the fence overlaps the wait for the last layer's output.
+        if (tid == 0) __threadfence();
+#endif
         {
             float ss = 0.f;
             if (step == 0) {
@@ -954,6 +1006,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             } else {
                 mega_read_words(a, s, a.x_words, d, (unsigned)(step * L), 9, fin_gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
             }
+            release_pending();  // the W2 chunk of the last layer
             consumer_sync();  // the RMSNorm scale is positive: the arg-max does not need it
         }
         stamp(step);
@@ -962,13 +1015,16 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         for (int r0 = 0; r0 < w.v_n; r0 += p.head_rpc) {
             const int nrows = min(p.head_rpc, w.v_n - r0);
             FINE();
-            float* sums = chunk_products(nrows, d >> 5, s.xa);
+            float* sums = chunk_products(nrows, d >> 5, s.xa, r0 + 2 * p.head_rpc >= w.v_n);
             // thread r keeps the best of rows r0 + r over the chunks (ascending rows: '>' keeps the first maximum)
             if (tid < nrows) {
                 const float v = mega_take_sum(sums, lg_parts, tid);
                 if (v > best_v) { best_v = v; best_i = w.v_begin + r0 + tid; }
             }
         }
+#ifdef MEGA_FINE_TRACE
+        if (a.trace && tid == 0 && step == a.n_steps - 1) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.trace[600 + blockIdx.x] = (long long)t; }
+#endif
         // CTA-wide best (larger value first, then smaller index), published as two tagged words
         {
             unsigned long long k = best_i != 0x7fffffff ? pack_best(best_v, best_i) : 0ull;
@@ -981,9 +1037,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             unsigned long long k = 0ull;
 #pragma unroll
             for (int x = 0; x < kMegaConsumerWarps; x++) k = max(k, s.key[x]);
-            // Everything this CTA wrote with plain stores during the step (KV-cache rows) is ordered before the words
-            // below, and a reader orders its later loads after seeing them: one fence pair per token.
-            __threadfence();
             const unsigned tag = (unsigned)step + 1u;
             unsigned long long* mine = a.cand_words + 4 * (size_t)blockIdx.x;
             st_word(mine, ((unsigned long long)tag << 32) | (k >> 32));
@@ -1003,7 +1056,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                         if (mega_spin_out(a, s, spins, 10)) break;
                     }
                 }
+#ifndef MEGA_NO_FENCE
+                // a reader orders its later loads (the KV-cache rows other CTAs appended during this step) after the
+                // candidate words it saw; the writers' side of the pair is the fence at the start of the head
                 __threadfence();
+#endif
                 k = ((v.x & 0xffffffffull) << 32) | (v.y & 0xffffffffull);
             }
 #pragma unroll
@@ -1017,7 +1074,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             for (int x = 0; x < kMegaConsumerWarps; x++) k = max(k, s.key[x]);
             tok = min(0xffffffffu - (uint32_t)(k & 0xffffffffull), (uint32_t)(m.vocab - 1));  // in range even if every logit was NaN
         }
+        release_pending();  // the last head chunks
         stamp(step);
+#ifdef MEGA_FINE_TRACE
+        if (a.trace && tid == 0 && step == a.n_steps - 1) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.trace[800 + blockIdx.x] = (long long)t; }
+#endif
         emitted = step + 1;
         if (blockIdx.x == 0 && tid == 0) {
             unsigned long long t;

@@ -363,7 +363,7 @@ class DecodeEngine:
 
     def stage_trace(self, next_cta: int = 0) -> np.ndarray:
         """SM clock stamps of the persistent kernel's last token (see ``esp_cuda_stage_trace``)."""
-        out = np.zeros(max(512, 10 * self.config.nLayer + 8), np.int64)
+        out = np.zeros(max(1024, 10 * self.config.nLayer + 8), np.int64)
         n = C.c_int32()
         _check(self._lib.esp_cuda_stage_trace(self._h, next_cta, out.ctypes.data_as(C.POINTER(C.c_int64)), out.size, C.byref(n)))
         return out[: n.value].copy()
