@@ -7,6 +7,11 @@ A "step" is one pass of the hot path over one batch of synthetic input: a greedy
 decode, token download all inside the timed region).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1] [--impl ours|reference]
+    python bench.py --kernel gemv|gemm --rows R --cols C --type f16|bf16|q8_0|q4_0 [--batch N]   # one stand-alone kernel
+
+The second form times a single kernel on a matrix of the given shape and prints one JSON line (mean kernel
+milliseconds, GB/s over the algorithmic bytes, TFLOP/s for the GEMM); it launches nothing but that kernel (plus, for
+a K-sliced GEMM, the clearing of its output), which makes it the command the profiler summaries capture.
 """
 from __future__ import annotations
 
@@ -288,59 +293,53 @@ def gemm_table(runtime, device: int, peak: float) -> dict:
     return out
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-steps", type=int, default=3)
-    ap.add_argument("--decode-tokens", type=int, default=0, help="override the workload's decode length (profiling of small cases)")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-gemv-table", action="store_true")
-    ap.add_argument("--per-stage", action="store_true", help="use the per-stage kernels even where the persistent kernel applies")
-    args = ap.parse_args()
-    if args.impl == "ours":
-        args.warmup = max(args.warmup, 3)
+def run_kernel_probe(args) -> None:
+    """Times one stand-alone kernel of the library on a seeded matrix (see the module docstring)."""
+    from espresso_b200 import gguf_quant, runtime
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    wl = dict(WORKLOADS[args.workload])
-    if args.decode_tokens > 0:
-        wl["decode"] = args.decode_tokens
-    cfg = wl["cfg"]()
-    metric, unit = "decode tokens/s (whole job)", "tokens/s"
+    bpw = {"f16": 2.0, "bf16": 2.0, "q8_0": 34 / 32, "q4_0": 18 / 32}[args.type]
+    rng = np.random.default_rng(3)
+    w = rng.standard_normal((args.rows, args.cols)).astype(np.float32) * np.float32(0.02)
+    stored = w.astype(np.float16) if args.type == "f16" else (w.view(np.uint32) >> 16).astype(np.uint16) if args.type == "bf16" else gguf_quant.quantize(args.type, w)
+    wbytes = args.rows * args.cols * bpw
+    if args.kernel == "gemm":
+        x = rng.standard_normal((args.batch, args.cols)).astype(np.float32)
+        _, ms = runtime.gemm_tc_bench(args.type, stored, args.rows, args.cols, x, args.warmup, args.iterations, 0)
+        nbytes = wbytes + args.batch * args.cols * 2 + args.batch * args.rows * 4
+        flops = 2.0 * args.rows * args.cols * args.batch
+    else:
+        x = rng.standard_normal(args.cols).astype(np.float32)
+        copies = max(2, int(400e6 // wbytes) + 1)  # rotate copies so that reads miss L2
+        _, ms = runtime.gemv_bench(args.type, stored, args.rows, args.cols, x, args.warmup, args.iterations, copies, 0)
+        nbytes = wbytes + args.cols * 4 + args.rows * 4
+        flops = 2.0 * args.rows * args.cols
+    print(json.dumps({"kernel": args.kernel, "type": args.type, "rows": args.rows, "cols": args.cols,
+                      "batch": args.batch if args.kernel == "gemm" else 1, "ms": ms, "algorithmic_bytes": nbytes,
+                      "GBps": nbytes / (ms / 1e3) / 1e9, "TFLOPs": flops / (ms / 1e3) / 1e12}))
 
-    if args.impl == "reference":
-        # The reference's own CPU implementation of the path, restated (the Swift/Accelerate original does not
-        # build on Linux); rank 0 alone runs it on all host cores.
-        if rank != 0:
-            return
-        r = run_cpu_oracle(wl, max(args.steps, 1), args.warmup)
-        line = {
-            "impl": "reference", "metric": metric, "value": r["value"], "unit": unit, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl["label"], "l2": "fp32 weights exceed the host caches"},
-            "cpu_baseline": {"value": r["value"], "unit": unit, "cores": r["cores"], "cpu_model": cpu_model(), "kind": "port", "sample": r["sample"]},
-            "e2e": {"value": r["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        }
-        print(json.dumps(line))
-        return
 
+def config_of(wl: dict, world: int) -> dict:
+    """The `config` object of a bench line: identical for both arms (ours and --impl reference)."""
+    if world > 1:
+        par = ("tensor parallel over the GPUs, partial sums after Wo and W2 added over NVLink peer memory, arg-max over NCCL" if wl.get("tp") else
+               "sequences sharded across GPUs, no collective" if wl.get("sharded") else
+               "replicas only (one independent job per GPU)")
+    else:
+        par = "single GPU"
+    return {"workload": wl["label"], "parallelism": par,
+            "l2": "no flush: every decode step streams more weight + KV bytes than the 126 MB L2 holds"}
+
+
+def measure(args, wl: dict, rank: int, local_rank: int, world: int, steps: int, warmup: int, full: bool) -> dict:
+    """Times one workload on this job's GPUs (every rank calls it).  Returns the numbers of a bench line; with `full`
+    also the end-to-end figure through the public generate call and, for the persistent kernel, its stage trace."""
     import torch
     import torch.distributed as dist
 
     from espresso_b200 import runtime
     from espresso_b200.sharding import shard_range
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU implementation")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg = wl["cfg"]()
 
     def barrier():
         if world > 1:
@@ -348,6 +347,7 @@ def main() -> None:
         torch.cuda.synchronize()
 
     tmp = tempfile.mkdtemp(prefix=f"esp_bench_r{rank}_")
+    eng = draft = None
     try:
         n_prompt, n_decode = wl["prompt"], wl["decode"]
         tp = bool(wl.get("tp")) and world > 1
@@ -373,7 +373,6 @@ def main() -> None:
         else:
             write_synthetic_model(cfg, tmp)
             eng = runtime.DecodeEngine.build(tmp, max_batch=n_seq, device=local_rank, flags=flags)
-        draft = None
         if "draft" in wl:
             dtmp = os.path.join(tmp, "draft")
             write_synthetic_model(wl["draft"](), dtmp, seed=1235)
@@ -391,7 +390,7 @@ def main() -> None:
             # ---- device-resident throughput: K timed steps, each a device-driven decode of n_decode tokens ----
             prefill()
             cp = eng.capture_checkpoint() if n_seq == 1 else None
-            for _ in range(args.warmup):
+            for _ in range(warmup):
                 if cp is not None:
                     eng.rollback(cp)
                 else:
@@ -399,7 +398,7 @@ def main() -> None:
                 eng.decode(n_decode, n_seq)
             barrier()
             sampler.start()
-            for _ in range(args.steps):
+            for _ in range(steps):
                 if cp is not None:
                     eng.rollback(cp)  # positions return to the end of the prompt; KV slots are simply overwritten
                 else:
@@ -411,12 +410,12 @@ def main() -> None:
             barrier()
         else:
             # ---- two-token speculative loop: host-driven passes, timed on the host from the end of prefill ----
-            for _ in range(args.warmup):
+            for _ in range(warmup):
                 eng.generate_two_token(draft, prompts[0], n_decode)
             barrier()
             sampler.start()
             acc, com = [], []
-            for _ in range(args.steps):
+            for _ in range(steps):
                 res = eng.generate_two_token(draft, prompts[0], n_decode)
                 assert len(res.tokens) == n_decode
                 step_ms.append(res.totalDecodeMs)
@@ -430,41 +429,43 @@ def main() -> None:
         total_ms = sum(step_ms)
 
         # ---- end to end through the public generate call with host buffers ----
-        e2e_times = []
-        for i in range(args.warmup + args.steps):
-            t0 = time.perf_counter()
-            if draft is not None:
-                res = eng.generate_two_token(draft, prompts[0], n_decode)
-            elif n_seq == 1:
-                res = eng.generate(prompts[0], n_decode)
-            else:
-                _, res = eng.generate_batch(prompts, n_decode)
-            torch.cuda.synchronize()
-            if i >= args.warmup:
-                e2e_times.append(time.perf_counter() - t0)
-        e2e_total = sum(e2e_times)
+        e2e_total = None
+        if full:
+            e2e_times = []
+            for i in range(warmup + steps):
+                t0 = time.perf_counter()
+                if draft is not None:
+                    res = eng.generate_two_token(draft, prompts[0], n_decode)
+                elif n_seq == 1:
+                    res = eng.generate(prompts[0], n_decode)
+                else:
+                    _, res = eng.generate_batch(prompts, n_decode)
+                torch.cuda.synchronize()
+                if i >= warmup:
+                    e2e_times.append(time.perf_counter() - t0)
+            e2e_total = sum(e2e_times)
 
-        tokens_local = n_seq * n_decode * args.steps
+        tokens_local = n_seq * n_decode * steps
         if wl.get("tp") and world > 1 and rank != 0:
             tokens_local = 0  # the ranks of a tensor-parallel group decode the same sequences together
         if world > 1:
-            t = torch.tensor([total_ms, e2e_total], dtype=torch.float64, device="cuda")
+            t = torch.tensor([total_ms, e2e_total or 0.0], dtype=torch.float64, device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            total_ms, e2e_total = float(t[0]), float(t[1])
+            total_ms, e2e_max = float(t[0]), float(t[1])
+            e2e_total = e2e_max if e2e_total is not None else None
             lt = torch.tensor([launches, tokens_local], dtype=torch.int64, device="cuda")
             dist.all_reduce(lt)
             launches, tokens_all = int(lt[0]), int(lt[1])
         else:
             tokens_all = tokens_local
         value = tokens_all / (total_ms / 1e3)
-        e2e_value = tokens_all / e2e_total
 
         # ---- roofline of the dominant kernel, timed live with CUDA events ----
         peak, peak_kind = read_peaks()
         bpw = wl["bpw"]
         head_bytes = cfg.vocab * cfg.dModel * bpw + cfg.dModel * 2
         bytes_tok = algorithmic_bytes_per_token(cfg, n_prompt, n_decode, n_seq, bpw)
-        persistent = draft is None and n_seq == 1 and launches == args.steps * world
+        persistent = draft is None and n_seq == 1 and launches == steps * world
         if persistent:
             # one launch of the persistent kernel = one whole step (n_decode heads, n_decode - 1 forward passes)
             launch_bytes = head_bytes + (n_decode - 1) * bytes_tok
@@ -472,13 +473,13 @@ def main() -> None:
             roofline = {"bound": "hbm", "kernel": "k_decode_mega (whole greedy loop: all layers + LM head, one launch per step)",
                         "achieved": launch_bytes / launch_s / 1e9, "peak": peak, "unit": "GB/s",
                         "frac": launch_bytes / launch_s / 1e9 / peak,
-                        # DRAM bytes of one launch: ncu measured 1.018 x the algorithmic bytes on a 4-token launch
-                        # (profiles/k_decode_mega_c1.md); traffic grows in proportion to the tokens of a launch
-                        "traffic": 1.018 * launch_bytes, "peak_kind": peak_kind,
+                        # DRAM bytes of one launch: measured with ncu on a 4-token launch of this kernel as a multiple of its
+                        # algorithmic bytes; traffic grows in proportion to the tokens of a launch
+                        "traffic": MEGA_TRAFFIC_RATIO * launch_bytes, "peak_kind": peak_kind,
                         "bytes_per_launch": launch_bytes, "bytes_per_token": bytes_tok}
         else:
             head_ms = []
-            if n_seq == 1 and draft is None and not wl.get("device_weights"):
+            if full and n_seq == 1 and draft is None and not wl.get("device_weights"):
                 prof = runtime.DecodeEngine.build(tmp, max_batch=n_seq, device=local_rank, flags=runtime.FLAG_NO_GRAPH)
                 prof.prefill(prompts[0])
                 tok = prof.select_greedy_token()
@@ -489,56 +490,207 @@ def main() -> None:
                 prof.close()
             head_t = statistics.mean(head_ms) if head_ms else None
             per_gpu_tok_s = value / world
+            if tp:
+                # a tensor-parallel rank streams its shard of the weights for all the sequences, and its KV heads
+                step_bytes = (cfg.weight_bytes_per_step(bpw) / world + (bytes_tok - cfg.weight_bytes_per_step(bpw) / n_seq) * n_seq / world)
+                whole = {"bytes_per_step_per_gpu": step_bytes, "achieved": step_bytes / (total_ms / steps / n_decode / 1e3) / 1e9}
+                whole["frac"] = whole["achieved"] / peak
+            else:
+                whole = {"bytes_per_token": bytes_tok, "achieved": per_gpu_tok_s * bytes_tok / 1e9, "frac": per_gpu_tok_s * bytes_tok / 1e9 / peak}
             roofline = {"bound": "hbm", "kernel": "k_lm_head (final norm + LM head + argmax)" if head_t else "whole decode step (all per-stage kernels of one token)",
-                        "achieved": (head_bytes / (head_t / 1e3) / 1e9) if head_t else per_gpu_tok_s * bytes_tok / 1e9, "peak": peak, "unit": "GB/s",
-                        "frac": ((head_bytes / (head_t / 1e3) / 1e9) if head_t else per_gpu_tok_s * bytes_tok / 1e9) / peak, "traffic": None,
-                        "peak_kind": peak_kind,
-                        "whole_step": {"bytes_per_token": bytes_tok, "achieved": per_gpu_tok_s * bytes_tok / 1e9,
-                                       "frac": per_gpu_tok_s * bytes_tok / 1e9 / peak}}
-
+                        "achieved": (head_bytes / (head_t / 1e3) / 1e9) if head_t else whole["achieved"], "peak": peak, "unit": "GB/s",
+                        "frac": ((head_bytes / (head_t / 1e3) / 1e9) if head_t else whole["achieved"]) / peak, "traffic": None,
+                        "peak_kind": peak_kind, "whole_step": whole}
         roofline["frac_of_nominal_8000_GBps"] = roofline["achieved"] / 8000.0  # beside the fraction of the measured copy peak
-        line = {
-            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": total_ms / args.steps, "ms_per_token": total_ms / args.steps / n_decode, "higher_is_better": True,
-            "scaling": scaling, "vs_baseline": None, "dtype": f"{wl['kind']} weights, f16 KV, f32 accumulate", "data": "synthetic",
-            "config": {"workload": wl["label"],
-                       "parallelism": (f"tensor parallel x{world}, partial sums after Wo and W2 added over NVLink peer memory (NCCL when ESP_CUDA_TP_NCCL_ONLY is set), arg-max over NCCL" if wl.get("tp") else
-                                       "sequences sharded across GPUs, no collective" if wl.get("sharded") else
-                                       "replicas only (one independent job per GPU)") if world > 1 else "single GPU",
-                       "l2": "no flush: every decode step streams more weight + KV bytes than the 126 MB L2 holds"},
-            "e2e": {"value": e2e_value, "unit": unit,
-                    "h2d_bytes_per_step": int(n_seq * n_prompt * 4), "d2h_bytes_per_step": int(n_seq * n_decode * 4),
-                    "note": "generate(): prompt upload + prefill + decode + token download, wall clock"},
-            "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
-        }
-        line.update(extra)
-        if rank == 0 and draft is None and n_seq == 1:
+
+        out = {"value": value, "ms_per_step": total_ms / steps, "ms_per_token": total_ms / steps / n_decode, "scaling": scaling,
+               "launches": launches, "clocks": clocks, "roofline": roofline, "extra": extra, "n_seq_per_gpu": n_seq,
+               "e2e_value": tokens_all / e2e_total if e2e_total else None,
+               "h2d": int(n_seq * n_prompt * 4), "d2h": int(n_seq * n_decode * 4), "steps": steps, "warmup": warmup}
+        if full and rank == 0 and draft is None and n_seq == 1:
             st = stage_trace_us(eng, cfg, prompts[0], n_decode, clocks.get("sm_mhz") or 1965.0)
             if st:
-                line["stage_trace_us"] = st
+                out["stage_trace_us"] = st
             tt = eng.token_times_ns()  # of the loop stage_trace_us just ran
             if tt.size > 2:
                 gaps = np.diff(tt.astype(np.int64)) / 1e6
-                line["ms_per_token_gaps"] = {"median": float(np.median(gaps)), "p95": float(np.percentile(gaps, 95)), "tokens": int(tt.size),
-                                             "note": "GPU-timer gaps between consecutive tokens inside one decode loop"}
-        if rank == 0 and not args.no_gemv_table:
-            line["gemv"] = gemv_table(runtime, local_rank, peak)
-            line["gemm_tc"] = gemm_table(runtime, local_rank, peak)
-        if rank == 0 and not args.no_cpu_baseline:
-            r = run_cpu_oracle(wl, args.cpu_steps, 1)
-            line["cpu_baseline"] = {"value": r["value"], "unit": unit, "cores": r["cores"], "cpu_model": cpu_model(), "kind": "port", "sample": r["sample"]}
+                out["ms_per_token_gaps"] = {"median": float(np.median(gaps)), "p95": float(np.percentile(gaps, 95)), "tokens": int(tt.size),
+                                            "note": "GPU-timer gaps between consecutive tokens inside one decode loop"}
+        return out
+    finally:
         if world > 1:
             dist.barrier()  # members of a tensor-parallel group tear their communicator down together
-        eng.close()
+        if eng is not None:
+            eng.close()
         if draft is not None:
             draft.close()
-        if rank == 0:
-            print(json.dumps(line))
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
-    finally:
         shutil.rmtree(tmp, ignore_errors=True)
+
+
+def tp_matches_single_gpu(rank: int, local_rank: int, world: int) -> bool | None:
+    """A small model decoded tensor parallel over this job's GPUs and, on rank 0, by a single-GPU engine of this library:
+    the greedy streams must be identical wherever the single-GPU logits leave no near tie (the comparison with the CPU
+    restatement of the reference is the test suite's job)."""
+    import torch.distributed as dist
+
+    from espresso_b200 import runtime
+    from espresso_b200.model_config import MultiModelConfig
+    from espresso_b200.sharding import tp_shard
+    from espresso_b200.synthetic import synthetic_tensors
+
+    if world < 2:
+        return None
+    cfg = MultiModelConfig("tp-check", 2, 8, 8, 256, 32, 512, 1024, 64, 1e-5, 10000.0, None, "llama")
+    if cfg.nKVHead % world:
+        return None
+    n_seq, n_prompt, n_decode = 6, 9, 14
+    prompts = np.stack([synthetic_prompt(cfg.vocab, n_prompt, stream=s) for s in range(n_seq)])
+    ids = [runtime.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    eng = runtime.DecodeEngine.empty(cfg, max_batch=n_seq, device=local_rank, tp_rank=rank, tp_size=world)
+    eng.tp_init(ids[0])
+    for name, vals in synthetic_tensors(cfg):
+        eng.load_tensor(name, "f16", np.ascontiguousarray(tp_shard(name, vals, rank, world)))
+    eng.finalize()
+    toks, _ = eng.generate_batch(prompts, n_decode)
+    ok = None
+    if rank == 0:
+        ref = runtime.DecodeEngine.empty(cfg, max_batch=n_seq, device=local_rank)
+        for name, vals in synthetic_tensors(cfg):
+            ref.load_tensor(name, "f16", np.ascontiguousarray(vals))
+        ref.finalize()
+        ok = True
+        for s in range(n_seq):
+            # teacher-forced: the single-GPU engine is fed the tensor-parallel stream
+            ref.reset()
+            ref.prefill(prompts[s])
+            for i, t in enumerate(toks[s]):
+                lg = ref.logits()
+                if int(t) != int(np.argmax(lg)) and float(lg.max() - lg[int(t)]) > 2e-2:
+                    ok = False
+                if i + 1 < len(toks[s]):
+                    ref.advance(int(t))
+        ref.close()
+    dist.barrier()
+    eng.close()
+    dist.barrier()
+    return ok
+
+
+# DRAM bytes of a launch of the persistent kernel as a multiple of its algorithmic bytes (ncu, 4-token launch)
+MEGA_TRAFFIC_RATIO = 1.018
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--decode-tokens", type=int, default=0, help="override the workload's decode length (profiling of small cases)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gemv-table", action="store_true")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the sequence-sharded (c3) and tensor-parallel (c5) figures that accompany the default workload")
+    ap.add_argument("--per-stage", action="store_true", help="use the per-stage kernels even where the persistent kernel applies")
+    ap.add_argument("--kernel", choices=["gemv", "gemm"], help="time one stand-alone kernel instead of a workload")
+    ap.add_argument("--rows", type=int, default=32768)
+    ap.add_argument("--cols", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=64, help="--kernel gemm: activation rows (1..256)")
+    ap.add_argument("--type", default="f16", choices=["f16", "bf16", "q8_0", "q4_0"])
+    ap.add_argument("--iterations", type=int, default=40)
+    args = ap.parse_args()
+    if args.kernel:
+        run_kernel_probe(args)
+        return
+    if args.impl == "ours":
+        args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    wl = dict(WORKLOADS[args.workload])
+    if args.decode_tokens > 0:
+        wl["decode"] = args.decode_tokens
+    metric, unit = "decode tokens/s (whole job)", "tokens/s"
+
+    if args.impl == "reference":
+        # The reference's own CPU implementation of the path, restated (the Swift/Accelerate original does not
+        # build on Linux); rank 0 alone runs it on all host cores, the other ranks leave at once.
+        if rank != 0:
+            return
+        r = run_cpu_oracle(wl, max(args.steps, 1), args.warmup)
+        line = {
+            "impl": "reference", "metric": metric, "value": r["value"], "unit": unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_of(wl, max(args.gpus, 1)),
+            "cpu_baseline": {"value": r["value"], "unit": unit, "cores": r["cores"], "cpu_model": cpu_model(), "kind": "port", "sample": r["sample"]},
+            "e2e": {"value": r["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "CPU restatement of the reference's path on the host cores, fp32 weights larger than the host caches",
+        }
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from espresso_b200 import runtime
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU implementation")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    r = measure(args, wl, rank, local_rank, world, args.steps, args.warmup, full=True)
+    line = {
+        "metric": metric, "value": r["value"], "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": r["ms_per_step"], "ms_per_token": r["ms_per_token"], "higher_is_better": True,
+        "scaling": r["scaling"], "vs_baseline": None, "dtype": f"{wl['kind']} weights, f16 KV, f32 accumulate", "data": "synthetic",
+        "config": config_of(wl, world),
+        "e2e": {"value": r["e2e_value"], "unit": unit, "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"],
+                "note": "generate(): prompt upload + prefill + decode + token download, wall clock"},
+        "gpu_launches": r["launches"], "clocks": r["clocks"], "roofline": r["roofline"],
+    }
+    line.update(r["extra"])
+    for k in ("stage_trace_us", "ms_per_token_gaps"):
+        if k in r:
+            line[k] = r[k]
+
+    # ---- the two configurations that partition work across GPUs, measured on the same GPUs in the same run ----
+    if args.workload == "c1" and not args.no_sharded and args.decode_tokens == 0:
+        for key, name, k_steps in (("sharded_c3", "c3", 2), ("tp_c5", "c5", 1)):
+            w2 = dict(WORKLOADS[name])
+            if name == "c5" and (w2["cfg"]().nKVHead % world or world > w2["cfg"]().nKVHead):
+                continue
+            m = measure(args, w2, rank, local_rank, world, k_steps, 1, full=False)
+            entry = {"workload": w2["label"], "tokens_per_s": m["value"], "ms_per_step": m["ms_per_step"], "ms_per_token_step": m["ms_per_token"],
+                     "sequences_per_gpu": m["n_seq_per_gpu"], "steps": k_steps, "warmup": 1, "gpu_launches": m["launches"],
+                     "roofline_whole_step_frac": m["roofline"].get("whole_step", {}).get("frac"), "clocks": m["clocks"],
+                     "parallelism": config_of(w2, world)["parallelism"]}
+            if name == "c5":
+                L = w2["cfg"]().nLayer
+                entry["all_reduce"] = {"path": "peer memory (k_tp_sum_peers)" if world > 1 and not os.environ.get("ESP_CUDA_TP_NCCL_ONLY") else ("NCCL" if world > 1 else "none (one GPU)"),
+                                       "per_decode_step": 2 * L if world > 1 else 0, "bytes_each": w2["n_seq"] * w2["cfg"]().dModel * 4}
+                entry["matches_single_gpu_engine"] = tp_matches_single_gpu(rank, local_rank, world)
+            line[key] = entry
+
+    # kernel-level tables and the CPU baseline belong to the single-GPU line: under torchrun no rank may sit in a
+    # collective while rank 0 works on the host
+    if world == 1 and not args.no_gemv_table:
+        peak, _ = read_peaks()
+        line["gemv"] = gemv_table(runtime, local_rank, peak)
+        line["gemm_tc"] = gemm_table(runtime, local_rank, peak)
+    if world == 1 and not args.no_cpu_baseline:
+        c = run_cpu_oracle(wl, args.cpu_steps, 1)
+        line["cpu_baseline"] = {"value": c["value"], "unit": unit, "cores": c["cores"], "cpu_model": cpu_model(), "kind": "port", "sample": c["sample"]}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -317,6 +317,13 @@ Engine::~Engine() {
     if (cfg_.device >= 0) cudaSetDevice(cfg_.device);
     if (stream_) cudaStreamSynchronize(stream_);
     for (auto& g : graphs_) cudaGraphExecDestroy(g.second);  // graphs hold captured collectives: they go first
+    // Destroying a tensor-parallel engine is a collective call: a peer may still be reading this rank's exchange block
+    // (its last k_tp_sum_peers of a forward-only pass), so the ranks meet once more before any mapping or block goes away.
+    if (tp_peer_ready_ && nccl_comm_ && nccl_api().ok && tp_epoch_) {
+        unsigned long long* d_sync = reinterpret_cast<unsigned long long*>(tp_epoch_);  // two words of scratch the kernels no longer use
+        if (nccl_api().AllReduce(d_sync, d_sync, 1, ncclUint64, ncclMax, static_cast<ncclComm_t>(nccl_comm_), stream_) == ncclSuccess)
+            cudaStreamSynchronize(stream_);
+    }
     for (int p = 0; p < 8; p++)
         if (tp_peer_block_[p] && p != tp_rank_) cudaIpcCloseMemHandle(tp_peer_block_[p]);
     if (tp_block_) cudaFree(tp_block_);
@@ -874,6 +881,9 @@ int32_t Engine::reset() {
     ESP_CUDA_TRY(cudaMemsetAsync(rs_.best, 0, sizeof(unsigned long long) * max_rows_, stream_));
     ESP_CUDA_TRY(cudaMemsetAsync(rs_.ticket, 0, 16, stream_));
     ESP_CUDA_TRY(cudaMemsetAsync(act_.att_ticket, 0, sizeof(unsigned int) * (size_t)max_rows_ * m_.n_head, stream_));
+    // a bounded wait of the batched or tensor-parallel kernels that ran out left its code here and makes every later
+    // kernel skip its waits: reset() is the documented way back (on a tensor-parallel group every rank must reset)
+    if (d_tc_error_) ESP_CUDA_TRY(cudaMemsetAsync(d_tc_error_, 0, sizeof(int), stream_));
     ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
     std::fill(h_visible_.begin(), h_visible_.end(), 0);
     for (auto& c : checkpoints_) c.visible = -1;
@@ -1309,6 +1319,9 @@ float* Engine::tp_current_partial() const {
 }
 
 // Collective: every rank calls it once (from finalize).  On any failure the engine keeps the NCCL all-reduce.
+// Collective: every rank runs the same two NCCL calls (handle exchange, vote) whatever happens locally, so a rank whose
+// allocation or mapping fails cannot leave the others blocked inside a collective; one failure makes the whole group
+// fall back to NCCL all-reduces.
 int32_t Engine::tp_peer_setup() {
     tp_peer_ready_ = false;
     if (tp_size_ <= 1 || tp_size_ > 8 || !nccl_comm_ || getenv("ESP_CUDA_TP_NCCL_ONLY")) return ESP_CUDA_OK;
@@ -1316,42 +1329,52 @@ int32_t Engine::tp_peer_setup() {
     if (!api.AllGather) return ESP_CUDA_OK;
     tp_buf_floats_ = ((size_t)max_rows_ * m_.d_model + 63) / 64 * 64;
     const size_t block_bytes = 2 * tp_buf_floats_ * sizeof(float) + 256;
-    ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&tp_block_), block_bytes));
-    ESP_CUDA_TRY(cudaMemset(tp_block_, 0, block_bytes));
-    int32_t rc;
-    if ((rc = dev_alloc(owned_, &tp_epoch_, 2))) return rc;
-    cudaIpcMemHandle_t mine;
-    ESP_CUDA_TRY(cudaIpcGetMemHandle(&mine, tp_block_));
+    bool ok = true;  // this rank's part worked so far
+    cudaIpcMemHandle_t mine{};
+    if (cudaMalloc(reinterpret_cast<void**>(&tp_block_), block_bytes) != cudaSuccess) { cudaGetLastError(); tp_block_ = nullptr; ok = false; }
+    if (ok && cudaMemset(tp_block_, 0, block_bytes) != cudaSuccess) { cudaGetLastError(); ok = false; }
+    if (ok && dev_alloc(owned_, &tp_epoch_, 2) != ESP_CUDA_OK) ok = false;
+    if (ok && cudaIpcGetMemHandle(&mine, tp_block_) != cudaSuccess) { cudaGetLastError(); ok = false; }
+    // exchange of the handles (a rank that failed sends zeros; nobody maps anything unless every rank voted "ok")
     uint8_t* d_handles = nullptr;
-    ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_handles), sizeof(mine) * (size_t)(tp_size_ + 1)));
+    ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_handles), sizeof(mine) * (size_t)(tp_size_ + 1) + 16));
     std::vector<cudaIpcMemHandle_t> all((size_t)tp_size_);
     cudaError_t e = cudaMemcpy(d_handles + sizeof(mine) * tp_size_, &mine, sizeof(mine), cudaMemcpyHostToDevice);
-    ncclResult_t r = ncclSuccess;
-    if (e == cudaSuccess) r = api.AllGather(d_handles + sizeof(mine) * tp_size_, d_handles, sizeof(mine), ncclInt8, static_cast<ncclComm_t>(nccl_comm_), stream_);
+    ncclResult_t r = api.AllGather(d_handles + sizeof(mine) * tp_size_, d_handles, sizeof(mine), ncclInt8, static_cast<ncclComm_t>(nccl_comm_), stream_);
     if (e == cudaSuccess && r == ncclSuccess) e = cudaStreamSynchronize(stream_);
     if (e == cudaSuccess && r == ncclSuccess) e = cudaMemcpy(all.data(), d_handles, sizeof(mine) * tp_size_, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess || r != ncclSuccess) ok = false;
+    // first vote: did every rank export a block?
+    auto vote = [&](bool mine_ok, bool* all_ok) -> int32_t {
+        unsigned long long h = mine_ok ? 0ull : 1ull;  // max over ranks of "failed"
+        unsigned long long* d_in = nullptr;
+        ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_in), 16));
+        cudaError_t ce = cudaMemcpy(d_in, &h, 8, cudaMemcpyHostToDevice);
+        ncclResult_t nr = api.AllReduce(d_in, d_in + 1, 1, ncclUint64, ncclMax, static_cast<ncclComm_t>(nccl_comm_), stream_);
+        if (ce == cudaSuccess && nr == ncclSuccess) ce = cudaStreamSynchronize(stream_);
+        if (ce == cudaSuccess && nr == ncclSuccess) ce = cudaMemcpy(&h, d_in + 1, 8, cudaMemcpyDeviceToHost);
+        cudaFree(d_in);
+        if (nr != ncclSuccess) return nccl_fail(nr, "ncclAllReduce");
+        ESP_CUDA_TRY(ce);
+        *all_ok = h == 0ull;
+        return ESP_CUDA_OK;
+    };
+    bool everyone = false;
+    int32_t rc = vote(ok, &everyone);
     cudaFree(d_handles);
-    if (r != ncclSuccess) return nccl_fail(r, "ncclAllGather");
-    ESP_CUDA_TRY(e);
-    bool ok = true;
-    for (int p = 0; p < tp_size_; p++) {
-        if (p == tp_rank_) { tp_peer_block_[p] = tp_block_; continue; }
-        void* ptr = nullptr;
-        if (cudaIpcOpenMemHandle(&ptr, all[(size_t)p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); ok = false; break; }
-        tp_peer_block_[p] = static_cast<uint8_t*>(ptr);
+    if (rc) return rc;
+    if (everyone) {
+        for (int p = 0; p < tp_size_; p++) {
+            if (p == tp_rank_) { tp_peer_block_[p] = tp_block_; continue; }
+            void* ptr = nullptr;
+            if (cudaIpcOpenMemHandle(&ptr, all[(size_t)p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); ok = false; break; }
+            tp_peer_block_[p] = static_cast<uint8_t*>(ptr);
+        }
     }
-    // all ranks must agree: one that could not map a peer makes everybody fall back
-    unsigned long long* d_ok = nullptr;
-    ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_ok), 16));
-    unsigned long long h_ok = ok ? 0ull : 1ull;  // max over ranks of "failed"
-    e = cudaMemcpy(d_ok, &h_ok, 8, cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) r = api.AllReduce(d_ok, d_ok + 1, 1, ncclUint64, ncclMax, static_cast<ncclComm_t>(nccl_comm_), stream_);
-    if (e == cudaSuccess && r == ncclSuccess) e = cudaStreamSynchronize(stream_);
-    if (e == cudaSuccess && r == ncclSuccess) e = cudaMemcpy(&h_ok, d_ok + 1, 8, cudaMemcpyDeviceToHost);
-    cudaFree(d_ok);
-    if (r != ncclSuccess) return nccl_fail(r, "ncclAllReduce");
-    ESP_CUDA_TRY(e);
-    tp_peer_ready_ = h_ok == 0ull;
+    // second vote: one rank that could not map a peer makes everybody fall back
+    bool mapped = false;
+    if ((rc = vote(ok && everyone, &mapped))) return rc;
+    tp_peer_ready_ = mapped;
     tp_parity_ = 0;
     return ESP_CUDA_OK;
 }
@@ -1619,7 +1642,7 @@ int32_t Engine::build_mega() {
     if ((cfg_.flags & ESP_CUDA_FLAG_NO_MEGAKERNEL) || tp_size_ > 1) return ESP_CUDA_OK;
     if (m_.arch != ARCH_LLAMA) return ESP_CUDA_OK;
     if (m_.head_dim != 32 && m_.head_dim != 64 && m_.head_dim != 128) return ESP_CUDA_OK;
-    if (m_.d_model % 32 || m_.hidden % 32 || m_.n_head > sm_count_ || m_.n_head > 255) return ESP_CUDA_OK;
+    if (m_.d_model % 32 || m_.hidden % 32 || m_.n_head > sm_count_ || m_.n_head > 255 || m_.vocab >= (1 << 24)) return ESP_CUDA_OK;
     // fp16 source of a matrix: its own storage, or the fp16 expansion of a quantised matrix
     auto f16_source = [&](const std::string& name) -> const __half* {
         const DeviceTensor& t = tensors_.at(name);

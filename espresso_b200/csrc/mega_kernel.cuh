@@ -3,7 +3,7 @@
 // One cooperative launch runs an entire greedy decode loop: `n_steps` heads and up to `n_steps - 1` forward
 // passes.  The grid has one CTA per SM.  Inside a CTA one producer warp streams that CTA's weights from HBM into a
 // shared-memory ring with bulk async copies (cp.async.bulk + mbarrier), always running ahead of the sixteen
-// consumer warps, so HBM keeps streaming while the consumers wait on the activation dependencies of the step.
+// consumer warps (a watcher warp turns the copies' completions into a counter the consumers can read cheaply), so HBM keeps streaming while the consumers wait on the activation dependencies of the step.
 // Weights are re-laid out once ("pack") so that everything a CTA needs for one layer is contiguous.
 //
 // Batch-1 decode is bound by the chain of dependent vector exchanges between CTAs, not by bytes, so the kernel has
@@ -43,7 +43,7 @@ namespace esp {
 
 constexpr int kMegaConsumerWarps = 16;
 constexpr int kMegaConsumers = kMegaConsumerWarps * 32;
-constexpr int kMegaThreads = kMegaConsumers + 32;  // + one producer warp
+constexpr int kMegaThreads = kMegaConsumers + 64;  // + the producer warp and the watcher warp
 constexpr unsigned kMegaSpinLimit = 1u << 21;      // default attempts per wait before the kernel gives up (a few seconds)
 constexpr int kMegaTraceLayer = 10;                // stamps per layer
 constexpr int kMegaTraceHead = 4;                  // stamps of the head
@@ -94,7 +94,7 @@ struct MegaArgs {
     unsigned long long* act_words;  // [hidden] tagged: FFN activation
     unsigned long long* qkv_words;  // [n_kv_head][2 * group_items] tagged: post-RoPE q / k / v of one token
     unsigned long long* mid_sums;   // [d_model] counted: residual + attention projection
-    unsigned long long* cand_words; // [n_cta][4] tagged: {logit bits, index} of each CTA's best row
+    unsigned long long* cand_words; // [n_cta] {logit bits, index, 8-bit tag} of each CTA's best row
     float* hidden_io;         // [d_model] last hidden state of the sequence (in and out)
     int* error;               // [1] 0 = ok
     unsigned long long* stamps; // [3] globaltimer at kernel start and when the first token is known; number of tokens emitted
@@ -237,6 +237,7 @@ struct MegaShared {
     struct MegaShare* share;  // this CTA's work shares, computed once
     int* abort;    // [1] a wait gave up: no more waiting in this CTA
     int* stop;     // [1] the loop ended early (EOS): the producer stops issuing
+    unsigned* landed;  // [1] number of chunks whose bytes have arrived (written by the producer warp's watcher lane)
 };
 
 // The areas sit at offsets the host computed once (mega_layout): an address is the base plus a kernel-argument
@@ -262,6 +263,7 @@ __device__ __forceinline__ MegaShared mega_carve(uint8_t* base, const MegaArgs& 
     s.partial = reinterpret_cast<float*>(base + p.off_outv);
     s.abort = reinterpret_cast<int*>(base + p.off_flags);
     s.stop = s.abort + 1;
+    s.landed = reinterpret_cast<unsigned*>(s.abort + 2);
     s.share = reinterpret_cast<MegaShare*>(base + p.off_share);
     return s;
 }
@@ -295,6 +297,14 @@ __device__ __forceinline__ void mega_fail(const MegaArgs& a, const MegaShared& s
 }
 __device__ __forceinline__ bool mega_aborting(const MegaShared& s) { return *reinterpret_cast<volatile int*>(s.abort) != 0; }
 
+#ifndef MEGA_POLL_NS
+#define MEGA_POLL_NS 100
+#endif
+// Between two attempts of a poll of global memory: every CTA polls the same few cache lines, and requests that
+// arrive back to back would queue up in front of the very stores they are waiting for.
+__device__ __forceinline__ void mega_backoff() {
+    if (MEGA_POLL_NS > 0) __nanosleep(MEGA_POLL_NS);
+}
 // One failed attempt of a polling loop: true when the loop must give up (limit reached, or the kernel is aborting).
 __device__ __forceinline__ bool mega_spin_out(const MegaArgs& a, const MegaShared& s, unsigned& spins, int code) {
     ++spins;
@@ -323,10 +333,25 @@ struct MegaCursor {
     }
 };
 
-__device__ __forceinline__ const uint8_t* mega_acquire(const MegaArgs& a, const MegaShared& s, const MegaCursor& c) {
-    // one lane per warp polls the barrier (many threads polling one shared-memory word serialise); the warp barrier
-    // that follows orders the other lanes' reads of the chunk after the observed completion
-    if ((threadIdx.x & 31) == 0) mega_wait(a, s, s.full + c.slot, c.phase, 3);
+// A consumer does not test the slot's mbarrier itself: that test costs ~280 cycles per call on this part even when the
+// phase completed long ago.  The producer warp's second lane follows the chunks in order, waits on each barrier and
+// publishes the count of landed chunks in a plain shared-memory word (release), which the consumers read (acquire).
+__device__ __forceinline__ unsigned ld_acquire_cta_shared(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_cta_shared(unsigned* p, unsigned v) {
+    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ const uint8_t* mega_acquire(const MegaArgs& a, const MegaShared& s, const MegaCursor& c, unsigned index) {
+    // one lane per warp polls; the warp barrier that follows orders the other lanes' reads of the chunk after it
+    if ((threadIdx.x & 31) == 0 && !mega_aborting(s)) {
+        unsigned spins = 0;
+        while ((int)(ld_acquire_cta_shared(s.landed) - index) <= 0) {
+            if (mega_spin_out(a, s, spins, 3)) break;
+        }
+    }
     __syncwarp();
     return s.slots + (size_t)c.slot * a.plan.slot_bytes;
 }
@@ -378,6 +403,7 @@ __device__ __forceinline__ void mega_read_words(const MegaArgs& a, const MegaSha
                 }
                 if (all) break;
                 if (mega_spin_out(a, s, spins, code)) break;
+                mega_backoff();
             }
         }
 #pragma unroll
@@ -422,6 +448,7 @@ __device__ __forceinline__ void mega_read_sums(const MegaArgs& a, const MegaShar
                 }
                 if (all) break;
                 if (mega_spin_out(a, s, spins, code)) break;
+                mega_backoff();
             }
         }
 #pragma unroll
@@ -443,10 +470,11 @@ __device__ __forceinline__ float mega_block_sum(float v, float* red) {
     v = warp_sum(v);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
     consumer_sync();
-    float t = 0.f;
-#pragma unroll
-    for (int i = 0; i < kMegaConsumerWarps; i++) t += red[i];
-    return t;
+    // sixteen partial sums: four 16-byte loads and a tree of additions instead of a chain of sixteen
+    const float4* r4 = reinterpret_cast<const float4*>(red);
+    const float4 a = r4[0], b = r4[1], c = r4[2], e = r4[3];
+    static_assert(kMegaConsumerWarps == 16, "mega_block_sum reads sixteen partial sums");
+    return (((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w))) + (((c.x + c.y) + (c.z + c.w)) + ((e.x + e.y) + (e.z + e.w)));
 }
 
 // ------------------------------------------------------------------------------------------------ products
@@ -673,7 +701,7 @@ __device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShar
             num = fmaf(s.part[x * HD + tid], f, num);
             den = fmaf(s.red[kMegaConsumerWarps + x], f, den);
         }
-        xa_store(reinterpret_cast<__half*>(s.ctx), tid, den > 0.f ? num / den : 0.f);  // the A operand of the Wo products
+        xa_store(reinterpret_cast<__half*>(s.ctx), tid, den > 0.f ? __fdividef(num, den) : 0.f);  // the A operand of the Wo products
     }
     consumer_sync();
 }
@@ -693,6 +721,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         for (int i = 0; i < p.n_slots; i++) { mbar_init(s.full + i, 1); mbar_init(s.empty + i, kMegaConsumerWarps); }
         *s.abort = 0;
         *s.stop = 0;
+        *s.landed = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int k = tid; k < m.d_model; k += kMegaThreads) s.prev[k] = 0ull;  // the counted sums are zero at launch
@@ -772,6 +801,26 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         }
         return;
     }
+    if (warp == kMegaConsumerWarps + 1) {
+        // ---------------- watcher: follows the chunks in order and counts the ones whose bytes have arrived ----------------
+        if (lane == 0) {
+            auto chunks_of = [](int items, int per_chunk) { return (items + per_chunk - 1) / per_chunk; };
+            const unsigned per_layer = (w.in_group ? chunks_of(w.s1_n, p.s1_ipc) + chunks_of(p.rpb, p.s2_rpc) : 0) + chunks_of(w.h_n, p.s3a_ipc) + chunks_of(w.d_n, p.s3b_rpc);
+            const unsigned total = (unsigned)a.n_steps * chunks_of(w.v_n, p.head_rpc) + (unsigned)(a.n_steps - 1) * L * per_layer;
+            MegaCursor k;
+            for (unsigned i = 0; i < total; i++) {
+                unsigned spins = 0;
+                bool gone = false;
+                while (!mbar_try_wait(s.full + k.slot, k.phase)) {
+                    if (*reinterpret_cast<volatile int*>(s.stop) || mega_spin_out(a, s, spins, 3)) { gone = true; break; }
+                }
+                if (gone) break;
+                st_release_cta_shared(s.landed, i + 1);
+                k.next((unsigned)p.n_slots);
+            }
+        }
+        return;
+    }
 
     // ---------------- consumers ----------------
     if (blockIdx.x == 0 && tid == 0) {
@@ -791,12 +840,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         if (a.trace && (int)blockIdx.x == a.trace_cta && tid == 0 && step == a.n_steps - 1) a.trace[n_stamp++] = clock64();
     };
     MegaCursor c;        // ring position, advances in lock step with the producer's
+    unsigned n_chunk = 0;  // chunks consumed so far
     int pos = a.pos0;    // visible tokens
     uint32_t tok = 0;
     int emitted = 0;
     int par = 0;         // which half of s.partial the next chunk's sums go to
     constexpr int half = HD / 2;
     const int d = m.d_model;
+    const float inv_d = 1.0f / (float)d;
     const float* fin_gain = a.norms + (size_t)(2 * L) * d;
     unsigned long long* my_qkv = a.qkv_words + (size_t)w.kvh * 2 * p.group_items;
     __half* xa_h = reinterpret_cast<__half*>(s.xa);
@@ -820,7 +871,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         n_pend = 0;
     };
     auto chunk_products = [&](int rows, int n_kb, const uint8_t* xa, bool defer) {
-        const uint8_t* ch = mega_acquire(a, s, c);
+        const uint8_t* ch = mega_acquire(a, s, c, n_chunk++);
         FINE();
         float* partial = s.partial + par * kMegaChunkRows;
         par ^= 1;
@@ -861,7 +912,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     FINE();
                     release_pending();  // the W2 chunk of the previous layer
                     ss = mega_block_sum(ss, s.red);
-                    inv = 1.0f / sqrtf(ss / (float)d + m.eps);
+                    inv = rsqrtf(ss * inv_d + m.eps);  // (a correctly rounded division and square root cost ~200 cycles here)
                     FINE();
                     stamp(step);
                     // q/k/v row pairs of this CTA, RoPE, words for the CTAs that share the KV head, KV-cache append.
@@ -907,6 +958,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                                     v = ld_words2(my_qkv + 2 * item);
                                     if ((unsigned)(v.x >> 32) == seq && (unsigned)(v.y >> 32) == seq) break;
                                     if (mega_spin_out(a, s, spins, 6)) break;
+                                    mega_backoff();
                                 }
                             }
                             const float v0 = __uint_as_float((unsigned)v.x), v1 = __uint_as_float((unsigned)v.y);
@@ -945,7 +997,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     // The arg-max candidate words are used once per token; between two uses a whole model's worth of
                     // weights streams through L2.  Reading them once per layer keeps their lines resident, so that the
                     // token exchange does not start with a round trip to memory.
-                    if (tid < p.n_cta) (void)ld_words2(a.cand_words + 4 * (size_t)tid);
+                    if (tid < p.n_cta) { unsigned long long keep; asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(keep) : "l"(a.cand_words + tid) : "memory"); }
                     const float* gain = a.norms + (size_t)(2 * l + 1) * d;
                     float ss = 0.f;
                     FINE();
@@ -953,7 +1005,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     FINE();
                     release_pending();  // the Wo chunk (CTAs outside the head groups: the W2 chunk of the previous layer)
                     ss = mega_block_sum(ss, s.red);
-                    inv = 1.0f / sqrtf(ss / (float)d + m.eps);
+                    inv = rsqrtf(ss * inv_d + m.eps);  // (a correctly rounded division and square root cost ~200 cycles here)
                 }
                 stamp(step);
                 // (gate, up) row pairs of this CTA's hidden units, SiLU(gate) * up.  act_words is re-written one layer later,
@@ -966,7 +1018,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                         const float g = mega_take_sum(sums, lg_parts, 2 * j) * inv;
                         const float u = mega_take_sum(sums, lg_parts, 2 * j + 1) * inv;
                         // silu(g) = g * sigmoid(g) = 0.5 g (1 + tanh(g / 2))
-                        st_word(a.act_words + w.h_begin + j0 + j, tagged(g / (1.0f + __expf(-g)) * u, seq));
+                        st_word(a.act_words + w.h_begin + j0 + j, tagged(__fdividef(g, 1.0f + __expf(-g)) * u, seq));
                     }
                 }
                 stamp(step);
@@ -1025,9 +1077,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
 #ifdef MEGA_FINE_TRACE
         if (a.trace && tid == 0 && step == a.n_steps - 1) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.trace[600 + blockIdx.x] = (long long)t; }
 #endif
-        // CTA-wide best (larger value first, then smaller index), published as two tagged words
+        // CTA-wide best (larger value first, then smaller index), published as one word per CTA:
+        // [ordered logit bits : 32][0xffffff - index : 24][tag : 8].  The tag is the same in every word of a step, so the
+        // largest word is the best candidate; 148 consecutive words are ten cache lines for every reader.
+        const unsigned long long tag8 = (unsigned long long)(step % 255 + 1);
         {
-            unsigned long long k = best_i != 0x7fffffff ? pack_best(best_v, best_i) : 0ull;
+            unsigned long long k = best_i != 0x7fffffff ? ((unsigned long long)ordered_bits(best_v) << 32) | ((unsigned long long)(0xffffffu - (unsigned)best_i) << 8) : 0ull;
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) k = max(k, __shfl_xor_sync(0xffffffffu, k, off));
             if (lane == 0) s.key[warp] = k;
@@ -1037,23 +1092,19 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             unsigned long long k = 0ull;
 #pragma unroll
             for (int x = 0; x < kMegaConsumerWarps; x++) k = max(k, s.key[x]);
-            const unsigned tag = (unsigned)step + 1u;
-            unsigned long long* mine = a.cand_words + 4 * (size_t)blockIdx.x;
-            st_word(mine, ((unsigned long long)tag << 32) | (k >> 32));
-            st_word(mine + 1, ((unsigned long long)tag << 32) | (k & 0xffffffffull));
+            st_word(a.cand_words + blockIdx.x, k | tag8);
         }
         stamp(step);
         {
             unsigned long long k = 0ull;
             if (tid < p.n_cta) {
-                const unsigned tag = (unsigned)step + 1u;
-                ulonglong2 v = make_ulonglong2(0, 0);
                 unsigned spins = 0;
                 if (!mega_aborting(s)) {
                     while (true) {
-                        v = ld_words2(a.cand_words + 4 * (size_t)tid);
-                        if ((unsigned)(v.x >> 32) == tag && (unsigned)(v.y >> 32) == tag) break;
+                        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(k) : "l"(a.cand_words + tid) : "memory");
+                        if ((k & 0xffull) == tag8) break;
                         if (mega_spin_out(a, s, spins, 10)) break;
+                        mega_backoff();
                     }
                 }
 #ifndef MEGA_NO_FENCE
@@ -1061,7 +1112,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 // candidate words it saw; the writers' side of the pair is the fence at the start of the head
                 __threadfence();
 #endif
-                k = ((v.x & 0xffffffffull) << 32) | (v.y & 0xffffffffull);
             }
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) k = max(k, __shfl_xor_sync(0xffffffffu, k, off));
@@ -1072,7 +1122,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             k = 0ull;
 #pragma unroll
             for (int x = 0; x < kMegaConsumerWarps; x++) k = max(k, s.key[x]);
-            tok = min(0xffffffffu - (uint32_t)(k & 0xffffffffull), (uint32_t)(m.vocab - 1));  // in range even if every logit was NaN
+            tok = min(0xffffffu - (uint32_t)((k >> 8) & 0xffffffull), (uint32_t)(m.vocab - 1));  // in range even if every logit was NaN
         }
         release_pending();  // the last head chunks
         stamp(step);

@@ -91,8 +91,21 @@ int32_t lm_head_argmax_static(const void* d_lm_head_f16, int32_t vocab, int32_t 
         os << "lm_head_argmax_static: d_model must be a multiple of 8 in [8, " << kStaticHeadMaxDModel << "] and vocab >= 1";
         return esp::fail(ESP_CUDA_ERR_INVALID_ARGUMENT, os.str());
     }
+    // the kernel reads the matrix with 16-byte loads and the vectors as 4-byte words: a view that starts elsewhere would
+    // fault on the device, so it is refused here
+    if (reinterpret_cast<uintptr_t>(d_lm_head_f16) % 16 != 0)
+        return esp::fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "lm_head_argmax_static: d_lm_head_f16 must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(d_hidden) % 4 != 0 || reinterpret_cast<uintptr_t>(d_norm_gain) % 4 != 0 || reinterpret_cast<uintptr_t>(d_tokens) % 4 != 0)
+        return esp::fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "lm_head_argmax_static: d_hidden, d_norm_gain and d_tokens must be 4-byte aligned");
     if (force_failure_enabled()) return esp::fail(ESP_CUDA_ERR_FORCED_FAILURE, "forced failure is enabled");
-    ESP_CUDA_TRY(cudaSetDevice(device));
+    // the call runs on `device` and leaves the caller's current device as it found it
+    struct DeviceGuard {
+        int prev = -1;
+        ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+    } guard;
+    ESP_CUDA_TRY(cudaGetDevice(&guard.prev));
+    if (guard.prev == device) guard.prev = -1;
+    else ESP_CUDA_TRY(cudaSetDevice(device));
     unsigned char* base = nullptr;
     int32_t rc = static_head_address(device, &base);
     if (rc) return rc;

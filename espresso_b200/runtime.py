@@ -375,6 +375,10 @@ class DecodeEngine:
         _check(self._lib.esp_cuda_token_times(self._h, out.ctypes.data_as(C.POINTER(C.c_uint64)), out.size, C.byref(n)))
         return out[: n.value].copy()
 
+    def set_wait_limit(self, spins: int) -> None:
+        """Test hook: every device-side wait of the persistent decode kernel polls at most ``spins`` times (0 = default)."""
+        _check(self._lib.esp_cuda_set_wait_limit(self._h, spins))
+
     def set_debug_layer(self, layer: int) -> None:
         _check(self._lib.esp_cuda_set_debug_layer(self._h, layer))
 

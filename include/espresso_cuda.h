@@ -292,7 +292,9 @@ ESP_CUDA_API int32_t esp_cuda_gemm_tc_bench(int32_t type, const void* weights, i
  * this point.  All calls on a device share the array and it keeps the previous call's contents: the call resets
  * what it needs, and calls whose kernels overlap on the GPU race - serialise them.  The first call on a device
  * looks up the array's address and should be made before any stream capture begins.  The call itself performs
- * no cudaMalloc, cudaFree or other allocating routine. */
+ * no cudaMalloc, cudaFree or other allocating routine.  d_lm_head_f16 must be 16-byte aligned and the other pointers
+ * 4-byte aligned (a view that starts elsewhere is refused with ESP_CUDA_ERR_INVALID_ARGUMENT); the call runs on
+ * `device` and leaves the caller's current device unchanged. */
 #define ESP_CUDA_STATIC_HEAD_MAX_ROWS 64
 ESP_CUDA_API int32_t esp_cuda_lm_head_argmax_static(const void* d_lm_head_f16, int32_t vocab, int32_t d_model,
                                                     const float* d_hidden, int32_t rows, const float* d_norm_gain,

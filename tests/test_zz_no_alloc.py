@@ -5,7 +5,8 @@ has then already run every other test).
 device-memory budget, someone else's arena, a loop that must not stall the device); its working memory is an
 array built into the library.  The test drives it through the C ABI with caller-owned device buffers (held in
 torch tensors here) and checks the tokens against the logits of the existing ``esp_cuda_gemv_bench`` entry
-point, which allocates its own buffers, on two calls in a row that share the built-in array."""
+point, which allocates its own buffers, and against a numpy fp32 product, on two calls in a row that share the
+built-in array."""
 import numpy as np
 import pytest
 
@@ -13,7 +14,9 @@ pytestmark = pytest.mark.gpu
 
 
 def _reference_tokens(rt, lm_head, hidden, gain, eps):
-    toks, margins = [], []
+    """Tokens and top-2 margins from the allocating entry point, and tokens from a numpy fp32 product."""
+    toks, margins, np_toks = [], [], []
+    w32 = lm_head.astype(np.float32)
     for h in hidden:
         x = h.astype(np.float32)
         if gain is not None:
@@ -22,7 +25,10 @@ def _reference_tokens(rt, lm_head, hidden, gain, eps):
         order = np.argsort(-logits, kind="stable")
         toks.append(int(np.argmax(logits)))
         margins.append(float(logits[order[0]] - logits[order[1]]))
-    return toks, margins
+        host = w32 @ x
+        assert np.abs(host - logits).max() <= 1e-3  # the allocating entry point itself agrees with the host product
+        np_toks.append(int(np.argmax(host)))
+    return toks, margins, np_toks
 
 
 def test_static_lm_head_matches_allocating_entry_point_on_two_calls():
@@ -32,14 +38,27 @@ def test_static_lm_head_matches_allocating_entry_point_on_two_calls():
     rt.load_library()
     dev = torch.device("cuda", 0)
     rng = np.random.default_rng(2024)
-    vocab, d = 5003, 768  # odd vocab: the last work item holds a single row
+    _two_calls(rt, torch, dev, rng, vocab=5003, d=768, calls=((7, True), (3, False)))  # odd vocab: the last work item holds a single row
+
+
+def test_static_lm_head_at_its_row_limit_and_with_a_ragged_width():
+    """Every slot of the built-in array (rows = the maximum) and a d_model that is not a multiple of the 256-element
+    slices of the dot products."""
+    import torch
+    from espresso_b200 import runtime as rt
+
+    rt.load_library()
+    _two_calls(rt, torch, torch.device("cuda", 0), np.random.default_rng(7), vocab=1201, d=72, calls=((rt.STATIC_HEAD_MAX_ROWS, True), (5, False)))
+
+
+def _two_calls(rt, torch, dev, rng, vocab, d, calls):
     lm_head = (rng.standard_normal((vocab, d)) * 0.02).astype(np.float16)
     gain = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32)
     d_w = torch.from_numpy(lm_head).to(dev)
     d_gain = torch.from_numpy(gain).to(dev)
-    d_tok = torch.zeros(rt.STATIC_HEAD_MAX_ROWS, dtype=torch.int32, device=dev)
+    d_tok = torch.zeros(rt.STATIC_HEAD_MAX_ROWS + 4, dtype=torch.int32, device=dev)
     # two calls in a row with different row counts and inputs; the second must not see the first's leftovers
-    for call, (rows, use_gain) in enumerate(((7, True), (3, False))):
+    for call, (rows, use_gain) in enumerate(calls):
         hidden = rng.standard_normal((rows, d)).astype(np.float32)
         d_h = torch.from_numpy(hidden).to(dev)
         d_tok.fill_(-1)
@@ -48,10 +67,11 @@ def test_static_lm_head_matches_allocating_entry_point_on_two_calls():
                                  d_tok.data_ptr(), stream=0, device=0)
         torch.cuda.synchronize()
         got = d_tok.cpu().numpy()[:rows].astype(np.int64)
-        ref, margins = _reference_tokens(rt, lm_head, hidden, gain if use_gain else None, 1e-5)
+        ref, margins, host = _reference_tokens(rt, lm_head, hidden, gain if use_gain else None, 1e-5)
         for r in range(rows):
             # identical tokens wherever the top-2 gap exceeds the rounding tolerance of the two summation orders
             assert got[r] == ref[r] or margins[r] <= 2e-4, f"call {call} row {r}: {got[r]} vs {ref[r]} (margin {margins[r]:.2e})"
+            assert got[r] == host[r] or margins[r] <= 2e-4, f"call {call} row {r}: {got[r]} vs numpy {host[r]}"
         assert (d_tok.cpu().numpy()[rows:] == -1).all()  # nothing beyond `rows` is written
 
 
@@ -68,3 +88,7 @@ def test_static_lm_head_rejects_sizes_beyond_its_fixed_array():
     assert ei.value.status == rt.ERR_INVALID_ARGUMENT and "fixed array" in ei.value.message
     with pytest.raises(rt.RealModelInferenceError):
         rt.lm_head_argmax_static(w.data_ptr(), 16, 8200, h.data_ptr(), 1, None, 1e-5, t.data_ptr())
+    # a matrix view that does not start on a 16-byte boundary is refused on the host instead of faulting on the device
+    with pytest.raises(rt.RealModelInferenceError) as ea:
+        rt.lm_head_argmax_static(w.data_ptr() + 2, 15, 64, h.data_ptr(), 1, None, 1e-5, t.data_ptr())
+    assert ea.value.status == rt.ERR_INVALID_ARGUMENT and "aligned" in ea.value.message
