@@ -171,6 +171,72 @@ int32_t esp_cuda_generate_batch(esp_cuda_engine* engine, const uint32_t* prompts
     return engine->impl.generate_batch(prompts, n_seq, n_prompt, max_tokens, out_tokens, n_out, result);
 }
 
+// Step-by-step generation with the caller's callback invoked inline after every token, as the reference's loop does
+// with onStep (Engine.swift:6393-6405): prefill, select the first token, then one decode step per token.  Limits and
+// stop rules as in generate (Llama: the EOS token is emitted, then the loop stops, :6385-6388; GPT-2: 50256 stops
+// without being emitted, :4918-4922).
+int32_t esp_cuda_generate_steps(esp_cuda_engine* engine, const uint32_t* prompt, int32_t n_prompt, int32_t max_tokens,
+                                esp_cuda_step_callback on_step, void* user, uint32_t* out_tokens, int32_t* n_out,
+                                esp_cuda_generation_result* result) {
+    ESP_GUARD(engine);
+    if (!prompt || !out_tokens || !n_out) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "generate_steps: null argument");
+    esp::Engine& e = engine->impl;
+    const esp_cuda_config& c = e.config();
+    if (n_prompt <= 0) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "Prompt tokens must not be empty");
+    if (max_tokens < 0) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "maxTokens must be >= 0");
+    if (n_prompt >= c.max_seq) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "Prompt token count exceeds model context");
+    const int eff = std::min(max_tokens, c.max_seq - n_prompt);
+    if (result) { *result = esp_cuda_generation_result{}; result->prompt_tokens = n_prompt; }
+    *n_out = 0;
+    if (eff == 0) return ESP_CUDA_OK;
+    auto now = [] { return std::chrono::steady_clock::now(); };
+    auto ms = [](auto a, auto b) { return std::chrono::duration<double, std::milli>(b - a).count(); };
+    auto t0 = now();
+    int32_t rc;
+    if ((rc = e.prefill(prompt, n_prompt))) return rc;
+    auto t_prefill = now();
+    auto t_last = t_prefill;
+    std::vector<float> latencies;
+    int gen = 0;
+    bool hit_eos = false;
+    double first_ms = 0.0;
+    uint32_t tok = 0;
+    if ((rc = e.select_greedy(&tok))) return rc;
+    while (true) {
+        if (c.architecture == ESP_CUDA_ARCH_GPT2 && tok == 50256u) { hit_eos = true; break; }
+        auto t = now();
+        const double lat = ms(t_last, t);
+        t_last = t;
+        if (gen == 0) first_ms = lat;
+        out_tokens[gen] = tok;
+        latencies.push_back((float)lat);
+        if (on_step) on_step(user, tok, gen, lat);
+        gen++;
+        if (c.architecture != ESP_CUDA_ARCH_GPT2 && c.eos_token >= 0 && tok == (uint32_t)c.eos_token) { hit_eos = true; break; }
+        if (gen >= eff || n_prompt + gen >= c.max_seq) break;
+        uint32_t next = 0;
+        if ((rc = e.decode_step(tok, &next))) return rc;
+        tok = next;
+    }
+    auto t_end = now();
+    *n_out = gen;
+    e.set_token_latencies(latencies);
+    if (result) {
+        result->generated_tokens = gen;
+        result->prefill_ms = ms(t0, t_prefill);
+        result->first_token_latency_ms = first_ms;
+        result->total_decode_ms = ms(t_prefill, t_end);
+        result->tokens_per_second = gen / std::max(result->total_decode_ms / 1000.0, 1e-9);
+        result->stopped_on_eos = hit_eos ? 1 : 0;
+    }
+    return ESP_CUDA_OK;
+}
+
+int32_t esp_cuda_token_latencies(esp_cuda_engine* engine, float* out_ms, int32_t capacity, int32_t* n) {
+    ESP_GUARD(engine);
+    return engine->impl.token_latencies(out_ms, capacity, n);
+}
+
 int32_t esp_cuda_decode(esp_cuda_engine* engine, int32_t n_seq, int32_t count, uint32_t* out_tokens, int32_t* n_out,
                         float* device_ms) {
     ESP_GUARD(engine);

@@ -332,6 +332,7 @@ Engine::~Engine() {
         nccl_api().CommDestroy(static_cast<ncclComm_t>(nccl_comm_));
     }
     for (auto e : prof_events_) cudaEventDestroy(e);
+    for (auto e : step_events_) cudaEventDestroy(e);
     if (ev_begin_) cudaEventDestroy(ev_begin_);
     if (ev_end_) cudaEventDestroy(ev_end_);
     for (void* p : owned_) cudaFree(p);
@@ -1172,14 +1173,19 @@ int32_t Engine::decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, 
     if (!ev_begin_) { ESP_CUDA_TRY(cudaEventCreate(&ev_begin_)); ESP_CUDA_TRY(cudaEventCreate(&ev_end_)); }
     auto t0 = std::chrono::steady_clock::now();
     ESP_CUDA_TRY(cudaEventRecord(ev_begin_, stream_));
+    while ((int)step_events_.size() < max_lim) { cudaEvent_t ev; ESP_CUDA_TRY(cudaEventCreate(&ev)); step_events_.push_back(ev); }
     if ((rc = submit(n_seq, STEP_HEAD | STEP_FEEDBACK))) return rc;
+    ESP_CUDA_TRY(cudaEventRecord(step_events_[0], stream_));  // one event per token: the per-token latencies
     if (first_token_ms) {
         ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
         *first_token_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     }
     const bool may_stop_early = m_.arch == ARCH_GPT2 || m_.eos_token >= 0;
+    int steps_submitted = 1;
     for (int i = 1; i < max_lim; i++) {
         if ((rc = submit(n_seq, STEP_FORWARD | STEP_HEAD | STEP_FEEDBACK))) return rc;
+        ESP_CUDA_TRY(cudaEventRecord(step_events_[i], stream_));
+        steps_submitted = i + 1;
         if (may_stop_early && (i % 32) == 0) {
             ESP_CUDA_TRY(cudaMemcpyAsync(h_rows_block_ + 3 * max_rows_, rs_.active, sizeof(int) * n_seq, cudaMemcpyDeviceToHost, stream_));
             ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
@@ -1199,6 +1205,17 @@ int32_t Engine::decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, 
         if (herr) return fail(ESP_CUDA_ERR_TIMEOUT, herr == 8 ? "peer all-reduce gave up waiting for another rank" : "tensor-core GEMM gave up waiting on a barrier");
     }
     if (device_ms) ESP_CUDA_TRY(cudaEventElapsedTime(device_ms, ev_begin_, ev_end_));
+    latencies_ms_.clear();
+    {
+        const int n0 = std::min(std::min(h_rows_block_[4 * max_rows_], lim[0]), steps_submitted);
+        cudaEvent_t prev = ev_begin_;
+        for (int i = 0; i < n0; i++) {
+            float t = 0.f;
+            ESP_CUDA_TRY(cudaEventElapsedTime(&t, prev, step_events_[i]));
+            latencies_ms_.push_back(t);
+            prev = step_events_[i];
+        }
+    }
     for (int s = 0; s < n_seq; s++) {
         int n = std::min(h_rows_block_[4 * max_rows_ + s], lim[s]);
         if (n_out) n_out[s] = n;
@@ -1794,6 +1811,13 @@ int32_t Engine::run_mega(int n_steps, int* emitted, float* device_ms, double* fi
     token_times_n_ = a.token_times ? n : 0;
     if (device_ms) ESP_CUDA_TRY(cudaEventElapsedTime(device_ms, ev_begin_, ev_end_));
     if (first_token_ms) *first_token_ms = (double)(h_mega_ctl_[4] - h_mega_ctl_[3]) / 1e6;
+    latencies_ms_.clear();
+    if (a.token_times) {
+        std::vector<unsigned long long> tt((size_t)n);
+        ESP_CUDA_TRY(cudaMemcpy(tt.data(), d_token_times_, sizeof(unsigned long long) * n, cudaMemcpyDeviceToHost));
+        unsigned long long prev = h_mega_ctl_[3];  // kernel start
+        for (int i = 0; i < n; i++) { latencies_ms_.push_back((float)((double)(tt[i] - prev) / 1e6)); prev = tt[i]; }
+    }
     h_visible_[0] += n - 1;
     return ESP_CUDA_OK;
 }
@@ -1825,6 +1849,15 @@ int32_t Engine::token_times(unsigned long long* out_ns, int32_t capacity, int32_
     ESP_CUDA_TRY(cudaSetDevice(cfg_.device));
     ESP_CUDA_TRY(cudaMemcpy(out_ns, d_token_times_, sizeof(unsigned long long) * token_times_n_, cudaMemcpyDeviceToHost));
     *n = token_times_n_;
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::token_latencies(float* out_ms, int32_t capacity, int32_t* n) {
+    if (!out_ms || !n) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "token_latencies: null argument");
+    *n = 0;
+    if (capacity < (int32_t)latencies_ms_.size()) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "token_latencies: capacity too small");
+    std::copy(latencies_ms_.begin(), latencies_ms_.end(), out_ms);
+    *n = (int32_t)latencies_ms_.size();
     return ESP_CUDA_OK;
 }
 

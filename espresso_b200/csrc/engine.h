@@ -70,6 +70,8 @@ public:
                         float* device_ms, double* first_token_ms);
     int32_t stage_trace(int32_t cta, long long* out, int32_t capacity, int32_t* n);
     int32_t token_times(unsigned long long* out_ns, int32_t capacity, int32_t* n);
+    int32_t token_latencies(float* out_ms, int32_t capacity, int32_t* n);
+    void set_token_latencies(const std::vector<float>& v) { latencies_ms_ = v; }
     int32_t set_debug_layer(int32_t layer);
     int32_t debug_dump(int32_t stage, float* out, int32_t capacity);
     int32_t get_timings(esp_cuda_timings* out);
@@ -172,6 +174,8 @@ private:
     long long* d_mega_trace_ = nullptr;
     unsigned long long* d_token_times_ = nullptr;  // [max_seq] emission time of every token of the last persistent loop
     int token_times_n_ = 0;
+    std::vector<float> latencies_ms_;              // per-token latencies of sequence 0, most recent generation
+    std::vector<cudaEvent_t> step_events_;         // one per step of a decode loop of the per-stage kernels
     int mega_trace_cta_ = 0;
     esp_cuda_timings timings_{};
     int launches_last_step_ = 0;

@@ -149,7 +149,10 @@ int32_t GgufFile::open(const char* path) {
             return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "truncated or malformed GGUF metadata near key '" + key + "'");
         kv[key] = v;
     }
-    if (const GgufValue* a = find("general.alignment")) alignment = (uint64_t)a->i;
+    if (const GgufValue* a = find("general.alignment")) {
+        if (a->i <= 0 || a->i > (1ll << 30)) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF alignment out of range");
+        alignment = (uint64_t)a->i;
+    }
     if (alignment == 0 || (alignment & (alignment - 1))) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF alignment is not a power of two");
     tensors.resize((size_t)n_tensors);
     for (auto& t : tensors) {
@@ -160,14 +163,20 @@ int32_t GgufFile::open(const char* path) {
         if (!take(&t.type, 4) || !take(&t.offset, 8)) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "truncated GGUF tensor directory");
         uint64_t be = 0, bb = 0;
         if (ggml_block(t.type, &be, &bb)) {
-            const uint64_t n = t.dims[0] * t.dims[1] * t.dims[2] * t.dims[3];
+            // an untrusted file: the element count and the byte size are computed with overflow checks
+            uint64_t n = 1;
+            bool wrapped = false;
+            for (int d = 0; d < 4; d++) wrapped = wrapped || __builtin_mul_overflow(n, t.dims[d], &n);
+            if (wrapped) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF tensor " + t.name + ": dimensions overflow");
             if (t.dims[0] % be) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF tensor " + t.name + ": row length is not a multiple of the block size");
-            t.nbytes = n / be * bb;
+            if (__builtin_mul_overflow(n / be, bb, &t.nbytes)) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF tensor " + t.name + ": size overflows");
         }  // other GGML types are listed but cannot be uploaded
     }
     data_start_ = (cur_ + alignment - 1) / alignment * alignment;
+    if (data_start_ > size_) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF file ends before its tensor data");
     for (auto& t : tensors)
-        if (t.nbytes && (t.offset % alignment || data_start_ + t.offset + t.nbytes > size_))
+        // written so that neither sum can wrap: offset and size are each compared with what is left of the file
+        if (t.nbytes && (t.offset % alignment || t.offset > size_ - data_start_ || t.nbytes > size_ - data_start_ - t.offset))
             return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF tensor " + t.name + " lies outside the file or is misaligned");
     return ESP_CUDA_OK;
 }
@@ -191,6 +200,10 @@ static bool gguf_rows_interleaved(const std::string& arch_name) {
     return a == "llama" || a == "llama2" || a == "llama3" || a == "mistral";
 }
 
+// Metadata integers are 64-bit in the file and 32-bit in the config: a value that does not fit is an invalid file,
+// not something to truncate silently.
+static bool fits_i32(long long v) { return v >= -2147483647LL - 1 && v <= 2147483647LL; }
+
 static int32_t gguf_config(const GgufFile& f, esp_cuda_config* c, std::string* arch_name, int32_t* tied) {
     const GgufValue* an = f.find("general.architecture");
     if (!an || an->type != GGUF_STRING) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF metadata lacks general.architecture");
@@ -201,6 +214,13 @@ static int32_t gguf_config(const GgufFile& f, esp_cuda_config* c, std::string* a
     auto need = [&](const char* key, int32_t* dst) -> int32_t {
         const GgufValue* v = f.find(p + key);
         if (!v) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF metadata lacks " + p + key);
+        if (!fits_i32((long long)v->i)) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF metadata value out of range: " + p + key);
+        *dst = (int32_t)v->i;
+        return ESP_CUDA_OK;
+    };
+    auto opt = [&](const GgufValue* v, int32_t fallback, int32_t* dst) -> int32_t {
+        if (!v) { *dst = fallback; return ESP_CUDA_OK; }
+        if (!fits_i32((long long)v->i)) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF metadata value out of range");
         *dst = (int32_t)v->i;
         return ESP_CUDA_OK;
     };
@@ -212,19 +232,24 @@ static int32_t gguf_config(const GgufFile& f, esp_cuda_config* c, std::string* a
     if ((rc = need("embedding_length", &c->d_model))) return rc;
     if ((rc = need("context_length", &c->max_seq))) return rc;
     const GgufValue* v;
-    c->n_kv_head = (v = f.find(p + "attention.head_count_kv")) ? (int32_t)v->i : c->n_head;
+    if ((rc = opt(f.find(p + "attention.head_count_kv"), c->n_head, &c->n_kv_head))) return rc;
     if (c->n_head <= 0) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF head count must be positive");
-    c->head_dim = (v = f.find(p + "attention.key_length")) ? (int32_t)v->i : c->d_model / c->n_head;
-    if ((v = f.find(p + "feed_forward_length"))) c->hidden_dim = (int32_t)v->i;
+    if ((rc = opt(f.find(p + "attention.key_length"), c->d_model / c->n_head, &c->head_dim))) return rc;
+    if ((v = f.find(p + "feed_forward_length"))) { if ((rc = opt(v, 0, &c->hidden_dim))) return rc; }
     else if (arch == ESP_CUDA_ARCH_GPT2) c->hidden_dim = 4 * c->d_model;
     else return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF metadata lacks " + p + "feed_forward_length");
-    if ((v = f.find("tokenizer.ggml.tokens")) && v->type == GGUF_ARRAY) c->vocab = (int32_t)v->count;
-    else if ((v = f.find(p + "vocab_size"))) c->vocab = (int32_t)v->i;
-    else if (const GgufTensor* te = f.tensor("token_embd.weight")) c->vocab = (int32_t)te->dims[1];
+    if ((v = f.find("tokenizer.ggml.tokens")) && v->type == GGUF_ARRAY) {
+        if (v->count > 2147483647ull) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF vocabulary size out of range");
+        c->vocab = (int32_t)v->count;
+    } else if ((v = f.find(p + "vocab_size"))) { if ((rc = opt(v, 0, &c->vocab))) return rc; }
+    else if (const GgufTensor* te = f.tensor("token_embd.weight")) {
+        if (te->dims[1] > 2147483647ull) return esp::fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "GGUF vocabulary size out of range");
+        c->vocab = (int32_t)te->dims[1];
+    }
     const char* eps_key = arch == ESP_CUDA_ARCH_GPT2 ? "attention.layer_norm_epsilon" : "attention.layer_norm_rms_epsilon";
     c->norm_eps = (v = f.find(p + eps_key)) ? (float)v->f : 1e-5f;
     c->rope_theta = (v = f.find(p + "rope.freq_base")) ? (float)v->f : 10000.0f;  // GGUFModelLoader.swift:307-308
-    c->eos_token = (v = f.find("tokenizer.ggml.eos_token_id")) ? (int32_t)v->i : -1;
+    if ((rc = opt(f.find("tokenizer.ggml.eos_token_id"), -1, &c->eos_token))) return rc;
     c->max_batch = 1;
     c->tp_size = 1;
     *tied = f.tensor("output.weight") ? 0 : 1;

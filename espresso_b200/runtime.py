@@ -107,6 +107,8 @@ SIGNATURES = {
     "esp_cuda_last_error_string": (C.c_char_p, []),
     "esp_cuda_set_force_failure": (None, [C.c_int32]),
     "esp_cuda_set_wait_limit": (C.c_int32, [_vp, C.c_uint32]),
+    "esp_cuda_generate_steps": (C.c_int32, [_vp, _u32p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, _u32p, _i32p, C.POINTER(EspCudaGenerationResult)]),
+    "esp_cuda_token_latencies": (C.c_int32, [_vp, _f32p, C.c_int32, _i32p]),
     "esp_cuda_live_engine_count": (C.c_int32, []),
     "esp_cuda_version": (C.c_char_p, []),
     "esp_cuda_dequantize": (C.c_int32, [C.c_int32, _vp, C.c_int64, _f32p, C.c_int32]),
@@ -158,6 +160,7 @@ class GenerationResult:
     acceptedFutureTokensPerPass: Optional[float] = None
     speculativePasses: int = 0
     stoppedOnEOS: bool = False
+    tokenLatenciesMs: Optional[np.ndarray] = None
 
 
 def make_c_config(cfg: MultiModelConfig, max_batch: int = 1, device: int = 0, flags: int = 0, tp_rank: int = 0,
@@ -314,14 +317,30 @@ class DecodeEngine:
             prefillMs=res.prefill_ms, firstTokenLatencyMs=res.first_token_latency_ms, totalDecodeMs=res.total_decode_ms,
             committedExactTokensPerPass=res.committed_exact_tokens_per_pass if two_token else None,
             acceptedFutureTokensPerPass=res.accepted_future_tokens_per_pass if two_token else None,
-            speculativePasses=res.speculative_passes, stoppedOnEOS=bool(res.stopped_on_eos))
+            speculativePasses=res.speculative_passes, stoppedOnEOS=bool(res.stopped_on_eos),
+            tokenLatenciesMs=None if two_token else self.token_latencies_ms())
 
-    def generate(self, prompt_tokens: Sequence[int], max_tokens: int = 128) -> GenerationResult:
+    def token_latencies_ms(self) -> np.ndarray:
+        """``GenerationResult.tokenLatenciesMs`` of the most recent generation of sequence 0 (see ``esp_cuda_token_latencies``)."""
+        out = np.zeros(self.config.maxSeq + 1, np.float32)
+        n = C.c_int32()
+        _check(self._lib.esp_cuda_token_latencies(self._h, out.ctypes.data_as(_f32p), out.size, C.byref(n)))
+        return out[: n.value].copy()
+
+    def generate(self, prompt_tokens: Sequence[int], max_tokens: int = 128, on_step=None) -> GenerationResult:
+        """Greedy generation.  With ``on_step(token, index, latency_ms)`` the loop runs token by token and calls it inline
+        after every token (the reference's ``onStep``, Engine.swift:6393-6405); without it the loop is device-driven."""
         arr, p = _u32(prompt_tokens)
         out = np.zeros(max(max_tokens, 1), np.uint32)
         n = C.c_int32()
         res = EspCudaGenerationResult()
-        _check(self._lib.esp_cuda_generate(self._h, p, arr.size, max_tokens, out.ctypes.data_as(_u32p), C.byref(n), C.byref(res)))
+        if on_step is None:
+            _check(self._lib.esp_cuda_generate(self._h, p, arr.size, max_tokens, out.ctypes.data_as(_u32p), C.byref(n), C.byref(res)))
+        else:
+            cb_type = C.CFUNCTYPE(None, C.c_void_p, C.c_uint32, C.c_int32, C.c_double)
+            cb = cb_type(lambda _user, token, index, latency: on_step(int(token), int(index), float(latency)))
+            _check(self._lib.esp_cuda_generate_steps(self._h, p, arr.size, max_tokens, C.cast(cb, C.c_void_p), None,
+                                                     out.ctypes.data_as(_u32p), C.byref(n), C.byref(res)))
         return self._result(res, out[: n.value].copy(), arr)
 
     def generate_text(self, tokenizer, prompt: str, max_tokens: int = 128) -> tuple[str, GenerationResult]:

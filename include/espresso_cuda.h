@@ -217,6 +217,19 @@ ESP_CUDA_API int32_t esp_cuda_generate(esp_cuda_engine* engine, const uint32_t* 
 ESP_CUDA_API int32_t esp_cuda_generate_batch(esp_cuda_engine* engine, const uint32_t* prompts, int32_t n_seq,
                                              int32_t n_prompt, int32_t max_tokens, uint32_t* out_tokens,
                                              int32_t* n_out, esp_cuda_generation_result* result);
+/* The same generation, token by token, with `on_step(user, token, index, latency_ms)` called inline on the caller's
+ * thread as each token becomes known: the reference's onStep callback (Engine.swift:6393-6405, GenerationStep
+ * :57-83).  on_step may be NULL.  One host round trip per token, like the reference's loop. */
+typedef void (*esp_cuda_step_callback)(void* user, uint32_t token, int32_t index, double latency_ms);
+ESP_CUDA_API int32_t esp_cuda_generate_steps(esp_cuda_engine* engine, const uint32_t* prompt, int32_t n_prompt,
+                                             int32_t max_tokens, esp_cuda_step_callback on_step, void* user,
+                                             uint32_t* out_tokens, int32_t* n_out, esp_cuda_generation_result* result);
+/* GenerationResult.tokenLatenciesMs (Engine.swift:17-55; the CLI's median / p95, Sources/EspressoGenerate/CLI.swift:
+ * 1153-1165, 1283-1284) of sequence 0 for the most recent esp_cuda_generate / esp_cuda_generate_steps /
+ * esp_cuda_decode: milliseconds between consecutive tokens (the first entry counts from the start of decoding).
+ * Device timers inside the persistent kernel, CUDA events between the steps of the other kernels, the host clock for
+ * esp_cuda_generate_steps. */
+ESP_CUDA_API int32_t esp_cuda_token_latencies(esp_cuda_engine* engine, float* out_ms, int32_t capacity, int32_t* n);
 /* Exact two-token speculative generation with a draft engine (Engine.swift:6014-6190); the emitted
  * stream equals plain greedy decoding of `engine`. */
 ESP_CUDA_API int32_t esp_cuda_generate_two_token(esp_cuda_engine* engine, esp_cuda_engine* draft,

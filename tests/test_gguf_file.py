@@ -68,6 +68,23 @@ def test_gguf_error_kinds(rt, tmp_path):
         with pytest.raises(rt.RealModelInferenceError) as ei:
             rt.gguf_inspect(p)
         assert ei.value.status == rt.ERR_INVALID_WEIGHTS, name
+    # crafted tensor directory entries: an offset near 2^64 (offset + size wraps around) and dimensions whose product
+    # overflows 64 bits must be refused, not turned into a wild host pointer
+    name = b"token_embd.weight"
+    at = raw.index(name) + len(name)
+    n_dims = int.from_bytes(raw[at:at + 4], "little")
+    dims_at, off_at = at + 4, at + 4 + 8 * n_dims + 4
+    wild = bytearray(raw)
+    wild[off_at:off_at + 8] = (2**64 - 32).to_bytes(8, "little")
+    huge = bytearray(raw)
+    for k in range(n_dims):
+        huge[dims_at + 8 * k:dims_at + 8 * k + 8] = (2**40 + 32 * 1024).to_bytes(8, "little")
+    for label, blob in (("wrapping_offset", wild), ("overflowing_dims", huge)):
+        p = str(tmp_path / f"{label}.gguf")
+        open(p, "wb").write(bytes(blob))
+        with pytest.raises(rt.RealModelInferenceError) as ei:
+            rt.gguf_inspect(p)
+        assert ei.value.status == rt.ERR_INVALID_WEIGHTS, label
     with pytest.raises(rt.RealModelInferenceError) as ei:
         rt.gguf_inspect(str(tmp_path / "absent.gguf"))
     assert ei.value.status == rt.ERR_IO

@@ -208,3 +208,27 @@ def test_device_wait_that_runs_out_reports_a_timeout(rt, oracle_lib, tmp_models)
     assert list(again) == list(good)
     compare_greedy_stream(oracle_lib.Runtime(oracle_lib.Model.from_dir(d)), prompt, again)
     eng.close()
+
+
+def test_per_token_latencies_and_step_callback(rt, oracle_lib, tmp_models):
+    """GenerationResult.tokenLatenciesMs and the inline onStep callback (Engine.swift:17-55, 6393-6405): the device-driven
+    loops report one latency per token, and the token-by-token form calls back once per token with the same stream."""
+    from espresso_b200.model_config import tiny_llama
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = tiny_llama(vocab=512, max_seq=64, n_layer=2)
+    d = tmp_models(cfg)
+    prompt = synthetic_prompt(cfg.vocab, 6)
+    ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(d))
+    for flags in (0, rt.FLAG_NO_MEGAKERNEL):
+        eng = rt.DecodeEngine.build(d, flags=flags)
+        res = eng.generate(prompt, 18)
+        lat = res.tokenLatenciesMs
+        assert lat is not None and lat.size == 18 and np.all(lat > 0) and lat.sum() < 1e3
+        seen = []
+        stepped = eng.generate(prompt, 18, on_step=lambda tok, idx, ms: seen.append((tok, idx, ms)))
+        assert [t for t, _, _ in seen] == list(stepped.tokens) and [i for _, i, _ in seen] == list(range(18))
+        assert all(ms > 0 for _, _, ms in seen) and stepped.tokenLatenciesMs.size == 18
+        compare_greedy_stream(ora, prompt, stepped.tokens)
+        compare_greedy_stream(ora, prompt, res.tokens)
+        eng.close()
