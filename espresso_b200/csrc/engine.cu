@@ -804,6 +804,10 @@ int32_t Engine::launch_step(int rows, int mode, cudaStream_t s, bool profile) {
 
 int32_t Engine::submit(int rows, int mode) {
     if (force_failure_enabled()) return fail(ESP_CUDA_ERR_FORCED_FAILURE, "forced failure is enabled");
+    if (tc_ready_ && !tc_operands_ready_ && (rows >= kTcMinRows || tp_size_ > 1)) {
+        int32_t rc = tc_operands();  // before any capture: it allocates
+        if (rc) return rc;
+    }
     const bool direct = (cfg_.flags & ESP_CUDA_FLAG_NO_GRAPH) || debug_layer_ >= 0;
     if (direct) {
         bool profile = (cfg_.flags & ESP_CUDA_FLAG_NO_GRAPH) && (mode & STEP_FORWARD) && (mode & STEP_HEAD);
@@ -1444,21 +1448,14 @@ int32_t Engine::build_tc() {
     }
     if (quantised && (cfg_.flags & ESP_CUDA_FLAG_NO_TC_SHADOW)) return ESP_CUDA_OK;
     tc_bf16_ = t0 == ESP_CUDA_BF16;
-    for (auto& n : mats) {
-        DeviceTensor& t = tensors_.at(n);
-        const void* base = t.data;
-        if (quantised) {
-            // batches multiply by an fp16 expansion of the quantised matrix; single rows keep reading the blocks
-            const int64_t nb = (int64_t)t.rows * t.cols / 32;
-            int32_t rc = dev_alloc(owned_, &t.shadow16, (size_t)t.rows * t.cols, false);
-            if (rc) return rc;
-            k_expand_quant<<<(unsigned)((nb * 4 + 255) / 256), 256, 0, stream_>>>(t.data, t.scales, t.type == ESP_CUDA_Q8_0 ? WT_Q8_0 : WT_Q4_0, nb, t.shadow16);
-            ESP_CUDA_TRY(cudaGetLastError());
-            base = t.shadow16;
-        }
-        int32_t rc = tc_make_map(&t.map, base, tc_bf16_, t.rows, t.cols, kTcHalf);
-        if (rc) return rc;
-        t.has_map = true;
+    tc_mats_ = mats;
+    tc_operands_ready_ = false;
+    // 16-bit matrices get their TMA maps now.  A quantised model's fp16 expansion (what batches and prefill chunks
+    // multiply by) is built by the first step that takes the batched path: an engine that only ever decodes one
+    // sequence through the persistent kernel, which streams the GGUF blocks themselves, never allocates it.
+    if (!quantised) {
+        int32_t rc0 = tc_operands();
+        if (rc0) return rc0;
     }
     tc_rows_alloc_ = (max_rows_ + 15) / 16 * 16;
     int32_t rc;
@@ -1472,6 +1469,30 @@ int32_t Engine::build_tc() {
     if (tp_size_ > 1 && (rc = dev_alloc(owned_, &tp_partial_, (size_t)max_rows_ * m_.d_model))) return rc;
     ESP_CUDA_TRY(cudaDeviceSynchronize());
     tc_ready_ = true;
+    return ESP_CUDA_OK;
+}
+
+// TMA maps of the weight matrices for the batched path; for a quantised model first the fp16 expansion fp16(d * q) of
+// every matrix.  Called outside stream capture (it allocates).
+int32_t Engine::tc_operands() {
+    if (tc_operands_ready_) return ESP_CUDA_OK;
+    for (auto& n : tc_mats_) {
+        DeviceTensor& t = tensors_.at(n);
+        const void* base = t.data;
+        if (t.type == ESP_CUDA_Q8_0 || t.type == ESP_CUDA_Q4_0) {
+            const int64_t nb = (int64_t)t.rows * t.cols / 32;
+            int32_t rc = dev_alloc(owned_, &t.shadow16, (size_t)t.rows * t.cols, false);
+            if (rc) return rc;
+            k_expand_quant<<<(unsigned)((nb * 4 + 255) / 256), 256, 0, stream_>>>(t.data, t.scales, t.type == ESP_CUDA_Q8_0 ? WT_Q8_0 : WT_Q4_0, nb, t.shadow16);
+            ESP_CUDA_TRY(cudaGetLastError());
+            base = t.shadow16;
+        }
+        int32_t rc = tc_make_map(&t.map, base, tc_bf16_, t.rows, t.cols, kTcHalf);
+        if (rc) return rc;
+        t.has_map = true;
+    }
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    tc_operands_ready_ = true;
     return ESP_CUDA_OK;
 }
 
@@ -1646,10 +1667,16 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
 
 static int pad128(long long v) { return (int)((v + 127) / 128 * 128); }
 
-static const void* mega_kernel_for(int head_dim) {
-    if (head_dim == 64) return reinterpret_cast<const void*>(&k_decode_mega<64>);
-    if (head_dim == 128) return reinterpret_cast<const void*>(&k_decode_mega<128>);
-    return reinterpret_cast<const void*>(&k_decode_mega<32>);
+template <int WT>
+static const void* mega_kernel_of(int head_dim) {
+    if (head_dim == 64) return reinterpret_cast<const void*>(&k_decode_mega<64, WT>);
+    if (head_dim == 128) return reinterpret_cast<const void*>(&k_decode_mega<128, WT>);
+    return reinterpret_cast<const void*>(&k_decode_mega<32, WT>);
+}
+static const void* mega_kernel_for(int head_dim, int wt) {
+    if (wt == WT_Q8_0) return mega_kernel_of<WT_Q8_0>(head_dim);
+    if (wt == WT_Q4_0) return mega_kernel_of<WT_Q4_0>(head_dim);
+    return mega_kernel_of<WT_F16>(head_dim);
 }
 
 // Plans and packs the persistent decode kernel.  Every CTA owns a contiguous share of the rows of every matrix;
@@ -1660,16 +1687,19 @@ int32_t Engine::build_mega() {
     if (m_.arch != ARCH_LLAMA) return ESP_CUDA_OK;
     if (m_.head_dim != 32 && m_.head_dim != 64 && m_.head_dim != 128) return ESP_CUDA_OK;
     if (m_.d_model % 32 || m_.hidden % 32 || m_.n_head > sm_count_ || m_.n_head > 255 || m_.vocab >= (1 << 24)) return ESP_CUDA_OK;
-    // fp16 source of a matrix: its own storage, or the fp16 expansion of a quantised matrix
-    auto f16_source = [&](const std::string& name) -> const __half* {
-        const DeviceTensor& t = tensors_.at(name);
-        if (t.type == ESP_CUDA_F16) return static_cast<const __half*>(t.data);
-        return t.shadow16;  // null unless build_tc made one
-    };
-    if (tensors_.at("embeddings/token").type != ESP_CUDA_F16 || !f16_source("lm_head")) return ESP_CUDA_OK;
+    // The layer matrices share one storage type (fp16, or GGUF Q8_0 / Q4_0 blocks, which travel through the ring as they
+    // are); the LM head has that type or fp16.  Anything else is left to the per-stage kernels.
+    auto type_of = [&](const std::string& name) { return tensors_.at(name).type; };
+    const int wt_layer = type_of("layers/0/wq");
+    const int wt_head = type_of("lm_head");
+    if (wt_layer != ESP_CUDA_F16 && wt_layer != ESP_CUDA_Q8_0 && wt_layer != ESP_CUDA_Q4_0) return ESP_CUDA_OK;
+    if (wt_head != wt_layer && wt_head != ESP_CUDA_F16) return ESP_CUDA_OK;
+    if (tensors_.at("embeddings/token").type != ESP_CUDA_F16) return ESP_CUDA_OK;
     for (int l = 0; l < m_.n_layer; l++)
         for (const char* n : {"wq", "wk", "wv", "wo", "w1", "w2", "w3"})
-            if (!f16_source("layers/" + std::to_string(l) + "/" + n)) return ESP_CUDA_OK;
+            if (type_of("layers/" + std::to_string(l) + "/" + n) != wt_layer) return ESP_CUDA_OK;
+    const bool quant = wt_layer != ESP_CUDA_F16 || wt_head != ESP_CUDA_F16;
+    if (quant && (m_.d_model % 256 || m_.hidden % 256)) return ESP_CUDA_OK;  // chunk sizes must stay multiples of 16 bytes
     int coop = 0, smem_max = 0;
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, cfg_.device);
     cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, cfg_.device);
@@ -1689,14 +1719,22 @@ int32_t Engine::build_mega() {
     p.hpc_max = (m_.hidden + P - 1) / P;
     p.dpc_max = (m_.d_model + P - 1) / P;
     p.vpc_max = (m_.vocab + P - 1) / P;
-    p.row_bytes = m_.d_model * 2;
-    p.down_row_bytes = m_.hidden * 2;
+    p.wt_layer = wt_layer;
+    p.wt_head = wt_head;
+    p.row_bytes = mega_row_bytes(wt_layer, m_.d_model);
+    p.down_row_bytes = mega_row_bytes(wt_layer, m_.hidden);
+    p.wo_row_bytes = mega_row_bytes(wt_layer, m_.head_dim);
+    p.head_row_bytes = mega_row_bytes(wt_head, m_.d_model);
+    // a quantised row of head_dim columns is 68 / 36 / ... bytes: chunks of the Wo stage must hold a multiple of `wo_rows`
+    // rows to stay multiples of 16 bytes
+    const int wo_rows = wt_layer == ESP_CUDA_F16 ? 1 : std::max(1, 8 / (m_.head_dim / 32));
+    if (p.rpb % wo_rows) return ESP_CUDA_OK;
     p.s1_bytes = pad128((long long)2 * p.s1_max * p.row_bytes);
-    p.s2_bytes = pad128((long long)p.rpb * m_.head_dim * 2);
+    p.s2_bytes = pad128((long long)p.rpb * p.wo_row_bytes);
     p.s3a_bytes = pad128((long long)2 * p.hpc_max * p.row_bytes);
     p.s3b_bytes = pad128((long long)p.dpc_max * p.down_row_bytes);
     p.layer_bytes = (long long)p.s1_bytes + p.s2_bytes + p.s3a_bytes + p.s3b_bytes;
-    p.head_bytes = pad128((long long)p.vpc_max * p.row_bytes);
+    p.head_bytes = pad128((long long)p.vpc_max * p.head_row_bytes);
     p.cta_bytes = p.layer_bytes * m_.n_layer + p.head_bytes;
     // ring slots of 48 KB (more when one item of a stage is larger); a stage slice travels as chunks of whole items,
     // at most kMegaChunkRows rows each (the products of a chunk are spread over the warps as 8-row tiles)
@@ -1705,8 +1743,9 @@ int32_t Engine::build_mega() {
     p.s1_ipc = std::max(1, std::min(std::min(p.s1_max, kMegaChunkRows / 2), p.slot_bytes / (2 * p.row_bytes)));
     p.s3a_ipc = std::max(1, std::min(std::min(p.hpc_max, kMegaChunkRows / 2), p.slot_bytes / (2 * p.row_bytes)));
     p.s3b_rpc = std::max(1, std::min(std::min(p.dpc_max, kMegaChunkRows), p.slot_bytes / p.down_row_bytes));
-    p.head_rpc = std::max(1, std::min(std::min(p.vpc_max, kMegaChunkRows), p.slot_bytes / p.row_bytes));
-    p.s2_rpc = std::max(1, std::min(std::min(p.rpb, kMegaChunkRows), p.slot_bytes / (m_.head_dim * 2)));
+    p.head_rpc = std::max(1, std::min(std::min(p.vpc_max, kMegaChunkRows), p.slot_bytes / p.head_row_bytes));
+    p.s2_rpc = std::max(1, std::min(std::min(p.rpb, kMegaChunkRows), p.slot_bytes / p.wo_row_bytes));
+    p.s2_rpc = std::max(wo_rows, p.s2_rpc / wo_rows * wo_rows);
     p.n_slots = 0;
     for (int ns = 8; ns >= 2; ns--) {
         MegaPlan probe = p;
@@ -1715,7 +1754,7 @@ int32_t Engine::build_mega() {
         if (probe.smem_bytes <= smem_max) { p = probe; break; }
     }
     if (p.n_slots == 0) return ESP_CUDA_OK;  // does not fit: the per-stage kernels serve this model
-    const void* kern = mega_kernel_for(m_.head_dim);
+    const void* kern = mega_kernel_for(m_.head_dim, wt_layer);
     ESP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes));
     int occ = 0;
     ESP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kMegaThreads, p.smem_bytes));
@@ -1731,20 +1770,23 @@ int32_t Engine::build_mega() {
     if ((rc = dev_alloc(owned_, &d_mega_trace_, (size_t)kMegaTraceLayer * m_.n_layer + kMegaTraceHead + 4 + 1024))) return rc;
     if ((rc = dev_alloc(owned_, &d_token_times_, (size_t)m_.max_seq + 1))) return rc;
     ESP_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&h_mega_ctl_), 8 * sizeof(unsigned long long)));
-    // per-layer source pointers
-    std::vector<const __half*> ptrs((size_t)7 * m_.n_layer);
+    // per-layer source matrices
+    std::vector<PackMatrix> mats((size_t)7 * m_.n_layer);
     const char* names[7] = {"wq", "wk", "wv", "wo", "w1", "w2", "w3"};
     for (int k = 0; k < 7; k++)
-        for (int l = 0; l < m_.n_layer; l++)
-            ptrs[(size_t)k * m_.n_layer + l] = f16_source("layers/" + std::to_string(l) + "/" + names[k]);
-    const __half** d_ptrs = nullptr;
-    ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_ptrs), ptrs.size() * sizeof(void*)));
-    cudaError_t e = cudaMemcpy(d_ptrs, ptrs.data(), ptrs.size() * sizeof(void*), cudaMemcpyHostToDevice);
+        for (int l = 0; l < m_.n_layer; l++) {
+            const DeviceTensor& t = tensors_.at("layers/" + std::to_string(l) + "/" + names[k]);
+            mats[(size_t)k * m_.n_layer + l] = PackMatrix{t.data, t.scales};
+        }
+    PackMatrix* d_mats = nullptr;
+    ESP_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&d_mats), mats.size() * sizeof(PackMatrix)));
+    cudaError_t e = cudaMemcpy(d_mats, mats.data(), mats.size() * sizeof(PackMatrix), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) {
         PackSources src{};
-        src.wq = d_ptrs; src.wk = d_ptrs + m_.n_layer; src.wv = d_ptrs + 2 * m_.n_layer; src.wo = d_ptrs + 3 * m_.n_layer;
-        src.w1 = d_ptrs + 4 * m_.n_layer; src.w2 = d_ptrs + 5 * m_.n_layer; src.w3 = d_ptrs + 6 * m_.n_layer;
-        src.lm_head = f16_source("lm_head");
+        src.wq = d_mats; src.wk = d_mats + m_.n_layer; src.wv = d_mats + 2 * m_.n_layer; src.wo = d_mats + 3 * m_.n_layer;
+        src.w1 = d_mats + 4 * m_.n_layer; src.w2 = d_mats + 5 * m_.n_layer; src.w3 = d_mats + 6 * m_.n_layer;
+        const DeviceTensor& lh = tensors_.at("lm_head");
+        src.lm_head = PackMatrix{lh.data, lh.scales};
         k_build_pack<<<P, 256, 0, stream_>>>(src, p, m_, d_pack_);
         e = cudaGetLastError();
     }
@@ -1757,7 +1799,7 @@ int32_t Engine::build_mega() {
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(d_norms_ + (size_t)(2 * m_.n_layer) * m_.d_model, tensors_.at("rms_final").f32, sizeof(float) * m_.d_model, cudaMemcpyDeviceToDevice, stream_);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream_);
-    cudaFree(d_ptrs);
+    cudaFree(d_mats);
     ESP_CUDA_TRY(e);
     mega_plan_ = p;
     mega_ready_ = true;
@@ -1792,7 +1834,7 @@ int32_t Engine::run_mega(int n_steps, int* emitted, float* device_ms, double* fi
     ESP_CUDA_TRY(cudaMemsetAsync(d_mega_arena_, 0, mega_arena_words_ * sizeof(unsigned long long), stream_));
     ESP_CUDA_TRY(cudaEventRecord(ev_begin_, stream_));
     void* args[] = {&a};
-    ESP_CUDA_TRY(cudaLaunchCooperativeKernel(mega_kernel_for(m_.head_dim), dim3(p.n_cta), dim3(kMegaThreads), args, (size_t)p.smem_bytes, stream_));
+    ESP_CUDA_TRY(cudaLaunchCooperativeKernel(mega_kernel_for(m_.head_dim, p.wt_layer), dim3(p.n_cta), dim3(kMegaThreads), args, (size_t)p.smem_bytes, stream_));
     ESP_CUDA_TRY(cudaEventRecord(ev_end_, stream_));
     ESP_CUDA_TRY(cudaMemcpyAsync(h_mega_ctl_, d_mega_ctl_, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream_));
     ESP_CUDA_TRY(cudaStreamSynchronize(stream_));

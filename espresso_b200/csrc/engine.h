@@ -95,6 +95,7 @@ private:
     int32_t launch_step(int rows, int mode, cudaStream_t s, bool profile);
     int32_t launch_step_tc(int rows, int mode, cudaStream_t s);  // batched path: tensor-core GEMMs + element-wise stages
     int32_t build_tc();
+    int32_t tc_operands();  // weight maps (and a quantised model's fp16 expansion), built on first use of the batched path
     int32_t all_reduce(const void* send, void* recv, size_t count, bool sum_f32, cudaStream_t s);
     const CUtensorMap* activation_map(const uint16_t* buf, int K, int tile);
     int32_t feed_rows(int rows, const int* seq, const uint32_t* tok, bool with_head, uint32_t* next_out);
@@ -154,6 +155,8 @@ private:
 
     // batched tensor-core path (rows >= kTcMinRows, 16-bit weights)
     bool tc_ready_ = false;
+    bool tc_operands_ready_ = false;
+    std::vector<std::string> tc_mats_;
     int tc_bf16_ = 0;
     int tc_rows_alloc_ = 0;
     uint16_t *xh_d_ = nullptr, *xh_q_ = nullptr, *xh_h_ = nullptr;  // 16-bit operand rows [tc_rows_alloc_][K]

@@ -30,6 +30,10 @@
 // instructions: sixteen weight rows are the A operand, and the fp32 activation vector, split exactly into two fp16
 // vectors (x = hi + lo, |error| <= 2^-22 |x|), occupies columns 0 and 1 of the B operand; the accumulators are fp32.  The
 // pack stores every chunk in the order the A fragments are read: for each block of 32 columns, for each row, 64 bytes.
+// GGUF Q8_0 / Q4_0 matrices travel through the ring as their blocks (32 or 16 bytes per row and block of 32 columns,
+// the fp16 scales behind them): 34/32 or 18/32 bytes per weight from HBM, never an fp16 copy.  A block of 32 columns
+// is exactly two m16n8k16 steps: the integers are widened to fp16 exactly in registers, the products of a block are
+// accumulated from zero and multiplied by the block's scale in fp32 (value = fp32(d) * q as in the GGUF definition).
 // Why single buffers suffice: each exchange is re-written only after an exchange of another kind that every
 // reader of the old contents must have passed (see the notes at each stage).
 // Every wait (mbarrier, tagged word, counted sum) is bounded: when a limit is hit the kernel records an error code,
@@ -61,8 +65,11 @@ struct MegaPlan {
     int s1_max;       // largest number of S1 row pairs of a CTA
     int rpb;          // S2: output rows per block
     int hpc_max, dpc_max, vpc_max;  // largest number of FFN units / W2 rows / vocabulary rows of a CTA
-    int row_bytes;    // d_model * 2
-    int down_row_bytes;  // hidden * 2
+    int wt_layer, wt_head;  // storage type of the layer matrices and of the LM head: WT_F16, WT_Q8_0 or WT_Q4_0
+    int row_bytes;       // packed bytes of a row of d_model columns of a layer matrix
+    int down_row_bytes;  // ... of hidden columns (W2)
+    int wo_row_bytes;    // ... of head_dim columns (this head's part of a row of Wo)
+    int head_row_bytes;  // ... of d_model columns of the LM head
     int s1_bytes, s2_bytes, s3a_bytes, s3b_bytes;  // packed bytes of a stage per layer (multiples of 128, sized for the largest CTA share)
     // A stage whose slice is larger than a ring slot arrives in several chunks of whole items:
     int s1_ipc;       // S1 row pairs per chunk
@@ -76,6 +83,9 @@ struct MegaPlan {
     // byte offsets of the shared-memory areas behind the ring (see MegaShared)
     int off_bar, off_prev, off_key, off_xs, off_xraw, off_xmid, off_rope, off_qs, off_ctx, off_kn, off_vn, off_part, off_red, off_outv, off_flags, off_share;
 };
+
+// Packed bytes of K columns of one row: fp16, or GGUF blocks of 32 (int8 / nibbles) with one fp16 scale each.
+__host__ __device__ inline int mega_row_bytes(int wt, int K) { return wt == WT_Q8_0 ? K + K / 16 : wt == WT_Q4_0 ? K / 2 + K / 16 : K * 2; }
 
 // Contiguous share [begin, end) of `n` items owned by part `i` of `parts` (every part gets floor or ceil of n/parts).
 // (n * parts stays far below 2^32 for every model size the plan accepts)
@@ -298,10 +308,10 @@ __device__ __forceinline__ void mega_fail(const MegaArgs& a, const MegaShared& s
 __device__ __forceinline__ bool mega_aborting(const MegaShared& s) { return *reinterpret_cast<volatile int*>(s.abort) != 0; }
 
 #ifndef MEGA_POLL_NS
-#define MEGA_POLL_NS 100
+#define MEGA_POLL_NS 0
 #endif
-// Between two attempts of a poll of global memory: every CTA polls the same few cache lines, and requests that
-// arrive back to back would queue up in front of the very stores they are waiting for.
+// Optional pause between two attempts of a poll of global memory.  Measured on the 6-layer d768 model: 0 and 100 ns
+// give the same token time within 1 %, 300 ns costs 11 %, so the default polls back to back.
 __device__ __forceinline__ void mega_backoff() {
     if (MEGA_POLL_NS > 0) __nanosleep(MEGA_POLL_NS);
 }
@@ -479,19 +489,22 @@ __device__ __forceinline__ float mega_block_sum(float v, float* red) {
 
 // ------------------------------------------------------------------------------------------------ products
 
-// Where element k of a staged vector lives (in halves): block of 32 columns kb, column g of the B operand (0 = hi part,
-// 1 = lo part), piece t; the 16 bytes of a piece are the B registers of the two m16n8k16 steps of the block.
-__device__ __forceinline__ int xa_index(int k, int g) {
+// Where element k of a staged vector lives (in halves): block of 32 columns kb, column c of the B operand (position q's
+// hi part is column 2q, its lo part column 2q + 1; NP positions are staged side by side), piece t; the 16 bytes of a
+// piece are the B registers of the two m16n8k16 steps of the block.
+template <int NP = 1>
+__device__ __forceinline__ int xa_index(int k, int c) {
     const int kb = k >> 5, kk = k & 31;
-    return (((kb * 2 + g) * 4 + ((kk & 7) >> 1)) << 3) + ((kk >> 3) << 1) + (kk & 1);
+    return (((kb * 2 * NP + c) * 4 + ((kk & 7) >> 1)) << 3) + ((kk >> 3) << 1) + (kk & 1);
 }
 
-// Stores v as hi + lo (both fp16, hi saturating) at position k of a staged vector.
-__device__ __forceinline__ void xa_store(__half* xa, int k, float v) {
+// Stores v as hi + lo (both fp16, hi saturating) at element k of position q of a staged vector.
+template <int NP = 1>
+__device__ __forceinline__ void xa_store(__half* xa, int k, float v, int q = 0) {
     __half hi;
     asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(*reinterpret_cast<unsigned short*>(&hi)) : "f"(v));
-    xa[xa_index(k, 0)] = hi;
-    xa[xa_index(k, 1)] = __float2half_rn(v - __half2float(hi));
+    xa[xa_index<NP>(k, 2 * q)] = hi;
+    xa[xa_index<NP>(k, 2 * q + 1)] = __float2half_rn(v - __half2float(hi));
 }
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -503,8 +516,11 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
 // Partial products of the 16-row tile `tile` of a chunk of R rows with the staged vector over the column blocks
 // [kb0, kb1).  The weights are the A operand (rows g and g + 8 of the tile: one 16-byte shared-memory load each per two
 // m16n8k16 steps), the staged vector the B operand (column 0 = hi part, column 1 = lo part, held by lanes 0..7).  The
-// lanes with lane % 4 == 0 return the sums of rows tile*16 + lane/4 (.x) and + 8 (.y); rows past R are meaningless.
-__device__ __forceinline__ float2 mega_tile_dot(const uint8_t* chunk, int R, int tile, int kb0, int kb1, const uint8_t* xa, int lane) {
+// lanes with lane % 4 == q < NP return the sums of position q for rows tile*16 + lane/4 (.x) and + 8 (.y); rows past R are
+// meaningless.  With NP positions the staged vector holds 2 NP columns (lanes 0 .. 8 NP - 1 feed the B operand): the
+// products of a second position ride in columns the instruction computes anyway.
+template <int NP>
+__device__ __forceinline__ float2 mega_tile_dot_f16(const uint8_t* chunk, int R, int n_kb, int tile, int kb0, int kb1, const uint8_t* xa, int lane) {
     // four independent accumulator sets: a dependent m16n8k16 costs ~40-60 cycles, and a warp has only a few blocks
     float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f}, c3[4] = {0.f, 0.f, 0.f, 0.f};
     const uint8_t* wp = chunk + ((size_t)(tile * 16 + (lane >> 2)) * 64 + (lane & 3) * 16);
@@ -515,7 +531,7 @@ __device__ __forceinline__ float2 mega_tile_dot(const uint8_t* chunk, int R, int
         const uint4 w0 = *reinterpret_cast<const uint4*>(wp + kb * kstride);
         const uint4 w8 = *reinterpret_cast<const uint4*>(wp + kb * kstride + 8 * 64);
         uint4 xv = make_uint4(0, 0, 0, 0);
-        if (lane < 8) xv = *reinterpret_cast<const uint4*>(xp + kb * 128);
+        if (lane < 8 * NP) xv = *reinterpret_cast<const uint4*>(xp + kb * (128 * NP));
         mma_16816(ce, w0.x, w8.x, w0.y, w8.y, xv.x, xv.y);
         mma_16816(co, w0.z, w8.z, w0.w, w8.w, xv.z, xv.w);
     };
@@ -531,10 +547,95 @@ __device__ __forceinline__ float2 mega_tile_dot(const uint8_t* chunk, int R, int
                        ((c0[2] + c1[2]) + (c2[2] + c3[2])) + ((c0[3] + c1[3]) + (c2[3] + c3[3])));
 }
 
+// Four int8 -> two half2 (b0, b1), (b2, b3), exactly: xor 0x80 makes the byte unsigned, a byte permute drops it into the
+// mantissa of 1024.0 (0x6400), and subtracting 1152 = 1024 + 128 leaves the signed value.
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ void q8_widen(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    const uint32_t u = w ^ 0x80808080u;
+    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+    lo = h2_bits(__hsub2(u32_as_h2(__byte_perm(u, 0x64646464u, 0x4140)), bias));
+    hi = h2_bits(__hsub2(u32_as_h2(__byte_perm(u, 0x64646464u, 0x4342)), bias));
+}
+// Four bytes of a Q4_0 block (low nibble = element j, high nibble = element j + 16) -> four half2: the low nibbles of
+// bytes (0,1), (2,3), then the high nibbles of (0,1), (2,3), each minus 8.
+__device__ __forceinline__ void q4_widen(uint32_t w, uint32_t (&o)[4]) {
+    const uint32_t x = w & 0x0F0F0F0Fu, y = (w >> 4) & 0x0F0F0F0Fu;
+    const __half2 bias = __floats2half2_rn(1032.f, 1032.f);
+    o[0] = h2_bits(__hsub2(u32_as_h2(__byte_perm(x, 0x64646464u, 0x4140)), bias));
+    o[1] = h2_bits(__hsub2(u32_as_h2(__byte_perm(x, 0x64646464u, 0x4342)), bias));
+    o[2] = h2_bits(__hsub2(u32_as_h2(__byte_perm(y, 0x64646464u, 0x4140)), bias));
+    o[3] = h2_bits(__hsub2(u32_as_h2(__byte_perm(y, 0x64646464u, 0x4342)), bias));
+}
+
+// Q8_0 chunk: [block][row][32 int8 in the order the lanes read them], then the scales [block][row] fp16.
+template <int NP>
+__device__ __forceinline__ float2 mega_tile_dot_q8(const uint8_t* chunk, int R, int n_kb, int tile, int kb0, int kb1, const uint8_t* xa, int lane) {
+    float a0 = 0.f, a8 = 0.f;
+    const int row = tile * 16 + (lane >> 2);
+    const uint8_t* wp = chunk + ((size_t)row * 32 + (lane & 3) * 8);
+    const size_t kstride = (size_t)R * 32;
+    const __half* sp = reinterpret_cast<const __half*>(chunk + (size_t)R * n_kb * 32) + row;
+    const uint8_t* xp = xa + lane * 16;
+#pragma unroll 2
+    for (int kb = kb0; kb < kb1; kb++) {
+        const uint2 w0 = *reinterpret_cast<const uint2*>(wp + kb * kstride);
+        const uint2 w8 = *reinterpret_cast<const uint2*>(wp + kb * kstride + 8 * 32);
+        const float s0 = __half2float(sp[(size_t)kb * R]), s8 = __half2float(sp[(size_t)kb * R + 8]);
+        uint4 xv = make_uint4(0, 0, 0, 0);
+        if (lane < 8 * NP) xv = *reinterpret_cast<const uint4*>(xp + kb * (128 * NP));
+        uint32_t g01, g23, g45, g67, h01, h23, h45, h67;
+        q8_widen(w0.x, g01, g23); q8_widen(w0.y, g45, g67);
+        q8_widen(w8.x, h01, h23); q8_widen(w8.y, h45, h67);
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_16816(c, g01, h01, g23, h23, xv.x, xv.y);
+        mma_16816(c, g45, h45, g67, h67, xv.z, xv.w);
+        a0 = fmaf(s0, c[0] + c[1], a0);
+        a8 = fmaf(s8, c[2] + c[3], a8);
+    }
+    return make_float2(a0, a8);
+}
+
+// Q4_0 chunk: [block][row][16 bytes: piece t = bytes 2t, 2t+1, 2t+8, 2t+9 of the GGUF block], then the scales.
+template <int NP>
+__device__ __forceinline__ float2 mega_tile_dot_q4(const uint8_t* chunk, int R, int n_kb, int tile, int kb0, int kb1, const uint8_t* xa, int lane) {
+    float a0 = 0.f, a8 = 0.f;
+    const int row = tile * 16 + (lane >> 2);
+    const uint8_t* wp = chunk + ((size_t)row * 16 + (lane & 3) * 4);
+    const size_t kstride = (size_t)R * 16;
+    const __half* sp = reinterpret_cast<const __half*>(chunk + (size_t)R * n_kb * 16) + row;
+    const uint8_t* xp = xa + lane * 16;
+#pragma unroll 2
+    for (int kb = kb0; kb < kb1; kb++) {
+        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(wp + kb * kstride);
+        const uint32_t w8 = *reinterpret_cast<const uint32_t*>(wp + kb * kstride + 8 * 16);
+        const float s0 = __half2float(sp[(size_t)kb * R]), s8 = __half2float(sp[(size_t)kb * R + 8]);
+        uint4 xv = make_uint4(0, 0, 0, 0);
+        if (lane < 8 * NP) xv = *reinterpret_cast<const uint4*>(xp + kb * (128 * NP));
+        uint32_t g[4], h[4];
+        q4_widen(w0, g);
+        q4_widen(w8, h);
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_16816(c, g[0], h[0], g[1], h[1], xv.x, xv.y);
+        mma_16816(c, g[2], h[2], g[3], h[3], xv.z, xv.w);
+        a0 = fmaf(s0, c[0] + c[1], a0);
+        a8 = fmaf(s8, c[2] + c[3], a8);
+    }
+    return make_float2(a0, a8);
+}
+
+template <int WT, int NP>
+__device__ __forceinline__ float2 mega_tile_dot(const uint8_t* chunk, int R, int n_kb, int tile, int kb0, int kb1, const uint8_t* xa, int lane) {
+    if constexpr (WT == WT_Q8_0) return mega_tile_dot_q8<NP>(chunk, R, n_kb, tile, kb0, kb1, xa, lane);
+    else if constexpr (WT == WT_Q4_0) return mega_tile_dot_q4<NP>(chunk, R, n_kb, tile, kb0, kb1, xa, lane);
+    else return mega_tile_dot_f16<NP>(chunk, R, n_kb, tile, kb0, kb1, xa, lane);
+}
+
 // All products of one chunk (R <= kMegaChunkRows rows over n_kb column blocks), spread over the consumer warps as
 // (16-row tile, column range) units; the number of column ranges is a power of two so that a warp finds its unit with
 // shifts (per chunk every scalar instruction of this set-up is on the critical path of the token).  Unit u = tile <<
-// lg | range stores its sixteen partial sums at partial[u * 16 ...]; returns lg.  The caller synchronises before reading.
+// lg | range stores its sixteen partial sums at partial[u * 16 ...] (position q: + q * kMegaChunkRows); returns lg.  The
+// caller synchronises before reading.
+template <int WT, int NP = 1>
 __device__ __forceinline__ int mega_chunk_dots(const uint8_t* chunk, int R, int n_kb, const uint8_t* xa, float* partial, int warp, int lane) {
     const int n_tiles = (R + 15) >> 4;
     // lg = log2(column ranges): the largest value with tiles << lg <= warps and 1 << lg <= n_kb
@@ -543,9 +644,9 @@ __device__ __forceinline__ int mega_chunk_dots(const uint8_t* chunk, int R, int 
     const int per = (n_kb + (1 << lg) - 1) >> lg;
     for (int u = warp; u < (n_tiles << lg); u += kMegaConsumerWarps) {
         const int tile = u >> lg, part = u & ((1 << lg) - 1);
-        const float2 y = mega_tile_dot(chunk, R, tile, part * per, min(n_kb, (part + 1) * per), xa, lane);
-        if ((lane & 3) == 0) {
-            float* dst = partial + u * 16 + (lane >> 2);
+        const float2 y = mega_tile_dot<WT, NP>(chunk, R, n_kb, tile, part * per, min(n_kb, (part + 1) * per), xa, lane);
+        if ((lane & 3) < NP) {
+            float* dst = partial + (NP > 1 ? (lane & 3) * kMegaChunkRows : 0) + u * 16 + (lane >> 2);
             dst[0] = y.x;
             dst[8] = y.y;
         }
@@ -607,14 +708,17 @@ __device__ __forceinline__ void mega_kv_load(MegaKvRound<HD>& r, const __half* K
     }
 }
 
-template <int HD, class WaitQ>
-__device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShared& s, const MegaShare& w, int layer, int pos, WaitQ wait_q) {
-    const ModelDims& m = a.m;
+// With NP positions per pass the call serves query `qi`: it sees the n_cached cached positions and the new positions
+// 0 .. qi, whose keys and values are rows of s.kn / s.vn; its context lands in position qi of the staged s.ctx.
+template <int HD, int NP = 1, class WaitQ>
+__device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShared& s, const MegaShare& w, const ModelDims& m, const KvLayout& kv, int layer, int n_cached, int qi,
+                                               WaitQ wait_q) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int cpl = HD / 32, KV4 = HD / 32;
-    const int visible = pos + 1;
-    const __half* K = a.kv.k + a.kv.offset(m, layer, 0, w.kvh, 0);
-    const __half* V = a.kv.v + a.kv.offset(m, layer, 0, w.kvh, 0);
+    const int visible = n_cached + 1;
+    const __half* K = kv.k + kv.offset(m, layer, 0, w.kvh, 0);
+    const __half* V = kv.v + kv.offset(m, layer, 0, w.kvh, 0);
+    const float* qs = s.qs + qi * HD;
     const float scale = 1.0f / sqrtf((float)HD);
     const int sub = lane & 3, tl = lane >> 2;
     constexpr int kRound = kMegaConsumerWarps * 16;  // positions per round
@@ -634,7 +738,7 @@ __device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShar
 #pragma unroll
             for (int c = 0; c < KV4; c++) {
                 const uint32_t ww[4] = {cur.kreg[st][c].x, cur.kreg[st][c].y, cur.kreg[st][c].z, cur.kreg[st][c].w};
-                const float* qv = s.qs + sub * (HD / 4) + c * 8;
+                const float* qv = qs + sub * (HD / 4) + c * 8;
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[i]));
@@ -669,20 +773,25 @@ __device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShar
         }
         m_w = m_new;
     }
-    // the newest position: key and value from shared memory, handled by one warp as a round of a single position
-    if (warp == (visible - 1) % kMegaConsumerWarps) {
-        float dot = 0.f;
+    // the new positions: keys and values from shared memory, each handled by one warp as a round of a single position
 #pragma unroll
-        for (int c = 0; c < cpl; c++) dot = fmaf(s.qs[lane * cpl + c], __half2float(s.kn[lane * cpl + c]), dot);
-        const float sn = warp_sum(dot) * scale;
-        const float m_new = fmaxf(m_w, sn);
-        const float corr = m_w == -INFINITY ? 0.f : __expf(m_w - m_new);
-        const float pn = __expf(sn - m_new);
-        l_w = l_w * corr + pn;
+    for (int j = 0; j < NP; j++) {
+        if (j <= qi && warp == (n_cached + j) % kMegaConsumerWarps) {
+            const __half* kn = s.kn + j * HD;
+            const __half* vn = s.vn + j * HD;
+            float dot = 0.f;
 #pragma unroll
-        for (int c = 0; c < 4; c++)
-            if (c < cpl) acc[c] = fmaf(pn, __half2float(s.vn[lane * cpl + c]), acc[c] * corr);
-        m_w = m_new;
+            for (int c = 0; c < cpl; c++) dot = fmaf(qs[lane * cpl + c], __half2float(kn[lane * cpl + c]), dot);
+            const float sn = warp_sum(dot) * scale;
+            const float m_new = fmaxf(m_w, sn);
+            const float corr = m_w == -INFINITY ? 0.f : __expf(m_w - m_new);
+            const float pn = __expf(sn - m_new);
+            l_w = l_w * corr + pn;
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+                if (c < cpl) acc[c] = fmaf(pn, __half2float(vn[lane * cpl + c]), acc[c] * corr);
+            m_w = m_new;
+        }
     }
     // merge the per-warp partial results (a warp that saw no position carries max = -inf, sum = 0)
 #pragma unroll
@@ -701,14 +810,14 @@ __device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShar
             num = fmaf(s.part[x * HD + tid], f, num);
             den = fmaf(s.red[kMegaConsumerWarps + x], f, den);
         }
-        xa_store(reinterpret_cast<__half*>(s.ctx), tid, den > 0.f ? __fdividef(num, den) : 0.f);  // the A operand of the Wo products
+        xa_store<NP>(reinterpret_cast<__half*>(s.ctx), tid, den > 0.f ? __fdividef(num, den) : 0.f, qi);  // the A operand of the Wo products
     }
     consumer_sync();
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel
 
-template <int HD>
+template <int HD, int WT>
 __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs a) {
     extern __shared__ __align__(128) uint8_t mega_smem[];
     const MegaShared s = mega_carve(mega_smem, a);
@@ -742,8 +851,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             uint64_t keep_policy;
             asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep_policy));
             // head rows behind the first (n_slots - 1) chunks: what still has to come from memory when the head begins
-            const long long tail_off = (long long)min(w.v_n, (p.n_slots - 1) * p.head_rpc) * p.row_bytes;
-            const long long tail_bytes = (long long)w.v_n * p.row_bytes - tail_off;
+            const long long tail_off = (long long)min(w.v_n, (p.n_slots - 1) * p.head_rpc) * p.head_row_bytes;
+            const long long tail_bytes = (long long)w.v_n * p.head_row_bytes - tail_off;
             auto issue = [&](long long off, int bytes) {
                 if (mega_aborting(s) || *reinterpret_cast<volatile int*>(s.stop)) return;  // nothing more is copied
 #ifdef MEGA_FINE_TRACE
@@ -782,13 +891,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                         long long off = (long long)l * p.layer_bytes;
                         if (w.in_group) issue_stage(off, w.s1_n, p.s1_ipc, 2 * p.row_bytes);
                         off += p.s1_bytes;
-                        if (w.in_group) issue_stage(off, p.rpb, p.s2_rpc, HD * 2);
+                        if (w.in_group) issue_stage(off, p.rpb, p.s2_rpc, p.wo_row_bytes);
                         off += p.s2_bytes;
                         issue_stage(off, w.h_n, p.s3a_ipc, 2 * p.row_bytes); off += p.s3a_bytes;
                         issue_stage(off, w.d_n, p.s3b_rpc, p.down_row_bytes);
                     }
                 }
-                issue_stage(head_off, w.v_n, p.head_rpc, p.row_bytes);
+                issue_stage(head_off, w.v_n, p.head_rpc, p.head_row_bytes);
             }
             // every copy that was issued must have landed before the CTA may exit: walk the last n_slots chunks backwards
             MegaCursor k = c;
@@ -870,12 +979,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         if (n_pend) mega_release_deferred(a, s, pend_from, n_pend);
         n_pend = 0;
     };
-    auto chunk_products = [&](int rows, int n_kb, const uint8_t* xa, bool defer) {
+    auto chunk_products = [&](int rows, int n_kb, const uint8_t* xa, bool defer, bool is_head = false) {
         const uint8_t* ch = mega_acquire(a, s, c, n_chunk++);
         FINE();
         float* partial = s.partial + par * kMegaChunkRows;
         par ^= 1;
-        lg_parts = mega_chunk_dots(ch, rows, n_kb, xa, partial, warp, lane);
+        if (WT != WT_F16 && is_head && p.wt_head == WT_F16) lg_parts = mega_chunk_dots<WT_F16>(ch, rows, n_kb, xa, partial, warp, lane);  // an fp16 head on quantised layers
+        else lg_parts = mega_chunk_dots<WT>(ch, rows, n_kb, xa, partial, warp, lane);
         if (defer) {
             if (n_pend == 0) pend_from = c;
             n_pend++;
@@ -945,7 +1055,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     stamp(step);
                     // ---- S2: attention of this CTA's head (the cached K/V rows are requested before the query is awaited)
                     FINE();
-                    mega_attention<HD>(a, s, w, l, pos, [&]() {
+                    mega_attention<HD>(a, s, w, m, a.kv, l, pos, 0, [&]() {
                         // q of this CTA's head, k and v of the KV head: pairs in the order S1 published them
                         FINE();
                         if (tid < 3 * half) {
@@ -1067,7 +1177,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         for (int r0 = 0; r0 < w.v_n; r0 += p.head_rpc) {
             const int nrows = min(p.head_rpc, w.v_n - r0);
             FINE();
-            float* sums = chunk_products(nrows, d >> 5, s.xa, r0 + 2 * p.head_rpc >= w.v_n);
+            float* sums = chunk_products(nrows, d >> 5, s.xa, r0 + 2 * p.head_rpc >= w.v_n, true);
             // thread r keeps the best of rows r0 + r over the chunks (ascending rows: '>' keeps the first maximum)
             if (tid < nrows) {
                 const float v = mega_take_sum(sums, lg_parts, tid);
@@ -1159,34 +1269,83 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
 
 // ------------------------------------------------------------------------------------------------ pack builder
 
+// One source matrix: row-major [rows][cols] fp16, or the split GGUF storage of the engine (Q8_0: int8 [rows][cols] +
+// fp16 scales [rows][cols/32]; Q4_0: 16-byte nibble groups [rows][cols/32] + scales).
+struct PackMatrix {
+    const void* data;
+    const __half* scales;
+};
 struct PackSources {
-    const __half* const* wq;  // per-layer device pointers (row-major [out, in] fp16)
-    const __half* const* wk;
-    const __half* const* wv;
-    const __half* const* wo;
-    const __half* const* w1;
-    const __half* const* w2;
-    const __half* const* w3;
-    const __half* lm_head;
+    const PackMatrix* wq;  // per-layer device arrays
+    const PackMatrix* wk;
+    const PackMatrix* wv;
+    const PackMatrix* wo;
+    const PackMatrix* w1;
+    const PackMatrix* w2;
+    const PackMatrix* w3;
+    PackMatrix lm_head;
 };
 
-// Writes `nr` rows of K halves each in the order the products read them: for every block of 32 columns, for every row,
-// 64 bytes = four 16-byte pieces; piece t holds columns {2t, 2t+1, 2t+8, 2t+9, 16+2t, 17+2t, 24+2t, 25+2t} of the block
-// (A registers of two m16n8k16 steps for the lanes with that t).  row_of(r) returns the row's first element or
-// null for a row of zeros.
+// Where a row starts: matrix `m` of `cols` columns, row `row`, first column `col0` (a multiple of 32).
+struct PackRow {
+    const uint8_t* data;     // null: a row of zeros
+    const __half* scales;
+};
+__device__ __forceinline__ PackRow pack_row(int wt, const PackMatrix& m, int cols, size_t row, int col0) {
+    PackRow r;
+    const uint8_t* d = static_cast<const uint8_t*>(m.data);
+    if (wt == WT_Q8_0) r.data = d + row * cols + col0;
+    else if (wt == WT_Q4_0) r.data = d + (row * (cols / 32) + col0 / 32) * 16;
+    else r.data = d + (row * cols + col0) * 2;
+    r.scales = m.scales ? m.scales + row * (cols / 32) + col0 / 32 : nullptr;
+    return r;
+}
+
+// Writes `nr` rows of K columns each in the order the products read them: for every block of 32 columns, for every row,
+// four pieces; piece t holds columns {2t, 2t+1, 2t+8, 2t+9, 16+2t, 17+2t, 24+2t, 25+2t} of the block (the A registers of
+// two m16n8k16 steps for the lanes with that t): 16 bytes of fp16, 8 int8 of a Q8_0 block, or the 4 bytes 2t, 2t+1,
+// 2t+8, 2t+9 of a Q4_0 block (whose low and high nibbles are exactly those eight columns).  The quantised types put
+// the scales [block][row] behind the data.  row_of(r) names the row's source.
 template <class RowOf>
-__device__ __forceinline__ void pack_tiled(uint8_t* dst, int nr, int K, RowOf row_of) {
+__device__ __forceinline__ void pack_tiled(int wt, uint8_t* dst, int nr, int K, RowOf row_of) {
     const int n_kb = K >> 5;
+    const int piece = wt == WT_Q8_0 ? 8 : wt == WT_Q4_0 ? 4 : 16;
     for (int i = threadIdx.x; i < n_kb * nr * 4; i += blockDim.x) {
         const int t = i & 3, q = i >> 2;
         const int kb = q / nr, r = q - kb * nr;
-        const __half* src = row_of(r);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (src) {
-            const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src + (size_t)kb * 32);
-            v = make_uint4(s32[t], s32[t + 4], s32[t + 8], s32[t + 12]);
+        const PackRow src = row_of(r);
+        uint8_t* out = dst + ((size_t)q * 4 + t) * piece;
+        if (wt == WT_F16) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (src.data) {
+                const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src.data + (size_t)kb * 64);
+                v = make_uint4(s32[t], s32[t + 4], s32[t + 8], s32[t + 12]);
+            }
+            *reinterpret_cast<uint4*>(out) = v;
+        } else if (wt == WT_Q8_0) {
+            uint2 v = make_uint2(0, 0);
+            if (src.data) {
+                const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src.data + (size_t)kb * 32);  // pairs of columns
+                v.x = (uint32_t)s16[t] | ((uint32_t)s16[t + 4] << 16);
+                v.y = (uint32_t)s16[t + 8] | ((uint32_t)s16[t + 12] << 16);
+            }
+            *reinterpret_cast<uint2*>(out) = v;
+        } else {
+            uint32_t v = 0x88888888u;  // nibble 8 = value 0
+            if (src.data) {
+                const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src.data + (size_t)kb * 16);  // pairs of bytes
+                v = (uint32_t)s16[t] | ((uint32_t)s16[t + 4] << 16);
+            }
+            *reinterpret_cast<uint32_t*>(out) = v;
         }
-        *reinterpret_cast<uint4*>(dst + ((size_t)q * 64 + t * 16)) = v;
+    }
+    if (wt != WT_F16) {
+        __half* sc = reinterpret_cast<__half*>(dst + (size_t)n_kb * nr * 4 * piece);
+        for (int i = threadIdx.x; i < n_kb * nr; i += blockDim.x) {
+            const int kb = i / nr, r = i - kb * nr;
+            const PackRow src = row_of(r);
+            sc[i] = src.data ? src.scales[kb] : __float2half(0.f);
+        }
     }
 }
 
@@ -1196,6 +1355,7 @@ __global__ void k_build_pack(PackSources src, MegaPlan p, ModelDims m, uint8_t* 
     const int cta = blockIdx.x;
     uint8_t* blob = pack + (size_t)cta * p.cta_bytes;
     const int d = m.d_model, hd = m.head_dim;
+    const int wt = p.wt_layer;
     const MegaShare w = mega_share(m, p, cta);
     for (int l = 0; l < m.n_layer; l++) {
         uint8_t* base = blob + (size_t)l * p.layer_bytes;
@@ -1203,11 +1363,11 @@ __global__ void k_build_pack(PackSources src, MegaPlan p, ModelDims m, uint8_t* 
         if (w.in_group)
             for (int i0 = 0; i0 < w.s1_n; i0 += p.s1_ipc) {
                 const int n = min(p.s1_ipc, w.s1_n - i0);
-                pack_tiled(base + (size_t)i0 * 2 * p.row_bytes, 2 * n, d, [&](int r) {
+                pack_tiled(wt, base + (size_t)i0 * 2 * p.row_bytes, 2 * n, d, [&](int r) {
                     int kind, row0, row1, idx;
                     mega_s1_rows(m, p, w.kvh, w.s1_begin + i0 + (r >> 1), kind, row0, row1, idx);
-                    const __half* W = kind == 0 ? src.wq[l] : kind == 1 ? src.wk[l] : src.wv[l];
-                    return W + (size_t)((r & 1) ? row1 : row0) * d;
+                    const PackMatrix& W = kind == 0 ? src.wq[l] : kind == 1 ? src.wk[l] : src.wv[l];
+                    return pack_row(wt, W, d, (size_t)((r & 1) ? row1 : row0), 0);
                 });
             }
         base += p.s1_bytes;
@@ -1215,30 +1375,30 @@ __global__ void k_build_pack(PackSources src, MegaPlan p, ModelDims m, uint8_t* 
         if (w.in_group)
             for (int r0 = 0; r0 < p.rpb; r0 += p.s2_rpc) {
                 const int n = min(p.s2_rpc, p.rpb - r0);
-                pack_tiled(base + (size_t)r0 * hd * 2, n, hd, [&](int r) {
+                pack_tiled(wt, base + (size_t)r0 * p.wo_row_bytes, n, hd, [&](int r) {
                     const int orow = w.blk * p.rpb + r0 + r;
-                    return orow < d ? src.wo[l] + (size_t)orow * m.q_dim + (size_t)w.head * hd : (const __half*)nullptr;
+                    return orow < d ? pack_row(wt, src.wo[l], m.q_dim, (size_t)orow, w.head * hd) : PackRow{nullptr, nullptr};
                 });
             }
         base += p.s2_bytes;
         // S3: (gate_j, up_j) row pairs
         for (int j0 = 0; j0 < w.h_n; j0 += p.s3a_ipc) {
             const int n = min(p.s3a_ipc, w.h_n - j0);
-            pack_tiled(base + (size_t)j0 * 2 * p.row_bytes, 2 * n, d, [&](int r) {
-                return ((r & 1) ? src.w3[l] : src.w1[l]) + (size_t)(w.h_begin + j0 + (r >> 1)) * d;
+            pack_tiled(wt, base + (size_t)j0 * 2 * p.row_bytes, 2 * n, d, [&](int r) {
+                return pack_row(wt, (r & 1) ? src.w3[l] : src.w1[l], d, (size_t)(w.h_begin + j0 + (r >> 1)), 0);
             });
         }
         base += p.s3a_bytes;
         // S3: this CTA's rows of W2
         for (int r0 = 0; r0 < w.d_n; r0 += p.s3b_rpc) {
             const int n = min(p.s3b_rpc, w.d_n - r0);
-            pack_tiled(base + (size_t)r0 * p.down_row_bytes, n, m.hidden, [&](int r) { return src.w2[l] + (size_t)(w.d_begin + r0 + r) * m.hidden; });
+            pack_tiled(wt, base + (size_t)r0 * p.down_row_bytes, n, m.hidden, [&](int r) { return pack_row(wt, src.w2[l], m.hidden, (size_t)(w.d_begin + r0 + r), 0); });
         }
     }
     uint8_t* hb = blob + (size_t)m.n_layer * p.layer_bytes;
     for (int r0 = 0; r0 < w.v_n; r0 += p.head_rpc) {
         const int n = min(p.head_rpc, w.v_n - r0);
-        pack_tiled(hb + (size_t)r0 * p.row_bytes, n, d, [&](int r) { return src.lm_head + (size_t)(w.v_begin + r0 + r) * d; });
+        pack_tiled(p.wt_head, hb + (size_t)r0 * p.head_row_bytes, n, d, [&](int r) { return pack_row(p.wt_head, src.lm_head, d, (size_t)(w.v_begin + r0 + r), 0); });
     }
 }
 

@@ -7,13 +7,16 @@ from espresso_b200.weight_blob import is_matrix
 
 ABS_TOL = 2e-2   # max-abs logit tolerance (fp16 KV cache, different summation order)
 REL_TOL = 1e-2   # relative tolerance
+# bf16 activations on the tensor-core path carry 8 mantissa bits against fp16's 11: rounding per product is 8x
+# coarser, so the max-abs bound of a bf16 model is 4x the fp16 one (the relative bound stays)
+BF16_ABS_TOL = 8e-2
 
 
-def assert_logits_close(got, ref, what=""):
+def assert_logits_close(got, ref, what="", abs_tol=ABS_TOL):
     got = np.asarray(got, np.float32)
     ref = np.asarray(ref, np.float32)
     err = np.abs(got - ref)
-    assert err.max() <= ABS_TOL, f"{what}: max-abs {err.max():.3e} > {ABS_TOL}"
+    assert err.max() <= abs_tol, f"{what}: max-abs {err.max():.3e} > {abs_tol}"
     rel = np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-12)
     assert rel <= REL_TOL, f"{what}: relative error {rel:.3e} > {REL_TOL}"
 

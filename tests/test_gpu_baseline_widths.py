@@ -11,7 +11,7 @@ import dataclasses
 import numpy as np
 import pytest
 
-from helpers import assert_logits_close, compare_greedy_stream, quantised_pair, upload_all
+from helpers import BF16_ABS_TOL, assert_logits_close, compare_greedy_stream, quantised_pair, upload_all
 
 pytestmark = pytest.mark.gpu
 
@@ -127,12 +127,12 @@ def test_c5_llama3_8b_widths_bf16_64_sequences(rt, oracle_lib):
     streams, _ = eng.generate_batch(prompts, 6)
     assert all(len(t) == 6 for t in streams)
     _check_sequences(oracle_lib, model, prompts, streams, (0, 63))
-    # logits of one sequence after its prompt (single-row kernels read the same bf16 weights)
+    # logits of one sequence after its prompt: the prompt runs through the tensor-core path with bf16 activations
     eng.reset()
     eng.prefill(prompts[5])
     ora = oracle_lib.Runtime(model)
     assert ora.prefill(prompts[5]) == 0
-    assert_logits_close(eng.logits(), ora.logits(), "bf16 8B widths after the prompt")
+    assert_logits_close(eng.logits(), ora.logits(), "bf16 8B widths after the prompt", abs_tol=BF16_ABS_TOL)
     eng.close()
 
 
