@@ -378,11 +378,16 @@ def measure(args, wl: dict, rank: int, local_rank: int, world: int, steps: int, 
             write_synthetic_model(wl["draft"](), dtmp, seed=1235)
             draft = runtime.DecodeEngine.build(dtmp, device=local_rank, flags=flags)
 
+        prefill_s = []  # wall time of every prompt pass (the call returns after the device has finished)
+
         def prefill():
+            t0 = time.perf_counter()
             if n_seq == 1:
                 eng.prefill(prompts[0])
             else:
                 eng.prefill_batch(prompts)
+            torch.cuda.synchronize()
+            prefill_s.append(time.perf_counter() - t0)
 
         sampler = ClockSampler(physical_gpu_index(local_rank))
         step_ms, launches, extra = [], 0, {}
@@ -409,7 +414,8 @@ def measure(args, wl: dict, rank: int, local_rank: int, world: int, steps: int, 
                 launches += eng.timings()["kernel_launches"]
             barrier()
         else:
-            # ---- two-token speculative loop: host-driven passes, timed on the host from the end of prefill ----
+            # ---- two-token speculative loop (one device-driven launch when draft and target share their widths, else
+            # host-driven passes), timed on the host from the end of prefill ----
             for _ in range(warmup):
                 eng.generate_two_token(draft, prompts[0], n_decode)
             barrier()
@@ -421,9 +427,12 @@ def measure(args, wl: dict, rank: int, local_rank: int, world: int, steps: int, 
                 step_ms.append(res.totalDecodeMs)
                 acc.append(res.acceptedFutureTokensPerPass)
                 com.append(res.committedExactTokensPerPass)
-                launches += res.speculativePasses * (eng.timings()["kernel_launches"] + draft.timings()["kernel_launches"])
+                per_call = eng.timings()["kernel_launches"]
+                fused = per_call == 1  # a host-driven verify pass is dozens of launches
+                launches += 1 if fused else res.speculativePasses * (per_call + draft.timings()["kernel_launches"])
             barrier()
             extra["two_token"] = {"accepted_future_tokens_per_pass": statistics.mean(acc), "committed_exact_tokens_per_pass": statistics.mean(com),
+                                  "loop": "one launch of k_spec_mega (draft, two-position verify and commit rule on the device)" if fused else "host-driven passes",
                                   "note": "draft and target are independent random models, so proposals are almost never accepted"}
         clocks = sampler.stop()
         total_ms = sum(step_ms)
@@ -507,6 +516,23 @@ def measure(args, wl: dict, rank: int, local_rank: int, world: int, steps: int, 
                "launches": launches, "clocks": clocks, "roofline": roofline, "extra": extra, "n_seq_per_gpu": n_seq,
                "e2e_value": tokens_all / e2e_total if e2e_total else None,
                "h2d": int(n_seq * n_prompt * 4), "d2h": int(n_seq * n_decode * 4), "steps": steps, "warmup": warmup}
+        if n_seq > 1 and len(prefill_s) > warmup:
+            # prompt processing: rows of a pass = positions x sequences on the tensor-core path; FLOPs = 2 per weight of the
+            # layer matrices per token + the causal attention products (the LM head is not run on prompt tokens)
+            t = statistics.mean(prefill_s[-steps:])
+            toks = n_seq * n_prompt
+            layer_w = cfg.nLayer * (cfg.dModel * (cfg.attentionDim + 2 * cfg.kvDim) + cfg.attentionDim * cfg.dModel
+                                    + (3 if cfg.architecture == "llama" else 2) * cfg.dModel * cfg.hiddenDim)
+            att = cfg.nLayer * 4 * cfg.attentionDim * (n_prompt + 1) / 2
+            tflops = toks * (2 * layer_w / (world if tp else 1) + att / (world if tp else 1)) / t / 1e12
+            peaks = {}
+            if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+                with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                    peaks = json.load(f)
+            sustained = float(peaks.get("bf16_tflops_sustained", 1400.0))
+            out["prefill"] = {"tokens_per_s": toks / t, "ms": t * 1e3, "TFLOPs_per_gpu": tflops, "frac_of_bf16_sustained": tflops / sustained,
+                              "peak_kind": "measured" if peaks else "fallback", "prompt_tokens": toks,
+                              "note": "prefill_batch(): host wall clock around the call incl. prompt upload; passes of up to 256 rows"}
         if full and rank == 0 and draft is None and n_seq == 1:
             st = stage_trace_us(eng, cfg, prompts[0], n_decode, clocks.get("sm_mhz") or 1965.0)
             if st:
@@ -655,7 +681,7 @@ def main() -> None:
         "gpu_launches": r["launches"], "clocks": r["clocks"], "roofline": r["roofline"],
     }
     line.update(r["extra"])
-    for k in ("stage_trace_us", "ms_per_token_gaps"):
+    for k in ("stage_trace_us", "ms_per_token_gaps", "prefill"):
         if k in r:
             line[k] = r[k]
 
@@ -670,6 +696,8 @@ def main() -> None:
                      "sequences_per_gpu": m["n_seq_per_gpu"], "steps": k_steps, "warmup": 1, "gpu_launches": m["launches"],
                      "roofline_whole_step_frac": m["roofline"].get("whole_step", {}).get("frac"), "clocks": m["clocks"],
                      "parallelism": config_of(w2, world)["parallelism"]}
+            if "prefill" in m:
+                entry["prefill"] = m["prefill"]
             if name == "c5":
                 L = w2["cfg"]().nLayer
                 entry["all_reduce"] = {"path": "peer memory (k_tp_sum_peers)" if world > 1 and not os.environ.get("ESP_CUDA_TP_NCCL_ONLY") else ("NCCL" if world > 1 else "none (one GPU)"),

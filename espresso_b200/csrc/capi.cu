@@ -283,6 +283,30 @@ int32_t esp_cuda_generate_two_token(esp_cuda_engine* engine, esp_cuda_engine* dr
     if ((rc = full.select_greedy(&current))) return rc;
     auto t_first = now();
     // `current` is always an exact target token that has been selected but not yet fed to either model.
+    if (full.spec_compatible(dr) && !(eos >= 0 && current == (uint32_t)eos) && eff > 1 && n_prompt + 1 < max_seq) {
+        // draft and target share one plan: the whole loop below runs as one device-driven launch
+        out_tokens[0] = current;
+        int stats[5] = {0, 0, 0, 0, 0};
+        rc = full.run_spec(dr, prompt[n_prompt - 1], current, 1, eff, max_seq, out_tokens, stats);
+        if (rc == ESP_CUDA_OK) {
+            auto t_end = now();
+            *n_out = stats[0];
+            if (result) {
+                result->generated_tokens = stats[0];
+                result->prefill_ms = ms(t0, t_prefill);
+                result->first_token_latency_ms = ms(t_prefill, t_first);
+                result->total_decode_ms = ms(t_prefill, t_end);
+                result->tokens_per_second = stats[0] / std::max(result->total_decode_ms / 1000.0, 1e-9);
+                result->speculative_passes = stats[1];
+                result->committed_exact_tokens_per_pass = stats[1] ? (double)stats[2] / stats[1] : 0.0;
+                result->accepted_future_tokens_per_pass = stats[1] ? (double)stats[3] / stats[1] : 0.0;
+                result->stopped_on_eos = stats[4];
+            }
+            return ESP_CUDA_OK;
+        }
+        // ERR_STATE: nothing ran (the two-position working set does not fit shared memory); the host loop below takes over
+        if (rc != ESP_CUDA_ERR_STATE) return rc;
+    }
     std::vector<uint32_t> draft_backlog;  // committed tokens the draft has not consumed yet
     while (true) {
         // emit `current`

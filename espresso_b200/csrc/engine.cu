@@ -3,6 +3,7 @@
 #include "engine.h"
 #include "batch_kernels.cuh"
 #include "tc_gemm.cuh"
+#include "spec_kernel.cuh"
 
 #include <dlfcn.h>
 #include <nccl.h>
@@ -49,6 +50,7 @@ int tc_tile_for(int rows);
 TcPlan tc_plan(int w_tiles, int rows, int kb, bool may_split_k, bool dual, int sms);
 cudaError_t tc_launch(const TcPlan& plan, bool dual, const CUtensorMap* const* mw, const CUtensorMap& mx, TcArgs a, cudaStream_t s);
 constexpr int kTcMinRows = 9;  // below this the row-batched GEMV stages are used
+constexpr int kPrefillRows = 256;  // rows of a prefill pass on the batched path: every pass streams all the weights once
 
 // ---------------------------------------------------------------------------------------------- kernels
 
@@ -404,7 +406,7 @@ int32_t Engine::init() {
     m_.max_seq = cfg_.max_seq; m_.q_dim = m_.n_head * m_.head_dim; m_.kv_dim = m_.n_kv_head * m_.head_dim;
     m_.n_seq = cfg_.max_batch; m_.eps = cfg_.norm_eps; m_.eos_token = cfg_.eos_token;
 
-    max_rows_ = std::max(cfg_.max_batch, 64);  // rows of one pass: sequences of a batch, or positions of a prefill chunk
+    max_rows_ = std::max(cfg_.max_batch, kPrefillRows);  // rows of one pass: sequences of a batch, or positions of a prefill chunk
     n_splits_ = (m_.max_seq + kAttSplitTokens - 1) / kAttSplitTokens;
     out_stride_ = m_.max_seq;
 
@@ -965,7 +967,7 @@ int32_t Engine::prefill(const uint32_t* tokens, int32_t n) {
     if (!tokens || n <= 0) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "Prompt tokens must not be empty");
     if ((rc = reset())) return rc;
     // the prompt is processed in chunks of rows that share sequence 0 at consecutive positions
-    const int chunk = std::min(max_rows_, tc_ready_ ? 64 : 8);
+    const int chunk = std::min(max_rows_, tc_ready_ ? kPrefillRows : 8);
     std::vector<int> seq(chunk, 0);
     for (int i = 0; i < n; i += chunk) {
         int c = std::min(chunk, n - i);
@@ -1078,12 +1080,30 @@ int32_t Engine::prefill_batch(const uint32_t* tokens, int32_t n_seq, int32_t len
     if (!tokens || len <= 0) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "Prompt tokens must not be empty");
     if (n_seq < 1 || n_seq > cfg_.max_batch) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "n_seq exceeds max_batch");
     if ((rc = reset())) return rc;
-    std::vector<int> seq(n_seq);
-    std::vector<uint32_t> tok(n_seq);
-    for (int s = 0; s < n_seq; s++) seq[s] = s;
-    for (int t = 0; t < len; t++) {
-        for (int s = 0; s < n_seq; s++) tok[s] = tokens[(size_t)s * len + t];
-        if ((rc = feed_rows(n_seq, seq.data(), tok.data(), false, nullptr))) return rc;
+    // A pass carries `c` consecutive positions of every sequence (row = sequence * c + position), as many as the row
+    // budget allows: every pass streams all the weights once, so fewer, fuller passes are what makes prefill fast.
+    const int budget = tc_ready_ ? std::min(max_rows_, kPrefillRows) : n_seq;
+    const int c_max = std::max(1, budget / n_seq);
+    std::vector<int> seq((size_t)n_seq * c_max);
+    std::vector<uint32_t> tok((size_t)n_seq * c_max);
+    int c_last = 1;
+    for (int t = 0; t < len; t += c_max) {
+        const int c = std::min(c_max, len - t);
+        for (int s = 0; s < n_seq; s++)
+            for (int j = 0; j < c; j++) {
+                seq[(size_t)s * c + j] = s;
+                tok[(size_t)s * c + j] = tokens[(size_t)s * len + t + j];
+            }
+        if ((rc = feed_rows(n_seq * c, seq.data(), tok.data(), false, nullptr))) return rc;
+        c_last = c;
+    }
+    // row s must hold the last hidden state of sequence s (decode passes have one row per sequence).  Ascending order is
+    // safe: the source row of sequence s, s * c + c - 1, lies above every destination written before it.
+    if (c_last > 1) {
+        for (int s = 0; s < n_seq; s++)
+            ESP_CUDA_TRY(cudaMemcpyAsync(act_.hidden + (size_t)s * m_.d_model, act_.hidden + ((size_t)s * c_last + c_last - 1) * m_.d_model, sizeof(float) * m_.d_model,
+                                         cudaMemcpyDeviceToDevice, stream_));
+        ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
     }
     return ESP_CUDA_OK;
 }
@@ -1861,6 +1881,127 @@ int32_t Engine::run_mega(int n_steps, int* emitted, float* device_ms, double* fi
         for (int i = 0; i < n; i++) { latencies_ms_.push_back((float)((double)(tt[i] - prev) / 1e6)); prev = tt[i]; }
     }
     h_visible_[0] += n - 1;
+    return ESP_CUDA_OK;
+}
+
+static const void* spec_kernel_for(int head_dim) {
+    if (head_dim == 64) return reinterpret_cast<const void*>(&k_spec_mega<64>);
+    if (head_dim == 128) return reinterpret_cast<const void*>(&k_spec_mega<128>);
+    return reinterpret_cast<const void*>(&k_spec_mega<32>);
+}
+
+int32_t Engine::ensure_norms2() {
+    if (d_norms2_) return ESP_CUDA_OK;
+    const size_t d = (size_t)m_.d_model, rows = (size_t)2 * m_.n_layer + 1;
+    int32_t rc;
+    if ((rc = dev_alloc(owned_, &d_norms2_, rows * 2 * d, false))) return rc;
+    for (int copy = 0; copy < 2; copy++)
+        ESP_CUDA_TRY(cudaMemcpy2DAsync(d_norms2_ + copy * d, 2 * d * sizeof(float), d_norms_, d * sizeof(float), d * sizeof(float), rows, cudaMemcpyDeviceToDevice, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    return ESP_CUDA_OK;
+}
+
+// The two-token kernel serves a target and a draft that are both fp16 Llama models on the persistent-kernel path, on one
+// device, with the same widths: they then share one plan (chunk sizes, work shares, ring) and differ in depth only.
+bool Engine::spec_compatible(const Engine& draft) const {
+    if (!mega_ready_ || !draft.mega_ready_ || tp_size_ > 1 || draft.tp_size_ > 1) return false;
+    if ((cfg_.flags | draft.cfg_.flags) & (ESP_CUDA_FLAG_NO_MEGAKERNEL | ESP_CUDA_FLAG_NO_GRAPH)) return false;
+    if (debug_layer_ >= 0 || draft.debug_layer_ >= 0 || cfg_.device != draft.cfg_.device) return false;
+    const MegaPlan &a = mega_plan_, &b = draft.mega_plan_;
+    if (a.wt_layer != ESP_CUDA_F16 || a.wt_head != ESP_CUDA_F16 || b.wt_layer != ESP_CUDA_F16 || b.wt_head != ESP_CUDA_F16) return false;
+    const ModelDims &x = m_, &y = draft.m_;
+    if (x.d_model != y.d_model || x.n_head != y.n_head || x.n_kv_head != y.n_kv_head || x.head_dim != y.head_dim || x.hidden != y.hidden || x.vocab != y.vocab ||
+        x.eps != y.eps || cfg_.rope_theta != draft.cfg_.rope_theta)
+        return false;
+    return a.n_cta == b.n_cta && a.cph == b.cph && a.slot_bytes == b.slot_bytes && a.s1_ipc == b.s1_ipc && a.s2_rpc == b.s2_rpc && a.s3a_ipc == b.s3a_ipc &&
+           a.s3b_rpc == b.s3b_rpc && a.head_rpc == b.head_rpc && a.layer_bytes == b.layer_bytes;
+}
+
+int32_t Engine::spec_prepare() {
+    if (spec_ready_) return ESP_CUDA_OK;
+    int smem_max = 0;
+    cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, cfg_.device);
+    MegaPlan p = mega_plan_;
+    p.n_slots = 0;
+    for (int ns = mega_plan_.n_slots; ns >= 3; ns--) {  // a stage holds back one slot past its exchange: fewer than three would stall the ring
+        MegaPlan probe = mega_plan_;
+        probe.n_slots = ns;
+        spec_layout(m_, probe);
+        if (probe.smem_bytes <= smem_max) { p = probe; break; }
+    }
+    if (p.n_slots == 0) return fail(ESP_CUDA_ERR_STATE, "two-token kernel: the model's working set does not fit shared memory");
+    const void* kern = spec_kernel_for(m_.head_dim);
+    ESP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes));
+    int occ = 0;
+    ESP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kMegaThreads, p.smem_bytes));
+    if (occ < 1) return fail(ESP_CUDA_ERR_STATE, "two-token kernel: no CTA fits an SM");
+    int32_t rc;
+    spec_arena_words_ = (size_t)kSpecNP * ((size_t)2 * m_.d_model + m_.hidden + (size_t)m_.n_kv_head * 2 * p.group_items + (size_t)p.n_cta) + 16;
+    if ((rc = dev_alloc(owned_, &d_spec_arena_, spec_arena_words_))) return rc;
+    if ((rc = dev_alloc(owned_, &d_spec_out_, (size_t)m_.max_seq + 2))) return rc;
+    if ((rc = dev_alloc(owned_, &d_spec_result_, 16))) return rc;
+    spec_plan_ = p;
+    spec_ready_ = true;
+    return ESP_CUDA_OK;
+}
+
+int32_t Engine::run_spec(Engine& draft, uint32_t prev, uint32_t current, int gen0, int eff, int max_seq, uint32_t* out_tokens, int* stats) {
+    int32_t rc;
+    if (!spec_compatible(draft)) return fail(ESP_CUDA_ERR_STATE, "two-token kernel: draft and target do not share one plan");
+    if (gen0 < 1 || eff <= gen0 || h_visible_[0] < 1 || h_visible_[0] + 1 >= max_seq) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "two-token kernel: nothing left to generate");
+    if ((rc = spec_prepare())) return rc;
+    if ((rc = ensure_norms2())) return rc;
+    if ((rc = draft.ensure_norms2())) return rc;
+    ESP_CUDA_TRY(cudaStreamSynchronize(draft.stream_));  // the draft's prefill ran on its own stream
+    const MegaPlan& p = spec_plan_;
+    SpecArgs sa{};
+    MegaArgs& a = sa.base;
+    a.m = m_; a.plan = p; a.rope = d_rope_;
+    a.x_words = d_spec_arena_;
+    a.mid_sums = a.x_words + (size_t)kSpecNP * m_.d_model;
+    a.act_words = a.mid_sums + (size_t)kSpecNP * m_.d_model;
+    a.qkv_words = a.act_words + (size_t)kSpecNP * m_.hidden;
+    a.cand_words = a.qkv_words + (size_t)kSpecNP * m_.n_kv_head * 2 * p.group_items;
+    a.error = d_spec_result_ + 8;
+    a.spin_limit = mega_spin_limit_;
+    Engine* eng[2] = {&draft, this};
+    for (int i = 0; i < 2; i++) {
+        SpecModel& M = sa.model[i];
+        M.m = eng[i]->m_;
+        M.pack = eng[i]->d_pack_;
+        M.cta_bytes = eng[i]->mega_plan_.cta_bytes;
+        M.norms2 = eng[i]->d_norms2_;
+        M.tok_emb = static_cast<const uint16_t*>(eng[i]->tensors_.at("embeddings/token").data);
+        M.kv = eng[i]->kv_;
+    }
+    sa.out = d_spec_out_;
+    sa.result = d_spec_result_;
+    sa.hidden_out = act_.hidden;
+    sa.prev = prev; sa.current = current;
+    sa.pos = h_visible_[0];
+    sa.gen0 = gen0; sa.eff = eff; sa.max_seq = max_seq;
+    sa.eos_token = m_.eos_token;
+    ESP_CUDA_TRY(cudaMemsetAsync(d_spec_result_, 0, 16 * sizeof(int), stream_));
+    ESP_CUDA_TRY(cudaMemsetAsync(d_spec_arena_, 0, spec_arena_words_ * sizeof(unsigned long long), stream_));
+    void* args[] = {&sa};
+    ESP_CUDA_TRY(cudaLaunchCooperativeKernel(spec_kernel_for(m_.head_dim), dim3(p.n_cta), dim3(kMegaThreads), args, (size_t)p.smem_bytes, stream_));
+    int h[16];
+    ESP_CUDA_TRY(cudaMemcpyAsync(h, d_spec_result_, sizeof(h), cudaMemcpyDeviceToHost, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    launches_last_step_ = 1;
+    timings_.kernel_launches = 1;
+    if (h[8] != 0) {
+        std::ostringstream os;
+        os << "two-token kernel gave up waiting (code " << h[8] << ": 3 = weight chunk, 4 = ring slot, 5/9 = layer output words, 6 = q/k/v words, 7 = attention sums, 8 = activation words, 10 = arg-max words)";
+        return fail(ESP_CUDA_ERR_TIMEOUT, os.str());
+    }
+    const int n = h[0];
+    if (n <= gen0 || n > eff) return fail(ESP_CUDA_ERR_CUDA, "two-token kernel reported an impossible token count");
+    ESP_CUDA_TRY(cudaMemcpy(out_tokens + gen0, d_spec_out_ + gen0, sizeof(uint32_t) * (size_t)(n - gen0), cudaMemcpyDeviceToHost));
+    for (int i = 0; i < 5; i++) stats[i] = h[i];
+    h_visible_[0] = h[5];
+    draft.h_visible_[0] = h[6];
+    pending_verify_ = 0;
     return ESP_CUDA_OK;
 }
 

@@ -76,6 +76,11 @@ public:
     int32_t debug_dump(int32_t stage, float* out, int32_t capacity);
     int32_t get_timings(esp_cuda_timings* out);
     int32_t set_wait_limit(uint32_t spins);
+    // Exact two-token generation as one device-driven launch (spec_kernel.cuh).  `draft` must pass spec_compatible().
+    // out_tokens[0 .. gen0) are already emitted (`current` is the newest of them, `prev` the token before it); the call
+    // appends up to eff - gen0 more and fills stats[0..4] = tokens in total, passes, committed, accepted, stopped on EOS.
+    bool spec_compatible(const Engine& draft) const;
+    int32_t run_spec(Engine& draft, uint32_t prev, uint32_t current, int gen0, int eff, int max_seq, uint32_t* out_tokens, int* stats);
 
     const esp_cuda_config& config() const { return cfg_; }
     int visible(int seq) const { return h_visible_[seq]; }
@@ -104,6 +109,8 @@ private:
     size_t gemv_smem(int type, int K, bool with_tmp) const;
     int32_t build_mega();   // packs the weights for the persistent decode kernel when the model qualifies
     int32_t run_mega(int n_steps, int* emitted, float* device_ms, double* first_token_ms);
+    int32_t ensure_norms2();  // the gain vectors twice over, as the two-position kernel reads them
+    int32_t spec_prepare();   // plan, arena and result block of the two-position kernel
 
     esp_cuda_config cfg_;
     ModelDims m_{};
@@ -180,6 +187,14 @@ private:
     std::vector<float> latencies_ms_;              // per-token latencies of sequence 0, most recent generation
     std::vector<cudaEvent_t> step_events_;         // one per step of a decode loop of the per-stage kernels
     int mega_trace_cta_ = 0;
+    // two-token kernel (built on first use)
+    bool spec_ready_ = false;
+    MegaPlan spec_plan_{};
+    float* d_norms2_ = nullptr;
+    unsigned long long* d_spec_arena_ = nullptr;
+    size_t spec_arena_words_ = 0;
+    uint32_t* d_spec_out_ = nullptr;   // [max_seq + 1] emitted tokens
+    int* d_spec_result_ = nullptr;     // [16]: results [0..7], error word [8]
     esp_cuda_timings timings_{};
     int launches_last_step_ = 0;
 };

@@ -379,7 +379,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
         int best_i = 0x7fffffff;
         for (int r0 = 0; r0 < w.v_n; r0 += p.head_rpc) {
             const int nrows = min(p.head_rpc, w.v_n - r0);
-            float* sums = chunk_products(nrows, d >> 5, s.xa, r0 + 2 * p.head_rpc >= w.v_n);
+            float* sums = chunk_products(nrows, d >> 5, s.xa, r0 + p.head_rpc >= w.v_n);
             if (hr < nrows) {
                 const float v = mega_take_sum(sums + hq * kMegaChunkRows, lg_parts, hr);
                 if (v > best_v) { best_v = v; best_i = w.v_begin + r0 + hr; }
@@ -439,6 +439,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
     int P = sa.pos;
     int passes = 0, committed = 0, accepted = 0, hit_eos = 0, row_sel = 0;
     int visible = sa.pos;  // tokens of the target's context that are committed
+    int draft_visible = sa.pos;  // positions the draft has processed
     const bool writer = blockIdx.x == 0 && tid == 0;
     auto is_eos = [&](uint32_t t) { return sa.eos_token >= 0 && t == (uint32_t)sa.eos_token; };
     while (true) {
@@ -446,6 +447,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
         passes++;
         uint32_t d0, proposed, next, future;
         forward(sa.model[0], prev, current, P - 1, d0, proposed);
+        draft_visible = P + 1;
         if (s.red[63] != 0.f) break;
         forward(sa.model[1], current, proposed, P, next, future);
         if (s.red[63] != 0.f) break;
@@ -482,7 +484,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
             sa.result[3] = accepted;
             sa.result[4] = hit_eos;
             sa.result[5] = visible;
-            sa.result[6] = P;  // the draft has processed every committed token but the newest
+            sa.result[6] = draft_visible;
             sa.result[7] = row_sel;
         }
     }

@@ -62,3 +62,32 @@ def upload_all(engine, uploads):
     for name, kind, arr in uploads:
         engine.load_tensor(name, kind, arr)
     engine.finalize()
+
+
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even fp32 -> bf16, returned as the 16 stored bits."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+
+
+def dense_pair(rt, oracle_lib, cfg, kind="f16", max_batch=1, seed=1234):
+    """Engine and oracle model holding the same seeded weights in a 16-bit storage type (f16 or bf16)."""
+    from espresso_b200.synthetic import synthetic_tensor
+    from espresso_b200.weight_blob import is_matrix, tensor_shapes
+
+    eng = rt.DecodeEngine.empty(cfg, max_batch=max_batch)
+    model = oracle_lib.Model(cfg.to_metadata())
+    for name, shape in tensor_shapes(cfg).items():
+        vals = synthetic_tensor(cfg, name, shape, seed)
+        wide = is_matrix(name) or name.startswith("embeddings/")
+        if kind == "bf16" and wide:
+            bits = to_bf16_bits(vals)
+            eng.load_tensor(name, "bf16", bits)
+            model.set_tensor(name, (bits.astype(np.uint32) << np.uint32(16)).view(np.float32).reshape(shape))
+        else:
+            h = vals.astype(np.float16)
+            eng.load_tensor(name, "f16", h)
+            model.set_tensor(name, h.astype(np.float32))
+        del vals
+    eng.finalize()
+    return eng, model

@@ -11,7 +11,7 @@ import dataclasses
 import numpy as np
 import pytest
 
-from helpers import BF16_ABS_TOL, assert_logits_close, compare_greedy_stream, quantised_pair, upload_all
+from helpers import BF16_ABS_TOL, assert_logits_close, compare_greedy_stream, dense_pair, quantised_pair, upload_all
 
 pytestmark = pytest.mark.gpu
 
@@ -22,35 +22,6 @@ def rt():
 
     runtime.load_library()
     return runtime
-
-
-def _to_bf16_bits(x: np.ndarray) -> np.ndarray:
-    """Round-to-nearest-even fp32 -> bf16, returned as the 16 stored bits."""
-    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
-    return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
-
-
-def _dense_pair(rt, oracle_lib, cfg, kind, max_batch, seed=1234):
-    """Engine and oracle model holding the same seeded weights in a 16-bit storage type (f16 or bf16)."""
-    from espresso_b200.synthetic import synthetic_tensor
-    from espresso_b200.weight_blob import is_matrix, tensor_shapes
-
-    eng = rt.DecodeEngine.empty(cfg, max_batch=max_batch)
-    model = oracle_lib.Model(cfg.to_metadata())
-    for name, shape in tensor_shapes(cfg).items():
-        vals = synthetic_tensor(cfg, name, shape, seed)
-        wide = is_matrix(name) or name.startswith("embeddings/")
-        if kind == "bf16" and wide:
-            bits = _to_bf16_bits(vals)
-            eng.load_tensor(name, "bf16", bits)
-            model.set_tensor(name, (bits.astype(np.uint32) << np.uint32(16)).view(np.float32).reshape(shape))
-        else:
-            h = vals.astype(np.float16)
-            eng.load_tensor(name, "f16", h)
-            model.set_tensor(name, h.astype(np.float32))
-        del vals
-    eng.finalize()
-    return eng, model
 
 
 def _check_sequences(oracle_lib, model, prompts, streams, which, max_near=2):
@@ -83,7 +54,7 @@ def test_c3_gpt2_256_sequences_context_past_256(rt, oracle_lib):
     from espresso_b200.synthetic import synthetic_prompt
 
     cfg = dataclasses.replace(gpt2_117m(), nLayer=2, name="gpt2-2l")
-    eng, model = _dense_pair(rt, oracle_lib, cfg, "f16", 256)
+    eng, model = dense_pair(rt, oracle_lib, cfg, "f16", 256)
     prompts = np.stack([synthetic_prompt(cfg.vocab, 64, stream=s) for s in range(256)])
     streams, _ = eng.generate_batch(prompts, 200)
     assert min(len(t) for t in streams) >= 1 and max(len(t) for t in streams) == 200  # 50256 may end a sequence early
@@ -122,7 +93,7 @@ def test_c5_llama3_8b_widths_bf16_64_sequences(rt, oracle_lib):
     from espresso_b200.synthetic import synthetic_prompt
 
     cfg = dataclasses.replace(llama3_8b(max_seq=128), nLayer=2, name="llama3-8b-2l")
-    eng, model = _dense_pair(rt, oracle_lib, cfg, "bf16", 64)
+    eng, model = dense_pair(rt, oracle_lib, cfg, "bf16", 64)
     prompts = np.stack([synthetic_prompt(cfg.vocab, 12, stream=s) for s in range(64)])
     streams, _ = eng.generate_batch(prompts, 6)
     assert all(len(t) == 6 for t in streams)

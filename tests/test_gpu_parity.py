@@ -8,7 +8,7 @@ import os
 import numpy as np
 import pytest
 
-from helpers import ABS_TOL, assert_logits_close, compare_greedy_stream, quantised_pair, upload_all
+from helpers import ABS_TOL, assert_logits_close, compare_greedy_stream, dense_pair, quantised_pair, upload_all
 
 pytestmark = pytest.mark.gpu
 
@@ -187,6 +187,51 @@ def test_prefill_equals_token_by_token(rt, tmp_models):
     # the chunked prefill runs on the tensor cores with 16-bit activation rows, the single steps on the GEMV path
     assert_logits_close(a, b, "chunked prefill vs token by token")
     assert eng.visible_token_count() == 21
+    eng.close()
+
+
+def test_long_prefill_in_256_row_passes_equals_token_by_token(rt, oracle_lib):
+    """A 300-token prompt (one full 256-row pass and a ragged one) on a head_dim-128 GQA model: same logits as feeding
+    the tokens one by one, and as the oracle."""
+    from espresso_b200.model_config import MultiModelConfig
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = MultiModelConfig("gqa-hd128", 2, 4, 2, 512, 128, 1024, 640, 384, 1e-5, 500000.0, None, "llama")
+
+    eng, model = dense_pair(rt, oracle_lib, cfg)
+    prompt = synthetic_prompt(cfg.vocab, 300)
+    eng.prefill(prompt)
+    a = eng.logits()
+    assert eng.visible_token_count() == 300
+    ora = oracle_lib.Runtime(model)
+    assert ora.prefill(prompt) == 0
+    assert_logits_close(a, ora.logits(), "300-token prefill vs oracle")
+    eng.reset()
+    for t in prompt:
+        eng.advance(int(t))
+    assert_logits_close(a, eng.logits(), "300-token prefill vs token by token")
+    eng.close()
+
+
+def test_prefill_batch_packs_positions_and_equals_per_sequence_prefill(rt, oracle_lib):
+    """prefill_batch feeds several positions of every sequence per pass (row = sequence x position); the state it leaves
+    (KV cache, last hidden state per sequence) must be the one a per-sequence prefill leaves."""
+    from espresso_b200.model_config import MultiModelConfig
+    from espresso_b200.synthetic import synthetic_prompt
+
+    cfg = MultiModelConfig("gqa-hd64-batch", 2, 8, 4, 512, 64, 1024, 640, 128, 1e-5, 10000.0, None, "llama")
+    n_seq, n_prompt = 12, 45  # 256 // 12 = 21 positions per pass: passes of 21, 21 and 3 positions
+    eng, model = dense_pair(rt, oracle_lib, cfg, max_batch=n_seq)
+    prompts = np.stack([synthetic_prompt(cfg.vocab, n_prompt, stream=s) for s in range(n_seq)])
+    eng.prefill_batch(prompts)
+    for s in (0, 5, 11):
+        ora = oracle_lib.Runtime(model)
+        assert ora.prefill(prompts[s]) == 0
+        assert_logits_close(eng.logits(s), ora.logits(), f"sequence {s} after the packed prefill")
+    # and decoding continues from that state
+    streams, _ = eng.generate_batch(prompts, 12)
+    for s in (0, 11):
+        compare_greedy_stream(oracle_lib.Runtime(model), prompts[s], streams[s])
     eng.close()
 
 
