@@ -1687,6 +1687,23 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
 
 static int pad128(long long v) { return (int)((v + 127) / 128 * 128); }
 
+// Carves the exchange arena of a persistent kernel for `np` token positions: every array starts on a cache line.
+// Returns the words needed; with `a` != null (a->x_words = arena base) it also sets the pointers.
+static size_t mega_arena_layout(const ModelDims& m, const MegaPlan& p, int np, MegaArgs* a) {
+    auto line = [](size_t words) { return (words + kMegaLineWords - 1) / kMegaLineWords * kMegaLineWords; };
+    size_t o = 0;
+    const size_t x_at = o;   o += line((size_t)np * (p.x_wpc ? (size_t)p.n_cta * p.x_wpc : (size_t)m.d_model));
+    const size_t act_at = o; o += line((size_t)np * (p.act_wpc ? (size_t)p.n_cta * p.act_wpc : (size_t)m.hidden));
+    const size_t mid_at = o; o += line((size_t)np * m.d_model);
+    const size_t qkv_at = o; o += line((size_t)np * m.n_kv_head * 2 * p.group_items);
+    const size_t cand_at = o; o += line((size_t)np * p.n_cta * kMegaCandStride);
+    if (a) {
+        unsigned long long* base = a->x_words;
+        a->x_words = base + x_at; a->act_words = base + act_at; a->mid_sums = base + mid_at; a->qkv_words = base + qkv_at; a->cand_words = base + cand_at;
+    }
+    return o + kMegaLineWords;
+}
+
 template <int WT>
 static const void* mega_kernel_of(int head_dim) {
     if (head_dim == 64) return reinterpret_cast<const void*>(&k_decode_mega<64, WT>);
@@ -1739,6 +1756,11 @@ int32_t Engine::build_mega() {
     p.hpc_max = (m_.hidden + P - 1) / P;
     p.dpc_max = (m_.d_model + P - 1) / P;
     p.vpc_max = (m_.vocab + P - 1) / P;
+    // Exchange arrays: the activation vector gets cache lines per CTA when every reader can poll all of it in one round
+    // (four 16-byte loads per consumer thread); the layer output stays compact (see mega_kernel.cuh).
+    p.x_wpc = 0;
+    p.act_wpc = (p.hpc_max + kMegaLineWords - 1) / kMegaLineWords * kMegaLineWords;
+    if (P * ((p.hpc_max + 1) / 2) > 4 * kMegaConsumers) p.act_wpc = 0;
     p.wt_layer = wt_layer;
     p.wt_head = wt_head;
     p.row_bytes = mega_row_bytes(wt_layer, m_.d_model);
@@ -1784,7 +1806,7 @@ int32_t Engine::build_mega() {
     if ((rc = dev_alloc(owned_, &d_pack_, (size_t)P * p.cta_bytes, false))) return rc;
     if ((rc = dev_alloc(owned_, &d_norms_, (size_t)(2 * m_.n_layer + 1) * m_.d_model, false))) return rc;
     // exchange arena: x words, activation words, q/k/v words per KV head, counted sums, arg-max candidates
-    mega_arena_words_ = (size_t)2 * m_.d_model + m_.hidden + (size_t)m_.n_kv_head * 2 * p.group_items + (size_t)4 * P + 8;
+    mega_arena_words_ = mega_arena_layout(m_, p, 1, nullptr);
     if ((rc = dev_alloc(owned_, &d_mega_arena_, mega_arena_words_))) return rc;
     if ((rc = dev_alloc(owned_, &d_mega_ctl_, 8))) return rc;
     if ((rc = dev_alloc(owned_, &d_mega_trace_, (size_t)kMegaTraceLayer * m_.n_layer + kMegaTraceHead + 4 + 1024))) return rc;
@@ -1835,10 +1857,7 @@ int32_t Engine::run_mega(int n_steps, int* emitted, float* device_ms, double* fi
     a.tok_emb = static_cast<const uint16_t*>(tensors_.at("embeddings/token").data);
     a.rope = d_rope_; a.kv = kv_; a.hidden_io = act_.hidden;
     a.x_words = d_mega_arena_;
-    a.mid_sums = a.x_words + m_.d_model;
-    a.act_words = a.mid_sums + m_.d_model;
-    a.qkv_words = a.act_words + m_.hidden;
-    a.cand_words = a.qkv_words + (size_t)m_.n_kv_head * 2 * p.group_items;
+    mega_arena_layout(m_, p, 1, &a);
     a.error = reinterpret_cast<int*>(d_mega_ctl_ + 2) + 1;
     a.stamps = d_mega_ctl_ + 3;
     a.rs = rs_;
@@ -1930,13 +1949,14 @@ int32_t Engine::spec_prepare() {
         if (probe.smem_bytes <= smem_max) { p = probe; break; }
     }
     if (p.n_slots == 0) return fail(ESP_CUDA_ERR_STATE, "two-token kernel: the model's working set does not fit shared memory");
+    if (kSpecNP * p.n_cta * ((p.hpc_max + 1) / 2) > 4 * kMegaConsumers) p.act_wpc = 0;  // two positions no longer fit one polling round
     const void* kern = spec_kernel_for(m_.head_dim);
     ESP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes));
     int occ = 0;
     ESP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kMegaThreads, p.smem_bytes));
     if (occ < 1) return fail(ESP_CUDA_ERR_STATE, "two-token kernel: no CTA fits an SM");
     int32_t rc;
-    spec_arena_words_ = (size_t)kSpecNP * ((size_t)2 * m_.d_model + m_.hidden + (size_t)m_.n_kv_head * 2 * p.group_items + (size_t)p.n_cta) + 16;
+    spec_arena_words_ = mega_arena_layout(m_, p, kSpecNP, nullptr);
     if ((rc = dev_alloc(owned_, &d_spec_arena_, spec_arena_words_))) return rc;
     if ((rc = dev_alloc(owned_, &d_spec_out_, (size_t)m_.max_seq + 2))) return rc;
     if ((rc = dev_alloc(owned_, &d_spec_result_, 16))) return rc;
@@ -1958,10 +1978,7 @@ int32_t Engine::run_spec(Engine& draft, uint32_t prev, uint32_t current, int gen
     MegaArgs& a = sa.base;
     a.m = m_; a.plan = p; a.rope = d_rope_;
     a.x_words = d_spec_arena_;
-    a.mid_sums = a.x_words + (size_t)kSpecNP * m_.d_model;
-    a.act_words = a.mid_sums + (size_t)kSpecNP * m_.d_model;
-    a.qkv_words = a.act_words + (size_t)kSpecNP * m_.hidden;
-    a.cand_words = a.qkv_words + (size_t)kSpecNP * m_.n_kv_head * 2 * p.group_items;
+    mega_arena_layout(m_, p, kSpecNP, &a);
     a.error = d_spec_result_ + 8;
     a.spin_limit = mega_spin_limit_;
     Engine* eng[2] = {&draft, this};

@@ -52,6 +52,16 @@ constexpr unsigned kMegaSpinLimit = 1u << 21;      // default attempts per wait 
 constexpr int kMegaTraceLayer = 10;                // stamps per layer
 constexpr int kMegaTraceHead = 4;                  // stamps of the head
 constexpr int kMegaChunkRows = 256;                // most rows of one chunk (16 tiles of 16 rows)
+#ifndef MEGA_CAND_STRIDE
+#define MEGA_CAND_STRIDE 16
+#endif
+// Which exchanges give every CTA cache lines of its own (see mega_read_lines) is the plan's choice (x_wpc / act_wpc > 0).
+// Measured on the 6-layer d768 model against compact arrays: arg-max candidates -4.6 us per token, activation vector
+// -1.4 us, layer output x +0.3 us (five words per CTA: three times as many lines to poll for little contention saved).
+// On the 22-layer d2048 model, whose activation vector needs two polling rounds either way, lines per CTA cost 1.8 us
+// per layer.  So: candidates always, the activation vector when all of it is polled in one round, x never.
+constexpr int kMegaLineWords = 16;  // 8-byte words of a 128-byte cache line
+constexpr int kMegaCandStride = MEGA_CAND_STRIDE;  // 8-byte words between the arg-max candidates of two CTAs (16 = a cache line each)
 constexpr float kMegaFix = 4294967296.0f;          // counted sums: fixed point with 32 fractional bits
 constexpr float kMegaUnfix = 2.3283064365386963e-10f;
 
@@ -65,6 +75,7 @@ struct MegaPlan {
     int s1_max;       // largest number of S1 row pairs of a CTA
     int rpb;          // S2: output rows per block
     int hpc_max, dpc_max, vpc_max;  // largest number of FFN units / W2 rows / vocabulary rows of a CTA
+    int x_wpc, act_wpc;  // exchange words reserved per CTA for its elements of x / of the activation vector (whole cache lines); 0 = compact array
     int wt_layer, wt_head;  // storage type of the layer matrices and of the LM head: WT_F16, WT_Q8_0 or WT_Q4_0
     int row_bytes;       // packed bytes of a row of d_model columns of a layer matrix
     int down_row_bytes;  // ... of hidden columns (W2)
@@ -81,7 +92,7 @@ struct MegaPlan {
     long long layer_bytes, head_bytes, cta_bytes;  // packed bytes per CTA: one layer, the head, everything
     int smem_bytes;
     // byte offsets of the shared-memory areas behind the ring (see MegaShared)
-    int off_bar, off_prev, off_key, off_xs, off_xraw, off_xmid, off_rope, off_qs, off_ctx, off_kn, off_vn, off_part, off_red, off_outv, off_flags, off_share;
+    int off_bar, off_prev, off_key, off_xs, off_xraw, off_xmid, off_rope, off_qs, off_ctx, off_kn, off_vn, off_part, off_red, off_outv, off_flags, off_share, off_beg;
 };
 
 // Packed bytes of K columns of one row: fp16, or GGUF blocks of 32 (int8 / nibbles) with one fp16 scale each.
@@ -100,11 +111,11 @@ struct MegaArgs {
     const float2* rope;       // [max_seq][head_dim/2]
     KvLayout kv;
     // exchange arena (zero at launch)
-    unsigned long long* x_words;    // [d_model] tagged: output of a layer
-    unsigned long long* act_words;  // [hidden] tagged: FFN activation
+    unsigned long long* x_words;    // [d_model], or [n_cta][x_wpc] (every CTA's rows in cache lines of its own); tagged: output of a layer
+    unsigned long long* act_words;  // [hidden] or [n_cta][act_wpc]; tagged: FFN activation
     unsigned long long* qkv_words;  // [n_kv_head][2 * group_items] tagged: post-RoPE q / k / v of one token
     unsigned long long* mid_sums;   // [d_model] counted: residual + attention projection
-    unsigned long long* cand_words; // [n_cta] {logit bits, index, 8-bit tag} of each CTA's best row
+    unsigned long long* cand_words; // [n_cta][kMegaCandStride] {logit bits, index, 8-bit tag} of each CTA's best row in word 0
     float* hidden_io;         // [d_model] last hidden state of the sequence (in and out)
     int* error;               // [1] 0 = ok
     unsigned long long* stamps; // [3] globaltimer at kernel start and when the first token is known; number of tokens emitted
@@ -245,6 +256,8 @@ struct MegaShared {
     float* partial;  // [2][kMegaChunkRows] partial row sums of a chunk (alternating halves)
     unsigned long long* key;   // [32] arg-max keys
     struct MegaShare* share;  // this CTA's work shares, computed once
+    int* xbeg;     // [n_cta + 1] first W2 row (= element of x) of every CTA
+    int* hbeg;     // [n_cta + 1] first FFN unit (= element of the activation vector) of every CTA
     int* abort;    // [1] a wait gave up: no more waiting in this CTA
     int* stop;     // [1] the loop ended early (EOS): the producer stops issuing
     unsigned* landed;  // [1] number of chunks whose bytes have arrived (written by the producer warp's watcher lane)
@@ -275,6 +288,8 @@ __device__ __forceinline__ MegaShared mega_carve(uint8_t* base, const MegaArgs& 
     s.stop = s.abort + 1;
     s.landed = reinterpret_cast<unsigned*>(s.abort + 2);
     s.share = reinterpret_cast<MegaShare*>(base + p.off_share);
+    s.xbeg = reinterpret_cast<int*>(base + p.off_beg);
+    s.hbeg = s.xbeg + p.n_cta + 1;
     return s;
 }
 
@@ -298,6 +313,7 @@ inline void mega_layout(const ModelDims& m, MegaPlan& p) {
     p.off_outv = take(sizeof(float) * 2 * kMegaChunkRows);
     p.off_flags = take(16);
     p.off_share = take(sizeof(MegaShare));
+    p.off_beg = take(sizeof(int) * 2 * ((size_t)p.n_cta + 1));
     p.smem_bytes = (int)((o + 127) & ~(size_t)127);
 }
 
@@ -423,6 +439,68 @@ __device__ __forceinline__ void mega_read_words(const MegaArgs& a, const MegaSha
                 sink(2 * p, __uint_as_float((unsigned)w[j].x), g[j].x);
                 sink(2 * p + 1, __uint_as_float((unsigned)w[j].y), g[j].y);
             }
+        }
+    }
+}
+
+// Tagged words written line by line: the CTA that owns elements [beg[c], beg[c + 1]) of a vector writes them to the
+// first words of slot c (`wpc` words per slot: whole cache lines, at least the largest share).  Cache lines with a single
+// writer matter: a store to a line that every CTA is polling costs a round of invalidations, and the stores of several
+// writers to one line queue up behind one another (sixteen writers per line made the arg-max exchange take 6 us).
+// `lines` = positions x CTAs (position q's lines follow position q - 1's); the sink receives (q * n + element, value,
+// gain).  `ppl` = pairs of words to read per line = ceil(largest share / 2); every thread takes up to four pairs.
+template <class Sink>
+__device__ __forceinline__ void mega_read_lines(const MegaArgs& a, const MegaShared& s, const unsigned long long* base, int wpc, const int* beg, int n, int lines, int ppl,
+                                                unsigned tag, int code, const float* gain, Sink sink) {
+    const int n_cta = a.plan.n_cta;
+    const int slots = lines * ppl;
+    for (int s0 = 0; s0 < slots; s0 += 4 * kMegaConsumers) {
+        ulonglong2 w[4];
+        float2 g[4];
+        const unsigned long long* src[4];
+        int k0[4], cnt[4];
+        bool ok[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int slot = s0 + j * kMegaConsumers + (int)threadIdx.x;
+            w[j] = make_ulonglong2(0, 0);
+            g[j] = make_float2(1.f, 1.f);
+            cnt[j] = 0; k0[j] = 0; src[j] = base;
+            if (slot < slots) {
+                const int line = (int)((unsigned)slot / (unsigned)ppl), jj = slot - line * ppl;
+                const int q = line >= n_cta ? 1 : 0, cta = line - q * n_cta;  // at most two positions
+                const int first = beg[cta] + 2 * jj;
+                cnt[j] = max(0, min(2, beg[cta + 1] - first));
+                k0[j] = q * n + first;
+                src[j] = base + (size_t)line * wpc + 2 * jj;
+                if (gain && cnt[j] > 0) {
+                    g[j].x = __ldg(gain + k0[j]);
+                    if (cnt[j] > 1) g[j].y = __ldg(gain + k0[j] + 1);
+                }
+            }
+            ok[j] = cnt[j] == 0;
+        }
+        unsigned spins = 0;
+        if (!mega_aborting(s)) {
+            while (true) {
+                bool all = true;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if (!ok[j]) {
+                        w[j] = ld_words2(src[j]);
+                        ok[j] = (unsigned)(w[j].x >> 32) == tag && (cnt[j] < 2 || (unsigned)(w[j].y >> 32) == tag);
+                        all = all && ok[j];
+                    }
+                }
+                if (all) break;
+                if (mega_spin_out(a, s, spins, code)) break;
+                mega_backoff();
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            if (cnt[j] > 0) sink(k0[j], __uint_as_float((unsigned)w[j].x), g[j].x);
+            if (cnt[j] > 1) sink(k0[j] + 1, __uint_as_float((unsigned)w[j].y), g[j].y);
         }
     }
 }
@@ -834,6 +912,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int k = tid; k < m.d_model; k += kMegaThreads) s.prev[k] = 0ull;  // the counted sums are zero at launch
+    for (int c = tid; c <= p.n_cta; c += kMegaThreads) {
+        s.xbeg[c] = mega_share_begin(m.d_model, p.n_cta, c);
+        s.hbeg[c] = mega_share_begin(m.hidden, p.n_cta, c);
+    }
     __syncthreads();
     const MegaShare& w = *s.share;  // read from shared memory wherever it is needed: no registers, no recomputation
     const uint8_t* blob = a.pack + (size_t)blockIdx.x * p.cta_bytes;
@@ -1017,7 +1099,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     if (l == 0) {
                         for (int k = tid; k < d; k += kMegaConsumers) stage_x(s.xraw, k, __half2float(__ushort_as_half(emb_row[k])), __ldg(gain + k), ss);
                     } else {
-                        mega_read_words(a, s, a.x_words, d, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+                        if (p.x_wpc) mega_read_lines(a, s, a.x_words, p.x_wpc, s.xbeg, d, p.n_cta, (p.dpc_max + 1) >> 1, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+                        else mega_read_words(a, s, a.x_words, d, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
                     }
                     FINE();
                     release_pending();  // the W2 chunk of the previous layer
@@ -1107,7 +1190,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     // The arg-max candidate words are used once per token; between two uses a whole model's worth of
                     // weights streams through L2.  Reading them once per layer keeps their lines resident, so that the
                     // token exchange does not start with a round trip to memory.
-                    if (tid < p.n_cta) { unsigned long long keep; asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(keep) : "l"(a.cand_words + tid) : "memory"); }
+                    if (tid < p.n_cta) { unsigned long long keep; asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(keep) : "l"(a.cand_words + (size_t)tid * kMegaCandStride) : "memory"); }
                     const float* gain = a.norms + (size_t)(2 * l + 1) * d;
                     float ss = 0.f;
                     FINE();
@@ -1128,13 +1211,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                         const float g = mega_take_sum(sums, lg_parts, 2 * j) * inv;
                         const float u = mega_take_sum(sums, lg_parts, 2 * j + 1) * inv;
                         // silu(g) = g * sigmoid(g) = 0.5 g (1 + tanh(g / 2))
-                        st_word(a.act_words + w.h_begin + j0 + j, tagged(__fdividef(g, 1.0f + __expf(-g)) * u, seq));
+                        st_word(a.act_words + (p.act_wpc ? (size_t)blockIdx.x * p.act_wpc : (size_t)w.h_begin) + j0 + j, tagged(__fdividef(g, 1.0f + __expf(-g)) * u, seq));
                     }
                 }
                 stamp(step);
                 // ---- the whole activation vector, then this CTA's rows of W2 (+ residual) = the next layer's x
                 FINE();
-                mega_read_words(a, s, a.act_words, m.hidden, seq, 8, nullptr, [&](int k, float v, float) { xa_store(xa_h, k, v); });
+                if (p.act_wpc) mega_read_lines(a, s, a.act_words, p.act_wpc, s.hbeg, m.hidden, p.n_cta, (p.hpc_max + 1) >> 1, seq, 8, nullptr, [&](int k, float v, float) { xa_store(xa_h, k, v); });
+                else mega_read_words(a, s, a.act_words, m.hidden, seq, 8, nullptr, [&](int k, float v, float) { xa_store(xa_h, k, v); });
                 FINE();
                 release_pending();  // the gate/up chunk
                 consumer_sync();
@@ -1144,7 +1228,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     const int nr = min(p.s3b_rpc, w.d_n - r0);
                     float* sums = chunk_products(nr, m.hidden >> 5, s.xa, r0 + p.s3b_rpc >= w.d_n);
                     for (int r = tid; r < nr; r += kMegaConsumers)
-                        st_word(a.x_words + w.d_begin + r0 + r, tagged(mega_take_sum(sums, lg_parts, r) + s.xmid[w.d_begin + r0 + r], seq));
+                        st_word(a.x_words + (p.x_wpc ? (size_t)blockIdx.x * p.x_wpc : (size_t)w.d_begin) + r0 + r, tagged(mega_take_sum(sums, lg_parts, r) + s.xmid[w.d_begin + r0 + r], seq));
                 }
                 stamp(step);
             }
@@ -1166,7 +1250,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             if (step == 0) {
                 for (int k = tid; k < d; k += kMegaConsumers) stage_x(s.xraw, k, __ldcg(a.hidden_io + k), __ldg(fin_gain + k), ss);
             } else {
-                mega_read_words(a, s, a.x_words, d, (unsigned)(step * L), 9, fin_gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+                if (p.x_wpc) mega_read_lines(a, s, a.x_words, p.x_wpc, s.xbeg, d, p.n_cta, (p.dpc_max + 1) >> 1, (unsigned)(step * L), 9, fin_gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+                else mega_read_words(a, s, a.x_words, d, (unsigned)(step * L), 9, fin_gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
             }
             release_pending();  // the W2 chunk of the last layer
             consumer_sync();  // the RMSNorm scale is positive: the arg-max does not need it
@@ -1202,7 +1287,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
             unsigned long long k = 0ull;
 #pragma unroll
             for (int x = 0; x < kMegaConsumerWarps; x++) k = max(k, s.key[x]);
-            st_word(a.cand_words + blockIdx.x, k | tag8);
+            st_word(a.cand_words + (size_t)blockIdx.x * kMegaCandStride, k | tag8);
         }
         stamp(step);
         {
@@ -1211,7 +1296,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 unsigned spins = 0;
                 if (!mega_aborting(s)) {
                     while (true) {
-                        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(k) : "l"(a.cand_words + tid) : "memory");
+                        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(k) : "l"(a.cand_words + (size_t)tid * kMegaCandStride) : "memory");
                         if ((k & 0xffull) == tag8) break;
                         if (mega_spin_out(a, s, spins, 10)) break;
                         mega_backoff();

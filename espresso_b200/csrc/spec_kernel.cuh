@@ -69,6 +69,7 @@ inline void spec_layout(const ModelDims& m, MegaPlan& p) {
     p.off_outv = take(sizeof(float) * 2 * NP * kMegaChunkRows);
     p.off_flags = take(16);
     p.off_share = take(sizeof(MegaShare));
+    p.off_beg = take(sizeof(int) * 2 * ((size_t)p.n_cta + 1));
     p.smem_bytes = (int)((o + 127) & ~(size_t)127);
 }
 
@@ -107,6 +108,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int k = tid; k < NP * m.d_model; k += kMegaThreads) s.prev[k] = 0ull;  // the counted sums are zero at launch
+    for (int c = tid; c <= p.n_cta; c += kMegaThreads) {
+        s.xbeg[c] = mega_share_begin(m.d_model, p.n_cta, c);
+        s.hbeg[c] = mega_share_begin(m.hidden, p.n_cta, c);
+    }
     __syncthreads();
     const MegaShare& w = *s.share;
     const int max_passes = sa.eff - sa.gen0;  // every pass emits at least one token
@@ -250,7 +255,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                         stage_x(s.xraw, k, __half2float(__ushort_as_half(emb_row[k - q * d])), __ldg(gain + k), ss);
                     }
                 } else {
-                    mega_read_words(a, s, a.x_words, NP * d, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+                    if (p.x_wpc) mega_read_lines(a, s, a.x_words, p.x_wpc, s.xbeg, d, NP * p.n_cta, (p.dpc_max + 1) >> 1, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+                    else mega_read_words(a, s, a.x_words, NP * d, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
                 }
                 release_pending();  // the W2 chunk of the previous layer
                 const float2 tot = spec_block_sum2(ss[0], ss[1], s.red);
@@ -326,7 +332,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
             }
             // ---- S3: x_mid = residual + attention projection
             {
-                if (tid < NP * p.n_cta) { unsigned long long keep; asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(keep) : "l"(a.cand_words + tid) : "memory"); }
+                if (tid < NP * p.n_cta) { unsigned long long keep; asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(keep) : "l"(a.cand_words + (size_t)tid * kMegaCandStride) : "memory"); }
                 const float* gain = M.norms2 + (size_t)(2 * l + 1) * NP * d;
                 float ss[NP] = {0.f, 0.f};
                 mega_read_sums(a, s, a.mid_sums, NP * d, m.n_head, 7, gain, [&](int k, float v, float g) { stage_x(s.xmid, k, v, g, ss); });
@@ -343,14 +349,16 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                     const float* sq = sums + q * kMegaChunkRows;
                     const float g = mega_take_sum(sq, lg_parts, 2 * j) * inv[q];
                     const float u = mega_take_sum(sq, lg_parts, 2 * j + 1) * inv[q];
-                    st_word(a.act_words + q * hidden + w.h_begin + j0 + j, tagged(__fdividef(g, 1.0f + __expf(-g)) * u, seq));
+                    st_word(a.act_words + (p.act_wpc ? (size_t)(q * p.n_cta + blockIdx.x) * p.act_wpc : (size_t)q * hidden + w.h_begin) + j0 + j, tagged(__fdividef(g, 1.0f + __expf(-g)) * u, seq));
                 }
             }
             // ---- the whole activation vector of both positions, then this CTA's rows of W2 (+ residual) = the next layer's x
-            mega_read_words(a, s, a.act_words, NP * hidden, seq, 8, nullptr, [&](int k, float v, float) {
+            auto stage_act = [&](int k, float v, float) {
                 const int q = k >= hidden ? 1 : 0;
                 xa_store<NP>(xa_h, k - q * hidden, v, q);
-            });
+            };
+            if (p.act_wpc) mega_read_lines(a, s, a.act_words, p.act_wpc, s.hbeg, hidden, NP * p.n_cta, (p.hpc_max + 1) >> 1, seq, 8, nullptr, stage_act);
+            else mega_read_words(a, s, a.act_words, NP * hidden, seq, 8, nullptr, stage_act);
             release_pending();  // the gate/up chunk
             consumer_sync();
             for (int r0 = 0; r0 < w.d_n; r0 += p.s3b_rpc) {
@@ -359,7 +367,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                 for (int i = tid; i < NP * nr; i += kMegaConsumers) {
                     const int q = i >= nr ? 1 : 0, r = i - q * nr;
                     const int row = w.d_begin + r0 + r;
-                    st_word(a.x_words + q * d + row, tagged(mega_take_sum(sums + q * kMegaChunkRows, lg_parts, r) + s.xmid[q * d + row], seq));
+                    st_word(a.x_words + (p.x_wpc ? (size_t)(q * p.n_cta + blockIdx.x) * p.x_wpc : (size_t)q * d + w.d_begin) + r0 + r, tagged(mega_take_sum(sums + q * kMegaChunkRows, lg_parts, r) + s.xmid[q * d + row], seq));
                 }
             }
         }
@@ -368,7 +376,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
         {
             const float* gain = M.norms2 + (size_t)(2 * L) * NP * d;
             float ss[NP] = {0.f, 0.f};
-            mega_read_words(a, s, a.x_words, NP * d, seq, 9, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+            if (p.x_wpc) mega_read_lines(a, s, a.x_words, p.x_wpc, s.xbeg, d, NP * p.n_cta, (p.dpc_max + 1) >> 1, seq, 9, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+            else mega_read_words(a, s, a.x_words, NP * d, seq, 9, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
             release_pending();  // the W2 chunk of the last layer
             consumer_sync();    // the RMSNorm scale is positive: the arg-max does not need it
         }
@@ -398,7 +407,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
             unsigned long long k = 0ull;
 #pragma unroll
             for (int x = 0; x < kMegaConsumerWarps / NP; x++) k = max(k, s.key[tid * (kMegaConsumerWarps / NP) + x]);
-            st_word(a.cand_words + tid * p.n_cta + blockIdx.x, k | tag8);
+            st_word(a.cand_words + (size_t)(tid * p.n_cta + blockIdx.x) * kMegaCandStride, k | tag8);
         }
         {
             unsigned long long k = 0ull;
@@ -406,7 +415,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                 unsigned spins = 0;
                 if (!mega_aborting(s)) {
                     while (true) {
-                        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(k) : "l"(a.cand_words + tid) : "memory");
+                        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(k) : "l"(a.cand_words + (size_t)tid * kMegaCandStride) : "memory");
                         if ((k & 0xffull) == tag8) break;
                         if (mega_spin_out(a, s, spins, 10)) break;
                         mega_backoff();
