@@ -567,7 +567,9 @@ def tp_matches_single_gpu(rank: int, local_rank: int, world: int) -> bool | None
 
     if world < 2:
         return None
-    cfg = MultiModelConfig("tp-check", 2, 8, 8, 256, 32, 512, 1024, 64, 1e-5, 10000.0, None, "llama")
+    # eight KV heads of 64 channels and 512 hidden units: every shard of a group of 2, 4 or 8 ranks keeps the 64-element
+    # alignment the tensor-core path needs
+    cfg = MultiModelConfig("tp-check", 2, 8, 8, 256, 64, 512, 1024, 64, 1e-5, 10000.0, None, "llama")
     if cfg.nKVHead % world:
         return None
     n_seq, n_prompt, n_decode = 6, 9, 14

@@ -180,10 +180,16 @@ struct RopeArgs {
     const float2* rope;  // [max_seq][head_dim/2] (cos, sin); null for GPT-2
     int layer;
     float* debug;        // optional capture of row 0 (q, k, v as stored)
+    const float* q_norm; // [head_dim] per-head RMSNorm weights applied to q and k before RoPE (Qwen3), or null
+    const float* k_norm;
 };
 
 // grid = (rows, chunks): one thread per rotation pair of q, per rotation pair of k, or per pair of v elements.
+// The head_dim / 2 threads of a head are neighbours inside one CTA (256 is a multiple of 16, 32 and 64), which is what
+// the optional per-head norm (applyPerHeadRMSNormInPlace, Sources/RealModelInference/RealModelInferenceEngine.swift:
+// 6648-6672: v * rsqrt(mean(v^2) + eps) * w, before RoPE) uses for its sum of squares.
 __global__ void __launch_bounds__(kThreads) k_rope_append(const RopeArgs p) {
+    __shared__ float head_ss[kThreads / 32];
     const int r = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
@@ -193,15 +199,32 @@ __global__ void __launch_bounds__(kThreads) k_rope_append(const RopeArgs p) {
     const int half = m.head_dim / 2;
     const int q_pairs = m.q_dim / 2, k_pairs = m.kv_dim / 2;
     const int i = blockIdx.y * kThreads + threadIdx.x;
+    const bool rot = i < q_pairs + k_pairs;
+    const bool is_q = i < q_pairs;
+    const int local = is_q ? i : i - q_pairs;
+    const int head = rot ? local / half : 0, idx = rot ? local - head * half : 0;
+    const int i0 = head * m.head_dim + idx, i1 = i0 + half;
+    float* q = p.q + (size_t)r * m.q_dim;
+    const float* kr = p.k_raw + (size_t)r * m.kv_dim;
+    float v0 = 0.f, v1 = 0.f;
+    if (rot) { v0 = is_q ? q[i0] : kr[i0]; v1 = is_q ? q[i1] : kr[i1]; }
+    if (p.q_norm) {  // uniform over the grid: every thread of the CTA takes part in the barrier
+        float ss = v0 * v0 + v1 * v1;
+        for (int o = (half < 32 ? half : 32) >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (half == 64) {  // a head spans two warps
+            if ((threadIdx.x & 31) == 0) head_ss[threadIdx.x >> 5] = ss;
+            __syncthreads();
+            ss = head_ss[(threadIdx.x >> 5) & ~1] + head_ss[(threadIdx.x >> 5) | 1];
+        }
+        if (rot) {
+            const float inv = 1.0f / sqrtf(ss / (float)m.head_dim + m.eps);
+            const float* w = is_q ? p.q_norm : p.k_norm;
+            v0 *= inv * w[idx];
+            v1 *= inv * w[idx + half];
+        }
+    }
     if (i >= q_pairs + 2 * k_pairs) return;
-    if (i < q_pairs + k_pairs) {
-        const bool is_q = i < q_pairs;
-        const int local = is_q ? i : i - q_pairs;
-        const int head = local / half, idx = local - head * half;
-        const int i0 = head * m.head_dim + idx, i1 = i0 + half;
-        float* q = p.q + (size_t)r * m.q_dim;
-        const float* kr = p.k_raw + (size_t)r * m.kv_dim;
-        float v0 = is_q ? q[i0] : kr[i0], v1 = is_q ? q[i1] : kr[i1];
+    if (rot) {
         if (p.rope) {
             const float2 cs = p.rope[(size_t)pos * half + idx];
             const float r0 = v0 * cs.x - v1 * cs.y, r1 = v0 * cs.y + v1 * cs.x;

@@ -541,6 +541,10 @@ struct QkvArgs {
     int emb_type;            // WT_F16 or WT_BF16
     const float2* rope;      // [max_seq][head_dim/2] (cos, sin), Llama only
     int from_embedding;
+    // Models with a per-head q/k norm (Qwen3): the norm needs a whole head, which no single work item holds, so this
+    // stage stores the plain projections (q in place, k and v here) and k_rope_append applies norm, RoPE and the append.
+    float* k_raw;            // [rows][kv_dim] or null
+    float* v_raw;            // [rows][kv_dim] or null
 };
 
 template <int WT>
@@ -623,6 +627,11 @@ __device__ void stage_qkv(const QkvArgs& p, int cta, int n_cta, float* xs, float
                     float v0 = acc[2 * j], v1 = acc[2 * j + 1];
                     const float* bias = cur_g.biases[j];
                     if (bias) { v0 += bias[row0]; v1 += bias[row1]; }
+                    if (p.k_raw) {
+                        float* dst = kind == 0 ? p.a.q + (size_t)r * m.q_dim : (kind == 1 ? p.k_raw : p.v_raw) + (size_t)r * m.kv_dim;
+                        dst[row0] = v0; dst[row1] = v1;
+                        continue;
+                    }
                     if (kind < 2 && !gpt2) {
                         float2 cs = p.rope[(size_t)pos * half + cur_g.idx[j]];
                         float r0 = v0 * cs.x - v1 * cs.y, r1 = v0 * cs.y + v1 * cs.x;

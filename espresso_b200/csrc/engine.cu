@@ -490,6 +490,7 @@ DeviceTensor* Engine::slot(const std::string& raw, int* rows, int* cols, bool* i
             {"wq", q, d, true, -1}, {"wk", kv, d, true, -1}, {"wv", kv, d, true, -1}, {"wo", d, q, true, -1},
             {"w1", h, d, true, -1}, {"w2", d, h, true, -1}, {"w3", h, d, true, ARCH_LLAMA},
             {"rms_att", 1, d, false, ARCH_LLAMA}, {"rms_ffn", 1, d, false, ARCH_LLAMA},
+            {"q_norm", 1, m_.head_dim, false, ARCH_LLAMA}, {"k_norm", 1, m_.head_dim, false, ARCH_LLAMA},  // optional (Qwen3)
             {"ln_1_gamma", 1, d, false, ARCH_GPT2}, {"ln_1_beta", 1, d, false, ARCH_GPT2},
             {"ln_2_gamma", 1, d, false, ARCH_GPT2}, {"ln_2_beta", 1, d, false, ARCH_GPT2},
             {"bq", 1, q, false, ARCH_GPT2}, {"bk", 1, kv, false, ARCH_GPT2}, {"bv", 1, kv, false, ARCH_GPT2},
@@ -600,17 +601,45 @@ static int32_t read_blob(const std::string& path, std::vector<uint16_t>& out) {
     return ESP_CUDA_OK;
 }
 
+// loadWeightTablePreferringFloat32Sidecar (Sources/RealModelInference/RealModelInferenceEngine.swift:7830-7879):
+// "<name>.float32.bin" (raw little-endian fp32, exactly the tensor's element count) wins over "<name>.bin" (BLOBFILE
+// fp16).  Norm gains and biases keep the fp32 values; matrices and embeddings are rounded to the fp16 the device
+// computes in (load_tensor).  Returns -1 when neither file exists.
+int32_t Engine::load_file_tensor(const std::string& dir, const std::string& name) {
+    const std::string side = dir + "/" + name + ".float32.bin", blob = dir + "/" + name + ".bin";
+    if (path_exists(side)) {
+        std::ifstream f(side, std::ios::binary | std::ios::ate);
+        if (!f) return fail(ESP_CUDA_ERR_IO, "Failed to read float32 sidecar " + side);
+        const std::streamoff size = f.tellg();
+        int rows = 0, cols = 0;
+        bool is_matrix = false, is_embedding = false;
+        if (!slot(name, &rows, &cols, &is_matrix, &is_embedding)) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "unknown tensor: " + name);
+        const long long expect = (long long)rows * cols;
+        if (size != (std::streamoff)(expect * 4)) {
+            std::ostringstream os;
+            os << "invalidWeightCount: " << side << " expected " << expect << " actual " << (long long)size / 4;
+            return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, os.str());
+        }
+        std::vector<float> buf((size_t)expect);
+        f.seekg(0);
+        f.read(reinterpret_cast<char*>(buf.data()), size);
+        if (f.gcount() != size) return fail(ESP_CUDA_ERR_IO, "Failed to read float32 sidecar " + side);
+        return load_tensor(name.c_str(), ESP_CUDA_F32, buf.data(), buf.size() * 4);
+    }
+    if (!path_exists(blob)) return -1;
+    std::vector<uint16_t> buf;
+    int32_t rc = read_blob(blob, buf);
+    if (rc) return rc;
+    return load_tensor(name.c_str(), ESP_CUDA_F16, buf.data(), buf.size() * 2);
+}
+
 int32_t Engine::load_directory(const char* dir_c) {
     std::string dir(dir_c ? dir_c : "");
     if (!is_directory(dir)) return fail(ESP_CUDA_ERR_IO, "weight directory not found: " + dir);
     auto load_first = [&](std::initializer_list<const char*> cands, const char* label) -> int32_t {
         for (const char* c : cands) {
-            std::string p = dir + "/" + c + ".bin";
-            if (!path_exists(p)) continue;
-            std::vector<uint16_t> buf;
-            int32_t rc = read_blob(p, buf);
-            if (rc) return rc;
-            return load_tensor(c, ESP_CUDA_F16, buf.data(), buf.size() * 2);
+            int32_t rc = load_file_tensor(dir, c);
+            if (rc != -1) return rc;
         }
         return fail(ESP_CUDA_ERR_IO, std::string("missing ") + label + " in " + dir);
     };
@@ -632,13 +661,19 @@ int32_t Engine::load_directory(const char* dir_c) {
         int n = m_.arch == ARCH_GPT2 ? 16 : 9;
         for (int i = 0; i < n; i++) {
             std::string name = "layers/" + std::to_string(l) + "/" + names[i];
-            std::vector<uint16_t> buf;
-            if ((rc = read_blob(dir + "/" + name + ".bin", buf))) return rc;
-            if ((rc = load_tensor(name.c_str(), ESP_CUDA_F16, buf.data(), buf.size() * 2))) return rc;
+            rc = load_file_tensor(dir, name);
+            if (rc == -1) return fail(ESP_CUDA_ERR_IO, "missing weight file: " + dir + "/" + name + ".bin");
+            if (rc) return rc;
         }
-        if (m_.arch == ARCH_LLAMA && (path_exists(dir + "/layers/" + std::to_string(l) + "/q_norm.bin") ||
-                                      path_exists(dir + "/layers/" + std::to_string(l) + "/k_norm.bin")))
-            return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "per-head q_norm/k_norm weights are not supported by this build");
+        if (m_.arch == ARCH_LLAMA) {
+            // optional per-head q/k norm weights: both or neither (Engine.swift:6589-6596)
+            const std::string base = "layers/" + std::to_string(l) + "/";
+            const int32_t rq = load_file_tensor(dir, base + "q_norm"), rk = load_file_tensor(dir, base + "k_norm");
+            if (rq > 0) return rq;
+            if (rk > 0) return rk;
+            if ((rq == -1) != (rk == -1))
+                return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "Mismatched llama Q/K norm weights for " + dir + "/" + base + "; expected both q_norm.bin and k_norm.bin");
+        }
     }
     return ESP_CUDA_OK;
 }
@@ -670,11 +705,26 @@ int32_t Engine::finalize() {
     if (m_.arch == ARCH_GPT2 && tensors_["embeddings/position"].type != tensors_["embeddings/token"].type)
         return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "token and position embeddings must share one storage type");
     int32_t rc;
+    // per-head q/k norm (Qwen3): every layer carries both vectors, or none does
+    int n_qk = 0;
+    for (int l = 0; l < m_.n_layer; l++) {
+        const std::string p = "layers/" + std::to_string(l) + "/";
+        const bool hq = need(p + "q_norm"), hk = need(p + "k_norm");
+        if (hq != hk) return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "Mismatched llama Q/K norm weights in layer " + std::to_string(l) + "; expected both q_norm and k_norm");
+        n_qk += hq ? 1 : 0;
+    }
+    if (n_qk != 0 && n_qk != m_.n_layer) return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "q_norm/k_norm must be present in every layer or in none");
+    qk_norm_ = n_qk > 0;
+    if (qk_norm_ && tp_size_ > 1) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "per-head q/k norm is not available with tensor parallelism");
     if ((rc = dev_alloc(owned_, &act_.logits, (size_t)max_rows_ * m_.vocab))) return rc;
     size_t dbg = (size_t)m_.q_dim * 2 + 2 * m_.kv_dim + 2 * m_.d_model + m_.hidden;
     if ((rc = dev_alloc(owned_, &d_debug_, dbg))) return rc;
     ESP_CUDA_TRY(cudaDeviceSynchronize());
-    if ((rc = build_tc())) return rc;  // first: it makes the fp16 expansions the persistent kernel may pack
+    if ((rc = build_tc())) return rc;
+    if (qk_norm_ && !kraw_) {  // the per-stage q/k/v kernel hands k and v to the norm + RoPE + append kernel through these
+        if ((rc = dev_alloc(owned_, &kraw_, (size_t)max_rows_ * m_.kv_dim))) return rc;
+        if ((rc = dev_alloc(owned_, &vraw_, (size_t)max_rows_ * m_.kv_dim))) return rc;
+    }
     if (tp_size_ > 1 && tc_ready_ && (rc = tp_peer_setup())) return rc;
     if ((rc = build_mega())) return rc;
     finalized_ = true;
@@ -743,10 +793,21 @@ int32_t Engine::launch_step(int rows, int mode, cudaStream_t s, bool profile) {
             qa.emb_type = te.type == ESP_CUDA_BF16 ? WT_BF16 : WT_F16;
             qa.rope = d_rope_;
             qa.from_embedding = l == 0;
+            qa.k_raw = qk_norm_ ? kraw_ : nullptr;
+            qa.v_raw = qk_norm_ ? vraw_ : nullptr;
             int items = (m_.q_dim + 2 * m_.kv_dim) / 2;
             int grid = std::max(1, std::min((items + kWarps - 1) / kWarps, cap));
             ESP_CUDA_TRY(launch_qkv(lw.wq.type, dim3(grid), gemv_smem(lw.wq.type, m_.d_model, true), s, qa));
             launches++;
+            if (qk_norm_) {  // per-head norm, RoPE and the cache append need whole heads: one more small kernel
+                RopeArgs ra{};
+                ra.m = m_; ra.rs = rs_; ra.kv = kv_; ra.q = act_.q; ra.k_raw = kraw_; ra.v_raw = vraw_; ra.rope = d_rope_; ra.layer = l;
+                ra.debug = (a.debug && l == debug_layer_) ? a.debug : nullptr;
+                ra.q_norm = tensors_.at("layers/" + std::to_string(l) + "/q_norm").f32;
+                ra.k_norm = tensors_.at("layers/" + std::to_string(l) + "/k_norm").f32;
+                ESP_CUDA_TRY(launch_pdl(k_rope_append, dim3(rows, (m_.q_dim / 2 + m_.kv_dim + kThreads - 1) / kThreads), dim3(kThreads), 0, s, ra));
+                launches++;
+            }
             mark();
             AttArgs aa{};
             aa.m = m_; aa.layer = l; aa.rows = rows; aa.n_splits = n_splits_; aa.rs = rs_; aa.a = a; aa.kv = kv_;
@@ -1048,6 +1109,12 @@ int32_t Engine::verify2(uint32_t current, uint32_t proposed, uint32_t* exact_nex
     if (rc) return rc;
     if (!exact_next || !exact_future) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "verify2: null output");
     if (h_visible_[0] + 2 > m_.max_seq) return fail(ESP_CUDA_ERR_OUT_OF_RANGE, "verify2: two positions do not fit in the context");
+    if (current >= (uint32_t)vocab_global_ || proposed >= (uint32_t)vocab_global_) return fail(ESP_CUDA_ERR_OUT_OF_RANGE, "verify2: token is outside the vocabulary");
+    if (spec_verify_ok()) {
+        rc = run_spec_verify(current, proposed, exact_next, exact_future);
+        if (rc == ESP_CUDA_OK) { pending_verify_ = 2; return rc; }
+        if (rc != ESP_CUDA_ERR_STATE) return rc;  // ERR_STATE: the two-position working set does not fit; the row-wise path below
+    }
     int saved = h_visible_[0];
     int seq[2] = {0, 0};
     uint32_t tok[2] = {current, proposed};
@@ -1621,6 +1688,7 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
             RopeArgs ra{};
             ra.m = m_; ra.rs = rs_; ra.kv = kv_; ra.q = act_.q; ra.k_raw = kraw_; ra.v_raw = vraw_; ra.rope = gpt2 ? nullptr : d_rope_; ra.layer = l;
             ra.debug = cap ? dbg : nullptr;
+            if (qk_norm_) { ra.q_norm = tensors_.at(pre + "q_norm").f32; ra.k_norm = tensors_.at(pre + "k_norm").f32; }
             ESP_CUDA_TRY(launch_pdl(k_rope_append, dim3(rows, (q / 2 + kv + kThreads - 1) / kThreads), dim3(kThreads), 0, s, ra));
             launches++;
             if (att_rows) {
@@ -1721,7 +1789,7 @@ static const void* mega_kernel_for(int head_dim, int wt) {
 int32_t Engine::build_mega() {
     mega_ready_ = false;
     if ((cfg_.flags & ESP_CUDA_FLAG_NO_MEGAKERNEL) || tp_size_ > 1) return ESP_CUDA_OK;
-    if (m_.arch != ARCH_LLAMA) return ESP_CUDA_OK;
+    if (m_.arch != ARCH_LLAMA || qk_norm_) return ESP_CUDA_OK;  // (the per-head q/k norm lives in the per-stage and batched kernels)
     if (m_.head_dim != 32 && m_.head_dim != 64 && m_.head_dim != 128) return ESP_CUDA_OK;
     if (m_.d_model % 32 || m_.hidden % 32 || m_.n_head > sm_count_ || m_.n_head > 255 || m_.vocab >= (1 << 24)) return ESP_CUDA_OK;
     // The layer matrices share one storage type (fp16, or GGUF Q8_0 / Q4_0 blocks, which travel through the ring as they
@@ -1962,6 +2030,57 @@ int32_t Engine::spec_prepare() {
     if ((rc = dev_alloc(owned_, &d_spec_result_, 16))) return rc;
     spec_plan_ = p;
     spec_ready_ = true;
+    return ESP_CUDA_OK;
+}
+
+bool Engine::spec_verify_ok() const {
+    if (!mega_ready_ || tp_size_ > 1 || debug_layer_ >= 0) return false;
+    if (cfg_.flags & (ESP_CUDA_FLAG_NO_MEGAKERNEL | ESP_CUDA_FLAG_NO_GRAPH | ESP_CUDA_FLAG_KEEP_LOGITS)) return false;
+    return mega_plan_.wt_layer == ESP_CUDA_F16 && mega_plan_.wt_head == ESP_CUDA_F16;
+}
+
+// verify2 as one launch: both positions share one pass over the weights (the second rides in spare columns of the
+// tensor-core products).  Leaves both rows' hidden states in act_.hidden as the row-wise path does, for commit().
+int32_t Engine::run_spec_verify(uint32_t current, uint32_t proposed, uint32_t* exact_next, uint32_t* exact_future) {
+    int32_t rc;
+    if ((rc = spec_prepare())) return rc;
+    if ((rc = ensure_norms2())) return rc;
+    const MegaPlan& p = spec_plan_;
+    SpecArgs sa{};
+    MegaArgs& a = sa.base;
+    a.m = m_; a.plan = p; a.rope = d_rope_;
+    a.x_words = d_spec_arena_;
+    mega_arena_layout(m_, p, kSpecNP, &a);
+    a.error = d_spec_result_ + 8;
+    a.spin_limit = mega_spin_limit_;
+    SpecModel& M = sa.model[1];
+    M.m = m_; M.pack = d_pack_; M.cta_bytes = mega_plan_.cta_bytes; M.norms2 = d_norms2_;
+    M.tok_emb = static_cast<const uint16_t*>(tensors_.at("embeddings/token").data);
+    M.kv = kv_;
+    sa.model[0] = M;
+    sa.out = d_spec_out_;
+    sa.result = d_spec_result_;
+    sa.hidden_out = act_.hidden;
+    sa.prev = current; sa.current = proposed;
+    sa.pos = h_visible_[0];
+    sa.gen0 = 0; sa.eff = 1; sa.max_seq = m_.max_seq; sa.eos_token = -1;
+    sa.verify_only = 1;
+    ESP_CUDA_TRY(cudaMemsetAsync(d_spec_result_, 0, 16 * sizeof(int), stream_));
+    ESP_CUDA_TRY(cudaMemsetAsync(d_spec_arena_, 0, spec_arena_words_ * sizeof(unsigned long long), stream_));
+    void* args[] = {&sa};
+    ESP_CUDA_TRY(cudaLaunchCooperativeKernel(spec_kernel_for(m_.head_dim), dim3(p.n_cta), dim3(kMegaThreads), args, (size_t)p.smem_bytes, stream_));
+    int h[16];
+    ESP_CUDA_TRY(cudaMemcpyAsync(h, d_spec_result_, sizeof(h), cudaMemcpyDeviceToHost, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    launches_last_step_ = 1;
+    timings_.kernel_launches = 1;
+    if (h[8] != 0) {
+        std::ostringstream os;
+        os << "two-position verify kernel gave up waiting (code " << h[8] << ")";
+        return fail(ESP_CUDA_ERR_TIMEOUT, os.str());
+    }
+    *exact_next = (uint32_t)h[0];
+    *exact_future = (uint32_t)h[1];
     return ESP_CUDA_OK;
 }
 

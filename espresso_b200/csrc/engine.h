@@ -94,6 +94,7 @@ private:
 
     int32_t check_ready(const char* what) const;
     DeviceTensor* slot(const std::string& name, int* rows, int* cols, bool* is_matrix, bool* is_embedding);
+    int32_t load_file_tensor(const std::string& dir, const std::string& name);  // sidecar-first file loader; 1 = no such file
     int32_t upload_rows(int rows, const int* seq, const int* pos, const uint32_t* tok, const int* active,
                         const int* limit, bool zero_out_counts);
     int32_t submit(int rows, int mode);                  // graph replay or direct launch
@@ -111,11 +112,14 @@ private:
     int32_t run_mega(int n_steps, int* emitted, float* device_ms, double* first_token_ms);
     int32_t ensure_norms2();  // the gain vectors twice over, as the two-position kernel reads them
     int32_t spec_prepare();   // plan, arena and result block of the two-position kernel
+    bool spec_verify_ok() const;  // verify2 can run as one launch of the two-position kernel
+    int32_t run_spec_verify(uint32_t current, uint32_t proposed, uint32_t* exact_next, uint32_t* exact_future);
 
     esp_cuda_config cfg_;
     ModelDims m_{};
     cudaStream_t stream_ = nullptr;
     bool finalized_ = false;
+    bool qk_norm_ = false;  // every layer has per-head q_norm / k_norm weights (Qwen3)
     int max_rows_ = 0;
     int n_splits_ = 1;
     int sm_count_ = 148;

@@ -287,6 +287,7 @@ static bool gguf_slot(int32_t arch, const std::string& name, std::string* slot) 
         {"attn_q.bias", nullptr, "bq"}, {"attn_k.bias", nullptr, "bk"}, {"attn_v.bias", nullptr, "bv"},
         {"attn_qkv.weight", nullptr, "wqkv"}, {"attn_qkv.bias", nullptr, "bqkv"},
         {"attn_output.weight", "wo", "wo"}, {"attn_output.bias", nullptr, "bo"},
+        {"attn_q_norm.weight", "q_norm", nullptr}, {"attn_k_norm.weight", "k_norm", nullptr},  // Qwen3 per-head q/k norm
         {"ffn_norm.weight", "rms_ffn", "ln_2_gamma"}, {"ffn_norm.bias", nullptr, "ln_2_beta"},
         {"ffn_gate.weight", "w1", nullptr}, {"ffn_up.weight", "w3", "w1"}, {"ffn_up.bias", nullptr, "b1"},
         {"ffn_down.weight", "w2", "w2"}, {"ffn_down.bias", nullptr, "b2"},
@@ -343,8 +344,6 @@ int32_t gguf_load_into(Engine& eng, const GgufFile& f, const esp_cuda_config& c,
     for (const GgufTensor& t : f.tensors) {
         std::string slot;
         if (!gguf_slot(c.architecture, t.name, &slot)) {
-            if (t.name.find("attn_q_norm") != std::string::npos || t.name.find("attn_k_norm") != std::string::npos)
-                return esp::fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "per-head q/k norm tensors (" + t.name + ") are not supported by this decode path");
             continue;  // rope tables and other tensors the decode path does not read
         }
         if (!t.nbytes) return esp::fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "GGUF tensor " + t.name + " has GGML type " + std::to_string(t.type) + "; supported: F32, F16, BF16, Q8_0, Q4_0");

@@ -46,6 +46,8 @@ struct SpecArgs {
     int eff;                // emission limit
     int max_seq;            // context limit (min over the two models)
     int eos_token;
+    int verify_only;        // 1: a single target pass over (prev at pos, current at pos + 1), no draft, no loop: result[0..1] =
+                            // the two greedy tokens, hidden_out[2][d_model] = both rows' hidden states (verify2 of the C ABI)
 };
 
 // Shared-memory layout for two positions (host side; p.n_slots and p.slot_bytes must be set).
@@ -114,7 +116,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
     }
     __syncthreads();
     const MegaShare& w = *s.share;
-    const int max_passes = sa.eff - sa.gen0;  // every pass emits at least one token
+    const int max_passes = sa.verify_only ? 1 : sa.eff - sa.gen0;  // every pass emits at least one token
+    const int first_model = sa.verify_only ? 1 : 0;
     auto chunks_of = [](int items, int per_chunk) { return (items + per_chunk - 1) / per_chunk; };
 
     if (warp == kMegaConsumerWarps) {
@@ -137,7 +140,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                 for (int i0 = 0; i0 < items; i0 += per_chunk) issue(src + (long long)i0 * item_bytes, min(per_chunk, items - i0) * item_bytes);
             };
             for (int pass = 0; pass < max_passes && !stopped(); pass++) {
-                for (int mi = 0; mi < 2; mi++) {
+                for (int mi = first_model; mi < 2; mi++) {
                     const SpecModel& M = sa.model[mi];
                     const uint8_t* blob = M.pack + (size_t)blockIdx.x * M.cta_bytes;
                     for (int l = 0; l < M.m.n_layer; l++) {
@@ -168,7 +171,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
         // ---------------- watcher: follows the chunks in order and counts the ones whose bytes have arrived ----------------
         if (lane == 0) {
             const unsigned per_layer = (w.in_group ? chunks_of(w.s1_n, p.s1_ipc) + chunks_of(p.rpb, p.s2_rpc) : 0) + chunks_of(w.h_n, p.s3a_ipc) + chunks_of(w.d_n, p.s3b_rpc);
-            const unsigned per_pass = (unsigned)(sa.model[0].m.n_layer + sa.model[1].m.n_layer) * per_layer + 2u * chunks_of(w.v_n, p.head_rpc);
+            const unsigned per_pass = (unsigned)((first_model ? 0 : sa.model[0].m.n_layer) + sa.model[1].m.n_layer) * per_layer + (first_model ? 1u : 2u) * chunks_of(w.v_n, p.head_rpc);
             const unsigned total = (unsigned)max_passes * per_pass;
             MegaCursor k;
             for (unsigned i = 0; i < total; i++) {
@@ -442,6 +445,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
         release_pending();  // the last head chunks
     };
 
+    if (sa.verify_only) {
+        // ---- one verify pass (CPUExactLlamaRuntime's two-token verify): both greedy tokens and both hidden states
+        uint32_t next, future;
+        forward(sa.model[1], sa.prev, sa.current, sa.pos, next, future);
+        if (tid == 0) *reinterpret_cast<volatile int*>(s.stop) = 1;
+        if (blockIdx.x == 0) {
+            if (sa.hidden_out)
+                for (int k = tid; k < NP * d; k += kMegaConsumers) sa.hidden_out[k] = s.xraw[k];
+            if (tid == 0) { sa.result[0] = (int)next; sa.result[1] = (int)future; }
+        }
+        return;
+    }
     // ---- the generation loop (Sources/Espresso/GenerationHarness.swift:1281-1344; every CTA takes the same decisions)
     int gen = sa.gen0, total = sa.pos + 1;  // `current` sits at position sa.pos and has been emitted
     uint32_t prev = sa.prev, current = sa.current;

@@ -101,7 +101,10 @@ typedef struct esp_cuda_timings {
 /* ---- lifetime (replaces ane_interop_compile / ane_interop_free, ane_interop.h:24-35) ------------ */
 
 /* Creates an engine.  weight_dir != NULL: loads every tensor from a weight directory in the
- * reference layout (BLOBFILE fp16 files, "<name>.float32.bin" sidecars ignored by the device path;
+ * reference layout (BLOBFILE fp16 files; a "<name>.float32.bin" sidecar of exactly the tensor's element
+ * count wins over "<name>.bin" as in Engine.swift:7830-7879 -- norm gains and biases keep its fp32
+ * values, matrices and embeddings are rounded to the fp16 the device computes in; a sidecar of another
+ * size is ESP_CUDA_ERR_INVALID_WEIGHTS;
  * layout: Sources/ModelSupport/LayerWeightPaths.swift:22-77, Engine.swift:2066-2154) and finalises.
  * weight_dir == NULL: the caller uploads tensors with esp_cuda_load_tensor and then calls
  * esp_cuda_finalize. */

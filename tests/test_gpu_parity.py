@@ -190,6 +190,79 @@ def test_prefill_equals_token_by_token(rt, tmp_models):
     eng.close()
 
 
+def test_float32_sidecars_win_over_the_fp16_blobs(rt, oracle_lib, tmp_models, tmp_path):
+    """loadWeightTablePreferringFloat32Sidecar (Sources/RealModelInference/RealModelInferenceEngine.swift:7830-7879):
+    "<name>.float32.bin" beside "<name>.bin" is what gets loaded.  The sidecars here hold values that differ from the
+    blobs (gains that fp16 cannot represent, a negated matrix), so ignoring them would show in the logits."""
+    import shutil
+
+    from espresso_b200.model_config import tiny_llama
+    from espresso_b200.synthetic import synthetic_prompt
+    from espresso_b200.weight_blob import read_blob
+
+    cfg = tiny_llama(vocab=512, max_seq=64, n_layer=2)
+    d = str(tmp_path / "sidecars")
+    shutil.copytree(tmp_models(cfg), d)
+    rng = np.random.default_rng(5)
+    gains = (1.0 + 0.05 * rng.standard_normal(cfg.dModel)).astype(np.float32)
+    assert not np.array_equal(gains, gains.astype(np.float16).astype(np.float32))
+    gains.tofile(os.path.join(d, "layers/0/rms_att.float32.bin"))
+    (3.0 + 0.05 * rng.standard_normal(cfg.dModel)).astype(np.float32).tofile(os.path.join(d, "rms_final.float32.bin"))
+    wq = read_blob(os.path.join(d, "layers/1/wq.bin")).astype(np.float32)
+    (-wq).tofile(os.path.join(d, "layers/1/wq.float32.bin"))
+    prompt = synthetic_prompt(cfg.vocab, 9)
+    eng = rt.DecodeEngine.build(d)
+    eng.prefill(prompt)
+    ora = oracle_lib.Runtime(oracle_lib.Model.from_dir(d))
+    assert ora.prefill(prompt) == 0
+    assert_logits_close(eng.logits(), ora.logits(), "directory with float32 sidecars")
+    plain = oracle_lib.Runtime(oracle_lib.Model.from_dir(tmp_models(cfg)))
+    assert plain.prefill(prompt) == 0
+    assert np.abs(plain.logits() - ora.logits()).max() > 5 * ABS_TOL  # the sidecars do change the model (final gains x3)
+    eng.close()
+    # a sidecar of the wrong size is an error, not a fallback to the blob
+    np.zeros(7, np.float32).tofile(os.path.join(d, "layers/0/rms_ffn.float32.bin"))
+    with pytest.raises(rt.RealModelInferenceError) as ei:
+        rt.DecodeEngine.build(d)
+    assert ei.value.status == rt.ERR_INVALID_WEIGHTS and "invalidWeightCount" in ei.value.message
+
+
+@pytest.mark.parametrize("head_dim,n_head,n_kv", [(32, 8, 2), (64, 4, 4), (128, 4, 2)])
+def test_per_head_qk_norm_matches_oracle(rt, oracle_lib, tmp_path, head_dim, n_head, n_kv):
+    """Qwen3-style directories carry layers/N/q_norm.bin and k_norm.bin: RMSNorm over each head of q and k before RoPE
+    (applyPerHeadRMSNormInPlace, Sources/RealModelInference/RealModelInferenceEngine.swift:6648-6672).  One sequence
+    runs on the row-wise kernels, twelve on the tensor-core path; both against the oracle."""
+    from espresso_b200.model_config import MultiModelConfig
+    from espresso_b200.synthetic import synthetic_prompt, write_synthetic_model
+    from espresso_b200.weight_blob import write_blob
+
+    cfg = MultiModelConfig(f"qk-norm-hd{head_dim}", 2, n_head, n_kv, 256, head_dim, 512, 640, 96, 1e-6, 1000000.0, None, "llama")
+    d = write_synthetic_model(cfg, str(tmp_path / "m"))
+    rng = np.random.default_rng(head_dim)
+    for l in range(cfg.nLayer):
+        for leaf in ("q_norm", "k_norm"):
+            write_blob(os.path.join(d, f"layers/{l}/{leaf}.bin"), (1.0 + 0.2 * rng.standard_normal(head_dim)).astype(np.float16))
+    model = oracle_lib.Model.from_dir(d)
+    eng = rt.DecodeEngine.build(d, max_batch=12)
+    prompts = np.stack([synthetic_prompt(cfg.vocab, 11, stream=s) for s in range(12)])
+    eng.prefill(prompts[0])
+    ora = oracle_lib.Runtime(model)
+    assert ora.prefill(prompts[0]) == 0
+    assert_logits_close(eng.logits(), ora.logits(), "q/k norm, one sequence")
+    res = eng.generate(prompts[0], 20)
+    assert eng.timings()["kernel_launches"] > 1  # not the persistent kernel, which has no per-head norm
+    compare_greedy_stream(oracle_lib.Runtime(model), prompts[0], res.tokens)
+    streams, _ = eng.generate_batch(prompts, 16)
+    for s_ in (0, 7, 11):
+        compare_greedy_stream(oracle_lib.Runtime(model), prompts[s_], streams[s_])
+    eng.close()
+    # one of the two vectors alone is an error (Engine.swift:6589-6596)
+    os.remove(os.path.join(d, "layers/1/k_norm.bin"))
+    with pytest.raises(rt.RealModelInferenceError) as ei:
+        rt.DecodeEngine.build(d)
+    assert "Mismatched llama Q/K norm weights" in ei.value.message
+
+
 def test_long_prefill_in_256_row_passes_equals_token_by_token(rt, oracle_lib):
     """A 300-token prompt (one full 256-row pass and a ragged one) on a head_dim-128 GQA model: same logits as feeding
     the tokens one by one, and as the oracle."""
