@@ -4,6 +4,7 @@
 #include "batch_kernels.cuh"
 #include "tc_gemm.cuh"
 #include "spec_kernel.cuh"
+#include "prefill_attention.cuh"
 
 #include <dlfcn.h>
 #include <nccl.h>
@@ -268,6 +269,9 @@ static void raise_smem_limits_on_current_device() {
     ESP_SET_ALL(WT_F16) ESP_SET_ALL(WT_BF16) ESP_SET_ALL(WT_Q8_0) ESP_SET_ALL(WT_Q4_0)
 #undef ESP_SET_ALL
 #undef ESP_SET
+    cudaFuncSetAttribute(k_attention_prefill<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem_bytes<32>());
+    cudaFuncSetAttribute(k_attention_prefill<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem_bytes<64>());
+    cudaFuncSetAttribute(k_attention_prefill<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem_bytes<128>());
 }
 // Function attributes belong to a device: set them once per device ordinal.
 static void raise_smem_limits(int device) {
@@ -896,7 +900,7 @@ int32_t Engine::submit(int rows, int mode) {
         timings_.kernel_launches = launches_last_step_;
         return ESP_CUDA_OK;
     }
-    const int key = rows * 8 + mode;
+    const int key = rows * 16 + mode;
     auto it = graphs_.find(key);
     if (it == graphs_.end()) {
         cudaGraph_t graph = nullptr;
@@ -981,7 +985,15 @@ int32_t Engine::feed_rows(int rows, const int* seq, const uint32_t* tok, bool wi
     }
     int32_t rc = upload_rows(rows, seq, pos.data(), tok, nullptr, nullptr, true);
     if (rc) return rc;
-    if ((rc = submit(rows, STEP_FORWARD | (with_head ? STEP_HEAD : 0)))) return rc;
+    // A prompt pass whose 64-row tiles each hold consecutive positions of one sequence takes the tiled tensor-core
+    // attention (prefill_attention.cuh); the choice is part of the graph key.
+    int tiled = 0;
+    if (tc_ready_ && rows >= 32 && !with_head && (m_.head_dim == 32 || m_.head_dim == 64 || m_.head_dim == 128)) {
+        tiled = STEP_TILED_ATT;
+        for (int r = 1; r < rows && tiled; r++)
+            if (r % kPfRows != 0 && (seq[r] != seq[r - 1] || pos[r] != pos[r - 1] + 1)) tiled = 0;
+    }
+    if ((rc = submit(rows, STEP_FORWARD | (with_head ? STEP_HEAD : 0) | tiled))) return rc;
     if (with_head) ESP_CUDA_TRY(cudaMemcpyAsync(h_next_, rs_.next, sizeof(uint32_t) * rows, cudaMemcpyDeviceToHost, stream_));
     ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
     if (tc_ready_ && (rows >= kTcMinRows || tp_size_ > 1)) {
@@ -1147,31 +1159,48 @@ int32_t Engine::prefill_batch(const uint32_t* tokens, int32_t n_seq, int32_t len
     if (!tokens || len <= 0) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "Prompt tokens must not be empty");
     if (n_seq < 1 || n_seq > cfg_.max_batch) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "n_seq exceeds max_batch");
     if ((rc = reset())) return rc;
-    // A pass carries `c` consecutive positions of every sequence (row = sequence * c + position), as many as the row
-    // budget allows: every pass streams all the weights once, so fewer, fuller passes are what makes prefill fast.
-    const int budget = tc_ready_ ? std::min(max_rows_, kPrefillRows) : n_seq;
-    const int c_max = std::max(1, budget / n_seq);
-    std::vector<int> seq((size_t)n_seq * c_max);
-    std::vector<uint32_t> tok((size_t)n_seq * c_max);
-    int c_last = 1;
-    for (int t = 0; t < len; t += c_max) {
-        const int c = std::min(c_max, len - t);
-        for (int s = 0; s < n_seq; s++)
-            for (int j = 0; j < c; j++) {
-                seq[(size_t)s * c + j] = s;
-                tok[(size_t)s * c + j] = tokens[(size_t)s * len + t + j];
-            }
-        if ((rc = feed_rows(n_seq * c, seq.data(), tok.data(), false, nullptr))) return rc;
-        c_last = c;
+    // Rows are filled sequence by sequence: a pass of the tensor-core path holds up to kPrefillRows consecutive
+    // positions, long runs of one sequence first (every pass streams all the weights once, and runs of consecutive
+    // positions are what the tiled attention kernel wants).  Without that path a pass is one position of every sequence.
+    if (!tc_ready_) {
+        std::vector<int> seq(n_seq);
+        std::vector<uint32_t> tok(n_seq);
+        for (int s = 0; s < n_seq; s++) seq[s] = s;
+        for (int t = 0; t < len; t++) {
+            for (int s = 0; s < n_seq; s++) tok[s] = tokens[(size_t)s * len + t];
+            if ((rc = feed_rows(n_seq, seq.data(), tok.data(), false, nullptr))) return rc;
+        }
+        return ESP_CUDA_OK;
     }
-    // row s must hold the last hidden state of sequence s (decode passes have one row per sequence).  Ascending order is
-    // safe: the source row of sequence s, s * c + c - 1, lies above every destination written before it.
-    if (c_last > 1) {
-        for (int s = 0; s < n_seq; s++)
-            ESP_CUDA_TRY(cudaMemcpyAsync(act_.hidden + (size_t)s * m_.d_model, act_.hidden + ((size_t)s * c_last + c_last - 1) * m_.d_model, sizeof(float) * m_.d_model,
+    const int budget = std::min(max_rows_, kPrefillRows);
+    if (!d_last_hidden_ && (rc = dev_alloc(owned_, &d_last_hidden_, (size_t)cfg_.max_batch * m_.d_model))) return rc;
+    std::vector<int> seq;
+    std::vector<uint32_t> tok;
+    std::vector<std::pair<int, int>> ends;  // (row, sequence) of every sequence that ends in the pass being built
+    auto flush = [&]() -> int32_t {
+        if (seq.empty()) return ESP_CUDA_OK;
+        int32_t r = feed_rows((int)seq.size(), seq.data(), tok.data(), false, nullptr);
+        if (r) return r;
+        for (auto& e : ends)  // the sequence's last hidden state, before the next pass overwrites the rows
+            ESP_CUDA_TRY(cudaMemcpyAsync(d_last_hidden_ + (size_t)e.second * m_.d_model, act_.hidden + (size_t)e.first * m_.d_model, sizeof(float) * m_.d_model,
                                          cudaMemcpyDeviceToDevice, stream_));
-        ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+        seq.clear(); tok.clear(); ends.clear();
+        return ESP_CUDA_OK;
+    };
+    for (int s = 0; s < n_seq; s++) {
+        int t = 0;
+        while (t < len) {
+            const int take = std::min(len - t, budget - (int)seq.size());
+            for (int j = 0; j < take; j++) { seq.push_back(s); tok.push_back(tokens[(size_t)s * len + t + j]); }
+            t += take;
+            if (t == len) ends.emplace_back((int)seq.size() - 1, s);
+            if ((int)seq.size() == budget && (rc = flush())) return rc;
+        }
     }
+    if ((rc = flush())) return rc;
+    // row s must hold the last hidden state of sequence s (decode passes have one row per sequence)
+    ESP_CUDA_TRY(cudaMemcpyAsync(act_.hidden, d_last_hidden_, sizeof(float) * (size_t)n_seq * m_.d_model, cudaMemcpyDeviceToDevice, stream_));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
     return ESP_CUDA_OK;
 }
 
@@ -1286,7 +1315,7 @@ int32_t Engine::decode_loop(int32_t n_seq, int32_t count, uint32_t* out_tokens, 
         }
     }
     ESP_CUDA_TRY(cudaEventRecord(ev_end_, stream_));
-    timings_.kernel_launches = launches_by_key_.count(n_seq * 8 + (STEP_HEAD | STEP_FEEDBACK)) ? launches_by_key_[n_seq * 8 + (STEP_HEAD | STEP_FEEDBACK)] : 1;
+    timings_.kernel_launches = launches_by_key_.count(n_seq * 16 + (STEP_HEAD | STEP_FEEDBACK)) ? launches_by_key_[n_seq * 16 + (STEP_HEAD | STEP_FEEDBACK)] : 1;
     if (max_lim > 1) timings_.kernel_launches += (max_lim - 1) * launches_last_step_;
     ESP_CUDA_TRY(cudaMemcpyAsync(h_rows_block_, d_rows_block_, sizeof(int) * 6 * max_rows_, cudaMemcpyDeviceToHost, stream_));
     ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
@@ -1670,7 +1699,8 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
         if (dbg) { k_copy_debug<<<(n + 255) / 256, 256, 0, s>>>(src, dbg + offset, n); launches++; }
     };
     // many (row, head) pairs: one warp each; few rows with long contexts: the split-KV kernel of the GEMV path
-    const bool att_rows = (m_.head_dim == 32 || m_.head_dim == 64 || m_.head_dim == 128) && (long long)rows * m_.n_head >= 4LL * sm_count_;
+    const bool att_ok_hd = m_.head_dim == 32 || m_.head_dim == 64 || m_.head_dim == 128;
+    const bool att_rows = att_ok_hd && (long long)rows * m_.n_head >= 4LL * sm_count_;
     int32_t rc;
     if (mode & STEP_FORWARD) {
         const TcPlan plan_qkv = tc_plan(tiles_of(q) + 2 * tiles_of(kv), rows, d / kTcBlockK, true, false, sm_count_);
@@ -1691,7 +1721,16 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
             if (qk_norm_) { ra.q_norm = tensors_.at(pre + "q_norm").f32; ra.k_norm = tensors_.at(pre + "k_norm").f32; }
             ESP_CUDA_TRY(launch_pdl(k_rope_append, dim3(rows, (q / 2 + kv + kThreads - 1) / kThreads), dim3(kThreads), 0, s, ra));
             launches++;
-            if (att_rows) {
+            if ((mode & STEP_TILED_ATT) && att_ok_hd) {
+                PrefillAttArgs pa{};
+                pa.m = m_; pa.rs = rs_; pa.kv = kv_; pa.q = act_.q; pa.ctx16 = xh_q_; pa.bf16 = tc_bf16_; pa.layer = l; pa.rows = rows;
+                pa.debug = cap ? dbg + q + 2 * kv : nullptr;
+                const dim3 grid((rows + kPfRows - 1) / kPfRows, m_.n_head);
+                if (m_.head_dim == 32) ESP_CUDA_TRY(launch_pdl(k_attention_prefill<32>, grid, dim3(kPfThreads), (size_t)pf_smem_bytes<32>(), s, pa));
+                else if (m_.head_dim == 64) ESP_CUDA_TRY(launch_pdl(k_attention_prefill<64>, grid, dim3(kPfThreads), (size_t)pf_smem_bytes<64>(), s, pa));
+                else ESP_CUDA_TRY(launch_pdl(k_attention_prefill<128>, grid, dim3(kPfThreads), (size_t)pf_smem_bytes<128>(), s, pa));
+                launches++;
+            } else if (att_rows) {
                 AttRowsArgs ar{};
                 ar.m = m_; ar.rs = rs_; ar.kv = kv_; ar.q = act_.q; ar.ctx16 = xh_q_; ar.bf16 = tc_bf16_; ar.layer = l; ar.rows = rows;
                 ar.debug = cap ? dbg + q + 2 * kv : nullptr;

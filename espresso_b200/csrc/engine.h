@@ -87,7 +87,7 @@ public:
     bool finalized() const { return finalized_; }
 
 private:
-    enum StepMode { STEP_FORWARD = 1, STEP_HEAD = 2, STEP_FEEDBACK = 4 };
+    enum StepMode { STEP_FORWARD = 1, STEP_HEAD = 2, STEP_FEEDBACK = 4, STEP_TILED_ATT = 8 };  // TILED_ATT: prompt pass, tiled attention
     struct RowsHost {  // pinned mirror of the device row-control block
         int* base = nullptr;
     };
@@ -172,6 +172,7 @@ private:
     int tc_rows_alloc_ = 0;
     uint16_t *xh_d_ = nullptr, *xh_q_ = nullptr, *xh_h_ = nullptr;  // 16-bit operand rows [tc_rows_alloc_][K]
     float *kraw_ = nullptr, *vraw_ = nullptr, *up_ = nullptr;
+    float* d_last_hidden_ = nullptr;  // [max_batch][d_model] last hidden state per sequence while a batch of prompts is fed
     int* d_tc_error_ = nullptr;
     std::map<std::pair<const void*, int>, CUtensorMap> act_maps_;
 
