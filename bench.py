@@ -533,7 +533,7 @@ def measure(args, wl: dict, rank: int, local_rank: int, world: int, steps: int, 
             sustained = float(peaks.get("bf16_tflops_sustained", 1400.0))
             out["prefill"] = {"tokens_per_s": toks / t, "ms": t * 1e3, "TFLOPs_per_gpu": tflops, "frac_of_bf16_sustained": tflops / sustained,
                               "peak_kind": "measured" if peaks else "fallback", "prompt_tokens": toks,
-                              "note": "prefill_batch(): host wall clock around the call incl. prompt upload; passes of up to 256 rows"}
+                              "note": "prefill_batch(): host wall clock around the call incl. prompt upload; passes of up to 512 rows"}
         if full and rank == 0 and draft is None and n_seq == 1:
             st = stage_trace_us(eng, cfg, prompts[0], n_decode, clocks.get("sm_mhz") or 1965.0)
             if st:

@@ -51,7 +51,7 @@ int tc_tile_for(int rows);
 TcPlan tc_plan(int w_tiles, int rows, int kb, bool may_split_k, bool dual, int sms);
 cudaError_t tc_launch(const TcPlan& plan, bool dual, const CUtensorMap* const* mw, const CUtensorMap& mx, TcArgs a, cudaStream_t s);
 constexpr int kTcMinRows = 9;  // below this the row-batched GEMV stages are used
-constexpr int kPrefillRows = 256;  // rows of a prefill pass on the batched path: every pass streams all the weights once
+constexpr int kPrefillRows = 512;  // rows of a prefill pass on the batched path: every pass streams all the weights once
 
 // ---------------------------------------------------------------------------------------------- kernels
 
@@ -720,7 +720,10 @@ int32_t Engine::finalize() {
     if (n_qk != 0 && n_qk != m_.n_layer) return fail(ESP_CUDA_ERR_INVALID_WEIGHTS, "q_norm/k_norm must be present in every layer or in none");
     qk_norm_ = n_qk > 0;
     if (qk_norm_ && tp_size_ > 1) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "per-head q/k norm is not available with tensor parallelism");
-    if ((rc = dev_alloc(owned_, &act_.logits, (size_t)max_rows_ * m_.vocab))) return rc;
+    // full logits are kept for rows that run the head: sequences of a batch (or the two rows of a verify pass), every
+    // row of a pass only when the engine was asked to keep logits
+    const int logit_rows = (cfg_.flags & ESP_CUDA_FLAG_KEEP_LOGITS) ? max_rows_ : std::max(cfg_.max_batch, 2);
+    if ((rc = dev_alloc(owned_, &act_.logits, (size_t)logit_rows * m_.vocab))) return rc;
     size_t dbg = (size_t)m_.q_dim * 2 + 2 * m_.kv_dim + 2 * m_.d_model + m_.hidden;
     if ((rc = dev_alloc(owned_, &d_debug_, dbg))) return rc;
     ESP_CUDA_TRY(cudaDeviceSynchronize());
@@ -1547,7 +1550,7 @@ int32_t Engine::all_reduce(const void* send, void* recv, size_t count, bool sum_
 
 int32_t Engine::build_tc() {
     tc_ready_ = false;
-    if (max_rows_ > 256) return ESP_CUDA_OK;
+    if (max_rows_ > kPrefillRows) return ESP_CUDA_OK;
     if (m_.d_model % 64 || m_.q_dim % 64 || m_.hidden % 64 || m_.kv_dim % 16) return ESP_CUDA_OK;
     const int t0 = tensors_.at("lm_head").type;
     if (t0 != ESP_CUDA_F16 && t0 != ESP_CUDA_BF16 && t0 != ESP_CUDA_Q8_0 && t0 != ESP_CUDA_Q4_0) return ESP_CUDA_OK;

@@ -44,7 +44,7 @@ int32_t tc_make_map(CUtensorMap* map, const void* base, bool bf16, uint64_t rows
 
 // Rows of the activation TMA box for `rows` batch rows (one batch tile holds at most 128).
 int tc_tile_for(int rows) {
-    if (rows > 2 * kTcBatch) return 0;
+    if (rows > 4 * kTcBatch) return 0;
     for (int t : {16, 32, 64, 128})
         if (rows <= t) return t;
     return 128;

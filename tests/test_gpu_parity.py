@@ -263,26 +263,26 @@ def test_per_head_qk_norm_matches_oracle(rt, oracle_lib, tmp_path, head_dim, n_h
     assert "Mismatched llama Q/K norm weights" in ei.value.message
 
 
-def test_long_prefill_in_256_row_passes_equals_token_by_token(rt, oracle_lib):
-    """A 300-token prompt (one full 256-row pass and a ragged one) on a head_dim-128 GQA model: same logits as feeding
-    the tokens one by one, and as the oracle."""
+def test_long_prefill_in_wide_passes_equals_token_by_token(rt, oracle_lib):
+    """A 600-token prompt (one full 512-row pass and a ragged one, tiled attention across ten cache tiles) on a
+    head_dim-128 GQA model: same logits as feeding the tokens one by one, and as the oracle."""
     from espresso_b200.model_config import MultiModelConfig
     from espresso_b200.synthetic import synthetic_prompt
 
-    cfg = MultiModelConfig("gqa-hd128", 2, 4, 2, 512, 128, 1024, 640, 384, 1e-5, 500000.0, None, "llama")
+    cfg = MultiModelConfig("gqa-hd128", 2, 4, 2, 512, 128, 1024, 640, 768, 1e-5, 500000.0, None, "llama")
 
     eng, model = dense_pair(rt, oracle_lib, cfg)
-    prompt = synthetic_prompt(cfg.vocab, 300)
+    prompt = synthetic_prompt(cfg.vocab, 600)
     eng.prefill(prompt)
     a = eng.logits()
-    assert eng.visible_token_count() == 300
+    assert eng.visible_token_count() == 600
     ora = oracle_lib.Runtime(model)
     assert ora.prefill(prompt) == 0
-    assert_logits_close(a, ora.logits(), "300-token prefill vs oracle")
+    assert_logits_close(a, ora.logits(), "600-token prefill vs oracle")
     eng.reset()
     for t in prompt:
         eng.advance(int(t))
-    assert_logits_close(a, eng.logits(), "300-token prefill vs token by token")
+    assert_logits_close(a, eng.logits(), "600-token prefill vs token by token")
     eng.close()
 
 
