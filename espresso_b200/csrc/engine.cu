@@ -1802,7 +1802,7 @@ static int pad128(long long v) { return (int)((v + 127) / 128 * 128); }
 static size_t mega_arena_layout(const ModelDims& m, const MegaPlan& p, int np, MegaArgs* a) {
     auto line = [](size_t words) { return (words + kMegaLineWords - 1) / kMegaLineWords * kMegaLineWords; };
     size_t o = 0;
-    const size_t x_at = o;   o += line((size_t)np * (p.x_wpc ? (size_t)p.n_cta * p.x_wpc : (size_t)m.d_model));
+    const size_t x_at = o;   o += line((size_t)np * m.d_model);
     const size_t act_at = o; o += line((size_t)np * (p.act_wpc ? (size_t)p.n_cta * p.act_wpc : (size_t)m.hidden));
     const size_t mid_at = o; o += line((size_t)np * m.d_model);
     const size_t qkv_at = o; o += line((size_t)np * m.n_kv_head * 2 * p.group_items);
@@ -1868,9 +1868,9 @@ int32_t Engine::build_mega() {
     p.vpc_max = (m_.vocab + P - 1) / P;
     // Exchange arrays: the activation vector gets cache lines per CTA when every reader can poll all of it in one round
     // (four 16-byte loads per consumer thread); the layer output stays compact (see mega_kernel.cuh).
-    p.x_wpc = 0;
     p.act_wpc = (p.hpc_max + kMegaLineWords - 1) / kMegaLineWords * kMegaLineWords;
     if (P * ((p.hpc_max + 1) / 2) > 4 * kMegaConsumers) p.act_wpc = 0;
+    if (quant) p.act_wpc = 0;  // the int8 staging of Q8_0 works on whole blocks of consecutive elements (and the wide quantised models need two polling rounds anyway)
     p.wt_layer = wt_layer;
     p.wt_head = wt_head;
     p.row_bytes = mega_row_bytes(wt_layer, m_.d_model);

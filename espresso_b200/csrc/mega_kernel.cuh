@@ -55,7 +55,7 @@ constexpr int kMegaChunkRows = 256;                // most rows of one chunk (16
 #ifndef MEGA_CAND_STRIDE
 #define MEGA_CAND_STRIDE 16
 #endif
-// Which exchanges give every CTA cache lines of its own (see mega_read_lines) is the plan's choice (x_wpc / act_wpc > 0).
+// Which exchanges give every CTA cache lines of its own (see mega_read_lines) is the plan's choice (act_wpc > 0).
 // Measured on the 6-layer d768 model against compact arrays: arg-max candidates -4.6 us per token, activation vector
 // -1.4 us, layer output x +0.3 us (five words per CTA: three times as many lines to poll for little contention saved).
 // On the 22-layer d2048 model, whose activation vector needs two polling rounds either way, lines per CTA cost 1.8 us
@@ -75,7 +75,7 @@ struct MegaPlan {
     int s1_max;       // largest number of S1 row pairs of a CTA
     int rpb;          // S2: output rows per block
     int hpc_max, dpc_max, vpc_max;  // largest number of FFN units / W2 rows / vocabulary rows of a CTA
-    int x_wpc, act_wpc;  // exchange words reserved per CTA for its elements of x / of the activation vector (whole cache lines); 0 = compact array
+    int act_wpc;  // exchange words reserved per CTA for its elements of the activation vector (whole cache lines); 0 = compact array
     int wt_layer, wt_head;  // storage type of the layer matrices and of the LM head: WT_F16, WT_Q8_0 or WT_Q4_0
     int row_bytes;       // packed bytes of a row of d_model columns of a layer matrix
     int down_row_bytes;  // ... of hidden columns (W2)
@@ -111,7 +111,7 @@ struct MegaArgs {
     const float2* rope;       // [max_seq][head_dim/2]
     KvLayout kv;
     // exchange arena (zero at launch)
-    unsigned long long* x_words;    // [d_model], or [n_cta][x_wpc] (every CTA's rows in cache lines of its own); tagged: output of a layer
+    unsigned long long* x_words;    // [d_model] tagged: output of a layer
     unsigned long long* act_words;  // [hidden] or [n_cta][act_wpc]; tagged: FFN activation
     unsigned long long* qkv_words;  // [n_kv_head][2 * group_items] tagged: post-RoPE q / k / v of one token
     unsigned long long* mid_sums;   // [d_model] counted: residual + attention projection
@@ -233,8 +233,10 @@ __host__ __device__ inline void mega_s1_rows(const ModelDims& m, const MegaPlan&
     }
 }
 
-// Bytes of a staged vector of K values (hi and lo fp16 parts; see xa_index).
+// Bytes of a staged vector of K values (hi and lo fp16 parts, see xa_index; or int8 digits, see qx_store_pair).
 __host__ __device__ inline int xa_bytes(int K) { return (K / 32) * 128; }
+// Bytes of the per-block scales that accompany a vector staged as int8 digits.
+__host__ __device__ inline int qx_scale_bytes(int K) { return (K / 32) * 4; }
 
 // ------------------------------------------------------------------------------------------------ shared state
 
@@ -256,7 +258,6 @@ struct MegaShared {
     float* partial;  // [2][kMegaChunkRows] partial row sums of a chunk (alternating halves)
     unsigned long long* key;   // [32] arg-max keys
     struct MegaShare* share;  // this CTA's work shares, computed once
-    int* xbeg;     // [n_cta + 1] first W2 row (= element of x) of every CTA
     int* hbeg;     // [n_cta + 1] first FFN unit (= element of the activation vector) of every CTA
     int* abort;    // [1] a wait gave up: no more waiting in this CTA
     int* stop;     // [1] the loop ended early (EOS): the producer stops issuing
@@ -288,8 +289,7 @@ __device__ __forceinline__ MegaShared mega_carve(uint8_t* base, const MegaArgs& 
     s.stop = s.abort + 1;
     s.landed = reinterpret_cast<unsigned*>(s.abort + 2);
     s.share = reinterpret_cast<MegaShare*>(base + p.off_share);
-    s.xbeg = reinterpret_cast<int*>(base + p.off_beg);
-    s.hbeg = s.xbeg + p.n_cta + 1;
+    s.hbeg = reinterpret_cast<int*>(base + p.off_beg);
     return s;
 }
 
@@ -300,12 +300,12 @@ inline void mega_layout(const ModelDims& m, MegaPlan& p) {
     p.off_bar = take(16 * (size_t)p.n_slots);
     p.off_prev = take(8 * (size_t)m.d_model);
     p.off_key = take(8 * 32);
-    p.off_xs = take((size_t)xa_bytes(m.d_model > m.hidden ? m.d_model : m.hidden));
+    p.off_xs = take((size_t)xa_bytes(m.d_model > m.hidden ? m.d_model : m.hidden) + qx_scale_bytes(m.d_model > m.hidden ? m.d_model : m.hidden));
     p.off_xraw = take(sizeof(float) * (size_t)m.d_model);
     p.off_xmid = take(sizeof(float) * (size_t)m.d_model);
     p.off_rope = take(sizeof(float2) * (size_t)(m.head_dim / 2));
     p.off_qs = take(sizeof(float) * (size_t)m.head_dim);
-    p.off_ctx = take(sizeof(float) * (size_t)m.head_dim);
+    p.off_ctx = take((size_t)xa_bytes(m.head_dim) + qx_scale_bytes(m.head_dim));
     p.off_kn = take(sizeof(__half) * (size_t)m.head_dim);
     p.off_vn = take(sizeof(__half) * (size_t)m.head_dim);
     p.off_part = take(sizeof(float) * (size_t)kMegaConsumerWarps * m.head_dim);
@@ -313,7 +313,7 @@ inline void mega_layout(const ModelDims& m, MegaPlan& p) {
     p.off_outv = take(sizeof(float) * 2 * kMegaChunkRows);
     p.off_flags = take(16);
     p.off_share = take(sizeof(MegaShare));
-    p.off_beg = take(sizeof(int) * 2 * ((size_t)p.n_cta + 1));
+    p.off_beg = take(sizeof(int) * ((size_t)p.n_cta + 1));
     p.smem_bytes = (int)((o + 127) & ~(size_t)127);
 }
 
@@ -397,7 +397,8 @@ __device__ __forceinline__ void mega_release_deferred(const MegaArgs& a, const M
 
 // ------------------------------------------------------------------------------------------------ exchanges
 
-// Reads `n` tagged words (n even, 16-byte aligned base) and hands (index, value, gain) to `sink`.  A thread keeps up to
+// Reads `n` tagged words (n even, 16-byte aligned base) and hands pairs (even index, two values, two gains) to `sink`
+// (when n is a multiple of 64 every warp reaches the sink with all its lanes, consecutive pairs in consecutive lanes).  A thread keeps up to
 // four 16-byte loads in flight; words that validated are not read again.  The gains (or 1 when `gain` is null) are
 // requested before the polling starts, so they cost nothing once the words arrive.
 template <class Sink>
@@ -435,10 +436,7 @@ __device__ __forceinline__ void mega_read_words(const MegaArgs& a, const MegaSha
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int p = p0 + j * kMegaConsumers + (int)threadIdx.x;
-            if (p < n_pairs) {
-                sink(2 * p, __uint_as_float((unsigned)w[j].x), g[j].x);
-                sink(2 * p + 1, __uint_as_float((unsigned)w[j].y), g[j].y);
-            }
+            if (p < n_pairs) sink(2 * p, __uint_as_float((unsigned)w[j].x), __uint_as_float((unsigned)w[j].y), g[j].x, g[j].y);
         }
     }
 }
@@ -546,8 +544,7 @@ __device__ __forceinline__ void mega_read_sums(const MegaArgs& a, const MegaShar
                 *reinterpret_cast<ulonglong2*>(s.prev + 2 * p) = w[j];
                 const long long v0 = (long long)(w[j].x - pv[j].x - (unsigned long long)n_contrib) >> 8;
                 const long long v1 = (long long)(w[j].y - pv[j].y - (unsigned long long)n_contrib) >> 8;
-                sink(2 * p, (float)v0 * kMegaUnfix, g[j].x);
-                sink(2 * p + 1, (float)v1 * kMegaUnfix, g[j].y);
+                sink(2 * p, (float)v0 * kMegaUnfix, (float)v1 * kMegaUnfix, g[j].x, g[j].y);
             }
         }
     }
@@ -625,15 +622,99 @@ __device__ __forceinline__ float2 mega_tile_dot_f16(const uint8_t* chunk, int R,
                        ((c0[2] + c1[2]) + (c2[2] + c3[2])) + ((c0[3] + c1[3]) + (c2[3] + c3[3])));
 }
 
-// Four int8 -> two half2 (b0, b1), (b2, b3), exactly: xor 0x80 makes the byte unsigned, a byte permute drops it into the
-// mantissa of 1024.0 (0x6400), and subtracting 1152 = 1024 + 128 leaves the signed value.
-__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
-__device__ __forceinline__ void q8_widen(uint32_t w, uint32_t& lo, uint32_t& hi) {
-    const uint32_t u = w ^ 0x80808080u;
-    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
-    lo = h2_bits(__hsub2(u32_as_h2(__byte_perm(u, 0x64646464u, 0x4140)), bias));
-    hi = h2_bits(__hsub2(u32_as_h2(__byte_perm(u, 0x64646464u, 0x4342)), bias));
+// ---- Q8_0: the activation as int8 digits, the products on the int8 tensor-core path ----
+// A Q8_0 weight is an int8: instead of widening it to fp16 (eight byte permutes and subtractions per 32 weights and
+// lane), the staged activation is turned into integers.  Per block of 32 columns: q = max|x| / 127 and
+// x_i ~ q (d0 + d1 / 128 + d2 / 16384) with three int8 digits (22 bits relative to the block's largest value; the
+// weights stay exact).  The digits are B columns 0..2 of one mma.sync.m16n8k32 (s8 x s8), the int32 results are combined
+// and scaled by q and the weight block's scale in fp32.  (Q4_0 keeps the fp16 widening: its nibbles carry an offset of 8
+// that has to be taken out through a per-block sum of the staged values, and the extra warp reduction per staged block
+// cost more than the cheaper products gained: 492 against 460 us per token on the 22-layer d2048 model; Q8_0 gained 3 %.)
+//
+// Staged layout: block kb holds 128 bytes = [digit c][piece t][8 bytes: columns 4t..4t+3 then 16+4t..16+4t+3], the B
+// registers of lane (g = c, t); the block scales q sit behind the vector (qx_scale_bytes).
+__device__ __forceinline__ int qx_byte(int kb, int c, int e) { return kb * 128 + c * 32 + (((e & 15) >> 2) << 3) + ((e >> 4) << 2) + (e & 3); }
+
+// Rounding and integer <-> float conversion without conversion instructions (they issue at a quarter of the rate of an
+// addition, and this code runs once per staged element and four times per product block): adding 1.5 * 2^23 to a float
+// of magnitude below 2^22 rounds it to the nearest integer and leaves that integer in the low mantissa bits.
+constexpr float kRoundMagic = 12582912.0f;          // 1.5 * 2^23 = 0x4B400000
+constexpr int kRoundMagicBits = 0x4B400000;
+__device__ __forceinline__ float int_to_float_small(int v) { return __int_as_float(kRoundMagicBits + v) - kRoundMagic; }  // |v| < 2^22
+
+// The three int8 digits of v * inv (|v * inv| <= 127); dg[c] carries digit c in its low 8 bits (two's complement).
+__device__ __forceinline__ void qx_digits(float v, float inv, int (&dg)[3]) {
+    const float s0 = v * inv, t0 = s0 + kRoundMagic, d0 = t0 - kRoundMagic;
+    const float s1 = (s0 - d0) * 128.f, t1 = s1 + kRoundMagic, d1 = t1 - kRoundMagic;
+    const float t2 = (s1 - d1) * 128.f + kRoundMagic;
+    dg[0] = __float_as_int(t0); dg[1] = __float_as_int(t1); dg[2] = __float_as_int(t2);
 }
+// Stages elements k, k + 1 (k even).  Must be called by all 32 lanes of a warp with consecutive pairs: the 16 lanes of a
+// half-warp hold one block of 32 columns.  The block's maximum comes from one warp reduction on integers (the bit
+// pattern of a non-negative float orders like the float).
+__device__ __forceinline__ void qx_store_pair(uint8_t* xq, float* qs, int k, float v0, float v1) {
+    const unsigned half_mask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+    const float mx = __uint_as_float(__reduce_max_sync(half_mask, __float_as_uint(fmaxf(fabsf(v0), fabsf(v1)))));
+    const float inv = mx > 0.f ? __fdividef(127.0f, mx) : 0.f;
+    int d0[3], d1[3];
+    qx_digits(v0, inv, d0);
+    qx_digits(v1, inv, d1);
+    const int kb = k >> 5, e = k & 31;
+#pragma unroll
+    for (int c = 0; c < 3; c++)
+        *reinterpret_cast<uint16_t*>(xq + qx_byte(kb, c, e)) = (uint16_t)__byte_perm((unsigned)d0[c], (unsigned)d1[c], 0x0040);
+    if ((threadIdx.x & 15) == 0) qs[kb] = mx * (1.0f / 127.0f);
+}
+// Stages element k.  Must be called by all 32 lanes of a warp with consecutive k: the warp holds one block.
+__device__ __forceinline__ void qx_store_elem(uint8_t* xq, float* qs, int k, float v) {
+    const float mx = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(v))));
+    const float inv = mx > 0.f ? __fdividef(127.0f, mx) : 0.f;
+    int dg[3];
+    qx_digits(v, inv, dg);
+    const int kb = k >> 5, e = k & 31;
+#pragma unroll
+    for (int c = 0; c < 3; c++) xq[qx_byte(kb, c, e)] = (uint8_t)dg[c];
+    if ((threadIdx.x & 31) == 0) qs[kb] = mx * (1.0f / 127.0f);
+}
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Q8_0 chunk: [block][row][piece t: the int8 of columns 4t..4t+3 and 16+4t..16+4t+3], then the scales [block][row] fp16.
+__device__ __forceinline__ float2 mega_tile_dot_q8(const uint8_t* chunk, int R, int n_kb, int tile, int kb0, int kb1, const uint8_t* xq, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int row = tile * 16 + g;
+    const uint8_t* wp = chunk + ((size_t)row * 32 + t * 8);
+    const size_t kstride = (size_t)R * 32;
+    const __half* sp = reinterpret_cast<const __half*>(chunk + (size_t)R * n_kb * 32) + row;
+    const uint8_t* xp = xq + (g < 3 ? g * 32 + t * 8 : 0);
+    const float* qs = reinterpret_cast<const float*>(xq + (size_t)n_kb * 128);
+    // what this lane's two result columns mean: t = 0 holds digits 0 and 1, t = 1 digit 2, the others nothing
+    const float k0 = t == 0 ? 1.0f : t == 1 ? (1.0f / 16384.0f) : 0.f, k1 = t == 0 ? (1.0f / 128.0f) : 0.f;
+    float a0 = 0.f, a8 = 0.f;
+#pragma unroll 4
+    for (int kb = kb0; kb < kb1; kb++) {
+        uint2 b = make_uint2(0, 0);
+        if (g < 3) b = *reinterpret_cast<const uint2*>(xp + kb * 128);
+        const float q = qs[kb];
+        const float s0 = __half2float(sp[(size_t)kb * R]), s8 = __half2float(sp[(size_t)kb * R + 8]);
+        const uint2 w0 = *reinterpret_cast<const uint2*>(wp + kb * kstride);
+        const uint2 w8 = *reinterpret_cast<const uint2*>(wp + kb * kstride + 8 * 32);
+        int c[4] = {0, 0, 0, 0};
+        mma_s8(c, w0.x, w8.x, w0.y, w8.y, b.x, b.y);
+        a0 = fmaf(s0 * q, fmaf(int_to_float_small(c[1]), k1, int_to_float_small(c[0]) * k0), a0);
+        a8 = fmaf(s8 * q, fmaf(int_to_float_small(c[3]), k1, int_to_float_small(c[2]) * k0), a8);
+    }
+    // lanes t = 0 and t = 1 hold the two parts of every row's sum
+    a0 += __shfl_xor_sync(0xffffffffu, a0, 1);
+    a8 += __shfl_xor_sync(0xffffffffu, a8, 1);
+    return make_float2(a0, a8);
+}
+
+// ---- Q4_0: widened to fp16 in registers (why not the int8 path: see the note above qx_byte) ----
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
 // Four bytes of a Q4_0 block (low nibble = element j, high nibble = element j + 16) -> four half2: the low nibbles of
 // bytes (0,1), (2,3), then the high nibbles of (0,1), (2,3), each minus 8.
 __device__ __forceinline__ void q4_widen(uint32_t w, uint32_t (&o)[4]) {
@@ -643,34 +724,6 @@ __device__ __forceinline__ void q4_widen(uint32_t w, uint32_t (&o)[4]) {
     o[1] = h2_bits(__hsub2(u32_as_h2(__byte_perm(x, 0x64646464u, 0x4342)), bias));
     o[2] = h2_bits(__hsub2(u32_as_h2(__byte_perm(y, 0x64646464u, 0x4140)), bias));
     o[3] = h2_bits(__hsub2(u32_as_h2(__byte_perm(y, 0x64646464u, 0x4342)), bias));
-}
-
-// Q8_0 chunk: [block][row][32 int8 in the order the lanes read them], then the scales [block][row] fp16.
-template <int NP>
-__device__ __forceinline__ float2 mega_tile_dot_q8(const uint8_t* chunk, int R, int n_kb, int tile, int kb0, int kb1, const uint8_t* xa, int lane) {
-    float a0 = 0.f, a8 = 0.f;
-    const int row = tile * 16 + (lane >> 2);
-    const uint8_t* wp = chunk + ((size_t)row * 32 + (lane & 3) * 8);
-    const size_t kstride = (size_t)R * 32;
-    const __half* sp = reinterpret_cast<const __half*>(chunk + (size_t)R * n_kb * 32) + row;
-    const uint8_t* xp = xa + lane * 16;
-#pragma unroll 2
-    for (int kb = kb0; kb < kb1; kb++) {
-        const uint2 w0 = *reinterpret_cast<const uint2*>(wp + kb * kstride);
-        const uint2 w8 = *reinterpret_cast<const uint2*>(wp + kb * kstride + 8 * 32);
-        const float s0 = __half2float(sp[(size_t)kb * R]), s8 = __half2float(sp[(size_t)kb * R + 8]);
-        uint4 xv = make_uint4(0, 0, 0, 0);
-        if (lane < 8 * NP) xv = *reinterpret_cast<const uint4*>(xp + kb * (128 * NP));
-        uint32_t g01, g23, g45, g67, h01, h23, h45, h67;
-        q8_widen(w0.x, g01, g23); q8_widen(w0.y, g45, g67);
-        q8_widen(w8.x, h01, h23); q8_widen(w8.y, h45, h67);
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
-        mma_16816(c, g01, h01, g23, h23, xv.x, xv.y);
-        mma_16816(c, g45, h45, g67, h67, xv.z, xv.w);
-        a0 = fmaf(s0, c[0] + c[1], a0);
-        a8 = fmaf(s8, c[2] + c[3], a8);
-    }
-    return make_float2(a0, a8);
 }
 
 // Q4_0 chunk: [block][row][16 bytes: piece t = bytes 2t, 2t+1, 2t+8, 2t+9 of the GGUF block], then the scales.
@@ -703,7 +756,7 @@ __device__ __forceinline__ float2 mega_tile_dot_q4(const uint8_t* chunk, int R, 
 
 template <int WT, int NP>
 __device__ __forceinline__ float2 mega_tile_dot(const uint8_t* chunk, int R, int n_kb, int tile, int kb0, int kb1, const uint8_t* xa, int lane) {
-    if constexpr (WT == WT_Q8_0) return mega_tile_dot_q8<NP>(chunk, R, n_kb, tile, kb0, kb1, xa, lane);
+    if constexpr (WT == WT_Q8_0) return mega_tile_dot_q8(chunk, R, n_kb, tile, kb0, kb1, xa, lane);
     else if constexpr (WT == WT_Q4_0) return mega_tile_dot_q4<NP>(chunk, R, n_kb, tile, kb0, kb1, xa, lane);
     else return mega_tile_dot_f16<NP>(chunk, R, n_kb, tile, kb0, kb1, xa, lane);
 }
@@ -788,7 +841,7 @@ __device__ __forceinline__ void mega_kv_load(MegaKvRound<HD>& r, const __half* K
 
 // With NP positions per pass the call serves query `qi`: it sees the n_cached cached positions and the new positions
 // 0 .. qi, whose keys and values are rows of s.kn / s.vn; its context lands in position qi of the staged s.ctx.
-template <int HD, int NP = 1, class WaitQ>
+template <int HD, int NP = 1, int QCTX = 0, class WaitQ>  // QCTX: 0 = fp16 context staging, 1 = int8 digits
 __device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShared& s, const MegaShare& w, const ModelDims& m, const KvLayout& kv, int layer, int n_cached, int qi,
                                                WaitQ wait_q) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -888,7 +941,10 @@ __device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShar
             num = fmaf(s.part[x * HD + tid], f, num);
             den = fmaf(s.red[kMegaConsumerWarps + x], f, den);
         }
-        xa_store<NP>(reinterpret_cast<__half*>(s.ctx), tid, den > 0.f ? __fdividef(num, den) : 0.f, qi);  // the A operand of the Wo products
+        // the staged operand of the Wo products (whole warps come here: HD is a multiple of 32)
+        const float cv = den > 0.f ? __fdividef(num, den) : 0.f;
+        if constexpr (QCTX != 0) qx_store_elem(reinterpret_cast<uint8_t*>(s.ctx), reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s.ctx) + xa_bytes(HD)), tid, cv);
+        else xa_store<NP>(reinterpret_cast<__half*>(s.ctx), tid, cv, qi);
     }
     consumer_sync();
 }
@@ -913,7 +969,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
     }
     for (int k = tid; k < m.d_model; k += kMegaThreads) s.prev[k] = 0ull;  // the counted sums are zero at launch
     for (int c = tid; c <= p.n_cta; c += kMegaThreads) {
-        s.xbeg[c] = mega_share_begin(m.d_model, p.n_cta, c);
         s.hbeg[c] = mega_share_begin(m.hidden, p.n_cta, c);
     }
     __syncthreads();
@@ -1043,12 +1098,26 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
     unsigned long long* my_qkv = a.qkv_words + (size_t)w.kvh * 2 * p.group_items;
     __half* xa_h = reinterpret_cast<__half*>(s.xa);
 
-    // Stages one value of the residual stream: raw copy, gained copy as the products' A operand, sum of squares.
-    auto stage_x = [&](float* raw, int k, float v, float g, float& ss) {
+    // Stages values of the residual stream: raw copy, gained copy as the products' staged operand (fp16 hi/lo parts, or
+    // int8 digits for the quantised types; `K` = length of the vector being staged), sum of squares.
+    constexpr bool kQuant = WT == WT_Q8_0;  // int8 digit staging (Q4_0 widens its nibbles to fp16 and reads the fp16 staging)
+    auto stage_x = [&](float* raw, int K, bool digits, int k, float v, float g, float& ss) {  // one element per lane, consecutive k
         raw[k] = v;
-        xa_store(xa_h, k, v * g);
+        if (kQuant && digits) qx_store_elem(s.xa, reinterpret_cast<float*>(s.xa + xa_bytes(K)), k, v * g);
+        else xa_store(xa_h, k, v * g);
         ss = fmaf(v, v, ss);
     };
+    auto stage_x2 = [&](float* raw, int K, bool digits, int k, float v0, float v1, float g0, float g1, float& ss) {  // a pair per lane
+        raw[k] = v0; raw[k + 1] = v1;
+        if (kQuant && digits) {
+            qx_store_pair(s.xa, reinterpret_cast<float*>(s.xa + xa_bytes(K)), k, v0 * g0, v1 * g1);
+        } else {
+            xa_store(xa_h, k, v0 * g0);
+            xa_store(xa_h, k + 1, v1 * g1);
+        }
+        ss = fmaf(v0, v0, fmaf(v1, v1, ss));
+    };
+    const bool head_digits = kQuant && p.wt_head != WT_F16;  // an fp16 head on quantised layers reads the fp16 staging
     // One chunk of a stage: acquire, all products, release, CTA barrier; returns where the sums are.
     int lg_parts = 0;    // log2 of the column ranges of the chunk whose sums are being read
     // A freed slot makes the producer request the chunk that is n_slots ahead at once: megabytes of reads over all
@@ -1097,10 +1166,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     const float* gain = a.norms + (size_t)(2 * l) * d;
                     float ss = 0.f;
                     if (l == 0) {
-                        for (int k = tid; k < d; k += kMegaConsumers) stage_x(s.xraw, k, __half2float(__ushort_as_half(emb_row[k])), __ldg(gain + k), ss);
+                        for (int k = tid; k < d; k += kMegaConsumers) stage_x(s.xraw, d, true, k, __half2float(__ushort_as_half(emb_row[k])), __ldg(gain + k), ss);
                     } else {
-                        if (p.x_wpc) mega_read_lines(a, s, a.x_words, p.x_wpc, s.xbeg, d, p.n_cta, (p.dpc_max + 1) >> 1, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
-                        else mega_read_words(a, s, a.x_words, d, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+                        mega_read_words(a, s, a.x_words, d, seq - 1, 5, gain, [&](int k, float v0, float v1, float g0, float g1) { stage_x2(s.xraw, d, true, k, v0, v1, g0, g1, ss); });
                     }
                     FINE();
                     release_pending();  // the W2 chunk of the previous layer
@@ -1138,7 +1206,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     stamp(step);
                     // ---- S2: attention of this CTA's head (the cached K/V rows are requested before the query is awaited)
                     FINE();
-                    mega_attention<HD>(a, s, w, m, a.kv, l, pos, 0, [&]() {
+                    mega_attention<HD, 1, WT == WT_Q8_0 ? 1 : 0>(a, s, w, m, a.kv, l, pos, 0, [&]() {
                         // q of this CTA's head, k and v of the KV head: pairs in the order S1 published them
                         FINE();
                         if (tid < 3 * half) {
@@ -1194,7 +1262,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     const float* gain = a.norms + (size_t)(2 * l + 1) * d;
                     float ss = 0.f;
                     FINE();
-                    mega_read_sums(a, s, a.mid_sums, d, m.n_head, 7, gain, [&](int k, float v, float g) { stage_x(s.xmid, k, v, g, ss); });
+                    mega_read_sums(a, s, a.mid_sums, d, m.n_head, 7, gain, [&](int k, float v0, float v1, float g0, float g1) { stage_x2(s.xmid, d, true, k, v0, v1, g0, g1, ss); });
                     FINE();
                     release_pending();  // the Wo chunk (CTAs outside the head groups: the W2 chunk of the previous layer)
                     ss = mega_block_sum(ss, s.red);
@@ -1217,8 +1285,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 stamp(step);
                 // ---- the whole activation vector, then this CTA's rows of W2 (+ residual) = the next layer's x
                 FINE();
-                if (p.act_wpc) mega_read_lines(a, s, a.act_words, p.act_wpc, s.hbeg, m.hidden, p.n_cta, (p.hpc_max + 1) >> 1, seq, 8, nullptr, [&](int k, float v, float) { xa_store(xa_h, k, v); });
-                else mega_read_words(a, s, a.act_words, m.hidden, seq, 8, nullptr, [&](int k, float v, float) { xa_store(xa_h, k, v); });
+                if (p.act_wpc) {  // (cache lines per CTA: fp16 models only, see the plan)
+                    mega_read_lines(a, s, a.act_words, p.act_wpc, s.hbeg, m.hidden, p.n_cta, (p.hpc_max + 1) >> 1, seq, 8, nullptr, [&](int k, float v, float) { xa_store(xa_h, k, v); });
+                } else {
+                    mega_read_words(a, s, a.act_words, m.hidden, seq, 8, nullptr, [&](int k, float v0, float v1, float, float) {
+                        if (kQuant) {
+                            qx_store_pair(s.xa, reinterpret_cast<float*>(s.xa + xa_bytes(m.hidden)), k, v0, v1);
+                        } else {
+                            xa_store(xa_h, k, v0);
+                            xa_store(xa_h, k + 1, v1);
+                        }
+                    });
+                }
                 FINE();
                 release_pending();  // the gate/up chunk
                 consumer_sync();
@@ -1228,7 +1306,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     const int nr = min(p.s3b_rpc, w.d_n - r0);
                     float* sums = chunk_products(nr, m.hidden >> 5, s.xa, r0 + p.s3b_rpc >= w.d_n);
                     for (int r = tid; r < nr; r += kMegaConsumers)
-                        st_word(a.x_words + (p.x_wpc ? (size_t)blockIdx.x * p.x_wpc : (size_t)w.d_begin) + r0 + r, tagged(mega_take_sum(sums, lg_parts, r) + s.xmid[w.d_begin + r0 + r], seq));
+                        st_word(a.x_words + w.d_begin + r0 + r, tagged(mega_take_sum(sums, lg_parts, r) + s.xmid[w.d_begin + r0 + r], seq));
                 }
                 stamp(step);
             }
@@ -1248,10 +1326,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         {
             float ss = 0.f;
             if (step == 0) {
-                for (int k = tid; k < d; k += kMegaConsumers) stage_x(s.xraw, k, __ldcg(a.hidden_io + k), __ldg(fin_gain + k), ss);
+                for (int k = tid; k < d; k += kMegaConsumers) stage_x(s.xraw, d, head_digits, k, __ldcg(a.hidden_io + k), __ldg(fin_gain + k), ss);
             } else {
-                if (p.x_wpc) mega_read_lines(a, s, a.x_words, p.x_wpc, s.xbeg, d, p.n_cta, (p.dpc_max + 1) >> 1, (unsigned)(step * L), 9, fin_gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
-                else mega_read_words(a, s, a.x_words, d, (unsigned)(step * L), 9, fin_gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+                mega_read_words(a, s, a.x_words, d, (unsigned)(step * L), 9, fin_gain, [&](int k, float v0, float v1, float g0, float g1) { stage_x2(s.xraw, d, head_digits, k, v0, v1, g0, g1, ss); });
             }
             release_pending();  // the W2 chunk of the last layer
             consumer_sync();  // the RMSNorm scale is positive: the arg-max does not need it
@@ -1387,10 +1464,10 @@ __device__ __forceinline__ PackRow pack_row(int wt, const PackMatrix& m, int col
 }
 
 // Writes `nr` rows of K columns each in the order the products read them: for every block of 32 columns, for every row,
-// four pieces; piece t holds columns {2t, 2t+1, 2t+8, 2t+9, 16+2t, 17+2t, 24+2t, 25+2t} of the block (the A registers of
-// two m16n8k16 steps for the lanes with that t): 16 bytes of fp16, 8 int8 of a Q8_0 block, or the 4 bytes 2t, 2t+1,
-// 2t+8, 2t+9 of a Q4_0 block (whose low and high nibbles are exactly those eight columns).  The quantised types put
-// the scales [block][row] behind the data.  row_of(r) names the row's source.
+// four pieces.  fp16: piece t holds columns {2t, 2t+1, 2t+8, 2t+9, 16+2t, 17+2t, 24+2t, 25+2t} of the block (the A registers
+// of two m16n8k16 steps for the lanes with that t).  Q8_0: the int8 of columns 4t..4t+3 and 16+4t..16+4t+3 (the A registers
+// of one m16n8k32 step); Q4_0: bytes 2t, 2t+1, 2t+8, 2t+9 of the GGUF block, whose low and high nibbles are the fp16 piece's columns.
+// The quantised types put the scales [block][row] behind the data.  row_of(r) names the row's source.
 template <class RowOf>
 __device__ __forceinline__ void pack_tiled(int wt, uint8_t* dst, int nr, int K, RowOf row_of) {
     const int n_kb = K >> 5;
@@ -1410,9 +1487,9 @@ __device__ __forceinline__ void pack_tiled(int wt, uint8_t* dst, int nr, int K, 
         } else if (wt == WT_Q8_0) {
             uint2 v = make_uint2(0, 0);
             if (src.data) {
-                const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src.data + (size_t)kb * 32);  // pairs of columns
-                v.x = (uint32_t)s16[t] | ((uint32_t)s16[t + 4] << 16);
-                v.y = (uint32_t)s16[t + 8] | ((uint32_t)s16[t + 12] << 16);
+                const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src.data + (size_t)kb * 32);  // four columns each
+                v.x = s32[t];      // columns 4t .. 4t+3
+                v.y = s32[4 + t];  // columns 16+4t .. 16+4t+3
             }
             *reinterpret_cast<uint2*>(out) = v;
         } else {

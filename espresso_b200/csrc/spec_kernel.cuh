@@ -71,7 +71,7 @@ inline void spec_layout(const ModelDims& m, MegaPlan& p) {
     p.off_outv = take(sizeof(float) * 2 * NP * kMegaChunkRows);
     p.off_flags = take(16);
     p.off_share = take(sizeof(MegaShare));
-    p.off_beg = take(sizeof(int) * 2 * ((size_t)p.n_cta + 1));
+    p.off_beg = take(sizeof(int) * ((size_t)p.n_cta + 1));
     p.smem_bytes = (int)((o + 127) & ~(size_t)127);
 }
 
@@ -111,7 +111,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
     }
     for (int k = tid; k < NP * m.d_model; k += kMegaThreads) s.prev[k] = 0ull;  // the counted sums are zero at launch
     for (int c = tid; c <= p.n_cta; c += kMegaThreads) {
-        s.xbeg[c] = mega_share_begin(m.d_model, p.n_cta, c);
         s.hbeg[c] = mega_share_begin(m.hidden, p.n_cta, c);
     }
     __syncthreads();
@@ -141,9 +140,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
             };
             for (int pass = 0; pass < max_passes && !stopped(); pass++) {
                 for (int mi = first_model; mi < 2; mi++) {
-                    const SpecModel& M = sa.model[mi];
-                    const uint8_t* blob = M.pack + (size_t)blockIdx.x * M.cta_bytes;
-                    for (int l = 0; l < M.m.n_layer; l++) {
+                    // (fields picked one by one: a reference into the kernel parameters would force a local copy of all of them)
+                    const uint8_t* blob = (mi ? sa.model[1].pack : sa.model[0].pack) + (size_t)blockIdx.x * (mi ? sa.model[1].cta_bytes : sa.model[0].cta_bytes);
+                    const int n_layer = mi ? sa.model[1].m.n_layer : sa.model[0].m.n_layer;
+                    for (int l = 0; l < n_layer; l++) {
                         const uint8_t* src = blob + (long long)l * p.layer_bytes;
                         if (w.in_group) issue_stage(src, w.s1_n, p.s1_ipc, 2 * p.row_bytes);
                         src += p.s1_bytes;
@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                         src += p.s3a_bytes;
                         issue_stage(src, w.d_n, p.s3b_rpc, p.down_row_bytes);
                     }
-                    issue_stage(blob + (long long)M.m.n_layer * p.layer_bytes, w.v_n, p.head_rpc, p.head_row_bytes);
+                    issue_stage(blob + (long long)n_layer * p.layer_bytes, w.v_n, p.head_rpc, p.head_row_bytes);
                 }
             }
             // every copy that was issued must have landed before the CTA may exit: walk the last n_slots chunks backwards
@@ -211,6 +211,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
         xa_store<NP>(xa_h, k - q * d, v * g, q);
         if (q) ss[1] = fmaf(v, v, ss[1]); else ss[0] = fmaf(v, v, ss[0]);
     };
+    auto stage_x2 = [&](float* raw, int k, float v0, float v1, float g0, float g1, float (&ss)[NP]) {  // k even: both in one position
+        stage_x(raw, k, v0, g0, ss);
+        stage_x(raw, k + 1, v1, g1, ss);
+    };
     int lg_parts = 0;
     MegaCursor pend_from;
     int n_pend = 0;
@@ -238,8 +242,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
 
     // One pass of model M over the tokens (t0 at position pos0, t1 at pos0 + 1); every CTA learns both greedy tokens.
     // `row_sel` >= 0: CTA 0 keeps the hidden state of that row in sa.hidden_out.
-    auto forward = [&](const SpecModel& M, uint32_t t0, uint32_t t1, int pos0, uint32_t& o0, uint32_t& o1) {
-        const int L = M.m.n_layer;
+    auto forward = [&](int mi, uint32_t t0, uint32_t t1, int pos0, uint32_t& o0, uint32_t& o1) {
+        // the model's fields as scalars (a reference into the kernel parameters would force a local copy of all of them)
+        const int L = mi ? sa.model[1].m.n_layer : sa.model[0].m.n_layer;
+        const float* norms2 = mi ? sa.model[1].norms2 : sa.model[0].norms2;
+        const uint16_t* tok_emb = mi ? sa.model[1].tok_emb : sa.model[0].tok_emb;
+        KvLayout kv;
+        kv.k = mi ? sa.model[1].kv.k : sa.model[0].kv.k;
+        kv.v = mi ? sa.model[1].kv.v : sa.model[0].kv.v;
+        ModelDims md = a.m;  // the widths are the target's; the cache strides are the model's own
+        md.n_layer = L;
+        md.n_seq = mi ? sa.model[1].m.n_seq : sa.model[0].m.n_seq;
+        md.max_seq = mi ? sa.model[1].m.max_seq : sa.model[0].m.max_seq;
         if (tid < NP * half) {
             const int q = tid / half, i = tid - q * half;
             s.rope[tid] = a.rope[(size_t)min(pos0 + q, m.max_seq - 1) * half + i];  // published by the barrier of the first norm
@@ -249,17 +263,16 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
             float inv[NP] = {0.f, 0.f};
             if (w.in_group) {
                 // ---- S1: x of this layer for both positions, q/k/v row pairs, RoPE, words for the KV-head group, cache append
-                const float* gain = M.norms2 + (size_t)(2 * l) * NP * d;
+                const float* gain = norms2 + (size_t)(2 * l) * NP * d;
                 float ss[NP] = {0.f, 0.f};
                 if (l == 0) {
                     for (int k = tid; k < NP * d; k += kMegaConsumers) {
                         const int q = k >= d ? 1 : 0;
-                        const uint16_t* emb_row = M.tok_emb + (size_t)(q ? t1 : t0) * d;
+                        const uint16_t* emb_row = tok_emb + (size_t)(q ? t1 : t0) * d;
                         stage_x(s.xraw, k, __half2float(__ushort_as_half(emb_row[k - q * d])), __ldg(gain + k), ss);
                     }
                 } else {
-                    if (p.x_wpc) mega_read_lines(a, s, a.x_words, p.x_wpc, s.xbeg, d, NP * p.n_cta, (p.dpc_max + 1) >> 1, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
-                    else mega_read_words(a, s, a.x_words, NP * d, seq - 1, 5, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+                    mega_read_words(a, s, a.x_words, NP * d, seq - 1, 5, gain, [&](int k, float v0, float v1, float g0, float g1) { stage_x2(s.xraw, k, v0, v1, g0, g1, ss); });
                 }
                 release_pending();  // the W2 chunk of the previous layer
                 const float2 tot = spec_block_sum2(ss[0], ss[1], s.red);
@@ -283,9 +296,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                         unsigned long long* dst = my_qkv + q * gi2 + 2 * (w.s1_begin + i0 + it);
                         st_word(dst, tagged(v0, seq));
                         st_word(dst + 1, tagged(v1, seq));
-                        if (kind > 0 && pos0 + q < M.m.max_seq) {
-                            __half* base = kind == 1 ? M.kv.k : M.kv.v;
-                            const size_t off = M.kv.offset(M.m, l, 0, w.kvh, pos0 + q);
+                        if (kind > 0 && pos0 + q < md.max_seq) {
+                            __half* base = kind == 1 ? kv.k : kv.v;
+                            const size_t off = kv.offset(md, l, 0, w.kvh, pos0 + q);
                             base[off + (row0 - w.kvh * HD)] = __float2half_rn(v0);
                             base[off + (row1 - w.kvh * HD)] = __float2half_rn(v1);
                         }
@@ -293,7 +306,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                 }
                 // ---- S2: attention of this CTA's head, one call per query (the cached rows of the first call are requested
                 // before the queries are awaited; the second call finds them in L2)
-                mega_attention<HD, NP>(a, s, w, M.m, M.kv, l, pos0, 0, [&]() {
+                mega_attention<HD, NP, 0>(a, s, w, md, kv, l, pos0, 0, [&]() {
                     if (tid < NP * 3 * half) {
                         const int q = tid / (3 * half), r = tid - q * 3 * half;
                         const int section = r / half, idx = r - section * half;
@@ -316,7 +329,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                     release_pending();  // the q/k/v chunk
                     consumer_sync();
                 });
-                mega_attention<HD, NP>(a, s, w, M.m, M.kv, l, pos0, 1, [&]() {});
+                mega_attention<HD, NP, 0>(a, s, w, md, kv, l, pos0, 1, [&]() {});
                 // ---- rows [blk*rpb, ...) of Wo restricted to this head's columns: one contribution per position to the
                 // counted sum of every row (head 0 also carries the residual)
                 for (int r0 = 0; r0 < p.rpb; r0 += p.s2_rpc) {
@@ -336,9 +349,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
             // ---- S3: x_mid = residual + attention projection
             {
                 if (tid < NP * p.n_cta) { unsigned long long keep; asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(keep) : "l"(a.cand_words + (size_t)tid * kMegaCandStride) : "memory"); }
-                const float* gain = M.norms2 + (size_t)(2 * l + 1) * NP * d;
+                const float* gain = norms2 + (size_t)(2 * l + 1) * NP * d;
                 float ss[NP] = {0.f, 0.f};
-                mega_read_sums(a, s, a.mid_sums, NP * d, m.n_head, 7, gain, [&](int k, float v, float g) { stage_x(s.xmid, k, v, g, ss); });
+                mega_read_sums(a, s, a.mid_sums, NP * d, m.n_head, 7, gain, [&](int k, float v0, float v1, float g0, float g1) { stage_x2(s.xmid, k, v0, v1, g0, g1, ss); });
                 release_pending();  // the Wo chunk (CTAs outside the head groups: the W2 chunk of the previous layer)
                 const float2 tot = spec_block_sum2(ss[0], ss[1], s.red);
                 inv[0] = rsqrtf(tot.x * inv_d + m.eps);
@@ -361,7 +374,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                 xa_store<NP>(xa_h, k - q * hidden, v, q);
             };
             if (p.act_wpc) mega_read_lines(a, s, a.act_words, p.act_wpc, s.hbeg, hidden, NP * p.n_cta, (p.hpc_max + 1) >> 1, seq, 8, nullptr, stage_act);
-            else mega_read_words(a, s, a.act_words, NP * hidden, seq, 8, nullptr, stage_act);
+            else mega_read_words(a, s, a.act_words, NP * hidden, seq, 8, nullptr, [&](int k, float v0, float v1, float, float) { stage_act(k, v0, 1.f); stage_act(k + 1, v1, 1.f); });
             release_pending();  // the gate/up chunk
             consumer_sync();
             for (int r0 = 0; r0 < w.d_n; r0 += p.s3b_rpc) {
@@ -370,17 +383,16 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                 for (int i = tid; i < NP * nr; i += kMegaConsumers) {
                     const int q = i >= nr ? 1 : 0, r = i - q * nr;
                     const int row = w.d_begin + r0 + r;
-                    st_word(a.x_words + (p.x_wpc ? (size_t)(q * p.n_cta + blockIdx.x) * p.x_wpc : (size_t)q * d + w.d_begin) + r0 + r, tagged(mega_take_sum(sums + q * kMegaChunkRows, lg_parts, r) + s.xmid[q * d + row], seq));
+                    st_word(a.x_words + (size_t)q * d + w.d_begin + r0 + r, tagged(mega_take_sum(sums + q * kMegaChunkRows, lg_parts, r) + s.xmid[q * d + row], seq));
                 }
             }
         }
         // ---- LM head over this CTA's vocabulary rows for both positions, first-max argmax
         if (tid == 0) __threadfence();  // this CTA's cache rows of the pass, before the candidate words (see the decode kernel)
         {
-            const float* gain = M.norms2 + (size_t)(2 * L) * NP * d;
+            const float* gain = norms2 + (size_t)(2 * L) * NP * d;
             float ss[NP] = {0.f, 0.f};
-            if (p.x_wpc) mega_read_lines(a, s, a.x_words, p.x_wpc, s.xbeg, d, NP * p.n_cta, (p.dpc_max + 1) >> 1, seq, 9, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
-            else mega_read_words(a, s, a.x_words, NP * d, seq, 9, gain, [&](int k, float v, float g) { stage_x(s.xraw, k, v, g, ss); });
+            mega_read_words(a, s, a.x_words, NP * d, seq, 9, gain, [&](int k, float v0, float v1, float g0, float g1) { stage_x2(s.xraw, k, v0, v1, g0, g1, ss); });
             release_pending();  // the W2 chunk of the last layer
             consumer_sync();    // the RMSNorm scale is positive: the arg-max does not need it
         }
@@ -445,18 +457,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
         release_pending();  // the last head chunks
     };
 
-    if (sa.verify_only) {
-        // ---- one verify pass (CPUExactLlamaRuntime's two-token verify): both greedy tokens and both hidden states
-        uint32_t next, future;
-        forward(sa.model[1], sa.prev, sa.current, sa.pos, next, future);
-        if (tid == 0) *reinterpret_cast<volatile int*>(s.stop) = 1;
-        if (blockIdx.x == 0) {
-            if (sa.hidden_out)
-                for (int k = tid; k < NP * d; k += kMegaConsumers) sa.hidden_out[k] = s.xraw[k];
-            if (tid == 0) { sa.result[0] = (int)next; sa.result[1] = (int)future; }
-        }
-        return;
-    }
     // ---- the generation loop (Sources/Espresso/GenerationHarness.swift:1281-1344; every CTA takes the same decisions)
     int gen = sa.gen0, total = sa.pos + 1;  // `current` sits at position sa.pos and has been emitted
     uint32_t prev = sa.prev, current = sa.current;
@@ -469,12 +469,29 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
     while (true) {
         const int remaining = min(sa.eff - gen, sa.max_seq - total);
         passes++;
-        uint32_t d0, proposed, next, future;
-        forward(sa.model[0], prev, current, P - 1, d0, proposed);
-        draft_visible = P + 1;
-        if (s.red[63] != 0.f) break;
-        forward(sa.model[1], current, proposed, P, next, future);
-        if (s.red[63] != 0.f) break;
+        // verify-only launches (verify2 of the C ABI) take the target's pass alone: `prev` and `current` of the arguments
+        // are then the two tokens to verify
+        uint32_t proposed = sa.verify_only ? sa.current : 0u, next = 0, future = 0;
+        if (sa.verify_only) current = sa.prev;
+        bool gave_up = false;
+        for (int mi = first_model; mi < 2 && !gave_up; mi++) {  // the only call site: the draft's pass, then the target's
+            uint32_t o0, o1;
+            forward(mi, mi ? current : prev, mi ? proposed : current, mi ? P : P - 1, o0, o1);
+            if (mi == 0) { proposed = o1; draft_visible = P + 1; }
+            else { next = o0; future = o1; }
+            gave_up = s.red[63] != 0.f;
+        }
+        if (gave_up) break;
+        if (sa.verify_only) {
+            // both greedy tokens and both rows' hidden states; nothing is committed or emitted
+            if (blockIdx.x == 0) {
+                if (sa.hidden_out)
+                    for (int k = tid; k < NP * d; k += kMegaConsumers) sa.hidden_out[k] = s.xraw[k];
+                if (tid == 0) { sa.result[0] = (int)next; sa.result[1] = (int)future; }
+            }
+            if (tid == 0) *reinterpret_cast<volatile int*>(s.stop) = 1;
+            return;
+        }
         const bool two = remaining > 1 && total + 1 < sa.max_seq;
         if (two && proposed == next) {
             // both tokens are exact: the proposal is committed and emitted, the token after it becomes `current`
