@@ -1137,6 +1137,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         par ^= 1;
         if (WT != WT_F16 && is_head && p.wt_head == WT_F16) lg_parts = mega_chunk_dots<WT_F16>(ch, rows, n_kb, xa, partial, warp, lane);  // an fp16 head on quantised layers
         else lg_parts = mega_chunk_dots<WT>(ch, rows, n_kb, xa, partial, warp, lane);
+        FINE();
         if (defer) {
             if (n_pend == 0) pend_from = c;
             n_pend++;
