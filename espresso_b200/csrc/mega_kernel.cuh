@@ -52,16 +52,13 @@ constexpr unsigned kMegaSpinLimit = 1u << 21;      // default attempts per wait 
 constexpr int kMegaTraceLayer = 10;                // stamps per layer
 constexpr int kMegaTraceHead = 4;                  // stamps of the head
 constexpr int kMegaChunkRows = 256;                // most rows of one chunk (16 tiles of 16 rows)
-#ifndef MEGA_CAND_STRIDE
-#define MEGA_CAND_STRIDE 16
-#endif
 // Which exchanges give every CTA cache lines of its own (see mega_read_lines) is the plan's choice (act_wpc > 0).
 // Measured on the 6-layer d768 model against compact arrays: arg-max candidates -4.6 us per token, activation vector
 // -1.4 us, layer output x +0.3 us (five words per CTA: three times as many lines to poll for little contention saved).
 // On the 22-layer d2048 model, whose activation vector needs two polling rounds either way, lines per CTA cost 1.8 us
 // per layer.  So: candidates always, the activation vector when all of it is polled in one round, x never.
 constexpr int kMegaLineWords = 16;  // 8-byte words of a 128-byte cache line
-constexpr int kMegaCandStride = MEGA_CAND_STRIDE;  // 8-byte words between the arg-max candidates of two CTAs (16 = a cache line each)
+constexpr int kMegaCandStride = kMegaLineWords;  // 8-byte words between the arg-max candidates of two CTAs: a cache line each
 constexpr float kMegaFix = 4294967296.0f;          // counted sums: fixed point with 32 fractional bits
 constexpr float kMegaUnfix = 2.3283064365386963e-10f;
 
@@ -1318,12 +1315,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
         fine_layer = 99; fine_step = step;
 #endif
         stamp(step);
-#ifndef MEGA_NO_FENCE
         // Everything this CTA wrote with plain stores during the step (KV-cache rows; the CTA barriers since then order
         // them before this thread) is made visible before the candidate words that thread 0 publishes at the end of the
         // head.  Issued here, the fence overlaps the wait for the last layer's output.
         if (tid == 0) __threadfence();
-#endif
         {
             float ss = 0.f;
             if (step == 0) {
@@ -1380,11 +1375,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                         mega_backoff();
                     }
                 }
-#ifndef MEGA_NO_FENCE
                 // a reader orders its later loads (the KV-cache rows other CTAs appended during this step) after the
                 // candidate words it saw; the writers' side of the pair is the fence at the start of the head
                 __threadfence();
-#endif
             }
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) k = max(k, __shfl_xor_sync(0xffffffffu, k, off));
