@@ -42,6 +42,10 @@ WORKLOADS = {
                label="llama 6L d768 target + 1-layer draft, exact two-token verify, batch 1, 16-token prompt, 128 tokens"),
     "c3": dict(cfg=mc.gpt2_117m, prompt=64, decode=256, n_seq=256, sharded=True, kind="f16", bpw=2.0,
                label="gpt2-117M shape 12L d768 vocab50257 ctx1024 fp16, 256 independent sequences sharded over the GPUs, 64-token prompts, 256 greedy steps"),
+    # profiling aid: the c3 shape truncated to 4 layers and 512 positions (1.6 GB of KV cache), decode at context ~450
+    "c3long": dict(cfg=lambda: dataclasses.replace(mc.gpt2_117m(max_seq=512), nLayer=4, name="gpt2-117m-4l"), prompt=448, decode=16, n_seq=256,
+                   sharded=True, kind="f16", bpw=2.0,
+                   label="gpt2-117M widths, 4 layers, ctx512, 256 sequences, 448-token prompts, 16 greedy steps (attention at long context)"),
     "c5": dict(cfg=mc.llama3_8b, prompt=512, decode=256, n_seq=64, kind="bf16", bpw=2.0, device_weights=True, tp=True,
                label="llama-3-8B shape 32L d4096 GQA 32/8 hd128 vocab128256 ctx1024 bf16, 64 sequences, 512-token prompts, 256 greedy steps, tensor parallel over the GPUs (sum after Wo and W2 over peer memory)"),
     "c4q8": dict(cfg=mc.llama_1b, prompt=128, decode=256, n_seq=1, kind="q8_0", bpw=34.0 / 32, device_weights=True,
