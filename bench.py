@@ -16,6 +16,7 @@ a K-sliced GEMM, the clearing of its output), which makes it the command the pro
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import shutil
