@@ -30,7 +30,8 @@ def test_tp_shard_shapes():
 
 
 @pytest.mark.gpu
-def test_tensor_parallel_two_gpus_matches_oracle():
+@pytest.mark.parametrize("case", ["small", "wide_bf16"])
+def test_tensor_parallel_two_gpus_matches_oracle(case):
     import torch
 
     if torch.cuda.device_count() < 2:
@@ -38,10 +39,10 @@ def test_tensor_parallel_two_gpus_matches_oracle():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", ESP_TP_CASE=case)
     res = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
          "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py")],
         capture_output=True, text=True, env=env, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    assert "tensor parallel x2 ok" in res.stdout
+    assert f"tensor parallel x2 ok ({case})" in res.stdout
