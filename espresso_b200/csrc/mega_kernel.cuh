@@ -810,13 +810,13 @@ struct MegaKvRound {
     uint2 vreg[16];
 };
 
-template <int HD>
+template <int HD, int NW = kMegaConsumerWarps>  // NW = warps that share one query (position t belongs to warp t % NW)
 __device__ __forceinline__ void mega_kv_load(MegaKvRound<HD>& r, const __half* K, const __half* V, int base, int n_cached, int warp, int lane) {
     constexpr int cpl = HD / 32, KV4 = HD / 32;
     const int sub = lane & 3, tl = lane >> 2;
 #pragma unroll
     for (int st = 0; st < 2; st++) {
-        const int t = base + warp + kMegaConsumerWarps * (st * 8 + tl);
+        const int t = base + warp + NW * (st * 8 + tl);
 #pragma unroll
         for (int c = 0; c < KV4; c++) {
             r.kreg[st][c] = make_uint4(0, 0, 0, 0);
@@ -825,7 +825,7 @@ __device__ __forceinline__ void mega_kv_load(MegaKvRound<HD>& r, const __half* K
     }
 #pragma unroll
     for (int j = 0; j < 16; j++) {
-        const int t = base + warp + kMegaConsumerWarps * j;
+        const int t = base + warp + NW * j;
         r.vreg[j] = make_uint2(0, 0);
         if (t < n_cached) {
             const __half* vr = V + (size_t)t * HD + lane * cpl;
@@ -836,12 +836,15 @@ __device__ __forceinline__ void mega_kv_load(MegaKvRound<HD>& r, const __half* K
     }
 }
 
-// With NP positions per pass the call serves query `qi`: it sees the n_cached cached positions and the new positions
-// 0 .. qi, whose keys and values are rows of s.kn / s.vn; its context lands in position qi of the staged s.ctx.
+// With NP positions per pass the consumer warps split into NP teams of NW = 16 / NP warps, one team per query: query qi
+// sees the n_cached cached positions and the new positions 0 .. qi, whose keys and values are rows of s.kn / s.vn; its
+// context lands in position qi of the staged s.ctx.  The teams run side by side (each reads the cached rows itself).
 template <int HD, int NP = 1, int QCTX = 0, class WaitQ>  // QCTX: 0 = fp16 context staging, 1 = int8 digits
-__device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShared& s, const MegaShare& w, const ModelDims& m, const KvLayout& kv, int layer, int n_cached, int qi,
+__device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShared& s, const MegaShare& w, const ModelDims& m, const KvLayout& kv, int layer, int n_cached,
                                                WaitQ wait_q) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int NW = kMegaConsumerWarps / NP;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int qi = (tid >> 5) / NW, warp = (tid >> 5) - qi * NW;  // this warp's query and its place in the team
     constexpr int cpl = HD / 32, KV4 = HD / 32;
     const int visible = n_cached + 1;
     const __half* K = kv.k + kv.offset(m, layer, 0, w.kvh, 0);
@@ -849,19 +852,19 @@ __device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShar
     const float* qs = s.qs + qi * HD;
     const float scale = 1.0f / sqrtf((float)HD);
     const int sub = lane & 3, tl = lane >> 2;
-    constexpr int kRound = kMegaConsumerWarps * 16;  // positions per round
+    constexpr int kRound = NW * 16;  // positions per round of a team
     float m_w = -INFINITY, l_w = 0.f;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int base = 0; base < visible - 1 || base == 0; base += kRound) {
         // cached rows of this round (the newest position is not in the cache: its key and value come with the query)
         MegaKvRound<HD> cur;
-        mega_kv_load<HD>(cur, K, V, base, visible - 1, warp, lane);
+        mega_kv_load<HD, NW>(cur, K, V, base, visible - 1, warp, lane);
         if (base == 0) wait_q();  // the loads above are in flight while the query is awaited
         float sc[2];
         float mx = -INFINITY;
 #pragma unroll
         for (int st = 0; st < 2; st++) {
-            const int t = base + warp + kMegaConsumerWarps * (st * 8 + tl);
+            const int t = base + warp + NW * (st * 8 + tl);
             float dot = 0.f;
 #pragma unroll
             for (int c = 0; c < KV4; c++) {
@@ -904,7 +907,7 @@ __device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShar
     // the new positions: keys and values from shared memory, each handled by one warp as a round of a single position
 #pragma unroll
     for (int j = 0; j < NP; j++) {
-        if (j <= qi && warp == (n_cached + j) % kMegaConsumerWarps) {
+        if (j <= qi && warp == (n_cached + j) % NW) {
             const __half* kn = s.kn + j * HD;
             const __half* vn = s.vn + j * HD;
             float dot = 0.f;
@@ -921,27 +924,29 @@ __device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShar
             m_w = m_new;
         }
     }
-    // merge the per-warp partial results (a warp that saw no position carries max = -inf, sum = 0)
+    // merge the per-warp partial results of every team (a warp that saw no position carries max = -inf, sum = 0)
+    const int gw = tid >> 5;  // warp index among all consumers
 #pragma unroll
     for (int c = 0; c < 4; c++)
-        if (c < cpl) s.part[warp * HD + lane * cpl + c] = acc[c];
-    if (lane == 0) { s.red[warp] = m_w; s.red[kMegaConsumerWarps + warp] = l_w; }
+        if (c < cpl) s.part[gw * HD + lane * cpl + c] = acc[c];
+    if (lane == 0) { s.red[gw] = m_w; s.red[kMegaConsumerWarps + gw] = l_w; }
     consumer_sync();
-    if (tid < HD) {
+    if (tid < NP * HD) {
+        const int qq = tid / HD, ch = tid - qq * HD;  // (whole warps per query: HD is a multiple of 32)
         float gm = -INFINITY;
 #pragma unroll
-        for (int x = 0; x < kMegaConsumerWarps; x++) gm = fmaxf(gm, s.red[x]);
+        for (int x = 0; x < NW; x++) gm = fmaxf(gm, s.red[qq * NW + x]);
         float num = 0.f, den = 0.f;
 #pragma unroll
-        for (int x = 0; x < kMegaConsumerWarps; x++) {
-            const float f = s.red[x] == -INFINITY ? 0.f : __expf(s.red[x] - gm);
-            num = fmaf(s.part[x * HD + tid], f, num);
-            den = fmaf(s.red[kMegaConsumerWarps + x], f, den);
+        for (int x = 0; x < NW; x++) {
+            const float f = s.red[qq * NW + x] == -INFINITY ? 0.f : __expf(s.red[qq * NW + x] - gm);
+            num = fmaf(s.part[(qq * NW + x) * HD + ch], f, num);
+            den = fmaf(s.red[kMegaConsumerWarps + qq * NW + x], f, den);
         }
-        // the staged operand of the Wo products (whole warps come here: HD is a multiple of 32)
+        // the staged operand of the Wo products
         const float cv = den > 0.f ? __fdividef(num, den) : 0.f;
-        if constexpr (QCTX != 0) qx_store_elem(reinterpret_cast<uint8_t*>(s.ctx), reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s.ctx) + xa_bytes(HD)), tid, cv);
-        else xa_store<NP>(reinterpret_cast<__half*>(s.ctx), tid, cv, qi);
+        if constexpr (QCTX != 0) qx_store_elem(reinterpret_cast<uint8_t*>(s.ctx), reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s.ctx) + xa_bytes(HD)), ch, cv);
+        else xa_store<NP>(reinterpret_cast<__half*>(s.ctx), ch, cv, qq);
     }
     consumer_sync();
 }
@@ -1204,7 +1209,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     stamp(step);
                     // ---- S2: attention of this CTA's head (the cached K/V rows are requested before the query is awaited)
                     FINE();
-                    mega_attention<HD, 1, WT == WT_Q8_0 ? 1 : 0>(a, s, w, m, a.kv, l, pos, 0, [&]() {
+                    mega_attention<HD, 1, WT == WT_Q8_0 ? 1 : 0>(a, s, w, m, a.kv, l, pos, [&]() {
                         // q of this CTA's head, k and v of the KV head: pairs in the order S1 published them
                         FINE();
                         if (tid < 3 * half) {

@@ -304,9 +304,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                         }
                     }
                 }
-                // ---- S2: attention of this CTA's head, one call per query (the cached rows of the first call are requested
-                // before the queries are awaited; the second call finds them in L2)
-                mega_attention<HD, NP, 0>(a, s, w, md, kv, l, pos0, 0, [&]() {
+                // ---- S2: attention of this CTA's head: the consumer warps split into one team per query (the cached rows are
+                // requested before the queries are awaited)
+                mega_attention<HD, NP, 0>(a, s, w, md, kv, l, pos0, [&]() {
                     if (tid < NP * 3 * half) {
                         const int q = tid / (3 * half), r = tid - q * 3 * half;
                         const int section = r / half, idx = r - section * half;
@@ -329,7 +329,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_spec_mega(const SpecArgs sa
                     release_pending();  // the q/k/v chunk
                     consumer_sync();
                 });
-                mega_attention<HD, NP, 0>(a, s, w, md, kv, l, pos0, 1, [&]() {});
                 // ---- rows [blk*rpb, ...) of Wo restricted to this head's columns: one contribution per position to the
                 // counted sum of every row (head 0 also carries the residual)
                 for (int r0 = 0; r0 < p.rpb; r0 += p.s2_rpc) {
