@@ -413,10 +413,14 @@ def measure(args, wl: dict, rank: int, local_rank: int, world: int, steps: int, 
                     eng.rollback(cp)  # positions return to the end of the prompt; KV slots are simply overwritten
                 else:
                     prefill()
+                if tp:
+                    eng.tp_sum_stats()  # (clears the counters: what follows covers the decode steps only)
                 toks, ms = eng.decode(n_decode, n_seq)
                 assert all(len(t) == n_decode for t in toks) or cfg.architecture == "gpt2"
                 step_ms.append(ms)
                 launches += eng.timings()["kernel_launches"]
+                if tp:
+                    extra["tp_sum"] = eng.tp_sum_stats()
             barrier()
         else:
             # ---- two-token speculative loop (one device-driven launch when draft and target share their widths, else
@@ -712,6 +716,8 @@ def main() -> None:
                 L = w2["cfg"]().nLayer
                 entry["all_reduce"] = {"path": "peer memory (k_tp_sum_peers)" if world > 1 and not os.environ.get("ESP_CUDA_TP_NCCL_ONLY") else ("NCCL" if world > 1 else "none (one GPU)"),
                                        "per_decode_step": 2 * L if world > 1 else 0, "bytes_each": w2["n_seq"] * w2["cfg"]().dModel * 4}
+                if "tp_sum" in m["extra"]:  # rank 0's kernel k_tp_sum_peers during the decode steps: arrival -> last sum, and the wait for the peers in it
+                    entry["all_reduce"].update(mean_us=m["extra"]["tp_sum"]["mean_us"], mean_wait_for_peers_us=m["extra"]["tp_sum"]["mean_wait_us"])
                 entry["matches_single_gpu_engine"] = tp_matches_single_gpu(rank, local_rank, world)
             line[key] = entry
 

@@ -32,8 +32,8 @@ struct PrepArgs {
     const float* b;
     uint16_t* dst;            // [rows][K] fp16/bf16
     int bf16;
-    float* zero[3];           // optional fp32 rows to clear ([rows][zero_n[i]]): outputs that K-sliced products add into
-    int zero_n[3];
+    float* zero[4];           // optional fp32 rows to clear ([rows][zero_n[i]]): outputs that K-sliced products add into
+    int zero_n[4];
 };
 
 // One CTA per row.  Rows of up to 8192 elements are held in registers (one global read, 16-byte accesses); longer
@@ -65,12 +65,13 @@ __global__ void __launch_bounds__(kThreads) k_prep_rows(const PrepArgs p) {
             pre[i] = idx < K / 4 ? reinterpret_cast<const float4*>(src)[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
-    if (!row_active) return;
-    for (int z = 0; z < 3; z++)
+    // (inactive rows are cleared too: a tensor-parallel sum reads every row of a partial buffer)
+    for (int z = 0; z < 4; z++)
         if (p.zero[z]) {
             float4* zr = reinterpret_cast<float4*>(p.zero[z] + (size_t)r * p.zero_n[z]);  // row lengths are multiples of 16
             for (int k = threadIdx.x; k < p.zero_n[z] / 4; k += kThreads) zr[k] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
+    if (!row_active) return;
     if (fast) {
         const int nvec = K / 4;
         float4 v[kVec];

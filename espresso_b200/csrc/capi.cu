@@ -378,6 +378,11 @@ int32_t esp_cuda_debug_dump(esp_cuda_engine* engine, int32_t stage, float* out, 
 const char* esp_cuda_last_error_string(void) { return esp::last_error_cstr(); }
 void esp_cuda_set_force_failure(int32_t enabled) { esp::set_force_failure(enabled); }
 int32_t esp_cuda_set_wait_limit(esp_cuda_engine* engine, uint32_t spins) { ESP_GUARD(engine); return engine->impl.set_wait_limit(spins); }
+int32_t esp_cuda_tp_sum_stats(esp_cuda_engine* engine, uint64_t* out3) {
+    ESP_GUARD(engine);
+    if (!out3) return fail(ESP_CUDA_ERR_INVALID_ARGUMENT, "tp_sum_stats: null output");
+    return engine->impl.tp_sum_stats(reinterpret_cast<unsigned long long*>(out3));
+}
 int32_t esp_cuda_live_engine_count(void) { return g_live_engines.load(); }
 const char* esp_cuda_version(void) { return "espresso-cuda 0.1 (sm_100a)"; }
 

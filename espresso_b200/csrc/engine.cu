@@ -1392,7 +1392,8 @@ struct TpSumArgs {
     unsigned int* peer_flags[8]; // every rank's arrival flags
     unsigned int* my_flags;
     unsigned int* epoch;         // [0] completed all-reduces, [1] CTA ticket (local)
-    float* out;
+    unsigned long long* stats;   // [0] all-reduces, [1] ns from this rank's arrival to its last sum, [2] ns of [1] spent waiting for the peers, [3] scratch
+    float* out;                  // the residual stream: out += sum of the partials
     int world, rank, count4;
     int* error;
 };
@@ -1419,6 +1420,11 @@ __global__ void __launch_bounds__(256) k_tp_sum_peers(const TpSumArgs a) {
     __syncthreads();
     const unsigned int epoch = s_epoch;
     const int p = threadIdx.x;
+    unsigned long long t0 = 0;
+    if (blockIdx.x == 0 && p == 0) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        a.stats[3] = t0;
+    }
     if (p < a.world && p != a.rank) {
         if (blockIdx.x == 0) {
             __threadfence_system();
@@ -1433,12 +1439,24 @@ __global__ void __launch_bounds__(256) k_tp_sum_peers(const TpSumArgs a) {
         }
     }
     __syncthreads();
+    if (blockIdx.x == 0 && p == 0) {
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        atomicAdd(a.stats + 2, t1 - t0);
+    }
+    // Every rank's 16 bytes are requested before the first addition: a peer load is a round trip over NVLink of a few
+    // microseconds, and loads issued one after the other made an 8-rank sum take seven of them per element.
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < a.count4; i += gridDim.x * blockDim.x) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-        for (int r = 0; r < a.world; r++) {
-            const float4 v = r == a.rank ? __ldcg(reinterpret_cast<const float4*>(a.partial[r]) + i) : ld_peer_v4(a.partial[r] + (size_t)i * 4);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        float4 v[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < a.world) v[r] = r == a.rank ? __ldcg(reinterpret_cast<const float4*>(a.partial[r]) + i) : ld_peer_v4(a.partial[r] + (size_t)i * 4);
+        }
+        float4 acc = reinterpret_cast<const float4*>(a.out)[i];  // the residual, then rank order: the same sum, bit for bit, on every rank
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            if (r < a.world) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
         }
         reinterpret_cast<float4*>(a.out)[i] = acc;
     }
@@ -1446,11 +1464,48 @@ __global__ void __launch_bounds__(256) k_tp_sum_peers(const TpSumArgs a) {
     if (threadIdx.x == 0) {
         const unsigned int t = atomicAdd(a.epoch + 1, 1u);
         if (t == gridDim.x - 1) {  // last CTA: this all-reduce is complete on this rank
+            __threadfence();
+            unsigned long long t2;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t2));
+            atomicAdd(a.stats + 1, t2 - *reinterpret_cast<volatile unsigned long long*>(a.stats + 3));
+            atomicAdd(a.stats, 1ull);
             a.epoch[1] = 0u;
             *reinterpret_cast<volatile unsigned int*>(a.epoch) = epoch;
             __threadfence();
         }
     }
+}
+
+// SiLU(gate) * up over fp32 rows -> the 16-bit operand rows of the W2 product.  Used where the gate and up products are
+// cut along K (a narrow tensor-parallel shard), so that their sums are complete only after the product kernel.
+struct SwigluArgs {
+    const float* gate;  // [rows][hidden]
+    const float* up;
+    uint16_t* dst;      // [rows][hidden]
+    float* debug;       // optional fp32 capture of row 0
+    int hidden, n4, bf16;
+};
+__global__ void __launch_bounds__(256) k_swiglu_rows(const SwigluArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < a.n4; i += gridDim.x * blockDim.x) {
+        const float4 g = __ldcg(reinterpret_cast<const float4*>(a.gate) + i), u = __ldcg(reinterpret_cast<const float4*>(a.up) + i);
+        const float v0 = silu_fast(g.x) * u.x, v1 = silu_fast(g.y) * u.y, v2 = silu_fast(g.z) * u.z, v3 = silu_fast(g.w) * u.w;
+        reinterpret_cast<uint2*>(a.dst)[i] = make_uint2(pack16x2(v0, v1, a.bf16), pack16x2(v2, v3, a.bf16));
+        if (a.debug && 4 * i < a.hidden) *reinterpret_cast<float4*>(a.debug + 4 * i) = make_float4(v0, v1, v2, v3);
+    }
+}
+
+// {all-reduces over peer memory, ns from arrival to the last sum, ns of that spent waiting for the peers} since the
+// previous call (zeros when the group uses NCCL).
+int32_t Engine::tp_sum_stats(unsigned long long* out3) {
+    out3[0] = out3[1] = out3[2] = 0;
+    if (!tp_peer_ready_ || !tp_stats_) return ESP_CUDA_OK;
+    ESP_CUDA_TRY(cudaSetDevice(cfg_.device));
+    ESP_CUDA_TRY(cudaStreamSynchronize(stream_));
+    ESP_CUDA_TRY(cudaMemcpy(out3, tp_stats_, 3 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    ESP_CUDA_TRY(cudaMemset(tp_stats_, 0, 3 * sizeof(unsigned long long)));
+    return ESP_CUDA_OK;
 }
 
 float* Engine::tp_current_partial() const {
@@ -1474,6 +1529,7 @@ int32_t Engine::tp_peer_setup() {
     if (cudaMalloc(reinterpret_cast<void**>(&tp_block_), block_bytes) != cudaSuccess) { cudaGetLastError(); tp_block_ = nullptr; ok = false; }
     if (ok && cudaMemset(tp_block_, 0, block_bytes) != cudaSuccess) { cudaGetLastError(); ok = false; }
     if (ok && dev_alloc(owned_, &tp_epoch_, 2) != ESP_CUDA_OK) ok = false;
+    if (ok && dev_alloc(owned_, &tp_stats_, 4) != ESP_CUDA_OK) ok = false;
     if (ok && cudaIpcGetMemHandle(&mine, tp_block_) != cudaSuccess) { cudaGetLastError(); ok = false; }
     // exchange of the handles (a rank that failed sends zeros; nobody maps anything unless every rank voted "ok")
     uint8_t* d_handles = nullptr;
@@ -1527,11 +1583,12 @@ int32_t Engine::tp_sum_peers(float* out, int rows, cudaStream_t s) {
     }
     a.my_flags = a.peer_flags[tp_rank_];
     a.epoch = tp_epoch_;
+    a.stats = tp_stats_;
     a.out = out;
     a.world = tp_size_; a.rank = tp_rank_;
     a.count4 = rows * m_.d_model / 4;
     a.error = d_tc_error_;
-    const int grid = std::max(1, std::min(sm_count_, (a.count4 + 1023) / 1024));
+    const int grid = std::max(1, std::min(4 * sm_count_, (a.count4 + 255) / 256));  // one element per thread up to four CTAs per SM
     ESP_CUDA_TRY(launch_pdl(k_tp_sum_peers, dim3(grid), dim3(256), 0, s, a));
     tp_parity_ ^= 1;
     return ESP_CUDA_OK;
@@ -1636,7 +1693,8 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
     float* dbg = debug_layer_ >= 0 ? d_debug_ : nullptr;
     const int q = m_.q_dim, kv = m_.kv_dim, d = m_.d_model, h = m_.hidden;
     auto tiles_of = [](int M) { return (M + kTcHalf - 1) / kTcHalf; };
-    auto prep = [&](const float* src, int K, int norm, const float* g, const float* b, uint16_t* dst, bool from_emb, bool zero_qkv) -> int32_t {
+    auto prep = [&](const float* src, int K, int norm, const float* g, const float* b, uint16_t* dst, bool from_emb, bool zero_qkv, bool zero_ffn = false,
+                    float* zero_partial = nullptr) -> int32_t {
         PrepArgs p{};
         p.m = m_; p.rs = rs_; p.src = src; p.hidden_out = act_.hidden; p.K = K; p.norm = norm; p.g = g; p.b = b; p.dst = dst; p.bf16 = tc_bf16_;
         p.from_embedding = from_emb ? 1 : 0;
@@ -1651,6 +1709,11 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
             p.zero[1] = kraw_; p.zero_n[1] = kv;
             p.zero[2] = vraw_; p.zero_n[2] = kv;
         }
+        if (zero_ffn) {
+            p.zero[0] = act_.act; p.zero_n[0] = h;
+            p.zero[1] = up_; p.zero_n[1] = h;
+        }
+        if (zero_partial) { p.zero[3] = zero_partial; p.zero_n[3] = d; }
         ESP_CUDA_TRY(launch_pdl(k_prep_rows, dim3(rows), dim3(kThreads), 0, s, p));
         launches++;
         return ESP_CUDA_OK;
@@ -1688,6 +1751,13 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
         if (tp_size_ <= 1) return gemm(plan, false, {{&W, act_.hidden, d, bias}}, xbuf, TC_RESIDUAL, nullptr, 0, nullptr);
         int32_t prc;
         float* partial = tp_current_partial();
+        if (tp_peer_ready_) {
+            // peer-memory sum: every rank's partial is the bare product (rank 0's carries the bias), cleared by the norm
+            // kernel before it where K slices add into it; the sum kernel adds the partials to the residual stream
+            if ((prc = gemm(plan, false, {{&W, partial, d, tp_rank_ == 0 ? bias : nullptr}}, xbuf, TC_STORE, nullptr, 0, nullptr))) return prc;
+            launches++;
+            return tp_sum_peers(act_.hidden, rows, s);
+        }
         if (tp_rank_ == 0) {
             ESP_CUDA_TRY(cudaMemcpyAsync(partial, act_.hidden, sizeof(float) * (size_t)rows * d, cudaMemcpyDeviceToDevice, s));
             if ((prc = gemm(plan, false, {{&W, partial, d, bias}}, xbuf, TC_RESIDUAL, nullptr, 0, nullptr))) return prc;
@@ -1695,7 +1765,6 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
             if (plan.splits > 1) ESP_CUDA_TRY(cudaMemsetAsync(partial, 0, sizeof(float) * (size_t)rows * d, s));
             if ((prc = gemm(plan, false, {{&W, partial, d, nullptr}}, xbuf, TC_STORE, nullptr, 0, nullptr))) return prc;
         }
-        if (tp_peer_ready_) { launches++; return tp_sum_peers(act_.hidden, rows, s); }
         return all_reduce(partial, act_.hidden, (size_t)rows * d, true, s);
     };
     auto copy_dbg = [&](const float* src, int offset, int n) {
@@ -1703,16 +1772,25 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
     };
     // many (row, head) pairs: one warp each; few rows with long contexts: the split-KV kernel of the GEMV path
     const bool att_ok_hd = m_.head_dim == 32 || m_.head_dim == 64 || m_.head_dim == 128;
-    const bool att_rows = att_ok_hd && (long long)rows * m_.n_head >= 4LL * sm_count_;
+    // (a tensor-parallel rank holds 1/size of the heads: the choice follows the whole model's count, so that the ranks of a
+    // group keep the kernel a single GPU would use)
+    const bool att_rows = att_ok_hd && (long long)rows * m_.n_head * std::max(1, tp_size_) >= 4LL * sm_count_;
     int32_t rc;
     if (mode & STEP_FORWARD) {
         const TcPlan plan_qkv = tc_plan(tiles_of(q) + 2 * tiles_of(kv), rows, d / kTcBlockK, true, false, sm_count_);
         const TcPlan plan_up = tc_plan(tiles_of(h), rows, d / kTcBlockK, false, !gpt2, sm_count_);
+        // The fused gate/up product (activation in the epilogue) cannot be cut along K.  A narrow tensor-parallel shard
+        // would leave most SMs without a weight tile, and the product would take as long as the whole matrix does on
+        // one GPU; there the two matrices run as a K-sliced grouped product into fp32 rows, and a small kernel applies
+        // SiLU(gate) * up.
+        const bool split_up = !gpt2 && tp_size_ > 1 && 2 * tiles_of(h) * ((rows + kTcBatch - 1) / kTcBatch) <= sm_count_ && (h & 3) == 0;
+        const TcPlan plan_up2 = tc_plan(2 * tiles_of(h), rows, d / kTcBlockK, true, false, sm_count_);
         for (int l = 0; l < m_.n_layer; l++) {
             const std::string pre = "layers/" + std::to_string(l) + "/";
             const LayerWeights lw = layer_weights(l);
             const bool cap = dbg && l == debug_layer_;
-            if ((rc = prep(l == 0 ? nullptr : act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, lw.norm1_g, lw.norm1_b, xh_d_, l == 0, plan_qkv.splits > 1)))
+            if ((rc = prep(l == 0 ? nullptr : act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, lw.norm1_g, lw.norm1_b, xh_d_, l == 0, plan_qkv.splits > 1, false,
+                           tp_peer_ready_ ? tp_current_partial() : nullptr)))
                 return rc;
             if ((rc = gemm(plan_qkv, false,
                            {{&tensors_.at(pre + "wq"), act_.q, q, lw.bq}, {&tensors_.at(pre + "wk"), kraw_, kv, lw.bk}, {&tensors_.at(pre + "wv"), vraw_, kv, lw.bv}},
@@ -1761,11 +1839,21 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
             }
             if ((rc = project(tensors_.at(pre + "wo"), xh_q_, lw.bo))) return rc;
             if (cap) copy_dbg(act_.hidden, 2 * q + 2 * kv, d);
-            if ((rc = prep(act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, lw.norm2_g, lw.norm2_b, xh_d_, false, false))) return rc;
+            if ((rc = prep(act_.hidden, d, gpt2 ? NORM_LAYER : NORM_RMS, lw.norm2_g, lw.norm2_b, xh_d_, false, false, split_up && plan_up2.splits > 1,
+                           tp_peer_ready_ ? tp_current_partial() : nullptr)))
+                return rc;
             // up projection with the activation in the epilogue: GELU(w1 x + b1), or SiLU(w1 x) * (w3 x) from two accumulators
             float* capture = cap ? dbg + 2 * q + 2 * kv + d : nullptr;
             if (gpt2) {
                 if ((rc = gemm(plan_up, false, {{&tensors_.at(pre + "w1"), nullptr, 0, lw.b1}}, xh_d_, TC_GELU16, xh_h_, h, capture))) return rc;
+            } else if (split_up) {
+                if ((rc = gemm(plan_up2, false, {{&tensors_.at(pre + "w1"), act_.act, h, nullptr}, {&tensors_.at(pre + "w3"), up_, h, nullptr}}, xh_d_, TC_STORE,
+                               nullptr, 0, nullptr)))
+                    return rc;
+                SwigluArgs sa{};
+                sa.gate = act_.act; sa.up = up_; sa.dst = xh_h_; sa.debug = capture; sa.hidden = h; sa.n4 = rows * h / 4; sa.bf16 = tc_bf16_;
+                ESP_CUDA_TRY(launch_pdl(k_swiglu_rows, dim3(std::max(1, std::min(4 * sm_count_, (sa.n4 + 255) / 256))), dim3(256), 0, s, sa));
+                launches++;
             } else if ((rc = gemm(plan_up, true, {{&tensors_.at(pre + "w1"), nullptr, 0, nullptr}, {&tensors_.at(pre + "w3"), nullptr, 0, nullptr}}, xh_d_,
                                   TC_SWIGLU16, xh_h_, h, capture)))
                 return rc;

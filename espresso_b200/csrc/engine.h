@@ -76,6 +76,7 @@ public:
     int32_t debug_dump(int32_t stage, float* out, int32_t capacity);
     int32_t get_timings(esp_cuda_timings* out);
     int32_t set_wait_limit(uint32_t spins);
+    int32_t tp_sum_stats(unsigned long long* out3);
     // Exact two-token generation as one device-driven launch (spec_kernel.cuh).  `draft` must pass spec_compatible().
     // out_tokens[0 .. gen0) are already emitted (`current` is the newest of them, `prev` the token before it); the call
     // appends up to eff - gen0 more and fills stats[0..4] = tokens in total, passes, committed, accepted, stopped on EOS.
@@ -162,6 +163,7 @@ private:
     uint8_t* tp_peer_block_[8] = {};            // mapped exchange blocks, index = rank (own block at own index)
     size_t tp_buf_floats_ = 0;                  // floats per partial buffer
     unsigned int* tp_epoch_ = nullptr;          // [2] local: completed all-reduces, CTA ticket
+    unsigned long long* tp_stats_ = nullptr;    // [4] local: count and device time of the peer-memory all-reduces
     int tp_parity_ = 0;                         // partial buffer of the next all-reduce (host side, fixed at graph capture)
 
     // batched tensor-core path (rows >= kTcMinRows, 16-bit weights)

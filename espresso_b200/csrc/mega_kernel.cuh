@@ -803,7 +803,8 @@ __device__ __forceinline__ float mega_take_sum(const float* partial, int lg, int
 // a quarter of its K row with 16-byte vectors and the score is completed with two shuffles.  The probabilities are
 // then broadcast position by position while every lane accumulates its own channels of V.  The K and V rows of the
 // first round are requested by the caller's thread before the query is known (see `prefetch`), and the sixteen
-// per-warp (max, sum, ctx) triples are merged once.
+// per-warp (max, sum, ctx) triples are merged once, by all threads: a few lanes per output channel, combined with
+// shuffles (two warps walking all sixteen triples took 0.3 us longer per layer).
 template <int HD>
 struct MegaKvRound {
     uint4 kreg[2][HD / 32];
@@ -931,22 +932,42 @@ __device__ __forceinline__ void mega_attention(const MegaArgs& a, const MegaShar
         if (c < cpl) s.part[gw * HD + lane * cpl + c] = acc[c];
     if (lane == 0) { s.red[gw] = m_w; s.red[kMegaConsumerWarps + gw] = l_w; }
     consumer_sync();
-    if (tid < NP * HD) {
-        const int qq = tid / HD, ch = tid - qq * HD;  // (whole warps per query: HD is a multiple of 32)
-        float gm = -INFINITY;
+    {
+        // G lanes per output channel, each with cpl of the team's NW partial results; the lanes combine with shuffles
+        constexpr int G = kMegaConsumers / (NP * HD);
+        static_assert(G >= 1 && G <= 32 && G * cpl == NW, "merge layout");
+        const int o = tid / G, xr = tid - o * G;
+        const int qq = o / HD, ch = o - qq * HD;
+        float mv[cpl], gm = -INFINITY;
 #pragma unroll
-        for (int x = 0; x < NW; x++) gm = fmaxf(gm, s.red[qq * NW + x]);
+        for (int k = 0; k < cpl; k++) { mv[k] = s.red[qq * NW + xr * cpl + k]; gm = fmaxf(gm, mv[k]); }
+#pragma unroll
+        for (int off = G / 2; off > 0; off >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, off));
         float num = 0.f, den = 0.f;
 #pragma unroll
-        for (int x = 0; x < NW; x++) {
-            const float f = s.red[qq * NW + x] == -INFINITY ? 0.f : __expf(s.red[qq * NW + x] - gm);
-            num = fmaf(s.part[(qq * NW + x) * HD + ch], f, num);
-            den = fmaf(s.red[kMegaConsumerWarps + qq * NW + x], f, den);
+        for (int k = 0; k < cpl; k++) {
+            const int x = qq * NW + xr * cpl + k;
+            const float f = mv[k] == -INFINITY ? 0.f : __expf(mv[k] - gm);
+            num = fmaf(s.part[x * HD + ch], f, num);
+            den = fmaf(s.red[kMegaConsumerWarps + x], f, den);
+        }
+#pragma unroll
+        for (int off = G / 2; off > 0; off >>= 1) {
+            num += __shfl_xor_sync(0xffffffffu, num, off);
+            den += __shfl_xor_sync(0xffffffffu, den, off);
         }
         // the staged operand of the Wo products
         const float cv = den > 0.f ? __fdividef(num, den) : 0.f;
-        if constexpr (QCTX != 0) qx_store_elem(reinterpret_cast<uint8_t*>(s.ctx), reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s.ctx) + xa_bytes(HD)), ch, cv);
-        else xa_store<NP>(reinterpret_cast<__half*>(s.ctx), ch, cv, qq);
+        if constexpr (QCTX != 0) {
+            // int8 digit staging works on whole warps of consecutive elements: the channel values are gathered first
+            // (in the query's place: every warp is past its scores)
+            static_assert(NP == 1, "int8 context staging handles one position");
+            if (xr == 0) s.qs[ch] = cv;
+            consumer_sync();
+            if (tid < HD) qx_store_elem(reinterpret_cast<uint8_t*>(s.ctx), reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s.ctx) + xa_bytes(HD)), tid, s.qs[tid]);
+        } else {
+            if (xr == 0) xa_store<NP>(reinterpret_cast<__half*>(s.ctx), ch, cv, qq);
+        }
     }
     consumer_sync();
 }

@@ -109,6 +109,7 @@ SIGNATURES = {
     "esp_cuda_set_wait_limit": (C.c_int32, [_vp, C.c_uint32]),
     "esp_cuda_generate_steps": (C.c_int32, [_vp, _u32p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, _u32p, _i32p, C.POINTER(EspCudaGenerationResult)]),
     "esp_cuda_token_latencies": (C.c_int32, [_vp, _f32p, C.c_int32, _i32p]),
+    "esp_cuda_tp_sum_stats": (C.c_int32, [_vp, C.POINTER(C.c_uint64)]),
     "esp_cuda_live_engine_count": (C.c_int32, []),
     "esp_cuda_version": (C.c_char_p, []),
     "esp_cuda_dequantize": (C.c_int32, [C.c_int32, _vp, C.c_int64, _f32p, C.c_int32]),
@@ -379,6 +380,13 @@ class DecodeEngine:
         t = EspCudaTimings()
         _check(self._lib.esp_cuda_get_timings(self._h, C.byref(t)))
         return {k: getattr(t, k) for k, _ in EspCudaTimings._fields_}
+
+    def tp_sum_stats(self) -> dict:
+        """Peer-memory all-reduces of this rank since the previous call: count, mean device microseconds, mean wait for the peers."""
+        out = (C.c_uint64 * 3)()
+        _check(self._lib.esp_cuda_tp_sum_stats(self._h, out))
+        n = int(out[0])
+        return {"count": n, "mean_us": out[1] / n / 1e3 if n else 0.0, "mean_wait_us": out[2] / n / 1e3 if n else 0.0}
 
     def stage_trace(self, next_cta: int = 0) -> np.ndarray:
         """SM clock stamps of the persistent kernel's last token (see ``esp_cuda_stage_trace``)."""

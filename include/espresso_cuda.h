@@ -160,6 +160,9 @@ ESP_CUDA_API int32_t esp_cuda_load_tensor(esp_cuda_engine* engine, const char* n
  * sequence of decode calls. */
 ESP_CUDA_API int32_t esp_cuda_tp_unique_id(uint8_t* out, int32_t capacity);
 ESP_CUDA_API int32_t esp_cuda_tp_init(esp_cuda_engine* engine, const uint8_t* unique_id, int32_t nbytes);
+/* Diagnostics of the peer-memory all-reduce on this rank since the previous call: out3 = {all-reduces, device ns from
+ * this rank's arrival to its last sum, device ns of that spent waiting for the peers' arrivals}; zeros under NCCL. */
+ESP_CUDA_API int32_t esp_cuda_tp_sum_stats(esp_cuda_engine* engine, uint64_t* out3);
 
 /* Checks that every required tensor is present and prepares the decode state. */
 ESP_CUDA_API int32_t esp_cuda_finalize(esp_cuda_engine* engine);
