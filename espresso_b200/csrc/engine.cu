@@ -1781,11 +1781,11 @@ int32_t Engine::launch_step_tc(int rows, int mode, cudaStream_t s) {
     if (mode & STEP_FORWARD) {
         const TcPlan plan_qkv = tc_plan(tiles_of(q) + 2 * tiles_of(kv), rows, d / kTcBlockK, true, false, sm_count_);
         const TcPlan plan_up = tc_plan(tiles_of(h), rows, d / kTcBlockK, false, !gpt2, sm_count_);
-        // The fused gate/up product (activation in the epilogue) cannot be cut along K.  A narrow tensor-parallel shard
-        // would leave most SMs without a weight tile, and the product would take as long as the whole matrix does on
-        // one GPU; there the two matrices run as a K-sliced grouped product into fp32 rows, and a small kernel applies
-        // SiLU(gate) * up.
-        const bool split_up = !gpt2 && tp_size_ > 1 && 2 * tiles_of(h) * ((rows + kTcBatch - 1) / kTcBatch) <= sm_count_ && (h & 3) == 0;
+        // The fused gate/up product (activation in the epilogue) cannot be cut along K.  Where its weight tiles cover less
+        // than half of the SMs (a narrow tensor-parallel shard, a small model) the rest would idle while each CTA streams
+        // its tile at one SM's pace; there the two matrices run as a K-sliced grouped product into fp32 rows, and a small
+        // kernel applies SiLU(gate) * up.
+        const bool split_up = !gpt2 && 2 * tiles_of(h) * ((rows + kTcBatch - 1) / kTcBatch) <= sm_count_ && (h & 3) == 0;
         const TcPlan plan_up2 = tc_plan(2 * tiles_of(h), rows, d / kTcBlockK, true, false, sm_count_);
         for (int l = 0; l < m_.n_layer; l++) {
             const std::string pre = "layers/" + std::to_string(l) + "/";
