@@ -1205,25 +1205,29 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                     // CTA's W2 rows, hence the whole activation vector, hence every group CTA past its S2 of this layer.
                     for (int i0 = 0; i0 < w.s1_n; i0 += p.s1_ipc) {
                         const int n_items = min(p.s1_ipc, w.s1_n - i0);
+                        // A chunk holds at most 128 row pairs: one per thread.  Where the pair goes (matrix, RoPE entry,
+                        // exchange words, cache rows) does not depend on the products: worked out before them, it is off
+                        // the path between the last product and the words the other CTAs are waiting for.
+                        int kind = 0, row0 = 0, row1 = 0, idx = 0;
+                        float2 cs = make_float2(1.f, 0.f);
+                        unsigned long long* dst = my_qkv;
+                        __half* kv_row = nullptr;
+                        if (tid < n_items) {
+                            mega_s1_rows(m, p, w.kvh, w.s1_begin + i0 + tid, kind, row0, row1, idx);
+                            if (kind < 2) cs = s.rope[idx];
+                            dst = my_qkv + 2 * (w.s1_begin + i0 + tid);
+                            if (kind > 0) kv_row = (kind == 1 ? a.kv.k : a.kv.v) + a.kv.offset(m, l, 0, w.kvh, pos) - w.kvh * HD;
+                        }
                         float* sums = chunk_products(2 * n_items, d >> 5, s.xa, i0 + p.s1_ipc >= w.s1_n);
-                        for (int i = tid; i < n_items; i += kMegaConsumers) {
-                            int kind, row0, row1, idx;
-                            mega_s1_rows(m, p, w.kvh, w.s1_begin + i0 + i, kind, row0, row1, idx);
-                            float v0 = mega_take_sum(sums, lg_parts, 2 * i) * inv;
-                            float v1 = mega_take_sum(sums, lg_parts, 2 * i + 1) * inv;
-                            if (kind < 2) {
-                                const float2 cs = s.rope[idx];
-                                const float r0 = v0 * cs.x - v1 * cs.y, r1 = v0 * cs.y + v1 * cs.x;
-                                v0 = r0; v1 = r1;
-                            }
-                            unsigned long long* dst = my_qkv + 2 * (w.s1_begin + i0 + i);
-                            st_word(dst, tagged(v0, seq));
-                            st_word(dst + 1, tagged(v1, seq));
+                        if (tid < n_items) {
+                            float v0 = mega_take_sum(sums, lg_parts, 2 * tid) * inv;
+                            float v1 = mega_take_sum(sums, lg_parts, 2 * tid + 1) * inv;
+                            const float r0 = v0 * cs.x - v1 * cs.y, r1 = v0 * cs.y + v1 * cs.x;  // (cos, sin) = (1, 0) for a value pair
+                            st_word(dst, tagged(r0, seq));
+                            st_word(dst + 1, tagged(r1, seq));
                             if (kind > 0) {
-                                __half* base = kind == 1 ? a.kv.k : a.kv.v;
-                                const size_t off = a.kv.offset(m, l, 0, w.kvh, pos);
-                                base[off + (row0 - w.kvh * HD)] = __float2half_rn(v0);
-                                base[off + (row1 - w.kvh * HD)] = __float2half_rn(v1);
+                                kv_row[row0] = __float2half_rn(r0);
+                                kv_row[row1] = __float2half_rn(r1);
                             }
                         }
                     }
