@@ -1302,12 +1302,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 // every CTA past its W2 rows and so past this activation vector.
                 for (int j0 = 0; j0 < w.h_n; j0 += p.s3a_ipc) {
                     const int n_items = min(p.s3a_ipc, w.h_n - j0);
+                    // (one item per thread; its word's address is known before the products)
+                    unsigned long long* const dst = a.act_words + (p.act_wpc ? (size_t)blockIdx.x * p.act_wpc : (size_t)w.h_begin) + j0 + tid;
                     float* sums = chunk_products(2 * n_items, d >> 5, s.xa, j0 + p.s3a_ipc >= w.h_n);
-                    for (int j = tid; j < n_items; j += kMegaConsumers) {
-                        const float g = mega_take_sum(sums, lg_parts, 2 * j) * inv;
-                        const float u = mega_take_sum(sums, lg_parts, 2 * j + 1) * inv;
+                    if (tid < n_items) {
+                        const float g = mega_take_sum(sums, lg_parts, 2 * tid) * inv;
+                        const float u = mega_take_sum(sums, lg_parts, 2 * tid + 1) * inv;
                         // silu(g) = g * sigmoid(g) = 0.5 g (1 + tanh(g / 2))
-                        st_word(a.act_words + (p.act_wpc ? (size_t)blockIdx.x * p.act_wpc : (size_t)w.h_begin) + j0 + j, tagged(__fdividef(g, 1.0f + __expf(-g)) * u, seq));
+                        st_word(dst, tagged(__fdividef(g, 1.0f + __expf(-g)) * u, seq));
                     }
                 }
                 stamp(step);
@@ -1332,9 +1334,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) k_decode_mega(const MegaArgs 
                 stamp(step);
                 for (int r0 = 0; r0 < w.d_n; r0 += p.s3b_rpc) {
                     const int nr = min(p.s3b_rpc, w.d_n - r0);
+                    // (at most 256 rows per chunk: one per thread; residual and address are fetched before the products)
+                    const float res = tid < nr ? s.xmid[w.d_begin + r0 + tid] : 0.f;
+                    unsigned long long* const dst = a.x_words + w.d_begin + r0 + tid;
                     float* sums = chunk_products(nr, m.hidden >> 5, s.xa, r0 + p.s3b_rpc >= w.d_n);
-                    for (int r = tid; r < nr; r += kMegaConsumers)
-                        st_word(a.x_words + w.d_begin + r0 + r, tagged(mega_take_sum(sums, lg_parts, r) + s.xmid[w.d_begin + r0 + r], seq));
+                    if (tid < nr) st_word(dst, tagged(mega_take_sum(sums, lg_parts, tid) + res, seq));
                 }
                 stamp(step);
             }
