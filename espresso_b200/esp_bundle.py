@@ -461,20 +461,107 @@ def select_backend(capabilities: DeviceCapabilities, manifest: Manifest, request
     raise BundleError("noCompatibleBackend")
 
 
+def draft_environment(manifest: Manifest) -> dict:
+    """The variables the bundled runtime hands to the engine for a ``[draft]`` section
+    (Sources/ESPRuntime/ESPBundledRuntime.swift:169-177)."""
+    d = manifest.draft
+    if d is None:
+        return {}
+    return {
+        "ESPRESSO_BUNDLE_DRAFT_KIND": d.kind, "ESPRESSO_BUNDLE_DRAFT_HORIZON": str(d.horizon),
+        "ESPRESSO_BUNDLE_DRAFT_VERIFIER": d.verifier, "ESPRESSO_BUNDLE_DRAFT_ROLLBACK": d.rollback,
+        "ESPRESSO_BUNDLE_DRAFT_ARTIFACT_REF": d.artifact_ref, "ESPRESSO_BUNDLE_DRAFT_ACCEPTANCE_METRIC": d.acceptance_metric,
+    }
+
+
+@dataclass
+class ResolvedDraft:
+    model_dir: str                 # the descriptor's model_dir as written
+    tokenizer_dir: Optional[str]
+    model_id: Optional[str]
+    descriptor_path: str
+    weight_dir: str                # absolute directory of the draft model's weights
+    config: "object"               # its MultiModelConfig
+
+
+def _inside(path: str, root: str) -> bool:
+    return path == root or path.startswith(root + os.sep)
+
+
+def resolve_exact_two_token_draft(config, weight_dir: str, environment) -> Optional[ResolvedDraft]:
+    """Where the exact two-token draft of a model lives, or None when none is asked for
+    (``resolveExactTwoTokenDraft``, Sources/RealModelInference/RealModelInferenceEngine.swift:5324-5390).
+
+    ``ESPRESSO_BUNDLE_DRAFT_KIND`` must be ``exact_two_token``; a horizon, if given, must be 2;
+    ``ESPRESSO_BUNDLE_DRAFT_ARTIFACT_REF`` names a JSON descriptor relative to the bundle root (the parent of the weight
+    directory) and may not leave it; the descriptor's ``model_dir`` is relative to the weight directory and may not leave
+    that; the draft must be a llama model with the target's vocabulary.  Failures raise ``BundleError("runtimeFailure")``
+    with the reference's message."""
+    from .model_config import MultiModelConfig
+
+    def fail(msg: str):
+        return BundleError("runtimeFailure", msg)
+
+    if environment.get("ESPRESSO_BUNDLE_DRAFT_KIND") != "exact_two_token":
+        return None
+    raw_horizon = environment.get("ESPRESSO_BUNDLE_DRAFT_HORIZON")
+    if raw_horizon is not None:
+        try:
+            horizon = int(raw_horizon)
+        except ValueError:
+            horizon = None
+        if horizon != 2:
+            raise fail(f"exact two-token draft requires horizon == 2, got {raw_horizon}")
+    artifact_ref = environment.get("ESPRESSO_BUNDLE_DRAFT_ARTIFACT_REF")
+    if not artifact_ref:
+        raise fail("exact two-token draft requires ESPRESSO_BUNDLE_DRAFT_ARTIFACT_REF")
+    weight_root = os.path.normpath(os.path.abspath(weight_dir))
+    bundle_root = os.path.dirname(weight_root)
+    descriptor_path = os.path.normpath(os.path.join(bundle_root, artifact_ref))
+    if not _inside(descriptor_path, bundle_root):
+        raise fail(f"Draft artifact ref escapes bundle root: {artifact_ref}")
+    if not os.path.exists(descriptor_path):
+        raise fail(f"Draft artifact file is missing: {descriptor_path}")
+    try:
+        with open(descriptor_path) as f:
+            desc = json.load(f)
+        model_dir = desc["model_dir"]
+        if not isinstance(model_dir, str):
+            raise TypeError("model_dir must be a string")
+    except (OSError, ValueError, KeyError, TypeError) as e:
+        raise fail(f"Failed to decode draft descriptor {descriptor_path}: {e}")
+    if not model_dir:
+        raise fail("Draft descriptor is missing model_dir")
+    draft_dir = os.path.normpath(os.path.join(weight_root, model_dir))
+    if not _inside(draft_dir, weight_root):
+        raise fail(f"Draft model_dir escapes weights root: {model_dir}")
+    if not os.path.isdir(draft_dir):
+        raise fail(f"Weight directory does not exist: {draft_dir}")
+    try:
+        draft_config = MultiModelConfig.load(draft_dir)
+    except (OSError, ValueError, KeyError) as e:
+        raise fail(f"Failed to load draft metadata in {draft_dir}: {e}")
+    if draft_config.architecture != "llama":
+        raise fail("exact two-token draft currently supports llama draft models only")
+    if draft_config.vocab != config.vocab:
+        raise fail(f"draft/full vocab mismatch: draft={draft_config.vocab} full={config.vocab}")
+    return ResolvedDraft(model_dir, desc.get("tokenizer_dir"), desc.get("model_id"), descriptor_path, draft_dir, draft_config)
+
+
 def open_engines(archive: BundleArchive, max_batch: int = 1, device: int = 0, flags: int = 0):
     """``(target engine, draft engine or None, tokenizer)`` for a bundle whose selection is the ``cuda`` backend: the
-    weights directory feeds the engine, a ``[draft]`` section names the draft model's weight directory through the
-    parent of ``artifact_ref`` (the reference resolves the draft the same way, RealModelInferenceEngine.swift:5324-5390),
-    and the tokenizer files are searched in ``tokenizer/``."""
+    weights directory feeds the engine; a ``[draft]`` section becomes the variables of ``draft_environment`` and the
+    draft's weight directory is resolved from them as the reference does (``resolve_exact_two_token_draft``); the
+    tokenizer files are searched in ``tokenizer/``."""
     from . import runtime, tokenizers
     from .model_config import MultiModelConfig
 
+    cfg = MultiModelConfig.load(archive.weights_dir)
+    resolved = resolve_exact_two_token_draft(cfg, archive.weights_dir, draft_environment(archive.manifest))
     target = runtime.DecodeEngine.build(archive.weights_dir, max_batch=max_batch, device=device, flags=flags)
     draft = None
-    if archive.manifest.draft is not None:
-        draft_dir = os.path.dirname(archive.resolve_reference(archive.manifest.draft.artifact_ref))
-        draft = runtime.DecodeEngine.build(draft_dir, max_batch=1, device=device, flags=flags)
-    cfg = MultiModelConfig.load(archive.weights_dir)
+    if resolved is not None:
+        draft = runtime.DecodeEngine.build(resolved.weight_dir, max_batch=1, device=device, flags=flags)
     try:
         tokenizer = tokenizers.load_tokenizer(cfg.architecture, archive.tokenizer_dir)
     except FileNotFoundError:

@@ -1,5 +1,6 @@
 """`.esp` bundle contract: the reference's manifest tests (Tests/ESPBundleTests/ESPManifestTests.swift) restated, plus
 create / open / tamper detection and backend selection with the added `cuda` kind."""
+import dataclasses
 import json
 import os
 
@@ -164,6 +165,65 @@ def test_backend_and_profile_selection():
     assert eb.select_profile(full_manifest(context_target_tokens=256, supported_profiles=["decode_2"])) == "decode_2"
 
 
+def test_draft_descriptor_resolution_follows_the_reference(tmp_path):
+    """The layout of the reference's own test (RealModelInferenceTests.swift:252-311): the artifact ref is relative to the
+    bundle root, the descriptor's model_dir to the weight directory; then every way the resolution can fail."""
+    from espresso_b200.model_config import MultiModelConfig
+
+    cfg = MultiModelConfig("stories110m", 12, 12, 12, 768, 64, 2048, 32000, 256, 1e-5, 10000.0, None, "llama")
+    weights = tmp_path / "bundle" / "weights"
+    student = weights / "draft" / "student"
+    student.mkdir(parents=True)
+    dataclasses.replace(cfg, name="stories110m-stable-copy").save(str(student))
+    desc = weights / "draft" / "exact-two-token.json"
+    desc.write_text(json.dumps({"model_dir": "draft/student", "tokenizer_dir": "tokenizer", "model_id": "stories110m-stable-copy"}))
+    env = {"ESPRESSO_BUNDLE_DRAFT_KIND": "exact_two_token", "ESPRESSO_BUNDLE_DRAFT_HORIZON": "2",
+           "ESPRESSO_BUNDLE_DRAFT_ARTIFACT_REF": "weights/draft/exact-two-token.json"}
+    r = eb.resolve_exact_two_token_draft(cfg, str(weights), env)
+    assert r.weight_dir == str(student) and r.model_id == "stories110m-stable-copy" and r.config.nLayer == 12
+    assert r.descriptor_path == str(desc) and r.tokenizer_dir == "tokenizer"
+    # no draft asked for
+    assert eb.resolve_exact_two_token_draft(cfg, str(weights), {}) is None
+    assert eb.resolve_exact_two_token_draft(cfg, str(weights), dict(env, ESPRESSO_BUNDLE_DRAFT_KIND="multi_token")) is None
+    # the horizon is optional, but if present it is 2
+    assert eb.resolve_exact_two_token_draft(cfg, str(weights), {k: v for k, v in env.items() if "HORIZON" not in k}) is not None
+
+    def fails(environment, config=cfg, text=""):
+        with pytest.raises(eb.BundleError) as e:
+            eb.resolve_exact_two_token_draft(config, str(weights), environment)
+        assert e.value.kind == "runtimeFailure" and text in e.value.detail
+
+    fails(dict(env, ESPRESSO_BUNDLE_DRAFT_HORIZON="3"), text="horizon == 2, got 3")
+    fails(dict(env, ESPRESSO_BUNDLE_DRAFT_HORIZON="two"), text="horizon == 2")
+    fails({k: v for k, v in env.items() if "ARTIFACT" not in k}, text="requires ESPRESSO_BUNDLE_DRAFT_ARTIFACT_REF")
+    fails(dict(env, ESPRESSO_BUNDLE_DRAFT_ARTIFACT_REF=""), text="requires ESPRESSO_BUNDLE_DRAFT_ARTIFACT_REF")
+    fails(dict(env, ESPRESSO_BUNDLE_DRAFT_ARTIFACT_REF="../elsewhere.json"), text="escapes bundle root")
+    fails(dict(env, ESPRESSO_BUNDLE_DRAFT_ARTIFACT_REF="weights/draft/none.json"), text="is missing")
+    fails(env, config=dataclasses.replace(cfg, vocab=32001), text="draft=32000 full=32001")
+    desc.write_text("{not json")
+    fails(env, text="Failed to decode draft descriptor")
+    desc.write_text(json.dumps({"tokenizer_dir": "tokenizer"}))
+    fails(env, text="Failed to decode draft descriptor")
+    desc.write_text(json.dumps({"model_dir": ""}))
+    fails(env, text="missing model_dir")
+    desc.write_text(json.dumps({"model_dir": "../outside"}))
+    fails(env, text="escapes weights root")
+    desc.write_text(json.dumps({"model_dir": "draft/absent"}))
+    fails(env, text="does not exist")
+    desc.write_text(json.dumps({"model_dir": "draft/student"}))
+    dataclasses.replace(cfg, architecture="gpt2").save(str(student))
+    fails(env, text="llama draft models only")
+
+
+def test_draft_environment_of_a_manifest():
+    d = eb.DraftMetadata("exact_two_token", "exact", 2, "exact", "exact_replay", "weights/draft/exact-two-token.json", "accepted_future_tokens")
+    env = eb.draft_environment(full_manifest(draft=d))
+    assert env["ESPRESSO_BUNDLE_DRAFT_KIND"] == "exact_two_token" and env["ESPRESSO_BUNDLE_DRAFT_HORIZON"] == "2"
+    assert env["ESPRESSO_BUNDLE_DRAFT_ARTIFACT_REF"] == "weights/draft/exact-two-token.json"
+    assert env["ESPRESSO_BUNDLE_DRAFT_ROLLBACK"] == "exact_replay" and env["ESPRESSO_BUNDLE_DRAFT_ACCEPTANCE_METRIC"] == "accepted_future_tokens"
+    assert eb.draft_environment(full_manifest(draft=None)) == {}
+
+
 @pytest.mark.gpu
 def test_bundle_to_engines_with_two_token_draft(tmp_path, tmp_models):
     """A bundle with a [draft] section opens into a target and a draft engine; the exact two-token loop matches greedy."""
@@ -175,11 +235,13 @@ def test_bundle_to_engines_with_two_token_draft(tmp_path, tmp_models):
     cfg, dcfg = tiny_llama(vocab=96, max_seq=48, n_layer=2), tiny_llama(vocab=96, max_seq=48, n_layer=1)
     w = str(tmp_path / "weights_src")
     shutil.copytree(tmp_models(cfg), w)
-    shutil.copytree(tmp_models(dcfg, 1235), os.path.join(w, "draft"))
+    shutil.copytree(tmp_models(dcfg, 1235), os.path.join(w, "draft", "student"))
+    with open(os.path.join(w, "draft", "exact-two-token.json"), "w") as f:
+        json.dump({"model_dir": "draft/student", "tokenizer_dir": "tokenizer", "model_id": "student"}, f)
     t = tmp_path / "tok"
     t.mkdir()
     m = full_manifest(supported_backends=["cuda", "cpu-safe"], output_head=None, max_context=48, context_target_tokens=48,
-                      draft=eb.DraftMetadata("exact_two_token", "exact", 2, "exact", "exact_replay", "weights/draft/metadata.json", "accepted_future_tokens"))
+                      draft=eb.DraftMetadata("exact_two_token", "exact", 2, "exact", "exact_replay", "weights/draft/exact-two-token.json", "accepted_future_tokens"))
     archive = eb.BundleArchive.open(eb.BundleArchive.create(str(tmp_path / "m.esp"), m, w, str(t)).bundle_dir)
     assert eb.select_backend(eb.DeviceCapabilities(supports_cuda=True), archive.manifest).backend == "cuda"
     target, draft, tokenizer = eb.open_engines(archive)
